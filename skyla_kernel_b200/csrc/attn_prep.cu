@@ -1,0 +1,102 @@
+// Per-head preparation of a step's new tokens, one warp per (token, head):
+//   q, k heads: RMSNorm over the head with one [head_dim] weight shared by all
+//               heads (skyla-ref/src/ops.rs:8-11, model.rs:138-145), then
+//               rotate-half RoPE on the first n_rot elements at the token's
+//               absolute position (skyla-ref/src/rope.rs:59-68);
+//   q is written back in place, k and v go to the token's place in the paged
+//   cache (the reference's qkv_prep does the same into its flat cache,
+//   skyla-shaders/shaders/qkv_prep.comp:67-123).
+// Norm and rotation are optional (null weight / null table), so a mixer that
+// uses neither, or another position encoding applied elsewhere, can share it.
+// All arithmetic is 32-bit; cos/sin come from a table built once on the host.
+#include "common.cuh"
+using namespace skyla;
+SKYLA_EXPORT_ERROR_MESSAGE()
+
+namespace {
+constexpr int kWarps = 4;
+constexpr int kMaxHeadDim = 512;
+
+struct PrepArgs {
+  void* qkv; int64_t ld; int q_off, k_off, v_off;
+  int n_tokens, nq, nkv, hd;
+  const float* q_norm; const float* k_norm; float eps;
+  const float* cos_t; const float* sin_t; int n_rot;
+  const int32_t* tok_pos; const int32_t* tok_slot;
+  void* k_pool; void* v_pool; const int32_t* page_table; int max_pages; int page_size;
+};
+
+template <typename TA, typename TC>
+__global__ void __launch_bounds__(kWarps * 32) prep_kernel(PrepArgs a) {
+  extern __shared__ float smem[];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int head = blockIdx.x * kWarps + warp;
+  const int t = blockIdx.y;
+  const int n_heads = a.nq + 2 * a.nkv;
+  if (head >= n_heads) return;
+  float* u = smem + warp * a.hd;
+  const int hd = a.hd;
+  const bool is_q = head < a.nq, is_k = !is_q && head < a.nq + a.nkv;
+  const int kvh = is_q ? 0 : (is_k ? head - a.nq : head - a.nq - a.nkv);
+  TA* src = (TA*)a.qkv + (int64_t)t * a.ld +
+            (is_q ? a.q_off + head * hd : (is_k ? a.k_off : a.v_off) + kvh * hd);
+  const int pos = a.tok_pos[t];
+
+  TC* dst = nullptr;
+  if (!is_q) {
+    if (a.k_pool == nullptr) return;  // this run reads another entry's cache
+    const int page = a.page_table[(int64_t)a.tok_slot[t] * a.max_pages + pos / a.page_size];
+    TC* pool = (TC*)(is_k ? a.k_pool : a.v_pool);
+    dst = pool + (((int64_t)page * a.nkv + kvh) * a.page_size + pos % a.page_size) * hd;
+  }
+  if (!is_q && !is_k) {  // v: a copy
+    for (int e = lane; e < hd; e += 32) dst[e] = from_float<TC>(to_float(src[e]));
+    return;
+  }
+  const float* nw = is_q ? a.q_norm : a.k_norm;
+  float ss = 0.f;
+  for (int e = lane; e < hd; e += 32) {
+    const float v = to_float(src[e]);
+    u[e] = v;
+    ss = fmaf(v, v, ss);
+  }
+  if (nw != nullptr) {
+    ss = warp_sum(ss);
+    const float inv = 1.0f / sqrtf(ss / (float)hd + a.eps);
+    for (int e = lane; e < hd; e += 32) u[e] *= inv * nw[e];
+  }
+  __syncwarp();
+  const int half = a.n_rot / 2;
+  for (int e = lane; e < hd; e += 32) {
+    float v = u[e];
+    if (a.cos_t != nullptr && e < a.n_rot) {
+      const int i = e < half ? e : e - half;
+      const float c = a.cos_t[(int64_t)pos * half + i], s = a.sin_t[(int64_t)pos * half + i];
+      const float x0 = u[i], x1 = u[i + half];
+      v = e < half ? x0 * c - x1 * s : x0 * s + x1 * c;
+    }
+    if (is_q) src[e] = from_float<TA>(v);
+    else dst[e] = from_float<TC>(v);
+  }
+}
+}  // namespace
+
+extern "C" int skyla_qk_norm_rope_cache(
+    void* qkv, int act_dtype, int64_t ld, int q_off, int k_off, int v_off, int n_tokens, int nq,
+    int nkv, int hd, const float* q_norm, const float* k_norm, float eps, const float* cos_t,
+    const float* sin_t, int n_rot, const int32_t* tok_pos, const int32_t* tok_slot, void* k_pool,
+    void* v_pool, int cache_dtype, const int32_t* page_table, int max_pages, int page_size,
+    cudaStream_t stream) {
+  if (n_tokens <= 0) return kOk;
+  if (hd <= 0 || hd > kMaxHeadDim) return fail(kBadArgument, "qk_norm_rope_cache: head size %d is outside 1..%d", hd, kMaxHeadDim);
+  if (n_rot < 0 || n_rot > hd || n_rot % 2) return fail(kBadArgument, "qk_norm_rope_cache: rotary width %d does not fit head size %d", n_rot, hd);
+  if (n_tokens > 65535) return fail(kBadArgument, "qk_norm_rope_cache: %d tokens exceed the grid", n_tokens);
+  PrepArgs a{qkv, ld, q_off, k_off, v_off, n_tokens, nq, nkv, hd, q_norm, k_norm, eps, cos_t, sin_t,
+             n_rot, tok_pos, tok_slot, k_pool, v_pool, page_table, max_pages, page_size};
+  dim3 grid((nq + 2 * nkv + kWarps - 1) / kWarps, n_tokens);
+  const size_t smem = (size_t)kWarps * hd * sizeof(float);
+  SKYLA_DISPATCH(act_dtype, TA, SKYLA_DISPATCH(cache_dtype, TC, {
+    prep_kernel<TA, TC><<<grid, kWarps * 32, smem, stream>>>(a);
+  }););
+  return check_launch("qk_norm_rope_cache");
+}

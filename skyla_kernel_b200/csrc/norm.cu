@@ -1,0 +1,42 @@
+// RMSNorm over rows: r = 1/sqrt(mean(x^2)+eps); y = (x*r)*w, all in 32-bit
+// (skyla-ref/src/ops.rs:1-16; GPU twin skyla-shaders/shaders/rmsnorm.comp:22-51).
+// An optional row list turns it into "gather the wanted rows, then norm", which
+// is what the reference does with take_last before the output head
+// (skyla-engine/src/graph.rs:219-229).
+#include "common.cuh"
+using namespace skyla;
+SKYLA_EXPORT_ERROR_MESSAGE()
+
+template <typename TI, typename TO>
+__global__ void rmsnorm_kernel(const TI* __restrict__ x, int64_t ldx, const int32_t* __restrict__ rows,
+                               int width, const float* __restrict__ w, float eps,
+                               TO* __restrict__ out, int64_t ldo) {
+  __shared__ float scratch[32];
+  const int r = blockIdx.x;
+  const TI* xr = x + (int64_t)(rows ? rows[r] : r) * ldx;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    const float v = to_float(xr[i]);
+    ss = fmaf(v, v, ss);
+  }
+  ss = block_sum(ss, scratch);
+  const float inv = 1.0f / sqrtf(ss / (float)width + eps);
+  TO* o = out + (int64_t)r * ldo;
+  for (int i = threadIdx.x; i < width; i += blockDim.x)
+    o[i] = from_float<TO>(to_float(xr[i]) * inv * w[i]);
+}
+
+extern "C" int skyla_rmsnorm(const void* x, int x_dtype, int64_t ldx, const int32_t* rows,
+                             int n_rows, int width, const float* weight, float eps, void* out,
+                             int out_dtype, int64_t ldo, cudaStream_t stream) {
+  if (n_rows <= 0) return kOk;
+  if (width <= 0 || ldx < width || ldo < width)
+    return fail(kBadArgument, "rmsnorm: bad width %d or row stride", width);
+  // the block size depends on the width only, so a row's sum has one order whatever the batch
+  const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
+  SKYLA_DISPATCH(x_dtype, TI, SKYLA_DISPATCH(out_dtype, TO, {
+    rmsnorm_kernel<TI, TO><<<n_rows, threads, 0, stream>>>(
+        (const TI*)x, ldx, rows, width, weight, eps, (TO*)out, ldo);
+  }););
+  return check_launch("rmsnorm");
+}

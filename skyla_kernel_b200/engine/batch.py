@@ -1,0 +1,180 @@
+"""One step's batch as the kernels see it.
+
+The reference keeps three control words in GPU-visible memory -- first token,
+position, token count -- so that its recorded command buffers never change
+(skyla-engine/src/engine.rs:121-123, README.md:161-162).  With many sequences of
+unequal length the control block becomes a set of int32 arrays, packed in one
+pinned host buffer and sent with one copy per step:
+
+  tokens[T]    the new tokens of all sequences, packed without padding
+  tok_pos[T]   absolute position of each token in its sequence
+  tok_seq[T]   row of its sequence in this batch
+  seq_slot[B]  cache slot of each sequence (for parts with per-slot state)
+  seq_start[B] positions already cached, seq_n[B] new tokens, cu[B+1] packed offsets
+  want[R]      rows (packed token indices) whose logits are asked for
+  pages[G][B,P] for each cache group the page list of each sequence
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+
+@dataclass
+class StepItem:
+    """One sequence's share of a step: its slot, its next tokens, the wanted places."""
+
+    slot: int
+    tokens: Sequence[int]
+    want: Sequence[int] = ()
+
+
+class Workspace:
+    """Named device buffers that grow and are reused from step to step."""
+
+    def __init__(self, device):
+        self.device = device
+        self._bufs: Dict[Tuple[str, torch.dtype], torch.Tensor] = {}
+
+    def get(self, name: str, shape: Tuple[int, ...], dtype: torch.dtype) -> torch.Tensor:
+        n = 1
+        for s in shape:
+            n *= int(s)
+        key = (name, dtype)
+        buf = self._bufs.get(key)
+        if buf is None or buf.numel() < n:
+            buf = torch.empty(max(n, 1), dtype=dtype, device=self.device)
+            self._bufs[key] = buf
+        return buf[:n].view(shape)
+
+    def bytes(self) -> int:
+        return sum(b.numel() * b.element_size() for b in self._bufs.values())
+
+
+@dataclass
+class StepContext:
+    """Everything a part may read during a step."""
+
+    rt: object
+    cache: object
+    workspace: Workspace
+    n_tokens: int
+    n_seqs: int
+    n_want: int
+    max_position: int          # largest absolute position among the new tokens
+    max_context: int           # largest sequence length after this step
+    max_new: int               # most new tokens of one sequence
+    page_size: int
+    tokens: torch.Tensor
+    tok_pos: torch.Tensor
+    tok_seq: torch.Tensor
+    seq_slot: torch.Tensor
+    seq_start: torch.Tensor
+    seq_n: torch.Tensor
+    cu: torch.Tensor
+    want: torch.Tensor
+    pages: List[torch.Tensor]
+    host: Dict[str, np.ndarray] = field(default_factory=dict)
+
+    @property
+    def is_decode(self) -> bool:
+        return self.max_new == 1
+
+    def buffer(self, name: str, shape, dtype) -> torch.Tensor:
+        return self.workspace.get(name, tuple(shape), dtype)
+
+
+class BatchBuilder:
+    """Packs a step's arrays on the host and moves them with one copy."""
+
+    def __init__(self, rt, cache):
+        self.rt = rt
+        self.cache = cache
+        self.workspace = Workspace(rt.device)
+        self._pinned: Optional[torch.Tensor] = None
+        self._device: Optional[torch.Tensor] = None
+        self._copied = None  # event after the last copy out of the pinned buffer
+
+    def _staging(self, n: int):
+        if self._pinned is None or self._pinned.numel() < n:
+            cap = max(1024, 1 << (n - 1).bit_length())
+            self._pinned = torch.empty(cap, dtype=torch.int32, pin_memory=self.rt.device.type == "cuda")
+            self._device = torch.empty(cap, dtype=torch.int32, device=self.rt.device)
+        return self._pinned, self._device
+
+    def build(self, items: List[StepItem]) -> StepContext:
+        cache = self.cache
+        B = len(items)
+        ns = [len(it.tokens) for it in items]
+        T = sum(ns)
+        starts = [cache.length(it.slot) for it in items]
+        R = sum(len(it.want) for it in items)
+        G = len(cache.groups)
+        P = max(1, max(-(-(s + n) // cache.page_size) for s, n in zip(starts, ns)))
+        total = 3 * T + 3 * B + (B + 1) + R + G * B * P
+        if self._copied is not None:
+            self._copied.synchronize()  # the last step's copy has left the pinned buffer
+        host, dev = self._staging(total)
+        h = host.numpy()
+        o = 0
+
+        def take(n):
+            nonlocal o
+            v = h[o:o + n]
+            o += n
+            return v, (o - n, o)
+
+        tokens, r_tokens = take(T)
+        tok_pos, r_pos = take(T)
+        tok_seq, r_seq = take(T)
+        seq_slot, r_slot = take(B)
+        seq_start, r_start = take(B)
+        seq_n, r_n = take(B)
+        cu, r_cu = take(B + 1)
+        want, r_want = take(R)
+        t = 0
+        w = 0
+        cu[0] = 0
+        for b, it in enumerate(items):
+            n = ns[b]
+            tokens[t:t + n] = np.asarray(it.tokens, dtype=np.int64)
+            tok_pos[t:t + n] = np.arange(starts[b], starts[b] + n)
+            tok_seq[t:t + n] = b
+            seq_slot[b], seq_start[b], seq_n[b] = it.slot, starts[b], n
+            for j in it.want:
+                if not 0 <= j < n:
+                    raise IndexError(f"wanted place {j} is outside the {n} tokens of this step")
+                want[w] = t + j
+                w += 1
+            t += n
+            cu[b + 1] = t
+        r_pages = []
+        for g in range(G):
+            pg, r = take(B * P)
+            pg = pg.reshape(B, P)
+            pg[:] = 0
+            for b, it in enumerate(items):
+                lst = cache.pages_of(g, it.slot)
+                m = min(len(lst), P)
+                pg[b, :m] = np.maximum(np.asarray(lst[:m], dtype=np.int64), 0)
+            r_pages.append(r)
+        dev[:total].copy_(host[:total], non_blocking=True)
+        if self.rt.device.type == "cuda":
+            self._copied = torch.cuda.Event()
+            self._copied.record()
+
+        def view(r):
+            return dev[r[0]:r[1]]
+
+        return StepContext(
+            rt=self.rt, cache=cache, workspace=self.workspace, n_tokens=T, n_seqs=B, n_want=R,
+            max_position=max(s + n - 1 for s, n in zip(starts, ns)),
+            max_context=max(s + n for s, n in zip(starts, ns)), max_new=max(ns),
+            page_size=cache.page_size, tokens=view(r_tokens), tok_pos=view(r_pos),
+            tok_seq=view(r_seq), seq_slot=view(r_slot), seq_start=view(r_start), seq_n=view(r_n),
+            cu=view(r_cu), want=view(r_want), pages=[view(r).view(B, P) for r in r_pages],
+            host={"starts": np.asarray(starts), "ns": np.asarray(ns)},
+        )

@@ -1,0 +1,107 @@
+"""The engine: a loaded model, its cache and the step function.
+
+``Engine.step`` is the one function between a batch of sequences' next tokens
+and their logits.  It is what the reference's ``Engine::prefill`` and
+``Engine::step`` are for one sequence (skyla-engine/src/engine.rs:137-152): it
+runs only the tokens it is given, from the cache that earlier steps left, and
+appends to it.  Prompts go in one step, then one token per sequence; any other
+cut of the tokens gives the same logits up to rounding.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional, Sequence
+
+import torch
+
+from ..cache import CacheError, CacheFull, SequenceCache
+from ..config import config_from_folder
+from ..kernels import build as kernel_build
+from ..parts.base import Runtime
+from ..weights import load_weights
+from .batch import BatchBuilder, StepItem
+from .model import DecoderModel, declared_tensors
+
+
+class EngineError(RuntimeError):
+    pass
+
+
+def _device(device) -> torch.device:
+    dev = torch.device(device)
+    if dev.type != "cuda":
+        raise EngineError("the engine runs on a CUDA device only; there is no host path")
+    if not torch.cuda.is_available():
+        raise EngineError("no CUDA device is available; the engine cannot run")
+    return dev
+
+
+class Engine:
+    """A model on one GPU with a cache of ``max_tokens`` positions.
+
+    ``max_tokens`` counts the positions held by live sequences, each sequence
+    rounded up to a whole page of 64.  ``max_slots`` bounds the live sequences
+    (default: one per page).
+    """
+
+    def __init__(self, config, tensors: Dict[str, torch.Tensor], dtype: str = "bfloat16",
+                 max_tokens: int = 4096, max_slots: Optional[int] = None, device="cuda:0"):
+        self.config = config
+        self.spec = config.to_spec()
+        self.rt = Runtime(_device(device), dtype)
+        torch.cuda.set_device(self.rt.device)
+        self.model = DecoderModel(self.spec, self.rt)
+        kernel_build.build_all(self.model.kernels_needed())
+        self.model.load(tensors)
+        self.cache = SequenceCache(self.model.kv_needs, self.model.state_needs, max_tokens, max_slots,
+                                   self.rt.cache_dtype, self.rt.device)
+        self.batcher = BatchBuilder(self.rt, self.cache)
+        self.vocab_size = self.spec.vocab_size
+
+    # ---------------------------------------------------------------- loading
+    @classmethod
+    def from_folder(cls, folder: str, dtype: str = "bfloat16", max_tokens: int = 4096,
+                    max_slots: Optional[int] = None, device="cuda:0") -> "Engine":
+        config = config_from_folder(folder)
+        spec = config.to_spec()
+        tensors = load_weights(folder, declared_tensors(spec), spec.optional_tensors)
+        return cls(config, tensors, dtype, max_tokens, max_slots, device)
+
+    # ------------------------------------------------------------------ slots
+    def alloc_slot(self) -> int:
+        return self.cache.alloc_slot()
+
+    def free_slot(self, slot: int) -> None:
+        self.cache.free_slot(slot)
+
+    # ------------------------------------------------------------------- step
+    def step(self, items: Sequence[StepItem], taps=None) -> torch.Tensor:
+        """Run the items' tokens as one batch; float32 logits at the wanted places.
+
+        Rows are ordered by item, then by the item's ``want`` list.  Raises
+        :class:`CacheFull` before anything is launched if the tokens do not fit,
+        and ``ValueError`` for a token outside the vocabulary (the reference:
+        "token {t} is outside the vocabulary", skyla-engine/src/engine.rs:110-112).
+        """
+        items = list(items)
+        if not items:
+            return torch.empty((0, self.vocab_size), dtype=torch.float32, device=self.rt.device)
+        for it in items:
+            if len(it.tokens) == 0:
+                raise ValueError(f"slot {it.slot}: a step must bring at least one token")
+            for t in it.tokens:
+                if not 0 <= int(t) < self.vocab_size:
+                    raise ValueError(f"token {t} is outside the vocabulary (0..{self.vocab_size - 1})")
+        growth = [(it.slot, len(it.tokens)) for it in items]
+        self.cache.reserve(growth)
+        with torch.cuda.device(self.rt.device):
+            ctx = self.batcher.build(items)
+            logits = self.model.forward(ctx, taps)
+        self.cache.advance(growth)
+        return logits
+
+    # ------------------------------------------------------------------ facts
+    def weight_bytes(self) -> int:
+        return self.model.weight_bytes_per_step()
+
+    def device_name(self) -> str:
+        return torch.cuda.get_device_name(self.rt.device)

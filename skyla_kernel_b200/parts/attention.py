@@ -1,0 +1,124 @@
+"""Grouped-query attention over the cache, with optional per-head q/k RMSNorm.
+
+For the new tokens of a step (skyla-ref/src/model.rs:124-172):
+``q = Wq h``, ``k = Wk h``, ``v = Wv h`` (no bias); each q and k head is
+RMS-normed with one ``[head_dim]`` weight, then rotated at its absolute position;
+k and v go to the cache; query head ``h`` attends the cache of key/value head
+``h // (heads / kv_heads)`` with ``softmax(q.k * scale)`` over the positions it
+may see; the heads are concatenated, projected by ``Wo`` and added to the
+residual stream (the add is fused into the product's epilogue, as the reference
+does with its ACCUM matvec, skyla-engine/src/graph.rs:110-112).
+
+Parameters: ``hidden_size``, ``num_heads``, ``num_kv_heads``, ``head_dim``,
+``qk_norm``, ``qk_norm_eps``, ``scale`` (``None``: ``1/sqrt(head_dim)``),
+``window`` (``None``: all earlier positions), ``position`` (a position part spec).
+The three input projections are stored as one matrix so that a step needs one
+product for them.
+"""
+from __future__ import annotations
+
+import math
+from typing import Dict, Optional
+
+import torch
+
+from ..cache.kv import KVNeed
+from ..kernels import ops
+from ..weights.loader import TensorDecl
+from .base import Part, build_part, register_mixer
+from .linear import ACCUMULATE, STORE, Linear
+
+
+class GQAttention(Part):
+    kernel_modules = ("linear_plain", "attn_prep", "attention_plain")
+
+    def __init__(self, spec, rt):
+        super().__init__(spec, rt)
+        p = spec.params
+        self.hidden = int(p["hidden_size"])
+        self.nq = int(p["num_heads"])
+        self.nkv = int(p["num_kv_heads"])
+        self.hd = int(p["head_dim"])
+        if self.nq % self.nkv:
+            raise ValueError(f"{self.nq} query heads do not divide into {self.nkv} key/value heads")
+        self.qk_norm = bool(p.get("qk_norm", False))
+        self.eps = float(p.get("qk_norm_eps", 0.0))
+        self.scale = float(p["scale"]) if p.get("scale") is not None else 1.0 / math.sqrt(self.hd)
+        self.window = int(p["window"]) if p.get("window") else 0
+        pos = p.get("position")
+        self.position = build_part("position", pos, rt) if pos is not None else None
+        self.q_norm_w = self.k_norm_w = None
+        self.qkv: Optional[Linear] = None
+        self.q_only: Optional[Linear] = None
+        self.out: Optional[Linear] = None
+
+    # ------------------------------------------------------------------ tensors
+    @classmethod
+    def declare(cls, spec) -> Dict[str, TensorDecl]:
+        p, t = spec.params, spec.tensors
+        h, nq, nkv, hd = (int(p[k]) for k in ("hidden_size", "num_heads", "num_kv_heads", "head_dim"))
+        d = {
+            t["q_proj"]: TensorDecl((nq * hd, h)),
+            t["k_proj"]: TensorDecl((nkv * hd, h)),
+            t["v_proj"]: TensorDecl((nkv * hd, h)),
+            t["o_proj"]: TensorDecl((h, nq * hd)),
+        }
+        if p.get("qk_norm", False):
+            d[t["q_norm"]] = TensorDecl((hd,), "norm")
+            d[t["k_norm"]] = TensorDecl((hd,), "norm")
+        return d
+
+    def load(self, tensors) -> None:
+        t = self.spec.tensors
+        parts = [tensors[t[k]] for k in ("q_proj", "k_proj", "v_proj")]
+        if len({w.dtype for w in parts}) > 1:
+            parts = [w.to(torch.float32) for w in parts]
+        fused = self.rt.matrix(torch.cat(parts, dim=0))
+        self.qkv = Linear(fused, self.rt)
+        self.q_only = Linear(fused[: self.nq * self.hd], self.rt)
+        self.out = Linear(self.rt.matrix(tensors[t["o_proj"]]), self.rt)
+        if self.qk_norm:
+            self.q_norm_w = self.rt.vector(tensors[t["q_norm"]])
+            self.k_norm_w = self.rt.vector(tensors[t["k_norm"]])
+
+    def weight_bytes(self) -> int:
+        return self.qkv.bytes() + self.out.bytes()
+
+    def kernels_needed(self):
+        return self.kernel_modules
+
+    # -------------------------------------------------------------------- cache
+    def cache_need(self) -> Optional[KVNeed]:
+        return KVNeed(self.nkv, self.hd, self.window or None)
+
+    def state_need(self):
+        return None
+
+    # --------------------------------------------------------------------- step
+    def forward(self, ctx, h: torch.Tensor, x: torch.Tensor, entry) -> None:
+        n = ctx.n_tokens
+        nq, nkv, hd = self.nq, self.nkv, self.hd
+        group, k_pool, v_pool = ctx.cache.kv_of_entry(entry.cache_entry)
+        pages = ctx.pages[group]
+        cos = sin = None
+        n_rot = 0
+        if self.position is not None:
+            cos, sin, n_rot = self.position.tables(ctx.max_position + 1)
+        if entry.owns_cache:
+            qkv = ctx.buffer("attn.qkv", (n, (nq + 2 * nkv) * hd), self.rt.act_dtype)
+            self.qkv.forward(h, qkv, STORE)
+            ops.qk_norm_rope_cache(qkv, 0, nq * hd, (nq + nkv) * hd, nq, nkv, hd, self.q_norm_w,
+                                   self.k_norm_w, self.eps, cos, sin, n_rot, ctx.tok_pos, ctx.tok_seq,
+                                   k_pool, v_pool, pages, ctx.page_size)
+        else:  # reads the cache another run wrote: only queries are needed
+            qkv = ctx.buffer("attn.q", (n, nq * hd), self.rt.act_dtype)
+            self.q_only.forward(h, qkv, STORE)
+            ops.qk_norm_rope_cache(qkv, 0, 0, 0, nq, 0, hd, self.q_norm_w, None, self.eps, cos, sin,
+                                   n_rot, ctx.tok_pos, ctx.tok_seq, None, None, pages, ctx.page_size)
+        attn = ctx.buffer("attn.out", (n, nq * hd), self.rt.act_dtype)
+        ops.attention_plain(qkv[:, : nq * hd], attn, nq, nkv, hd, k_pool, v_pool, pages,
+                            ctx.page_size, ctx.tok_pos, ctx.tok_seq, self.scale, self.window)
+        self.out.forward(attn, x, ACCUMULATE)
+
+
+register_mixer("gqa_attention", GQAttention)

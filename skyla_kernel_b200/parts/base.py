@@ -1,0 +1,158 @@
+"""What a part is, and the registries that the configuration's part names point into.
+
+A part is built from a :class:`~skyla_kernel_b200.config.PartSpec` (its sizes,
+constants and the checkpoint names of its tensors) and a :class:`Runtime` (device
+and precision).  It declares its tensors before any weight is read, takes them in
+``load`` and then runs inside a step.  A part never looks at the model it is in:
+the reference's ``Mixer`` and ``Ffn`` enums (skyla-ref/src/model.rs:17-20,
+skyla-ref/src/ffn.rs:6-19) become entries of these tables, so another kind of
+mixer, feed-forward, norm, position encoding or block is one ``register_*`` call.
+
+Interfaces (``ctx`` is the step's :class:`~skyla_kernel_b200.engine.batch.StepContext`;
+``x`` the float32 residual stream ``[tokens, hidden]``):
+
+* norm           ``forward(ctx, x, out, rows=None)``: ``out[r] = norm(x[rows[r]])``
+* mixer          ``cache_need()``, ``state_need()``, ``forward(ctx, h, x, entry)``:
+                 adds its output to ``x``; ``entry`` says which cache it uses
+* feed-forward   ``forward(ctx, h, x)``: adds its output to ``x``
+* position       whatever the mixers that accept it read (rotary: ``tables()``)
+* block          ``forward(ctx, x, entry)`` with the four parts above inside
+* embedding      ``forward(ctx, tokens, x)``;  head: ``forward(ctx, h, logits)``
+"""
+from __future__ import annotations
+
+import json
+from dataclasses import dataclass
+from typing import Callable, Dict, Optional
+
+import torch
+
+from ..config.base import ConfigError, PartSpec
+from ..weights.loader import TensorDecl
+
+
+@dataclass
+class Runtime:
+    """Where and in which precision a model runs.
+
+    ``float32``: weights, cache and activations in 32-bit, plain kernels only.
+    ``bfloat16``: 16-bit weights, cache and matrix-product operands; the residual
+    stream, norms, softmax, rotation and accumulation stay 32-bit.
+    """
+
+    device: torch.device
+    dtype: str = "bfloat16"
+
+    def __post_init__(self):
+        if self.dtype in ("fp32", "float"):
+            self.dtype = "float32"
+        if self.dtype in ("bf16",):
+            self.dtype = "bfloat16"
+        if self.dtype not in ("float32", "bfloat16"):
+            raise ValueError(f"dtype must be float32 or bfloat16, not {self.dtype!r}")
+        self.device = torch.device(self.device)
+        self._placed = {}
+        self.shared_parts = {}
+
+    def forget_host_tensors(self) -> None:
+        """Drop the host-to-device placement table once a model is loaded."""
+        self._placed = {}
+
+    @property
+    def full_precision(self) -> bool:
+        return self.dtype == "float32"
+
+    @property
+    def act_dtype(self) -> torch.dtype:
+        return torch.float32 if self.full_precision else torch.bfloat16
+
+    @property
+    def cache_dtype(self) -> torch.dtype:
+        return self.act_dtype
+
+    def matrix(self, t: torch.Tensor) -> torch.Tensor:
+        """A weight matrix on the device in the precision of this runtime.
+
+        In 32-bit mode everything is widened (exactly).  In bfloat16 mode a
+        matrix stored in 16 bits stays bfloat16 and one stored in 32 bits stays
+        32-bit; the matrix products take either.
+        """
+        key = (t.data_ptr(), tuple(t.shape), t.dtype)
+        placed = self._placed.get(key)
+        if placed is None:
+            if self.full_precision:
+                placed = t.to(device=self.device, dtype=torch.float32).contiguous()
+            else:
+                placed = t.to(device=self.device).contiguous()
+            self._placed[key] = placed  # a tensor used twice (a tied head) is placed once
+        return placed
+
+    def vector(self, t: torch.Tensor) -> torch.Tensor:
+        """A norm weight or other small table: always 32-bit on the device."""
+        return t.to(device=self.device, dtype=torch.float32).contiguous()
+
+
+class Part:
+    """Base of all parts."""
+
+    #: CUDA source modules (csrc/<name>.cu) the part launches, compiled before first use
+    kernel_modules = ()
+
+    def __init__(self, spec: PartSpec, rt: Runtime):
+        self.spec = spec
+        self.rt = rt
+
+    @classmethod
+    def declare(cls, spec: PartSpec) -> Dict[str, TensorDecl]:
+        """Checkpoint name -> shape and kind of every tensor the part reads."""
+        return {}
+
+    def load(self, tensors: Dict[str, torch.Tensor]) -> None:
+        """Take the declared tensors (CPU, as stored) and keep what the kernels need."""
+
+    def kernels_needed(self):
+        return tuple(self.kernel_modules)
+
+    def weight_bytes(self) -> int:
+        return 0
+
+
+_REGISTRIES: Dict[str, Dict[str, type]] = {
+    k: {} for k in ("norm", "mixer", "feed_forward", "position", "block", "embedding", "head")}
+
+
+def _register(category: str, kind: str, cls: type) -> type:
+    _REGISTRIES[category][kind] = cls
+    return cls
+
+
+def register_norm(kind: str, cls: type) -> type: return _register("norm", kind, cls)
+def register_mixer(kind: str, cls: type) -> type: return _register("mixer", kind, cls)
+def register_feed_forward(kind: str, cls: type) -> type: return _register("feed_forward", kind, cls)
+def register_position(kind: str, cls: type) -> type: return _register("position", kind, cls)
+def register_block(kind: str, cls: type) -> type: return _register("block", kind, cls)
+def register_embedding(kind: str, cls: type) -> type: return _register("embedding", kind, cls)
+def register_head(kind: str, cls: type) -> type: return _register("head", kind, cls)
+
+
+def part_class(category: str, kind: str) -> type:
+    try:
+        return _REGISTRIES[category][kind]
+    except KeyError:
+        known = ", ".join(sorted(_REGISTRIES[category])) or "(none)"
+        raise ConfigError(f"no {category.replace('_', '-')} part named {kind!r}; registered: {known}") from None
+
+
+def build_part(category: str, spec: PartSpec, rt: Runtime):
+    """Build a part; a class marked ``shareable`` is built once per runtime and parameter set."""
+    cls = part_class(category, spec.kind)
+    if getattr(cls, "shareable", False):
+        key = (category, spec.kind, json.dumps(spec.params, sort_keys=True, default=str))
+        if key not in rt.shared_parts:
+            rt.shared_parts[key] = cls(spec, rt)
+        return rt.shared_parts[key]
+    return cls(spec, rt)
+
+
+def declare_part(category: str, spec: PartSpec) -> Dict[str, TensorDecl]:
+    return part_class(category, spec.kind).declare(spec)

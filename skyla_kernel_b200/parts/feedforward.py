@@ -1,0 +1,68 @@
+"""Dense gated feed-forward: ``x += Wdown( silu(Wgate h) * (Wup h) )``.
+
+``silu(z) = z / (1 + exp(-z))`` (skyla-ref/src/ffn.rs:21-28, ops.rs:28-30); no
+bias.  Gate and up are stored as one matrix so that one product computes both and
+its epilogue multiplies them; the down product adds into the residual stream
+(skyla-engine/src/graph.rs:174-184 does the same in four dispatches).
+Parameters: ``hidden_size``, ``intermediate_size``.
+"""
+from __future__ import annotations
+
+from typing import Dict
+
+import torch
+
+from ..weights.loader import TensorDecl
+from .base import Part, register_feed_forward
+from .linear import ACCUMULATE, GATED, Linear
+
+
+def fuse_gate_up(gate: torch.Tensor, up: torch.Tensor, group: int) -> torch.Tensor:
+    """Rows in groups: ``group`` gate rows, then the ``group`` up rows of the same outputs."""
+    n, k = gate.shape
+    if n % group:
+        raise ValueError(f"gate/up group {group} does not divide {n}")
+    g = gate.reshape(n // group, group, k)
+    u = up.reshape(n // group, group, k)
+    return torch.stack((g, u), dim=1).reshape(2 * n, k).contiguous()
+
+
+class SwiGLU(Part):
+    kernel_modules = ("linear_plain",)
+
+    def __init__(self, spec, rt):
+        super().__init__(spec, rt)
+        self.hidden = int(spec.params["hidden_size"])
+        self.inter = int(spec.params["intermediate_size"])
+        self.gate_up: Linear = None
+        self.down: Linear = None
+
+    @classmethod
+    def declare(cls, spec) -> Dict[str, TensorDecl]:
+        h, i = int(spec.params["hidden_size"]), int(spec.params["intermediate_size"])
+        t = spec.tensors
+        return {t["gate_proj"]: TensorDecl((i, h)), t["up_proj"]: TensorDecl((i, h)),
+                t["down_proj"]: TensorDecl((h, i))}
+
+    def gate_up_group(self) -> int:
+        return self.inter
+
+    def load(self, tensors) -> None:
+        t = self.spec.tensors
+        gate, up = tensors[t["gate_proj"]], tensors[t["up_proj"]]
+        if gate.dtype != up.dtype:
+            gate, up = gate.to(torch.float32), up.to(torch.float32)
+        group = self.gate_up_group()
+        self.gate_up = Linear(self.rt.matrix(fuse_gate_up(gate, up, group)), self.rt, gated_group=group)
+        self.down = Linear(self.rt.matrix(tensors[t["down_proj"]]), self.rt)
+
+    def weight_bytes(self) -> int:
+        return self.gate_up.bytes() + self.down.bytes()
+
+    def forward(self, ctx, h: torch.Tensor, x: torch.Tensor) -> None:
+        act = ctx.buffer("ffn.act", (ctx.n_tokens, self.inter), self.rt.act_dtype)
+        self.gate_up.forward(h, act, GATED)
+        self.down.forward(act, x, ACCUMULATE)
+
+
+register_feed_forward("swiglu", SwiGLU)
