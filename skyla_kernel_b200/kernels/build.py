@@ -29,6 +29,9 @@ class KernelBuildError(RuntimeError):
     pass
 
 
+_DIR_LOCK = threading.Lock()
+
+
 def _nvcc() -> str:
     for cand in (os.environ.get("SKYLA_NVCC"), shutil.which("nvcc"), "/usr/local/cuda/bin/nvcc"):
         if cand and os.path.isfile(cand):
@@ -37,7 +40,19 @@ def _nvcc() -> str:
                            "(set SKYLA_NVCC or put nvcc on PATH)")
 
 
+_BUILD_DIR = None
+
+
 def _build_dir() -> str:
+    global _BUILD_DIR
+    if _BUILD_DIR is None:
+        with _DIR_LOCK:
+            if _BUILD_DIR is None:
+                _BUILD_DIR = _find_build_dir()
+    return _BUILD_DIR
+
+
+def _find_build_dir() -> str:
     cands = [os.environ.get("SKYLA_BUILD_DIR"), os.path.join(CSRC, "_build"),
              os.path.join(tempfile.gettempdir(), f"skyla_kernel_b200_build_{os.getuid()}")]
     for d in cands:

@@ -70,21 +70,24 @@ class Runtime:
     def cache_dtype(self) -> torch.dtype:
         return self.act_dtype
 
-    def matrix(self, t: torch.Tensor) -> torch.Tensor:
+    def matrix(self, t: torch.Tensor, shared: bool = False) -> torch.Tensor:
         """A weight matrix on the device in the precision of this runtime.
 
         In 32-bit mode everything is widened (exactly).  In bfloat16 mode a
         matrix stored in 16 bits stays bfloat16 and one stored in 32 bits stays
-        32-bit; the matrix products take either.
+        32-bit; the matrix products take either.  ``shared``: the same stored
+        tensor may be asked for by two parts (a tied head and the embedding) and
+        is then placed once; the host tensor is kept alive until the model is
+        loaded so that its identity cannot be taken by another tensor.
         """
-        key = (t.data_ptr(), tuple(t.shape), t.dtype)
-        placed = self._placed.get(key)
-        if placed is None:
-            if self.full_precision:
-                placed = t.to(device=self.device, dtype=torch.float32).contiguous()
-            else:
-                placed = t.to(device=self.device).contiguous()
-            self._placed[key] = placed  # a tensor used twice (a tied head) is placed once
+        if shared and id(t) in self._placed:
+            return self._placed[id(t)][1]
+        if self.full_precision:
+            placed = t.to(device=self.device, dtype=torch.float32).contiguous()
+        else:
+            placed = t.to(device=self.device).contiguous()
+        if shared:
+            self._placed[id(t)] = (t, placed)
         return placed
 
     def vector(self, t: torch.Tensor) -> torch.Tensor:

@@ -32,7 +32,7 @@ class TokenEmbedding(Part):
                                                     int(spec.params["hidden_size"])))}
 
     def load(self, tensors) -> None:
-        self.weight = self.rt.matrix(tensors[self.spec.tensors["weight"]])
+        self.weight = self.rt.matrix(tensors[self.spec.tensors["weight"]], shared=True)
 
     def weight_bytes(self) -> int:
         return self.weight.numel() * self.weight.element_size()
@@ -56,7 +56,7 @@ class LinearHead(Part):
                                                     int(spec.params["hidden_size"])))}
 
     def load(self, tensors) -> None:
-        self.proj = Linear(self.rt.matrix(tensors[self.spec.tensors["weight"]]), self.rt)
+        self.proj = Linear(self.rt.matrix(tensors[self.spec.tensors["weight"]], shared=True), self.rt)
 
     def weight_bytes(self) -> int:
         return self.proj.bytes()

@@ -88,18 +88,21 @@ def silu(z):
 
 # skyla-ref/src/model.rs:124-172 -- one sequence, all positions at once, causal
 def attention(n, wq, wk, wv, wo, q_norm, k_norm, nq, nkv, hd, eps, freqs, mscale, n_rot,
-              scale=None, window=None, positions=None):
+              scale=None, window=None, positions=None, rnd=lambda t: t):
+    """``rnd`` rounds stored intermediates (identity: everything stays 32-bit); with a
+    bfloat16 round trip it imitates where a 16-bit engine stores activations."""
     T = n.shape[0]
     positions = torch.arange(T) if positions is None else positions
-    q = (n @ wq.T).view(T, nq, hd)
-    k = (n @ wk.T).view(T, nkv, hd)
-    v = (n @ wv.T).view(T, nkv, hd)
+    q = rnd(n @ wq.T).view(T, nq, hd)
+    k = rnd(n @ wk.T).view(T, nkv, hd)
+    v = rnd(n @ wv.T).view(T, nkv, hd)
     if q_norm is not None:  # model.rs:138-145: norm over the head, then rotation
         q = rmsnorm(q, q_norm, eps)
         k = rmsnorm(k, k_norm, eps)
     if freqs is not None:
         q = rope_neox(q, positions, freqs, mscale, n_rot)
         k = rope_neox(k, positions, freqs, mscale, n_rot)
+    q, k = rnd(q), rnd(k)
     n_rep = nq // nkv                       # model.rs:149
     scale = 1.0 / math.sqrt(hd) if scale is None else scale  # model.rs:150
     out = torch.zeros(T, nq, hd, dtype=n.dtype)
@@ -112,16 +115,20 @@ def attention(n, wq, wk, wv, wo, q_norm, k_norm, nq, nkv, hd, eps, freqs, mscale
             mask = mask | (i[None, :] < i[:, None] - window + 1)
         s = s.masked_fill(mask, float("-inf"))
         out[:, h, :] = softmax(s) @ v[:, kvh, :]   # model.rs:159-165
-    return out.reshape(T, nq * hd) @ wo.T   # model.rs:171
+    return rnd(out.reshape(T, nq * hd)) @ wo.T   # model.rs:171
 
 
 # skyla-ref/src/ffn.rs:21-28
-def swiglu(n, w_gate, w_up, w_down):
-    return (silu(n @ w_gate.T) * (n @ w_up.T)) @ w_down.T
+def swiglu(n, w_gate, w_up, w_down, rnd=lambda t: t):
+    return rnd(silu(n @ w_gate.T) * (n @ w_up.T)) @ w_down.T
 
 
 # skyla-ref/src/model.rs:97-122
-def forward(cfg, w, tokens, dtype=torch.float32, taps=None):
+def bf16_round(t):
+    return t.to(torch.bfloat16).to(t.dtype)
+
+
+def forward(cfg, w, tokens, dtype=torch.float32, taps=None, rnd=lambda t: t):
     """Logits [T, vocab] for one whole sequence of token ids."""
     w = {k: v.to(dtype) for k, v in w.items()}
     H, nq = cfg["hidden_size"], cfg["num_attention_heads"]
@@ -132,17 +139,17 @@ def forward(cfg, w, tokens, dtype=torch.float32, taps=None):
     x = w["model.embed_tokens.weight"][torch.as_tensor(tokens, dtype=torch.long)]  # model.rs:99-100
     for l in range(cfg["num_hidden_layers"]):
         p = f"model.layers.{l}."
-        n = rmsnorm(x, w[p + "input_layernorm.weight"], eps)        # model.rs:105
+        n = rnd(rmsnorm(x, w[p + "input_layernorm.weight"], eps))   # model.rs:105
         x = x + attention(n, w[p + "self_attn.q_proj.weight"], w[p + "self_attn.k_proj.weight"],
                           w[p + "self_attn.v_proj.weight"], w[p + "self_attn.o_proj.weight"],
                           w[p + "self_attn.q_norm.weight"], w[p + "self_attn.k_norm.weight"],
-                          nq, nkv, hd, eps, freqs, mscale, hd)       # model.rs:108-110
-        n = rmsnorm(x, w[p + "post_attention_layernorm.weight"], eps)  # model.rs:112
+                          nq, nkv, hd, eps, freqs, mscale, hd, rnd=rnd)  # model.rs:108-110
+        n = rnd(rmsnorm(x, w[p + "post_attention_layernorm.weight"], eps))  # model.rs:112
         x = x + swiglu(n, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"],
-                       w[p + "mlp.down_proj.weight"])                 # model.rs:113-114
+                       w[p + "mlp.down_proj.weight"], rnd)            # model.rs:113-114
         if taps is not None:
             taps.append(x.clone())
-    x = rmsnorm(x, w["model.norm.weight"], eps)                      # model.rs:117
+    x = rnd(rmsnorm(x, w["model.norm.weight"], eps))                 # model.rs:117
     head = w["lm_head.weight"] if not cfg.get("tie_word_embeddings", False) else w["model.embed_tokens.weight"]
     return x @ head.T                                                # model.rs:118-119, 70-73
 
