@@ -1,0 +1,282 @@
+"""Each kernel alone against a plain reference of the same operation, at sizes other
+than the engine's test models."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import plain_qwen3 as plain
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def _ops():
+    from skyla_kernel_b200.kernels import ops
+    return ops
+
+
+def _rand(*shape, seed=0, dtype=torch.float32, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(*shape, generator=g) * scale).to(dtype).to(DEV)
+
+
+def _tol(dtype):
+    return dict(rtol=2e-2, atol=2e-2) if dtype == torch.bfloat16 else dict(rtol=1e-5, atol=1e-5)
+
+
+@pytest.mark.parametrize("width", [48, 80, 1000, 4096])
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+def test_rmsnorm(width, out_dtype):
+    ops = _ops()
+    x = _rand(9, width, seed=1, scale=3.0)
+    w = 1 + 0.1 * _rand(width, seed=2)
+    out = torch.empty(9, width, dtype=out_dtype, device=DEV)
+    ops.rmsnorm(x, w, 1e-5, out)
+    ref = plain.rmsnorm(x.cpu(), w.cpu(), 1e-5)
+    torch.testing.assert_close(out.float().cpu(), ref, **_tol(out_dtype))
+    rows = torch.tensor([8, 0, 3], dtype=torch.int32, device=DEV)
+    out2 = torch.empty(3, width, dtype=out_dtype, device=DEV)
+    ops.rmsnorm(x, w, 1e-5, out2, rows)
+    assert torch.equal(out2, out[rows.long()])  # the same row gives the same bits wherever it lies
+
+
+def test_embed_gather():
+    ops = _ops()
+    for dt in (torch.float32, torch.bfloat16):
+        table = _rand(131, 80, seed=3, dtype=dt)
+        toks = torch.tensor([130, 0, 5, 5, 77], dtype=torch.int32, device=DEV)
+        out = torch.empty(5, 80, dtype=torch.float32, device=DEV)
+        ops.embed_gather(toks, table, out)
+        assert torch.equal(out, table[toks.long()].float())
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 131, 80), (5, 64, 64), (70, 96, 160), (130, 509, 96)])
+@pytest.mark.parametrize("xdt,wdt", [(torch.float32, torch.float32), (torch.bfloat16, torch.bfloat16),
+                                      (torch.bfloat16, torch.float32)])
+def test_linear_plain_store_and_accumulate(m, n, k, xdt, wdt):
+    ops = _ops()
+    x, w = _rand(m, k, seed=4, dtype=xdt), _rand(n, k, seed=5, dtype=wdt, scale=0.1)
+    ref = (x.double() @ w.double().T).float()
+    y = torch.empty(m, n, dtype=xdt, device=DEV)
+    ops.linear_plain(x, w, y, ops.STORE)
+    torch.testing.assert_close(y.float(), ref, **_tol(xdt))
+    acc = _rand(m, n, seed=6)
+    before = acc.clone()
+    ops.linear_plain(x, w, acc, ops.ACCUMULATE)
+    torch.testing.assert_close(acc, before + ref, rtol=1e-4, atol=1e-4)
+    # a row's result does not depend on the rows around it
+    r = min(3, m - 1)
+    y1 = torch.empty(1, n, dtype=xdt, device=DEV)
+    ops.linear_plain(x[r:r + 1], w, y1, ops.STORE)
+    assert torch.equal(y1[0], y[r])
+
+
+@pytest.mark.parametrize("group", [None, 16])
+@pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
+def test_linear_plain_gated(group, dt):
+    ops = _ops()
+    from skyla_kernel_b200.parts.feedforward import fuse_gate_up
+    m, n, k = 37, 112, 80
+    x, g, u = _rand(m, k, seed=7, dtype=dt), _rand(n, k, seed=8, dtype=dt, scale=0.2), _rand(n, k, seed=9, dtype=dt, scale=0.2)
+    grp = group or n
+    w = fuse_gate_up(g, u, grp)
+    y = torch.empty(m, n, dtype=dt, device=DEV)
+    ops.linear_plain(x, w, y, ops.GATED, grp)
+    ref = plain.silu(x.double().cpu() @ g.double().cpu().T) * (x.double().cpu() @ u.double().cpu().T)
+    torch.testing.assert_close(y.float().cpu(), ref.float(), **_tol(dt))
+
+
+def _paged(n_seqs, lens, nkv, hd, dtype, seed, page_size=64, shuffle=True):
+    """Random keys/values per sequence scattered over shuffled pages; returns pools, table, dense copies."""
+    g = torch.Generator().manual_seed(seed)
+    P = max(-(-l // page_size) for l in lens)
+    n_pages = n_seqs * P + 3
+    order = torch.randperm(n_pages, generator=g).tolist() if shuffle else list(range(n_pages))
+    table = torch.zeros(n_seqs, P, dtype=torch.int32)
+    k_pool = torch.zeros(n_pages, nkv, page_size, hd, dtype=dtype)
+    v_pool = torch.zeros(n_pages, nkv, page_size, hd, dtype=dtype)
+    ks, vs = [], []
+    for b, l in enumerate(lens):
+        k = torch.randn(l, nkv, hd, generator=g).to(dtype)
+        v = torch.randn(l, nkv, hd, generator=g).to(dtype)
+        ks.append(k); vs.append(v)
+        for j in range(-(-l // page_size)):
+            pg = order.pop()
+            table[b, j] = pg
+            seg = slice(j * page_size, min(l, (j + 1) * page_size))
+            k_pool[pg, :, : seg.stop - seg.start] = k[seg].transpose(0, 1)
+            v_pool[pg, :, : seg.stop - seg.start] = v[seg].transpose(0, 1)
+    return k_pool.to(DEV), v_pool.to(DEV), table.to(DEV), ks, vs
+
+
+def _attn_ref(q, k, v, pos, nq, nkv, scale, window):
+    """q [nq, hd] at position pos over k, v [len, nkv, hd] (float64)."""
+    out = []
+    first = max(0, pos - window + 1) if window else 0
+    for h in range(nq):
+        kvh = h // (nq // nkv)
+        s = (k[first:pos + 1, kvh].double() @ q[h].double()) * scale
+        p = torch.softmax(s, 0)
+        out.append(p @ v[first:pos + 1, kvh].double())
+    return torch.stack(out)
+
+
+@pytest.mark.parametrize("nq,nkv,hd", [(4, 2, 16), (6, 1, 32), (3, 3, 48), (8, 2, 128), (5, 5, 80)])
+@pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("window", [0, 70])
+def test_attention_plain(nq, nkv, hd, dt, window):
+    ops = _ops()
+    lens = [1, 64, 65, 200, 333]
+    k_pool, v_pool, table, ks, vs = _paged(len(lens), lens, nkv, hd, dt, seed=nq * 100 + hd)
+    # tokens: for every sequence its last position, plus some inner ones of the long sequences
+    toks = [(b, l - 1) for b, l in enumerate(lens)] + [(3, 63), (3, 64), (4, 128), (4, 5)]
+    q = _rand(len(toks), nq * hd, seed=11, dtype=dt)
+    out = torch.empty(len(toks), nq * hd, dtype=dt, device=DEV)
+    tok_pos = torch.tensor([p for _, p in toks], dtype=torch.int32, device=DEV)
+    tok_seq = torch.tensor([b for b, _ in toks], dtype=torch.int32, device=DEV)
+    scale = 1.0 / math.sqrt(hd)
+    ops.attention_plain(q, out, nq, nkv, hd, k_pool, v_pool, table, 64, tok_pos, tok_seq, scale, window)
+    for i, (b, p) in enumerate(toks):
+        ref = _attn_ref(q[i].cpu().view(nq, hd), ks[b], vs[b], p, nq, nkv, scale, window)
+        torch.testing.assert_close(out[i].float().cpu().view(nq, hd), ref.float(), **_tol(dt))
+
+
+@pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
+def test_attention_finds_one_far_key(dt):
+    """One key among hundreds is made to stand out; the output must be its value."""
+    ops = _ops()
+    nq, nkv, hd, L = 4, 2, 32, 700
+    k_pool, v_pool, table, ks, vs = _paged(1, [L], nkv, hd, dt, seed=5)
+    q = _rand(1, nq * hd, seed=12, dtype=dt)
+    for target in (0, 63, 64, 411, L - 1):
+        kp = k_pool.clone()
+        page, off = int(table[0, target // 64]), target % 64
+        for kvh in range(nkv):
+            qh = q[0].view(nq, hd)[kvh * 2].float()
+            kp[page, kvh, off] = (qh / qh.norm() * 60.0).to(dt)  # score ~ 60*|q|/sqrt(hd) for heads of this group
+        out = torch.empty(1, nq * hd, dtype=dt, device=DEV)
+        ops.attention_plain(q, out, nq, nkv, hd, kp, v_pool, table, 64, torch.tensor([L - 1], dtype=torch.int32, device=DEV),
+                            torch.zeros(1, dtype=torch.int32, device=DEV), 1.0, 0)
+        for kvh in range(nkv):
+            got = out[0].view(nq, hd)[kvh * 2].float().cpu()
+            torch.testing.assert_close(got, vs[0][target, kvh].float(), rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("nq,nkv,hd,n_rot", [(4, 2, 16, 16), (6, 1, 32, 32), (3, 3, 48, 24), (2, 2, 128, 128)])
+@pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("use_norm", [True, False])
+def test_qk_norm_rope_cache(nq, nkv, hd, n_rot, dt, use_norm):
+    ops = _ops()
+    T = 7
+    positions = [0, 1, 63, 64, 130, 5, 64]
+    seqs = [0, 0, 0, 0, 0, 1, 1]
+    table = torch.tensor([[4, 2, 6], [1, 5, 0]], dtype=torch.int32, device=DEV)
+    width = (nq + 2 * nkv) * hd
+    qkv = _rand(T, width, seed=13, dtype=dt)
+    orig = qkv.clone()
+    qn, kn = 1 + 0.2 * _rand(hd, seed=14), 1 + 0.2 * _rand(hd, seed=15)
+    freqs, _ = plain.rope_frequencies(n_rot, 10000.0)
+    ang = (torch.arange(200, dtype=torch.float32)[:, None] * freqs[None, :]).double()
+    cos, sin = torch.cos(ang).float().to(DEV), torch.sin(ang).float().to(DEV)
+    k_pool = torch.zeros(7, nkv, 64, hd, dtype=dt, device=DEV)
+    v_pool = torch.zeros_like(k_pool)
+    ops.qk_norm_rope_cache(qkv, 0, nq * hd, (nq + nkv) * hd, nq, nkv, hd, qn if use_norm else None,
+                           kn if use_norm else None, 1e-6, cos, sin, n_rot,
+                           torch.tensor(positions, dtype=torch.int32, device=DEV),
+                           torch.tensor(seqs, dtype=torch.int32, device=DEV), k_pool, v_pool, table, 64)
+    o = orig.float().cpu()
+    pos_t = torch.tensor(positions)
+    q = o[:, : nq * hd].view(T, nq, hd)
+    k = o[:, nq * hd:(nq + nkv) * hd].view(T, nkv, hd)
+    v = o[:, (nq + nkv) * hd:].view(T, nkv, hd)
+    if use_norm:
+        q, k = plain.rmsnorm(q, qn.cpu(), 1e-6), plain.rmsnorm(k, kn.cpu(), 1e-6)
+    q, k = plain.rope_neox(q, pos_t, freqs, 1.0, n_rot), plain.rope_neox(k, pos_t, freqs, 1.0, n_rot)
+    tol = _tol(dt)
+    torch.testing.assert_close(qkv[:, : nq * hd].float().cpu().view(T, nq, hd), q, **tol)
+    assert torch.equal(qkv[:, nq * hd:], orig[:, nq * hd:])  # k and v rows of the buffer are untouched
+    for t in range(T):
+        page = int(table[seqs[t], positions[t] // 64])
+        torch.testing.assert_close(k_pool[page, :, positions[t] % 64].float().cpu(), k[t], **tol)
+        torch.testing.assert_close(v_pool[page, :, positions[t] % 64].float().cpu(), v[t], **tol)
+    written = {(int(table[seqs[t], positions[t] // 64]), positions[t] % 64) for t in range(T)}
+    mask = torch.ones(7, 64, dtype=torch.bool)
+    for pg, off in written:
+        mask[pg, off] = False
+    assert (k_pool.float().cpu().abs().sum((1, 3))[mask] == 0).all()  # nothing else was written
+
+
+def test_refused_sizes_are_errors_not_wrong_results():
+    ops = _ops()
+    from skyla_kernel_b200.kernels import KernelError
+    with pytest.raises(KernelError, match="head size"):
+        ops.attention_plain(_rand(1, 1024), torch.empty(1, 1024, device=DEV), 1, 1, 1024,
+                            torch.zeros(1, 1, 64, 1024, device=DEV), torch.zeros(1, 1, 64, 1024, device=DEV),
+                            torch.zeros(1, 1, dtype=torch.int32, device=DEV), 64,
+                            torch.zeros(1, dtype=torch.int32, device=DEV), torch.zeros(1, dtype=torch.int32, device=DEV), 1.0)
+    with pytest.raises(KernelError):
+        ops.rmsnorm(torch.zeros(2, 8), torch.ones(8), 1e-5, torch.zeros(2, 8))  # host tensors: no CPU path
+    with pytest.raises(KernelError, match="float32 or bfloat16"):
+        ops.linear_plain(torch.zeros(2, 8, dtype=torch.float16, device=DEV), torch.zeros(4, 8, dtype=torch.float16, device=DEV),
+                         torch.zeros(2, 4, dtype=torch.float16, device=DEV))
+
+
+def test_greedy_takes_lowest_index_among_equals():
+    ops = _ops()
+    logits = torch.full((3, 509), -1.0, device=DEV)
+    logits[0, [400, 17, 300]] = 2.0
+    logits[1, 508] = 5.0
+    logits[2, 0] = 0.5
+    out = torch.empty(3, dtype=torch.int32, device=DEV)
+    ops.sample(logits, out)
+    assert out.tolist() == [17, 508, 0]
+
+
+@pytest.mark.parametrize("temperature,top_k,top_p", [(0.8, 0, 1.0), (1.0, 5, 1.0), (0.6, 40, 0.95), (1.3, 0, 0.7)])
+def test_sampling_matches_its_plain_twin(temperature, top_k, top_p):
+    ops = _ops()
+    V, R = 1031, 24
+    logits = _rand(R, V, seed=21, scale=2.5)
+    req = torch.arange(R, dtype=torch.int32, device=DEV) % 5
+    steps = torch.arange(R, dtype=torch.int32, device=DEV) // 5
+    out = torch.empty(R, dtype=torch.int32, device=DEV)
+    ops.sample(logits, out, temperature, top_k, top_p, 1234567890123, req, steps)
+    for r in range(R):
+        scores, keep = plain.sample_scores(logits[r].cpu(), temperature, top_k, top_p, 1234567890123,
+                                           int(req[r]), int(steps[r]))
+        tok = int(out[r])
+        assert keep[tok], f"row {r}: token {tok} is outside the kept set"
+        best = np.max(scores)
+        assert scores[tok] >= best - 1e-4, f"row {r}: drew {tok} ({scores[tok]}), twin's best is {best}"
+    # a row's draw depends on its own keys only, not on its neighbours
+    out2 = torch.empty(1, dtype=torch.int32, device=DEV)
+    ops.sample(logits[7:8], out2, temperature, top_k, top_p, 1234567890123, req[7:8].contiguous(), steps[7:8].contiguous())
+    assert int(out2[0]) == int(out[7])
+
+
+def test_sampling_frequencies_follow_softmax():
+    ops = _ops()
+    logits = torch.tensor([[0.0, 3.0, 1.0, 2.9, -1.0, 2.0]], device=DEV).repeat(4000, 1)
+    out = torch.empty(4000, dtype=torch.int32, device=DEV)
+    ops.sample(logits, out, 1.0, 0, 1.0, 77, torch.zeros(4000, dtype=torch.int32, device=DEV),
+               torch.arange(4000, dtype=torch.int32, device=DEV))
+    freq = torch.bincount(out.long().cpu(), minlength=6).double() / 4000
+    assert (freq - torch.softmax(logits[0].double().cpu(), 0)).abs().max() < 0.03
+
+
+def test_fill_normal_and_bandwidth_probe():
+    ops = _ops()
+    for dt in (torch.float32, torch.bfloat16):
+        t = torch.empty(1_000_001, dtype=dt, device=DEV)
+        ops.fill_normal(t, 1.0, 0.02, 5)
+        assert abs(t.float().mean().item() - 1.0) < 1e-3 and abs(t.float().std().item() - 0.02) < 1e-3
+        t2 = torch.empty_like(t)
+        ops.fill_normal(t2, 1.0, 0.02, 5)
+        assert torch.equal(t, t2)
+    buf = torch.ones(1 << 22, dtype=torch.int32, device=DEV)
+    sink = torch.zeros(1, dtype=torch.int32, device=DEV)
+    ops.bandwidth_read(buf, 296, sink)
+    torch.cuda.synchronize()
+    assert int(sink[0]) == 0

@@ -1,0 +1,81 @@
+"""bin/trace_run replays the same requests whole, with the last 32 tokens one by one,
+and in batches of unequal lengths, in both precisions, against the plain implementation."""
+import json
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import plain_qwen3 as plain
+from helpers import TINY, assert_close, make_folder, random_tokens
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _replay(folder, dtype, steps, out, max_tokens):
+    proc = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", folder, "--dtype", dtype,
+                           "--out", out, "--max-tokens", str(max_tokens)],
+                          input="".join(json.dumps(s) + "\n" for s in steps), capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert proc.stdout.split("\n")[:-1] == [f"done {s['step']}" for s in steps]
+    return proc
+
+
+def _read(out, step, vocab):
+    return torch.from_numpy(np.fromfile(os.path.join(out, f"{step}.f32"), dtype="<f4").reshape(-1, vocab).copy())
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_replay_three_ways(tmp_path, name, dtype):
+    folder = make_folder(tmp_path, name)
+    cfg, w = plain.read_folder(folder)
+    V = cfg["vocab_size"]
+    lens = [45, 100, 64, 33, 129]
+    reqs = {f"r{i}": random_tokens(n, V, 70 + i) for i, n in enumerate(lens)}
+    refs = {k: plain.forward(cfg, w, v) for k, v in reqs.items()}
+    steps, expect = [], {}   # expect[step] = list of (request, first place, count)
+    n = 0
+    # 1) each request alone and whole
+    for k, toks in reqs.items():
+        steps.append({"step": n, "entries": [{"id": k + "w", "tokens": toks, "want": list(range(len(toks)))}], "end": [k + "w"]})
+        expect[n] = [(k, 0, len(toks))]; n += 1
+    # 2) whole minus 32, then the last 32 one by one
+    for k, toks in reqs.items():
+        head = len(toks) - 32
+        steps.append({"step": n, "entries": [{"id": k + "d", "tokens": toks[:head], "want": list(range(head))}], "end": []})
+        expect[n] = [(k, 0, head)]; n += 1
+        for t in range(head, len(toks)):
+            steps.append({"step": n, "entries": [{"id": k + "d", "tokens": [toks[t]], "want": [0]}],
+                          "end": [k + "d"] if t == len(toks) - 1 else []})
+            expect[n] = [(k, t, 1)]; n += 1
+    # 3) batches of unequal lengths; shorter requests end earlier; a second batch reuses what the first gave back
+    for batch in (["r0", "r1", "r2"], ["r3", "r4", "r0"]):
+        cut = {k: max(1, len(reqs[k]) - 20 - 7 * i) for i, k in enumerate(batch)}
+        steps.append({"step": n, "entries": [{"id": k + "b", "tokens": reqs[k][:cut[k]], "want": [cut[k] - 1]} for k in batch], "end": []})
+        expect[n] = [(k, cut[k] - 1, 1) for k in batch]; n += 1
+        t = 0
+        while True:
+            live = [k for k in batch if cut[k] + t < len(reqs[k])]
+            if not live:
+                break
+            ending = [k + "b" for k in live if cut[k] + t == len(reqs[k]) - 1]
+            steps.append({"step": n, "entries": [{"id": k + "b", "tokens": [reqs[k][cut[k] + t]], "want": [0]} for k in live], "end": ending})
+            expect[n] = [(k, cut[k] + t, 1) for k in live]; n += 1
+            t += 1
+    # one step that wants nothing writes no file
+    steps.append({"step": n, "entries": [{"id": "q", "tokens": [1, 2, 3], "want": []}], "end": ["q"]})
+    out = str(tmp_path / f"out_{dtype}")
+    _replay(folder, dtype, steps, out, max_tokens=64 * 7)  # the second batch only fits because the first gave its pages back
+    assert not os.path.exists(os.path.join(out, f"{n}.f32"))
+    for s, parts in expect.items():
+        got = _read(out, s, V)
+        o = 0
+        for k, first, count in parts:
+            assert_close(got[o:o + count], refs[k][first:first + count], dtype, f"{name} {dtype} step {s} request {k}")
+            o += count
+        assert o == got.shape[0]
