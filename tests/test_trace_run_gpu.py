@@ -54,7 +54,10 @@ def test_replay_three_ways(tmp_path, name, dtype):
                           "end": [k + "d"] if t == len(toks) - 1 else []})
             expect[n] = [(k, t, 1)]; n += 1
     # 3) batches of unequal lengths; shorter requests end earlier; a second batch reuses what the first gave back
+    first_batch_step = n
     for batch in (["r0", "r1", "r2"], ["r3", "r4", "r0"]):
+        if batch[0] == "r3":
+            second_batch_step = n
         cut = {k: max(1, len(reqs[k]) - 20 - 7 * i) for i, k in enumerate(batch)}
         steps.append({"step": n, "entries": [{"id": k + "b", "tokens": reqs[k][:cut[k]], "want": [cut[k] - 1]} for k in batch], "end": []})
         expect[n] = [(k, cut[k] - 1, 1) for k in batch]; n += 1
@@ -72,10 +75,19 @@ def test_replay_three_ways(tmp_path, name, dtype):
     out = str(tmp_path / f"out_{dtype}")
     _replay(folder, dtype, steps, out, max_tokens=64 * 7)  # the second batch only fits because the first gave its pages back
     assert not os.path.exists(os.path.join(out, f"{n}.f32"))
-    for s, parts in expect.items():
+    # rows of one request in one way of replaying are compared as one block
+    blocks = {}
+    for s, parts in sorted(expect.items()):
         got = _read(out, s, V)
         o = 0
         for k, first, count in parts:
-            assert_close(got[o:o + count], refs[k][first:first + count], dtype, f"{name} {dtype} step {s} request {k}")
+            mode = 0 if s < len(reqs) else (1 if s < first_batch_step else 2 + (s >= second_batch_step))
+            blocks.setdefault((mode, k), []).append((first, got[o:o + count]))
             o += count
         assert o == got.shape[0]
+    assert len(blocks) == 5 + 5 + 6
+    for (mode, k), rows in blocks.items():
+        places = [f + i for f, g in rows for i in range(g.shape[0])]
+        assert places == list(range(places[0], places[0] + len(places)))
+        assert_close(torch.cat([g for _, g in rows]), refs[k][places[0]:places[-1] + 1], dtype,
+                     f"{name} {dtype} way {mode} request {k}")
