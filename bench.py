@@ -1,0 +1,289 @@
+"""Decode and prefill throughput of the Qwen3-8B-shaped model with random weights.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--layers L]
+
+One "step" is one decode step of the batch.  Prints ONE JSON line: decoded tokens
+per second on the device (`value`), the same through the Python entry point with
+host tokens in and out (`e2e`), a 2,048-token prefill, the decode step's HBM
+roofline fraction, and decode at batch 1 and 64 (`points`).  The library runs on
+one GPU only; for --gpus N > 1 it says so and exits with 2.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+# layer sizes of the Qwen3-8B shape (the third benchmark configuration)
+QWEN3_8B = dict(hidden_size=4096, num_hidden_layers=36, num_attention_heads=32, num_key_value_heads=8,
+                head_dim=128, intermediate_size=12288, vocab_size=151936, rope_theta=1000000.0,
+                rms_norm_eps=1e-6, max_position_embeddings=40960, tie_word_embeddings=False)
+PROMPT_LEN = 2048
+CONTEXT = 4096
+FALLBACK_HBM_GBS = 6650.0       # an earlier measurement on this pool, used when no peaks file exists
+FALLBACK_BF16_TFLOPS = 1590.0
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        try:
+            with open(path) as f:
+                d = json.load(f)
+            return float(d["hbm_gbs"]), float(d["bf16_tflops"]), "measured"
+        except (OSError, ValueError, KeyError):
+            pass
+    return FALLBACK_HBM_GBS, FALLBACK_BF16_TFLOPS, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi in the background during the timed region (reads only)."""
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index=0):
+        self.proc = None
+        self.index = index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.strip().splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0])); mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, parts[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def build_model(layers: int, max_tokens: int, max_slots: int, seed: int = 0):
+    """The 8B-shaped model with seeded random weights drawn on the device."""
+    import torch
+    import skyla_kernel_b200 as skyla
+    from skyla_kernel_b200.config import Qwen3Config
+    from skyla_kernel_b200.engine import Engine, declared_tensors
+    from skyla_kernel_b200.kernels import ops
+    cfg = Qwen3Config(**dict(QWEN3_8B, num_hidden_layers=layers))
+    decl = declared_tensors(cfg.to_spec())
+    tensors = {}
+    for i, (name, d) in enumerate(decl.items()):
+        t = torch.empty(d.shape, dtype=torch.bfloat16, device="cuda:0")
+        if d.init == "norm":
+            ops.fill_normal(t, 1.0, 0.02, seed * 100003 + i)
+        else:
+            ops.fill_normal(t, 0.0, 0.02, seed * 100003 + i)
+        tensors[name] = t
+    engine = Engine(cfg, tensors, "bfloat16", max_tokens=max_tokens, max_slots=max_slots)
+    del tensors
+    torch.cuda.empty_cache()
+    return skyla.Model(engine), cfg
+
+
+def random_prompts(n, length, vocab, seed):
+    import torch
+    g = torch.Generator().manual_seed(seed)
+    return [torch.randint(0, vocab, (length,), generator=g).tolist() for _ in range(n)]
+
+
+def prefill_flops(cfg, T, n_logit_rows=1):
+    H, nq, nkv, hd, I, V, L = (cfg.hidden_size, cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim,
+                               cfg.intermediate_size, cfg.vocab_size, cfg.num_hidden_layers)
+    per_tok = 2 * L * (H * (nq + 2 * nkv) * hd + nq * hd * H + 3 * H * I)
+    attn = L * 4 * nq * hd * (T * (T + 1) // 2)  # causal: QK^T and PV over the visible half
+    return per_tok * T + attn + 2 * n_logit_rows * H * V
+
+
+def device_decode(model, batch, prompt_len, steps, warmup, vocab, sampler):
+    """Prefill `batch` prompts, then time `steps` decode steps on the device with CUDA events."""
+    import torch
+    from skyla_kernel_b200.engine import StepItem
+    from skyla_kernel_b200.kernels import ops
+    eng = model.engine
+    prompts = random_prompts(batch, prompt_len, vocab, 11 + batch)
+    slots = [eng.alloc_slot() for _ in range(batch)]
+    toks = []
+    chunk = max(1, 16384 // prompt_len)  # prompts per prefill step
+    for i in range(0, batch, chunk):
+        items = [StepItem(slots[j], prompts[j], [prompt_len - 1]) for j in range(i, min(batch, i + chunk))]
+        logits = eng.step(items)
+        toks += torch.argmax(logits, dim=-1).tolist()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    kv_bytes = 0
+    launches0 = 0
+    for s in range(warmup + steps):
+        if s == warmup:
+            torch.cuda.synchronize()
+            launches0 = ops.LAUNCHES
+            sampler.start()
+            start.record()
+        if s >= warmup:
+            kv_bytes += sum(eng.cache.length(sl) + 1 for sl in slots) * eng.cache.bytes_per_token()
+        logits = eng.step([StepItem(sl, [t], [0]) for sl, t in zip(slots, toks)])
+        toks = torch.argmax(logits, dim=-1).tolist() if s < warmup else toks  # timed steps feed fixed tokens
+    end.record()
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    ms = start.elapsed_time(end)
+    launches = ops.LAUNCHES - launches0
+    ctx_end = eng.cache.length(slots[0])
+    for sl in slots:
+        eng.free_slot(sl)
+    return {"ms_per_step": ms / steps, "tok_s": batch * steps / (ms / 1e3), "kv_bytes_per_step": kv_bytes / steps,
+            "launches": launches, "clocks": clocks, "context_end": ctx_end}
+
+
+class _NoSampler:
+    def start(self): pass
+    def stop(self): return None
+
+
+def e2e_decode(model, batch, prompt_len, steps, warmup, vocab):
+    """The same through model.generate: host token ids in, host token ids out every step."""
+    import torch
+    prompts = random_prompts(batch, prompt_len, vocab, 23 + batch)
+    marks = {}
+
+    def on_step(step, live):
+        # step 0 is the prefill; the tokens of step s have reached the host when this runs
+        if step == warmup:
+            marks["t0"] = time.perf_counter()
+        if step == warmup + steps:
+            marks["t1"] = time.perf_counter()
+
+    model.generate(prompts, max_new_tokens=warmup + steps + 1, stop_ids=[], max_batch=batch, on_step=on_step)
+    dt = marks["t1"] - marks["t0"]
+    pages = -(-(prompt_len + warmup + steps) // model.page_size)
+    groups = len(model.engine.cache.groups)
+    h2d = 4 * (3 * batch + 3 * batch + (batch + 1) + batch + groups * batch * pages)
+    return {"value": batch * steps / dt, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4 * batch,
+            "ms_per_step": dt / steps * 1e3}
+
+
+def prefill_once(model, cfg, length, reps=3, warmup=1):
+    import torch
+    from skyla_kernel_b200.engine import StepItem
+    eng = model.engine
+    prompt = random_prompts(1, length, cfg.vocab_size, 5)[0]
+    times = []
+    for r in range(warmup + reps):
+        s = eng.alloc_slot()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        a.record()
+        eng.step([StepItem(s, prompt, [length - 1])])
+        b.record()
+        torch.cuda.synchronize()
+        eng.free_slot(s)
+        if r >= warmup:
+            times.append(a.elapsed_time(b))
+    return statistics.median(times)
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours")
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--layers", type=int, default=QWEN3_8B["num_hidden_layers"])
+    ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
+    args = ap.parse_args()
+
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "the reference is a Rust workspace with Vulkan/Metal backends: no pip-installable package, "
+                          "no cargo/rustc and no graphics stack on this box"}))
+        return 0
+    if args.gpus != 1:
+        print(f"bench.py: this library runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    args.warmup = max(args.warmup, 3)
+
+    import torch
+    hbm_gbs, bf16_tflops, peak_kind = peaks()
+    batches = [args.batch] + ([] if args.no_points else [b for b in (1, 64) if b != args.batch])
+    max_tokens = max(batches) * (-(-CONTEXT // 64) * 64)
+    t_build = time.time()
+    model, cfg = build_model(args.layers, max_tokens=max_tokens, max_slots=max(batches))
+    print(f"[bench] model built in {time.time() - t_build:.1f} s: {args.layers} layers, "
+          f"{model.engine.weight_bytes() / 1e9:.2f} GB of weights per step", file=sys.stderr, flush=True)
+    V = cfg.vocab_size
+
+    # prefill of 2,048 tokens
+    pre_ms = prefill_once(model, cfg, PROMPT_LEN)
+    pre_flops = prefill_flops(cfg, PROMPT_LEN)
+    prefill = {"value": PROMPT_LEN / (pre_ms / 1e3), "tokens": PROMPT_LEN, "ms": pre_ms,
+               "frac": pre_flops / (pre_ms / 1e3) / (bf16_tflops * 1e12)}
+    print(f"[bench] prefill {PROMPT_LEN} tokens: {pre_ms:.1f} ms", file=sys.stderr, flush=True)
+
+    sampler = ClockSampler()
+    main_run = device_decode(model, args.batch, PROMPT_LEN, args.steps, args.warmup, V, sampler)
+    print(f"[bench] decode batch {args.batch}: {main_run['ms_per_step']:.3f} ms/step", file=sys.stderr, flush=True)
+    e2e = e2e_decode(model, args.batch, PROMPT_LEN, args.steps, args.warmup, V)
+    points = {}
+    for b in batches[1:]:
+        r = device_decode(model, b, PROMPT_LEN, args.steps, args.warmup, V, _NoSampler())
+        points[f"decode_b{b}"] = r["tok_s"]
+        print(f"[bench] decode batch {b}: {r['ms_per_step']:.3f} ms/step", file=sys.stderr, flush=True)
+    points[f"decode_b{args.batch}"] = main_run["tok_s"]
+
+    step_bytes = model.engine.weight_bytes() + main_run["kv_bytes_per_step"]
+    achieved = step_bytes / (main_run["ms_per_step"] / 1e3) / 1e9
+    line = {
+        "metric": "decode tokens/s, Qwen3-8B shape bf16, batch %d, 2048-token prompts" % args.batch,
+        "value": main_run["tok_s"], "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": main_run["ms_per_step"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic: seeded random weights N(0,0.02), norms 1+N(0,0.02), uniform token ids",
+        "config": {
+            "model": "Qwen3-8B shape", "global_batch": args.batch, "seq_len": CONTEXT, "parallelism": "single GPU",
+            "layers": args.layers, "layers_of_config": QWEN3_8B["num_hidden_layers"],
+            "hidden_size": cfg.hidden_size, "num_attention_heads": cfg.num_attention_heads,
+            "num_key_value_heads": cfg.num_key_value_heads, "head_dim": cfg.head_dim,
+            "intermediate_size": cfg.intermediate_size, "vocab_size": cfg.vocab_size,
+            "prompt_len": PROMPT_LEN, "context_at_end_of_timing": main_run["context_end"],
+            "kv_cache": "bf16 paged, 64 positions per page", "l2": "inputs larger than L2 (weights read every step)",
+            "peaks": peak_kind,
+        },
+        "e2e": e2e, "gpu_launches": main_run["launches"], "clocks": main_run["clocks"],
+        "prefill": prefill,
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_gbs, "unit": "GB/s", "frac": achieved / hbm_gbs},
+        "points": points,
+    }
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

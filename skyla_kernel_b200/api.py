@@ -61,11 +61,12 @@ class Model:
     def generate(self, prompts: Sequence[Sequence[int]], max_new_tokens: Union[int, Sequence[int]] = 16,
                  temperature: float = 0.0, top_k: int = 0, top_p: float = 1.0, seed: int = 0,
                  stop_ids: Optional[Sequence[int]] = None, max_batch: int = 64,
-                 emit_stop: bool = False, return_reasons: bool = False):
+                 emit_stop: bool = False, return_reasons: bool = False, on_step=None):
         """Token ids in, token ids out; one result per prompt, in order.
 
         ``temperature=0`` is greedy.  ``stop_ids=None`` takes the configuration's
-        end-of-sequence ids; pass ``[]`` for none.
+        end-of-sequence ids; pass ``[]`` for none.  ``on_step(step, live)`` is called on
+        the host after every step's tokens have arrived (measurement hooks in here).
         """
         params = SamplingParams(temperature, top_k, top_p, seed)
         sampler = self._samplers.get(params)
@@ -77,7 +78,7 @@ class Model:
             max_new_tokens = [max_new_tokens] * len(prompts)
         reqs = [Request(list(p), int(n), tuple(stop_ids)) for p, n in zip(prompts, max_new_tokens)]
         backend = _Backend(self, sampler)
-        done = generate(backend, reqs, max_batch=max_batch, emit_stop=emit_stop)
+        done = generate(backend, reqs, max_batch=max_batch, emit_stop=emit_stop, on_step=on_step)
         if return_reasons:
             return [d.tokens for d in done], [d.reason for d in done]
         return [d.tokens for d in done]

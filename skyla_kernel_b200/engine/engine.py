@@ -11,6 +11,7 @@ from __future__ import annotations
 
 from typing import Dict, List, Optional, Sequence
 
+import numpy as np
 import torch
 
 from ..cache import CacheError, CacheFull, SequenceCache
@@ -88,9 +89,12 @@ class Engine:
         for it in items:
             if len(it.tokens) == 0:
                 raise ValueError(f"slot {it.slot}: a step must bring at least one token")
-            for t in it.tokens:
-                if not 0 <= int(t) < self.vocab_size:
-                    raise ValueError(f"token {t} is outside the vocabulary (0..{self.vocab_size - 1})")
+            arr = np.asarray(it.tokens)
+            if arr.dtype.kind not in "iu":
+                raise ValueError(f"slot {it.slot}: tokens must be integers")
+            if arr.min() < 0 or arr.max() >= self.vocab_size:
+                bad = int(arr[(arr < 0) | (arr >= self.vocab_size)][0])
+                raise ValueError(f"token {bad} is outside the vocabulary (0..{self.vocab_size - 1})")
         growth = [(it.slot, len(it.tokens)) for it in items]
         self.cache.reserve(growth)
         with torch.cuda.device(self.rt.device):

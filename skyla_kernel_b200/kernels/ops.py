@@ -73,7 +73,13 @@ def _fn(module: str, name: str, argtypes):
     return f
 
 
+#: kernel launches made through this module since import (bench.py reports the difference)
+LAUNCHES = 0
+
+
 def _check(module: str, rc: int):
+    global LAUNCHES
+    LAUNCHES += 1
     if rc != 0:
         msg = build.load(module).skyla_error_message().decode("utf-8", "replace")
         raise KernelError(msg or f"{module}: error {rc}")
