@@ -1,0 +1,376 @@
+// Tensor-core matrix product for sm_100a: y = x W^T with bfloat16 operands and
+// 32-bit accumulation, x[M,K] (tokens) and W[N,K] (rows are outputs) both
+// K-major.  It takes the place of the reference's matvec/matmul shaders
+// (skyla-shaders/shaders/matmul.comp:113-185, matvec_q8_0.comp:33-76), including
+// their fused epilogues: residual add (ACCUM, skyla-engine/src/graph.rs:110-112)
+// and silu(gate)*up (skyla-shaders/shaders/silu_mul.comp:15-24).
+//
+// The weight is the 128-row operand of tcgen05.mma and the tokens are the N
+// operand (16..256 wide), so the same kernel serves a 2,048-token prompt and a
+// batch of a few decoded tokens that only has to stream the weight once:
+//   warp 0    one lane issues TMA loads (cp.async.bulk.tensor, 128-byte swizzle)
+//             of a [128 x 64] weight tile and a [BN x 64] token tile per stage;
+//   warp 1    allocates TMEM; one lane issues tcgen05.mma (M=128, N=BN, K=16),
+//             accumulating in TMEM, and commits each stage back to the loader;
+//   warps 2-5 read the accumulator with tcgen05.ld (lane = output feature,
+//             column = token) and write the epilogue.
+// grid = (feature tiles, token tiles, K splits).  Every mbarrier wait is bounded:
+// on a timeout the CTA records an error code, drains what it started, frees its
+// TMEM and returns.
+#include <cuda.h>
+
+#include <cstring>
+
+#include "common.cuh"
+using namespace skyla;
+SKYLA_EXPORT_ERROR_MESSAGE()
+
+namespace {
+
+enum Mode : int {
+  kStoreBf16 = 0,   // y[tok, f] = acc                     (bfloat16)
+  kStoreF32 = 1,    // y[tok, f] = acc                     (float)
+  kAccumF32 = 2,    // y[tok, f] += acc                    (float: the residual sum)
+  kGluBf16 = 3,     // y[tok, f] = silu(gate) * up         (bfloat16; W rows in groups of 128 gate, 128 up)
+  kPartialF32 = 4,  // y[split, tok, f] = acc of this K split (float scratch)
+};
+
+constexpr int BM = 128;  // weight rows per tile
+constexpr int BK = 64;   // K elements per stage: one 128-byte swizzle row
+constexpr int kThreads = 192;
+constexpr int kSmemBudget = 200 * 1024;
+constexpr long long kWaitCycles = 2000000000LL;  // about a second
+
+template <int BN, int MODE>
+struct Cfg {
+  static constexpr int kATiles = MODE == kGluBf16 ? 2 : 1;
+  static constexpr int kABytes = kATiles * BM * BK * 2;
+  static constexpr int kBBytes = BN * BK * 2;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kStagesRaw = kSmemBudget / kStageBytes;
+  static constexpr int kStages = kStagesRaw > 12 ? 12 : kStagesRaw;
+  static constexpr int kTmemColsRaw = kATiles * BN;
+  static constexpr int kTmemCols = kTmemColsRaw < 32 ? 32 : kTmemColsRaw;
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 256 /*barriers*/;
+  static_assert(kTmemCols <= 512 && (kTmemCols & (kTmemCols - 1)) == 0, "TMEM columns");
+  static_assert(kStages >= 2, "pipeline depth");
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+// Bounded wait: false on a timeout or when another role of this CTA gave up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          int* error_flag, int code) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  while (true) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (*abort_flag) return false;
+    if (clock64() - t0 > kWaitCycles) {
+      *abort_flag = 1;
+      if (error_flag != nullptr) atomicCAS(error_flag, 0, code);
+      return false;
+    }
+  }
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
+}
+// K-major operand tile in shared memory, rows of 128 bytes, 128-byte swizzle:
+// 8-row groups are 1024 bytes apart.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t saddr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)1 << 16;            // leading byte offset: unused for swizzled K-major
+  d |= (uint64_t)(1024 >> 4) << 32;  // stride byte offset between 8-row groups
+  d |= (uint64_t)1 << 46;            // descriptor version of sm_100
+  d |= (uint64_t)2 << 61;            // SWIZZLE_128B
+  return d;
+}
+__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a), "l"(b), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr) : "memory");
+}
+
+struct GemmArgs {
+  void* y;
+  int64_t ldy;            // elements between token rows of y
+  int64_t split_stride;   // elements between K splits of y (partial mode)
+  int M, N, K;            // tokens, output features (after gating), reduction length
+  int k_blocks_per_split;
+  int* error_flag;
+};
+
+template <int BN, int MODE>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+               const GemmArgs a) {
+  using C = Cfg<BN, MODE>;
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ volatile int abort_flag;
+
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t bars = base + C::kStages * C::kStageBytes;
+  auto full_bar = [&](int s) { return bars + 8u * s; };
+  auto empty_bar = [&](int s) { return bars + 8u * (C::kStages + s); };
+  const uint32_t tmem_full_bar = bars + 8u * (2 * C::kStages);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int f_tile = blockIdx.x, t_tile = blockIdx.y, split = blockIdx.z;
+  const int total_kb = (a.K + BK - 1) / BK;
+  const int kb0 = split * a.k_blocks_per_split;
+  const int n_kb = min(a.k_blocks_per_split, total_kb - kb0);
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    for (int s = 0; s < C::kStages; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    mbar_init(tmem_full_bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                 ::"r"(smem_u32(&tmem_base_slot)), "r"((uint32_t)C::kTmemCols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = tmem_base_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      uint32_t armed = 0, armed_parity = 0;  // per stage: a load is in flight, and its phase
+      int kb = 0;
+      for (; kb < n_kb; ++kb) {
+        const int s = kb % C::kStages;
+        const uint32_t phase = (kb / C::kStages) & 1;
+        if (!mbar_wait(empty_bar(s), phase ^ 1, &abort_flag, a.error_flag, 1)) break;
+        const uint32_t sa = base + s * C::kStageBytes, sb = sa + C::kABytes;
+        mbar_expect_tx(full_bar(s), C::kStageBytes);
+        tma_load_2d(sa, &map_w, full_bar(s), (kb0 + kb) * BK, f_tile * BM * C::kATiles);
+        tma_load_2d(sb, &map_x, full_bar(s), (kb0 + kb) * BK, t_tile * BN);
+        armed |= 1u << s;
+        armed_parity = (armed_parity & ~(1u << s)) | (phase << s);
+      }
+      if (kb < n_kb) {
+        // gave up: let the loads already issued land before the CTA's memory goes away
+        for (int s = 0; s < C::kStages; ++s)
+          if (armed & (1u << s)) {
+            const long long t0 = clock64();
+            while (!mbar_try_wait(full_bar(s), (armed_parity >> s) & 1) && clock64() - t0 < kWaitCycles) {}
+          }
+      }
+    }
+  } else if (warp == 1) {
+    // -------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      // instruction descriptor: D=f32, A=B=bf16, both K-major, N=BN, M=128
+      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) |
+                             ((uint32_t)(BM >> 4) << 24);
+      for (int kb = 0; kb < n_kb; ++kb) {
+        const int s = kb % C::kStages;
+        const uint32_t phase = (kb / C::kStages) & 1;
+        if (!mbar_wait(full_bar(s), phase, &abort_flag, a.error_flag, 2)) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t sa = base + s * C::kStageBytes, sb = sa + C::kABytes;
+        const uint64_t da = umma_desc(sa), db = umma_desc(sb);
+#pragma unroll
+        for (int k = 0; k < BK / 16; ++k) {
+          const uint32_t acc = (kb > 0 || k > 0) ? 1u : 0u;
+          umma_bf16(tmem_base, da + 2 * k, db + 2 * k, idesc, acc);
+          if (MODE == kGluBf16)  // the up rows: the next 128 rows of the tile, into the next BN columns
+            umma_bf16(tmem_base + BN, umma_desc(sa + BM * BK * 2) + 2 * k, db + 2 * k, idesc, acc);
+        }
+        umma_commit(empty_bar(s));  // the stage is free once these MMAs have read it
+      }
+      umma_commit(tmem_full_bar);   // always: the teardown waits for it
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue
+    const int quad = warp & 3;                   // the TMEM lanes this warp may read
+    const int f = f_tile * BM + quad * 32 + lane;  // output feature of this thread
+    if (n_kb > 0 && mbar_wait(tmem_full_bar, 0, &abort_flag, a.error_flag, 3)) {
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16);
+      const int tok0 = t_tile * BN;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 16) {
+        if (tok0 + c0 >= a.M) break;  // uniform for the warp
+        uint32_t r[16], u[16];
+        tmem_ld16(taddr + c0, r);
+        if (MODE == kGluBf16) tmem_ld16(taddr + BN + c0, u);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if (f < a.N) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int tok = tok0 + c0 + j;
+            if (tok >= a.M) break;
+            const float v = __uint_as_float(r[j]);
+            if (MODE == kStoreBf16) {
+              ((__nv_bfloat16*)a.y)[(int64_t)tok * a.ldy + f] = __float2bfloat16_rn(v);
+            } else if (MODE == kStoreF32) {
+              ((float*)a.y)[(int64_t)tok * a.ldy + f] = v;
+            } else if (MODE == kAccumF32) {
+              float* p = (float*)a.y + (int64_t)tok * a.ldy + f;
+              *p += v;
+            } else if (MODE == kGluBf16) {
+              const float up = __uint_as_float(u[j]);
+              ((__nv_bfloat16*)a.y)[(int64_t)tok * a.ldy + f] = __float2bfloat16_rn(v / (1.0f + expf(-v)) * up);
+            } else {
+              ((float*)a.y)[(int64_t)split * a.split_stride + (int64_t)tok * a.ldy + f] = v;
+            }
+          }
+        }
+      }
+    }
+  }
+  // ------------------------------------------------------------------ teardown
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    if (lane == 0 && n_kb > 0) {  // the accumulator must be idle before its columns are freed
+      const long long t0 = clock64();
+      while (!mbar_try_wait(tmem_full_bar, 0) && clock64() - t0 < kWaitCycles) {}
+    }
+    __syncwarp();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)C::kTmemCols) : "memory");
+  }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+  }
+  return fn;
+}
+
+template <int BN, int MODE>
+int launch(const CUtensorMap& mw, const CUtensorMap& mx, const GemmArgs& a, dim3 grid, cudaStream_t stream) {
+  using C = Cfg<BN, MODE>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         C::kSmemBytes);
+    if (e != cudaSuccess) return fail(kLaunchFailed, "gemm_tc: cannot reserve %d bytes of shared memory: %s",
+                                      C::kSmemBytes, cudaGetErrorString(e));
+    configured = true;
+  }
+  gemm_tc_kernel<BN, MODE><<<grid, kThreads, C::kSmemBytes, stream>>>(mw, mx, a);
+  return check_launch("gemm_tc");
+}
+
+template <int MODE>
+int launch_bn(int bn, const CUtensorMap& mw, const CUtensorMap& mx, const GemmArgs& a, dim3 grid, cudaStream_t s) {
+  switch (bn) {
+    case 16: return launch<16, MODE>(mw, mx, a, grid, s);
+    case 32: return launch<32, MODE>(mw, mx, a, grid, s);
+    case 64: return launch<64, MODE>(mw, mx, a, grid, s);
+    case 128: return launch<128, MODE>(mw, mx, a, grid, s);
+    case 256:
+      if (MODE == kGluBf16) break;
+      return launch<MODE == kGluBf16 ? 128 : 256, MODE>(mw, mx, a, grid, s);
+  }
+  return fail(kBadArgument, "gemm_tc: no kernel for a token tile of %d", bn);
+}
+}  // namespace
+
+// Fills a 128-byte tensor map for a row-major bfloat16 matrix [rows, cols] with
+// `ld` elements between rows; boxes are [box_rows x 64 columns], 128-byte swizzle.
+extern "C" int skyla_tensor_map_bf16(void* out, const void* ptr, uint64_t rows, uint64_t cols, uint64_t ld,
+                                     uint32_t box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr) return fail(kLaunchFailed, "tensor map: the driver does not offer cuTensorMapEncodeTiled");
+  if (((uintptr_t)ptr) % 16 || (ld * 2) % 16) return fail(kBadArgument, "tensor map: base or row stride is not a multiple of 16 bytes");
+  if (box_rows == 0 || box_rows > 256) return fail(kBadArgument, "tensor map: box of %u rows", box_rows);
+  alignas(64) CUtensorMap m;
+  const cuuint64_t dims[2] = {cols, rows};
+  const cuuint64_t strides[1] = {ld * 2};
+  const cuuint32_t box[2] = {BK, box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(kLaunchFailed, "tensor map: cuTensorMapEncodeTiled failed with %d", (int)r);
+  memcpy(out, &m, sizeof(m));
+  return kOk;
+}
+
+extern "C" int skyla_gemm_tc_stages(int bn, int mode) {
+  if (mode == kGluBf16) return bn == 16 ? Cfg<16, kGluBf16>::kStages : bn == 32 ? Cfg<32, kGluBf16>::kStages
+                             : bn == 64 ? Cfg<64, kGluBf16>::kStages : Cfg<128, kGluBf16>::kStages;
+  return bn == 16 ? Cfg<16, 0>::kStages : bn == 32 ? Cfg<32, 0>::kStages : bn == 64 ? Cfg<64, 0>::kStages
+       : bn == 128 ? Cfg<128, 0>::kStages : Cfg<256, 0>::kStages;
+}
+
+// map_w: weight [rows, K] with boxes of 128 rows (256 in gated mode); map_x: tokens [M, K] with boxes of bn rows.
+extern "C" int skyla_gemm_tc(const void* map_w, const void* map_x, void* y, int64_t ldy, int64_t split_stride,
+                             int M, int N, int K, int bn, int mode, int splits, int* error_flag,
+                             cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return kOk;
+  if (K <= 0 || K % 8) return fail(kBadArgument, "gemm_tc: K=%d must be a positive multiple of 8", K);
+  if (mode < 0 || mode > 4) return fail(kBadArgument, "gemm_tc: unknown epilogue %d", mode);
+  if (splits < 1 || (splits > 1 && mode != kPartialF32)) return fail(kBadArgument, "gemm_tc: %d K splits need the partial epilogue", splits);
+  const int total_kb = (K + BK - 1) / BK;
+  const int per = (total_kb + splits - 1) / splits;
+  if ((splits - 1) * per >= total_kb) return fail(kBadArgument, "gemm_tc: %d K splits leave one empty (K=%d)", splits, K);
+  alignas(64) CUtensorMap mw, mx;
+  memcpy(&mw, map_w, sizeof(mw));
+  memcpy(&mx, map_x, sizeof(mx));
+  GemmArgs a{y, ldy, split_stride, M, N, K, per, error_flag};
+  dim3 grid((N + BM - 1) / BM, (M + bn - 1) / bn, splits);
+  if (grid.y > 65535 || grid.z > 65535) return fail(kBadArgument, "gemm_tc: grid too large");
+  switch (mode) {
+    case kStoreBf16: return launch_bn<kStoreBf16>(bn, mw, mx, a, grid, stream);
+    case kStoreF32: return launch_bn<kStoreF32>(bn, mw, mx, a, grid, stream);
+    case kAccumF32: return launch_bn<kAccumF32>(bn, mw, mx, a, grid, stream);
+    case kGluBf16: return launch_bn<kGluBf16>(bn, mw, mx, a, grid, stream);
+    default: return launch_bn<kPartialF32>(bn, mw, mx, a, grid, stream);
+  }
+}

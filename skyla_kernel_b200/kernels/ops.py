@@ -77,6 +77,12 @@ def _fn(module: str, name: str, argtypes):
 LAUNCHES = 0
 
 
+def _check_nolaunch(module: str, rc: int):
+    if rc != 0:
+        msg = build.load(module).skyla_error_message().decode("utf-8", "replace")
+        raise KernelError(msg or f"{module}: error {rc}")
+
+
 def _check(module: str, rc: int):
     global LAUNCHES
     LAUNCHES += 1
@@ -145,6 +151,107 @@ def linear_plain(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, mode: int = 
              c_int, c_int, c_void_p])
     _check("linear_plain", f(_ptr(x), dtype_code(x), _rows(x, "x"), _ptr(w), dtype_code(w), m, n, k,
                              _ptr(y), dtype_code(y), _rows(y, "y"), mode, glu_group or n, _stream()))
+    return y
+
+
+# ---------------------------------------------------------- tensor-core linear
+TC_STORE_BF16, TC_STORE_F32, TC_ACCUM_F32, TC_GLU_BF16, TC_PARTIAL_F32 = 0, 1, 2, 3, 4
+TC_TOKEN_TILES = (16, 32, 64, 128, 256)
+
+_ERROR_FLAGS = {}
+
+
+def error_flag(device) -> torch.Tensor:
+    """One int32 per device that kernels with bounded waits set when a wait ran out."""
+    dev = torch.device(device)
+    t = _ERROR_FLAGS.get(dev)
+    if t is None:
+        t = _ERROR_FLAGS[dev] = torch.zeros(1, dtype=torch.int32, device=dev)
+    return t
+
+
+def check_device_errors(device) -> None:
+    """Raise if a kernel gave up on a wait since the last check (synchronizes)."""
+    t = _ERROR_FLAGS.get(torch.device(device))
+    if t is not None:
+        code = int(t.item())
+        if code:
+            t.zero_()
+            raise KernelError(f"a kernel's bounded wait ran out (code {code}); its results are not valid")
+
+
+class TensorMap:
+    """A TMA descriptor of a row-major bfloat16 matrix, boxes of [box_rows x 64]."""
+
+    __slots__ = ("buf", "key", "keep")
+
+    def __init__(self, t: torch.Tensor, box_rows: int):
+        _cuda(t)
+        if t.dtype != torch.bfloat16 or t.dim() != 2:
+            raise KernelError("tensor maps are built for 2-D bfloat16 tensors")
+        ld = _rows(t, "tensor map")
+        self.buf = ctypes.create_string_buffer(128)
+        self.keep = t
+        f = _fn("gemm_tc", "skyla_tensor_map_bf16",
+                [c_void_p, c_void_p, c_uint64, c_uint64, c_uint64, ctypes.c_uint32])
+        _check_nolaunch("gemm_tc", f(self.buf, _ptr(t), t.shape[0], t.shape[1], ld, box_rows))
+
+
+_X_MAPS = {}
+
+
+def activation_map(x: torch.Tensor, box_rows: int) -> TensorMap:
+    """Tensor maps of workspace buffers are few (the buffers are reused) and cached."""
+    key = (x.data_ptr(), x.shape[0], x.shape[1], x.stride(0), box_rows)
+    m = _X_MAPS.get(key)
+    if m is None:
+        if len(_X_MAPS) > 4096:
+            _X_MAPS.clear()
+        m = _X_MAPS[key] = TensorMap(x, box_rows)
+        m.keep = None  # do not pin workspace memory; the key holds the address
+    return m
+
+
+def tc_linear_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
+    """Whether the tensor-core kernel takes these operands (bfloat16, 16-byte rows)."""
+    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.dim() == 2 and w.is_contiguous()
+            and x.shape[1] % 8 == 0 and x.stride(1) == 1 and (x.shape[0] == 1 or x.stride(0) % 8 == 0)
+            and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def token_tile(m: int, gated: bool = False) -> int:
+    for bn in TC_TOKEN_TILES:
+        if m <= bn:
+            return min(bn, 128) if gated else bn
+    return 128 if gated else 256
+
+
+def gemm_tc(x: torch.Tensor, w_map: TensorMap, n_out: int, y: torch.Tensor, mode: int, splits: int = 1,
+            bn: Optional[int] = None) -> torch.Tensor:
+    """y = x W^T on the tensor cores.  ``w_map`` has boxes of 128 rows (256 when gated).
+
+    ``mode``: TC_STORE_BF16 / TC_STORE_F32 / TC_ACCUM_F32 / TC_GLU_BF16, or
+    TC_PARTIAL_F32 with ``y`` of shape [splits, tokens, n_out] float32.
+    """
+    m, k = x.shape
+    bn = bn or token_tile(m, mode == TC_GLU_BF16)
+    want = {TC_STORE_BF16: torch.bfloat16, TC_GLU_BF16: torch.bfloat16}.get(mode, torch.float32)
+    if y.dtype != want:
+        raise KernelError(f"gemm_tc: epilogue {mode} writes {want}, y is {y.dtype}")
+    if mode == TC_PARTIAL_F32:
+        if y.dim() != 3 or tuple(y.shape) != (splits, m, n_out) or not y.is_contiguous():
+            raise KernelError(f"gemm_tc: partial output must be contiguous [{splits}, {m}, {n_out}]")
+        ldy, sstride = n_out, m * n_out
+    else:
+        if y.shape[0] != m or y.shape[1] != n_out:
+            raise KernelError(f"gemm_tc: y {tuple(y.shape)} is not [{m}, {n_out}]")
+        ldy, sstride = _rows(y, "y"), 0
+    xm = activation_map(x, bn)
+    f = _fn("gemm_tc", "skyla_gemm_tc",
+            [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int, c_int, c_int, c_int, c_int, c_int,
+             c_void_p, c_void_p])
+    _check("gemm_tc", f(w_map.buf, xm.buf, _ptr(y), ldy, sstride, m, n_out, k, bn, mode, splits,
+                        _ptr(error_flag(x.device)), _stream()))
     return y
 
 

@@ -30,7 +30,7 @@ from .linear import ACCUMULATE, STORE, Linear
 
 
 class GQAttention(Part):
-    kernel_modules = ("linear_plain", "attn_prep", "attention_plain")
+    kernel_modules = Linear.kernel_modules + ("attn_prep", "attention_plain")
 
     def __init__(self, spec, rt):
         super().__init__(spec, rt)

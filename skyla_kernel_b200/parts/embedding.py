@@ -42,7 +42,7 @@ class TokenEmbedding(Part):
 
 
 class LinearHead(Part):
-    kernel_modules = ("linear_plain",)
+    kernel_modules = Linear.kernel_modules
 
     def __init__(self, spec, rt):
         super().__init__(spec, rt)

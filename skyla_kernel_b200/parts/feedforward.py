@@ -28,7 +28,7 @@ def fuse_gate_up(gate: torch.Tensor, up: torch.Tensor, group: int) -> torch.Tens
 
 
 class SwiGLU(Part):
-    kernel_modules = ("linear_plain",)
+    kernel_modules = Linear.kernel_modules
 
     def __init__(self, spec, rt):
         super().__init__(spec, rt)
@@ -44,15 +44,12 @@ class SwiGLU(Part):
         return {t["gate_proj"]: TensorDecl((i, h)), t["up_proj"]: TensorDecl((i, h)),
                 t["down_proj"]: TensorDecl((h, i))}
 
-    def gate_up_group(self) -> int:
-        return self.inter
-
     def load(self, tensors) -> None:
         t = self.spec.tensors
         gate, up = tensors[t["gate_proj"]], tensors[t["up_proj"]]
         if gate.dtype != up.dtype:
             gate, up = gate.to(torch.float32), up.to(torch.float32)
-        group = self.gate_up_group()
+        group = Linear.gated_group_for(self.rt, gate)
         self.gate_up = Linear(self.rt.matrix(fuse_gate_up(gate, up, group)), self.rt, gated_group=group)
         self.down = Linear(self.rt.matrix(tensors[t["down_proj"]]), self.rt)
 

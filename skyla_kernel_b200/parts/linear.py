@@ -15,7 +15,10 @@ STORE, ACCUMULATE, GATED = ops.STORE, ops.ACCUMULATE, ops.GATED
 
 
 class Linear:
-    kernel_modules = ("linear_plain",)
+    kernel_modules = ("linear_plain", "gemm_tc")
+
+    #: rows of gate and of up that alternate in a fused gate/up matrix for the tensor-core kernel
+    TC_GATED_GROUP = 128
 
     def __init__(self, weight: torch.Tensor, rt, gated_group: int = 0):
         """``weight`` on the device; ``gated_group`` > 0 marks a fused gate/up matrix."""
@@ -24,10 +27,34 @@ class Linear:
         self.gated_group = gated_group
         self.n_in = weight.shape[1]
         self.n_out = weight.shape[0] // 2 if gated_group else weight.shape[0]
+        self._map = None
+        self.tensor_cores = (not rt.full_precision and weight.dtype == torch.bfloat16 and self.n_in % 8 == 0
+                             and weight.is_contiguous() and weight.data_ptr() % 16 == 0
+                             and (not gated_group or gated_group == self.TC_GATED_GROUP))
+
+    @classmethod
+    def gated_group_for(cls, rt, gate: torch.Tensor) -> int:
+        """The gate/up grouping to fuse with: 128 where the tensor-core kernel will run, else one block."""
+        n, k = gate.shape
+        fast = not rt.full_precision and gate.dtype == torch.bfloat16 and n % cls.TC_GATED_GROUP == 0 and k % 8 == 0
+        return cls.TC_GATED_GROUP if fast else n
+
+    def weight_map(self):
+        if self._map is None:
+            self._map = ops.TensorMap(self.weight, 256 if self.gated_group else 128)
+        return self._map
 
     def forward(self, x: torch.Tensor, y: torch.Tensor, mode: int = STORE) -> torch.Tensor:
         if self.gated_group:
             mode = GATED
+        if self.tensor_cores and ops.tc_linear_ok(x, self.weight):
+            if mode == GATED:
+                tc = ops.TC_GLU_BF16
+            elif mode == ACCUMULATE:
+                tc = ops.TC_ACCUM_F32
+            else:
+                tc = ops.TC_STORE_BF16 if y.dtype == torch.bfloat16 else ops.TC_STORE_F32
+            return ops.gemm_tc(x, self.weight_map(), self.n_out, y, tc)
         return ops.linear_plain(x, self.weight, y, mode, self.gated_group)
 
     def bytes(self) -> int:

@@ -280,3 +280,73 @@ def test_fill_normal_and_bandwidth_probe():
     ops.bandwidth_read(buf, 296, sink)
     torch.cuda.synchronize()
     assert int(sink[0]) == 0
+
+
+# ------------------------------------------------------------- tensor-core GEMM
+@pytest.mark.parametrize("m,n,k", [(1, 131, 80), (8, 256, 64), (16, 128, 4096), (17, 509, 96), (70, 96, 160),
+                                   (130, 384, 1032), (300, 200, 264), (1000, 640, 512)])
+def test_gemm_tc_store_and_accumulate(m, n, k):
+    ops = _ops()
+    x = _rand(m, k, seed=31, dtype=torch.bfloat16)
+    w = _rand(n, k, seed=32, dtype=torch.bfloat16, scale=0.1)
+    ref = (x.double() @ w.double().T)
+    scale = ref.abs().max().item()
+    wm = ops.TensorMap(w, 128)
+    y32 = torch.full((m, n), float("nan"), dtype=torch.float32, device=DEV)
+    ops.gemm_tc(x, wm, n, y32, ops.TC_STORE_F32)
+    assert (y32.double() - ref).abs().max().item() <= 2e-5 * scale + 1e-6
+    y16 = torch.empty(m, n, dtype=torch.bfloat16, device=DEV)
+    ops.gemm_tc(x, wm, n, y16, ops.TC_STORE_BF16)
+    assert torch.equal(y16, y32.to(torch.bfloat16))
+    acc = _rand(m, n, seed=33)
+    before = acc.clone()
+    ops.gemm_tc(x, wm, n, acc, ops.TC_ACCUM_F32)
+    assert (acc.double() - before.double() - ref).abs().max().item() <= 2e-5 * scale + 1e-5
+    # every token tile width gives the same numbers for the rows it holds
+    for bn in ops.TC_TOKEN_TILES:
+        y = torch.empty(m, n, dtype=torch.float32, device=DEV)
+        ops.gemm_tc(x, wm, n, y, ops.TC_STORE_F32, bn=bn)
+        assert (y.double() - ref).abs().max().item() <= 2e-5 * scale + 1e-6, f"token tile {bn}"
+    ops.check_device_errors(DEV)
+
+
+@pytest.mark.parametrize("m,n,k,splits", [(8, 128, 4096, 4), (3, 300, 1032, 3), (64, 256, 512, 8), (20, 96, 160, 2)])
+def test_gemm_tc_split_k(m, n, k, splits):
+    ops = _ops()
+    x = _rand(m, k, seed=34, dtype=torch.bfloat16)
+    w = _rand(n, k, seed=35, dtype=torch.bfloat16, scale=0.1)
+    ref = (x.double() @ w.double().T)
+    part = torch.full((splits, m, n), float("nan"), dtype=torch.float32, device=DEV)
+    ops.gemm_tc(x, ops.TensorMap(w, 128), n, part, ops.TC_PARTIAL_F32, splits=splits)
+    assert (part.double().sum(0) - ref).abs().max().item() <= 2e-5 * ref.abs().max().item() + 1e-6
+    ops.check_device_errors(DEV)
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 128, 64), (9, 256, 80), (70, 384, 160), (200, 128, 520)])
+def test_gemm_tc_gated(m, n, k):
+    ops = _ops()
+    from skyla_kernel_b200.parts.feedforward import fuse_gate_up
+    x = _rand(m, k, seed=36, dtype=torch.bfloat16)
+    g, u = _rand(n, k, seed=37, dtype=torch.bfloat16, scale=0.2), _rand(n, k, seed=38, dtype=torch.bfloat16, scale=0.2)
+    w = fuse_gate_up(g, u, 128)
+    y = torch.empty(m, n, dtype=torch.bfloat16, device=DEV)
+    ops.gemm_tc(x, ops.TensorMap(w, 256), n, y, ops.TC_GLU_BF16)
+    gd, ud = x.double() @ g.double().T, x.double() @ u.double().T
+    ref = gd / (1 + torch.exp(-gd)) * ud
+    torch.testing.assert_close(y.double(), ref, rtol=1e-2, atol=1e-2 * ref.abs().max().item())
+    plain_y = torch.empty_like(y)
+    ops.linear_plain(x, w, plain_y, ops.GATED, 128)  # the plain twin on the same fused matrix
+    torch.testing.assert_close(y.float(), plain_y.float(), rtol=2e-2, atol=1e-3)
+    ops.check_device_errors(DEV)
+
+
+def test_gemm_tc_refuses_what_it_cannot_do():
+    ops = _ops()
+    from skyla_kernel_b200.kernels import KernelError
+    x = _rand(4, 100, seed=1, dtype=torch.bfloat16)   # K not a multiple of 8: rows are not 16-byte aligned
+    w = _rand(128, 100, seed=2, dtype=torch.bfloat16)
+    assert not ops.tc_linear_ok(x, w)
+    with pytest.raises(KernelError):
+        ops.TensorMap(w, 128)
+    with pytest.raises(KernelError):
+        ops.TensorMap(_rand(128, 64, seed=3), 128)  # float32
