@@ -1,0 +1,436 @@
+// Tensor-core attention over the paged bfloat16 cache, for prompts and for single
+// decoded tokens.  It computes what the plain kernel computes
+// (skyla-ref/src/model.rs:149-165): softmax(q.k * scale) over the visible
+// positions, times v, with the softmax in 32-bit and online across blocks of keys
+// (skyla-shaders/shaders/attention.comp:81-99).
+//
+// A warp owns a tile of 16 query rows and walks the cache 16 keys at a time:
+//   S = Q K^T   mma.sync m16n8k16 (bf16 in, f32 out); K rows come straight from
+//               global memory as 16-byte loads into B fragments.  The order of a
+//               head's elements inside a 32-wide block is permuted the same way
+//               in the Q and the K fragments, which a dot product does not notice.
+//   P = exp2(S*scale*log2e - max), running max/sum per row in 32-bit
+//   O += P V    P re-packed from the S accumulators as the A operand; V rows also
+//               come from global memory as contiguous 16..32-byte pieces, with the
+//               output columns permuted so that each thread's piece is contiguous;
+//               the permutation is undone when O is written.
+// No shared-memory staging: every key/value byte is loaded once per warp that
+// needs it, 16 bytes at a time.
+//
+// Decode: one CTA per (key/value head, sequence, split of the context); the 16 rows
+// are the query heads that share the key/value head (grouped-query attention), so
+// the cache is read once for all of them, as the reference does with N_REP
+// (attention.comp:60-79).  The CTA's four warps take pages in turn and are merged
+// in shared memory; splits are aligned to absolute positions and merged by a
+// second kernel in fixed order (skyla-shaders/shaders/attention_merge.comp:17-41).
+// Prefill: one CTA per (64 new tokens of one sequence, query head), a warp per 16
+// tokens, causal by row.
+#include "common.cuh"
+using namespace skyla;
+SKYLA_EXPORT_ERROR_MESSAGE()
+
+namespace {
+typedef __nv_bfloat16 bf16;
+constexpr float kLog2e = 1.4426950408889634f;
+
+template <int HD>
+struct Shape {
+  static constexpr int KB32 = HD / 32;
+  static constexpr bool TAIL16 = (HD % 32) == 16;
+  static constexpr int NQ = KB32 * 4 + (TAIL16 ? 2 : 0);  // 32-bit registers of a row's fragment
+  static constexpr int NV = HD / 16;                      // registers of a thread's piece of a V row
+  static constexpr int NT = HD / 8;                       // 8-wide output column tiles
+  static_assert(HD % 16 == 0 && HD >= 16, "head size in steps of 16");
+};
+
+__device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// A row's fragment: thread t of a quad takes elements 32*kb + 8t .. +7 of each
+// 32-wide block (and 4t .. +3 of a trailing 16-wide one).
+template <int HD>
+__device__ __forceinline__ void load_row(const bf16* __restrict__ row, int t, uint32_t (&out)[Shape<HD>::NQ]) {
+  using S = Shape<HD>;
+#pragma unroll
+  for (int kb = 0; kb < S::KB32; ++kb) {
+    const uint4 v = *reinterpret_cast<const uint4*>(row + 32 * kb + 8 * t);
+    out[4 * kb] = v.x; out[4 * kb + 1] = v.y; out[4 * kb + 2] = v.z; out[4 * kb + 3] = v.w;
+  }
+  if (S::TAIL16) {
+    const uint2 v = *reinterpret_cast<const uint2*>(row + 32 * S::KB32 + 4 * t);
+    out[4 * S::KB32] = v.x; out[4 * S::KB32 + 1] = v.y;
+  }
+}
+// A thread's piece of a V row: columns g*HD/8 .. (g+1)*HD/8 - 1.
+template <int HD>
+__device__ __forceinline__ void load_v(const bf16* __restrict__ row, int g, uint32_t (&out)[Shape<HD>::NV]) {
+  constexpr int NV = Shape<HD>::NV;
+  const bf16* p = row + g * (HD / 8);
+  if (NV % 4 == 0) {
+#pragma unroll
+    for (int i = 0; i < NV / 4; ++i) {
+      const uint4 v = reinterpret_cast<const uint4*>(p)[i];
+      out[4 * i] = v.x; out[4 * i + 1] = v.y; out[4 * i + 2] = v.z; out[4 * i + 3] = v.w;
+    }
+  } else if (NV % 2 == 0) {
+#pragma unroll
+    for (int i = 0; i < NV / 2; ++i) {
+      const uint2 v = reinterpret_cast<const uint2*>(p)[i];
+      out[2 * i] = v.x; out[2 * i + 1] = v.y;
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < NV; ++i) out[i] = reinterpret_cast<const uint32_t*>(p)[i];
+  }
+}
+
+template <int HD>
+struct RowState {
+  float m[2], l[2];                 // running maximum (log2 units) and this thread's share of the sum
+  float o[Shape<HD>::NT][4];        // output accumulators, columns permuted
+  __device__ __forceinline__ void init() {
+    m[0] = m[1] = -INFINITY; l[0] = l[1] = 0.f;
+#pragma unroll
+    for (int n = 0; n < Shape<HD>::NT; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+  }
+};
+
+// 16 keys starting at absolute position key0; k16/v16 point at their rows for one
+// key/value head (row stride HD).  Rows g and g+8 of the tile see positions lo..hi.
+template <int HD>
+__device__ __forceinline__ void attend16(const uint32_t (&qa)[Shape<HD>::NQ], const uint32_t (&qb)[Shape<HD>::NQ],
+                                         const bf16* __restrict__ k16, const bf16* __restrict__ v16, int key0,
+                                         int lo0, int hi0, int lo1, int hi1, float scale_log2, RowState<HD>& st,
+                                         int g, int t) {
+  using S = Shape<HD>;
+  uint32_t kf[2][S::NQ], vf[4][S::NV];
+  load_row<HD>(k16 + (size_t)g * HD, t, kf[0]);
+  load_row<HD>(k16 + (size_t)(8 + g) * HD, t, kf[1]);
+  load_v<HD>(v16 + (size_t)(2 * t) * HD, g, vf[0]);
+  load_v<HD>(v16 + (size_t)(2 * t + 1) * HD, g, vf[1]);
+  load_v<HD>(v16 + (size_t)(8 + 2 * t) * HD, g, vf[2]);
+  load_v<HD>(v16 + (size_t)(8 + 2 * t + 1) * HD, g, vf[3]);
+
+  float s[2][4];
+#pragma unroll
+  for (int j = 0; j < 2; ++j) {
+    s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+#pragma unroll
+    for (int kb = 0; kb < S::KB32; ++kb) {
+      mma_bf16(s[j], qa[4 * kb], qb[4 * kb], qa[4 * kb + 1], qb[4 * kb + 1], kf[j][4 * kb], kf[j][4 * kb + 1]);
+      mma_bf16(s[j], qa[4 * kb + 2], qb[4 * kb + 2], qa[4 * kb + 3], qb[4 * kb + 3], kf[j][4 * kb + 2], kf[j][4 * kb + 3]);
+    }
+    if (S::TAIL16)
+      mma_bf16(s[j], qa[4 * S::KB32], qb[4 * S::KB32], qa[4 * S::KB32 + 1], qb[4 * S::KB32 + 1],
+               kf[j][4 * S::KB32], kf[j][4 * S::KB32 + 1]);
+  }
+  float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+  for (int j = 0; j < 2; ++j) {
+    const int p = key0 + 8 * j + 2 * t;
+    s[j][0] = (p >= lo0 && p <= hi0) ? s[j][0] * scale_log2 : -INFINITY;
+    s[j][1] = (p + 1 >= lo0 && p + 1 <= hi0) ? s[j][1] * scale_log2 : -INFINITY;
+    s[j][2] = (p >= lo1 && p <= hi1) ? s[j][2] * scale_log2 : -INFINITY;
+    s[j][3] = (p + 1 >= lo1 && p + 1 <= hi1) ? s[j][3] * scale_log2 : -INFINITY;
+    mx0 = fmaxf(mx0, fmaxf(s[j][0], s[j][1]));
+    mx1 = fmaxf(mx1, fmaxf(s[j][2], s[j][3]));
+  }
+  mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+  mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+  mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+  mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+  const float mn0 = fmaxf(st.m[0], mx0), mn1 = fmaxf(st.m[1], mx1);
+  const float ref0 = mn0 == -INFINITY ? 0.f : mn0, ref1 = mn1 == -INFINITY ? 0.f : mn1;
+  const float al0 = exp2f(st.m[0] - ref0), al1 = exp2f(st.m[1] - ref1);
+  st.m[0] = mn0; st.m[1] = mn1;
+  float sum0 = 0.f, sum1 = 0.f;
+#pragma unroll
+  for (int j = 0; j < 2; ++j) {
+    s[j][0] = exp2f(s[j][0] - ref0); s[j][1] = exp2f(s[j][1] - ref0);
+    s[j][2] = exp2f(s[j][2] - ref1); s[j][3] = exp2f(s[j][3] - ref1);
+    sum0 += s[j][0] + s[j][1];
+    sum1 += s[j][2] + s[j][3];
+  }
+  st.l[0] = st.l[0] * al0 + sum0;
+  st.l[1] = st.l[1] * al1 + sum1;
+  const uint32_t a0 = pack_bf16(s[0][0], s[0][1]), a1 = pack_bf16(s[0][2], s[0][3]);
+  const uint32_t a2 = pack_bf16(s[1][0], s[1][1]), a3 = pack_bf16(s[1][2], s[1][3]);
+#pragma unroll
+  for (int n = 0; n < S::NT; ++n) {
+    st.o[n][0] *= al0; st.o[n][1] *= al0; st.o[n][2] *= al1; st.o[n][3] *= al1;
+    const uint32_t sel = (n & 1) ? 0x7632u : 0x5410u;
+    const uint32_t b0 = __byte_perm(vf[0][n >> 1], vf[1][n >> 1], sel);
+    const uint32_t b1 = __byte_perm(vf[2][n >> 1], vf[3][n >> 1], sel);
+    mma_bf16(st.o[n], a0, a1, a2, a3, b0, b1);
+  }
+}
+
+// Accumulator (n, i) of thread (g, t) holds row g + 8*(i>>1), column:
+template <int HD>
+__device__ __forceinline__ int out_col(int n, int i, int t) { return (2 * t + (i & 1)) * (HD / 8) + n; }
+
+struct PagedKV {
+  const bf16* k; const bf16* v; const int32_t* pages; int max_pages, page_size, nkv;
+};
+
+template <int HD>
+__device__ __forceinline__ void attend_pages(const uint32_t (&qa)[Shape<HD>::NQ], const uint32_t (&qb)[Shape<HD>::NQ],
+                                             const PagedKV& kv, const int32_t* seq_pages, int kvh, int page_begin,
+                                             int page_end, int page_step, int lo, int hi, int lo0, int hi0,
+                                             int lo1, int hi1, float scale_log2, RowState<HD>& st, int g, int t) {
+  // lo..hi: the positions any row of this warp sees; the same in all lanes, so the
+  // warp stays converged for mma.sync
+  for (int pg = page_begin; pg < page_end; pg += page_step) {
+    const size_t row0 = ((size_t)seq_pages[pg] * kv.nkv + kvh) * kv.page_size;
+    for (int off = 0; off < kv.page_size; off += 16) {
+      const int key0 = pg * kv.page_size + off;
+      if (key0 > hi) break;
+      if (key0 + 15 < lo) continue;
+      attend16<HD>(qa, qb, kv.k + (row0 + off) * HD, kv.v + (row0 + off) * HD, key0, lo0, hi0, lo1, hi1,
+                   scale_log2, st, g, t);
+    }
+  }
+}
+
+// ------------------------------------------------------------------------ decode
+struct DecodeArgs {
+  const bf16* q; int64_t ldq; float* part; int n_splits, pages_per_split;
+  int nq, nkv; PagedKV kv; const int32_t* tok_pos; float scale; int window;
+};
+
+template <int HD>
+__global__ void __launch_bounds__(128) attn_decode_kernel(DecodeArgs a) {
+  using S = Shape<HD>;
+  extern __shared__ float smem[];  // [4 warps][16 rows][HD] outputs, then [4][16] m and l
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const int kvh = blockIdx.x, b = blockIdx.y, split = blockIdx.z;
+  const int G = a.nq / a.nkv;
+  const int pos = a.tok_pos[b];
+  const int first = a.window > 0 ? max(0, pos - a.window + 1) : 0;
+  const int ps = a.kv.page_size;
+  const int page_begin = max(split * a.pages_per_split, first / ps);
+  const int page_end = min((split + 1) * a.pages_per_split, pos / ps + 1);
+
+  uint32_t qa[S::NQ], qb[S::NQ];
+#pragma unroll
+  for (int i = 0; i < S::NQ; ++i) qa[i] = qb[i] = 0u;
+  const bf16* qrow = a.q + (int64_t)b * a.ldq + (int64_t)kvh * G * HD;
+  if (g < G) load_row<HD>(qrow + g * HD, t, qa);
+  if (g + 8 < G) load_row<HD>(qrow + (g + 8) * HD, t, qb);
+  const int hi0 = g < G ? pos : -1, hi1 = g + 8 < G ? pos : -1;
+
+  RowState<HD> st;
+  st.init();
+  attend_pages<HD>(qa, qb, a.kv, a.kv.pages + (int64_t)b * a.kv.max_pages, kvh, page_begin + warp, page_end, 4,
+                   first, pos, first, hi0, first, hi1, a.scale * kLog2e, st, g, t);
+  // this thread's shares of the row sums -> whole rows
+  st.l[0] += __shfl_xor_sync(0xffffffffu, st.l[0], 1); st.l[0] += __shfl_xor_sync(0xffffffffu, st.l[0], 2);
+  st.l[1] += __shfl_xor_sync(0xffffffffu, st.l[1], 1); st.l[1] += __shfl_xor_sync(0xffffffffu, st.l[1], 2);
+
+  float* so = smem + (size_t)warp * 16 * HD;
+  float* sm = smem + (size_t)4 * 16 * HD + warp * 16;
+  float* sl = sm + 64;
+#pragma unroll
+  for (int n = 0; n < S::NT; ++n)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) so[(g + 8 * (i >> 1)) * HD + out_col<HD>(n, i, t)] = st.o[n][i];
+  if (t == 0) { sm[g] = st.m[0]; sm[g + 8] = st.m[1]; sl[g] = st.l[0]; sl[g + 8] = st.l[1]; }
+  __syncthreads();
+  // merge the four warps, fixed order; one partial per (head, split): m, l, acc[HD]
+  const float* am = smem + (size_t)4 * 16 * HD;
+  const float* al = am + 64;
+  for (int idx = threadIdx.x; idx < G * HD; idx += 128) {
+    const int r = idx / HD, c = idx % HD;
+    float M = -INFINITY;
+    for (int w = 0; w < 4; ++w) M = fmaxf(M, am[w * 16 + r]);
+    const float ref = M == -INFINITY ? 0.f : M;
+    float acc = 0.f, L = 0.f;
+    for (int w = 0; w < 4; ++w) {
+      const float f = exp2f(am[w * 16 + r] - ref);
+      acc += f * smem[((size_t)w * 16 + r) * HD + c];
+      L += f * al[w * 16 + r];
+    }
+    float* out = a.part + (((size_t)b * a.nq + kvh * G + r) * a.n_splits + split) * (HD + 2);
+    out[2 + c] = acc;
+    if (c == 0) { out[0] = M; out[1] = L; }
+  }
+}
+
+struct MergeArgs { const float* part; bf16* out; int64_t ldo; int nq, n_splits, hd; };
+
+__global__ void __launch_bounds__(128) attn_merge_kernel(MergeArgs a) {
+  const int h = blockIdx.x, b = blockIdx.y;
+  const float* p = a.part + ((size_t)b * a.nq + h) * a.n_splits * (a.hd + 2);
+  float M = -INFINITY;
+  for (int s = 0; s < a.n_splits; ++s) M = fmaxf(M, p[(size_t)s * (a.hd + 2)]);
+  float total = 0.f;
+  for (int s = 0; s < a.n_splits; ++s) total += exp2f(p[(size_t)s * (a.hd + 2)] - M) * p[(size_t)s * (a.hd + 2) + 1];
+  for (int c = threadIdx.x; c < a.hd; c += blockDim.x) {
+    float o = 0.f;
+    for (int s = 0; s < a.n_splits; ++s) o += exp2f(p[(size_t)s * (a.hd + 2)] - M) * p[(size_t)s * (a.hd + 2) + 2 + c];
+    a.out[(int64_t)b * a.ldo + (int64_t)h * a.hd + c] = __float2bfloat16_rn(o / total);
+  }
+}
+
+// ----------------------------------------------------------------------- prefill
+struct PrefillArgs {
+  const bf16* q; int64_t ldq; bf16* out; int64_t ldo;
+  int nq, nkv; PagedKV kv; const int32_t* tok_pos; const int32_t* tile_seq; const int32_t* tile_tok0;
+  const int32_t* tile_rows; float scale; int window;
+};
+
+template <int HD>
+__global__ void __launch_bounds__(128) attn_prefill_kernel(PrefillArgs a) {
+  using S = Shape<HD>;
+  extern __shared__ float smem[];  // [4 warps][16 rows][HD]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const int tile = blockIdx.x, h = blockIdx.y, kvh = h / (a.nq / a.nkv);
+  const int b = a.tile_seq[tile], tok0 = a.tile_tok0[tile], rows = a.tile_rows[tile];
+  const int r0 = warp * 16 + g, r1 = r0 + 8;
+  if (warp * 16 >= rows) return;  // whole warp idle
+  uint32_t qa[S::NQ], qb[S::NQ];
+#pragma unroll
+  for (int i = 0; i < S::NQ; ++i) qa[i] = qb[i] = 0u;
+  int hi0 = -1, hi1 = -1, lo0 = 0, lo1 = 0;
+  if (r0 < rows) {
+    hi0 = a.tok_pos[tok0 + r0];
+    lo0 = a.window > 0 ? max(0, hi0 - a.window + 1) : 0;
+    load_row<HD>(a.q + (int64_t)(tok0 + r0) * a.ldq + (int64_t)h * HD, t, qa);
+  }
+  if (r1 < rows) {
+    hi1 = a.tok_pos[tok0 + r1];
+    lo1 = a.window > 0 ? max(0, hi1 - a.window + 1) : 0;
+    load_row<HD>(a.q + (int64_t)(tok0 + r1) * a.ldq + (int64_t)h * HD, t, qb);
+  }
+  // the warp's 16 rows are consecutive positions: pages from its lowest visible key to its last row
+  int wlo = hi0 >= 0 ? lo0 : 0x7fffffff, whi = max(hi0, hi1);
+  if (hi1 >= 0) wlo = min(wlo, lo1);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    wlo = min(wlo, __shfl_xor_sync(0xffffffffu, wlo, o));
+    whi = max(whi, __shfl_xor_sync(0xffffffffu, whi, o));
+  }
+  const int ps = a.kv.page_size;
+  RowState<HD> st;
+  st.init();
+  // rows that do not exist see nothing: lo > hi
+  attend_pages<HD>(qa, qb, a.kv, a.kv.pages + (int64_t)b * a.kv.max_pages, kvh, wlo / ps, whi / ps + 1, 1,
+                   wlo, whi, hi0 >= 0 ? lo0 : 1, hi0 >= 0 ? hi0 : 0, hi1 >= 0 ? lo1 : 1, hi1 >= 0 ? hi1 : 0,
+                   a.scale * kLog2e, st, g, t);
+  st.l[0] += __shfl_xor_sync(0xffffffffu, st.l[0], 1); st.l[0] += __shfl_xor_sync(0xffffffffu, st.l[0], 2);
+  st.l[1] += __shfl_xor_sync(0xffffffffu, st.l[1], 1); st.l[1] += __shfl_xor_sync(0xffffffffu, st.l[1], 2);
+  const float inv0 = st.l[0] > 0.f ? 1.f / st.l[0] : 0.f, inv1 = st.l[1] > 0.f ? 1.f / st.l[1] : 0.f;
+  float* so = smem + (size_t)warp * 16 * HD;
+#pragma unroll
+  for (int n = 0; n < S::NT; ++n)
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      so[(g + 8 * (i >> 1)) * HD + out_col<HD>(n, i, t)] = st.o[n][i] * ((i >> 1) ? inv1 : inv0);
+  __syncwarp();
+  for (int idx = lane; idx < 16 * HD / 2; idx += 32) {
+    const int r = (2 * idx) / HD, c = (2 * idx) % HD;
+    if (warp * 16 + r >= rows) continue;
+    const __nv_bfloat162 v = __floats2bfloat162_rn(so[r * HD + c], so[r * HD + c + 1]);
+    *reinterpret_cast<__nv_bfloat162*>(a.out + (int64_t)(tok0 + warp * 16 + r) * a.ldo + (int64_t)h * HD + c) = v;
+  }
+}
+
+template <int HD>
+int launch_decode(const DecodeArgs& a, int n_seqs, cudaStream_t stream) {
+  const size_t smem = (size_t)(4 * 16 * HD + 128) * sizeof(float);
+  static bool configured = false;
+  if (!configured && smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return fail(kLaunchFailed, "attention_decode: shared memory: %s", cudaGetErrorString(e));
+  }
+  configured = true;
+  attn_decode_kernel<HD><<<dim3(a.nkv, n_seqs, a.n_splits), 128, smem, stream>>>(a);
+  return check_launch("attention_decode");
+}
+template <int HD>
+int launch_prefill(const PrefillArgs& a, int n_tiles, cudaStream_t stream) {
+  const size_t smem = (size_t)(4 * 16 * HD) * sizeof(float);
+  static bool configured = false;
+  if (!configured && smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return fail(kLaunchFailed, "attention_prefill: shared memory: %s", cudaGetErrorString(e));
+  }
+  configured = true;
+  attn_prefill_kernel<HD><<<dim3(n_tiles, a.nq), 128, smem, stream>>>(a);
+  return check_launch("attention_prefill");
+}
+
+#define SKYLA_HD_SWITCH(hd, CALL)                                                       \
+  switch (hd) {                                                                         \
+    case 16: { constexpr int HD = 16; CALL; }                                           \
+    case 32: { constexpr int HD = 32; CALL; }                                           \
+    case 48: { constexpr int HD = 48; CALL; }                                           \
+    case 64: { constexpr int HD = 64; CALL; }                                           \
+    case 80: { constexpr int HD = 80; CALL; }                                           \
+    case 96: { constexpr int HD = 96; CALL; }                                           \
+    case 112: { constexpr int HD = 112; CALL; }                                         \
+    case 128: { constexpr int HD = 128; CALL; }                                         \
+    default: return fail(kBadArgument, "attention_mma: no kernel for head size %d", hd); \
+  }
+
+int check_common(const void* q, int64_t ldq, int nq, int nkv, int page_size, const void* k, const void* v) {
+  if (nkv <= 0 || nq % nkv) return fail(kBadArgument, "attention_mma: %d query heads over %d key/value heads", nq, nkv);
+  if (page_size % 16) return fail(kBadArgument, "attention_mma: pages of %d positions are not whole blocks of 16", page_size);
+  if (((uintptr_t)q) % 16 || (ldq * 2) % 16 || ((uintptr_t)k) % 16 || ((uintptr_t)v) % 16)
+    return fail(kBadArgument, "attention_mma: operands must be 16-byte aligned");
+  return kOk;
+}
+}  // namespace
+
+// 1 when the tensor-core kernels take this head size.
+extern "C" int skyla_attention_mma_supports(int hd, int group) {
+  return (hd % 16 == 0 && hd >= 16 && hd <= 128) ? (group <= 16 ? 2 : 1) : 0;
+}
+
+// Decode: token b of the step is the one new token of sequence b.  `part` holds
+// n_seqs * nq * n_splits * (hd + 2) floats of scratch; out is [n_seqs, nq*hd] bf16.
+extern "C" int skyla_attention_decode(const void* q, int64_t ldq, void* out, int64_t ldo, float* part, int n_seqs,
+                                      int nq, int nkv, int hd, const void* k_pool, const void* v_pool,
+                                      const int32_t* pages, int max_pages, int page_size, const int32_t* tok_pos,
+                                      float scale, int window, int n_splits, int pages_per_split,
+                                      cudaStream_t stream) {
+  if (n_seqs <= 0) return kOk;
+  int rc = check_common(q, ldq, nq, nkv, page_size, k_pool, v_pool);
+  if (rc) return rc;
+  if (nq / nkv > 16) return fail(kBadArgument, "attention_decode: groups of %d query heads exceed 16", nq / nkv);
+  if (n_splits < 1 || pages_per_split < 1 || n_seqs > 65535 || n_splits > 65535)
+    return fail(kBadArgument, "attention_decode: bad split of the context");
+  DecodeArgs a{(const bf16*)q, ldq, part, n_splits, pages_per_split, nq, nkv,
+               PagedKV{(const bf16*)k_pool, (const bf16*)v_pool, pages, max_pages, page_size, nkv}, tok_pos, scale, window};
+  SKYLA_HD_SWITCH(hd, { rc = launch_decode<HD>(a, n_seqs, stream); break; });
+  if (rc) return rc;
+  MergeArgs m{part, (bf16*)out, ldo, nq, n_splits, hd};
+  attn_merge_kernel<<<dim3(nq, n_seqs), 128, 0, stream>>>(m);
+  return check_launch("attention_merge");
+}
+
+// Prefill: tiles of up to 64 consecutive new tokens of one sequence.
+extern "C" int skyla_attention_prefill(const void* q, int64_t ldq, void* out, int64_t ldo, int n_tiles, int nq, int nkv,
+                                       int hd, const void* k_pool, const void* v_pool, const int32_t* pages,
+                                       int max_pages, int page_size, const int32_t* tok_pos, const int32_t* tile_seq,
+                                       const int32_t* tile_tok0, const int32_t* tile_rows, float scale, int window,
+                                       cudaStream_t stream) {
+  if (n_tiles <= 0) return kOk;
+  int rc = check_common(q, ldq, nq, nkv, page_size, k_pool, v_pool);
+  if (rc) return rc;
+  if (nq > 65535) return fail(kBadArgument, "attention_prefill: too many heads");
+  PrefillArgs a{(const bf16*)q, ldq, (bf16*)out, ldo, nq, nkv,
+                PagedKV{(const bf16*)k_pool, (const bf16*)v_pool, pages, max_pages, page_size, nkv},
+                tok_pos, tile_seq, tile_tok0, tile_rows, scale, window};
+  SKYLA_HD_SWITCH(hd, { rc = launch_prefill<HD>(a, n_tiles, stream); break; });
+  return rc;
+}

@@ -238,6 +238,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         if (MODE == kGluBf16) tmem_ld16(taddr + BN + c0, u);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
         if (f < a.N) {
+          float old[16];
+          if (MODE == kAccumF32) {  // all loads first: they do not wait for one another
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const int tok = tok0 + c0 + j;
+              old[j] = tok < a.M ? ((const float*)a.y)[(int64_t)tok * a.ldy + f] : 0.f;
+            }
+          }
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
             const int tok = tok0 + c0 + j;
@@ -248,8 +256,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             } else if (MODE == kStoreF32) {
               ((float*)a.y)[(int64_t)tok * a.ldy + f] = v;
             } else if (MODE == kAccumF32) {
-              float* p = (float*)a.y + (int64_t)tok * a.ldy + f;
-              *p += v;
+              ((float*)a.y)[(int64_t)tok * a.ldy + f] = old[j] + v;
             } else if (MODE == kGluBf16) {
               const float up = __uint_as_float(u[j]);
               ((__nv_bfloat16*)a.y)[(int64_t)tok * a.ldy + f] = __float2bfloat16_rn(v / (1.0f + expf(-v)) * up);

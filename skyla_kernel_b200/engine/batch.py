@@ -12,6 +12,8 @@ pinned host buffer and sent with one copy per step:
   seq_slot[B]  cache slot of each sequence (for parts with per-slot state)
   seq_start[B] positions already cached, seq_n[B] new tokens, cu[B+1] packed offsets
   want[R]      rows (packed token indices) whose logits are asked for
+  tile_seq/tile_tok0/tile_rows[Q]  tiles of up to 64 consecutive new tokens of one
+               sequence, the units the prefill attention kernel works in
   pages[G][B,P] for each cache group the page list of each sequence
 """
 from __future__ import annotations
@@ -77,11 +79,25 @@ class StepContext:
     cu: torch.Tensor
     want: torch.Tensor
     pages: List[torch.Tensor]
+    n_tiles: int = 0
+    tile_seq: Optional[torch.Tensor] = None
+    tile_tok0: Optional[torch.Tensor] = None
+    tile_rows: Optional[torch.Tensor] = None
     host: Dict[str, np.ndarray] = field(default_factory=dict)
+    #: when profiling: (label, event) pairs, an event after each stage
+    #: (the reference's timestamp marks, skyla-engine/src/graph.rs:54-57)
+    marks: Optional[list] = None
 
     @property
     def is_decode(self) -> bool:
         return self.max_new == 1
+
+    def mark(self, label: str) -> None:
+        """End of a stage; a no-op unless the step is profiled."""
+        if self.marks is not None:
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record()
+            self.marks.append((label, ev))
 
     def buffer(self, name: str, shape, dtype) -> torch.Tensor:
         return self.workspace.get(name, tuple(shape), dtype)
@@ -114,7 +130,9 @@ class BatchBuilder:
         R = sum(len(it.want) for it in items)
         G = len(cache.groups)
         P = max(1, max(-(-(s + n) // cache.page_size) for s, n in zip(starts, ns)))
-        total = 3 * T + 3 * B + (B + 1) + R + G * B * P
+        TILE = 64
+        Q = sum(-(-n // TILE) for n in ns)
+        total = 3 * T + 3 * B + (B + 1) + R + 3 * Q + G * B * P
         if self._copied is not None:
             self._copied.synchronize()  # the last step's copy has left the pinned buffer
         host, dev = self._staging(total)
@@ -135,6 +153,10 @@ class BatchBuilder:
         seq_n, r_n = take(B)
         cu, r_cu = take(B + 1)
         want, r_want = take(R)
+        tile_seq, r_tseq = take(Q)
+        tile_tok0, r_ttok = take(Q)
+        tile_rows, r_trows = take(Q)
+        q = 0
         t = 0
         w = 0
         cu[0] = 0
@@ -149,6 +171,9 @@ class BatchBuilder:
                     raise IndexError(f"wanted place {j} is outside the {n} tokens of this step")
                 want[w] = t + j
                 w += 1
+            for j in range(0, n, TILE):
+                tile_seq[q], tile_tok0[q], tile_rows[q] = b, t + j, min(TILE, n - j)
+                q += 1
             t += n
             cu[b + 1] = t
         r_pages = []
@@ -176,5 +201,6 @@ class BatchBuilder:
             page_size=cache.page_size, tokens=view(r_tokens), tok_pos=view(r_pos),
             tok_seq=view(r_seq), seq_slot=view(r_slot), seq_start=view(r_start), seq_n=view(r_n),
             cu=view(r_cu), want=view(r_want), pages=[view(r).view(B, P) for r in r_pages],
+            n_tiles=Q, tile_seq=view(r_tseq), tile_tok0=view(r_ttok), tile_rows=view(r_trows),
             host={"starts": np.asarray(starts), "ns": np.asarray(ns)},
         )

@@ -75,7 +75,7 @@ class Engine:
         self.cache.free_slot(slot)
 
     # ------------------------------------------------------------------- step
-    def step(self, items: Sequence[StepItem], taps=None) -> torch.Tensor:
+    def step(self, items: Sequence[StepItem], taps=None, profile: bool = False) -> torch.Tensor:
         """Run the items' tokens as one batch; float32 logits at the wanted places.
 
         Rows are ordered by item, then by the item's ``want`` list.  Raises
@@ -99,9 +99,27 @@ class Engine:
         self.cache.reserve(growth)
         with torch.cuda.device(self.rt.device):
             ctx = self.batcher.build(items)
+            if profile:
+                ctx.marks = []
+                ctx.mark("start")
             logits = self.model.forward(ctx, taps)
+            if profile:
+                self._profile = self._read_marks(ctx.marks)
         self.cache.advance(growth)
         return logits
+
+    @staticmethod
+    def _read_marks(marks):
+        torch.cuda.synchronize()
+        total = {}
+        for (_, a), (label, b) in zip(marks, marks[1:]):
+            total[label] = total.get(label, 0.0) + a.elapsed_time(b) * 1e6
+        return sorted(total.items(), key=lambda kv: -kv[1])
+
+    def last_step_profile(self):
+        """``[(label, nanoseconds)]`` of the last step run with ``profile=True``, largest first
+        (the reference's ``Engine::last_step_profile``, skyla-engine/src/engine.rs:91-96)."""
+        return list(getattr(self, "_profile", []))
 
     # ------------------------------------------------------------------ facts
     def weight_bytes(self) -> int:

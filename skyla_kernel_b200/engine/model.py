@@ -103,6 +103,7 @@ class DecoderModel:
         hidden = self.spec.hidden_size
         x = ctx.buffer("model.x", (ctx.n_tokens, hidden), torch.float32)
         self.embedding.forward(ctx, ctx.tokens, x)
+        ctx.mark("embedding")
         for i, e in enumerate(self.spec.schedule):
             self.blocks[e.layer].forward(ctx, x, self.entries[i])
             if taps is not None and i in taps:
@@ -111,5 +112,7 @@ class DecoderModel:
         if ctx.n_want:
             h = ctx.buffer("model.final", (ctx.n_want, hidden), self.rt.act_dtype)
             self.final_norm.forward(ctx, x, h, rows=ctx.want)
+            ctx.mark("take wanted rows + rmsnorm")
             self.head.forward(ctx, h, logits)
+            ctx.mark("matvec output")
         return logits

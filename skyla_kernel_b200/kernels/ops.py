@@ -321,6 +321,63 @@ def attention_plain(q: torch.Tensor, out: torch.Tensor, nq: int, nkv: int, hd: i
     return out
 
 
+def attention_mma_supports(hd: int, group: int) -> int:
+    """0: the tensor-core attention does not take this head size; 1: prefill only; 2: prefill and decode."""
+    f = _fn("attention_mma", "skyla_attention_mma_supports", [c_int, c_int])
+    return int(f(hd, group))
+
+
+def _attn_common(q, out, k_pool, v_pool, nq, nkv, hd, page_size, *ints):
+    _cuda(q, out, k_pool, v_pool, *ints)
+    for t in ints:
+        _i32(t, "index array")
+    if q.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or k_pool.dtype != torch.bfloat16:
+        raise KernelError("tensor-core attention takes bfloat16 queries, outputs and cache")
+    if (tuple(k_pool.shape[1:]) != (nkv, page_size, hd) or k_pool.shape != v_pool.shape
+            or not k_pool.is_contiguous() or not v_pool.is_contiguous()):
+        raise KernelError(f"cache pools {tuple(k_pool.shape)} do not match [pages, {nkv}, {page_size}, {hd}]")
+
+
+def attention_decode(q: torch.Tensor, out: torch.Tensor, scratch: torch.Tensor, nq: int, nkv: int, hd: int,
+                     k_pool: torch.Tensor, v_pool: torch.Tensor, pages: torch.Tensor, page_size: int,
+                     tok_pos: torch.Tensor, scale: float, window: int, n_splits: int,
+                     pages_per_split: int) -> torch.Tensor:
+    """One new token per sequence (token b belongs to sequence b): split-context attention
+    over the cache for all query heads of a key/value head at once, then the merge.
+
+    ``scratch``: float32, at least ``n_seqs * nq * n_splits * (hd + 2)`` elements.
+    """
+    _attn_common(q, out, k_pool, v_pool, nq, nkv, hd, page_size, pages, tok_pos)
+    n = tok_pos.numel()
+    if scratch.dtype != torch.float32 or scratch.numel() < n * nq * n_splits * (hd + 2):
+        raise KernelError("attention_decode: scratch too small")
+    f = _fn("attention_mma", "skyla_attention_decode",
+            [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
+             c_void_p, c_int, c_int, c_void_p, c_float, c_int, c_int, c_int, c_void_p])
+    _check("attention_mma", f(_ptr(q), _rows(q, "q"), _ptr(out), _rows(out, "out"), _ptr(scratch), n, nq, nkv, hd,
+                              _ptr(k_pool), _ptr(v_pool), _ptr(pages), pages.shape[1], page_size, _ptr(tok_pos),
+                              float(scale), int(window or 0), n_splits, pages_per_split, _stream()))
+    global LAUNCHES
+    LAUNCHES += 1  # the merge kernel
+    return out
+
+
+def attention_prefill(q: torch.Tensor, out: torch.Tensor, nq: int, nkv: int, hd: int, k_pool: torch.Tensor,
+                      v_pool: torch.Tensor, pages: torch.Tensor, page_size: int, tok_pos: torch.Tensor,
+                      tile_seq: torch.Tensor, tile_tok0: torch.Tensor, tile_rows: torch.Tensor, scale: float,
+                      window: int = 0) -> torch.Tensor:
+    """Causal attention of new tokens in tiles of up to 64 tokens of one sequence."""
+    _attn_common(q, out, k_pool, v_pool, nq, nkv, hd, page_size, pages, tok_pos, tile_seq, tile_tok0, tile_rows)
+    f = _fn("attention_mma", "skyla_attention_prefill",
+            [c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
+             c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_int, c_void_p])
+    _check("attention_mma", f(_ptr(q), _rows(q, "q"), _ptr(out), _rows(out, "out"), tile_seq.numel(), nq, nkv, hd,
+                              _ptr(k_pool), _ptr(v_pool), _ptr(pages), pages.shape[1], page_size, _ptr(tok_pos),
+                              _ptr(tile_seq), _ptr(tile_tok0), _ptr(tile_rows), float(scale), int(window or 0),
+                              _stream()))
+    return out
+
+
 # ------------------------------------------------------------------- sampling
 def sample(logits: torch.Tensor, out: torch.Tensor, temperature: float = 0.0, top_k: int = 0,
            top_p: float = 1.0, seed: int = 0, req_ids: Optional[torch.Tensor] = None,

@@ -30,7 +30,7 @@ from .linear import ACCUMULATE, STORE, Linear
 
 
 class GQAttention(Part):
-    kernel_modules = Linear.kernel_modules + ("attn_prep", "attention_plain")
+    kernel_modules = Linear.kernel_modules + ("attn_prep", "attention_plain", "attention_mma")
 
     def __init__(self, spec, rt):
         super().__init__(spec, rt)
@@ -48,6 +48,11 @@ class GQAttention(Part):
         pos = p.get("position")
         self.position = build_part("position", pos, rt) if pos is not None else None
         self.q_norm_w = self.k_norm_w = None
+        # tensor-core attention: head sizes 16..128 in steps of 16 (prompts: 1); decode also
+        # needs the query heads of a key/value head to fit one 16-row tile (2)
+        self._fast = 0
+        if not rt.full_precision and self.hd % 16 == 0 and 16 <= self.hd <= 128:
+            self._fast = 2 if self.nq // self.nkv <= 16 else 1
         self.qkv: Optional[Linear] = None
         self.q_only: Optional[Linear] = None
         self.out: Optional[Linear] = None
@@ -88,6 +93,16 @@ class GQAttention(Part):
         return self.kernel_modules
 
     # -------------------------------------------------------------------- cache
+    def decode_splits(self, n_seqs: int, max_pages: int):
+        """How a decode step cuts the context: (splits, pages per split).
+
+        Enough blocks to fill the GPU about three times over, at least four pages
+        per block (one per warp); splits are aligned to absolute positions.
+        """
+        want = -(-3 * 148 // max(1, self.nkv * n_seqs))
+        per = max(4, -(-max_pages // want))
+        return -(-max_pages // per), per
+
     def cache_need(self) -> Optional[KVNeed]:
         return KVNeed(self.nkv, self.hd, self.window or None)
 
@@ -107,18 +122,34 @@ class GQAttention(Part):
         if entry.owns_cache:
             qkv = ctx.buffer("attn.qkv", (n, (nq + 2 * nkv) * hd), self.rt.act_dtype)
             self.qkv.forward(h, qkv, STORE)
+            ctx.mark("matvec qkv")
             ops.qk_norm_rope_cache(qkv, 0, nq * hd, (nq + nkv) * hd, nq, nkv, hd, self.q_norm_w,
                                    self.k_norm_w, self.eps, cos, sin, n_rot, ctx.tok_pos, ctx.tok_seq,
                                    k_pool, v_pool, pages, ctx.page_size)
         else:  # reads the cache another run wrote: only queries are needed
             qkv = ctx.buffer("attn.q", (n, nq * hd), self.rt.act_dtype)
             self.q_only.forward(h, qkv, STORE)
+            ctx.mark("matvec qkv")
             ops.qk_norm_rope_cache(qkv, 0, 0, 0, nq, 0, hd, self.q_norm_w, None, self.eps, cos, sin,
                                    n_rot, ctx.tok_pos, ctx.tok_seq, None, None, pages, ctx.page_size)
+        ctx.mark("qk norm + rope")
         attn = ctx.buffer("attn.out", (n, nq * hd), self.rt.act_dtype)
-        ops.attention_plain(qkv[:, : nq * hd], attn, nq, nkv, hd, k_pool, v_pool, pages,
-                            ctx.page_size, ctx.tok_pos, ctx.tok_seq, self.scale, self.window)
+        q = qkv[:, : nq * hd]
+        fast = self._fast if k_pool.dtype == torch.bfloat16 and q.dtype == torch.bfloat16 else 0
+        if fast == 2 and ctx.is_decode:
+            n_splits, per = self.decode_splits(ctx.n_seqs, pages.shape[1])
+            scratch = ctx.buffer("attn.partials", (n * nq * n_splits * (hd + 2),), torch.float32)
+            ops.attention_decode(q, attn, scratch, nq, nkv, hd, k_pool, v_pool, pages, ctx.page_size,
+                                 ctx.tok_pos, self.scale, self.window, n_splits, per)
+        elif fast:
+            ops.attention_prefill(q, attn, nq, nkv, hd, k_pool, v_pool, pages, ctx.page_size, ctx.tok_pos,
+                                  ctx.tile_seq, ctx.tile_tok0, ctx.tile_rows, self.scale, self.window)
+        else:
+            ops.attention_plain(q, attn, nq, nkv, hd, k_pool, v_pool, pages, ctx.page_size, ctx.tok_pos,
+                                ctx.tok_seq, self.scale, self.window)
+        ctx.mark("attention")
         self.out.forward(attn, x, ACCUMULATE)
+        ctx.mark("matvec o")
 
 
 register_mixer("gqa_attention", GQAttention)

@@ -60,8 +60,10 @@ class PrenormResidualBlock:
     def forward(self, ctx, x, entry: EntryBinding) -> None:
         h = ctx.buffer("block.normed", (ctx.n_tokens, x.shape[1]), self.rt.act_dtype)
         self.mixer_norm.forward(ctx, x, h)
+        ctx.mark("rmsnorm")
         self.mixer.forward(ctx, h, x, entry)
         self.ffn_norm.forward(ctx, x, h)
+        ctx.mark("rmsnorm")
         self.feed_forward.forward(ctx, h, x)
 
 

@@ -59,7 +59,9 @@ class SwiGLU(Part):
     def forward(self, ctx, h: torch.Tensor, x: torch.Tensor) -> None:
         act = ctx.buffer("ffn.act", (ctx.n_tokens, self.inter), self.rt.act_dtype)
         self.gate_up.forward(h, act, GATED)
+        ctx.mark("matvec gate+up, silu")
         self.down.forward(act, x, ACCUMULATE)
+        ctx.mark("matvec down")
 
 
 register_feed_forward("swiglu", SwiGLU)

@@ -350,3 +350,84 @@ def test_gemm_tc_refuses_what_it_cannot_do():
         ops.TensorMap(w, 128)
     with pytest.raises(KernelError):
         ops.TensorMap(_rand(128, 64, seed=3), 128)  # float32
+
+
+# -------------------------------------------------------- tensor-core attention
+@pytest.mark.parametrize("nq,nkv,hd", [(4, 2, 16), (6, 1, 32), (3, 3, 48), (8, 2, 64), (5, 5, 80), (32, 8, 128), (16, 1, 96)])
+@pytest.mark.parametrize("window", [0, 70])
+def test_attention_decode_mma(nq, nkv, hd, window):
+    ops = _ops()
+    dt = torch.bfloat16
+    lens = [1, 15, 64, 65, 200, 333, 1000]
+    k_pool, v_pool, table, ks, vs = _paged(len(lens), lens, nkv, hd, dt, seed=nq * 100 + hd)
+    B = len(lens)
+    q = _rand(B, nq * hd + 16, seed=41, dtype=dt)[:, : nq * hd]  # rows with a stride of their own
+    tok_pos = torch.tensor([l - 1 for l in lens], dtype=torch.int32, device=DEV)
+    scale = 1.0 / math.sqrt(hd)
+    ref = torch.stack([_attn_ref(q[b].cpu().view(nq, hd), ks[b], vs[b], lens[b] - 1, nq, nkv, scale, window)
+                       for b in range(B)]).float()
+    plain_out = torch.empty(B, nq * hd, dtype=dt, device=DEV)
+    ops.attention_plain(q, plain_out, nq, nkv, hd, k_pool, v_pool, table, 64, tok_pos,
+                        torch.arange(B, dtype=torch.int32, device=DEV), scale, window)
+    for n_splits, per in ((1, 16), (4, 4), (16, 1), (3, 6)):
+        out = torch.full((B, nq * hd), float("nan"), dtype=dt, device=DEV)
+        scratch = torch.full((B * nq * n_splits * (hd + 2),), float("nan"), dtype=torch.float32, device=DEV)
+        ops.attention_decode(q, out, scratch, nq, nkv, hd, k_pool, v_pool, table, 64, tok_pos, scale, window,
+                             n_splits, per)
+        torch.testing.assert_close(out.float().cpu().view(B, nq, hd), ref, rtol=2e-2, atol=2e-2)
+        torch.testing.assert_close(out.float(), plain_out.float(), rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("nq,nkv,hd", [(4, 2, 16), (6, 1, 32), (3, 3, 48), (8, 2, 64), (2, 1, 112), (8, 2, 128)])
+@pytest.mark.parametrize("window", [0, 70])
+def test_attention_prefill_mma(nq, nkv, hd, window):
+    ops = _ops()
+    dt = torch.bfloat16
+    # (cached before, new now) per sequence: whole prompts, a continued chunk, a single token
+    spans = [(0, 1), (0, 63), (0, 64), (0, 130), (100, 77), (64, 64), (199, 1), (5, 200)]
+    lens = [s + n for s, n in spans]
+    k_pool, v_pool, table, ks, vs = _paged(len(lens), lens, nkv, hd, dt, seed=nq * 7 + hd)
+    tok_pos, tok_seq, tile_seq, tile_tok0, tile_rows = [], [], [], [], []
+    for b, (s, n) in enumerate(spans):
+        for j in range(0, n, 64):
+            tile_seq.append(b); tile_tok0.append(len(tok_pos) + j); tile_rows.append(min(64, n - j))
+        tok_pos += list(range(s, s + n)); tok_seq += [b] * n
+    T = len(tok_pos)
+    q = _rand(T, nq * hd, seed=43, dtype=dt)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    scale = 1.0 / math.sqrt(hd)
+    out = torch.full((T, nq * hd), float("nan"), dtype=dt, device=DEV)
+    ops.attention_prefill(q, out, nq, nkv, hd, k_pool, v_pool, table, 64, i32(tok_pos), i32(tile_seq), i32(tile_tok0),
+                          i32(tile_rows), scale, window)
+    plain_out = torch.empty_like(out)
+    ops.attention_plain(q, plain_out, nq, nkv, hd, k_pool, v_pool, table, 64, i32(tok_pos), i32(tok_seq), scale, window)
+    torch.testing.assert_close(out.float(), plain_out.float(), rtol=2e-2, atol=2e-2)
+    for i in (0, 1, 63, 64, 64 + 129, T - 1, T - 200, T - 137):
+        ref = _attn_ref(q[i].cpu().view(nq, hd), ks[tok_seq[i]], vs[tok_seq[i]], tok_pos[i], nq, nkv, scale, window)
+        torch.testing.assert_close(out[i].float().cpu().view(nq, hd), ref.float(), rtol=2e-2, atol=2e-2)
+
+
+def test_attention_mma_finds_one_far_key():
+    ops = _ops()
+    dt = torch.bfloat16
+    nq, nkv, hd, L = 8, 2, 128, 1500
+    k_pool, v_pool, table, ks, vs = _paged(1, [L], nkv, hd, dt, seed=5)
+    q = _rand(1, nq * hd, seed=12, dtype=dt)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    for target in (0, 15, 16, 63, 64, 700, L - 2, L - 1):
+        kp = k_pool.clone()
+        page, off = int(table[0, target // 64]), target % 64
+        for kvh in range(nkv):
+            qh = q[0].view(nq, hd)[kvh * 4 + 1].float()
+            kp[page, kvh, off] = (qh / qh.norm() * 60.0).to(dt)
+        for mode in ("decode", "prefill"):
+            out = torch.empty(1, nq * hd, dtype=dt, device=DEV)
+            if mode == "decode":
+                scratch = torch.empty(nq * 5 * (hd + 2), dtype=torch.float32, device=DEV)
+                ops.attention_decode(q, out, scratch, nq, nkv, hd, kp, v_pool, table, 64, i32([L - 1]), 1.0, 0, 5, 5)
+            else:
+                ops.attention_prefill(q, out, nq, nkv, hd, kp, v_pool, table, 64, i32([L - 1]), i32([0]), i32([0]),
+                                      i32([1]), 1.0, 0)
+            for kvh in range(nkv):
+                got = out[0].view(nq, hd)[kvh * 4 + 1].float().cpu()
+                torch.testing.assert_close(got, vs[0][target, kvh].float(), rtol=2e-2, atol=2e-2)
