@@ -85,17 +85,21 @@ def random_tokens(n: int, vocab: int, seed: int):
 # Tolerances; the error is measured against the largest reference logit of the
 # compared block.
 #   float32: engine against the plain 32-bit implementation.
-#   bfloat16: engine against the plain implementation.  The plain implementation
-#     run with a bfloat16 round trip at the places where the engine stores 16-bit
-#     activations (plain.forward(..., rnd=plain.bf16_round)) differs from its own
-#     32-bit run by up to 9.7e-2 (worst) and 4e-3 (mean) of the largest logit over
-#     60 sequences of these tiny, deliberately sharp models: that is rounding alone,
-#     so the limits against the 32-bit run sit just above it.
-#   bfloat16-emulated: engine against that rounded run.  Two such runs that differ
-#     only in accumulation precision (32- and 64-bit) differ by up to 1.1e-2 / 4e-4
-#     because a value near a rounding boundary flips; the limits are 3x / 5x that.
-TOL = {"float32": 1e-4, "bfloat16": 1.5e-1, "bfloat16-emulated": 3e-2}
-TOL_MEAN = {"float32": 2e-5, "bfloat16": 1e-2, "bfloat16-emulated": 2e-3}
+#   bfloat16: engine against the plain 32-bit implementation.  How much of that
+#     difference is rounding alone was measured with the plain implementation itself:
+#     run with a bfloat16 round trip where a 16-bit engine stores activations
+#     (plain.forward(..., rnd=plain.bf16_round): normed inputs, q/k/v, rotated q/k,
+#     softmax weights, attention output, gated activation, final norm) it differs
+#     from its own 32-bit run by up to 9.7e-2 (worst element) and 4.4e-3 (mean) of the
+#     largest logit over 60 sequences of these tiny, deliberately sharp models.  The
+#     limits sit just above that.  A fault in a key, a position or a slot moves
+#     logits by the order of the largest logit itself and is far outside them.
+#     (The engine is not compared with that rounded run: its kernels round at other
+#     scales -- attention weights relative to a running maximum -- so every stored
+#     value draws its rounding anew and the two differ by as much as either differs
+#     from the 32-bit run.)
+TOL = {"float32": 1e-4, "bfloat16": 1.5e-1}
+TOL_MEAN = {"float32": 2e-5, "bfloat16": 1e-2}
 
 
 def assert_close(got: torch.Tensor, ref: torch.Tensor, dtype: str, what: str = ""):

@@ -114,7 +114,7 @@ def attention(n, wq, wk, wv, wo, q_norm, k_norm, nq, nkv, hd, eps, freqs, mscale
         if window:
             mask = mask | (i[None, :] < i[:, None] - window + 1)
         s = s.masked_fill(mask, float("-inf"))
-        out[:, h, :] = softmax(s) @ v[:, kvh, :]   # model.rs:159-165
+        out[:, h, :] = rnd(softmax(s)) @ v[:, kvh, :]   # model.rs:159-165 (a 16-bit engine rounds the weights too)
     return rnd(out.reshape(T, nq * hd)) @ wo.T   # model.rs:171
 
 

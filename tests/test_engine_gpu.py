@@ -26,14 +26,11 @@ _MODELS = {}
 
 
 def _check(folder, tokens, got, dtype, what):
-    """Compare with the plain implementation; in bfloat16 also with its rounded run."""
+    """Compare with the plain 32-bit implementation."""
     if folder not in _MODELS:
         _MODELS[folder] = plain.read_folder(folder)
     cfg, w = _MODELS[folder]
     assert_close(got, plain.forward(cfg, w, tokens), dtype, what)
-    if dtype == "bfloat16":
-        assert_close(got, plain.forward(cfg, w, tokens, rnd=plain.bf16_round), "bfloat16-emulated",
-                     what + " (against the plain run with 16-bit storage)")
 
 
 @pytest.mark.parametrize("dtype", DTYPES)

@@ -107,11 +107,6 @@ def test_attention_part_whole_then_one_by_one(dtype, hidden, nq, nkv, hd, n_rot,
         got.append(x.cpu())
     from helpers import assert_close
     assert_close(torch.cat(got), ref, dtype, "attention part")
-    if dtype == "bfloat16":  # and against the plain run that stores 16-bit values where the part does
-        emulated = plain.attention(plain.bf16_round(h_all), w["a.q_proj"], w["a.k_proj"], w["a.v_proj"], w["a.o_proj"],
-                                   w["a.q_norm"] if qk_norm else None, w["a.k_norm"] if qk_norm else None,
-                                   nq, nkv, hd, 1e-5, freqs, m, n_rot, scale=scale, window=window, rnd=plain.bf16_round)
-        assert_close(torch.cat(got), emulated, "bfloat16-emulated", "attention part, 16-bit storage")
     if window:  # pages wholly outside the window went back to the pool
         assert cache.groups[0].pages.n_held < -(-T // 64) + 1 and cache.groups[0].slot_pages[slot][0] == -1
 
