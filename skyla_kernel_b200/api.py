@@ -97,7 +97,7 @@ class _Backend:
         self.m.free_slot(slot)
 
     def step(self, items):
-        return self.m.engine.step(items)
+        return self.m.engine.step(items, borrow=True)  # sampled at once, before the next step
 
     def sample(self, logits, req_ids, steps) -> List[int]:
         return self.sampler(logits, req_ids, steps).cpu().tolist()

@@ -121,7 +121,9 @@ class BatchBuilder:
             self._device = torch.empty(cap, dtype=torch.int32, device=self.rt.device)
         return self._pinned, self._device
 
-    def build(self, items: List[StepItem]) -> StepContext:
+    def build(self, items: List[StepItem], pages_width: Optional[int] = None) -> StepContext:
+        """``pages_width``: columns of the page lists (default: what the longest sequence needs);
+        a fixed width keeps the layout of the arrays the same from step to step."""
         cache = self.cache
         B = len(items)
         ns = [len(it.tokens) for it in items]
@@ -130,6 +132,10 @@ class BatchBuilder:
         R = sum(len(it.want) for it in items)
         G = len(cache.groups)
         P = max(1, max(-(-(s + n) // cache.page_size) for s, n in zip(starts, ns)))
+        if pages_width is not None:
+            if pages_width < P:
+                raise ValueError(f"page lists need {P} columns, {pages_width} were given")
+            P = pages_width
         TILE = 64
         Q = sum(-(-n // TILE) for n in ns)
         total = 3 * T + 3 * B + (B + 1) + R + 3 * Q + G * B * P

@@ -9,6 +9,7 @@ cut of the tokens gives the same logits up to rounding.
 """
 from __future__ import annotations
 
+import os
 from typing import Dict, List, Optional, Sequence
 
 import numpy as np
@@ -20,6 +21,7 @@ from ..kernels import build as kernel_build
 from ..parts.base import Runtime
 from ..weights import load_weights
 from .batch import BatchBuilder, StepItem
+from .graphs import DecodeGraphs
 from .model import DecoderModel, declared_tensors
 
 
@@ -45,7 +47,8 @@ class Engine:
     """
 
     def __init__(self, config, tensors: Dict[str, torch.Tensor], dtype: str = "bfloat16",
-                 max_tokens: int = 4096, max_slots: Optional[int] = None, device="cuda:0"):
+                 max_tokens: int = 4096, max_slots: Optional[int] = None, device="cuda:0",
+                 cuda_graphs: Optional[bool] = None):
         self.config = config
         self.spec = config.to_spec()
         self.rt = Runtime(_device(device), dtype)
@@ -57,15 +60,20 @@ class Engine:
                                    self.rt.cache_dtype, self.rt.device)
         self.batcher = BatchBuilder(self.rt, self.cache)
         self.vocab_size = self.spec.vocab_size
+        if cuda_graphs is None:
+            cuda_graphs = os.environ.get("SKYLA_CUDA_GRAPHS", "1") != "0"
+        # decode steps of the 16-bit path replay captured graphs; the 32-bit path stays eager
+        self.graphs = (DecodeGraphs(self.model, self.rt, self.cache)
+                       if cuda_graphs and not self.rt.full_precision and self.model.graph_safe() else None)
 
     # ---------------------------------------------------------------- loading
     @classmethod
     def from_folder(cls, folder: str, dtype: str = "bfloat16", max_tokens: int = 4096,
-                    max_slots: Optional[int] = None, device="cuda:0") -> "Engine":
+                    max_slots: Optional[int] = None, device="cuda:0", cuda_graphs: Optional[bool] = None) -> "Engine":
         config = config_from_folder(folder)
         spec = config.to_spec()
         tensors = load_weights(folder, declared_tensors(spec), spec.optional_tensors)
-        return cls(config, tensors, dtype, max_tokens, max_slots, device)
+        return cls(config, tensors, dtype, max_tokens, max_slots, device, cuda_graphs)
 
     # ------------------------------------------------------------------ slots
     def alloc_slot(self) -> int:
@@ -75,8 +83,13 @@ class Engine:
         self.cache.free_slot(slot)
 
     # ------------------------------------------------------------------- step
-    def step(self, items: Sequence[StepItem], taps=None, profile: bool = False) -> torch.Tensor:
+    def step(self, items: Sequence[StepItem], taps=None, profile: bool = False,
+             borrow: bool = False) -> torch.Tensor:
         """Run the items' tokens as one batch; float32 logits at the wanted places.
+
+        ``borrow=True`` returns the engine's own logits buffer, which the next step
+        overwrites (the generation loop and the replay program read it at once);
+        otherwise the caller gets a copy.
 
         Rows are ordered by item, then by the item's ``want`` list.  Raises
         :class:`CacheFull` before anything is launched if the tokens do not fit,
@@ -98,6 +111,11 @@ class Engine:
         growth = [(it.slot, len(it.tokens)) for it in items]
         self.cache.reserve(growth)
         with torch.cuda.device(self.rt.device):
+            if (self.graphs is not None and taps is None and not profile
+                    and all(len(it.tokens) == 1 and list(it.want) == [0] for it in items)):
+                logits = self.graphs.run(items)
+                self.cache.advance(growth)
+                return logits if borrow else logits.clone()
             ctx = self.batcher.build(items)
             if profile:
                 ctx.marks = []
@@ -106,7 +124,7 @@ class Engine:
             if profile:
                 self._profile = self._read_marks(ctx.marks)
         self.cache.advance(growth)
-        return logits
+        return logits if borrow else logits.clone()
 
     @staticmethod
     def _read_marks(marks):

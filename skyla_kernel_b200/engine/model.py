@@ -71,6 +71,14 @@ class DecoderModel:
                                       f"their mixers need different caches")
                 self.entries.append(EntryBinding(owner_entry[j], False))
 
+    def graph_safe(self) -> bool:
+        """Whether every part only launches kernels on the current stream with device-side
+        control, so that a decode step can be captured in a CUDA graph and replayed."""
+        parts = [self.embedding, self.final_norm, self.head]
+        for b in self.blocks:
+            parts.extend(b.parts())
+        return all(getattr(p, "graph_safe", False) for p in parts)
+
     def kernels_needed(self):
         mods = list(self.embedding.kernels_needed())
         for b in self.blocks:
@@ -108,7 +116,7 @@ class DecoderModel:
             self.blocks[e.layer].forward(ctx, x, self.entries[i])
             if taps is not None and i in taps:
                 taps[i].copy_(x)
-        logits = torch.empty((ctx.n_want, self.spec.vocab_size), dtype=torch.float32, device=self.rt.device)
+        logits = ctx.buffer("model.logits", (ctx.n_want, self.spec.vocab_size), torch.float32)
         if ctx.n_want:
             h = ctx.buffer("model.final", (ctx.n_want, hidden), self.rt.act_dtype)
             self.final_norm.forward(ctx, x, h, rows=ctx.want)

@@ -30,6 +30,7 @@ from .linear import ACCUMULATE, STORE, Linear
 
 
 class GQAttention(Part):
+    graph_safe = True
     kernel_modules = Linear.kernel_modules + ("attn_prep", "attention_plain", "attention_mma")
 
     def __init__(self, spec, rt):

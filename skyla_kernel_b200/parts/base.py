@@ -100,6 +100,9 @@ class Part:
 
     #: CUDA source modules (csrc/<name>.cu) the part launches, compiled before first use
     kernel_modules = ()
+    #: True if forward() only launches kernels on the current stream and never reads
+    #: device memory on the host, so that a step may be captured in a CUDA graph
+    graph_safe = False
 
     def __init__(self, spec: PartSpec, rt: Runtime):
         self.spec = spec

@@ -18,6 +18,7 @@ from .linear import STORE, Linear
 
 
 class TokenEmbedding(Part):
+    graph_safe = True
     kernel_modules = ("embed",)
 
     def __init__(self, spec, rt):
@@ -42,6 +43,7 @@ class TokenEmbedding(Part):
 
 
 class LinearHead(Part):
+    graph_safe = True
     kernel_modules = Linear.kernel_modules
 
     def __init__(self, spec, rt):

@@ -28,6 +28,7 @@ def fuse_gate_up(gate: torch.Tensor, up: torch.Tensor, group: int) -> torch.Tens
 
 
 class SwiGLU(Part):
+    graph_safe = True
     kernel_modules = Linear.kernel_modules
 
     def __init__(self, spec, rt):

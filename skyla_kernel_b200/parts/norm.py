@@ -15,6 +15,7 @@ from .base import Part, register_norm
 
 
 class RMSNorm(Part):
+    graph_safe = True
     kernel_modules = ("norm",)
 
     def __init__(self, spec, rt):

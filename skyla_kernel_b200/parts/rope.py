@@ -63,9 +63,12 @@ class RotaryNeox(Part):
         self.freqs, self.mscale = rotary_frequencies(self.n_rot, self.theta, self.scaling)
         self.cos = self.sin = None
         self.version = 0
+        self._retired = []  # earlier, shorter tables stay valid for whoever captured their address
         self._grow(max(1, int(spec.params.get("max_positions", 1))))
 
     def _grow(self, n: int) -> None:
+        if self.cos is not None:
+            self._retired.append((self.cos, self.sin))
         pos = torch.arange(n, dtype=torch.float32)
         ang = (pos[:, None] * self.freqs[None, :]).to(torch.float64)  # the product itself is 32-bit
         self.cos = (torch.cos(ang) * self.mscale).to(torch.float32).to(self.rt.device).contiguous()
