@@ -18,7 +18,9 @@ constexpr int kWarps = 4;
 constexpr int kMaxHeadDim = 512;
 
 struct PrepArgs {
-  void* qkv; int64_t ld; int q_off, k_off, v_off;
+  const void* qkv; int64_t ld; int q_off, k_off, v_off;
+  int n_splits; int64_t split_stride;  // the input may be K-split partial sums: [split][token][width]
+  void* q_out; int64_t ldq;            // where the prepared queries go (may be the input itself)
   int n_tokens, nq, nkv, hd;
   const float* q_norm; const float* k_norm; float eps;
   const float* cos_t; const float* sin_t; int n_rot;
@@ -26,7 +28,7 @@ struct PrepArgs {
   void* k_pool; void* v_pool; const int32_t* page_table; int max_pages; int page_size;
 };
 
-template <typename TA, typename TC>
+template <typename TI, typename TA, typename TC>
 __global__ void __launch_bounds__(kWarps * 32) prep_kernel(PrepArgs a) {
   extern __shared__ float smem[];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -38,8 +40,13 @@ __global__ void __launch_bounds__(kWarps * 32) prep_kernel(PrepArgs a) {
   const int hd = a.hd;
   const bool is_q = head < a.nq, is_k = !is_q && head < a.nq + a.nkv;
   const int kvh = is_q ? 0 : (is_k ? head - a.nq : head - a.nq - a.nkv);
-  TA* src = (TA*)a.qkv + (int64_t)t * a.ld +
-            (is_q ? a.q_off + head * hd : (is_k ? a.k_off : a.v_off) + kvh * hd);
+  const TI* src = (const TI*)a.qkv + (int64_t)t * a.ld +
+                  (is_q ? a.q_off + head * hd : (is_k ? a.k_off : a.v_off) + kvh * hd);
+  auto load = [&](int e) {  // splits are summed in ascending order
+    float v = to_float(src[e]);
+    for (int s = 1; s < a.n_splits; ++s) v += to_float(src[(int64_t)s * a.split_stride + e]);
+    return v;
+  };
   const int pos = a.tok_pos[t];
 
   TC* dst = nullptr;
@@ -50,13 +57,13 @@ __global__ void __launch_bounds__(kWarps * 32) prep_kernel(PrepArgs a) {
     dst = pool + (((int64_t)page * a.nkv + kvh) * a.page_size + pos % a.page_size) * hd;
   }
   if (!is_q && !is_k) {  // v: a copy
-    for (int e = lane; e < hd; e += 32) dst[e] = from_float<TC>(to_float(src[e]));
+    for (int e = lane; e < hd; e += 32) dst[e] = from_float<TC>(load(e));
     return;
   }
   const float* nw = is_q ? a.q_norm : a.k_norm;
   float ss = 0.f;
   for (int e = lane; e < hd; e += 32) {
-    const float v = to_float(src[e]);
+    const float v = load(e);
     u[e] = v;
     ss = fmaf(v, v, ss);
   }
@@ -75,14 +82,17 @@ __global__ void __launch_bounds__(kWarps * 32) prep_kernel(PrepArgs a) {
       const float x0 = u[i], x1 = u[i + half];
       v = e < half ? x0 * c - x1 * s : x0 * s + x1 * c;
     }
-    if (is_q) src[e] = from_float<TA>(v);
+    if (is_q) ((TA*)a.q_out)[(int64_t)t * a.ldq + head * hd + e] = from_float<TA>(v);
     else dst[e] = from_float<TC>(v);
   }
 }
 }  // namespace
 
+// qkv: [n_splits][tokens][ld] (n_splits = 1: plain activations); the prepared queries go
+// to q_out [tokens][ldq] (heads contiguous), which may alias the q columns of qkv.
 extern "C" int skyla_qk_norm_rope_cache(
-    void* qkv, int act_dtype, int64_t ld, int q_off, int k_off, int v_off, int n_tokens, int nq,
+    const void* qkv, int in_dtype, int64_t ld, int n_splits, int64_t split_stride, void* q_out,
+    int act_dtype, int64_t ldq, int q_off, int k_off, int v_off, int n_tokens, int nq,
     int nkv, int hd, const float* q_norm, const float* k_norm, float eps, const float* cos_t,
     const float* sin_t, int n_rot, const int32_t* tok_pos, const int32_t* tok_slot, void* k_pool,
     void* v_pool, int cache_dtype, const int32_t* page_table, int max_pages, int page_size,
@@ -91,12 +101,13 @@ extern "C" int skyla_qk_norm_rope_cache(
   if (hd <= 0 || hd > kMaxHeadDim) return fail(kBadArgument, "qk_norm_rope_cache: head size %d is outside 1..%d", hd, kMaxHeadDim);
   if (n_rot < 0 || n_rot > hd || n_rot % 2) return fail(kBadArgument, "qk_norm_rope_cache: rotary width %d does not fit head size %d", n_rot, hd);
   if (n_tokens > 65535) return fail(kBadArgument, "qk_norm_rope_cache: %d tokens exceed the grid", n_tokens);
-  PrepArgs a{qkv, ld, q_off, k_off, v_off, n_tokens, nq, nkv, hd, q_norm, k_norm, eps, cos_t, sin_t,
+  if (n_splits < 1) return fail(kBadArgument, "qk_norm_rope_cache: bad split count");
+  PrepArgs a{qkv, ld, q_off, k_off, v_off, n_splits, split_stride, q_out, ldq, n_tokens, nq, nkv, hd, q_norm, k_norm, eps, cos_t, sin_t,
              n_rot, tok_pos, tok_slot, k_pool, v_pool, page_table, max_pages, page_size};
   dim3 grid((nq + 2 * nkv + kWarps - 1) / kWarps, n_tokens);
   const size_t smem = (size_t)kWarps * hd * sizeof(float);
-  SKYLA_DISPATCH(act_dtype, TA, SKYLA_DISPATCH(cache_dtype, TC, {
-    prep_kernel<TA, TC><<<grid, kWarps * 32, smem, stream>>>(a);
-  }););
+  SKYLA_DISPATCH(in_dtype, TI, SKYLA_DISPATCH(act_dtype, TA, SKYLA_DISPATCH(cache_dtype, TC, {
+    prep_kernel<TI, TA, TC><<<grid, kWarps * 32, smem, stream>>>(a);
+  });););
   return check_launch("qk_norm_rope_cache");
 }

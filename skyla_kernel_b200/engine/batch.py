@@ -87,10 +87,24 @@ class StepContext:
     #: when profiling: (label, event) pairs, an event after each stage
     #: (the reference's timestamp marks, skyla-engine/src/graph.rs:54-57)
     marks: Optional[list] = None
+    #: K-split partial sums [splits, tokens, hidden] that still have to be added to the
+    #: residual stream; the next norm (or fold_pending) adds them in a fixed order
+    pending: Optional[torch.Tensor] = None
 
     @property
     def is_decode(self) -> bool:
         return self.max_new == 1
+
+    def take_pending(self) -> Optional[torch.Tensor]:
+        p, self.pending = self.pending, None
+        return p
+
+    def fold_pending(self, x: torch.Tensor) -> None:
+        """Make ``x`` whole for a reader that is not a norm."""
+        p = self.take_pending()
+        if p is not None:
+            from ..kernels import ops
+            ops.fold_partials(x, p)
 
     def mark(self, label: str) -> None:
         """End of a stage; a no-op unless the step is profiled."""

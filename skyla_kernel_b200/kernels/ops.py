@@ -128,6 +128,42 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor
     return out
 
 
+def add_rmsnorm(x: torch.Tensor, partials: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,
+                rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """x[r] += sum_s partials[s, r] (written back), then out = rmsnorm(x[r]) * weight.
+
+    ``partials``: float32 [splits, tokens, width], the K-split sums a matrix product left.
+    """
+    _cuda(x, partials, weight, out, rows)
+    _i32(rows, "rows")
+    if x.dtype != torch.float32 or partials.dtype != torch.float32 or partials.dim() != 3 or not partials.is_contiguous():
+        raise KernelError("add_rmsnorm: x and the contiguous [splits, tokens, width] partials must be float32")
+    width = weight.numel()
+    n = rows.numel() if rows is not None else x.shape[0]
+    if x.shape[1] != width or partials.shape[2] != width or partials.shape[1] != x.shape[0] or out.shape[0] < n:
+        raise KernelError(f"add_rmsnorm: shapes x {tuple(x.shape)} partials {tuple(partials.shape)} out {tuple(out.shape)}")
+    f = _fn("norm", "skyla_add_rmsnorm",
+            [c_void_p, c_int64, c_void_p, c_int, c_int64, c_int64, c_void_p, c_int, c_int, c_void_p, c_float,
+             c_void_p, c_int, c_int64, c_void_p])
+    _check("norm", f(_ptr(x), _rows(x, "x"), _ptr(partials), partials.shape[0], partials.stride(0), partials.stride(1),
+                     _ptr(rows), n, width, _ptr(weight), float(eps), _ptr(out), dtype_code(out), _rows(out, "out"),
+                     _stream()))
+    return out
+
+
+def fold_partials(x: torch.Tensor, partials: torch.Tensor) -> torch.Tensor:
+    """x += sum_s partials[s] in ascending s."""
+    _cuda(x, partials)
+    if x.dtype != torch.float32 or partials.dtype != torch.float32 or partials.dim() != 3 or not partials.is_contiguous():
+        raise KernelError("fold_partials: float32 x and contiguous [splits, tokens, width] partials")
+    if tuple(partials.shape[1:]) != tuple(x.shape):
+        raise KernelError("fold_partials: shapes differ")
+    f = _fn("norm", "skyla_fold_partials", [c_void_p, c_int64, c_void_p, c_int, c_int64, c_int64, c_int, c_int, c_void_p])
+    _check("norm", f(_ptr(x), _rows(x, "x"), _ptr(partials), partials.shape[0], partials.stride(0), partials.stride(1),
+                     x.shape[0], x.shape[1], _stream()))
+    return x
+
+
 # --------------------------------------------------------------------- linear
 STORE, ACCUMULATE, GATED = 0, 1, 2
 
@@ -261,34 +297,49 @@ def qk_norm_rope_cache(qkv: torch.Tensor, q_off: int, k_off: int, v_off: int, nq
                        eps: float, cos: Optional[torch.Tensor], sin: Optional[torch.Tensor],
                        n_rot: int, tok_pos: torch.Tensor, tok_slot: torch.Tensor,
                        k_pool: Optional[torch.Tensor], v_pool: Optional[torch.Tensor],
-                       page_table: torch.Tensor, page_size: int) -> None:
-    """Per-head norm and rotation of the new tokens; q in place, k and v into the cache.
+                       page_table: torch.Tensor, page_size: int, q_out: Optional[torch.Tensor] = None) -> None:
+    """Per-head norm and rotation of the new tokens; q to ``q_out`` (default: in place), k and
+    v into the cache.
 
-    ``k_pool``/``v_pool`` of shape [pages, nkv, page_size, hd]; ``None`` skips the
-    cache write (a run that reads another entry's cache).
+    ``qkv``: [tokens, width] activations, or float32 [splits, tokens, width] K-split partial
+    sums that are added up on the way in (then ``q_out`` is required).  ``k_pool``/``v_pool``
+    of shape [pages, nkv, page_size, hd]; ``None`` skips the cache write (a run that reads
+    another entry's cache).
     """
-    _cuda(qkv, q_norm, k_norm, cos, sin, tok_pos, tok_slot, k_pool, v_pool, page_table)
+    _cuda(qkv, q_norm, k_norm, cos, sin, tok_pos, tok_slot, k_pool, v_pool, page_table, q_out)
     for t, what in ((tok_pos, "tok_pos"), (tok_slot, "tok_slot"), (page_table, "page_table")):
         _i32(t, what)
     for t, what in ((q_norm, "q_norm"), (k_norm, "k_norm"), (cos, "cos"), (sin, "sin")):
         if t is not None and (t.dtype != torch.float32 or not t.is_contiguous()):
             raise KernelError(f"{what}: expected a contiguous float32 tensor")
     n = tok_pos.numel()
+    if qkv.dim() == 3:
+        if q_out is None or not qkv.is_contiguous():
+            raise KernelError("qk_norm_rope_cache: partial sums need a separate, contiguous layout and q_out")
+        n_splits, split_stride, ld = qkv.shape[0], qkv.stride(0), qkv.stride(1)
+    else:
+        n_splits, split_stride, ld = 1, 0, _rows(qkv, "qkv")
+    if q_out is None:
+        q_ptr, q_dt, ldq = c_void_p(qkv.data_ptr() + q_off * qkv.element_size()), dtype_code(qkv), ld
+    else:
+        if q_out.shape[0] < n or q_out.shape[1] < nq * hd:
+            raise KernelError("qk_norm_rope_cache: q_out too small")
+        q_ptr, q_dt, ldq = _ptr(q_out), dtype_code(q_out), _rows(q_out, "q_out")
     if k_pool is not None:
         if (k_pool.shape != v_pool.shape or tuple(k_pool.shape[1:]) != (nkv, page_size, hd)
                 or not k_pool.is_contiguous() or not v_pool.is_contiguous()):
             raise KernelError(f"cache pools {tuple(k_pool.shape)} do not match [pages, {nkv}, {page_size}, {hd}]")
         cdt = dtype_code(k_pool)
     else:
-        cdt = dtype_code(qkv)
+        cdt = q_dt
     if cos is not None and (cos.shape != sin.shape or cos.shape[1] != n_rot // 2):
         raise KernelError("rotary table does not match the rotary width")
     f = _fn("attn_prep", "skyla_qk_norm_rope_cache",
-            [c_void_p, c_int, c_int64, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
-             c_void_p, c_float, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
-             c_int, c_void_p, c_int, c_int, c_void_p])
-    _check("attn_prep", f(_ptr(qkv), dtype_code(qkv), _rows(qkv, "qkv"), q_off, k_off, v_off, n, nq,
-                          nkv, hd, _ptr(q_norm), _ptr(k_norm), float(eps), _ptr(cos), _ptr(sin),
+            [c_void_p, c_int, c_int64, c_int, c_int64, c_void_p, c_int, c_int64, c_int, c_int, c_int, c_int, c_int,
+             c_int, c_int, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+             c_void_p, c_int, c_void_p, c_int, c_int, c_void_p])
+    _check("attn_prep", f(_ptr(qkv), dtype_code(qkv), ld, n_splits, split_stride, q_ptr, q_dt, ldq, q_off, k_off,
+                          v_off, n, nq, nkv, hd, _ptr(q_norm), _ptr(k_norm), float(eps), _ptr(cos), _ptr(sin),
                           n_rot if cos is not None else 0, _ptr(tok_pos), _ptr(tok_slot),
                           _ptr(k_pool), _ptr(v_pool), cdt, _ptr(page_table), page_table.shape[1],
                           page_size, _stream()))

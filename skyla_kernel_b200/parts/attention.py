@@ -121,12 +121,20 @@ class GQAttention(Part):
         if self.position is not None:
             cos, sin, n_rot = self.position.tables(ctx.max_position + 1)
         if entry.owns_cache:
-            qkv = ctx.buffer("attn.qkv", (n, (nq + 2 * nkv) * hd), self.rt.act_dtype)
-            self.qkv.forward(h, qkv, STORE)
-            ctx.mark("matvec qkv")
-            ops.qk_norm_rope_cache(qkv, 0, nq * hd, (nq + nkv) * hd, nq, nkv, hd, self.q_norm_w,
-                                   self.k_norm_w, self.eps, cos, sin, n_rot, ctx.tok_pos, ctx.tok_seq,
-                                   k_pool, v_pool, pages, ctx.page_size)
+            part = self.qkv.forward_partial(h, ctx, "attn.qkv_partials")
+            if part is not None:  # a small batch: the product is K-split, the splits are added up here
+                ctx.mark("matvec qkv")
+                qkv = ctx.buffer("attn.q", (n, nq * hd), self.rt.act_dtype)
+                ops.qk_norm_rope_cache(part, 0, nq * hd, (nq + nkv) * hd, nq, nkv, hd, self.q_norm_w,
+                                       self.k_norm_w, self.eps, cos, sin, n_rot, ctx.tok_pos, ctx.tok_seq,
+                                       k_pool, v_pool, pages, ctx.page_size, q_out=qkv)
+            else:
+                qkv = ctx.buffer("attn.qkv", (n, (nq + 2 * nkv) * hd), self.rt.act_dtype)
+                self.qkv.forward(h, qkv, STORE)
+                ctx.mark("matvec qkv")
+                ops.qk_norm_rope_cache(qkv, 0, nq * hd, (nq + nkv) * hd, nq, nkv, hd, self.q_norm_w,
+                                       self.k_norm_w, self.eps, cos, sin, n_rot, ctx.tok_pos, ctx.tok_seq,
+                                       k_pool, v_pool, pages, ctx.page_size)
         else:  # reads the cache another run wrote: only queries are needed
             qkv = ctx.buffer("attn.q", (n, nq * hd), self.rt.act_dtype)
             self.q_only.forward(h, qkv, STORE)
@@ -149,7 +157,9 @@ class GQAttention(Part):
             ops.attention_plain(q, attn, nq, nkv, hd, k_pool, v_pool, pages, ctx.page_size, ctx.tok_pos,
                                 ctx.tok_seq, self.scale, self.window)
         ctx.mark("attention")
-        self.out.forward(attn, x, ACCUMULATE)
+        ctx.pending = self.out.forward_partial(attn, ctx, "attn.o_partials")
+        if ctx.pending is None:
+            self.out.forward(attn, x, ACCUMULATE)
         ctx.mark("matvec o")
 
 

@@ -11,10 +11,15 @@ mixer, feed-forward, norm, position encoding or block is one ``register_*`` call
 Interfaces (``ctx`` is the step's :class:`~skyla_kernel_b200.engine.batch.StepContext`;
 ``x`` the float32 residual stream ``[tokens, hidden]``):
 
-* norm           ``forward(ctx, x, out, rows=None)``: ``out[r] = norm(x[rows[r]])``
+* norm           ``forward(ctx, x, out, rows=None)``: ``out[r] = norm(x[rows[r]])``; a norm
+                 with ``fuses_pending = True`` also takes ``pending=`` (see below)
 * mixer          ``cache_need()``, ``state_need()``, ``forward(ctx, h, x, entry)``:
                  adds its output to ``x``; ``entry`` says which cache it uses
 * feed-forward   ``forward(ctx, h, x)``: adds its output to ``x``
+                 A mixer or feed-forward may instead leave its output in ``ctx.pending``
+                 as float32 partial sums ``[splits, tokens, hidden]``; the block hands
+                 them to the next norm, which adds them to ``x`` in ascending order, or
+                 calls ``ctx.fold_pending(x)`` for any other reader of ``x``.
 * position       whatever the mixers that accept it read (rotary: ``tables()``)
 * block          ``forward(ctx, x, entry)`` with the four parts above inside
 * embedding      ``forward(ctx, tokens, x)``;  head: ``forward(ctx, h, logits)``

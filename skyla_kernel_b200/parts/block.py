@@ -59,12 +59,21 @@ class PrenormResidualBlock:
 
     def forward(self, ctx, x, entry: EntryBinding) -> None:
         h = ctx.buffer("block.normed", (ctx.n_tokens, x.shape[1]), self.rt.act_dtype)
-        self.mixer_norm.forward(ctx, x, h)
-        ctx.mark("rmsnorm")
+        self._norm(self.mixer_norm, ctx, x, h)
         self.mixer.forward(ctx, h, x, entry)
-        self.ffn_norm.forward(ctx, x, h)
-        ctx.mark("rmsnorm")
+        self._norm(self.ffn_norm, ctx, x, h)
         self.feed_forward.forward(ctx, h, x)
+
+    @staticmethod
+    def _norm(norm, ctx, x, h) -> None:
+        """Norm of the residual stream; partial sums that a product left pending are added
+        to x first, inside the norm kernel where the norm can do that."""
+        if ctx.pending is not None and getattr(norm, "fuses_pending", False):
+            norm.forward(ctx, x, h, pending=ctx.take_pending())
+        else:
+            ctx.fold_pending(x)
+            norm.forward(ctx, x, h)
+        ctx.mark("rmsnorm")
 
 
 register_block("prenorm_residual", PrenormResidualBlock)

@@ -61,7 +61,9 @@ class SwiGLU(Part):
         act = ctx.buffer("ffn.act", (ctx.n_tokens, self.inter), self.rt.act_dtype)
         self.gate_up.forward(h, act, GATED)
         ctx.mark("matvec gate+up, silu")
-        self.down.forward(act, x, ACCUMULATE)
+        ctx.pending = self.down.forward_partial(act, ctx, "ffn.down_partials")
+        if ctx.pending is None:
+            self.down.forward(act, x, ACCUMULATE)
         ctx.mark("matvec down")
 
 

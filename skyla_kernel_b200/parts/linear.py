@@ -57,5 +57,43 @@ class Linear:
             return ops.gemm_tc(x, self.weight_map(), self.n_out, y, tc)
         return ops.linear_plain(x, self.weight, y, mode, self.gated_group)
 
+    # ---- K-split products for small batches
+    N_SMS = 148
+
+    def choose_splits(self, m: int) -> int:
+        """How many K splits make a small batch's product fill the GPU (1: do not split).
+
+        One block per SM is resident; a block costs its K blocks plus about six more
+        for filling and draining its pipeline; at least 16 K blocks stay per split.
+        """
+        if m > 64:
+            return 1
+        bn = ops.token_tile(m)
+        tiles = -(-self.n_out // 128) * -(-m // bn)
+        total = -(-self.n_in // 64)
+        best, best_cost = 1, None
+        for s in range(1, max(1, total // 16) + 1):
+            per = -(-total // s)
+            if (s - 1) * per >= total:
+                continue
+            cost = -(-tiles * s // self.N_SMS) * (per + 6)
+            if best_cost is None or cost < best_cost:
+                best, best_cost = s, cost
+        return best
+
+    def forward_partial(self, x: torch.Tensor, ctx, name: str):
+        """The product as K-split partial sums [splits, tokens, n_out] (float32) in a workspace
+        buffer, or ``None`` when splitting does not pay or the tensor-core kernel does not
+        take these operands; the reader adds the splits up in ascending order."""
+        if self.gated_group or not self.tensor_cores or not ops.tc_linear_ok(x, self.weight):
+            return None
+        m = x.shape[0]
+        splits = self.choose_splits(m)
+        if splits <= 1:
+            return None
+        part = ctx.buffer(name, (splits, m, self.n_out), torch.float32)
+        ops.gemm_tc(x, self.weight_map(), self.n_out, part, ops.TC_PARTIAL_F32, splits=splits)
+        return part
+
     def bytes(self) -> int:
         return self.weight.numel() * self.weight.element_size()

@@ -31,7 +31,13 @@ class RMSNorm(Part):
     def load(self, tensors) -> None:
         self.weight = self.rt.vector(tensors[self.spec.tensors["weight"]])
 
-    def forward(self, ctx, x: torch.Tensor, out: torch.Tensor, rows: Optional[torch.Tensor] = None):
+    #: forward() accepts ``pending`` partial sums and adds them to x on the way
+    fuses_pending = True
+
+    def forward(self, ctx, x: torch.Tensor, out: torch.Tensor, rows: Optional[torch.Tensor] = None,
+                pending: Optional[torch.Tensor] = None):
+        if pending is not None:
+            return ops.add_rmsnorm(x, pending, self.weight, self.eps, out, rows)
         return ops.rmsnorm(x, self.weight, self.eps, out, rows)
 
     def weight_bytes(self) -> int:

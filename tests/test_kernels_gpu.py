@@ -431,3 +431,61 @@ def test_attention_mma_finds_one_far_key():
             for kvh in range(nkv):
                 got = out[0].view(nq, hd)[kvh * 4 + 1].float().cpu()
                 torch.testing.assert_close(got, vs[0][target, kvh].float(), rtol=2e-2, atol=2e-2)
+
+
+# ------------------------------------------------- folding of K-split partial sums
+@pytest.mark.parametrize("width,splits", [(80, 2), (4096, 4)])
+def test_add_rmsnorm_and_fold(width, splits):
+    ops = _ops()
+    x0 = _rand(9, width, seed=51, scale=2.0)
+    part = _rand(splits, 9, width, seed=52)
+    w = 1 + 0.1 * _rand(width, seed=53)
+    whole = x0.clone()
+    for s_ in range(splits):
+        whole += part[s_]
+    for out_dtype in (torch.float32, torch.bfloat16):
+        x = x0.clone()
+        out = torch.empty(9, width, dtype=out_dtype, device=DEV)
+        ops.add_rmsnorm(x, part, w, 1e-5, out)
+        assert torch.equal(x, whole)  # ascending order, the same bits
+        ref = torch.empty_like(out)
+        ops.rmsnorm(whole, w, 1e-5, ref)
+        assert torch.equal(out, ref)
+    rows = torch.tensor([8, 2], dtype=torch.int32, device=DEV)
+    x = x0.clone()
+    out = torch.empty(2, width, device=DEV)
+    ops.add_rmsnorm(x, part, w, 1e-5, out, rows)
+    ref = torch.empty(9, width, device=DEV)
+    ops.rmsnorm(whole, w, 1e-5, ref)
+    assert torch.equal(out, ref[rows.long()]) and torch.equal(x[8], whole[8]) and torch.equal(x[0], x0[0])
+    x = x0.clone()
+    ops.fold_partials(x, part)
+    assert torch.equal(x, whole)
+
+
+def test_prep_adds_up_partial_sums():
+    ops = _ops()
+    nq, nkv, hd, T, S = 4, 2, 32, 5, 3
+    width = (nq + 2 * nkv) * hd
+    part = _rand(S, T, width, seed=61)
+    whole = part[0].clone()
+    for s_ in range(1, S):
+        whole += part[s_]
+    qn, kn = 1 + 0.2 * _rand(hd, seed=62), 1 + 0.2 * _rand(hd, seed=63)
+    freqs, _ = plain.rope_frequencies(hd, 10000.0)
+    ang = (torch.arange(100, dtype=torch.float32)[:, None] * freqs[None, :]).double()
+    cos, sin = torch.cos(ang).float().to(DEV), torch.sin(ang).float().to(DEV)
+    pos = torch.tensor([0, 1, 64, 65, 3], dtype=torch.int32, device=DEV)
+    seq = torch.tensor([0, 0, 0, 0, 1], dtype=torch.int32, device=DEV)
+    table = torch.tensor([[1, 2], [0, 3]], dtype=torch.int32, device=DEV)
+    res = []
+    for src in (part, whole.to(torch.bfloat16)):
+        kp = torch.zeros(4, nkv, 64, hd, dtype=torch.bfloat16, device=DEV)
+        vp = torch.zeros_like(kp)
+        q = torch.zeros(T, nq * hd, dtype=torch.bfloat16, device=DEV)
+        ops.qk_norm_rope_cache(src, 0, nq * hd, (nq + nkv) * hd, nq, nkv, hd, qn, kn, 1e-6, cos, sin, hd, pos, seq,
+                               kp, vp, table, 64, q_out=q)
+        res.append((q, kp, vp))
+    for a, b in zip(res[0], res[1]):  # from 32-bit sums against from the rounded whole: bf16 apart at most
+        torch.testing.assert_close(a.float(), b.float(), rtol=2e-2, atol=2e-2)
+    assert res[0][0].abs().sum() > 0 and res[0][1].abs().sum() > 0
