@@ -14,14 +14,16 @@
 //               come from global memory as contiguous 16..32-byte pieces, with the
 //               output columns permuted so that each thread's piece is contiguous;
 //               the permutation is undone when O is written.
-// No shared-memory staging: every key/value byte is loaded once per warp that
-// needs it, 16 bytes at a time.
+// A block stages whole cache pages (64 positions of one key/value head, contiguous
+// in the pool) in shared memory with cp.async, several pages deep, with the 16-byte
+// chunks of a row swizzled (or the rows padded) so that the fragment reads spread
+// over the banks; the warps read their fragments from there, 16 bytes at a time.
 //
 // Decode: one CTA per (key/value head, sequence, split of the context); the 16 rows
 // are the query heads that share the key/value head (grouped-query attention), so
 // the cache is read once for all of them, as the reference does with N_REP
-// (attention.comp:60-79).  The CTA's four warps take pages in turn and are merged
-// in shared memory; splits are aligned to absolute positions and merged by a
+// (attention.comp:60-79).  The CTA's eight warps work on two pages at a time, 16 of
+// a page's 64 positions each; the warps are merged in shared memory; splits are aligned to absolute positions and merged by a
 // second kernel in fixed order (skyla-shaders/shaders/attention_merge.comp:17-41).
 // Prefill: one CTA per (64 new tokens of one sequence, query head), a warp per 16
 // tokens, causal by row.
@@ -55,14 +57,30 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
-// A row's fragment: thread t of a quad takes elements 32*kb + 8t .. +7 of each
-// 32-wide block (and 4t .. +3 of a trailing 16-wide one).
+// Shared-memory rows of 128 or 256 bytes are not padded; their 16-byte chunks are
+// XOR-swizzled so that the eight threads of a quarter warp hit eight different bank
+// groups.  K rows: chunk ^ 4*(row & 1).  V rows: chunk ^ a value that depends on which
+// thread of a quad reads the row.  Other head sizes use rows padded by 16 bytes.
 template <int HD>
-__device__ __forceinline__ void load_row(const bf16* __restrict__ row, int t, uint32_t (&out)[Shape<HD>::NQ]) {
+struct Swz {
+  static constexpr bool kOn = HD % 64 == 0;
+  static constexpr int RS = kOn ? HD : HD + 8;  // row stride in elements
+  __device__ static __forceinline__ int k(int row) { return kOn ? ((row & 1) << 2) : 0; }
+  __device__ static __forceinline__ int v(int row) {
+    const int q = (row >> 1) & 3;  // rows 2t, 2t+1, 8+2t, 9+2t are read by thread t of a quad
+    return !kOn ? 0 : (HD == 64 ? 2 * q : ((q & 1) | ((q & 2) << 1)));
+  }
+};
+
+// A row's fragment: thread t of a quad takes elements 32*kb + 8t .. +7 of each
+// 32-wide block (and 4t .. +3 of a trailing 16-wide one).  `x` is the XOR applied
+// to the 16-byte chunk index (0 for rows in global memory).
+template <int HD>
+__device__ __forceinline__ void load_row(const bf16* __restrict__ row, int t, uint32_t (&out)[Shape<HD>::NQ], int x = 0) {
   using S = Shape<HD>;
 #pragma unroll
   for (int kb = 0; kb < S::KB32; ++kb) {
-    const uint4 v = *reinterpret_cast<const uint4*>(row + 32 * kb + 8 * t);
+    const uint4 v = *reinterpret_cast<const uint4*>(row + 8 * ((4 * kb + t) ^ x));
     out[4 * kb] = v.x; out[4 * kb + 1] = v.y; out[4 * kb + 2] = v.z; out[4 * kb + 3] = v.w;
   }
   if (S::TAIL16) {
@@ -72,22 +90,23 @@ __device__ __forceinline__ void load_row(const bf16* __restrict__ row, int t, ui
 }
 // A thread's piece of a V row: columns g*HD/8 .. (g+1)*HD/8 - 1.
 template <int HD>
-__device__ __forceinline__ void load_v(const bf16* __restrict__ row, int g, uint32_t (&out)[Shape<HD>::NV]) {
+__device__ __forceinline__ void load_v(const bf16* __restrict__ row, int g, uint32_t (&out)[Shape<HD>::NV], int x = 0) {
   constexpr int NV = Shape<HD>::NV;
-  const bf16* p = row + g * (HD / 8);
   if (NV % 4 == 0) {
 #pragma unroll
     for (int i = 0; i < NV / 4; ++i) {
-      const uint4 v = reinterpret_cast<const uint4*>(p)[i];
+      const uint4 v = *reinterpret_cast<const uint4*>(row + 8 * ((g * (NV / 4) + i) ^ x));
       out[4 * i] = v.x; out[4 * i + 1] = v.y; out[4 * i + 2] = v.z; out[4 * i + 3] = v.w;
     }
   } else if (NV % 2 == 0) {
+    const bf16* p = row + g * (HD / 8);
 #pragma unroll
     for (int i = 0; i < NV / 2; ++i) {
       const uint2 v = reinterpret_cast<const uint2*>(p)[i];
       out[2 * i] = v.x; out[2 * i + 1] = v.y;
     }
   } else {
+    const bf16* p = row + g * (HD / 8);
 #pragma unroll
     for (int i = 0; i < NV; ++i) out[i] = reinterpret_cast<const uint32_t*>(p)[i];
   }
@@ -105,7 +124,7 @@ struct RowState {
 };
 
 // 16 keys starting at absolute position key0; k16/v16 point at their rows for one
-// key/value head (row stride HD).  Rows g and g+8 of the tile see positions lo..hi.
+// key/value head, staged in shared memory.  Rows g and g+8 of the tile see positions lo..hi.
 template <int HD>
 __device__ __forceinline__ void attend16(const uint32_t (&qa)[Shape<HD>::NQ], const uint32_t (&qb)[Shape<HD>::NQ],
                                          const bf16* __restrict__ k16, const bf16* __restrict__ v16, int key0,
@@ -113,12 +132,13 @@ __device__ __forceinline__ void attend16(const uint32_t (&qa)[Shape<HD>::NQ], co
                                          int g, int t) {
   using S = Shape<HD>;
   uint32_t kf[2][S::NQ], vf[4][S::NV];
-  load_row<HD>(k16 + (size_t)g * HD, t, kf[0]);
-  load_row<HD>(k16 + (size_t)(8 + g) * HD, t, kf[1]);
-  load_v<HD>(v16 + (size_t)(2 * t) * HD, g, vf[0]);
-  load_v<HD>(v16 + (size_t)(2 * t + 1) * HD, g, vf[1]);
-  load_v<HD>(v16 + (size_t)(8 + 2 * t) * HD, g, vf[2]);
-  load_v<HD>(v16 + (size_t)(8 + 2 * t + 1) * HD, g, vf[3]);
+  constexpr int RS = Swz<HD>::RS;  // k16/v16 are staged rows in shared memory
+  load_row<HD>(k16 + (size_t)g * RS, t, kf[0], Swz<HD>::k(g));
+  load_row<HD>(k16 + (size_t)(8 + g) * RS, t, kf[1], Swz<HD>::k(8 + g));
+  load_v<HD>(v16 + (size_t)(2 * t) * RS, g, vf[0], Swz<HD>::v(2 * t));
+  load_v<HD>(v16 + (size_t)(2 * t + 1) * RS, g, vf[1], Swz<HD>::v(2 * t + 1));
+  load_v<HD>(v16 + (size_t)(8 + 2 * t) * RS, g, vf[2], Swz<HD>::v(8 + 2 * t));
+  load_v<HD>(v16 + (size_t)(8 + 2 * t + 1) * RS, g, vf[3], Swz<HD>::v(8 + 2 * t + 1));
 
   float s[2][4];
 #pragma unroll
@@ -182,22 +202,38 @@ struct PagedKV {
   const bf16* k; const bf16* v; const int32_t* pages; int max_pages, page_size, nkv;
 };
 
+// ---- staging of cache pages in shared memory
+constexpr int kPage = 64;     // positions per staged page: the cache's page size
 template <int HD>
-__device__ __forceinline__ void attend_pages(const uint32_t (&qa)[Shape<HD>::NQ], const uint32_t (&qb)[Shape<HD>::NQ],
-                                             const PagedKV& kv, const int32_t* seq_pages, int kvh, int page_begin,
-                                             int page_end, int page_step, int lo, int hi, int lo0, int hi0,
-                                             int lo1, int hi1, float scale_log2, RowState<HD>& st, int g, int t) {
-  // lo..hi: the positions any row of this warp sees; the same in all lanes, so the
-  // warp stays converged for mma.sync
-  for (int pg = page_begin; pg < page_end; pg += page_step) {
-    const size_t row0 = ((size_t)seq_pages[pg] * kv.nkv + kvh) * kv.page_size;
-    for (int off = 0; off < kv.page_size; off += 16) {
-      const int key0 = pg * kv.page_size + off;
-      if (key0 > hi) break;
-      if (key0 + 15 < lo) continue;
-      attend16<HD>(qa, qb, kv.k + (row0 + off) * HD, kv.v + (row0 + off) * HD, key0, lo0, hi0, lo1, hi1,
-                   scale_log2, st, g, t);
-    }
+struct Stage {
+  static constexpr int RS = Swz<HD>::RS;
+  static constexpr int kElems = 2 * kPage * RS;        // K page then V page
+  static constexpr int kPageBytes = kElems * (int)sizeof(bf16);
+  // decode: eight warps work on two pages at a time and the block is alone on its SM, so its
+  // own loads must cover the memory latency: as many pages as about 192 KB hold (even, 4..6)
+  static constexpr int kDecodeRaw = (192 * 1024) / kPageBytes;
+  static constexpr int kDecodeStages = kDecodeRaw >= 6 ? 6 : 4;
+  // prefill: compute-bound; three pages deep leaves room for two blocks per SM
+  static constexpr int kPrefillStages = 3;
+};
+
+__device__ __forceinline__ void cp_async16(void* dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// NT threads (tid 0..NT-1) copy one page (64 rows of HD elements, contiguous in the pool) of K and of V.
+template <int HD, int NT>
+__device__ __forceinline__ void stage_page(bf16* stage, const bf16* __restrict__ kg, const bf16* __restrict__ vg, int tid) {
+  constexpr int RS = Stage<HD>::RS, CPR = HD / 8;  // 16-byte chunks per row
+  bf16* sk = stage;
+  bf16* sv = stage + kPage * RS;
+  for (int c = tid; c < kPage * CPR; c += NT) {
+    const int row = c / CPR, chunk = c % CPR;
+    cp_async16(sk + row * RS + 8 * (chunk ^ Swz<HD>::k(row)), kg + row * HD + 8 * chunk);
+    cp_async16(sv + row * RS + 8 * (chunk ^ Swz<HD>::v(row)), vg + row * HD + 8 * chunk);
   }
 }
 
@@ -207,18 +243,41 @@ struct DecodeArgs {
   int nq, nkv; PagedKV kv; const int32_t* tok_pos; float scale; int window;
 };
 
+constexpr int kDecodeWarps = 8;
+
 template <int HD>
-__global__ void __launch_bounds__(128) attn_decode_kernel(DecodeArgs a) {
+__global__ void __launch_bounds__(kDecodeWarps * 32) attn_decode_kernel(DecodeArgs a) {
   using S = Shape<HD>;
-  extern __shared__ float smem[];  // [4 warps][16 rows][HD] outputs, then [4][16] m and l
+  constexpr int RS = Stage<HD>::RS, kStages = Stage<HD>::kDecodeStages, NW = kDecodeWarps;
+  extern __shared__ __align__(16) uint8_t smem_raw[];
+  bf16* stages = reinterpret_cast<bf16*>(smem_raw);
+  float* smem = reinterpret_cast<float*>(smem_raw);  // after the loop: [NW][16 rows][HD], [NW][16] m, [NW][16] l
+  allow_dependents();
+  grid_dependency_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   const int kvh = blockIdx.x, b = blockIdx.y, split = blockIdx.z;
   const int G = a.nq / a.nkv;
   const int pos = a.tok_pos[b];
   const int first = a.window > 0 ? max(0, pos - a.window + 1) : 0;
-  const int ps = a.kv.page_size;
-  const int page_begin = max(split * a.pages_per_split, first / ps);
-  const int page_end = min((split + 1) * a.pages_per_split, pos / ps + 1);
+  const int page_begin = max(split * a.pages_per_split, first / kPage);
+  const int page_end = min((split + 1) * a.pages_per_split, pos / kPage + 1);
+  const int n_pages = max(0, page_end - page_begin);
+  const int n_pairs = (n_pages + 1) / 2;  // warps 0-3 take the first page of a pair, warps 4-7 the second
+  const int32_t* seq_pages = a.kv.pages + (int64_t)b * a.kv.max_pages;
+
+  // half of the threads copy the first page of a pair, the other half the second
+  auto issue = [&](int pair) {
+    const int i = 2 * pair + (warp >> 2);
+    if (i < n_pages) {
+      const size_t row0 = ((size_t)seq_pages[page_begin + i] * a.kv.nkv + kvh) * kPage;
+      stage_page<HD, 128>(stages + (size_t)(i % kStages) * Stage<HD>::kElems, a.kv.k + row0 * HD, a.kv.v + row0 * HD,
+                          threadIdx.x & 127);
+    }
+    cp_async_commit();  // an empty group keeps the count the same for every thread
+  };
+  constexpr int kPairsAhead = kStages / 2 - 1;
+#pragma unroll
+  for (int i = 0; i < kPairsAhead; ++i) issue(i);
 
   uint32_t qa[S::NQ], qb[S::NQ];
 #pragma unroll
@@ -227,34 +286,47 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(DecodeArgs a) {
   if (g < G) load_row<HD>(qrow + g * HD, t, qa);
   if (g + 8 < G) load_row<HD>(qrow + (g + 8) * HD, t, qb);
   const int hi0 = g < G ? pos : -1, hi1 = g + 8 < G ? pos : -1;
+  const float scale_log2 = a.scale * kLog2e;
 
   RowState<HD> st;
   st.init();
-  attend_pages<HD>(qa, qb, a.kv, a.kv.pages + (int64_t)b * a.kv.max_pages, kvh, page_begin + warp, page_end, 4,
-                   first, pos, first, hi0, first, hi1, a.scale * kLog2e, st, g, t);
+  for (int pr = 0; pr < n_pairs; ++pr) {
+    issue(pr + kPairsAhead);
+    cp_async_wait<kPairsAhead>();
+    __syncthreads();
+    const int i = 2 * pr + (warp >> 2);
+    const bf16* sk = stages + (size_t)(i % kStages) * Stage<HD>::kElems;
+    const int key0 = (page_begin + i) * kPage + 16 * (warp & 3);  // this warp's 16 positions
+    if (i < n_pages && key0 <= pos && key0 + 15 >= first)
+      attend16<HD>(qa, qb, sk + 16 * (warp & 3) * RS, sk + (kPage + 16 * (warp & 3)) * RS, key0, first, hi0, first, hi1,
+                   scale_log2, st, g, t);
+    __syncthreads();  // the stages are refilled in the next round
+  }
+  cp_async_wait<0>();
+  __syncthreads();
   // this thread's shares of the row sums -> whole rows
   st.l[0] += __shfl_xor_sync(0xffffffffu, st.l[0], 1); st.l[0] += __shfl_xor_sync(0xffffffffu, st.l[0], 2);
   st.l[1] += __shfl_xor_sync(0xffffffffu, st.l[1], 1); st.l[1] += __shfl_xor_sync(0xffffffffu, st.l[1], 2);
 
   float* so = smem + (size_t)warp * 16 * HD;
-  float* sm = smem + (size_t)4 * 16 * HD + warp * 16;
-  float* sl = sm + 64;
+  float* sm = smem + (size_t)NW * 16 * HD + warp * 16;
+  float* sl = sm + NW * 16;
 #pragma unroll
   for (int n = 0; n < S::NT; ++n)
 #pragma unroll
     for (int i = 0; i < 4; ++i) so[(g + 8 * (i >> 1)) * HD + out_col<HD>(n, i, t)] = st.o[n][i];
   if (t == 0) { sm[g] = st.m[0]; sm[g + 8] = st.m[1]; sl[g] = st.l[0]; sl[g + 8] = st.l[1]; }
   __syncthreads();
-  // merge the four warps, fixed order; one partial per (head, split): m, l, acc[HD]
-  const float* am = smem + (size_t)4 * 16 * HD;
-  const float* al = am + 64;
-  for (int idx = threadIdx.x; idx < G * HD; idx += 128) {
+  // merge the warps in fixed order; one partial per (head, split): m, l, acc[HD]
+  const float* am = smem + (size_t)NW * 16 * HD;
+  const float* al = am + NW * 16;
+  for (int idx = threadIdx.x; idx < G * HD; idx += NW * 32) {
     const int r = idx / HD, c = idx % HD;
     float M = -INFINITY;
-    for (int w = 0; w < 4; ++w) M = fmaxf(M, am[w * 16 + r]);
+    for (int w = 0; w < NW; ++w) M = fmaxf(M, am[w * 16 + r]);
     const float ref = M == -INFINITY ? 0.f : M;
     float acc = 0.f, L = 0.f;
-    for (int w = 0; w < 4; ++w) {
+    for (int w = 0; w < NW; ++w) {
       const float f = exp2f(am[w * 16 + r] - ref);
       acc += f * smem[((size_t)w * 16 + r) * HD + c];
       L += f * al[w * 16 + r];
@@ -268,6 +340,8 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(DecodeArgs a) {
 struct MergeArgs { const float* part; bf16* out; int64_t ldo; int nq, n_splits, hd; };
 
 __global__ void __launch_bounds__(128) attn_merge_kernel(MergeArgs a) {
+  allow_dependents();
+  grid_dependency_wait();
   const int h = blockIdx.x, b = blockIdx.y;
   const float* p = a.part + ((size_t)b * a.nq + h) * a.n_splits * (a.hd + 2);
   float M = -INFINITY;
@@ -291,41 +365,75 @@ struct PrefillArgs {
 template <int HD>
 __global__ void __launch_bounds__(128) attn_prefill_kernel(PrefillArgs a) {
   using S = Shape<HD>;
-  extern __shared__ float smem[];  // [4 warps][16 rows][HD]
+  constexpr int RS = Stage<HD>::RS, kStages = Stage<HD>::kPrefillStages;
+  extern __shared__ __align__(16) uint8_t smem_raw[];
+  bf16* stages = reinterpret_cast<bf16*>(smem_raw);
+  float* smem = reinterpret_cast<float*>(smem_raw);  // after the loop: [4 warps][16 rows][HD]
+  allow_dependents();
+  grid_dependency_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   const int tile = blockIdx.x, h = blockIdx.y, kvh = h / (a.nq / a.nkv);
   const int b = a.tile_seq[tile], tok0 = a.tile_tok0[tile], rows = a.tile_rows[tile];
+  // the tile's rows are consecutive positions of one sequence
+  const int pos_first = a.tok_pos[tok0], pos_last = pos_first + rows - 1;
+  const int tile_lo = a.window > 0 ? max(0, pos_first - a.window + 1) : 0;
+  const int page_begin = tile_lo / kPage, n_pages = pos_last / kPage + 1 - page_begin;
+  const int32_t* seq_pages = a.kv.pages + (int64_t)b * a.kv.max_pages;
+
+  auto issue = [&](int i) {
+    if (i < n_pages) {
+      const size_t row0 = ((size_t)seq_pages[page_begin + i] * a.kv.nkv + kvh) * kPage;
+      stage_page<HD, 128>(stages + (size_t)(i % kStages) * Stage<HD>::kElems, a.kv.k + row0 * HD, a.kv.v + row0 * HD,
+                          threadIdx.x);
+    }
+    cp_async_commit();
+  };
+#pragma unroll
+  for (int i = 0; i < kStages - 1; ++i) issue(i);
+
   const int r0 = warp * 16 + g, r1 = r0 + 8;
-  if (warp * 16 >= rows) return;  // whole warp idle
   uint32_t qa[S::NQ], qb[S::NQ];
 #pragma unroll
   for (int i = 0; i < S::NQ; ++i) qa[i] = qb[i] = 0u;
-  int hi0 = -1, hi1 = -1, lo0 = 0, lo1 = 0;
+  // rows that do not exist see nothing: lo > hi
+  int hi0 = 0, hi1 = 0, lo0 = 1, lo1 = 1;
   if (r0 < rows) {
-    hi0 = a.tok_pos[tok0 + r0];
+    hi0 = pos_first + r0;
     lo0 = a.window > 0 ? max(0, hi0 - a.window + 1) : 0;
     load_row<HD>(a.q + (int64_t)(tok0 + r0) * a.ldq + (int64_t)h * HD, t, qa);
   }
   if (r1 < rows) {
-    hi1 = a.tok_pos[tok0 + r1];
+    hi1 = pos_first + r1;
     lo1 = a.window > 0 ? max(0, hi1 - a.window + 1) : 0;
     load_row<HD>(a.q + (int64_t)(tok0 + r1) * a.ldq + (int64_t)h * HD, t, qb);
   }
-  // the warp's 16 rows are consecutive positions: pages from its lowest visible key to its last row
-  int wlo = hi0 >= 0 ? lo0 : 0x7fffffff, whi = max(hi0, hi1);
-  if (hi1 >= 0) wlo = min(wlo, lo1);
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) {
-    wlo = min(wlo, __shfl_xor_sync(0xffffffffu, wlo, o));
-    whi = max(whi, __shfl_xor_sync(0xffffffffu, whi, o));
-  }
-  const int ps = a.kv.page_size;
+  // what any row of this warp sees: the same in all lanes, so the warp stays converged for mma.sync
+  const bool warp_live = warp * 16 < rows;
+  const int w_first = pos_first + warp * 16, w_last = min(pos_last, w_first + 15);
+  const int wlo = a.window > 0 ? max(0, w_first - a.window + 1) : 0, whi = w_last;
+  const float scale_log2 = a.scale * kLog2e;
+
   RowState<HD> st;
   st.init();
-  // rows that do not exist see nothing: lo > hi
-  attend_pages<HD>(qa, qb, a.kv, a.kv.pages + (int64_t)b * a.kv.max_pages, kvh, wlo / ps, whi / ps + 1, 1,
-                   wlo, whi, hi0 >= 0 ? lo0 : 1, hi0 >= 0 ? hi0 : 0, hi1 >= 0 ? lo1 : 1, hi1 >= 0 ? hi1 : 0,
-                   a.scale * kLog2e, st, g, t);
+  for (int i = 0; i < n_pages; ++i) {
+    issue(i + kStages - 1);
+    cp_async_wait<kStages - 1>();
+    __syncthreads();
+    const bf16* sk = stages + (size_t)(i % kStages) * Stage<HD>::kElems;
+    if (warp_live) {
+#pragma unroll 1
+      for (int off = 0; off < kPage; off += 16) {
+        const int key0 = (page_begin + i) * kPage + off;
+        if (key0 > whi) break;
+        if (key0 + 15 < wlo) continue;
+        attend16<HD>(qa, qb, sk + off * RS, sk + (kPage + off) * RS, key0, lo0, hi0, lo1, hi1, scale_log2, st, g, t);
+      }
+    }
+    __syncthreads();
+  }
+  cp_async_wait<0>();
+  __syncthreads();
+  if (!warp_live) return;
   st.l[0] += __shfl_xor_sync(0xffffffffu, st.l[0], 1); st.l[0] += __shfl_xor_sync(0xffffffffu, st.l[0], 2);
   st.l[1] += __shfl_xor_sync(0xffffffffu, st.l[1], 1); st.l[1] += __shfl_xor_sync(0xffffffffu, st.l[1], 2);
   const float inv0 = st.l[0] > 0.f ? 1.f / st.l[0] : 0.f, inv1 = st.l[1] > 0.f ? 1.f / st.l[1] : 0.f;
@@ -346,26 +454,28 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(PrefillArgs a) {
 
 template <int HD>
 int launch_decode(const DecodeArgs& a, int n_seqs, cudaStream_t stream) {
-  const size_t smem = (size_t)(4 * 16 * HD + 128) * sizeof(float);
+  size_t smem = (size_t)(kDecodeWarps * 16 * HD + 2 * kDecodeWarps * 16) * sizeof(float);
+  if (smem < (size_t)Stage<HD>::kDecodeStages * Stage<HD>::kPageBytes) smem = (size_t)Stage<HD>::kDecodeStages * Stage<HD>::kPageBytes;
   static bool configured = false;
   if (!configured && smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return fail(kLaunchFailed, "attention_decode: shared memory: %s", cudaGetErrorString(e));
   }
   configured = true;
-  attn_decode_kernel<HD><<<dim3(a.nkv, n_seqs, a.n_splits), 128, smem, stream>>>(a);
+  launch_overlapped(attn_decode_kernel<HD>, dim3(a.nkv, n_seqs, a.n_splits), dim3(kDecodeWarps * 32), smem, stream, a);
   return check_launch("attention_decode");
 }
 template <int HD>
 int launch_prefill(const PrefillArgs& a, int n_tiles, cudaStream_t stream) {
-  const size_t smem = (size_t)(4 * 16 * HD) * sizeof(float);
+  size_t smem = (size_t)(4 * 16 * HD) * sizeof(float);
+  if (smem < (size_t)Stage<HD>::kPrefillStages * Stage<HD>::kPageBytes) smem = (size_t)Stage<HD>::kPrefillStages * Stage<HD>::kPageBytes;
   static bool configured = false;
   if (!configured && smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return fail(kLaunchFailed, "attention_prefill: shared memory: %s", cudaGetErrorString(e));
   }
   configured = true;
-  attn_prefill_kernel<HD><<<dim3(n_tiles, a.nq), 128, smem, stream>>>(a);
+  launch_overlapped(attn_prefill_kernel<HD>, dim3(n_tiles, a.nq), dim3(128), smem, stream, a);
   return check_launch("attention_prefill");
 }
 
@@ -384,7 +494,7 @@ int launch_prefill(const PrefillArgs& a, int n_tiles, cudaStream_t stream) {
 
 int check_common(const void* q, int64_t ldq, int nq, int nkv, int page_size, const void* k, const void* v) {
   if (nkv <= 0 || nq % nkv) return fail(kBadArgument, "attention_mma: %d query heads over %d key/value heads", nq, nkv);
-  if (page_size % 16) return fail(kBadArgument, "attention_mma: pages of %d positions are not whole blocks of 16", page_size);
+  if (page_size != kPage) return fail(kBadArgument, "attention_mma: pages of %d positions, the kernels stage pages of %d", page_size, kPage);
   if (((uintptr_t)q) % 16 || (ldq * 2) % 16 || ((uintptr_t)k) % 16 || ((uintptr_t)v) % 16)
     return fail(kBadArgument, "attention_mma: operands must be 16-byte aligned");
   return kOk;
@@ -414,7 +524,7 @@ extern "C" int skyla_attention_decode(const void* q, int64_t ldq, void* out, int
   SKYLA_HD_SWITCH(hd, { rc = launch_decode<HD>(a, n_seqs, stream); break; });
   if (rc) return rc;
   MergeArgs m{part, (bf16*)out, ldo, nq, n_splits, hd};
-  attn_merge_kernel<<<dim3(nq, n_seqs), 128, 0, stream>>>(m);
+  launch_overlapped(attn_merge_kernel, dim3(nq, n_seqs), dim3(128), 0, stream, m);
   return check_launch("attention_merge");
 }
 

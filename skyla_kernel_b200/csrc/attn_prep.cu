@@ -31,6 +31,8 @@ struct PrepArgs {
 template <typename TI, typename TA, typename TC>
 __global__ void __launch_bounds__(kWarps * 32) prep_kernel(PrepArgs a) {
   extern __shared__ float smem[];
+  allow_dependents();
+  grid_dependency_wait();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int head = blockIdx.x * kWarps + warp;
   const int t = blockIdx.y;
@@ -107,7 +109,7 @@ extern "C" int skyla_qk_norm_rope_cache(
   dim3 grid((nq + 2 * nkv + kWarps - 1) / kWarps, n_tokens);
   const size_t smem = (size_t)kWarps * hd * sizeof(float);
   SKYLA_DISPATCH(in_dtype, TI, SKYLA_DISPATCH(act_dtype, TA, SKYLA_DISPATCH(cache_dtype, TC, {
-    prep_kernel<TI, TA, TC><<<grid, kWarps * 32, smem, stream>>>(a);
+    launch_overlapped(prep_kernel<TI, TA, TC>, grid, dim3(kWarps * 32), smem, stream, a);
   });););
   return check_launch("qk_norm_rope_cache");
 }

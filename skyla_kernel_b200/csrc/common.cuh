@@ -7,6 +7,9 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <stdio.h>
+#include <stdlib.h>
+
+#include <utility>
 
 namespace skyla {
 
@@ -35,6 +38,42 @@ inline int check_launch(const char* what) {
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return fail(kLaunchFailed, "%s: %s", what, cudaGetErrorString(e));
   return kOk;
+}
+
+// Programmatic dependent launch: a kernel launched through launch_overlapped() may
+// start while the kernel before it in the stream is still running.  It must call
+// grid_dependency_wait() before it reads anything an earlier kernel wrote and before
+// it writes anything at all (an earlier kernel may still be reading it); what it does
+// before that (set up barriers, allocate tensor memory, prefetch weights that no
+// kernel writes) overlaps with its predecessor.  allow_dependents() lets the next
+// kernel be scheduled as soon as every block of this one has got that far.  Without
+// the launch attribute both are no-ops.  SKYLA_NO_PDL=1 turns the attribute off.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void allow_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+inline bool overlap_enabled() {
+  static int on = -1;
+  if (on < 0) {
+    const char* e = getenv("SKYLA_NO_PDL");
+    on = (e != nullptr && e[0] == '1') ? 0 : 1;
+  }
+  return on == 1;
+}
+
+template <typename... KArgs, typename... Args>
+inline void launch_overlapped(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                              Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = overlap_enabled() ? 1 : 0;
+  cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);  // errors are read by check_launch()
 }
 
 __device__ __forceinline__ float to_float(float v) { return v; }

@@ -8,6 +8,8 @@ SKYLA_EXPORT_ERROR_MESSAGE()
 template <typename TW, typename TO>
 __global__ void embed_gather_kernel(const int32_t* __restrict__ tokens, const TW* __restrict__ table,
                                     int hidden, TO* __restrict__ out, int64_t ldo) {
+  allow_dependents();
+  grid_dependency_wait();
   const int t = blockIdx.x;
   const TW* row = table + (int64_t)tokens[t] * hidden;
   TO* o = out + (int64_t)t * ldo;
@@ -22,8 +24,8 @@ extern "C" int skyla_embed_gather(const int32_t* tokens, int n_tokens, const voi
   if (hidden <= 0 || ldo < hidden) return fail(kBadArgument, "embed_gather: bad width %d", hidden);
   const int threads = hidden >= 1024 ? 256 : 128;
   SKYLA_DISPATCH(table_dtype, TW, SKYLA_DISPATCH(out_dtype, TO, {
-    embed_gather_kernel<TW, TO><<<n_tokens, threads, 0, stream>>>(
-        tokens, (const TW*)table, hidden, (TO*)out, ldo);
+    launch_overlapped(embed_gather_kernel<TW, TO>, dim3(n_tokens), dim3(threads), 0, stream,
+                      tokens, (const TW*)table, hidden, (TO*)out, ldo);
   }););
   return check_launch("embed_gather");
 }

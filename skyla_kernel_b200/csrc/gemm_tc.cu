@@ -172,12 +172,24 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = tmem_base_slot;
+  allow_dependents();
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
       uint32_t armed = 0, armed_parity = 0;  // per stage: a load is in flight, and its phase
-      int kb = 0;
+      // Weights are written by no kernel: the first stages' weight tiles are requested
+      // before this grid waits for its predecessor, the token tiles after.
+      const int n_pre = min(n_kb, C::kStages);
+      for (int kb = 0; kb < n_pre; ++kb) {
+        mbar_expect_tx(full_bar(kb), C::kStageBytes);
+        tma_load_2d(base + kb * C::kStageBytes, &map_w, full_bar(kb), (kb0 + kb) * BK, f_tile * BM * C::kATiles);
+        armed |= 1u << kb;
+      }
+      grid_dependency_wait();
+      for (int kb = 0; kb < n_pre; ++kb)
+        tma_load_2d(base + kb * C::kStageBytes + C::kABytes, &map_x, full_bar(kb), (kb0 + kb) * BK, t_tile * BN);
+      int kb = n_pre;
       for (; kb < n_kb; ++kb) {
         const int s = kb % C::kStages;
         const uint32_t phase = (kb / C::kStages) & 1;
@@ -224,6 +236,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     }
   } else {
     // ---------------------------------------------------------------- epilogue
+    grid_dependency_wait();                      // the epilogue reads and writes what earlier kernels touch
     const int quad = warp & 3;                   // the TMEM lanes this warp may read
     const int f = f_tile * BM + quad * 32 + lane;  // output feature of this thread
     if (n_kb > 0 && mbar_wait(tmem_full_bar, 0, &abort_flag, a.error_flag, 3)) {
@@ -309,7 +322,7 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, const GemmArgs& a, dim3
                                       C::kSmemBytes, cudaGetErrorString(e));
     configured = true;
   }
-  gemm_tc_kernel<BN, MODE><<<grid, kThreads, C::kSmemBytes, stream>>>(mw, mx, a);
+  launch_overlapped(gemm_tc_kernel<BN, MODE>, grid, dim3(kThreads), C::kSmemBytes, stream, mw, mx, a);
   return check_launch("gemm_tc");
 }
 

@@ -12,6 +12,8 @@ __global__ void rmsnorm_kernel(const TI* __restrict__ x, int64_t ldx, const int3
                                int width, const float* __restrict__ w, float eps,
                                TO* __restrict__ out, int64_t ldo) {
   __shared__ float scratch[32];
+  allow_dependents();
+  grid_dependency_wait();
   const int r = blockIdx.x;
   const TI* xr = x + (int64_t)(rows ? rows[r] : r) * ldx;
   float ss = 0.f;
@@ -36,6 +38,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, int64_t ldx, const flo
                                    const int32_t* __restrict__ rows, int width, const float* __restrict__ w,
                                    float eps, TO* __restrict__ out, int64_t ldo) {
   __shared__ float scratch[32];
+  allow_dependents();
+  grid_dependency_wait();
   const int r = blockIdx.x;
   const int64_t src = rows ? rows[r] : r;
   float* xr = x + src * ldx;
@@ -56,6 +60,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, int64_t ldx, const flo
 // x[r] += sum_s partial[s][r] for all rows, no norm (for readers of x that are not norms).
 __global__ void fold_partials_kernel(float* __restrict__ x, int64_t ldx, const float* __restrict__ part,
                                      int n_splits, int64_t split_stride, int64_t ldp, int width) {
+  allow_dependents();
+  grid_dependency_wait();
   const int r = blockIdx.x;
   for (int i = threadIdx.x; i < width; i += blockDim.x) {
     float v = x[(int64_t)r * ldx + i];
@@ -72,8 +78,8 @@ extern "C" int skyla_add_rmsnorm(float* x, int64_t ldx, const float* part, int n
     return fail(kBadArgument, "add_rmsnorm: bad width %d, stride or split count", width);
   const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
   SKYLA_DISPATCH(out_dtype, TO, {
-    add_rmsnorm_kernel<TO><<<n_rows, threads, 0, stream>>>(x, ldx, part, n_splits, split_stride, ldp, rows,
-                                                           width, weight, eps, (TO*)out, ldo);
+    launch_overlapped(add_rmsnorm_kernel<TO>, dim3(n_rows), dim3(threads), 0, stream, x, ldx, part, n_splits,
+                      split_stride, ldp, rows, width, weight, eps, (TO*)out, ldo);
   });
   return check_launch("add_rmsnorm");
 }
@@ -83,7 +89,8 @@ extern "C" int skyla_fold_partials(float* x, int64_t ldx, const float* part, int
   if (n_rows <= 0) return kOk;
   if (width <= 0 || ldx < width || ldp < width || n_splits < 1)
     return fail(kBadArgument, "fold_partials: bad width %d, stride or split count", width);
-  fold_partials_kernel<<<n_rows, 256, 0, stream>>>(x, ldx, part, n_splits, split_stride, ldp, width);
+  launch_overlapped(fold_partials_kernel, dim3(n_rows), dim3(256), 0, stream, x, ldx, part, n_splits, split_stride,
+                    ldp, width);
   return check_launch("fold_partials");
 }
 
@@ -96,8 +103,8 @@ extern "C" int skyla_rmsnorm(const void* x, int x_dtype, int64_t ldx, const int3
   // the block size depends on the width only, so a row's sum has one order whatever the batch
   const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
   SKYLA_DISPATCH(x_dtype, TI, SKYLA_DISPATCH(out_dtype, TO, {
-    rmsnorm_kernel<TI, TO><<<n_rows, threads, 0, stream>>>(
-        (const TI*)x, ldx, rows, width, weight, eps, (TO*)out, ldo);
+    launch_overlapped(rmsnorm_kernel<TI, TO>, dim3(n_rows), dim3(threads), 0, stream, (const TI*)x, ldx, rows, width,
+                      weight, eps, (TO*)out, ldo);
   }););
   return check_launch("rmsnorm");
 }

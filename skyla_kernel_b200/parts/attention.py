@@ -97,11 +97,13 @@ class GQAttention(Part):
     def decode_splits(self, n_seqs: int, max_pages: int):
         """How a decode step cuts the context: (splits, pages per split).
 
-        Enough blocks to fill the GPU about three times over, at least four pages
-        per block (one per warp); splits are aligned to absolute positions.
+        A block is alone on its SM and pays a few microseconds before its first page
+        arrives, so blocks are few and long: a quarter of the page-list width each,
+        at least four pages.  Splits are aligned to absolute positions and do not
+        depend on the other sequences of the batch; blocks past a sequence's end
+        return at once.
         """
-        want = -(-3 * 148 // max(1, self.nkv * n_seqs))
-        per = max(4, -(-max_pages // want))
+        per = max(4, max_pages // 4)
         return -(-max_pages // per), per
 
     def cache_need(self) -> Optional[KVNeed]:
