@@ -544,3 +544,53 @@ extern "C" int skyla_attention_prefill(const void* q, int64_t ldq, void* out, in
   SKYLA_HD_SWITCH(hd, { rc = launch_prefill<HD>(a, n_tiles, stream); break; });
   return rc;
 }
+
+// ---------------------------------------------------------------- no allocation
+#include "attention_no_alloc.h"
+
+// The scratch of the entry point below: part of the library's device image on every
+// GPU that loads it.  Host code may not use this name as an address; it asks the
+// runtime for the device address once per device (see scratch_address()).
+static __device__ __align__(256) float g_no_alloc_scratch[SKYLA_NO_ALLOC_SCRATCH_FLOATS];
+
+namespace {
+constexpr int kMaxDevices = 64;
+float* g_scratch_address[kMaxDevices] = {nullptr};
+
+// Device address of g_no_alloc_scratch on the current device, looked up on first use.
+int scratch_address(float** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fail(kLaunchFailed, "attention_decode_no_alloc: cudaGetDevice: %s", cudaGetErrorString(e));
+  if (dev < 0 || dev >= kMaxDevices) return fail(kBadArgument, "attention_decode_no_alloc: device %d is out of range", dev);
+  if (g_scratch_address[dev] == nullptr) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_no_alloc_scratch);
+    if (e != cudaSuccess || p == nullptr)
+      return fail(kLaunchFailed, "attention_decode_no_alloc: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+    g_scratch_address[dev] = static_cast<float*>(p);
+  }
+  *out = g_scratch_address[dev];
+  return kOk;
+}
+}  // namespace
+
+extern "C" int skyla_attention_decode_no_alloc(const void* q, int64_t ldq, void* out, int64_t ldo, int n_seqs, int nq,
+                                               int nkv, int hd, const void* k_pool, const void* v_pool,
+                                               const int32_t* pages, int max_pages, int page_size,
+                                               const int32_t* tok_pos, float scale, int window, int n_splits,
+                                               int pages_per_split, cudaStream_t stream) {
+  if (n_seqs <= 0) return kOk;
+  if (nq <= 0 || hd <= 0 || n_splits <= 0) return fail(kBadArgument, "attention_decode_no_alloc: bad sizes");
+  const unsigned long long need = (unsigned long long)n_seqs * nq * n_splits * (hd + 2);
+  if (need > SKYLA_NO_ALLOC_SCRATCH_FLOATS)
+    return fail(kBadArgument,
+                "attention_decode_no_alloc: %llu floats of scratch needed (%d sequences x %d heads x %d splits x %d), "
+                "the built-in array holds %u; use fewer splits or skyla_attention_decode with a buffer of your own",
+                need, n_seqs, nq, n_splits, hd + 2, (unsigned)SKYLA_NO_ALLOC_SCRATCH_FLOATS);
+  float* scratch = nullptr;
+  const int rc = scratch_address(&scratch);
+  if (rc) return rc;
+  return skyla_attention_decode(q, ldq, out, ldo, scratch, n_seqs, nq, nkv, hd, k_pool, v_pool, pages, max_pages,
+                                page_size, tok_pos, scale, window, n_splits, pages_per_split, stream);
+}

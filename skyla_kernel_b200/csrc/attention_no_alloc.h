@@ -1,0 +1,52 @@
+// Decode attention for callers that cannot allocate device memory.
+//
+// This entry point has no counterpart in the reference (maulanasdqn/skyla-kernel
+// keeps all of its buffers in one arena that its engine plans up front,
+// skyla-engine/src/arena.rs:83-181, and never hands a kernel to a foreign caller).
+//
+// Who needs it: code that wants this library's split-context decode attention but
+// runs where cudaMalloc is off limits -- inside another runtime's stream capture or
+// graph replay, in a real-time loop whose memory is fixed at start-up, or in a host
+// process that only received device pointers from somebody else's allocator and has
+// no allocator of its own to ask.  skyla_attention_decode() needs a float scratch
+// buffer from its caller for the per-split partial results; this variant brings its
+// own: one fixed array of SKYLA_NO_ALLOC_SCRATCH_FLOATS floats that lives in the
+// library's device image (so every GPU that loads the library holds those 8 MiB
+// until the process exits).  It calls no cudaMalloc, no cudaFree and no other
+// routine that allocates, on the host or on the device.
+//
+// Rules for callers:
+//  * The problem must fit: n_seqs * nq * n_splits * (hd + 2) floats of scratch must
+//    not exceed SKYLA_NO_ALLOC_SCRATCH_FLOATS; otherwise the call fails with a
+//    message and launches nothing.
+//  * The first call on a device looks up the array's device address
+//    (cudaGetSymbolAddress, with that device current) and remembers it.  Make that
+//    first call outside any stream capture.
+//  * All calls on a device share the one array, and it keeps whatever the last call
+//    left in it.  Nothing in it has to start at zero -- each call writes every slot
+//    that its merge step reads -- but two calls that overlap on the GPU (different
+//    streams, or one stream capture replayed concurrently with another call) race on
+//    it.  Order them on one stream or with events.
+//  * Inputs and outputs are still the caller's: q, out, the cache pools, the page
+//    lists and the positions, exactly as for skyla_attention_decode().
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define SKYLA_NO_ALLOC_SCRATCH_FLOATS (2u * 1024u * 1024u) /* 8 MiB */
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+// Same arguments and result as skyla_attention_decode() without the scratch pointer.
+// Returns 0, or a negative code whose text skyla_error_message() gives.
+int skyla_attention_decode_no_alloc(const void* q, int64_t ldq, void* out, int64_t ldo, int n_seqs, int nq,
+                                    int nkv, int hd, const void* k_pool, const void* v_pool,
+                                    const int32_t* pages, int max_pages, int page_size,
+                                    const int32_t* tok_pos, float scale, int window, int n_splits,
+                                    int pages_per_split, cudaStream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
