@@ -127,3 +127,32 @@ def test_step_refuses_bad_input_before_launching(folders):
         eng.step([StepItem(3, [1], [0])])
     with pytest.raises(IndexError):
         eng.free_slot(s); s = eng.alloc_slot(); eng.step([StepItem(s, [1, 2], [2])])
+
+
+def test_command_line_run_check_profile_and_bench_bw(folders, tmp_path):
+    import json
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cfg, w = plain.read_folder(folders["B"])
+    prompt = random_tokens(9, cfg["vocab_size"], 5)
+    r = subprocess.run([sys.executable, os.path.join(root, "bin", "skyla"), "run", folders["B"], "--prompt-ids",
+                        ",".join(map(str, prompt)), "-n", "5", "--dtype", "float32", "--check", "--profile", "--warmup"],
+                       capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert [int(t) for t in r.stdout.split()] == plain.greedy(cfg, w, prompt, 5)
+    assert "0 top-1 disagreements" in r.stderr and "matvec" in r.stderr
+    r = subprocess.run([sys.executable, os.path.join(root, "bin", "skyla"), "bench-bw", "--mib", "64", "--reps", "2"],
+                       capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert json.loads(r.stdout.strip().splitlines()[-1])["read_GBps"] > 100
+    conf = tmp_path / "c.json"
+    conf.write_text(open(os.path.join(folders["A"], "config.json")).read())
+    r = subprocess.run([sys.executable, os.path.join(root, "bin", "skyla"), "random", "--config", str(conf), "--out",
+                        str(tmp_path / "rnd"), "--seed", "4"], capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    r = subprocess.run([sys.executable, os.path.join(root, "bin", "skyla"), "run", str(tmp_path / "rnd"), "--prompt-ids",
+                        "1 2 3", "--prompt-ids", "4,5", "-n", "3", "--temperature", "0.7", "--top-k", "40", "--top-p", "0.95"],
+                       capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0 and len(r.stdout.strip().splitlines()) == 2, r.stderr[-2000:]
