@@ -33,6 +33,8 @@ enum Mode : int {
   kAccumF32 = 2,    // y[tok, f] += acc                    (float: the residual sum)
   kGluBf16 = 3,     // y[tok, f] = silu(gate) * up         (bfloat16; W rows in groups of 128 gate, 128 up)
   kPartialF32 = 4,  // y[split, tok, f] = acc of this K split (float scratch)
+  kAccumCluster = 5,  // y[tok, f] += sum over the K splits, which form one thread-block cluster: the
+                      // splits' tiles meet in rank 0 through distributed shared memory, in rank order
 };
 
 constexpr int BM = 128;  // weight rows per tile
@@ -89,6 +91,9 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     }
   }
 }
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
@@ -124,6 +129,22 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* r) {
       : "r"(taddr) : "memory");
 }
 
+// "Make the residual stream whole": x[r] += sum_s part[s][r], rows 0..M-1, width H.
+// A side job for warps that would otherwise idle; it runs after the dependency wait.
+struct FoldJob {
+  float* x; int64_t ldx; const float* part; int n_splits; int64_t split_stride, ldp; int M, H;
+};
+
+// The token operand made inside the kernel instead of loaded: rmsnorm(x + sum_s part[s]).
+// RMSNorm is x * r * w with one scalar r per row, and a row's scalar commutes with
+// the product, so the operand is bf16((x + sum part) * w) and r = 1/sqrt(mean(.^2) + eps)
+// is applied to the accumulator (or, for K-split partial output, handed on as the
+// split's share of the row's sum of squares in ssq_out[split][row]).
+struct NormSource {
+  const float* x; int64_t ldx; const float* part; int n_splits; int64_t split_stride, ldp;
+  const float* w; float eps; float* ssq_out;
+};
+
 struct GemmArgs {
   void* y;
   int64_t ldy;            // elements between token rows of y
@@ -131,9 +152,11 @@ struct GemmArgs {
   int M, N, K;            // tokens, output features (after gating), reduction length
   int k_blocks_per_split;
   int* error_flag;
+  FoldJob fold;           // fold.x == nullptr: none
+  NormSource norm;        // used by the NORMB kernels only
 };
 
-template <int BN, int MODE>
+template <int BN, int MODE, bool NORMB>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                const GemmArgs a) {
@@ -141,6 +164,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   extern __shared__ uint8_t smem_raw[];
   __shared__ uint32_t tmem_base_slot;
   __shared__ volatile int abort_flag;
+  __shared__ float row_ssq[NORMB ? BN : 1];  // sum of squares of each token row over this block's K range
+  __shared__ float warp_ssq[NORMB ? 4 : 1][NORMB ? BN : 1];
 
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t bars = base + C::kStages * C::kStageBytes;
@@ -157,7 +182,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   if (threadIdx.x == 0) {
     abort_flag = 0;
     for (int s = 0; s < C::kStages; ++s) {
-      mbar_init(full_bar(s), 1);
+      mbar_init(full_bar(s), NORMB ? 2 : 1);  // the loader, and with NORMB the warp that makes the stage's token tile
       mbar_init(empty_bar(s), 1);
     }
     mbar_init(tmem_full_bar, 1);
@@ -181,23 +206,26 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       // Weights are written by no kernel: the first stages' weight tiles are requested
       // before this grid waits for its predecessor, the token tiles after.
       const int n_pre = min(n_kb, C::kStages);
+      constexpr uint32_t kTxBytes = NORMB ? C::kABytes : C::kStageBytes;
       for (int kb = 0; kb < n_pre; ++kb) {
-        mbar_expect_tx(full_bar(kb), C::kStageBytes);
+        mbar_expect_tx(full_bar(kb), kTxBytes);
         tma_load_2d(base + kb * C::kStageBytes, &map_w, full_bar(kb), (kb0 + kb) * BK, f_tile * BM * C::kATiles);
         armed |= 1u << kb;
       }
-      grid_dependency_wait();
-      for (int kb = 0; kb < n_pre; ++kb)
-        tma_load_2d(base + kb * C::kStageBytes + C::kABytes, &map_x, full_bar(kb), (kb0 + kb) * BK, t_tile * BN);
+      if (!NORMB) {
+        grid_dependency_wait();
+        for (int kb = 0; kb < n_pre; ++kb)
+          tma_load_2d(base + kb * C::kStageBytes + C::kABytes, &map_x, full_bar(kb), (kb0 + kb) * BK, t_tile * BN);
+      }
       int kb = n_pre;
       for (; kb < n_kb; ++kb) {
         const int s = kb % C::kStages;
         const uint32_t phase = (kb / C::kStages) & 1;
         if (!mbar_wait(empty_bar(s), phase ^ 1, &abort_flag, a.error_flag, 1)) break;
         const uint32_t sa = base + s * C::kStageBytes, sb = sa + C::kABytes;
-        mbar_expect_tx(full_bar(s), C::kStageBytes);
+        mbar_expect_tx(full_bar(s), kTxBytes);
         tma_load_2d(sa, &map_w, full_bar(s), (kb0 + kb) * BK, f_tile * BM * C::kATiles);
-        tma_load_2d(sb, &map_x, full_bar(s), (kb0 + kb) * BK, t_tile * BN);
+        if (!NORMB) tma_load_2d(sb, &map_x, full_bar(s), (kb0 + kb) * BK, t_tile * BN);
         armed |= 1u << s;
         armed_parity = (armed_parity & ~(1u << s)) | (phase << s);
       }
@@ -239,6 +267,93 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     grid_dependency_wait();                      // the epilogue reads and writes what earlier kernels touch
     const int quad = warp & 3;                   // the TMEM lanes this warp may read
     const int f = f_tile * BM + quad * 32 + lane;  // output feature of this thread
+    const int et = threadIdx.x - 64;             // 0..127 among the four epilogue warps
+    if (a.fold.x != nullptr && f_tile == 0 && t_tile == 0) {
+      // side job while the main loop runs: this split's share of the columns of x
+      const int per = (a.fold.H + (int)gridDim.z - 1) / (int)gridDim.z;
+      const int c0 = split * per, c1 = min(a.fold.H, c0 + per);
+      for (int r = 0; r < a.fold.M; ++r)
+        for (int c = c0 + et; c < c1; c += 128) {
+          float v = a.fold.x[(int64_t)r * a.fold.ldx + c];
+          for (int sp = 0; sp < a.fold.n_splits; ++sp)
+            v += a.fold.part[(int64_t)sp * a.fold.split_stride + (int64_t)r * a.fold.ldp + c];
+          a.fold.x[(int64_t)r * a.fold.ldx + c] = v;
+        }
+    }
+    if (NORMB) {
+      // Make the token tiles (BN = 16): each of the four warps takes every fourth stage, so four
+      // stages' loads are in flight at once.  Lane l handles chunk l%8 (8 elements) of rows
+      // l/8, l/8+4, l/8+8, l/8+12.
+      static_assert(!NORMB || BN == 16, "the in-kernel norm is written for token tiles of 16");
+      const int ew = warp - 2, chunk = lane & 7;
+      float ssq[4] = {0.f, 0.f, 0.f, 0.f};
+      for (int kb = ew; kb < n_kb; kb += 4) {
+        const int s = kb % C::kStages;
+        const uint32_t phase = (kb / C::kStages) & 1;
+        if (!mbar_wait(empty_bar(s), phase ^ 1, &abort_flag, a.error_flag, 4)) break;
+        const int k = (kb0 + kb) * BK + chunk * 8;
+        uint8_t* sb = smem_raw + (base - smem_u32(smem_raw)) + s * C::kStageBytes + C::kABytes;
+        float4 v0[4], v1[4];
+        bool live[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {  // all loads first
+          const int tok = t_tile * BN + (lane >> 3) + 4 * i;
+          live[i] = tok < a.M && k < a.K;
+          v0[i] = v1[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (live[i]) {
+            const float* xp = a.norm.x + (int64_t)tok * a.norm.ldx + k;
+            v0[i] = *reinterpret_cast<const float4*>(xp);
+            v1[i] = *reinterpret_cast<const float4*>(xp + 4);
+          }
+        }
+        float4 w0 = make_float4(0.f, 0.f, 0.f, 0.f), w1 = w0;
+        if (k < a.K) {
+          w0 = *reinterpret_cast<const float4*>(a.norm.w + k);
+          w1 = *reinterpret_cast<const float4*>(a.norm.w + k + 4);
+        }
+        for (int sp = 0; sp < a.norm.n_splits; ++sp)  // pending partial sums, if any (ascending order)
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+            if (live[i]) {
+              const int tok = t_tile * BN + (lane >> 3) + 4 * i;
+              const float* pp = a.norm.part + (int64_t)sp * a.norm.split_stride + (int64_t)tok * a.norm.ldp + k;
+              const float4 p0 = *reinterpret_cast<const float4*>(pp), p1 = *reinterpret_cast<const float4*>(pp + 4);
+              v0[i].x += p0.x; v0[i].y += p0.y; v0[i].z += p0.z; v0[i].w += p0.w;
+              v1[i].x += p1.x; v1[i].y += p1.y; v1[i].z += p1.z; v1[i].w += p1.w;
+            }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int r = (lane >> 3) + 4 * i;
+          ssq[i] += v0[i].x * v0[i].x + v0[i].y * v0[i].y + v0[i].z * v0[i].z + v0[i].w * v0[i].w +
+                    v1[i].x * v1[i].x + v1[i].y * v1[i].y + v1[i].z * v1[i].z + v1[i].w * v1[i].w;
+          __nv_bfloat162 b0 = __floats2bfloat162_rn(v0[i].x * w0.x, v0[i].y * w0.y);
+          __nv_bfloat162 b1 = __floats2bfloat162_rn(v0[i].z * w0.z, v0[i].w * w0.w);
+          __nv_bfloat162 b2 = __floats2bfloat162_rn(v1[i].x * w1.x, v1[i].y * w1.y);
+          __nv_bfloat162 b3 = __floats2bfloat162_rn(v1[i].z * w1.z, v1[i].w * w1.w);
+          // the layout TMA's 128-byte swizzle would have written: chunk ^ (row mod 8)
+          *reinterpret_cast<uint4*>(sb + r * 128 + ((chunk ^ (r & 7)) << 4)) =
+              make_uint4(*reinterpret_cast<uint32_t*>(&b0), *reinterpret_cast<uint32_t*>(&b1),
+                         *reinterpret_cast<uint32_t*>(&b2), *reinterpret_cast<uint32_t*>(&b3));
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic writes -> visible to the MMA's reads
+        __syncwarp();
+        if (lane == 0) mbar_arrive(full_bar(s));
+      }
+      // whole rows: a row's 8 chunks sit in consecutive lanes; then the four warps, in order
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        float v = ssq[i];
+        v += __shfl_xor_sync(0xffffffffu, v, 1);
+        v += __shfl_xor_sync(0xffffffffu, v, 2);
+        v += __shfl_xor_sync(0xffffffffu, v, 4);
+        if (chunk == 0) warp_ssq[ew][(lane >> 3) + 4 * i] = v;
+      }
+      asm volatile("barrier.sync 1, 128;" ::: "memory");  // the four epilogue warps
+      if (et < BN) row_ssq[et] = warp_ssq[0][et] + warp_ssq[1][et] + warp_ssq[2][et] + warp_ssq[3][et];
+      asm volatile("barrier.sync 1, 128;" ::: "memory");
+      if (a.norm.ssq_out != nullptr && f_tile == 0 && et < BN && t_tile * BN + et < a.M)
+        a.norm.ssq_out[(int64_t)split * a.M + t_tile * BN + et] = row_ssq[et];
+    }
     if (n_kb > 0 && mbar_wait(tmem_full_bar, 0, &abort_flag, a.error_flag, 3)) {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16);
@@ -263,15 +378,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
           for (int j = 0; j < 16; ++j) {
             const int tok = tok0 + c0 + j;
             if (tok >= a.M) break;
-            const float v = __uint_as_float(r[j]);
+            float v = __uint_as_float(r[j]);
+            float inv = 1.f;
+            if (NORMB && MODE != kPartialF32) {  // one block sees the whole row: apply the norm's scalar here
+              inv = 1.0f / sqrtf(row_ssq[c0 + j] / (float)a.K + a.norm.eps);
+              v *= inv;
+            }
             if (MODE == kStoreBf16) {
               ((__nv_bfloat16*)a.y)[(int64_t)tok * a.ldy + f] = __float2bfloat16_rn(v);
             } else if (MODE == kStoreF32) {
               ((float*)a.y)[(int64_t)tok * a.ldy + f] = v;
             } else if (MODE == kAccumF32) {
               ((float*)a.y)[(int64_t)tok * a.ldy + f] = old[j] + v;
+            } else if (MODE == kAccumCluster) {
+              reinterpret_cast<float*>(smem_raw + (base - smem_u32(smem_raw)))[(c0 + j) * BM + quad * 32 + lane] = v;
             } else if (MODE == kGluBf16) {
-              const float up = __uint_as_float(u[j]);
+              const float up = __uint_as_float(u[j]) * inv;
               ((__nv_bfloat16*)a.y)[(int64_t)tok * a.ldy + f] = __float2bfloat16_rn(v / (1.0f + expf(-v)) * up);
             } else {
               ((float*)a.y)[(int64_t)split * a.split_stride + (int64_t)tok * a.ldy + f] = v;
@@ -280,6 +402,45 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         }
       }
     }
+  }
+  if (MODE == kAccumCluster) {
+    // every split's tile is in its block's shared memory; rank 0 adds them up in rank order
+    asm volatile("barrier.cluster.arrive.release;\n\tbarrier.cluster.wait.acquire;" ::: "memory");
+    uint32_t rank, n_ranks;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+    asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(n_ranks));
+    if (rank == 0 && warp >= 2 && !abort_flag) {
+      const int f = f_tile * BM + (warp & 3) * 32 + lane;
+      const int tok0 = t_tile * BN;
+      const int n_tok = min(BN, a.M - tok0);
+      if (f < a.N) {
+        for (int j0 = 0; j0 < n_tok; j0 += 8) {
+          float sum[8], old[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            sum[j] = 0.f; old[j] = 0.f;
+            if (j0 + j < n_tok) old[j] = ((const float*)a.y)[(int64_t)(tok0 + j0 + j) * a.ldy + f];
+          }
+          for (uint32_t rk = 0; rk < n_ranks; ++rk) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              if (j0 + j >= n_tok) break;
+              const uint32_t local = base + (uint32_t)(((j0 + j) * BM + (warp & 3) * 32 + lane) * 4);
+              uint32_t remote;
+              float v;
+              asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(rk));
+              asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+              sum[j] += v;
+            }
+          }
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            if (j0 + j < n_tok) ((float*)a.y)[(int64_t)(tok0 + j0 + j) * a.ldy + f] = old[j] + sum[j];
+        }
+      }
+    }
+    // the peers' shared memory must outlive rank 0's reads
+    asm volatile("barrier.cluster.arrive.release;\n\tbarrier.cluster.wait.acquire;" ::: "memory");
   }
   // ------------------------------------------------------------------ teardown
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -311,18 +472,21 @@ EncodeTiledFn encode_fn() {
   return fn;
 }
 
-template <int BN, int MODE>
+template <int BN, int MODE, bool NORMB = false>
 int launch(const CUtensorMap& mw, const CUtensorMap& mx, const GemmArgs& a, dim3 grid, cudaStream_t stream) {
   using C = Cfg<BN, MODE>;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, MODE, NORMB>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          C::kSmemBytes);
     if (e != cudaSuccess) return fail(kLaunchFailed, "gemm_tc: cannot reserve %d bytes of shared memory: %s",
                                       C::kSmemBytes, cudaGetErrorString(e));
     configured = true;
   }
-  launch_overlapped(gemm_tc_kernel<BN, MODE>, grid, dim3(kThreads), C::kSmemBytes, stream, mw, mx, a);
+  if (MODE == kAccumCluster)
+    launch_overlapped_cluster(gemm_tc_kernel<BN, MODE, NORMB>, grid, dim3(kThreads), C::kSmemBytes, stream, grid.z, mw, mx, a);
+  else
+    launch_overlapped(gemm_tc_kernel<BN, MODE, NORMB>, grid, dim3(kThreads), C::kSmemBytes, stream, mw, mx, a);
   return check_launch("gemm_tc");
 }
 
@@ -370,20 +534,27 @@ extern "C" int skyla_gemm_tc_stages(int bn, int mode) {
 }
 
 // map_w: weight [rows, K] with boxes of 128 rows (256 in gated mode); map_x: tokens [M, K] with boxes of bn rows.
+// fold_x (may be null): a residual stream [M, fold_h] to which fold_part [fold_splits][M][fold_h]
+// is added on the side, after this kernel's dependency wait.
 extern "C" int skyla_gemm_tc(const void* map_w, const void* map_x, void* y, int64_t ldy, int64_t split_stride,
                              int M, int N, int K, int bn, int mode, int splits, int* error_flag,
-                             cudaStream_t stream) {
+                             float* fold_x, int64_t fold_ldx, const float* fold_part, int fold_splits,
+                             int64_t fold_split_stride, int64_t fold_ldp, int fold_h, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return kOk;
   if (K <= 0 || K % 8) return fail(kBadArgument, "gemm_tc: K=%d must be a positive multiple of 8", K);
-  if (mode < 0 || mode > 4) return fail(kBadArgument, "gemm_tc: unknown epilogue %d", mode);
-  if (splits < 1 || (splits > 1 && mode != kPartialF32)) return fail(kBadArgument, "gemm_tc: %d K splits need the partial epilogue", splits);
+  if (mode < 0 || mode > 5) return fail(kBadArgument, "gemm_tc: unknown epilogue %d", mode);
+  if (splits < 1 || (splits > 1 && mode != kPartialF32 && mode != kAccumCluster))
+    return fail(kBadArgument, "gemm_tc: %d K splits need the partial or the cluster epilogue", splits);
+  if (mode == kAccumCluster && (splits > 8 || bn > 64))
+    return fail(kBadArgument, "gemm_tc: the cluster epilogue takes at most 8 K splits and 64 tokens per tile");
   const int total_kb = (K + BK - 1) / BK;
   const int per = (total_kb + splits - 1) / splits;
   if ((splits - 1) * per >= total_kb) return fail(kBadArgument, "gemm_tc: %d K splits leave one empty (K=%d)", splits, K);
   alignas(64) CUtensorMap mw, mx;
   memcpy(&mw, map_w, sizeof(mw));
   memcpy(&mx, map_x, sizeof(mx));
-  GemmArgs a{y, ldy, split_stride, M, N, K, per, error_flag};
+  GemmArgs a{y, ldy, split_stride, M, N, K, per, error_flag,
+             FoldJob{fold_x, fold_ldx, fold_part, fold_splits, fold_split_stride, fold_ldp, M, fold_h}, NormSource{}};
   dim3 grid((N + BM - 1) / BM, (M + bn - 1) / bn, splits);
   if (grid.y > 65535 || grid.z > 65535) return fail(kBadArgument, "gemm_tc: grid too large");
   switch (mode) {
@@ -391,6 +562,48 @@ extern "C" int skyla_gemm_tc(const void* map_w, const void* map_x, void* y, int6
     case kStoreF32: return launch_bn<kStoreF32>(bn, mw, mx, a, grid, stream);
     case kAccumF32: return launch_bn<kAccumF32>(bn, mw, mx, a, grid, stream);
     case kGluBf16: return launch_bn<kGluBf16>(bn, mw, mx, a, grid, stream);
+    case kAccumCluster:
+      switch (bn) {
+        case 16: return launch<16, kAccumCluster>(mw, mx, a, grid, stream);
+        case 32: return launch<32, kAccumCluster>(mw, mx, a, grid, stream);
+        default: return launch<64, kAccumCluster>(mw, mx, a, grid, stream);
+      }
     default: return launch_bn<kPartialF32>(bn, mw, mx, a, grid, stream);
   }
+}
+
+// The same product with the token operand made in the kernel: rmsnorm(x + sum_s part[s]) * w.
+// x [M, K] float, part [n_part][M][K] float or null, w [K] float.  Modes: gated (bf16 out),
+// store bf16/f32 (one K split only: the norm's scalar is applied in the epilogue), or partial
+// with ssq_out [splits][M] receiving each split's share of the rows' sums of squares.
+// Token tiles of 16, 32 or 64; x is not changed.
+extern "C" int skyla_gemm_tc_norm(const void* map_w, const float* x, int64_t ldx, const float* part, int n_part,
+                                  int64_t part_split_stride, int64_t ldp, const float* w, float eps, float* ssq_out,
+                                  void* y, int64_t ldy, int64_t split_stride, int M, int N, int K, int bn, int mode,
+                                  int splits, int* error_flag, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return kOk;
+  if (K <= 0 || K % 8) return fail(kBadArgument, "gemm_tc_norm: K=%d must be a positive multiple of 8", K);
+  if (bn != 16 || M > 16) return fail(kBadArgument, "gemm_tc_norm: at most 16 tokens (token tile 16), got %d", M);
+  if (ldx % 4 || ldp % 4 || part_split_stride % 4 || ((uintptr_t)x) % 16 || ((uintptr_t)part) % 16 || ((uintptr_t)w) % 16)
+    return fail(kBadArgument, "gemm_tc_norm: x, the partial sums and the weight must be 16-byte aligned");
+  if (mode == kPartialF32 ? ssq_out == nullptr : splits != 1)
+    return fail(kBadArgument, "gemm_tc_norm: K splits go with the partial epilogue and a place for the sums of squares");
+  if (mode != kPartialF32 && mode != kGluBf16 && mode != kStoreBf16 && mode != kStoreF32)
+    return fail(kBadArgument, "gemm_tc_norm: epilogue %d is not offered", mode);
+  const int total_kb = (K + BK - 1) / BK;
+  const int per = (total_kb + splits - 1) / splits;
+  if (splits < 1 || (splits - 1) * per >= total_kb) return fail(kBadArgument, "gemm_tc_norm: %d K splits leave one empty (K=%d)", splits, K);
+  alignas(64) CUtensorMap mw;
+  memcpy(&mw, map_w, sizeof(mw));
+  GemmArgs a{y, ldy, split_stride, M, N, K, per, error_flag, FoldJob{},
+             NormSource{x, ldx, part, part ? n_part : 0, part_split_stride, ldp, w, eps, ssq_out}};
+  dim3 grid((N + BM - 1) / BM, (M + bn - 1) / bn, splits);
+#define SKYLA_NORM_LAUNCH(MODE_) return launch<16, MODE_, true>(mw, mw, a, grid, stream);
+  switch (mode) {
+    case kPartialF32: SKYLA_NORM_LAUNCH(kPartialF32)
+    case kGluBf16: SKYLA_NORM_LAUNCH(kGluBf16)
+    case kStoreBf16: SKYLA_NORM_LAUNCH(kStoreBf16)
+    default: SKYLA_NORM_LAUNCH(kStoreF32)
+  }
+#undef SKYLA_NORM_LAUNCH
 }

@@ -191,7 +191,7 @@ def linear_plain(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, mode: int = 
 
 
 # ---------------------------------------------------------- tensor-core linear
-TC_STORE_BF16, TC_STORE_F32, TC_ACCUM_F32, TC_GLU_BF16, TC_PARTIAL_F32 = 0, 1, 2, 3, 4
+TC_STORE_BF16, TC_STORE_F32, TC_ACCUM_F32, TC_GLU_BF16, TC_PARTIAL_F32, TC_ACCUM_CLUSTER = 0, 1, 2, 3, 4, 5
 TC_TOKEN_TILES = (16, 32, 64, 128, 256)
 
 _ERROR_FLAGS = {}
@@ -262,12 +262,28 @@ def token_tile(m: int, gated: bool = False) -> int:
     return 128 if gated else 256
 
 
+def _fold_args(fold, m: int):
+    """(x, partials) -> the seven launcher arguments of a fold side job (all zero for none)."""
+    if fold is None:
+        return [c_void_p(0), 0, c_void_p(0), 0, 0, 0, 0]
+    x, part = fold
+    _cuda(x, part)
+    if (x.dtype != torch.float32 or part.dtype != torch.float32 or part.dim() != 3 or not part.is_contiguous()
+            or tuple(part.shape[1:]) != tuple(x.shape) or x.shape[0] != m):
+        raise KernelError("fold job: float32 x [tokens, width] and contiguous partial sums [splits, tokens, width]")
+    return [_ptr(x), _rows(x, "x"), _ptr(part), part.shape[0], part.stride(0), part.stride(1), x.shape[1]]
+
+
 def gemm_tc(x: torch.Tensor, w_map: TensorMap, n_out: int, y: torch.Tensor, mode: int, splits: int = 1,
-            bn: Optional[int] = None) -> torch.Tensor:
+            bn: Optional[int] = None, fold=None) -> torch.Tensor:
     """y = x W^T on the tensor cores.  ``w_map`` has boxes of 128 rows (256 when gated).
 
     ``mode``: TC_STORE_BF16 / TC_STORE_F32 / TC_ACCUM_F32 / TC_GLU_BF16, or
-    TC_PARTIAL_F32 with ``y`` of shape [splits, tokens, n_out] float32.
+    TC_PARTIAL_F32 with ``y`` of shape [splits, tokens, n_out] float32, or
+    TC_ACCUM_CLUSTER: ``y += x W^T`` with the product cut into ``splits`` (at most 8) along K,
+    the splits running as one thread-block cluster and added up in a fixed order.
+    ``fold=(r, partials)``: on the side, ``r += sum_s partials[s]`` (``r`` must not be an
+    operand of this product).
     """
     m, k = x.shape
     bn = bn or token_tile(m, mode == TC_GLU_BF16)
@@ -285,8 +301,54 @@ def gemm_tc(x: torch.Tensor, w_map: TensorMap, n_out: int, y: torch.Tensor, mode
     xm = activation_map(x, bn)
     f = _fn("gemm_tc", "skyla_gemm_tc",
             [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int, c_int, c_int, c_int, c_int, c_int,
-             c_void_p, c_void_p])
+             c_void_p, c_void_p, c_int64, c_void_p, c_int, c_int64, c_int64, c_int, c_void_p])
     _check("gemm_tc", f(w_map.buf, xm.buf, _ptr(y), ldy, sstride, m, n_out, k, bn, mode, splits,
+                        _ptr(error_flag(x.device)), *_fold_args(fold, m), _stream()))
+    return y
+
+
+def gemm_tc_norm(x: torch.Tensor, partials: Optional[torch.Tensor], norm_weight: torch.Tensor, eps: float,
+                 w_map: TensorMap, n_out: int, y: torch.Tensor, mode: int, splits: int = 1,
+                 ssq_out: Optional[torch.Tensor] = None, bn: Optional[int] = None) -> torch.Tensor:
+    """y = rmsnorm(x + sum_s partials[s]) W^T with the norm made inside the product.
+
+    ``x`` float32 [tokens, K] (not changed), ``partials`` float32 [s, tokens, K] or ``None``.
+    Modes TC_GLU_BF16 / TC_STORE_*: one K split, the norm's scalar is applied to the result.
+    Mode TC_PARTIAL_F32: ``y`` [splits, tokens, n_out] holds products of the rows *before*
+    their scalar, and ``ssq_out`` [splits, tokens] each split's share of the rows' sums of
+    squares, for the reader to finish (``qk_norm_rope_cache(..., row_ssq=...)``).
+    """
+    _cuda(x, partials, norm_weight, y, ssq_out)
+    m, k = x.shape
+    bn = bn or token_tile(m)
+    if bn > 64:
+        raise KernelError("gemm_tc_norm: at most 64 tokens")
+    if x.dtype != torch.float32 or norm_weight.dtype != torch.float32 or norm_weight.numel() != k:
+        raise KernelError("gemm_tc_norm: float32 x and a float32 norm weight of its width")
+    n_part, pstride, ldp = 0, 0, 0
+    if partials is not None:
+        if (partials.dtype != torch.float32 or partials.dim() != 3 or not partials.is_contiguous()
+                or tuple(partials.shape[1:]) != (m, k)):
+            raise KernelError("gemm_tc_norm: partial sums must be contiguous float32 [splits, tokens, K]")
+        n_part, pstride, ldp = partials.shape[0], partials.stride(0), partials.stride(1)
+    want = {TC_STORE_BF16: torch.bfloat16, TC_GLU_BF16: torch.bfloat16}.get(mode, torch.float32)
+    if y.dtype != want:
+        raise KernelError(f"gemm_tc_norm: epilogue {mode} writes {want}, y is {y.dtype}")
+    if mode == TC_PARTIAL_F32:
+        if tuple(y.shape) != (splits, m, n_out) or not y.is_contiguous():
+            raise KernelError(f"gemm_tc_norm: partial output must be contiguous [{splits}, {m}, {n_out}]")
+        if ssq_out is None or ssq_out.dtype != torch.float32 or tuple(ssq_out.shape) != (splits, m) or not ssq_out.is_contiguous():
+            raise KernelError(f"gemm_tc_norm: ssq_out must be contiguous float32 [{splits}, {m}]")
+        ldy, sstride = n_out, m * n_out
+    else:
+        if tuple(y.shape) != (m, n_out):
+            raise KernelError(f"gemm_tc_norm: y {tuple(y.shape)} is not [{m}, {n_out}]")
+        ldy, sstride = _rows(y, "y"), 0
+    f = _fn("gemm_tc", "skyla_gemm_tc_norm",
+            [c_void_p, c_void_p, c_int64, c_void_p, c_int, c_int64, c_int64, c_void_p, c_float, c_void_p,
+             c_void_p, c_int64, c_int64, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
+    _check("gemm_tc", f(w_map.buf, _ptr(x), _rows(x, "x"), _ptr(partials), n_part, pstride, ldp, _ptr(norm_weight),
+                        float(eps), _ptr(ssq_out), _ptr(y), ldy, sstride, m, n_out, k, bn, mode, splits,
                         _ptr(error_flag(x.device)), _stream()))
     return y
 
@@ -297,16 +359,23 @@ def qk_norm_rope_cache(qkv: torch.Tensor, q_off: int, k_off: int, v_off: int, nq
                        eps: float, cos: Optional[torch.Tensor], sin: Optional[torch.Tensor],
                        n_rot: int, tok_pos: torch.Tensor, tok_slot: torch.Tensor,
                        k_pool: Optional[torch.Tensor], v_pool: Optional[torch.Tensor],
-                       page_table: torch.Tensor, page_size: int, q_out: Optional[torch.Tensor] = None) -> None:
+                       page_table: torch.Tensor, page_size: int, q_out: Optional[torch.Tensor] = None,
+                       row_ssq: Optional[torch.Tensor] = None, norm_width: int = 0, norm_eps: float = 0.0,
+                       fold=None) -> None:
     """Per-head norm and rotation of the new tokens; q to ``q_out`` (default: in place), k and
     v into the cache.
 
     ``qkv``: [tokens, width] activations, or float32 [splits, tokens, width] K-split partial
     sums that are added up on the way in (then ``q_out`` is required).  ``k_pool``/``v_pool``
     of shape [pages, nkv, page_size, hd]; ``None`` skips the cache write (a run that reads
-    another entry's cache).
+    another entry's cache).  ``row_ssq`` [splits, tokens]: the rows still lack the scalar of an
+    RMSNorm over ``norm_width`` inputs, given as each split's share of the sum of squares
+    (``gemm_tc_norm``).  ``fold=(x, partials)``: on the side, ``x += sum_s partials[s]``.
     """
-    _cuda(qkv, q_norm, k_norm, cos, sin, tok_pos, tok_slot, k_pool, v_pool, page_table, q_out)
+    _cuda(qkv, q_norm, k_norm, cos, sin, tok_pos, tok_slot, k_pool, v_pool, page_table, q_out, row_ssq)
+    if row_ssq is not None and (row_ssq.dtype != torch.float32 or row_ssq.dim() != 2 or not row_ssq.is_contiguous()
+                                or row_ssq.shape[1] != tok_pos.numel() or norm_width <= 0):
+        raise KernelError("qk_norm_rope_cache: row_ssq must be contiguous float32 [splits, tokens] with a norm width")
     for t, what in ((tok_pos, "tok_pos"), (tok_slot, "tok_slot"), (page_table, "page_table")):
         _i32(t, what)
     for t, what in ((q_norm, "q_norm"), (k_norm, "k_norm"), (cos, "cos"), (sin, "sin")):
@@ -337,12 +406,14 @@ def qk_norm_rope_cache(qkv: torch.Tensor, q_off: int, k_off: int, v_off: int, nq
     f = _fn("attn_prep", "skyla_qk_norm_rope_cache",
             [c_void_p, c_int, c_int64, c_int, c_int64, c_void_p, c_int, c_int64, c_int, c_int, c_int, c_int, c_int,
              c_int, c_int, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
-             c_void_p, c_int, c_void_p, c_int, c_int, c_void_p])
+             c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_float,
+             c_void_p, c_int64, c_void_p, c_int, c_int64, c_int64, c_int, c_void_p])
     _check("attn_prep", f(_ptr(qkv), dtype_code(qkv), ld, n_splits, split_stride, q_ptr, q_dt, ldq, q_off, k_off,
                           v_off, n, nq, nkv, hd, _ptr(q_norm), _ptr(k_norm), float(eps), _ptr(cos), _ptr(sin),
                           n_rot if cos is not None else 0, _ptr(tok_pos), _ptr(tok_slot),
                           _ptr(k_pool), _ptr(v_pool), cdt, _ptr(page_table), page_table.shape[1],
-                          page_size, _stream()))
+                          page_size, _ptr(row_ssq), row_ssq.shape[0] if row_ssq is not None else 0,
+                          int(norm_width), float(norm_eps), *_fold_args(fold, n), _stream()))
 
 
 def attention_plain(q: torch.Tensor, out: torch.Tensor, nq: int, nkv: int, hd: int,

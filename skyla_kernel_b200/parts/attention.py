@@ -25,12 +25,13 @@ import torch
 from ..cache.kv import KVNeed
 from ..kernels import ops
 from ..weights.loader import TensorDecl
-from .base import Part, build_part, register_mixer
+from .base import NormedInput, Part, build_part, register_mixer
 from .linear import ACCUMULATE, STORE, Linear
 
 
 class GQAttention(Part):
     graph_safe = True
+    takes_normed_input = True
     kernel_modules = Linear.kernel_modules + ("attn_prep", "attention_plain", "attention_mma")
 
     def __init__(self, spec, rt):
@@ -113,8 +114,14 @@ class GQAttention(Part):
         return None
 
     # --------------------------------------------------------------------- step
-    def forward(self, ctx, h: torch.Tensor, x: torch.Tensor, entry) -> None:
+    def forward(self, ctx, h, x: torch.Tensor, entry) -> None:
         n = ctx.n_tokens
+        normed = None
+        if isinstance(h, NormedInput):
+            if entry.owns_cache and self.qkv.can_fuse_norm(h):
+                normed = h  # the norm is made inside the QKV product
+            else:
+                h = h.tensor()
         nq, nkv, hd = self.nq, self.nkv, self.hd
         group, k_pool, v_pool = ctx.cache.kv_of_entry(entry.cache_entry)
         pages = ctx.pages[group]
@@ -122,7 +129,17 @@ class GQAttention(Part):
         n_rot = 0
         if self.position is not None:
             cos, sin, n_rot = self.position.tables(ctx.max_position + 1)
-        if entry.owns_cache:
+        if normed is not None:
+            part, ssq = self.qkv.forward_normed_partial(normed, ctx, "attn.qkv_partials")
+            ctx.mark("matvec qkv")
+            qkv = ctx.buffer("attn.q", (n, nq * hd), self.rt.act_dtype)
+            pend = ctx.take_pending()  # if sums are pending, the prep kernel also makes x whole, after the product read it
+            ops.qk_norm_rope_cache(part, 0, nq * hd, (nq + nkv) * hd, nq, nkv, hd, self.q_norm_w,
+                                   self.k_norm_w, self.eps, cos, sin, n_rot, ctx.tok_pos, ctx.tok_seq,
+                                   k_pool, v_pool, pages, ctx.page_size, q_out=qkv, row_ssq=ssq,
+                                   norm_width=self.hidden, norm_eps=normed.norm.eps,
+                                   fold=(x, pend) if pend is not None else None)
+        elif entry.owns_cache:
             part = self.qkv.forward_partial(h, ctx, "attn.qkv_partials")
             if part is not None:  # a small batch: the product is K-split, the splits are added up here
                 ctx.mark("matvec qkv")
@@ -159,9 +176,7 @@ class GQAttention(Part):
             ops.attention_plain(q, attn, nq, nkv, hd, k_pool, v_pool, pages, ctx.page_size, ctx.tok_pos,
                                 ctx.tok_seq, self.scale, self.window)
         ctx.mark("attention")
-        ctx.pending = self.out.forward_partial(attn, ctx, "attn.o_partials")
-        if ctx.pending is None:
-            self.out.forward(attn, x, ACCUMULATE)
+        self.out.forward(attn, x, ACCUMULATE)
         ctx.mark("matvec o")
 
 

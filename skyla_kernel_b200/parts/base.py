@@ -128,6 +128,34 @@ class Part:
         return 0
 
 
+class NormedInput:
+    """The input of a mixer or feed-forward before it is computed: ``norm(x + pending)``.
+
+    A block hands this to parts that set ``takes_normed_input = True``; such a part either
+    calls :meth:`tensor` (the norm runs as a kernel of its own, the pending sums are added
+    to ``x``) or does the norm inside its first product (``parts.linear.Linear`` knows how
+    for RMSNorm and few tokens) and then sees to it that ``x`` is made whole later.
+    Parts without the flag get ``tensor()``.
+    """
+
+    def __init__(self, ctx, x: torch.Tensor, norm):
+        self.ctx, self.x, self.norm = ctx, x, norm
+        self._tensor = None
+
+    def tensor(self) -> torch.Tensor:
+        if self._tensor is None:
+            ctx, x = self.ctx, self.x
+            h = ctx.buffer("block.normed", (ctx.n_tokens, x.shape[1]), ctx.rt.act_dtype)
+            if ctx.pending is not None and getattr(self.norm, "fuses_pending", False):
+                self.norm.forward(ctx, x, h, pending=ctx.take_pending())
+            else:
+                ctx.fold_pending(x)
+                self.norm.forward(ctx, x, h)
+            ctx.mark("rmsnorm")
+            self._tensor = h
+        return self._tensor
+
+
 _REGISTRIES: Dict[str, Dict[str, type]] = {
     k: {} for k in ("norm", "mixer", "feed_forward", "position", "block", "embedding", "head")}
 

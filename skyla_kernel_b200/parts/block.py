@@ -9,7 +9,7 @@ from __future__ import annotations
 
 from dataclasses import dataclass
 
-from .base import build_part, declare_part, register_block
+from .base import NormedInput, build_part, declare_part, register_block
 
 
 @dataclass
@@ -58,22 +58,10 @@ class PrenormResidualBlock:
         return sum(p.weight_bytes() for p in self.parts())
 
     def forward(self, ctx, x, entry: EntryBinding) -> None:
-        h = ctx.buffer("block.normed", (ctx.n_tokens, x.shape[1]), self.rt.act_dtype)
-        self._norm(self.mixer_norm, ctx, x, h)
-        self.mixer.forward(ctx, h, x, entry)
-        self._norm(self.ffn_norm, ctx, x, h)
-        self.feed_forward.forward(ctx, h, x)
-
-    @staticmethod
-    def _norm(norm, ctx, x, h) -> None:
-        """Norm of the residual stream; partial sums that a product left pending are added
-        to x first, inside the norm kernel where the norm can do that."""
-        if ctx.pending is not None and getattr(norm, "fuses_pending", False):
-            norm.forward(ctx, x, h, pending=ctx.take_pending())
-        else:
-            ctx.fold_pending(x)
-            norm.forward(ctx, x, h)
-        ctx.mark("rmsnorm")
+        h = NormedInput(ctx, x, self.mixer_norm)
+        self.mixer.forward(ctx, h if getattr(self.mixer, "takes_normed_input", False) else h.tensor(), x, entry)
+        h = NormedInput(ctx, x, self.ffn_norm)
+        self.feed_forward.forward(ctx, h if getattr(self.feed_forward, "takes_normed_input", False) else h.tensor(), x)
 
 
 register_block("prenorm_residual", PrenormResidualBlock)

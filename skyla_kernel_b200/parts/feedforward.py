@@ -13,7 +13,8 @@ from typing import Dict
 import torch
 
 from ..weights.loader import TensorDecl
-from .base import Part, register_feed_forward
+from ..kernels import ops
+from .base import NormedInput, Part, register_feed_forward
 from .linear import ACCUMULATE, GATED, Linear
 
 
@@ -29,6 +30,7 @@ def fuse_gate_up(gate: torch.Tensor, up: torch.Tensor, group: int) -> torch.Tens
 
 class SwiGLU(Part):
     graph_safe = True
+    takes_normed_input = True
     kernel_modules = Linear.kernel_modules
 
     def __init__(self, spec, rt):
@@ -57,13 +59,23 @@ class SwiGLU(Part):
     def weight_bytes(self) -> int:
         return self.gate_up.bytes() + self.down.bytes()
 
-    def forward(self, ctx, h: torch.Tensor, x: torch.Tensor) -> None:
+    def forward(self, ctx, h, x: torch.Tensor) -> None:
         act = ctx.buffer("ffn.act", (ctx.n_tokens, self.inter), self.rt.act_dtype)
-        self.gate_up.forward(h, act, GATED)
+        fold = None
+        if isinstance(h, NormedInput):
+            if self.gate_up.can_fuse_norm(h):
+                self.gate_up.forward_normed(h, ctx, act)  # norm, both products and silu(g)*u in one kernel
+                pend = ctx.take_pending()                 # x still lacks these; the down product adds them on the side
+                fold = (x, pend) if pend is not None else None
+                h = None
+            else:
+                h = h.tensor()
+        if h is not None:
+            self.gate_up.forward(h, act, GATED)
         ctx.mark("matvec gate+up, silu")
-        ctx.pending = self.down.forward_partial(act, ctx, "ffn.down_partials")
-        if ctx.pending is None:
-            self.down.forward(act, x, ACCUMULATE)
+        if fold is not None:
+            ops.fold_partials(*fold)
+        self.down.forward(act, x, ACCUMULATE)
         ctx.mark("matvec down")
 
 

@@ -51,6 +51,9 @@ class Linear:
             if mode == GATED:
                 tc = ops.TC_GLU_BF16
             elif mode == ACCUMULATE:
+                splits = min(8, self.choose_splits(x.shape[0]))
+                if splits > 1:  # few tokens: K is cut across a cluster of blocks so that every SM streams
+                    return ops.gemm_tc(x, self.weight_map(), self.n_out, y, ops.TC_ACCUM_CLUSTER, splits=splits)
                 tc = ops.TC_ACCUM_F32
             else:
                 tc = ops.TC_STORE_BF16 if y.dtype == torch.bfloat16 else ops.TC_STORE_F32
@@ -81,10 +84,11 @@ class Linear:
                 best, best_cost = s, cost
         return best
 
-    def forward_partial(self, x: torch.Tensor, ctx, name: str):
+    def forward_partial(self, x: torch.Tensor, ctx, name: str, fold=None):
         """The product as K-split partial sums [splits, tokens, n_out] (float32) in a workspace
         buffer, or ``None`` when splitting does not pay or the tensor-core kernel does not
-        take these operands; the reader adds the splits up in ascending order."""
+        take these operands; the reader adds the splits up in ascending order.
+        ``fold=(r, partials)`` rides along (``r += sum partials``) when the product is made."""
         if self.gated_group or not self.tensor_cores or not ops.tc_linear_ok(x, self.weight):
             return None
         m = x.shape[0]
@@ -92,8 +96,39 @@ class Linear:
         if splits <= 1:
             return None
         part = ctx.buffer(name, (splits, m, self.n_out), torch.float32)
-        ops.gemm_tc(x, self.weight_map(), self.n_out, part, ops.TC_PARTIAL_F32, splits=splits)
+        ops.gemm_tc(x, self.weight_map(), self.n_out, part, ops.TC_PARTIAL_F32, splits=splits, fold=fold)
         return part
+
+    # ---- the RMSNorm of the input made inside the product
+    FUSED_NORM_MAX_TOKENS = 16  # every block re-reads the rows it normalises: only worth it for few
+
+    def can_fuse_norm(self, normed) -> bool:
+        """Whether ``norm(x + pending)`` can be made inside this product: RMSNorm, float32 rows
+        with 16-byte alignment, few tokens, and a weight the tensor-core kernel takes."""
+        x, norm, pend = normed.x, normed.norm, normed.ctx.pending
+        return (self.tensor_cores and type(norm).__name__ == "RMSNorm" and x.dtype == torch.float32
+                and x.shape[0] <= self.FUSED_NORM_MAX_TOKENS and x.shape[1] == self.n_in
+                and x.stride(1) == 1 and x.stride(0) % 4 == 0 and x.data_ptr() % 16 == 0
+                and (pend is None or (pend.dim() == 3 and tuple(pend.shape[1:]) == tuple(x.shape))))
+
+    def forward_normed_partial(self, normed, ctx, name: str):
+        """(partial sums [splits, tokens, n_out], row sums of squares [splits, tokens]) of the
+        product of the *un-scaled* normed input; the reader applies the rows' scalars.
+        ``x`` and ``ctx.pending`` are left as they are."""
+        x, norm = normed.x, normed.norm
+        m = x.shape[0]
+        splits = self.choose_splits(m)
+        part = ctx.buffer(name, (splits, m, self.n_out), torch.float32)
+        ssq = ctx.buffer(name + ".ssq", (splits, m), torch.float32)
+        ops.gemm_tc_norm(x, ctx.pending, norm.weight, norm.eps, self.weight_map(), self.n_out, part,
+                         ops.TC_PARTIAL_F32, splits=splits, ssq_out=ssq)
+        return part, ssq
+
+    def forward_normed(self, normed, ctx, y: torch.Tensor) -> torch.Tensor:
+        """``y = f(norm(x + pending) W^T)`` in one kernel (gated or plain store)."""
+        x, norm = normed.x, normed.norm
+        mode = ops.TC_GLU_BF16 if self.gated_group else (ops.TC_STORE_BF16 if y.dtype == torch.bfloat16 else ops.TC_STORE_F32)
+        return ops.gemm_tc_norm(x, ctx.pending, norm.weight, norm.eps, self.weight_map(), self.n_out, y, mode)
 
     def bytes(self) -> int:
         return self.weight.numel() * self.weight.element_size()

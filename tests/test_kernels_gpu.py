@@ -489,3 +489,113 @@ def test_prep_adds_up_partial_sums():
     for a, b in zip(res[0], res[1]):  # from 32-bit sums against from the rounded whole: bf16 apart at most
         torch.testing.assert_close(a.float(), b.float(), rtol=2e-2, atol=2e-2)
     assert res[0][0].abs().sum() > 0 and res[0][1].abs().sum() > 0
+
+
+# -------------------------------------------- RMSNorm made inside the matrix product
+@pytest.mark.parametrize("m,n,k,n_part", [(1, 128, 64, 0), (8, 384, 4096, 4), (5, 256, 264, 2), (16, 256, 1032, 3),
+                                          (11, 128, 512, 1)])
+def test_gemm_tc_norm_store_and_gated(m, n, k, n_part):
+    ops = _ops()
+    from skyla_kernel_b200.parts.feedforward import fuse_gate_up
+    x = _rand(m, k, seed=71, scale=1.5)
+    part = _rand(n_part, m, k, seed=72, scale=0.5) if n_part else None
+    nw = 1 + 0.2 * _rand(k, seed=73)
+    whole = x.double() + (part.double().sum(0) if n_part else 0)
+    h = plain.rmsnorm(whole.cpu(), nw.double().cpu(), 1e-5)
+    w = _rand(n, k, seed=74, dtype=torch.bfloat16, scale=0.1)
+    ref = h @ w.double().cpu().T
+    y = torch.full((m, n), float("nan"), dtype=torch.float32, device=DEV)
+    x_before = x.clone()
+    ops.gemm_tc_norm(x, part, nw, 1e-5, ops.TensorMap(w, 128), n, y, ops.TC_STORE_F32)
+    assert torch.equal(x, x_before)  # the residual stream is read, not written
+    # the operand is rounded to bfloat16 once (as a separate norm kernel would round it)
+    torch.testing.assert_close(y.double().cpu(), ref, rtol=2e-2, atol=2e-2 * ref.abs().max().item())
+    assert (y.double().cpu() - ref).abs().mean().item() < 4e-3 * ref.abs().max().item()
+    g, u = _rand(n, k, seed=75, dtype=torch.bfloat16, scale=0.1), _rand(n, k, seed=76, dtype=torch.bfloat16, scale=0.1)
+    act = torch.empty(m, n, dtype=torch.bfloat16, device=DEV)
+    ops.gemm_tc_norm(x, part, nw, 1e-5, ops.TensorMap(fuse_gate_up(g, u, 128), 256), n, act, ops.TC_GLU_BF16)
+    gd, ud = h @ g.double().cpu().T, h @ u.double().cpu().T
+    ref_act = gd / (1 + torch.exp(-gd)) * ud
+    torch.testing.assert_close(act.double().cpu(), ref_act, rtol=3e-2, atol=3e-2 * ref_act.abs().max().item())
+    ops.check_device_errors(DEV)
+
+
+@pytest.mark.parametrize("m,k,splits,n_part", [(8, 4096, 3, 4), (3, 264, 2, 0), (16, 1032, 4, 2)])
+def test_gemm_tc_norm_partial_then_prep_and_fold(m, k, splits, n_part):
+    """K-split product of un-scaled rows + shares of the sums of squares, finished by the prep
+    kernel, which also makes the residual stream whole."""
+    ops = _ops()
+    nq, nkv, hd = 4, 2, 32
+    n = (nq + 2 * nkv) * hd
+    x = _rand(m, k, seed=81, scale=1.5)
+    part = _rand(n_part, m, k, seed=82, scale=0.5) if n_part else None
+    nw = 1 + 0.2 * _rand(k, seed=83)
+    w = _rand(n, k, seed=84, dtype=torch.bfloat16, scale=0.1)
+    whole = x.double() + (part.double().sum(0) if n_part else 0)
+    qkv_ref = (plain.rmsnorm(whole.cpu(), nw.double().cpu(), 1e-5) @ w.double().cpu().T).float()
+    y = torch.empty(splits, m, n, dtype=torch.float32, device=DEV)
+    ssq = torch.empty(splits, m, dtype=torch.float32, device=DEV)
+    ops.gemm_tc_norm(x, part, nw, 1e-5, ops.TensorMap(w, 128), n, y, ops.TC_PARTIAL_F32, splits=splits, ssq_out=ssq)
+    torch.testing.assert_close(ssq.sum(0).double().cpu(), (whole.cpu() ** 2).sum(1), rtol=1e-4, atol=1e-4)
+    qn, kn = 1 + 0.2 * _rand(hd, seed=85), 1 + 0.2 * _rand(hd, seed=86)
+    freqs, _ = plain.rope_frequencies(hd, 10000.0)
+    ang = (torch.arange(64, dtype=torch.float32)[:, None] * freqs[None, :]).double()
+    cos, sin = torch.cos(ang).float().to(DEV), torch.sin(ang).float().to(DEV)
+    pos = torch.arange(m, dtype=torch.int32, device=DEV)
+    seq = torch.zeros(m, dtype=torch.int32, device=DEV)
+    table = torch.tensor([[1]], dtype=torch.int32, device=DEV)
+    out = {}
+    for name, src, kw in (("fused", y, dict(row_ssq=ssq, norm_width=k, norm_eps=1e-5,
+                                           fold=(x, part) if n_part else None)),
+                          ("plain", qkv_ref.to(DEV), {})):
+        kp = torch.zeros(2, nkv, 64, hd, dtype=torch.bfloat16, device=DEV)
+        vp = torch.zeros_like(kp)
+        q = torch.zeros(m, nq * hd, dtype=torch.bfloat16, device=DEV)
+        ops.qk_norm_rope_cache(src, 0, nq * hd, (nq + nkv) * hd, nq, nkv, hd, qn, kn, 1e-6, cos, sin, hd, pos, seq,
+                               kp, vp, table, 64, q_out=q, **kw)
+        out[name] = (q, kp, vp)
+    for a, b in zip(out["fused"], out["plain"]):
+        torch.testing.assert_close(a.float(), b.float(), rtol=3e-2, atol=3e-2)
+    if n_part:  # the side job added the partial sums to x, in ascending order
+        want = x_whole = None
+        ref_x = _rand(m, k, seed=81, scale=1.5)
+        for s_ in range(n_part):
+            ref_x += part[s_]
+        assert torch.equal(x, ref_x)
+    ops.check_device_errors(DEV)
+
+
+def test_gemm_tc_fold_side_job():
+    ops = _ops()
+    m, n, k, hidden = 8, 256, 512, 4096
+    x = _rand(m, k, seed=91, dtype=torch.bfloat16)
+    w = _rand(n, k, seed=92, dtype=torch.bfloat16, scale=0.1)
+    r0 = _rand(m, hidden, seed=93)
+    part = _rand(4, m, hidden, seed=94)
+    r = r0.clone()
+    y = torch.empty(2, m, n, dtype=torch.float32, device=DEV)
+    ops.gemm_tc(x, ops.TensorMap(w, 128), n, y, ops.TC_PARTIAL_F32, splits=2, fold=(r, part))
+    want = r0.clone()
+    for s_ in range(4):
+        want += part[s_]
+    assert torch.equal(r, want)
+    ref = x.double() @ w.double().T
+    assert (y.double().sum(0) - ref).abs().max().item() <= 2e-5 * ref.abs().max().item() + 1e-6
+
+
+@pytest.mark.parametrize("m,n,k,splits", [(8, 4096, 4096, 4), (1, 131, 520, 2), (33, 384, 12288, 8), (64, 200, 1032, 3)])
+def test_gemm_tc_cluster_accumulate(m, n, k, splits):
+    """K cut across a cluster of blocks; the splits meet in distributed shared memory."""
+    ops = _ops()
+    x = _rand(m, k, seed=95, dtype=torch.bfloat16)
+    w = _rand(n, k, seed=96, dtype=torch.bfloat16, scale=0.1)
+    acc0 = _rand(m, n, seed=97)
+    ref = acc0.double() + x.double() @ w.double().T
+    runs = []
+    for _ in range(2):
+        acc = acc0.clone()
+        ops.gemm_tc(x, ops.TensorMap(w, 128), n, acc, ops.TC_ACCUM_CLUSTER, splits=splits)
+        runs.append(acc)
+    assert (runs[0].double() - ref).abs().max().item() <= 3e-5 * ref.abs().max().item() + 1e-5
+    assert torch.equal(runs[0], runs[1])  # a fixed order of summation: the same bits every time
+    ops.check_device_errors(DEV)
