@@ -49,11 +49,13 @@ struct Cfg {
   static constexpr int kABytes = kATiles * BM * BK * 2;
   static constexpr int kBBytes = BN * BK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kStagesRaw = kSmemBudget / kStageBytes;
+  // cluster epilogue: a landing zone of BN x 128 floats that the K splits push their tiles into
+  static constexpr int kLandingBytes = MODE == kAccumCluster ? (BN + 8) * BM * 4 : 0;  // ranks x ceil(BN/ranks) columns
+  static constexpr int kStagesRaw = (kSmemBudget - kLandingBytes) / kStageBytes;
   static constexpr int kStages = kStagesRaw > 12 ? 12 : kStagesRaw;
   static constexpr int kTmemColsRaw = kATiles * BN;
   static constexpr int kTmemCols = kTmemColsRaw < 32 ? 32 : kTmemColsRaw;
-  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 256 /*barriers*/;
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 256 /*barriers*/ + kLandingBytes;
   static_assert(kTmemCols <= 512 && (kTmemCols & (kTmemCols - 1)) == 0, "TMEM columns");
   static_assert(kStages >= 2, "pipeline depth");
 };
@@ -172,6 +174,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   auto full_bar = [&](int s) { return bars + 8u * s; };
   auto empty_bar = [&](int s) { return bars + 8u * (C::kStages + s); };
   const uint32_t tmem_full_bar = bars + 8u * (2 * C::kStages);
+  const uint32_t landing = bars + 256u;  // [source rank][owned token][128 features] floats (cluster epilogue)
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int f_tile = blockIdx.x, t_tile = blockIdx.y, split = blockIdx.z;
@@ -268,6 +271,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     const int quad = warp & 3;                   // the TMEM lanes this warp may read
     const int f = f_tile * BM + quad * 32 + lane;  // output feature of this thread
     const int et = threadIdx.x - 64;             // 0..127 among the four epilogue warps
+    uint32_t my_rank = 0, n_ranks = 1;
+    if (MODE == kAccumCluster) {
+      asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(my_rank));
+      asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(n_ranks));
+    }
     if (a.fold.x != nullptr && f_tile == 0 && t_tile == 0) {
       // side job while the main loop runs: this split's share of the columns of x
       const int per = (a.fold.H + (int)gridDim.z - 1) / (int)gridDim.z;
@@ -391,7 +399,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             } else if (MODE == kAccumF32) {
               ((float*)a.y)[(int64_t)tok * a.ldy + f] = old[j] + v;
             } else if (MODE == kAccumCluster) {
-              reinterpret_cast<float*>(smem_raw + (base - smem_u32(smem_raw)))[(c0 + j) * BM + quad * 32 + lane] = v;
+              // token column c0+j belongs to rank (c0+j) % n_ranks: push this split's value into
+              // that block's landing zone, slot [my rank][(c0+j) / n_ranks][feature]
+              const uint32_t col = (uint32_t)(c0 + j);
+              const uint32_t local = landing + 4u * ((my_rank * ((BN + n_ranks - 1) / n_ranks) + col / n_ranks) * BM +
+                                                     quad * 32 + lane);
+              uint32_t remote;
+              asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(col % n_ranks));
+              asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
             } else if (MODE == kGluBf16) {
               const float up = __uint_as_float(u[j]) * inv;
               ((__nv_bfloat16*)a.y)[(int64_t)tok * a.ldy + f] = __float2bfloat16_rn(v / (1.0f + expf(-v)) * up);
@@ -404,43 +419,46 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     }
   }
   if (MODE == kAccumCluster) {
-    // every split's tile is in its block's shared memory; rank 0 adds them up in rank order
-    asm volatile("barrier.cluster.arrive.release;\n\tbarrier.cluster.wait.acquire;" ::: "memory");
+    // All splits have pushed their tiles; each block now owns the token columns c with
+    // c % n_ranks == its rank, adds the splits' values in rank order and updates y.
     uint32_t rank, n_ranks;
     asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
     asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(n_ranks));
-    if (rank == 0 && warp >= 2 && !abort_flag) {
-      const int f = f_tile * BM + (warp & 3) * 32 + lane;
-      const int tok0 = t_tile * BN;
-      const int n_tok = min(BN, a.M - tok0);
-      if (f < a.N) {
-        for (int j0 = 0; j0 < n_tok; j0 += 8) {
-          float sum[8], old[8];
+    const int f = f_tile * BM + (warp & 3) * 32 + lane;
+    const int tok0 = t_tile * BN;
+    const int n_tok = min(BN, a.M - tok0);
+    constexpr int kMaxOwned = BN;  // with one rank a block owns every column
+    const int per_rank = (BN + (int)n_ranks - 1) / (int)n_ranks;
+    float old[kMaxOwned > 16 ? 16 : kMaxOwned];
+    const bool worker = warp >= 2 && f < a.N;
+    if (worker) {  // the old values do not depend on the peers: fetch them while waiting
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            sum[j] = 0.f; old[j] = 0.f;
-            if (j0 + j < n_tok) old[j] = ((const float*)a.y)[(int64_t)(tok0 + j0 + j) * a.ldy + f];
-          }
-          for (uint32_t rk = 0; rk < n_ranks; ++rk) {
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              if (j0 + j >= n_tok) break;
-              const uint32_t local = base + (uint32_t)(((j0 + j) * BM + (warp & 3) * 32 + lane) * 4);
-              uint32_t remote;
-              float v;
-              asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(rk));
-              asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
-              sum[j] += v;
-            }
-          }
-#pragma unroll
-          for (int j = 0; j < 8; ++j)
-            if (j0 + j < n_tok) ((float*)a.y)[(int64_t)(tok0 + j0 + j) * a.ldy + f] = old[j] + sum[j];
-        }
+      for (int i = 0; i < (kMaxOwned > 16 ? 16 : kMaxOwned); ++i) {
+        const int col = i * (int)n_ranks + (int)rank;
+        old[i] = (i < per_rank && col < n_tok) ? ((const float*)a.y)[(int64_t)(tok0 + col) * a.ldy + f] : 0.f;
       }
     }
-    // the peers' shared memory must outlive rank 0's reads
+    __syncwarp();
     asm volatile("barrier.cluster.arrive.release;\n\tbarrier.cluster.wait.acquire;" ::: "memory");
+    if (worker && !abort_flag) {
+      const float* land = reinterpret_cast<const float*>(smem_raw + (landing - smem_u32(smem_raw)));
+#pragma unroll
+      for (int i = 0; i < (kMaxOwned > 16 ? 16 : kMaxOwned); ++i) {
+        const int col = i * (int)n_ranks + (int)rank;
+        if (i >= per_rank || col >= n_tok) continue;
+        float sum = 0.f;
+        for (uint32_t src = 0; src < n_ranks; ++src) sum += land[((int)src * per_rank + i) * BM + (warp & 3) * 32 + lane];
+        ((float*)a.y)[(int64_t)(tok0 + col) * a.ldy + f] = old[i] + sum;
+      }
+      for (int i = 16; i < per_rank; ++i) {  // a block that owns more than 16 columns (few splits, wide tile)
+        const int col = i * (int)n_ranks + (int)rank;
+        if (col >= n_tok) break;
+        float sum = 0.f;
+        for (uint32_t src = 0; src < n_ranks; ++src) sum += land[((int)src * per_rank + i) * BM + (warp & 3) * 32 + lane];
+        float* p = (float*)a.y + (int64_t)(tok0 + col) * a.ldy + f;
+        *p += sum;
+      }
+    }
   }
   // ------------------------------------------------------------------ teardown
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
