@@ -8,6 +8,7 @@ a random-weights writer and the replay program.
     skyla bench MODEL [--batch 8] [--prompt-len 512] [-n 64]
     skyla bench-bw [--mib 512] [--reps 9]
     skyla random --config CONFIG.json --out DIR [--seed S] [--dtype bfloat16|float32]
+    skyla kernel-bench linear|attention-decode|attention-prefill [sizes]
     skyla replay --model DIR --dtype D --out DIR --max-tokens N   (same as bin/trace_run)
 """
 from __future__ import annotations
@@ -203,6 +204,16 @@ def main(argv=None) -> int:
     p.add_argument("--linear-std", type=float, default=0.02)
     p.add_argument("--norm-std", type=float, default=0.02)
     p.set_defaults(fn=cmd_random)
+    p = sub.add_parser("kernel-bench", help="time one kernel on its own (also the target of profiler captures)")
+    p.add_argument("kernel", choices=["linear", "attention-decode", "attention-prefill"])
+    p.add_argument("--tokens", type=int, default=8)
+    p.add_argument("--n-out", type=int, default=4096)
+    p.add_argument("--n-in", type=int, default=4096)
+    p.add_argument("--mode", choices=["store", "store-f32", "accumulate", "gated"], default="store")
+    p.add_argument("--batch", type=int, default=8)
+    p.add_argument("--context", type=int, default=2048)
+    p.add_argument("--reps", type=int, default=5)
+    p.set_defaults(fn=lambda a: __import__("skyla_kernel_b200.kernel_bench", fromlist=["main"]).main(a))
     p = sub.add_parser("replay", help="replay a token trace from standard input (bin/trace_run)")
     p.add_argument("--model", required=True)
     p.add_argument("--dtype", choices=["bfloat16", "float32"], default="bfloat16")

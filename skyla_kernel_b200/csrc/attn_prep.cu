@@ -108,6 +108,73 @@ __global__ void __launch_bounds__(kWarps * 32) prep_kernel(PrepArgs a) {
     else dst[e] = from_float<TC>(v);
   }
 }
+// The common case on prompts: bfloat16 in and out, one split, the whole head rotates and its
+// size is a multiple of 32.  A lane owns hd/32 consecutive elements, so lanes 0-15 hold the
+// first half of the head and lane l+16 holds the rotation partners of lane l: loads and stores
+// are contiguous and the partner comes by one shuffle.
+template <int EPL>  // elements per lane
+__global__ void __launch_bounds__(kWarps * 32) prep_bf16_kernel(PrepArgs a) {
+  allow_dependents();
+  grid_dependency_wait();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int head = blockIdx.x * kWarps + warp, t = blockIdx.y;
+  const int hd = a.hd;
+  if (head >= a.nq + 2 * a.nkv) return;
+  const bool is_q = head < a.nq, is_k = !is_q && head < a.nq + a.nkv;
+  const int kvh = is_q ? 0 : (is_k ? head - a.nq : head - a.nq - a.nkv);
+  typedef __nv_bfloat16 bf16;
+  const bf16* src = (const bf16*)a.qkv + (int64_t)t * a.ld +
+                    (is_q ? a.q_off + head * hd : (is_k ? a.k_off : a.v_off) + kvh * hd) + lane * EPL;
+  const int pos = a.tok_pos[t];
+  bf16* dst;
+  if (is_q) {
+    dst = (bf16*)a.q_out + (int64_t)t * a.ldq + head * hd + lane * EPL;
+  } else {
+    if (a.k_pool == nullptr) return;
+    const int page = a.page_table[(int64_t)a.tok_slot[t] * a.max_pages + pos / a.page_size];
+    dst = (bf16*)(is_k ? a.k_pool : a.v_pool) +
+          (((int64_t)page * a.nkv + kvh) * a.page_size + pos % a.page_size) * hd + lane * EPL;
+  }
+  bf16 raw[EPL];
+  if (EPL == 4) *reinterpret_cast<uint2*>(raw) = *reinterpret_cast<const uint2*>(src);
+  else if (EPL == 2) *reinterpret_cast<uint32_t*>(raw) = *reinterpret_cast<const uint32_t*>(src);
+  else if (EPL == 8) *reinterpret_cast<uint4*>(raw) = *reinterpret_cast<const uint4*>(src);
+  else
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) raw[i] = src[i];
+  if (is_q || is_k) {
+    float u[EPL];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) { u[i] = __bfloat162float(raw[i]); ss = fmaf(u[i], u[i], ss); }
+    const float* nw = is_q ? a.q_norm : a.k_norm;
+    if (nw != nullptr) {
+      ss = warp_sum(ss);
+      const float inv = 1.0f / sqrtf(ss / (float)hd + a.eps);
+#pragma unroll
+      for (int i = 0; i < EPL; ++i) u[i] *= inv * nw[lane * EPL + i];
+    }
+    if (a.cos_t != nullptr) {
+      const int half = hd / 2;
+      const bool low = lane < 16;
+#pragma unroll
+      for (int i = 0; i < EPL; ++i) {
+        const float other = __shfl_xor_sync(0xffffffffu, u[i], 16);
+        const int j = (lane & 15) * EPL + i;  // index of the pair
+        const float c = a.cos_t[(int64_t)pos * half + j], s = a.sin_t[(int64_t)pos * half + j];
+        u[i] = low ? u[i] * c - other * s : other * s + u[i] * c;
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) raw[i] = __float2bfloat16_rn(u[i]);
+  }
+  if (EPL == 4) *reinterpret_cast<uint2*>(dst) = *reinterpret_cast<uint2*>(raw);
+  else if (EPL == 2) *reinterpret_cast<uint32_t*>(dst) = *reinterpret_cast<uint32_t*>(raw);
+  else if (EPL == 8) *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<uint4*>(raw);
+  else
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) dst[i] = raw[i];
+}
 }  // namespace
 
 // qkv: [n_splits][tokens][ld] (n_splits = 1: plain activations); the prepared queries go
@@ -132,6 +199,22 @@ extern "C" int skyla_qk_norm_rope_cache(
              n_rot, tok_pos, tok_slot, k_pool, v_pool, page_table, max_pages, page_size};
   dim3 grid((nq + 2 * nkv + kWarps - 1) / kWarps, n_tokens);
   const size_t smem = (size_t)kWarps * hd * sizeof(float);
+  if (in_dtype == kBF16 && act_dtype == kBF16 && (k_pool == nullptr || cache_dtype == kBF16) && n_splits == 1 &&
+      row_ssq == nullptr && fold_x == nullptr && hd % 32 == 0 && hd <= 256 && (cos_t == nullptr || n_rot == hd) &&
+      ld % 8 == 0 && ldq % 8 == 0 && q_off % 8 == 0 && k_off % 8 == 0 && v_off % 8 == 0 &&
+      ((uintptr_t)qkv) % 16 == 0 && ((uintptr_t)q_out) % 16 == 0) {
+    switch (hd / 32) {
+      case 1: launch_overlapped(prep_bf16_kernel<1>, grid, dim3(kWarps * 32), 0, stream, a); break;
+      case 2: launch_overlapped(prep_bf16_kernel<2>, grid, dim3(kWarps * 32), 0, stream, a); break;
+      case 3: launch_overlapped(prep_bf16_kernel<3>, grid, dim3(kWarps * 32), 0, stream, a); break;
+      case 4: launch_overlapped(prep_bf16_kernel<4>, grid, dim3(kWarps * 32), 0, stream, a); break;
+      case 5: launch_overlapped(prep_bf16_kernel<5>, grid, dim3(kWarps * 32), 0, stream, a); break;
+      case 6: launch_overlapped(prep_bf16_kernel<6>, grid, dim3(kWarps * 32), 0, stream, a); break;
+      case 7: launch_overlapped(prep_bf16_kernel<7>, grid, dim3(kWarps * 32), 0, stream, a); break;
+      default: launch_overlapped(prep_bf16_kernel<8>, grid, dim3(kWarps * 32), 0, stream, a); break;
+    }
+    return check_launch("qk_norm_rope_cache");
+  }
   SKYLA_DISPATCH(in_dtype, TI, SKYLA_DISPATCH(act_dtype, TA, SKYLA_DISPATCH(cache_dtype, TC, {
     launch_overlapped(prep_kernel<TI, TA, TC>, grid, dim3(kWarps * 32), smem, stream, a);
   });););

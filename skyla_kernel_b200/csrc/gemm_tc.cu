@@ -515,9 +515,7 @@ int launch_bn(int bn, const CUtensorMap& mw, const CUtensorMap& mx, const GemmAr
     case 32: return launch<32, MODE>(mw, mx, a, grid, s);
     case 64: return launch<64, MODE>(mw, mx, a, grid, s);
     case 128: return launch<128, MODE>(mw, mx, a, grid, s);
-    case 256:
-      if (MODE == kGluBf16) break;
-      return launch<MODE == kGluBf16 ? 128 : 256, MODE>(mw, mx, a, grid, s);
+    case 256: return launch<256, MODE>(mw, mx, a, grid, s);
   }
   return fail(kBadArgument, "gemm_tc: no kernel for a token tile of %d", bn);
 }
@@ -546,7 +544,8 @@ extern "C" int skyla_tensor_map_bf16(void* out, const void* ptr, uint64_t rows, 
 
 extern "C" int skyla_gemm_tc_stages(int bn, int mode) {
   if (mode == kGluBf16) return bn == 16 ? Cfg<16, kGluBf16>::kStages : bn == 32 ? Cfg<32, kGluBf16>::kStages
-                             : bn == 64 ? Cfg<64, kGluBf16>::kStages : Cfg<128, kGluBf16>::kStages;
+                             : bn == 64 ? Cfg<64, kGluBf16>::kStages : bn == 128 ? Cfg<128, kGluBf16>::kStages
+                             : Cfg<256, kGluBf16>::kStages;
   return bn == 16 ? Cfg<16, 0>::kStages : bn == 32 ? Cfg<32, 0>::kStages : bn == 64 ? Cfg<64, 0>::kStages
        : bn == 128 ? Cfg<128, 0>::kStages : Cfg<256, 0>::kStages;
 }

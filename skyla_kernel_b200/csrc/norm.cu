@@ -94,6 +94,35 @@ extern "C" int skyla_fold_partials(float* x, int64_t ldx, const float* part, int
   return check_launch("fold_partials");
 }
 
+// float32 rows whose width is a multiple of 4 and that start on 16 bytes: four elements per load.
+template <typename TO>
+__global__ void rmsnorm_vec4_kernel(const float* __restrict__ x, int64_t ldx, const int32_t* __restrict__ rows,
+                                    int width, const float* __restrict__ w, float eps, TO* __restrict__ out,
+                                    int64_t ldo) {
+  __shared__ float scratch[32];
+  allow_dependents();
+  grid_dependency_wait();
+  const int r = blockIdx.x;
+  const float4* xr = reinterpret_cast<const float4*>(x + (int64_t)(rows ? rows[r] : r) * ldx);
+  const float4* wr = reinterpret_cast<const float4*>(w);
+  const int n4 = width / 4;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < n4; i += blockDim.x) {
+    const float4 v = xr[i];
+    ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
+  }
+  ss = block_sum(ss, scratch);
+  const float inv = 1.0f / sqrtf(ss / (float)width + eps);
+  TO* o = out + (int64_t)r * ldo;
+  for (int i = threadIdx.x; i < n4; i += blockDim.x) {
+    const float4 v = xr[i], g = wr[i];
+    o[4 * i] = from_float<TO>(v.x * inv * g.x);
+    o[4 * i + 1] = from_float<TO>(v.y * inv * g.y);
+    o[4 * i + 2] = from_float<TO>(v.z * inv * g.z);
+    o[4 * i + 3] = from_float<TO>(v.w * inv * g.w);
+  }
+}
+
 extern "C" int skyla_rmsnorm(const void* x, int x_dtype, int64_t ldx, const int32_t* rows,
                              int n_rows, int width, const float* weight, float eps, void* out,
                              int out_dtype, int64_t ldo, cudaStream_t stream) {
@@ -102,6 +131,14 @@ extern "C" int skyla_rmsnorm(const void* x, int x_dtype, int64_t ldx, const int3
     return fail(kBadArgument, "rmsnorm: bad width %d or row stride", width);
   // the block size depends on the width only, so a row's sum has one order whatever the batch
   const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
+  // the vector kernel adds a row's squares in another order than the scalar one: it serves the
+  // 16-bit path only, so that the 32-bit path keeps one order for every way of calling it
+  if (x_dtype == kF32 && out_dtype == kBF16 && width % 4 == 0 && ldx % 4 == 0 && ((uintptr_t)x) % 16 == 0 &&
+      ((uintptr_t)weight) % 16 == 0) {
+    launch_overlapped(rmsnorm_vec4_kernel<__nv_bfloat16>, dim3(n_rows), dim3(threads), 0, stream, (const float*)x, ldx,
+                      rows, width, weight, eps, (__nv_bfloat16*)out, ldo);
+    return check_launch("rmsnorm");
+  }
   SKYLA_DISPATCH(x_dtype, TI, SKYLA_DISPATCH(out_dtype, TO, {
     launch_overlapped(rmsnorm_kernel<TI, TO>, dim3(n_rows), dim3(threads), 0, stream, (const TI*)x, ldx, rows, width,
                       weight, eps, (TO*)out, ldo);

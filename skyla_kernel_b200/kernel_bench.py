@@ -1,0 +1,125 @@
+"""Times one kernel on its own (CUDA events, a CUDA graph of back-to-back launches over
+different weights so that nothing is served from L2), the way the reference times a single
+dispatch (skyla-vk/src/submit.rs:31-76).  Also the target of profiler captures:
+
+    skyla kernel-bench linear --tokens 8 --n-out 4096 --n-in 12288 --mode accumulate
+    skyla kernel-bench attention-decode --batch 8 --context 2048
+    skyla kernel-bench attention-prefill --tokens 2048
+"""
+from __future__ import annotations
+
+import json
+import math
+
+import torch
+
+from .kernels import ops
+
+DEV = "cuda:0"
+
+
+def _time(fn, copies: int, reps: int) -> float:
+    """Microseconds per call of ``fn(i)``, i = 0..copies-1, replayed as one graph."""
+    for i in range(copies):
+        fn(i)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        for i in range(copies):
+            fn(i)
+    g.replay()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(reps):
+        g.replay()
+    b.record()
+    torch.cuda.synchronize()
+    return a.elapsed_time(b) * 1e3 / reps / copies
+
+
+def linear(tokens: int, n_out: int, n_in: int, mode: str, copies: int = 0, reps: int = 5) -> dict:
+    """The tensor-core product as the linear part would launch it for this many tokens."""
+    from .parts.base import Runtime
+    from .parts.feedforward import fuse_gate_up
+    from .parts.linear import ACCUMULATE, GATED, STORE, Linear
+    rt = Runtime(torch.device(DEV), "bfloat16")
+    gated = mode == "gated"
+    rows = n_out * (2 if gated else 1)
+    copies = copies or max(2, min(24, int(400e6 // (rows * n_in * 2)) + 1))  # > L2 in total
+    lins = []
+    for i in range(copies):
+        w = torch.empty(rows, n_in, dtype=torch.bfloat16, device=DEV)
+        ops.fill_normal(w, 0.0, 0.02, i)
+        lins.append(Linear(w, rt, gated_group=128 if gated else 0))
+    x = torch.randn(tokens, n_in, device=DEV).to(torch.bfloat16)
+    if mode == "accumulate":
+        y = torch.zeros(tokens, n_out, device=DEV)
+        fn = lambda i: lins[i].forward(x, y, ACCUMULATE)
+    elif gated:
+        y = torch.empty(tokens, n_out, dtype=torch.bfloat16, device=DEV)
+        fn = lambda i: lins[i].forward(x, y, GATED)
+    elif mode == "store-f32":
+        y = torch.empty(tokens, n_out, device=DEV)
+        fn = lambda i: lins[i].forward(x, y, STORE)
+    else:
+        y = torch.empty(tokens, n_out, dtype=torch.bfloat16, device=DEV)
+        fn = lambda i: lins[i].forward(x, y, STORE)
+    us = _time(fn, copies, reps)
+    flops = 2.0 * tokens * rows * n_in
+    return {"kernel": "linear", "tokens": tokens, "n_out": n_out, "n_in": n_in, "mode": mode, "us": us,
+            "weight_GBps": rows * n_in * 2 / us / 1e3, "TFLOPs": flops / us / 1e6,
+            "splits": lins[0].choose_splits(tokens) if tokens <= 64 and not gated else 1}
+
+
+def _paged(batch: int, context: int, nkv: int, hd: int):
+    pages = -(-context // 64)
+    width = 8
+    while width < pages:
+        width *= 2
+    pool = batch * width
+    k = torch.randn(pool, nkv, 64, hd, device=DEV).to(torch.bfloat16)
+    v = torch.randn(pool, nkv, 64, hd, device=DEV).to(torch.bfloat16)
+    table = torch.randperm(pool, device=DEV).to(torch.int32).view(batch, width).contiguous()
+    return k, v, table, width
+
+
+def attention_decode(batch: int, context: int, nq: int = 32, nkv: int = 8, hd: int = 128, reps: int = 5) -> dict:
+    k, v, table, width = _paged(batch, context, nkv, hd)
+    q = torch.randn(batch, nq * hd, device=DEV).to(torch.bfloat16)
+    out = torch.empty_like(q)
+    pos = torch.full((batch,), context - 1, dtype=torch.int32, device=DEV)
+    per = max(4, width // 4)
+    n_splits = -(-width // per)
+    scratch = torch.empty(batch * nq * n_splits * (hd + 2), device=DEV)
+    us = _time(lambda i: ops.attention_decode(q, out, scratch, nq, nkv, hd, k, v, table, 64, pos, 1 / math.sqrt(hd), 0,
+                                              n_splits, per), 8, reps)
+    kv_bytes = 2 * batch * context * nkv * hd * 2
+    return {"kernel": "attention-decode", "batch": batch, "context": context, "us": us, "splits": n_splits,
+            "kv_GBps": kv_bytes / us / 1e3}
+
+
+def attention_prefill(tokens: int, nq: int = 32, nkv: int = 8, hd: int = 128, reps: int = 5) -> dict:
+    k, v, table, width = _paged(1, tokens, nkv, hd)
+    q = torch.randn(tokens, nq * hd, device=DEV).to(torch.bfloat16)
+    out = torch.empty_like(q)
+    i32 = lambda t: t.to(torch.int32).to(DEV)
+    pos = i32(torch.arange(tokens))
+    n_tiles = -(-tokens // 64)
+    tile_seq, tile_tok0 = i32(torch.zeros(n_tiles)), i32(torch.arange(n_tiles) * 64)
+    tile_rows = i32(torch.tensor([min(64, tokens - 64 * i) for i in range(n_tiles)]))
+    us = _time(lambda i: ops.attention_prefill(q, out, nq, nkv, hd, k, v, table, 64, pos, tile_seq, tile_tok0, tile_rows,
+                                               1 / math.sqrt(hd), 0), 4, reps)
+    flops = 4.0 * nq * hd * tokens * (tokens + 1) / 2
+    return {"kernel": "attention-prefill", "tokens": tokens, "us": us, "TFLOPs": flops / us / 1e6}
+
+
+def main(a) -> int:
+    if a.kernel == "linear":
+        r = linear(a.tokens, a.n_out, a.n_in, a.mode, reps=a.reps)
+    elif a.kernel == "attention-decode":
+        r = attention_decode(a.batch, a.context, reps=a.reps)
+    else:
+        r = attention_prefill(a.tokens, reps=a.reps)
+    print(json.dumps(r))
+    return 0

@@ -258,8 +258,8 @@ def tc_linear_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
 def token_tile(m: int, gated: bool = False) -> int:
     for bn in TC_TOKEN_TILES:
         if m <= bn:
-            return min(bn, 128) if gated else bn
-    return 128 if gated else 256
+            return bn
+    return 256
 
 
 def _fold_args(fold, m: int):
