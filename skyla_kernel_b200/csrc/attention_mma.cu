@@ -198,6 +198,78 @@ __device__ __forceinline__ void attend16(const uint32_t (&qa)[Shape<HD>::NQ], co
 template <int HD>
 __device__ __forceinline__ int out_col(int n, int i, int t) { return (2 * t + (i & 1)) * (HD / 8) + n; }
 
+// A thread's accumulators of one row are HD/4 consecutive columns starting at t*HD/4: as float4
+// "units" they are stored to shared memory with the unit index XOR-swizzled (head sizes 64 and
+// 128), so that the eight lanes of a quarter warp -- two rows, four t -- hit eight bank groups.
+template <int HD>
+__device__ __forceinline__ int out_unit_xor(int row, int t) {
+  return !Swz<HD>::kOn ? 0 : (HD == 128 ? t + 4 * (row & 1) : (t >> 1) + 2 * (row & 1));
+}
+// Position of column c of row r in a staged [16][HD] float tile.
+template <int HD>
+__device__ __forceinline__ int staged_index(int r, int c) {
+  const int t = c / (HD / 4);
+  return r * HD + 4 * ((c >> 2) ^ out_unit_xor<HD>(r, t)) + (c & 3);
+}
+// Store rows g (half 0) and g+8 (half 1) of the accumulators, scaled, into a staged tile.
+template <int HD>
+__device__ __forceinline__ void stage_rows(float* tile, const float (&o)[Shape<HD>::NT][4], int g, int t,
+                                           bool row0, bool row1, float s0, float s1) {
+  constexpr int NT = Shape<HD>::NT;
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    if (!(half ? row1 : row0)) continue;
+    const int r = g + 8 * half;
+    const float sc = half ? s1 : s0;
+#pragma unroll
+    for (int b = 0; b < 2; ++b)       // columns (2t+b)*NT + n
+#pragma unroll
+      for (int n = 0; n < NT; n += 2) {
+        const int c = (2 * t + b) * NT + n;
+        if (NT % 4 == 0) {
+          if (n % 4 == 0)
+            *reinterpret_cast<float4*>(tile + staged_index<HD>(r, c)) =
+                make_float4(o[n][2 * half + b] * sc, o[n + 1][2 * half + b] * sc, o[n + 2][2 * half + b] * sc,
+                            o[n + 3][2 * half + b] * sc);
+        } else {
+          tile[staged_index<HD>(r, c)] = o[n][2 * half + b] * sc;
+          tile[staged_index<HD>(r, c + 1)] = o[n + 1][2 * half + b] * sc;
+        }
+      }
+  }
+}
+// The same rows straight to global memory as bfloat16 (row pointers at column 0 of the head).
+template <int HD>
+__device__ __forceinline__ void store_rows_bf16(bf16* p0, bf16* p1, const float (&o)[Shape<HD>::NT][4], int t,
+                                                float s0, float s1) {
+  constexpr int NT = Shape<HD>::NT;
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    bf16* p = half ? p1 : p0;
+    if (p == nullptr) continue;
+    const float sc = half ? s1 : s0;
+#pragma unroll
+    for (int b = 0; b < 2; ++b) {
+      bf16* q = p + (2 * t + b) * NT;
+      if (NT % 8 == 0) {
+#pragma unroll
+        for (int n = 0; n < NT; n += 8) {
+          uint4 v;
+          v.x = pack_bf16(o[n][2 * half + b] * sc, o[n + 1][2 * half + b] * sc);
+          v.y = pack_bf16(o[n + 2][2 * half + b] * sc, o[n + 3][2 * half + b] * sc);
+          v.z = pack_bf16(o[n + 4][2 * half + b] * sc, o[n + 5][2 * half + b] * sc);
+          v.w = pack_bf16(o[n + 6][2 * half + b] * sc, o[n + 7][2 * half + b] * sc);
+          *reinterpret_cast<uint4*>(q + n) = v;
+        }
+      } else {
+#pragma unroll
+        for (int n = 0; n < NT; n += 2)
+          *reinterpret_cast<uint32_t*>(q + n) = pack_bf16(o[n][2 * half + b] * sc, o[n + 1][2 * half + b] * sc);
+      }
+    }
+  }
+}
+
 struct PagedKV {
   const bf16* k; const bf16* v; const int32_t* pages; int max_pages, page_size, nkv;
 };
@@ -311,10 +383,7 @@ __global__ void __launch_bounds__(kDecodeWarps * 32) attn_decode_kernel(DecodeAr
   float* so = smem + (size_t)warp * 16 * HD;
   float* sm = smem + (size_t)NW * 16 * HD + warp * 16;
   float* sl = sm + NW * 16;
-#pragma unroll
-  for (int n = 0; n < S::NT; ++n)
-#pragma unroll
-    for (int i = 0; i < 4; ++i) so[(g + 8 * (i >> 1)) * HD + out_col<HD>(n, i, t)] = st.o[n][i];
+  stage_rows<HD>(so, st.o, g, t, g < G, g + 8 < G, 1.f, 1.f);
   if (t == 0) { sm[g] = st.m[0]; sm[g + 8] = st.m[1]; sl[g] = st.l[0]; sl[g + 8] = st.l[1]; }
   __syncthreads();
   // merge the warps in fixed order; one partial per (head, split): m, l, acc[HD]
@@ -328,7 +397,7 @@ __global__ void __launch_bounds__(kDecodeWarps * 32) attn_decode_kernel(DecodeAr
     float acc = 0.f, L = 0.f;
     for (int w = 0; w < NW; ++w) {
       const float f = exp2f(am[w * 16 + r] - ref);
-      acc += f * smem[((size_t)w * 16 + r) * HD + c];
+      acc += f * smem[(size_t)w * 16 * HD + staged_index<HD>(r, c)];
       L += f * al[w * 16 + r];
     }
     float* out = a.part + (((size_t)b * a.nq + kvh * G + r) * a.n_splits + split) * (HD + 2);
@@ -368,7 +437,6 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(PrefillArgs a) {
   constexpr int RS = Stage<HD>::RS, kStages = Stage<HD>::kPrefillStages;
   extern __shared__ __align__(16) uint8_t smem_raw[];
   bf16* stages = reinterpret_cast<bf16*>(smem_raw);
-  float* smem = reinterpret_cast<float*>(smem_raw);  // after the loop: [4 warps][16 rows][HD]
   allow_dependents();
   grid_dependency_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
@@ -437,19 +505,10 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(PrefillArgs a) {
   st.l[0] += __shfl_xor_sync(0xffffffffu, st.l[0], 1); st.l[0] += __shfl_xor_sync(0xffffffffu, st.l[0], 2);
   st.l[1] += __shfl_xor_sync(0xffffffffu, st.l[1], 1); st.l[1] += __shfl_xor_sync(0xffffffffu, st.l[1], 2);
   const float inv0 = st.l[0] > 0.f ? 1.f / st.l[0] : 0.f, inv1 = st.l[1] > 0.f ? 1.f / st.l[1] : 0.f;
-  float* so = smem + (size_t)warp * 16 * HD;
-#pragma unroll
-  for (int n = 0; n < S::NT; ++n)
-#pragma unroll
-    for (int i = 0; i < 4; ++i)
-      so[(g + 8 * (i >> 1)) * HD + out_col<HD>(n, i, t)] = st.o[n][i] * ((i >> 1) ? inv1 : inv0);
-  __syncwarp();
-  for (int idx = lane; idx < 16 * HD / 2; idx += 32) {
-    const int r = (2 * idx) / HD, c = (2 * idx) % HD;
-    if (warp * 16 + r >= rows) continue;
-    const __nv_bfloat162 v = __floats2bfloat162_rn(so[r * HD + c], so[r * HD + c + 1]);
-    *reinterpret_cast<__nv_bfloat162*>(a.out + (int64_t)(tok0 + warp * 16 + r) * a.ldo + (int64_t)h * HD + c) = v;
-  }
+  // each thread owns HD/4 consecutive columns of its two rows: straight to global memory
+  bf16* p0 = r0 < rows ? a.out + (int64_t)(tok0 + r0) * a.ldo + (int64_t)h * HD : nullptr;
+  bf16* p1 = r1 < rows ? a.out + (int64_t)(tok0 + r1) * a.ldo + (int64_t)h * HD : nullptr;
+  store_rows_bf16<HD>(p0, p1, st.o, t, inv0, inv1);
 }
 
 template <int HD>
