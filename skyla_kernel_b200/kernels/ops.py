@@ -256,10 +256,12 @@ def tc_linear_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
 
 
 def token_tile(m: int, gated: bool = False) -> int:
+    """Tokens per tile.  From 129 tokens on the persistent kernel takes over: tiles of 256
+    (128 for the gated product, whose two accumulators are twice as wide)."""
     for bn in TC_TOKEN_TILES:
         if m <= bn:
-            return bn
-    return 256
+            return 128 if gated and bn == 256 else bn
+    return 128 if gated else 256
 
 
 def _fold_args(fold, m: int):
