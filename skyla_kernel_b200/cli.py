@@ -213,6 +213,7 @@ def main(argv=None) -> int:
     p.add_argument("--batch", type=int, default=8)
     p.add_argument("--context", type=int, default=2048)
     p.add_argument("--reps", type=int, default=5)
+    p.add_argument("--splits", type=int, default=0, help="attention-decode: override the number of context splits")
     p.set_defaults(fn=lambda a: __import__("skyla_kernel_b200.kernel_bench", fromlist=["main"]).main(a))
     p = sub.add_parser("replay", help="replay a token trace from standard input (bin/trace_run)")
     p.add_argument("--model", required=True)

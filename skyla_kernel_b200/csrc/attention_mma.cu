@@ -310,9 +310,26 @@ __device__ __forceinline__ void stage_page(bf16* stage, const bf16* __restrict__
 }
 
 // ------------------------------------------------------------------------ decode
+// The new token's q, k and v made inside the decode kernel instead of by a kernel before it:
+// `qkv` holds K-split partial sums [n_splits][tokens][ld] of the QKV product of un-scaled
+// rows and `ssq` each split's share of the rows' sums of squares (see gemm_tc.cu); every
+// block finishes the q heads of its group (row scalar, per-head RMSNorm, rotation), and the
+// block whose pages end at the token's own position also finishes k and v, writes them to
+// the cache and patches them into the page it has staged.
+struct FusedPrep {
+  const float* qkv; int n_splits; int64_t split_stride, ld; int q_off, k_off, v_off;
+  const float* ssq; int n_ssq; int norm_width; float norm_eps;
+  const float* q_norm; const float* k_norm; float eps; const float* cos_t; const float* sin_t; int n_rot;
+  bf16* k_pool; bf16* v_pool; int n_tokens;
+};
+
 struct DecodeArgs {
   const bf16* q; int64_t ldq; float* part; int n_splits, pages_per_split;
   int nq, nkv; PagedKV kv; const int32_t* tok_pos; float scale; int window;
+  FusedPrep prep;  // prep.qkv == nullptr: q comes prepared in `q`, k and v are in the cache
+  // if set: the pages the longest sequence of this step needs; the splits then share those
+  // evenly (pages_per_split is ignored), so a launch recorded once fits every context length
+  const int32_t* pages_needed;
 };
 
 constexpr int kDecodeWarps = 8;
@@ -331,8 +348,10 @@ __global__ void __launch_bounds__(kDecodeWarps * 32) attn_decode_kernel(DecodeAr
   const int G = a.nq / a.nkv;
   const int pos = a.tok_pos[b];
   const int first = a.window > 0 ? max(0, pos - a.window + 1) : 0;
-  const int page_begin = max(split * a.pages_per_split, first / kPage);
-  const int page_end = min((split + 1) * a.pages_per_split, pos / kPage + 1);
+  const int per_split = a.pages_needed != nullptr
+                            ? max(1, (a.pages_needed[0] + a.n_splits - 1) / a.n_splits) : a.pages_per_split;
+  const int page_begin = max(split * per_split, first / kPage);
+  const int page_end = min((split + 1) * per_split, pos / kPage + 1);
   const int n_pages = max(0, page_end - page_begin);
   const int n_pairs = (n_pages + 1) / 2;  // warps 0-3 take the first page of a pair, warps 4-7 the second
   const int32_t* seq_pages = a.kv.pages + (int64_t)b * a.kv.max_pages;
@@ -354,9 +373,63 @@ __global__ void __launch_bounds__(kDecodeWarps * 32) attn_decode_kernel(DecodeAr
   uint32_t qa[S::NQ], qb[S::NQ];
 #pragma unroll
   for (int i = 0; i < S::NQ; ++i) qa[i] = qb[i] = 0u;
-  const bf16* qrow = a.q + (int64_t)b * a.ldq + (int64_t)kvh * G * HD;
-  if (g < G) load_row<HD>(qrow + g * HD, t, qa);
-  if (g + 8 < G) load_row<HD>(qrow + (g + 8) * HD, t, qb);
+  // after the page stages: [G+2][HD] bf16 finished heads (q heads, then k, then v), [NW][HD] float scratch
+  bf16* fresh = stages + (size_t)kStages * Stage<HD>::kElems;
+  const bool fused = a.prep.qkv != nullptr;
+  const bool owner = fused && page_end == pos / kPage + 1 && n_pages > 0;  // this block's pages end at the new token
+  if (fused) {
+    float* u = reinterpret_cast<float*>(fresh + (size_t)(G + 2) * HD) + (size_t)warp * HD;
+    const FusedPrep& p = a.prep;
+    float ssq = 0.f;
+    for (int sp = 0; sp < p.n_ssq; ++sp) ssq += p.ssq[(int64_t)sp * p.n_tokens + b];
+    const float row_scale = 1.0f / sqrtf(ssq / (float)p.norm_width + p.norm_eps);
+    for (int job = warp; job < G + 2; job += NW) {  // q heads of the group, then k, then v
+      if (job >= G && !owner) continue;
+      const bool is_q = job < G, is_k = job == G;
+      const float* src = p.qkv + (int64_t)b * p.ld +
+                         (is_q ? p.q_off + (kvh * G + job) * HD : (is_k ? p.k_off : p.v_off) + kvh * HD);
+      float ss = 0.f;
+      for (int e = lane; e < HD; e += 32) {
+        float v = src[e];
+        for (int sp = 1; sp < p.n_splits; ++sp) v += src[(int64_t)sp * p.split_stride + e];
+        v *= row_scale;
+        u[e] = v;
+        ss = fmaf(v, v, ss);
+      }
+      const float* nw = is_q ? p.q_norm : (is_k ? p.k_norm : nullptr);
+      if (nw != nullptr) {
+        ss = warp_sum(ss);
+        const float inv = 1.0f / sqrtf(ss / (float)HD + p.eps);
+        for (int e = lane; e < HD; e += 32) u[e] *= inv * nw[e];
+      }
+      __syncwarp();
+      const int half = p.n_rot / 2;
+      bf16* dst = fresh + (size_t)job * HD;
+      for (int e = lane; e < HD; e += 32) {
+        float v = u[e];
+        if ((is_q || is_k) && p.cos_t != nullptr && e < p.n_rot) {
+          const int i = e < half ? e : e - half;
+          const float c = p.cos_t[(int64_t)pos * half + i], sn = p.sin_t[(int64_t)pos * half + i];
+          const float x0 = u[i], x1 = u[i + half];
+          v = e < half ? x0 * c - x1 * sn : x0 * sn + x1 * c;
+        }
+        dst[e] = __float2bfloat16_rn(v);
+      }
+      __syncwarp();
+      if (!is_q) {  // the token's place in the cache, for the steps to come
+        const size_t row = ((size_t)seq_pages[pos / kPage] * a.kv.nkv + kvh) * kPage + pos % kPage;
+        bf16* pool = is_k ? p.k_pool : p.v_pool;
+        for (int e = lane; e < HD; e += 32) pool[row * HD + e] = dst[e];
+      }
+    }
+    __syncthreads();
+    if (g < G) load_row<HD>(fresh + (size_t)g * HD, t, qa);
+    if (g + 8 < G) load_row<HD>(fresh + (size_t)(g + 8) * HD, t, qb);
+  } else {
+    const bf16* qrow = a.q + (int64_t)b * a.ldq + (int64_t)kvh * G * HD;
+    if (g < G) load_row<HD>(qrow + g * HD, t, qa);
+    if (g + 8 < G) load_row<HD>(qrow + (g + 8) * HD, t, qb);
+  }
   const int hi0 = g < G ? pos : -1, hi1 = g + 8 < G ? pos : -1;
   const float scale_log2 = a.scale * kLog2e;
 
@@ -366,6 +439,19 @@ __global__ void __launch_bounds__(kDecodeWarps * 32) attn_decode_kernel(DecodeAr
     issue(pr + kPairsAhead);
     cp_async_wait<kPairsAhead>();
     __syncthreads();
+    if (owner && pr == n_pairs - 1) {
+      // the staged copy of the token's page was read before k and v were written: put them in
+      bf16* page = stages + (size_t)((n_pages - 1) % kStages) * Stage<HD>::kElems;
+      const int r = pos % kPage;
+      for (int c = threadIdx.x; c < 2 * (HD / 8); c += NW * 32) {
+        const bool is_v = c >= HD / 8;
+        const int chunk = is_v ? c - HD / 8 : c;
+        const int x = is_v ? Swz<HD>::v(r) : Swz<HD>::k(r);
+        *reinterpret_cast<uint4*>(page + (is_v ? kPage * RS : 0) + r * RS + 8 * (chunk ^ x)) =
+            *reinterpret_cast<const uint4*>(fresh + (size_t)(G + (is_v ? 1 : 0)) * HD + 8 * chunk);
+      }
+      __syncthreads();
+    }
     const int i = 2 * pr + (warp >> 2);
     const bf16* sk = stages + (size_t)(i % kStages) * Stage<HD>::kElems;
     const int key0 = (page_begin + i) * kPage + 16 * (warp & 3);  // this warp's 16 positions
@@ -515,6 +601,8 @@ template <int HD>
 int launch_decode(const DecodeArgs& a, int n_seqs, cudaStream_t stream) {
   size_t smem = (size_t)(kDecodeWarps * 16 * HD + 2 * kDecodeWarps * 16) * sizeof(float);
   if (smem < (size_t)Stage<HD>::kDecodeStages * Stage<HD>::kPageBytes) smem = (size_t)Stage<HD>::kDecodeStages * Stage<HD>::kPageBytes;
+  // after the stages: up to 18 finished heads (bf16) and a float scratch row per warp
+  smem += (size_t)18 * HD * sizeof(bf16) + (size_t)kDecodeWarps * HD * sizeof(float);
   static bool configured = false;
   if (!configured && smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -571,7 +659,7 @@ extern "C" int skyla_attention_decode(const void* q, int64_t ldq, void* out, int
                                       int nq, int nkv, int hd, const void* k_pool, const void* v_pool,
                                       const int32_t* pages, int max_pages, int page_size, const int32_t* tok_pos,
                                       float scale, int window, int n_splits, int pages_per_split,
-                                      cudaStream_t stream) {
+                                      const int32_t* pages_needed, cudaStream_t stream) {
   if (n_seqs <= 0) return kOk;
   int rc = check_common(q, ldq, nq, nkv, page_size, k_pool, v_pool);
   if (rc) return rc;
@@ -579,7 +667,39 @@ extern "C" int skyla_attention_decode(const void* q, int64_t ldq, void* out, int
   if (n_splits < 1 || pages_per_split < 1 || n_seqs > 65535 || n_splits > 65535)
     return fail(kBadArgument, "attention_decode: bad split of the context");
   DecodeArgs a{(const bf16*)q, ldq, part, n_splits, pages_per_split, nq, nkv,
-               PagedKV{(const bf16*)k_pool, (const bf16*)v_pool, pages, max_pages, page_size, nkv}, tok_pos, scale, window};
+               PagedKV{(const bf16*)k_pool, (const bf16*)v_pool, pages, max_pages, page_size, nkv}, tok_pos, scale, window,
+               FusedPrep{}, pages_needed};
+  SKYLA_HD_SWITCH(hd, { rc = launch_decode<HD>(a, n_seqs, stream); break; });
+  if (rc) return rc;
+  MergeArgs m{part, (bf16*)out, ldo, nq, n_splits, hd};
+  launch_overlapped(attn_merge_kernel, dim3(nq, n_seqs), dim3(128), 0, stream, m);
+  return check_launch("attention_merge");
+}
+
+// Decode with the new token's q, k and v finished inside the kernel: `qkv` are the K-split
+// partial sums [qkv_splits][n_seqs][ld] (float) of the QKV product of un-scaled rows, `ssq`
+// [n_ssq][n_seqs] the splits' shares of the rows' sums of squares over `norm_width` inputs.
+// k and v of the new token are written to the pools (which this call therefore changes).
+extern "C" int skyla_attention_decode_fused(
+    const float* qkv, int qkv_splits, int64_t qkv_split_stride, int64_t ld, int q_off, int k_off, int v_off,
+    const float* ssq, int n_ssq, int norm_width, float norm_eps, const float* q_norm, const float* k_norm,
+    float eps, const float* cos_t, const float* sin_t, int n_rot, void* out, int64_t ldo, float* part, int n_seqs,
+    int nq, int nkv, int hd, void* k_pool, void* v_pool, const int32_t* pages, int max_pages, int page_size,
+    const int32_t* tok_pos, float scale, int window, int n_splits, int pages_per_split,
+    const int32_t* pages_needed, cudaStream_t stream) {
+  if (n_seqs <= 0) return kOk;
+  int rc = check_common(k_pool, 8, nq, nkv, page_size, k_pool, v_pool);
+  if (rc) return rc;
+  if (nq / nkv > 16) return fail(kBadArgument, "attention_decode: groups of %d query heads exceed 16", nq / nkv);
+  if (n_splits < 1 || pages_per_split < 1 || n_seqs > 65535 || n_splits > 65535)
+    return fail(kBadArgument, "attention_decode: bad split of the context");
+  if (qkv == nullptr || ssq == nullptr || qkv_splits < 1 || n_ssq < 1 || norm_width <= 0 || n_rot < 0 || n_rot > hd || n_rot % 2)
+    return fail(kBadArgument, "attention_decode_fused: bad description of the unfinished q, k and v");
+  DecodeArgs a{nullptr, 0, part, n_splits, pages_per_split, nq, nkv,
+               PagedKV{(const bf16*)k_pool, (const bf16*)v_pool, pages, max_pages, page_size, nkv}, tok_pos, scale, window,
+               FusedPrep{qkv, qkv_splits, qkv_split_stride, ld, q_off, k_off, v_off, ssq, n_ssq, norm_width, norm_eps,
+                         q_norm, k_norm, eps, cos_t, sin_t, cos_t ? n_rot : 0, (bf16*)k_pool, (bf16*)v_pool, n_seqs},
+               pages_needed};
   SKYLA_HD_SWITCH(hd, { rc = launch_decode<HD>(a, n_seqs, stream); break; });
   if (rc) return rc;
   MergeArgs m{part, (bf16*)out, ldo, nq, n_splits, hd};
@@ -651,5 +771,5 @@ extern "C" int skyla_attention_decode_no_alloc(const void* q, int64_t ldq, void*
   const int rc = scratch_address(&scratch);
   if (rc) return rc;
   return skyla_attention_decode(q, ldq, out, ldo, scratch, n_seqs, nq, nkv, hd, k_pool, v_pool, pages, max_pages,
-                                page_size, tok_pos, scale, window, n_splits, pages_per_split, stream);
+                                page_size, tok_pos, scale, window, n_splits, pages_per_split, nullptr, stream);
 }

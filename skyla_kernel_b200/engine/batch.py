@@ -79,6 +79,7 @@ class StepContext:
     cu: torch.Tensor
     want: torch.Tensor
     pages: List[torch.Tensor]
+    pages_needed: Optional[torch.Tensor] = None  # one int32: pages of the longest sequence after this step
     n_tiles: int = 0
     tile_seq: Optional[torch.Tensor] = None
     tile_tok0: Optional[torch.Tensor] = None
@@ -152,7 +153,7 @@ class BatchBuilder:
             P = pages_width
         TILE = 64
         Q = sum(-(-n // TILE) for n in ns)
-        total = 3 * T + 3 * B + (B + 1) + R + 3 * Q + G * B * P
+        total = 3 * T + 3 * B + (B + 1) + R + 3 * Q + 1 + G * B * P
         if self._copied is not None:
             self._copied.synchronize()  # the last step's copy has left the pinned buffer
         host, dev = self._staging(total)
@@ -176,6 +177,8 @@ class BatchBuilder:
         tile_seq, r_tseq = take(Q)
         tile_tok0, r_ttok = take(Q)
         tile_rows, r_trows = take(Q)
+        needed, r_needed = take(1)
+        needed[0] = max(1, max(-(-(s + n) // cache.page_size) for s, n in zip(starts, ns)))
         q = 0
         t = 0
         w = 0
@@ -221,6 +224,6 @@ class BatchBuilder:
             page_size=cache.page_size, tokens=view(r_tokens), tok_pos=view(r_pos),
             tok_seq=view(r_seq), seq_slot=view(r_slot), seq_start=view(r_start), seq_n=view(r_n),
             cu=view(r_cu), want=view(r_want), pages=[view(r).view(B, P) for r in r_pages],
-            n_tiles=Q, tile_seq=view(r_tseq), tile_tok0=view(r_ttok), tile_rows=view(r_trows),
+            pages_needed=view(r_needed), n_tiles=Q, tile_seq=view(r_tseq), tile_tok0=view(r_ttok), tile_rows=view(r_trows),
             host={"starts": np.asarray(starts), "ns": np.asarray(ns)},
         )

@@ -84,16 +84,26 @@ def _paged(batch: int, context: int, nkv: int, hd: int):
     return k, v, table, width
 
 
-def attention_decode(batch: int, context: int, nq: int = 32, nkv: int = 8, hd: int = 128, reps: int = 5) -> dict:
+def attention_decode(batch: int, context: int, nq: int = 32, nkv: int = 8, hd: int = 128, reps: int = 5,
+                     splits: int = 0) -> dict:
+    """Split-context decode attention plus its merge, cut as the attention part would cut it
+    (``splits`` > 0 overrides the number of splits)."""
+    from .config import PartSpec
+    from .parts.attention import GQAttention
+    from .parts.base import Runtime
     k, v, table, width = _paged(batch, context, nkv, hd)
     q = torch.randn(batch, nq * hd, device=DEV).to(torch.bfloat16)
     out = torch.empty_like(q)
     pos = torch.full((batch,), context - 1, dtype=torch.int32, device=DEV)
-    per = max(4, width // 4)
-    n_splits = -(-width // per)
+    part = GQAttention(PartSpec("gqa_attention", {"hidden_size": nq * hd, "num_heads": nq, "num_kv_heads": nkv,
+                                                  "head_dim": hd}), Runtime(torch.device(DEV), "bfloat16"))
+    n_splits, per = part.decode_splits(batch, width)
+    if splits:
+        n_splits, per = splits, -(-width // splits)
+    needed = torch.tensor([-(-context // 64)], dtype=torch.int32, device=DEV)
     scratch = torch.empty(batch * nq * n_splits * (hd + 2), device=DEV)
     us = _time(lambda i: ops.attention_decode(q, out, scratch, nq, nkv, hd, k, v, table, 64, pos, 1 / math.sqrt(hd), 0,
-                                              n_splits, per), 8, reps)
+                                              n_splits, per, needed), 8, reps)
     kv_bytes = 2 * batch * context * nkv * hd * 2
     return {"kernel": "attention-decode", "batch": batch, "context": context, "us": us, "splits": n_splits,
             "kv_GBps": kv_bytes / us / 1e3}
@@ -118,7 +128,7 @@ def main(a) -> int:
     if a.kernel == "linear":
         r = linear(a.tokens, a.n_out, a.n_in, a.mode, reps=a.reps)
     elif a.kernel == "attention-decode":
-        r = attention_decode(a.batch, a.context, reps=a.reps)
+        r = attention_decode(a.batch, a.context, reps=a.reps, splits=a.splits)
     else:
         r = attention_prefill(a.tokens, reps=a.reps)
     print(json.dumps(r))

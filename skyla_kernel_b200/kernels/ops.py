@@ -465,22 +465,66 @@ def _attn_common(q, out, k_pool, v_pool, nq, nkv, hd, page_size, *ints):
 def attention_decode(q: torch.Tensor, out: torch.Tensor, scratch: torch.Tensor, nq: int, nkv: int, hd: int,
                      k_pool: torch.Tensor, v_pool: torch.Tensor, pages: torch.Tensor, page_size: int,
                      tok_pos: torch.Tensor, scale: float, window: int, n_splits: int,
-                     pages_per_split: int) -> torch.Tensor:
+                     pages_per_split: int, pages_needed: Optional[torch.Tensor] = None) -> torch.Tensor:
     """One new token per sequence (token b belongs to sequence b): split-context attention
     over the cache for all query heads of a key/value head at once, then the merge.
 
     ``scratch``: float32, at least ``n_seqs * nq * n_splits * (hd + 2)`` elements.
+    ``pages_needed`` (one int32 on the device): the pages the longest sequence needs; the splits
+    then share those evenly and ``pages_per_split`` is ignored.
     """
     _attn_common(q, out, k_pool, v_pool, nq, nkv, hd, page_size, pages, tok_pos)
+    _cuda(pages_needed); _i32(pages_needed, "pages_needed")
     n = tok_pos.numel()
     if scratch.dtype != torch.float32 or scratch.numel() < n * nq * n_splits * (hd + 2):
         raise KernelError("attention_decode: scratch too small")
     f = _fn("attention_mma", "skyla_attention_decode",
             [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
-             c_void_p, c_int, c_int, c_void_p, c_float, c_int, c_int, c_int, c_void_p])
+             c_void_p, c_int, c_int, c_void_p, c_float, c_int, c_int, c_int, c_void_p, c_void_p])
     _check("attention_mma", f(_ptr(q), _rows(q, "q"), _ptr(out), _rows(out, "out"), _ptr(scratch), n, nq, nkv, hd,
                               _ptr(k_pool), _ptr(v_pool), _ptr(pages), pages.shape[1], page_size, _ptr(tok_pos),
-                              float(scale), int(window or 0), n_splits, pages_per_split, _stream()))
+                              float(scale), int(window or 0), n_splits, pages_per_split, _ptr(pages_needed), _stream()))
+    global LAUNCHES
+    LAUNCHES += 1  # the merge kernel
+    return out
+
+
+def attention_decode_fused(qkv_partials: torch.Tensor, row_ssq: torch.Tensor, norm_width: int, norm_eps: float,
+                           q_off: int, k_off: int, v_off: int, q_norm: Optional[torch.Tensor],
+                           k_norm: Optional[torch.Tensor], eps: float, cos: Optional[torch.Tensor],
+                           sin: Optional[torch.Tensor], n_rot: int, out: torch.Tensor, scratch: torch.Tensor,
+                           nq: int, nkv: int, hd: int, k_pool: torch.Tensor, v_pool: torch.Tensor,
+                           pages: torch.Tensor, page_size: int, tok_pos: torch.Tensor, scale: float, window: int,
+                           n_splits: int, pages_per_split: int,
+                           pages_needed: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Decode attention that also finishes the new token's q, k and v (what
+    ``qk_norm_rope_cache`` does) from the K-split partial sums of the QKV product and the
+    rows' sums of squares, and writes k and v to the cache."""
+    _cuda(qkv_partials, row_ssq, q_norm, k_norm, cos, sin, out, scratch, k_pool, v_pool, pages, tok_pos, pages_needed)
+    _i32(pages, "pages"); _i32(tok_pos, "tok_pos"); _i32(pages_needed, "pages_needed")
+    n = tok_pos.numel()
+    if (qkv_partials.dtype != torch.float32 or qkv_partials.dim() != 3 or not qkv_partials.is_contiguous()
+            or qkv_partials.shape[1] != n or row_ssq.dtype != torch.float32 or not row_ssq.is_contiguous()
+            or row_ssq.dim() != 2 or row_ssq.shape[1] != n):
+        raise KernelError("attention_decode_fused: partial sums [splits, tokens, width] and sums of squares [splits, tokens], float32")
+    if out.dtype != torch.bfloat16 or k_pool.dtype != torch.bfloat16 or tuple(k_pool.shape[1:]) != (nkv, page_size, hd) \
+            or k_pool.shape != v_pool.shape or not k_pool.is_contiguous() or not v_pool.is_contiguous():
+        raise KernelError("attention_decode_fused: bfloat16 output and cache pools [pages, kv heads, page, head]")
+    for t_, what in ((q_norm, "q_norm"), (k_norm, "k_norm"), (cos, "cos"), (sin, "sin")):
+        if t_ is not None and (t_.dtype != torch.float32 or not t_.is_contiguous()):
+            raise KernelError(f"{what}: expected a contiguous float32 tensor")
+    if scratch.dtype != torch.float32 or scratch.numel() < n * nq * n_splits * (hd + 2):
+        raise KernelError("attention_decode_fused: scratch too small")
+    f = _fn("attention_mma", "skyla_attention_decode_fused",
+            [c_void_p, c_int, c_int64, c_int64, c_int, c_int, c_int, c_void_p, c_int, c_int, c_float, c_void_p, c_void_p,
+             c_float, c_void_p, c_void_p, c_int, c_void_p, c_int64, c_void_p, c_int, c_int, c_int, c_int, c_void_p,
+             c_void_p, c_void_p, c_int, c_int, c_void_p, c_float, c_int, c_int, c_int, c_void_p, c_void_p])
+    _check("attention_mma", f(_ptr(qkv_partials), qkv_partials.shape[0], qkv_partials.stride(0), qkv_partials.stride(1),
+                              q_off, k_off, v_off, _ptr(row_ssq), row_ssq.shape[0], int(norm_width), float(norm_eps),
+                              _ptr(q_norm), _ptr(k_norm), float(eps), _ptr(cos), _ptr(sin), n_rot if cos is not None else 0,
+                              _ptr(out), _rows(out, "out"), _ptr(scratch), n, nq, nkv, hd, _ptr(k_pool), _ptr(v_pool),
+                              _ptr(pages), pages.shape[1], page_size, _ptr(tok_pos), float(scale), int(window or 0),
+                              n_splits, pages_per_split, _ptr(pages_needed), _stream()))
     global LAUNCHES
     LAUNCHES += 1  # the merge kernel
     return out

@@ -96,16 +96,21 @@ class GQAttention(Part):
 
     # -------------------------------------------------------------------- cache
     def decode_splits(self, n_seqs: int, max_pages: int):
-        """How a decode step cuts the context: (splits, pages per split).
+        """Into how many blocks a decode step cuts each sequence's context: (splits, pages per split).
 
-        A block is alone on its SM and pays a few microseconds before its first page
-        arrives, so blocks are few and long: a quarter of the page-list width each,
-        at least four pages.  Splits are aligned to absolute positions and do not
-        depend on the other sequences of the batch; blocks past a sequence's end
-        return at once.
+        A block is alone on its SM and pays for about six pages' time before its first page
+        arrives; blocks run in waves of 148.  The count is fixed per (batch, page-list width) so
+        that a recorded launch keeps its grid; how many pages a split covers follows the step's
+        longest sequence, which the kernel reads from device memory.
         """
-        per = max(4, max_pages // 4)
-        return -(-max_pages // per), per
+        items = max(1, self.nkv * n_seqs)
+        typical = max(1.0, 0.75 * max_pages)
+        best, best_cost = 1, None
+        for n in range(1, max(1, min(32, max_pages // 2)) + 1):
+            cost = -(-items * n // 148) * (6.0 + typical / n)
+            if best_cost is None or cost < best_cost:
+                best, best_cost = n, cost
+        return best, -(-max_pages // best)
 
     def cache_need(self) -> Optional[KVNeed]:
         return KVNeed(self.nkv, self.hd, self.window or None)
@@ -132,8 +137,23 @@ class GQAttention(Part):
         if normed is not None:
             part, ssq = self.qkv.forward_normed_partial(normed, ctx, "attn.qkv_partials")
             ctx.mark("matvec qkv")
+            pend = ctx.take_pending()
+            if (pend is None and self._fast == 2 and ctx.is_decode and k_pool.dtype == torch.bfloat16
+                    and self.rt.act_dtype == torch.bfloat16):
+                # one new token per sequence: its q, k and v are finished inside the attention kernel
+                attn = ctx.buffer("attn.out", (n, nq * hd), self.rt.act_dtype)
+                n_splits, per = self.decode_splits(ctx.n_seqs, pages.shape[1])
+                scratch = ctx.buffer("attn.partials", (n * nq * n_splits * (hd + 2),), torch.float32)
+                ops.attention_decode_fused(part, ssq, self.hidden, normed.norm.eps, 0, nq * hd, (nq + nkv) * hd,
+                                           self.q_norm_w, self.k_norm_w, self.eps, cos, sin, n_rot, attn, scratch,
+                                           nq, nkv, hd, k_pool, v_pool, pages, ctx.page_size, ctx.tok_pos,
+                                           self.scale, self.window, n_splits, per, ctx.pages_needed)
+                ctx.mark("attention")
+                self.out.forward(attn, x, ACCUMULATE)
+                ctx.mark("matvec o")
+                return
             qkv = ctx.buffer("attn.q", (n, nq * hd), self.rt.act_dtype)
-            pend = ctx.take_pending()  # if sums are pending, the prep kernel also makes x whole, after the product read it
+            # if sums are pending, the prep kernel also makes x whole, after the product read it
             ops.qk_norm_rope_cache(part, 0, nq * hd, (nq + nkv) * hd, nq, nkv, hd, self.q_norm_w,
                                    self.k_norm_w, self.eps, cos, sin, n_rot, ctx.tok_pos, ctx.tok_seq,
                                    k_pool, v_pool, pages, ctx.page_size, q_out=qkv, row_ssq=ssq,
@@ -168,7 +188,7 @@ class GQAttention(Part):
             n_splits, per = self.decode_splits(ctx.n_seqs, pages.shape[1])
             scratch = ctx.buffer("attn.partials", (n * nq * n_splits * (hd + 2),), torch.float32)
             ops.attention_decode(q, attn, scratch, nq, nkv, hd, k_pool, v_pool, pages, ctx.page_size,
-                                 ctx.tok_pos, self.scale, self.window, n_splits, per)
+                                 ctx.tok_pos, self.scale, self.window, n_splits, per, ctx.pages_needed)
         elif fast:
             ops.attention_prefill(q, attn, nq, nkv, hd, k_pool, v_pool, pages, ctx.page_size, ctx.tok_pos,
                                   ctx.tile_seq, ctx.tile_tok0, ctx.tile_rows, self.scale, self.window)

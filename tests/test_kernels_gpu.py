@@ -599,3 +599,41 @@ def test_gemm_tc_cluster_accumulate(m, n, k, splits):
     assert (runs[0].double() - ref).abs().max().item() <= 3e-5 * ref.abs().max().item() + 1e-5
     assert torch.equal(runs[0], runs[1])  # a fixed order of summation: the same bits every time
     ops.check_device_errors(DEV)
+
+
+@pytest.mark.parametrize("nq,nkv,hd,n_rot,window", [(32, 8, 128, 128, 0), (6, 1, 32, 32, 0), (3, 3, 48, 24, 70), (8, 2, 64, 64, 0)])
+def test_attention_decode_fused_prep(nq, nkv, hd, n_rot, window):
+    """The decode kernel finishing q, k and v itself against prep kernel + decode kernel."""
+    ops = _ops()
+    dt = torch.bfloat16
+    lens = [1, 64, 65, 200, 333, 128]   # lengths after the new token
+    B, S = len(lens), 3
+    width = (nq + 2 * nkv) * hd
+    k_pool, v_pool, table, ks, vs = _paged(B, lens, nkv, hd, dt, seed=nq + hd)
+    part = _rand(S, B, width, seed=101)
+    hidden = 777
+    ssq = (_rand(S, B, seed=102).abs() + 0.5) * hidden
+    qn, kn = 1 + 0.2 * _rand(hd, seed=103), 1 + 0.2 * _rand(hd, seed=104)
+    freqs, _ = plain.rope_frequencies(n_rot, 10000.0)
+    ang = (torch.arange(512, dtype=torch.float32)[:, None] * freqs[None, :]).double()
+    cos, sin = torch.cos(ang).float().to(DEV), torch.sin(ang).float().to(DEV)
+    tok_pos = torch.tensor([l - 1 for l in lens], dtype=torch.int32, device=DEV)
+    seq = torch.arange(B, dtype=torch.int32, device=DEV)
+    scale = 1.0 / math.sqrt(hd)
+    n_splits, per = 3, 2
+    # two kernels
+    kp1, vp1 = k_pool.clone(), v_pool.clone()
+    q = torch.empty(B, nq * hd, dtype=dt, device=DEV)
+    ops.qk_norm_rope_cache(part, 0, nq * hd, (nq + nkv) * hd, nq, nkv, hd, qn, kn, 1e-6, cos, sin, n_rot, tok_pos, seq,
+                           kp1, vp1, table, 64, q_out=q, row_ssq=ssq, norm_width=hidden, norm_eps=1e-5)
+    want = torch.empty(B, nq * hd, dtype=dt, device=DEV)
+    scratch = torch.empty(B * nq * n_splits * (hd + 2), dtype=torch.float32, device=DEV)
+    ops.attention_decode(q, want, scratch, nq, nkv, hd, kp1, vp1, table, 64, tok_pos, scale, window, n_splits, per)
+    # one kernel
+    kp2, vp2 = k_pool.clone(), v_pool.clone()
+    got = torch.full_like(want, float("nan"))
+    ops.attention_decode_fused(part, ssq, hidden, 1e-5, 0, nq * hd, (nq + nkv) * hd, qn, kn, 1e-6, cos, sin, n_rot, got,
+                               scratch, nq, nkv, hd, kp2, vp2, table, 64, tok_pos, scale, window, n_splits, per)
+    torch.testing.assert_close(got.float(), want.float(), rtol=2e-2, atol=2e-2)
+    assert torch.equal(kp2, kp1) and torch.equal(vp2, vp1)  # the same k and v reached the cache
+    assert not torch.equal(kp2, k_pool)
