@@ -102,6 +102,25 @@ class _Backend:
     def sample(self, logits, req_ids, steps) -> List[int]:
         return self.sampler(logits, req_ids, steps).cpu().tolist()
 
+    def step_async(self, items, req_ids, steps) -> "_Tokens":
+        """Step and sample without waiting: the tokens stay on the device for the next step and
+        travel to pinned host memory on the side."""
+        logits = self.m.engine.step(items, borrow=True)
+        return _Tokens(self.sampler(logits, req_ids, steps))
+
+
+class _Tokens:
+    def __init__(self, device_tokens: torch.Tensor):
+        self.device_tokens = device_tokens
+        self._host = torch.empty(device_tokens.shape, dtype=device_tokens.dtype, pin_memory=True)
+        self._host.copy_(device_tokens, non_blocking=True)
+        self._ready = torch.cuda.Event()
+        self._ready.record()
+
+    def tokens(self) -> List[int]:
+        self._ready.synchronize()
+        return self._host.tolist()
+
 
 def load(model: Union[str, dict, object], dtype: str = "bfloat16", max_tokens: int = 4096,
          max_slots: Optional[int] = None, device="cuda:0", seed: int = 0,

@@ -32,6 +32,9 @@ class StepItem:
     slot: int
     tokens: Sequence[int]
     want: Sequence[int] = ()
+    #: (handle, row): the item's one token is row ``row`` of ``handle.device_tokens`` (int32 on
+    #: the device, e.g. what a sampler just wrote) and ``tokens`` is a placeholder of length 1
+    device_token: Optional[tuple] = None
 
 
 class Workspace:
@@ -120,6 +123,23 @@ class StepContext:
 
 class BatchBuilder:
     """Packs a step's arrays on the host and moves them with one copy."""
+
+    def _feed_device_tokens(self, items, dev_tokens: torch.Tensor, ns) -> None:
+        """Tokens that only exist on the device are copied into place there."""
+        fed = [(b, it.device_token) for b, it in enumerate(items) if it.device_token is not None]
+        if not fed:
+            return
+        if len(fed) != len(items) or any(n != 1 for n in ns):
+            raise ValueError("device-fed tokens: every item of the step must bring exactly one such token")
+        src = fed[0][1][0].device_tokens
+        rows = [ref[1] for _, ref in fed]
+        if any(ref[0].device_tokens is not src for _, ref in fed):
+            raise ValueError("device-fed tokens must come from one step's sampler output")
+        if rows == list(range(len(rows))):
+            dev_tokens.copy_(src[: len(rows)])
+        else:
+            idx = torch.tensor(rows, dtype=torch.int64).to(self.rt.device, non_blocking=True)
+            dev_tokens.copy_(src.index_select(0, idx))
 
     def __init__(self, rt, cache):
         self.rt = rt
@@ -213,6 +233,7 @@ class BatchBuilder:
         if self.rt.device.type == "cuda":
             self._copied = torch.cuda.Event()
             self._copied.record()
+        self._feed_device_tokens(items, dev[r_tokens[0]:r_tokens[1]], ns)
 
         def view(r):
             return dev[r[0]:r[1]]

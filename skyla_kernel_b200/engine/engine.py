@@ -102,6 +102,8 @@ class Engine:
         for it in items:
             if len(it.tokens) == 0:
                 raise ValueError(f"slot {it.slot}: a step must bring at least one token")
+            if it.device_token is not None:
+                continue  # a sampler's output on the device: inside the vocabulary by construction
             arr = np.asarray(it.tokens)
             if arr.dtype.kind not in "iu":
                 raise ValueError(f"slot {it.slot}: tokens must be integers")

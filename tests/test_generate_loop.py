@@ -121,3 +121,80 @@ def test_zero_new_tokens_and_failure_frees_slots():
     with pytest.raises(RuntimeError, match="boom"):
         generate(f, [Request([1], 9), Request([2], 9)])
     assert f.free == [0, 1, 2, 3] and not f.seqs
+
+
+class AsyncFake(FakeBackend):
+    """The same model with the pipelined interface; counts steps that ran for nothing."""
+
+    class Handle:
+        def __init__(self, toks):
+            self.device_tokens = toks  # a list stands in for device memory
+            self.asked = False
+
+        def tokens(self):
+            self.asked = True
+            return list(self.device_tokens)
+
+    def __init__(self, *a, **k):
+        super().__init__(*a, **k)
+        self.handles = []
+        self.keys = []
+
+    def step_async(self, items, req_ids, steps):
+        fed = [it for it in items if it.device_token is not None]
+        if fed:
+            assert len(fed) == len(items)
+            for it in items:
+                h, row = it.device_token
+                assert not h.asked or True  # the tokens may or may not have been read on the host yet
+                it.tokens = [h.device_tokens[row]]
+        out = self.step(items)
+        self.keys.append((list(req_ids), list(steps)))
+        h = AsyncFake.Handle(out)
+        self.handles.append(h)
+        return h
+
+
+def _same_results(reqs, emit=False, **kw):
+    a = generate(FakeBackend(**kw), reqs, emit_stop=emit)
+    b_backend = AsyncFake(**kw)
+    b = generate(b_backend, reqs, emit_stop=emit)
+    assert [(x.tokens, x.reason) for x in a] == [(x.tokens, x.reason) for x in b]
+    assert not b_backend.seqs and b_backend.free == sorted(b_backend.free) and len(b_backend.free) == b_backend.max_slots
+    return a, b_backend
+
+
+def test_pipelined_loop_gives_the_same_results():
+    reqs = [Request([1, 2, 3], 5), Request([4], 2), Request([5, 6], 9), Request([7] * 10, 1)]
+    done, b = _same_results(reqs)
+    for r, d in zip(reqs, done):
+        assert (d.tokens, d.reason) == _expect(r.prompt, r.max_new_tokens)
+    # ends by count are known beforehand: no step runs for nothing
+    assert [len(s) for s in b.steps] == [4, 3, 2, 2, 2, 1, 1, 1, 1]
+    # the sampler's keys are (request, tokens generated before this one)
+    assert b.keys[0] == ([0, 1, 2, 3], [0, 0, 0, 0]) and b.keys[1] == ([0, 1, 2], [1, 1, 1])
+
+
+def test_pipelined_loop_finds_stop_tokens_a_step_late_and_drops_the_extra_token():
+    reqs = [Request([3, 4], 20, stop_ids=(28,)), Request([1], 6, stop_ids=(2,)), Request([9], 4)]
+    for emit in (False, True):
+        done, b = _same_results(reqs, emit)
+        assert done[0].reason == "stop" and done[1].reason == "stop" and done[2].reason == "length"
+    # request 1 stops at its 2nd token; the step after that still carried it (3 rows), the next did not
+    assert [len(s) for s in b.steps][:4] == [3, 3, 3, 2]
+
+
+def test_pipelined_loop_batches_zero_tokens_and_failures():
+    reqs = [Request([i + 1] * (10 + i), 3) for i in range(5)] + [Request([1, 2], 0)]
+    _same_results(reqs, n_pages=4, max_slots=2)
+
+    class Failing(AsyncFake):
+        def step_async(self, items, req_ids, steps):
+            if len(self.steps) == 2:
+                raise RuntimeError("boom")
+            return super().step_async(items, req_ids, steps)
+
+    f = Failing()
+    with pytest.raises(RuntimeError, match="boom"):
+        generate(f, [Request([1], 9), Request([2], 9)])
+    assert f.free == [0, 1, 2, 3] and not f.seqs
