@@ -212,3 +212,99 @@ def test_bad_schedules_are_refused():
         _two_layer_engine([(0, None), (1, 2), (0, None)])
     with pytest.raises(ConfigError, match="names layer"):
         _two_layer_engine([(0, None), (5, None)])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_embedding_and_head_parts(dtype):
+    from skyla_kernel_b200.config import PartSpec
+    from skyla_kernel_b200.parts import build_part, declare_part
+    rt = _rt(dtype)
+    emb_spec = PartSpec("token_embedding", {"vocab_size": 131, "hidden_size": 80}, {"weight": "e.weight"})
+    head_spec = PartSpec("linear_head", {"vocab_size": 131, "hidden_size": 80}, {"weight": "e.weight"})
+    w = _tensors(declare_part("embedding", emb_spec), 11, std=0.3)
+    assert declare_part("head", head_spec).keys() == w.keys()  # tied: one tensor, declared by both
+    emb, head = build_part("embedding", emb_spec, rt), build_part("head", head_spec, rt)
+    emb.load(w); head.load(w)
+    assert head.proj.weight.data_ptr() == emb.weight.data_ptr()  # and placed on the device once
+    toks = torch.tensor([130, 0, 7, 7], dtype=torch.int32, device=DEV)
+    x = torch.empty(4, 80, device=DEV)
+    emb.forward(None, toks, x)
+    assert torch.equal(x.cpu(), w["e.weight"].to(rt.act_dtype if dtype == "bfloat16" else torch.float32).float()[toks.long().cpu()]) \
+        or torch.allclose(x.cpu(), w["e.weight"][toks.long().cpu()])
+    h = torch.randn(4, 80, generator=torch.Generator().manual_seed(1)).to(DEV).to(rt.act_dtype)
+    logits = torch.empty(4, 131, device=DEV)
+    head.forward(None, h, logits)
+    torch.testing.assert_close(logits.cpu(), h.float().cpu() @ w["e.weight"].T, **_tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_block_alone(dtype):
+    """One pre-norm block from a layer spec: whole, then the same tokens in three steps."""
+    from helpers import assert_close
+    from skyla_kernel_b200.config import LayerSpec, PartSpec
+    from skyla_kernel_b200.engine.batch import StepItem
+    from skyla_kernel_b200.parts import EntryBinding, part_class
+    rt = _rt(dtype)
+    H, nq, nkv, hd, I = 96, 6, 2, 32, 256
+    norm = lambda n: PartSpec("rmsnorm", {"width": H, "eps": 2e-5}, {"weight": n})
+    spec = LayerSpec("l", "prenorm_residual", norm("l.n1"), _attention_spec(H, nq, nkv, hd), norm("l.n2"),
+                     PartSpec("swiglu", {"hidden_size": H, "intermediate_size": I},
+                              {k: f"l.{k}" for k in ("gate_proj", "up_proj", "down_proj")}))
+    cls = part_class("block", spec.block)
+    w = _tensors(cls.declare(spec), 21, std=0.08, sharp=2.0)
+    if dtype == "bfloat16":  # stored in 16 bits, as a served model would be: the tensor-core kernels run
+        w = {k: v.to(torch.bfloat16) for k, v in w.items()}
+    block = cls(spec, rt)
+    block.load(w)
+    wf = {k: v.float() for k, v in w.items()}
+    T = 90
+    x0 = torch.randn(T, H, generator=torch.Generator().manual_seed(3)) * 0.5
+    freqs, m = plain.rope_frequencies(hd, 10000.0)
+    ref = x0 + plain.attention(plain.rmsnorm(x0, wf["l.n1"], 2e-5), wf["a.q_proj"], wf["a.k_proj"], wf["a.v_proj"],
+                               wf["a.o_proj"], wf["a.q_norm"], wf["a.k_norm"], nq, nkv, hd, 1e-5, freqs, m, hd)
+    ref = ref + plain.swiglu(plain.rmsnorm(ref, wf["l.n2"], 2e-5), wf["l.gate_proj"], wf["l.up_proj"], wf["l.down_proj"])
+    cache, batcher = _ctx(rt, [block.mixer.cache_need()], [None], None)
+    slot = cache.alloc_slot()
+    got = []
+    for a, b in ((0, 70), (70, 71), (71, 90)):  # a prompt, one token (the few-token kernels), a second chunk
+        cache.reserve([(slot, b - a)])
+        ctx = batcher.build([StepItem(slot, [0] * (b - a), [])])
+        x = x0[a:b].clone().to(DEV)
+        block.forward(ctx, x, EntryBinding(0, True))
+        ctx.fold_pending(x)
+        cache.advance([(slot, b - a)])
+        got.append(x.cpu())
+    assert_close(torch.cat(got), ref, dtype, f"block alone {dtype}")
+
+
+def test_wide_groups_decode_through_the_prompt_kernel():
+    """More than 16 query heads per key/value head: the decode kernel's 16-row tile is too small,
+    the part must route single tokens through the prompt kernel (and get the same numbers)."""
+    from helpers import assert_close
+    from skyla_kernel_b200.engine.batch import StepItem
+    from skyla_kernel_b200.parts import EntryBinding, build_part, declare_part
+    rt = _rt("bfloat16")
+    hidden, nq, nkv, hd = 64, 34, 2, 16
+    spec = _attention_spec(hidden, nq, nkv, hd)
+    part = build_part("mixer", spec, rt)
+    assert part._fast == 1
+    w = {k: v.to(torch.bfloat16) for k, v in _tensors(declare_part("mixer", spec), 5, sharp=2.0).items()}
+    part.load(w)
+    wf = {k: v.float() for k, v in w.items()}
+    T = 80
+    h_all = torch.randn(T, hidden, generator=torch.Generator().manual_seed(6))
+    freqs, m = plain.rope_frequencies(hd, 10000.0)
+    ref = plain.attention(plain.bf16_round(h_all), wf["a.q_proj"], wf["a.k_proj"], wf["a.v_proj"], wf["a.o_proj"],
+                          wf["a.q_norm"], wf["a.k_norm"], nq, nkv, hd, 1e-5, freqs, m, hd)
+    cache, batcher = _ctx(rt, [part.cache_need()], [None], None)
+    slot = cache.alloc_slot()
+    got = []
+    for a, b in [(0, 66)] + [(i, i + 1) for i in range(66, T)]:
+        cache.reserve([(slot, b - a)])
+        ctx = batcher.build([StepItem(slot, [0] * (b - a), [])])
+        x = torch.zeros(b - a, hidden, device=DEV)
+        part.forward(ctx, h_all[a:b].to(DEV).to(torch.bfloat16), x, EntryBinding(0, True))
+        ctx.fold_pending(x)
+        cache.advance([(slot, b - a)])
+        got.append(x.cpu())
+    assert_close(torch.cat(got), ref, "bfloat16", "34 query heads over 2 key/value heads")
