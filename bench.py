@@ -25,6 +25,10 @@ sys.path.insert(0, ROOT)
 QWEN3_8B = dict(hidden_size=4096, num_hidden_layers=36, num_attention_heads=32, num_key_value_heads=8,
                 head_dim=128, intermediate_size=12288, vocab_size=151936, rope_theta=1000000.0,
                 rms_norm_eps=1e-6, max_position_embeddings=40960, tie_word_embeddings=False)
+# the other two shapes of the benchmark list, for --shape
+QWEN3_4B = dict(QWEN3_8B, hidden_size=2560, intermediate_size=9728, tie_word_embeddings=True)
+QWEN3_32B = dict(QWEN3_8B, num_hidden_layers=64, hidden_size=5120, num_attention_heads=64, intermediate_size=25600)
+SHAPES = {"8b": QWEN3_8B, "4b": QWEN3_4B, "32b": QWEN3_32B}
 PROMPT_LEN = 2048
 CONTEXT = 4096
 FALLBACK_HBM_GBS = 6650.0       # an earlier measurement on this pool, used when no peaks file exists
@@ -87,14 +91,14 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def build_model(layers: int, max_tokens: int, max_slots: int, seed: int = 0):
-    """The 8B-shaped model with seeded random weights drawn on the device."""
+def build_model(layers: int, max_tokens: int, max_slots: int, seed: int = 0, shape: dict = None):
+    """The 8B-shaped (or ``shape``d) model with seeded random weights drawn on the device."""
     import torch
     import skyla_kernel_b200 as skyla
     from skyla_kernel_b200.config import Qwen3Config
     from skyla_kernel_b200.engine import Engine, declared_tensors
     from skyla_kernel_b200.kernels import ops
-    cfg = Qwen3Config(**dict(QWEN3_8B, num_hidden_layers=layers))
+    cfg = Qwen3Config(**dict(shape or QWEN3_8B, num_hidden_layers=layers))
     decl = declared_tensors(cfg.to_spec())
     tensors = {}
     for i, (name, d) in enumerate(decl.items()):
@@ -149,7 +153,7 @@ def device_decode(model, batch, prompt_len, steps, warmup, vocab, sampler):
             start.record()
         if s >= warmup:
             kv_bytes += sum(eng.cache.length(sl) + 1 for sl in slots) * eng.cache.bytes_per_token()
-        logits = eng.step([StepItem(sl, [t], [0]) for sl, t in zip(slots, toks)])
+        logits = eng.step([StepItem(sl, [t], [0]) for sl, t in zip(slots, toks)], borrow=True)
         toks = torch.argmax(logits, dim=-1).tolist() if s < warmup else toks  # timed steps feed fixed tokens
     end.record()
     torch.cuda.synchronize()
@@ -217,7 +221,8 @@ def main() -> int:
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--batch", type=int, default=8)
-    ap.add_argument("--layers", type=int, default=QWEN3_8B["num_hidden_layers"])
+    ap.add_argument("--shape", choices=sorted(SHAPES), default="8b", help="layer sizes: Qwen3-8B (the default), -4B or -32B")
+    ap.add_argument("--layers", type=int, default=0, help="fewer layers than the shape has (0: all)")
     ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
     args = ap.parse_args()
 
@@ -230,13 +235,15 @@ def main() -> int:
         print(f"bench.py: this library runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
     args.warmup = max(args.warmup, 3)
+    shape = SHAPES[args.shape]
+    args.layers = args.layers or shape["num_hidden_layers"]
 
     import torch
     hbm_gbs, bf16_tflops, peak_kind = peaks()
     batches = [args.batch] + ([] if args.no_points else [b for b in (1, 64) if b != args.batch])
     max_tokens = max(batches) * (-(-CONTEXT // 64) * 64)
     t_build = time.time()
-    model, cfg = build_model(args.layers, max_tokens=max_tokens, max_slots=max(batches))
+    model, cfg = build_model(args.layers, max_tokens=max_tokens, max_slots=max(batches), shape=shape)
     print(f"[bench] model built in {time.time() - t_build:.1f} s: {args.layers} layers, "
           f"{model.engine.weight_bytes() / 1e9:.2f} GB of weights per step", file=sys.stderr, flush=True)
     V = cfg.vocab_size
@@ -262,13 +269,13 @@ def main() -> int:
     step_bytes = model.engine.weight_bytes() + main_run["kv_bytes_per_step"]
     achieved = step_bytes / (main_run["ms_per_step"] / 1e3) / 1e9
     line = {
-        "metric": "decode tokens/s, Qwen3-8B shape bf16, batch %d, 2048-token prompts" % args.batch,
+        "metric": "decode tokens/s, Qwen3-%s shape bf16, batch %d, 2048-token prompts" % (args.shape.upper(), args.batch),
         "value": main_run["tok_s"], "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": main_run["ms_per_step"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic: seeded random weights N(0,0.02), norms 1+N(0,0.02), uniform token ids",
         "config": {
-            "model": "Qwen3-8B shape", "global_batch": args.batch, "seq_len": CONTEXT, "parallelism": "single GPU",
-            "layers": args.layers, "layers_of_config": QWEN3_8B["num_hidden_layers"],
+            "model": "Qwen3-%s shape" % args.shape.upper(), "global_batch": args.batch, "seq_len": CONTEXT, "parallelism": "single GPU",
+            "layers": args.layers, "layers_of_config": shape["num_hidden_layers"],
             "hidden_size": cfg.hidden_size, "num_attention_heads": cfg.num_attention_heads,
             "num_key_value_heads": cfg.num_key_value_heads, "head_dim": cfg.head_dim,
             "intermediate_size": cfg.intermediate_size, "vocab_size": cfg.vocab_size,

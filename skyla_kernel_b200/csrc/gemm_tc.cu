@@ -35,6 +35,8 @@ enum Mode : int {
   kPartialF32 = 4,  // y[split, tok, f] = acc of this K split (float scratch)
   kAccumCluster = 5,  // y[tok, f] += sum over the K splits, which form one thread-block cluster: the
                       // splits' tiles meet in rank 0 through distributed shared memory, in rank order
+  kAccumLast = 6,     // y[tok, f] += sum over the K splits: every split leaves its tile in scratch and
+                      // counts itself in; the one that counts last adds them up in split order
 };
 
 constexpr int BM = 128;  // weight rows per tile
@@ -159,6 +161,8 @@ struct GemmArgs {
   int* error_flag;
   FoldJob fold;           // fold.x == nullptr: none
   NormSource norm;        // used by the NORMB kernels only
+  float* scratch;         // kAccumLast: [splits][M][N] tiles of the K splits
+  int* counters;          // kAccumLast: one per output tile, zero between launches
 };
 
 template <int BN, int MODE, bool NORMB>
@@ -169,6 +173,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   extern __shared__ uint8_t smem_raw[];
   __shared__ uint32_t tmem_base_slot;
   __shared__ volatile int abort_flag;
+  __shared__ int last_split;                 // kAccumLast: this block counted in last
   __shared__ float row_ssq[NORMB ? BN : 1];  // sum of squares of each token row over this block's K range
   __shared__ float warp_ssq[NORMB ? 4 : 1][NORMB ? BN : 1];
 
@@ -417,10 +422,44 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             } else if (MODE == kGluBf16) {
               const float up = __uint_as_float(u[j]) * inv;
               ((__nv_bfloat16*)a.y)[(int64_t)tok * a.ldy + f] = __float2bfloat16_rn(v / (1.0f + expf(-v)) * up);
+            } else if (MODE == kAccumLast) {
+              a.scratch[((int64_t)split * a.M + tok) * a.N + f] = v;
             } else {
               ((float*)a.y)[(int64_t)split * a.split_stride + (int64_t)tok * a.ldy + f] = v;
             }
           }
+        }
+      }
+    }
+    if (MODE == kAccumLast) {
+      // count this split in; whoever counts last has every split's tile in reach and adds them up
+      __threadfence();
+      asm volatile("barrier.sync 1, 128;" ::: "memory");
+      if (et == 0) {
+        const int tile_id = f_tile * (int)gridDim.y + t_tile;
+        const int before = atomicAdd(&a.counters[tile_id], 1);
+        last_split = before == (int)gridDim.z - 1;
+        if (last_split) a.counters[tile_id] = 0;  // ready for the next launch
+      }
+      asm volatile("barrier.sync 1, 128;" ::: "memory");
+      if (last_split && f < a.N && !abort_flag) {
+        __threadfence();
+        const int tok0 = t_tile * BN;
+        const int n_tok = min(BN, a.M - tok0);
+        for (int j0 = 0; j0 < n_tok; j0 += 8) {
+          float sum[8], old[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            sum[j] = 0.f;
+            old[j] = j0 + j < n_tok ? ((const float*)a.y)[(int64_t)(tok0 + j0 + j) * a.ldy + f] : 0.f;
+          }
+          for (int sp = 0; sp < (int)gridDim.z; ++sp)
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              if (j0 + j < n_tok) sum[j] += __ldcg(&a.scratch[((int64_t)sp * a.M + tok0 + j0 + j) * a.N + f]);
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            if (j0 + j < n_tok) ((float*)a.y)[(int64_t)(tok0 + j0 + j) * a.ldy + f] = old[j] + sum[j];
         }
       }
     }
@@ -773,12 +812,15 @@ extern "C" int skyla_gemm_tc_stages(int bn, int mode) {
 extern "C" int skyla_gemm_tc(const void* map_w, const void* map_x, void* y, int64_t ldy, int64_t split_stride,
                              int M, int N, int K, int bn, int mode, int splits, int* error_flag,
                              float* fold_x, int64_t fold_ldx, const float* fold_part, int fold_splits,
-                             int64_t fold_split_stride, int64_t fold_ldp, int fold_h, cudaStream_t stream) {
+                             int64_t fold_split_stride, int64_t fold_ldp, int fold_h, float* scratch, int* counters,
+                             cudaStream_t stream) {
   if (M <= 0 || N <= 0) return kOk;
   if (K <= 0 || K % 8) return fail(kBadArgument, "gemm_tc: K=%d must be a positive multiple of 8", K);
-  if (mode < 0 || mode > 5) return fail(kBadArgument, "gemm_tc: unknown epilogue %d", mode);
-  if (splits < 1 || (splits > 1 && mode != kPartialF32 && mode != kAccumCluster))
-    return fail(kBadArgument, "gemm_tc: %d K splits need the partial or the cluster epilogue", splits);
+  if (mode < 0 || mode > 6) return fail(kBadArgument, "gemm_tc: unknown epilogue %d", mode);
+  if (splits < 1 || (splits > 1 && mode != kPartialF32 && mode != kAccumCluster && mode != kAccumLast))
+    return fail(kBadArgument, "gemm_tc: %d K splits need the partial, the cluster or the last-arriver epilogue", splits);
+  if (mode == kAccumLast && (scratch == nullptr || counters == nullptr || bn > 64))
+    return fail(kBadArgument, "gemm_tc: the last-arriver epilogue needs scratch, counters and at most 64 tokens per tile");
   if (mode == kAccumCluster && (splits > 8 || bn > 64))
     return fail(kBadArgument, "gemm_tc: the cluster epilogue takes at most 8 K splits and 64 tokens per tile");
   const int total_kb = (K + BK - 1) / BK;
@@ -788,7 +830,8 @@ extern "C" int skyla_gemm_tc(const void* map_w, const void* map_x, void* y, int6
   memcpy(&mw, map_w, sizeof(mw));
   memcpy(&mx, map_x, sizeof(mx));
   GemmArgs a{y, ldy, split_stride, M, N, K, per, error_flag,
-             FoldJob{fold_x, fold_ldx, fold_part, fold_splits, fold_split_stride, fold_ldp, M, fold_h}, NormSource{}};
+             FoldJob{fold_x, fold_ldx, fold_part, fold_splits, fold_split_stride, fold_ldp, M, fold_h}, NormSource{},
+             scratch, counters};
   dim3 grid((N + BM - 1) / BM, (M + bn - 1) / bn, splits);
   if (grid.y > 65535 || grid.z > 65535) return fail(kBadArgument, "gemm_tc: grid too large");
   if (splits == 1 && mode <= kGluBf16 && ((mode == kGluBf16 && bn == 128) || (mode != kGluBf16 && bn == 256))) {
@@ -811,6 +854,12 @@ extern "C" int skyla_gemm_tc(const void* map_w, const void* map_x, void* y, int6
         case 16: return launch<16, kAccumCluster>(mw, mx, a, grid, stream);
         case 32: return launch<32, kAccumCluster>(mw, mx, a, grid, stream);
         default: return launch<64, kAccumCluster>(mw, mx, a, grid, stream);
+      }
+    case kAccumLast:
+      switch (bn) {
+        case 16: return launch<16, kAccumLast>(mw, mx, a, grid, stream);
+        case 32: return launch<32, kAccumLast>(mw, mx, a, grid, stream);
+        default: return launch<64, kAccumLast>(mw, mx, a, grid, stream);
       }
     default: return launch_bn<kPartialF32>(bn, mw, mx, a, grid, stream);
   }
@@ -840,7 +889,7 @@ extern "C" int skyla_gemm_tc_norm(const void* map_w, const float* x, int64_t ldx
   alignas(64) CUtensorMap mw;
   memcpy(&mw, map_w, sizeof(mw));
   GemmArgs a{y, ldy, split_stride, M, N, K, per, error_flag, FoldJob{},
-             NormSource{x, ldx, part, part ? n_part : 0, part_split_stride, ldp, w, eps, ssq_out}};
+             NormSource{x, ldx, part, part ? n_part : 0, part_split_stride, ldp, w, eps, ssq_out}, nullptr, nullptr};
   dim3 grid((N + BM - 1) / BM, (M + bn - 1) / bn, splits);
 #define SKYLA_NORM_LAUNCH(MODE_) return launch<16, MODE_, true>(mw, mw, a, grid, stream);
   switch (mode) {

@@ -191,7 +191,7 @@ def linear_plain(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, mode: int = 
 
 
 # ---------------------------------------------------------- tensor-core linear
-TC_STORE_BF16, TC_STORE_F32, TC_ACCUM_F32, TC_GLU_BF16, TC_PARTIAL_F32, TC_ACCUM_CLUSTER = 0, 1, 2, 3, 4, 5
+TC_STORE_BF16, TC_STORE_F32, TC_ACCUM_F32, TC_GLU_BF16, TC_PARTIAL_F32, TC_ACCUM_CLUSTER, TC_ACCUM_LAST = 0, 1, 2, 3, 4, 5, 6
 TC_TOKEN_TILES = (16, 32, 64, 128, 256)
 
 _ERROR_FLAGS = {}
@@ -276,14 +276,42 @@ def _fold_args(fold, m: int):
     return [_ptr(x), _rows(x, "x"), _ptr(part), part.shape[0], part.stride(0), part.stride(1), x.shape[1]]
 
 
+_TILE_COUNTERS = {}
+
+
+def tile_counters(device, n: int) -> torch.Tensor:
+    """Zeroed int32 counters, one per output tile, that the last-arriver epilogue leaves zeroed."""
+    dev = torch.device(device)
+    t = _TILE_COUNTERS.get(dev)
+    if t is None or t.numel() < n:
+        t = _TILE_COUNTERS[dev] = torch.zeros(max(4096, n), dtype=torch.int32, device=dev)
+    return t
+
+
+_ACCUM_SCRATCH = {}
+
+
+def accum_scratch(device, n: int) -> torch.Tensor:
+    """Float32 scratch for the K splits' tiles, shared by all products of a device (they run one
+    after another on one stream).  A larger request gets a new buffer; the old ones stay alive
+    for recorded launches that still point at them."""
+    dev = torch.device(device)
+    bufs = _ACCUM_SCRATCH.setdefault(dev, [])
+    if not bufs or bufs[-1].numel() < n:
+        bufs.append(torch.empty(max(n, 1 << 22), dtype=torch.float32, device=dev))
+    return bufs[-1]
+
+
 def gemm_tc(x: torch.Tensor, w_map: TensorMap, n_out: int, y: torch.Tensor, mode: int, splits: int = 1,
-            bn: Optional[int] = None, fold=None) -> torch.Tensor:
+            bn: Optional[int] = None, fold=None, scratch: Optional[torch.Tensor] = None) -> torch.Tensor:
     """y = x W^T on the tensor cores.  ``w_map`` has boxes of 128 rows (256 when gated).
 
     ``mode``: TC_STORE_BF16 / TC_STORE_F32 / TC_ACCUM_F32 / TC_GLU_BF16, or
     TC_PARTIAL_F32 with ``y`` of shape [splits, tokens, n_out] float32, or
     TC_ACCUM_CLUSTER: ``y += x W^T`` with the product cut into ``splits`` (at most 8) along K,
-    the splits running as one thread-block cluster and added up in a fixed order.
+    the splits running as one thread-block cluster and added up in a fixed order; or
+    TC_ACCUM_LAST: the same sum, but every split leaves its tile in ``scratch`` (float32,
+    ``splits * tokens * n_out`` elements) and the split that finishes last adds them up.
     ``fold=(r, partials)``: on the side, ``r += sum_s partials[s]`` (``r`` must not be an
     operand of this product).
     """
@@ -301,11 +329,17 @@ def gemm_tc(x: torch.Tensor, w_map: TensorMap, n_out: int, y: torch.Tensor, mode
             raise KernelError(f"gemm_tc: y {tuple(y.shape)} is not [{m}, {n_out}]")
         ldy, sstride = _rows(y, "y"), 0
     xm = activation_map(x, bn)
+    counters = None
+    if mode == TC_ACCUM_LAST:
+        _cuda(scratch)
+        if scratch is None or scratch.dtype != torch.float32 or scratch.numel() < splits * m * n_out:
+            raise KernelError("gemm_tc: the last-arriver epilogue needs float32 scratch of splits * tokens * n_out")
+        counters = tile_counters(x.device, -(-n_out // 128) * -(-m // bn))
     f = _fn("gemm_tc", "skyla_gemm_tc",
             [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int, c_int, c_int, c_int, c_int, c_int,
-             c_void_p, c_void_p, c_int64, c_void_p, c_int, c_int64, c_int64, c_int, c_void_p])
+             c_void_p, c_void_p, c_int64, c_void_p, c_int, c_int64, c_int64, c_int, c_void_p, c_void_p, c_void_p])
     _check("gemm_tc", f(w_map.buf, xm.buf, _ptr(y), ldy, sstride, m, n_out, k, bn, mode, splits,
-                        _ptr(error_flag(x.device)), *_fold_args(fold, m), _stream()))
+                        _ptr(error_flag(x.device)), *_fold_args(fold, m), _ptr(scratch), _ptr(counters), _stream()))
     return y
 
 

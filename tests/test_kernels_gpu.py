@@ -583,6 +583,26 @@ def test_gemm_tc_fold_side_job():
     assert (y.double().sum(0) - ref).abs().max().item() <= 2e-5 * ref.abs().max().item() + 1e-6
 
 
+@pytest.mark.parametrize("m,n,k,splits", [(8, 4096, 4096, 4), (1, 131, 520, 2), (33, 384, 12288, 12), (64, 200, 1032, 3)])
+def test_gemm_tc_last_arriver_accumulate(m, n, k, splits):
+    """K cut across blocks; each leaves its tile in scratch and the last one to finish adds them up."""
+    ops = _ops()
+    x = _rand(m, k, seed=95, dtype=torch.bfloat16)
+    w = _rand(n, k, seed=96, dtype=torch.bfloat16, scale=0.1)
+    acc0 = _rand(m, n, seed=97)
+    ref = acc0.double() + x.double() @ w.double().T
+    scratch = torch.full((splits * m * n,), float("nan"), device=DEV)
+    runs = []
+    for _ in range(3):  # the counters must come back to zero by themselves
+        acc = acc0.clone()
+        ops.gemm_tc(x, ops.TensorMap(w, 128), n, acc, ops.TC_ACCUM_LAST, splits=splits, scratch=scratch)
+        runs.append(acc)
+    assert (runs[0].double() - ref).abs().max().item() <= 3e-5 * ref.abs().max().item() + 1e-5
+    assert torch.equal(runs[0], runs[1]) and torch.equal(runs[0], runs[2])  # split order, whoever finishes last
+    assert int(ops.tile_counters(DEV, 1).abs().sum()) == 0
+    ops.check_device_errors(DEV)
+
+
 @pytest.mark.parametrize("m,n,k,splits", [(8, 4096, 4096, 4), (1, 131, 520, 2), (33, 384, 12288, 8), (64, 200, 1032, 3)])
 def test_gemm_tc_cluster_accumulate(m, n, k, splits):
     """K cut across a cluster of blocks; the splits meet in distributed shared memory."""
