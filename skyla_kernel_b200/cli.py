@@ -214,6 +214,9 @@ def main(argv=None) -> int:
     p.add_argument("--context", type=int, default=2048)
     p.add_argument("--reps", type=int, default=5)
     p.add_argument("--splits", type=int, default=0, help="attention-decode: override the number of context splits")
+    p.add_argument("--plan", default="", help="linear: rows,splits,kkb,kstack of the weight-streaming kernel instead of the part's choice")
+    p.add_argument("--rows-max", type=int, default=-1,
+                   help="linear: up to how many tokens the rows-per-SM kernel runs (default: the part's own limit)")
     p.set_defaults(fn=lambda a: __import__("skyla_kernel_b200.kernel_bench", fromlist=["main"]).main(a))
     p = sub.add_parser("replay", help="replay a token trace from standard input (bin/trace_run)")
     p.add_argument("--model", required=True)

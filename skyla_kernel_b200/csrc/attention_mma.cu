@@ -281,10 +281,11 @@ struct Stage {
   static constexpr int RS = Swz<HD>::RS;
   static constexpr int kElems = 2 * kPage * RS;        // K page then V page
   static constexpr int kPageBytes = kElems * (int)sizeof(bf16);
-  // decode: eight warps work on two pages at a time and the block is alone on its SM, so its
-  // own loads must cover the memory latency: as many pages as about 192 KB hold (even, 4..6)
-  static constexpr int kDecodeRaw = (192 * 1024) / kPageBytes;
-  static constexpr int kDecodeStages = kDecodeRaw >= 6 ? 6 : 4;
+  // decode: four warps work on one page at a time; two blocks share an SM, so that one block's
+  // start and end (no loads in flight) hide behind the other's loop: as many pages as about
+  // 96 KB hold (3..6)
+  static constexpr int kDecodeRaw = (96 * 1024) / kPageBytes;
+  static constexpr int kDecodeStages = kDecodeRaw >= 6 ? 6 : (kDecodeRaw < 3 ? 3 : kDecodeRaw);
   // prefill: compute-bound; three pages deep leaves room for two blocks per SM
   static constexpr int kPrefillStages = 3;
 };
@@ -330,19 +331,36 @@ struct DecodeArgs {
   // if set: the pages the longest sequence of this step needs; the splits then share those
   // evenly (pages_per_split is ignored), so a launch recorded once fits every context length
   const int32_t* pages_needed;
+  // if set: the split of a (sequence, kv head) that finishes last merges the splits itself and
+  // writes the heads' rows here; else attn_merge_kernel does that in a launch of its own
+  bf16* out; int64_t ldo;
+  long long* timeline;  // optional [blocks][8] clock readings of each block's phases (for tuning)
 };
 
-constexpr int kDecodeWarps = 8;
+// One counter per (sequence, kv head) for "who finishes last"; zero between launches (the last
+// arriver puts it back).  Shared by all launches of this module: they must not overlap, which
+// holds for launches on one stream.
+constexpr int kMergeCounters = 1 << 16;
+__device__ int g_merge_counters[kMergeCounters];
+
+constexpr int kDecodeWarps = 4;
 
 template <int HD>
-__global__ void __launch_bounds__(kDecodeWarps * 32) attn_decode_kernel(DecodeArgs a) {
+__global__ void __launch_bounds__(kDecodeWarps * 32, 2) attn_decode_kernel(DecodeArgs a) {
   using S = Shape<HD>;
   constexpr int RS = Stage<HD>::RS, kStages = Stage<HD>::kDecodeStages, NW = kDecodeWarps;
   extern __shared__ __align__(16) uint8_t smem_raw[];
   bf16* stages = reinterpret_cast<bf16*>(smem_raw);
   float* smem = reinterpret_cast<float*>(smem_raw);  // after the loop: [NW][16 rows][HD], [NW][16] m, [NW][16] l
+  __shared__ int merges;
+  long long* tl = a.timeline ? a.timeline + 8 * ((size_t)(blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) : nullptr;
+  if (tl && threadIdx.x == 0) { uint32_t smid; asm volatile("mov.u32 %0, %%smid;" : "=r"(smid)); tl[0] = smid; tl[1] = clock64(); }
   allow_dependents();
-  grid_dependency_wait();
+  // What the kernel before this one wrote: the unfinished q, k, v (fused) or q and the new
+  // token's row of the cache (not fused).  Positions, page lists and the pages of earlier
+  // tokens are older than that, so the fused kernel starts fetching pages right away.
+  const bool fused = a.prep.qkv != nullptr;
+  if (!fused) grid_dependency_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   const int kvh = blockIdx.x, b = blockIdx.y, split = blockIdx.z;
   const int G = a.nq / a.nkv;
@@ -353,36 +371,37 @@ __global__ void __launch_bounds__(kDecodeWarps * 32) attn_decode_kernel(DecodeAr
   const int page_begin = max(split * per_split, first / kPage);
   const int page_end = min((split + 1) * per_split, pos / kPage + 1);
   const int n_pages = max(0, page_end - page_begin);
-  const int n_pairs = (n_pages + 1) / 2;  // warps 0-3 take the first page of a pair, warps 4-7 the second
   const int32_t* seq_pages = a.kv.pages + (int64_t)b * a.kv.max_pages;
 
-  // half of the threads copy the first page of a pair, the other half the second
-  auto issue = [&](int pair) {
-    const int i = 2 * pair + (warp >> 2);
+  auto issue = [&](int i) {
     if (i < n_pages) {
       const size_t row0 = ((size_t)seq_pages[page_begin + i] * a.kv.nkv + kvh) * kPage;
-      stage_page<HD, 128>(stages + (size_t)(i % kStages) * Stage<HD>::kElems, a.kv.k + row0 * HD, a.kv.v + row0 * HD,
-                          threadIdx.x & 127);
+      stage_page<HD, NW * 32>(stages + (size_t)(i % kStages) * Stage<HD>::kElems, a.kv.k + row0 * HD, a.kv.v + row0 * HD,
+                              threadIdx.x);
     }
     cp_async_commit();  // an empty group keeps the count the same for every thread
   };
-  constexpr int kPairsAhead = kStages / 2 - 1;
+  constexpr int kAhead = kStages - 1;
 #pragma unroll
-  for (int i = 0; i < kPairsAhead; ++i) issue(i);
+  for (int i = 0; i < kAhead; ++i) issue(i);
+  if (fused) grid_dependency_wait();
+  if (tl && threadIdx.x == 0) tl[2] = clock64();
 
   uint32_t qa[S::NQ], qb[S::NQ];
 #pragma unroll
   for (int i = 0; i < S::NQ; ++i) qa[i] = qb[i] = 0u;
   // after the page stages: [G+2][HD] bf16 finished heads (q heads, then k, then v), [NW][HD] float scratch
   bf16* fresh = stages + (size_t)kStages * Stage<HD>::kElems;
-  const bool fused = a.prep.qkv != nullptr;
   const bool owner = fused && page_end == pos / kPage + 1 && n_pages > 0;  // this block's pages end at the new token
   if (fused) {
     float* u = reinterpret_cast<float*>(fresh + (size_t)(G + 2) * HD) + (size_t)warp * HD;
     const FusedPrep& p = a.prep;
-    float ssq = 0.f;
-    for (int sp = 0; sp < p.n_ssq; ++sp) ssq += p.ssq[(int64_t)sp * p.n_tokens + b];
-    const float row_scale = 1.0f / sqrtf(ssq / (float)p.norm_width + p.norm_eps);
+    float row_scale = 1.0f;  // no sums of squares: the rows came finished
+    if (p.ssq != nullptr) {
+      float ssq = 0.f;
+      for (int sp = 0; sp < p.n_ssq; ++sp) ssq += p.ssq[(int64_t)sp * p.n_tokens + b];
+      row_scale = 1.0f / sqrtf(ssq / (float)p.norm_width + p.norm_eps);
+    }
     for (int job = warp; job < G + 2; job += NW) {  // q heads of the group, then k, then v
       if (job >= G && !owner) continue;
       const bool is_q = job < G, is_k = job == G;
@@ -435,13 +454,14 @@ __global__ void __launch_bounds__(kDecodeWarps * 32) attn_decode_kernel(DecodeAr
 
   RowState<HD> st;
   st.init();
-  for (int pr = 0; pr < n_pairs; ++pr) {
-    issue(pr + kPairsAhead);
-    cp_async_wait<kPairsAhead>();
+  if (tl && threadIdx.x == 0) tl[3] = clock64();
+  for (int pg = 0; pg < n_pages; ++pg) {
+    issue(pg + kAhead);  // into the stage that the round before this one read
+    cp_async_wait<kAhead>();
     __syncthreads();
-    if (owner && pr == n_pairs - 1) {
+    if (owner && pg == n_pages - 1) {
       // the staged copy of the token's page was read before k and v were written: put them in
-      bf16* page = stages + (size_t)((n_pages - 1) % kStages) * Stage<HD>::kElems;
+      bf16* page = stages + (size_t)(pg % kStages) * Stage<HD>::kElems;
       const int r = pos % kPage;
       for (int c = threadIdx.x; c < 2 * (HD / 8); c += NW * 32) {
         const bool is_v = c >= HD / 8;
@@ -452,16 +472,16 @@ __global__ void __launch_bounds__(kDecodeWarps * 32) attn_decode_kernel(DecodeAr
       }
       __syncthreads();
     }
-    const int i = 2 * pr + (warp >> 2);
-    const bf16* sk = stages + (size_t)(i % kStages) * Stage<HD>::kElems;
-    const int key0 = (page_begin + i) * kPage + 16 * (warp & 3);  // this warp's 16 positions
-    if (i < n_pages && key0 <= pos && key0 + 15 >= first)
-      attend16<HD>(qa, qb, sk + 16 * (warp & 3) * RS, sk + (kPage + 16 * (warp & 3)) * RS, key0, first, hi0, first, hi1,
+    const bf16* sk = stages + (size_t)(pg % kStages) * Stage<HD>::kElems;
+    const int key0 = (page_begin + pg) * kPage + 16 * warp;  // this warp's 16 positions
+    if (key0 <= pos && key0 + 15 >= first)
+      attend16<HD>(qa, qb, sk + 16 * warp * RS, sk + (kPage + 16 * warp) * RS, key0, first, hi0, first, hi1,
                    scale_log2, st, g, t);
-    __syncthreads();  // the stages are refilled in the next round
+    __syncthreads();  // the stage is refilled in the next round
   }
   cp_async_wait<0>();
   __syncthreads();
+  if (tl && threadIdx.x == 0) tl[4] = clock64();
   // this thread's shares of the row sums -> whole rows
   st.l[0] += __shfl_xor_sync(0xffffffffu, st.l[0], 1); st.l[0] += __shfl_xor_sync(0xffffffffu, st.l[0], 2);
   st.l[1] += __shfl_xor_sync(0xffffffffu, st.l[1], 1); st.l[1] += __shfl_xor_sync(0xffffffffu, st.l[1], 2);
@@ -490,6 +510,55 @@ __global__ void __launch_bounds__(kDecodeWarps * 32) attn_decode_kernel(DecodeAr
     out[2 + c] = acc;
     if (c == 0) { out[0] = M; out[1] = L; }
   }
+  if (tl && threadIdx.x == 0) tl[5] = clock64();
+  if (a.out == nullptr) return;
+  // who finishes last of this (sequence, kv head) merges its splits, in the order of the splits
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int* counter = &g_merge_counters[b * a.nkv + kvh];
+    const int before = atomicAdd(counter, 1);
+    merges = before == a.n_splits - 1;
+    if (merges) *counter = 0;  // all are in: ready for the next launch
+  }
+  __syncthreads();
+  if (tl && threadIdx.x == 0) tl[6] = clock64();
+  if (!merges) return;
+  __threadfence();
+  // Every partial is a round trip to the L2, so they are asked for eight splits at a time, all
+  // at once, and then folded into the running (maximum, sum, row) in the order of the splits.
+  for (int idx = threadIdx.x; idx < G * HD; idx += NW * 32) {
+    const int r = idx / HD, c = idx % HD, h = kvh * G + r;
+    const float* p = a.part + ((size_t)b * a.nq + h) * a.n_splits * (HD + 2);
+    float M = -INFINITY, total = 0.f, o = 0.f;
+    for (int s0 = 0; s0 < a.n_splits; s0 += 8) {
+      float m8[8], l8[8], o8[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const bool in = s0 + j < a.n_splits;
+        const float* ps = p + (size_t)(s0 + j) * (HD + 2);
+        m8[j] = in ? __ldcg(ps) : -INFINITY;
+        l8[j] = in ? __ldcg(ps + 1) : 0.f;
+        o8[j] = in ? __ldcg(ps + 2 + c) : 0.f;
+      }
+      float Mn = M;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) Mn = fmaxf(Mn, m8[j]);
+      if (Mn == -INFINITY) continue;
+      const float keep = exp2f(M - Mn);  // 0 for the first chunk (M is -inf)
+      total *= keep;
+      o *= keep;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float f = exp2f(m8[j] - Mn);
+        total += f * l8[j];
+        o += f * o8[j];
+      }
+      M = Mn;
+    }
+    a.out[(int64_t)b * a.ldo + (int64_t)h * HD + c] = __float2bfloat16_rn(o / total);
+  }
+  if (tl && threadIdx.x == 0) tl[7] = clock64();
 }
 
 struct MergeArgs { const float* part; bf16* out; int64_t ldo; int nq, n_splits, hd; };
@@ -597,8 +666,12 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(PrefillArgs a) {
   store_rows_bf16<HD>(p0, p1, st.o, t, inv0, inv1);
 }
 
+long long* g_decode_timeline = nullptr;  // see skyla_attention_decode_timeline
+
 template <int HD>
-int launch_decode(const DecodeArgs& a, int n_seqs, cudaStream_t stream) {
+int launch_decode(const DecodeArgs& a_in, int n_seqs, cudaStream_t stream) {
+  DecodeArgs a = a_in;
+  a.timeline = g_decode_timeline;
   size_t smem = (size_t)(kDecodeWarps * 16 * HD + 2 * kDecodeWarps * 16) * sizeof(float);
   if (smem < (size_t)Stage<HD>::kDecodeStages * Stage<HD>::kPageBytes) smem = (size_t)Stage<HD>::kDecodeStages * Stage<HD>::kPageBytes;
   // after the stages: up to 18 finished heads (bf16) and a float scratch row per warp
@@ -648,6 +721,14 @@ int check_common(const void* q, int64_t ldq, int nq, int nkv, int page_size, con
 }
 }  // namespace
 
+// For tuning: from now on every decode launch leaves, per block, its SM's number and clock readings
+// (start, pages asked for and dependency met, loop start, loop end, partial written, counted in,
+// merged) in `buffer` (int64 [blocks][8]; null: stop).
+extern "C" int skyla_attention_decode_timeline(long long* buffer) {
+  g_decode_timeline = buffer;
+  return kOk;
+}
+
 // 1 when the tensor-core kernels take this head size.
 extern "C" int skyla_attention_mma_supports(int hd, int group) {
   return (hd % 16 == 0 && hd >= 16 && hd <= 128) ? (group <= 16 ? 2 : 1) : 0;
@@ -668,9 +749,11 @@ extern "C" int skyla_attention_decode(const void* q, int64_t ldq, void* out, int
     return fail(kBadArgument, "attention_decode: bad split of the context");
   DecodeArgs a{(const bf16*)q, ldq, part, n_splits, pages_per_split, nq, nkv,
                PagedKV{(const bf16*)k_pool, (const bf16*)v_pool, pages, max_pages, page_size, nkv}, tok_pos, scale, window,
-               FusedPrep{}, pages_needed};
+               FusedPrep{}, pages_needed, nullptr, 0, nullptr};
+  const bool merge_inside = (int64_t)n_seqs * nkv <= kMergeCounters;
+  if (merge_inside) { a.out = (bf16*)out; a.ldo = ldo; }
   SKYLA_HD_SWITCH(hd, { rc = launch_decode<HD>(a, n_seqs, stream); break; });
-  if (rc) return rc;
+  if (rc || merge_inside) return rc;
   MergeArgs m{part, (bf16*)out, ldo, nq, n_splits, hd};
   launch_overlapped(attn_merge_kernel, dim3(nq, n_seqs), dim3(128), 0, stream, m);
   return check_launch("attention_merge");
@@ -693,15 +776,17 @@ extern "C" int skyla_attention_decode_fused(
   if (nq / nkv > 16) return fail(kBadArgument, "attention_decode: groups of %d query heads exceed 16", nq / nkv);
   if (n_splits < 1 || pages_per_split < 1 || n_seqs > 65535 || n_splits > 65535)
     return fail(kBadArgument, "attention_decode: bad split of the context");
-  if (qkv == nullptr || ssq == nullptr || qkv_splits < 1 || n_ssq < 1 || norm_width <= 0 || n_rot < 0 || n_rot > hd || n_rot % 2)
+  if (qkv == nullptr || qkv_splits < 1 || (ssq != nullptr && (n_ssq < 1 || norm_width <= 0)) || n_rot < 0 || n_rot > hd || n_rot % 2)
     return fail(kBadArgument, "attention_decode_fused: bad description of the unfinished q, k and v");
   DecodeArgs a{nullptr, 0, part, n_splits, pages_per_split, nq, nkv,
                PagedKV{(const bf16*)k_pool, (const bf16*)v_pool, pages, max_pages, page_size, nkv}, tok_pos, scale, window,
                FusedPrep{qkv, qkv_splits, qkv_split_stride, ld, q_off, k_off, v_off, ssq, n_ssq, norm_width, norm_eps,
                          q_norm, k_norm, eps, cos_t, sin_t, cos_t ? n_rot : 0, (bf16*)k_pool, (bf16*)v_pool, n_seqs},
-               pages_needed};
+               pages_needed, nullptr, 0, nullptr};
+  const bool merge_inside = (int64_t)n_seqs * nkv <= kMergeCounters;
+  if (merge_inside) { a.out = (bf16*)out; a.ldo = ldo; }
   SKYLA_HD_SWITCH(hd, { rc = launch_decode<HD>(a, n_seqs, stream); break; });
-  if (rc) return rc;
+  if (rc || merge_inside) return rc;
   MergeArgs m{part, (bf16*)out, ldo, nq, n_splits, hd};
   launch_overlapped(attn_merge_kernel, dim3(nq, n_seqs), dim3(128), 0, stream, m);
   return check_launch("attention_merge");

@@ -31,7 +31,7 @@ enum Mode : int {
   kStoreBf16 = 0,   // y[tok, f] = acc                     (bfloat16)
   kStoreF32 = 1,    // y[tok, f] = acc                     (float)
   kAccumF32 = 2,    // y[tok, f] += acc                    (float: the residual sum)
-  kGluBf16 = 3,     // y[tok, f] = silu(gate) * up         (bfloat16; W rows in groups of 128 gate, 128 up)
+  kGluBf16 = 3,     // y[tok, f] = silu(gate) * up         (bfloat16; W = N gate rows, then the N up rows)
   kPartialF32 = 4,  // y[split, tok, f] = acc of this K split (float scratch)
   kAccumCluster = 5,  // y[tok, f] += sum over the K splits, which form one thread-block cluster: the
                       // splits' tiles meet in rank 0 through distributed shared memory, in rank order
@@ -152,6 +152,14 @@ struct NormSource {
   const float* w; float eps; float* ssq_out;
 };
 
+// "Norm ahead": the product that writes the residual stream last (y += x W^T) also leaves, for the
+// RMSNorm that reads it next, the rows times that norm's weight in bfloat16 (the next product's
+// token operand) and each block's share of the rows' sums of squares (ssq_part[block * M + tok]).
+struct NormAhead { const float* w; __nv_bfloat16* xw; int64_t ldxw; float* ssq_part; };
+// The other side: the token operand came without its norm's scalar; the rows' sums of squares lie in
+// `n_parts` shares (ssq_part[p * M + tok]) and the result is multiplied by 1/sqrt(sum / width + eps).
+struct ScaleIn { const float* ssq_part; int n_parts; float eps; int width; };
+
 struct GemmArgs {
   void* y;
   int64_t ldy;            // elements between token rows of y
@@ -163,6 +171,8 @@ struct GemmArgs {
   NormSource norm;        // used by the NORMB kernels only
   float* scratch;         // kAccumLast: [splits][M][N] tiles of the K splits
   int* counters;          // kAccumLast: one per output tile, zero between launches
+  NormAhead ahead;        // weight-streaming kernel, accumulate epilogue: ahead.xw == nullptr: none
+  ScaleIn scale;          // weight-streaming kernel: scale.ssq_part == nullptr: none
 };
 
 template <int BN, int MODE, bool NORMB>
@@ -220,7 +230,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       constexpr uint32_t kTxBytes = NORMB ? C::kABytes : C::kStageBytes;
       for (int kb = 0; kb < n_pre; ++kb) {
         mbar_expect_tx(full_bar(kb), kTxBytes);
-        tma_load_2d(base + kb * C::kStageBytes, &map_w, full_bar(kb), (kb0 + kb) * BK, f_tile * BM * C::kATiles);
+        tma_load_2d(base + kb * C::kStageBytes, &map_w, full_bar(kb), (kb0 + kb) * BK, f_tile * BM);
+        if (MODE == kGluBf16)  // the up rows of the same outputs follow the a.N gate rows
+          tma_load_2d(base + kb * C::kStageBytes + BM * BK * 2, &map_w, full_bar(kb), (kb0 + kb) * BK, a.N + f_tile * BM);
         armed |= 1u << kb;
       }
       if (!NORMB) {
@@ -235,7 +247,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         if (!mbar_wait(empty_bar(s), phase ^ 1, &abort_flag, a.error_flag, 1)) break;
         const uint32_t sa = base + s * C::kStageBytes, sb = sa + C::kABytes;
         mbar_expect_tx(full_bar(s), kTxBytes);
-        tma_load_2d(sa, &map_w, full_bar(s), (kb0 + kb) * BK, f_tile * BM * C::kATiles);
+        tma_load_2d(sa, &map_w, full_bar(s), (kb0 + kb) * BK, f_tile * BM);
+        if (MODE == kGluBf16) tma_load_2d(sa + BM * BK * 2, &map_w, full_bar(s), (kb0 + kb) * BK, a.N + f_tile * BM);
         if (!NORMB) tma_load_2d(sb, &map_x, full_bar(s), (kb0 + kb) * BK, t_tile * BN);
         armed |= 1u << s;
         armed_parity = (armed_parity & ~(1u << s)) | (phase << s);
@@ -520,6 +533,570 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   }
 }
 
+// ------------------------------------------------------------------ few tokens: weight streaming
+// A few decoded tokens: the product has to stream the weight once, at the memory's speed, and
+// little else.  What that takes on this machine (all measured):
+//   * a TMA tensor load occupies the SM's TMA unit for about 0.16 us whatever its size, so a
+//     box has to carry tens of KB: one box brings `kkb` K blocks of a tile (a 3-D tensor map
+//     whose outermost dimension is the K block), and so does the token operand's box;
+//   * a tcgen05.mma of 16 tokens takes about 50 cycles whatever its shape, so an instruction
+//     should cover 64 or more useful weight rows;
+//   * every SM has to stream.  The tile height R (a multiple of 8, at most 128) and the number
+//     of K splits are chosen by the host so that tiles x splits fills the SMs.  The MMA still
+//     reads 128 rows: the rows past R hold whatever lies behind the tile in shared memory and
+//     feed accumulator lanes that nobody reads.
+//   * stacking: with tiles of R <= 64 rows the MMA's 128 rows take `kstack` = 128 / R K blocks
+//     at once: the box of kstack K blocks lies in shared memory as kstack tiles of R rows one
+//     after the other, which is a 128-row operand whose row group q holds K block q; the token
+//     operand's box likewise is a (kstack x BN)-row operand.  One MMA then computes all pairs
+//     (row group q, token group q'); the kstack diagonal blocks are the wanted partial products
+//     (the others are never read), and the epilogue adds them up through shared memory.  So a
+//     block covers its whole K with K/64/kstack x 4 instructions and needs no K split.
+// K splits (without stacking) form a thread-block cluster: each pushes its tile into the landing
+// zones of the blocks that own the token columns, one cluster barrier, the owners add up in rank order.
+constexpr int kRowsMaxStages = 24;
+// Ring + landing zone + barriers of one block: one block per SM.  (Half of it, so that the next
+// product's blocks move in beside this one's and fill their rings early, measured slower for every
+// product of the 8B shape: 27.2 against 22.3 us for the down product, 38.4 against 34.4 gated.)
+// Asking the L2 for the next product's first boxes (cp.async.bulk.prefetch.tensor) once a block's own
+// loads are issued also measured slower: a decode step of the 8B shape took 4.09, 4.18, 4.25 ms with
+// 64, 128, 256 KB per block against 4.07 without.
+constexpr int kRowsSmemBytes = 212 * 1024;
+constexpr int kRowsMaxSplits = 8;
+
+struct RowsArgs {
+  int rows_per_block;   // R
+  int n_stages;         // ring depth chosen by the host
+  int kkb;              // K blocks per stage and per TMA box; 1: the tensor maps are 2-D
+  int kstack;           // K blocks that one MMA takes at once, stacked along its rows (see below); divides kkb
+  int tmem_cols;        // accumulator columns to allocate: a power of two >= 32
+  int landing_bytes;    // behind the ring: the cluster's landing zone, at least the 16 KB the MMA may over-read
+  long long* timeline;  // optional [blocks][12]: SM id and clock64 at the phases of each block (for tuning)
+};
+
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y, int z) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y), "r"(z) : "memory");
+}
+
+template <int BN, int MODE, bool NORMB>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tc_rows_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                    const GemmArgs a, const RowsArgs ra) {
+  constexpr int kATiles = MODE == kGluBf16 ? 2 : 1;
+  constexpr int kBBytes = BN * BK * 2;
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ volatile int abort_flag;
+  __shared__ float row_ssq[BN];  // the rows' sums of squares: over this block's K range (NORMB), or handed in
+  __shared__ float warp_ssq[NORMB ? 4 : 1][NORMB ? BN : 1];
+  __shared__ float rank_ssq[NORMB ? kRowsMaxSplits : 1][NORMB ? BN : 1];  // every split's share, pushed by the splits
+
+  const int n_stages = ra.n_stages, kkb = ra.kkb;
+  long long* tl = ra.timeline ? ra.timeline + 12 * ((size_t)blockIdx.z * gridDim.x + blockIdx.x) : nullptr;
+  if (tl && threadIdx.x == 0) {
+    uint32_t smid;
+    asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+    tl[0] = smid;
+    tl[1] = clock64();
+    unsigned long long g;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g));
+    tl[11] = (long long)g;
+  }
+  const int a_tile = ra.rows_per_block * BK * 2;  // R rows of 128 bytes: a multiple of 1024
+  const uint32_t stage_bytes = (uint32_t)(kkb * (kATiles * a_tile + kBBytes));
+  const uint32_t bars = (smem_u32(smem_raw) + 15u) & ~15u;                       // barriers first
+  const uint32_t base = (bars + 8u * (2 * kRowsMaxStages + 1) + 1023u) & ~1023u;  // then the ring
+  const uint32_t landing = base + (uint32_t)n_stages * stage_bytes;               // then the landing zone
+  auto full_bar = [&](int s) { return bars + 8u * s; };
+  auto empty_bar = [&](int s) { return bars + 8u * (kRowsMaxStages + s); };
+  const uint32_t tmem_full_bar = bars + 8u * (2 * kRowsMaxStages);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int f0 = blockIdx.x * ra.rows_per_block;  // first output feature of this block
+  const int split = blockIdx.z;
+  const bool clustered = gridDim.z > 1;
+  const int total_kb = (a.K + BK - 1) / BK;
+  const int kb0 = split * a.k_blocks_per_split;
+  const int n_kb = max(0, min(a.k_blocks_per_split, total_kb - kb0));
+  const int n_st = (n_kb + kkb - 1) / kkb;  // stages' worth of K blocks
+  // every block walks its stages from a start of its own (and wraps): at any moment the blocks
+  // read different lines of the token rows, which they all share, not all the same L2 line
+  const int st_start = n_st > 0 ? (int)(((unsigned)blockIdx.x * 5u) % (unsigned)n_st) : 0;
+  auto st_of = [&](int i) { int t = i + st_start; return t >= n_st ? t - n_st : t; };
+  const uint32_t tx_bytes = (uint32_t)(kkb * kATiles * a_tile) + (NORMB ? 0u : (uint32_t)(kkb * kBBytes));
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    for (int s = 0; s < n_stages; ++s) {
+      mbar_init(full_bar(s), NORMB ? 1 + kkb : 1);  // the loader, and with NORMB one arrival per token tile made
+      mbar_init(empty_bar(s), 1);
+    }
+    mbar_init(tmem_full_bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                 ::"r"(smem_u32(&tmem_base_slot)), "r"((uint32_t)ra.tmem_cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = tmem_base_slot;
+  allow_dependents();
+  if (tl && threadIdx.x == 0) tl[2] = clock64();
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      auto load_weights = [&](int i, int s) {
+        const uint32_t sa = base + s * stage_bytes;
+        const int kb = kb0 + st_of(i) * kkb;
+        mbar_expect_tx(full_bar(s), tx_bytes);
+        if (kkb == 1) {
+          tma_load_2d(sa, &map_w, full_bar(s), kb * BK, f0);
+          if (MODE == kGluBf16) tma_load_2d(sa + a_tile, &map_w, full_bar(s), kb * BK, a.N + f0);
+        } else {
+          tma_load_3d(sa, &map_w, full_bar(s), 0, f0, kb);
+          if (MODE == kGluBf16) tma_load_3d(sa + kkb * a_tile, &map_w, full_bar(s), 0, a.N + f0, kb);
+        }
+      };
+      auto load_tokens = [&](int i, int s) {
+        const uint32_t sb = base + s * stage_bytes + kkb * kATiles * a_tile;
+        const int kb = kb0 + st_of(i) * kkb;
+        if (kkb == 1) tma_load_2d(sb, &map_x, full_bar(s), kb * BK, 0);
+        else tma_load_3d(sb, &map_x, full_bar(s), 0, 0, kb);
+      };
+      // weights are written by no kernel: fill the ring before waiting for the predecessor
+      const int n_pre = min(n_st, n_stages);
+      for (int i = 0; i < n_pre; ++i) load_weights(i, i);
+      if (!NORMB) {
+        grid_dependency_wait();
+        if (tl) tl[3] = clock64();
+        for (int i = 0; i < n_pre; ++i) load_tokens(i, i);
+      }
+      int i = n_pre, s = 0;
+      uint32_t phase = 1;
+      for (; i < n_st; ++i) {
+        if (!mbar_wait(empty_bar(s), phase ^ 1, &abort_flag, a.error_flag, 1)) break;
+        load_weights(i, s);
+        if (!NORMB) load_tokens(i, s);
+        if (++s == n_stages) { s = 0; phase ^= 1; }
+      }
+      if (i < n_st) {  // gave up: let the loads in flight land before the block's memory goes away
+        for (int j = max(0, i - n_stages); j < i; ++j) {
+          const long long t0 = clock64();
+          while (!mbar_try_wait(full_bar(j % n_stages), (j / n_stages) & 1) && clock64() - t0 < kWaitCycles) {}
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const int kstack = ra.kstack;
+      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)((kstack * BN) >> 3) << 17) |
+                             ((uint32_t)(BM >> 4) << 24);
+      int s = 0;
+      uint32_t phase = 0, started = 0;
+      for (int i = 0; i < n_st; ++i) {
+        if (!mbar_wait(full_bar(s), phase, &abort_flag, a.error_flag, 2)) break;
+        if (tl && i == 0) tl[4] = clock64();
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t sa = base + s * stage_bytes, sb = sa + kkb * kATiles * a_tile;
+        // K blocks past the end of K hold zeros (the loads fill them, the norm's producers write them)
+        for (int j = 0; j < kkb; j += kstack) {
+          const uint64_t da = umma_desc(sa + j * a_tile), db = umma_desc(sb + j * kBBytes);
+          const uint64_t du = umma_desc(sa + (kkb + j) * a_tile);
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            umma_bf16(tmem_base, da + 2 * k, db + 2 * k, idesc, started);
+            if (MODE == kGluBf16) umma_bf16(tmem_base + BN, du + 2 * k, db + 2 * k, idesc, started);
+            started = 1u;
+          }
+        }
+        umma_commit(empty_bar(s));
+        if (++s == n_stages) { s = 0; phase ^= 1; }
+      }
+      umma_commit(tmem_full_bar);
+      if (tl) tl[5] = clock64();
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue warps
+    grid_dependency_wait();
+    const int quad = warp & 3;
+    const int r_local = quad * 32 + lane;  // row of the tile that this thread's TMEM lane holds
+    const int f = f0 + r_local;
+    const bool mine = r_local < ra.rows_per_block && f < a.N;
+    const int et = threadIdx.x - 64;
+    uint32_t my_rank = 0, n_ranks = 1;
+    if (clustered) {
+      asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(my_rank));
+      asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(n_ranks));
+    }
+    if (NORMB) {
+      static_assert(!NORMB || BN == 16, "the in-kernel norm is written for token tiles of 16");
+      // Warp w makes the tiles j with j % 4 == w of every stage, so it visits every ring slot in
+      // every round and is never two phases ahead of a slot's barrier.  The rows of the next
+      // tile are fetched before the current one is written: the fetch does not depend on the ring.
+      const int ew = warp - 2, chunk = lane & 7;
+      float ssq[4] = {0.f, 0.f, 0.f, 0.f};
+      struct Rows { float4 v0[4], v1[4], w0, w1; };
+      auto fetch = [&](int unit, Rows& t) {  // unit = stage index * kkb + tile of the stage
+        const int i = unit / kkb, j = unit - i * kkb;
+        const int k = (kb0 + st_of(i) * kkb + j) * BK + chunk * 8;  // past K: a tile of zeros
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const int tok = (lane >> 3) + 4 * q;
+          t.v0[q] = t.v1[q] = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (tok < a.M && k < a.K) {
+            const float* xp = a.norm.x + (int64_t)tok * a.norm.ldx + k;
+            t.v0[q] = *reinterpret_cast<const float4*>(xp);
+            t.v1[q] = *reinterpret_cast<const float4*>(xp + 4);
+            for (int sp = 0; sp < a.norm.n_splits; ++sp) {
+              const float* pp = a.norm.part + (int64_t)sp * a.norm.split_stride + (int64_t)tok * a.norm.ldp + k;
+              const float4 p0 = *reinterpret_cast<const float4*>(pp), p1 = *reinterpret_cast<const float4*>(pp + 4);
+              t.v0[q].x += p0.x; t.v0[q].y += p0.y; t.v0[q].z += p0.z; t.v0[q].w += p0.w;
+              t.v1[q].x += p1.x; t.v1[q].y += p1.y; t.v1[q].z += p1.z; t.v1[q].w += p1.w;
+            }
+          }
+        }
+        t.w0 = t.w1 = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (k < a.K) {
+          t.w0 = *reinterpret_cast<const float4*>(a.norm.w + k);
+          t.w1 = *reinterpret_cast<const float4*>(a.norm.w + k + 4);
+        }
+      };
+      // this warp's units in order: (stage 0, tiles ew, ew+4, ..), (stage 1, ..), ..
+      auto next_unit = [&](int unit) {
+        int i = unit / kkb, j = unit - i * kkb + 4;
+        if (j >= kkb) { ++i; j = ew; }
+        return i * kkb + j;
+      };
+      const int end_unit = n_st * kkb;
+      int unit = ew < kkb ? ew : end_unit;
+      Rows cur, nxt;
+      if (unit < end_unit) fetch(unit, cur);
+      while (unit < end_unit) {
+        const int following = next_unit(unit);
+        if (following < end_unit) fetch(following, nxt);
+        const int i = unit / kkb, j = unit - i * kkb;
+        const int s = i % n_stages;
+        const uint32_t phase = (i / n_stages) & 1;
+        if (!mbar_wait(empty_bar(s), phase ^ 1, &abort_flag, a.error_flag, 4)) break;
+        uint8_t* sb = smem_raw + (base - smem_u32(smem_raw)) + s * stage_bytes + kkb * kATiles * a_tile + j * kBBytes;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const int r = (lane >> 3) + 4 * q;
+          const float4 v0 = cur.v0[q], v1 = cur.v1[q];
+          ssq[q] += v0.x * v0.x + v0.y * v0.y + v0.z * v0.z + v0.w * v0.w +
+                    v1.x * v1.x + v1.y * v1.y + v1.z * v1.z + v1.w * v1.w;
+          __nv_bfloat162 b0 = __floats2bfloat162_rn(v0.x * cur.w0.x, v0.y * cur.w0.y);
+          __nv_bfloat162 b1 = __floats2bfloat162_rn(v0.z * cur.w0.z, v0.w * cur.w0.w);
+          __nv_bfloat162 b2 = __floats2bfloat162_rn(v1.x * cur.w1.x, v1.y * cur.w1.y);
+          __nv_bfloat162 b3 = __floats2bfloat162_rn(v1.z * cur.w1.z, v1.w * cur.w1.w);
+          *reinterpret_cast<uint4*>(sb + r * 128 + ((chunk ^ (r & 7)) << 4)) =
+              make_uint4(*reinterpret_cast<uint32_t*>(&b0), *reinterpret_cast<uint32_t*>(&b1),
+                         *reinterpret_cast<uint32_t*>(&b2), *reinterpret_cast<uint32_t*>(&b3));
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) mbar_arrive(full_bar(s));  // one arrival per tile of the stage
+        cur = nxt;
+        unit = following;
+      }
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        float v = ssq[q];
+        v += __shfl_xor_sync(0xffffffffu, v, 1);
+        v += __shfl_xor_sync(0xffffffffu, v, 2);
+        v += __shfl_xor_sync(0xffffffffu, v, 4);
+        if (chunk == 0) warp_ssq[ew][(lane >> 3) + 4 * q] = v;
+      }
+      asm volatile("barrier.sync 1, 128;" ::: "memory");
+      if (et < BN) {
+        const float v = warp_ssq[0][et] + warp_ssq[1][et] + warp_ssq[2][et] + warp_ssq[3][et];
+        row_ssq[et] = v;
+        if (clustered) {  // every split needs every split's share
+          for (uint32_t r = 0; r < n_ranks; ++r) {
+            uint32_t remote;
+            asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(&rank_ssq[my_rank][et])), "r"(r));
+            asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
+          }
+        }
+      }
+      asm volatile("barrier.sync 1, 128;" ::: "memory");
+    }
+    const bool scale_in = !NORMB && a.scale.ssq_part != nullptr;
+    if (scale_in) {  // while the main loop runs: add up the shares of the rows' sums of squares
+      if (et < BN) {
+        float v = 0.f;
+        if (et < a.M)
+          for (int p = 0; p < a.scale.n_parts; ++p) v += a.scale.ssq_part[(int64_t)p * a.M + et];
+        row_ssq[et] = v;
+      }
+      asm volatile("barrier.sync 1, 128;" ::: "memory");
+    }
+    const bool scaled = NORMB || scale_in;
+    const float norm_width = NORMB ? (float)a.K : (float)a.scale.width;
+    const float norm_eps = NORMB ? a.norm.eps : a.scale.eps;
+    const bool ahead = MODE == kAccumF32 && a.ahead.xw != nullptr && !clustered;
+    const int kstack = ra.kstack, R = ra.rows_per_block;
+    float* red = reinterpret_cast<float*>(smem_raw + (landing - smem_u32(smem_raw)));
+    float* sqbuf = red + (kstack > 1 ? kstack * BN * R : 0);  // [tok][row of the tile]: squares of the new x
+    // the old values of y do not depend on the product: fetch them while the main loop runs
+    float old_pre[4] = {0.f, 0.f, 0.f, 0.f}, wn_pre[4] = {0.f, 0.f, 0.f, 0.f}, old16[16];
+    if (MODE == kAccumF32 && kstack > 1) {
+#pragma unroll
+      for (int n = 0; n < 4; ++n) {
+        const int idx = et + 128 * n;
+        const int tok = idx / R, ff = f0 + idx - tok * R;
+        if (idx < a.M * R && ff < a.N) {
+          old_pre[n] = ((const float*)a.y)[(int64_t)tok * a.ldy + ff];
+          if (ahead) wn_pre[n] = a.ahead.w[ff];
+        }
+      }
+    }
+    if (MODE == kAccumF32 && kstack == 1 && !clustered && mine) {
+#pragma unroll
+      for (int j = 0; j < 16; ++j) old16[j] = j < a.M ? ((const float*)a.y)[(int64_t)j * a.ldy + f] : 0.f;
+    }
+    const bool ok = n_kb > 0 && mbar_wait(tmem_full_bar, 0, &abort_flag, a.error_flag, 3);
+    if (ok) {
+      if (tl && threadIdx.x == 64) tl[6] = clock64();
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    }
+    const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16);
+    if (kstack > 1) {
+      // lane L of the accumulator is row L % R of K-block group L / R; its partial products are the
+      // columns [q*BN, q*BN + BN) of its own group q.  red[(q*BN + tok)*R + r], then a sum over q.
+      if (ok) {
+        const int L = quad * 32 + lane;
+        const int q_mine = L / R, r_mine = L - q_mine * R;
+        const int q_lo = (quad * 32) / R, q_hi = min(kstack - 1, (quad * 32 + 31) / R);  // uniform for the warp
+        for (int q = q_lo; q <= q_hi; ++q) {
+#pragma unroll 1
+          for (int c0 = 0; c0 < BN; c0 += 16) {
+            if (c0 >= a.M) break;
+            uint32_t r[16];
+            tmem_ld16(taddr + q * BN + c0, r);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            if (q == q_mine) {
+#pragma unroll
+              for (int j = 0; j < 16; ++j)
+                if (c0 + j < a.M) red[(q * BN + c0 + j) * R + r_mine] = __uint_as_float(r[j]);
+            }
+          }
+        }
+      }
+      asm volatile("barrier.sync 1, 128;" ::: "memory");
+      for (int idx = et; ok && idx < a.M * R; idx += 128) {
+        const int tok = idx / R, rr = idx - tok * R;
+        const int ff = f0 + rr;
+        if (ff >= a.N) {
+          if (ahead) sqbuf[idx] = 0.f;
+          continue;
+        }
+        float v = 0.f;
+        for (int q = 0; q < kstack; ++q) v += red[(q * BN + tok) * R + rr];
+        if (scaled) v *= 1.0f / sqrtf(row_ssq[tok] / norm_width + norm_eps);
+        if (MODE == kStoreBf16) ((__nv_bfloat16*)a.y)[(int64_t)tok * a.ldy + ff] = __float2bfloat16_rn(v);
+        else if (MODE == kStoreF32) ((float*)a.y)[(int64_t)tok * a.ldy + ff] = v;
+        else if (MODE == kAccumF32) {
+          float* p = (float*)a.y + (int64_t)tok * a.ldy + ff;
+          const int n = (idx - et) >> 7;  // which of this thread's items
+          const float nv = (n == 0 ? old_pre[0] : n == 1 ? old_pre[1] : n == 2 ? old_pre[2] : n == 3 ? old_pre[3] : *p) + v;
+          *p = nv;
+          if (ahead) {
+            const float wn = n == 0 ? wn_pre[0] : n == 1 ? wn_pre[1] : n == 2 ? wn_pre[2] : n == 3 ? wn_pre[3] : a.ahead.w[ff];
+            a.ahead.xw[(int64_t)tok * a.ahead.ldxw + ff] = __float2bfloat16_rn(nv * wn);
+            sqbuf[idx] = nv * nv;
+          }
+        }
+      }
+    }
+    const bool warp_has_rows = ok && kstack == 1 && quad * 32 < R;  // uniform for the warp
+#pragma unroll 1
+    for (int c0 = 0; c0 < BN && warp_has_rows; c0 += 16) {
+      if (c0 >= a.M) break;
+      uint32_t r[16], u[16];
+      tmem_ld16(taddr + c0, r);
+      if (MODE == kGluBf16) tmem_ld16(taddr + BN + c0, u);
+      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      if (!mine) {
+        if (ahead && r_local < R)
+          for (int j = 0; j < 16 && c0 + j < a.M; ++j) sqbuf[(c0 + j) * R + r_local] = 0.f;
+        continue;
+      }
+      if (clustered) {
+        // token column c belongs to rank c % n_ranks: push this split's value into that
+        // block's landing zone, slot [my rank][c / n_ranks][row of the tile]
+        const uint32_t per_rank = ((uint32_t)BN + n_ranks - 1) / n_ranks;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const uint32_t col = (uint32_t)(c0 + j);
+          if ((int)col >= a.M) break;
+          const uint32_t local = landing + 4u * ((my_rank * per_rank + col / n_ranks) * BM + (uint32_t)r_local);
+          uint32_t remote;
+          asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(col % n_ranks));
+          asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "r"(r[j]) : "memory");
+        }
+        continue;
+      }
+      float old[16];
+      if (MODE == kAccumF32) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j)
+          old[j] = c0 == 0 ? old16[j] : (c0 + j < a.M ? ((const float*)a.y)[(int64_t)(c0 + j) * a.ldy + f] : 0.f);
+      }
+      const float w_next = ahead ? a.ahead.w[f] : 0.f;
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        const int tok = c0 + j;
+        if (tok >= a.M) break;
+        float v = __uint_as_float(r[j]);
+        float inv = 1.f;
+        if (scaled) {
+          inv = 1.0f / sqrtf(row_ssq[tok] / norm_width + norm_eps);
+          v *= inv;
+        }
+        if (MODE == kStoreBf16) {
+          ((__nv_bfloat16*)a.y)[(int64_t)tok * a.ldy + f] = __float2bfloat16_rn(v);
+        } else if (MODE == kStoreF32) {
+          ((float*)a.y)[(int64_t)tok * a.ldy + f] = v;
+        } else if (MODE == kAccumF32) {
+          const float nv = old[j] + v;
+          ((float*)a.y)[(int64_t)tok * a.ldy + f] = nv;
+          if (ahead) {
+            a.ahead.xw[(int64_t)tok * a.ahead.ldxw + f] = __float2bfloat16_rn(nv * w_next);
+            sqbuf[tok * R + r_local] = nv * nv;
+          }
+        } else {
+          const float up = __uint_as_float(u[j]) * inv;
+          ((__nv_bfloat16*)a.y)[(int64_t)tok * a.ldy + f] = __float2bfloat16_rn(v / (1.0f + expf(-v)) * up);
+        }
+      }
+    }
+    if (ahead) {  // this block's share of the new rows' sums of squares, added up in a fixed order
+      asm volatile("barrier.sync 1, 128;" ::: "memory");
+      if (ok && et < a.M) {
+        float v = 0.f;
+        for (int rr = 0; rr < R; ++rr) v += sqbuf[et * R + rr];
+        a.ahead.ssq_part[(int64_t)blockIdx.x * a.M + et] = v;
+      }
+    }
+  }
+  if (clustered) {
+    // All splits have pushed their tiles (and their shares of the rows' sums of squares); each
+    // block owns the token columns c with c % n_ranks == its rank and adds the splits' values
+    // in rank order.  A block that gave up on a wait still arrives, so that its peers go on.
+    uint32_t rank, n_ranks;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+    asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(n_ranks));
+    const int r_local = (warp & 3) * 32 + lane;
+    const int f = f0 + r_local;
+    const int per_rank = (BN + (int)n_ranks - 1) / (int)n_ranks;
+    const bool worker = warp >= 2 && r_local < ra.rows_per_block && f < a.N;
+    float old[16];
+    if (worker && MODE == kAccumF32) {  // the old values do not depend on the peers: fetch them while waiting
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const int col = i * (int)n_ranks + (int)rank;
+        old[i] = (i < per_rank && col < a.M) ? ((const float*)a.y)[(int64_t)col * a.ldy + f] : 0.f;
+      }
+    }
+    __syncwarp();
+    if (tl && threadIdx.x == 64) tl[8] = clock64();
+    asm volatile("barrier.cluster.arrive.release;\n\tbarrier.cluster.wait.acquire;" ::: "memory");
+    if (tl && threadIdx.x == 64) tl[9] = clock64();
+    if (worker && !abort_flag) {
+      const float* land = reinterpret_cast<const float*>(smem_raw + (landing - smem_u32(smem_raw)));
+      auto finish = [&](int i, int col, float before) {
+        float sum = 0.f;
+        for (uint32_t src = 0; src < n_ranks; ++src) sum += land[((int)src * per_rank + i) * BM + r_local];
+        if (NORMB) {
+          float ssq = 0.f;
+          for (uint32_t src = 0; src < n_ranks; ++src) ssq += rank_ssq[src][col];
+          sum *= 1.0f / sqrtf(ssq / (float)a.K + a.norm.eps);
+        }
+        if (MODE == kStoreBf16) ((__nv_bfloat16*)a.y)[(int64_t)col * a.ldy + f] = __float2bfloat16_rn(sum);
+        else ((float*)a.y)[(int64_t)col * a.ldy + f] = before + sum;
+      };
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const int col = i * (int)n_ranks + (int)rank;
+        if (i < per_rank && col < a.M) finish(i, col, MODE == kAccumF32 ? old[i] : 0.f);
+      }
+      for (int i = 16; i < per_rank; ++i) {  // a block that owns more than 16 columns (few splits, wide tile)
+        const int col = i * (int)n_ranks + (int)rank;
+        if (col >= a.M) break;
+        finish(i, col, MODE == kAccumF32 ? ((const float*)a.y)[(int64_t)col * a.ldy + f] : 0.f);
+      }
+    }
+  }
+  // ------------------------------------------------------------------ teardown
+  if (tl && threadIdx.x == 64) tl[10] = clock64();
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    if (lane == 0 && n_kb > 0) {  // the accumulator must be idle before its columns are freed
+      const long long t0 = clock64();
+      while (!mbar_try_wait(tmem_full_bar, 0) && clock64() - t0 < kWaitCycles) {}
+    }
+    __syncwarp();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)ra.tmem_cols) : "memory");
+  }
+  if (tl && threadIdx.x == 0) {
+    tl[7] = clock64();
+    unsigned long long g;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g));
+    if (!clustered) tl[8] = (long long)g;
+  }
+}
+
+template <int BN, int MODE, bool NORMB>
+int launch_rows(const CUtensorMap& mw, const CUtensorMap& mx, const GemmArgs& a, int rows_per_block, int kkb, int kstack,
+                int splits, long long* timeline, cudaStream_t stream) {
+  constexpr int kATiles = MODE == kGluBf16 ? 2 : 1;
+  RowsArgs ra;
+  ra.timeline = timeline;
+  ra.rows_per_block = rows_per_block;
+  ra.kkb = kkb;
+  ra.kstack = kstack;
+  int cols = kATiles * kstack * BN;
+  ra.tmem_cols = 32;
+  while (ra.tmem_cols < cols) ra.tmem_cols *= 2;
+  const int stage = kkb * (kATiles * rows_per_block * BK * 2 + BN * BK * 2);
+  // behind the ring: the landing zone of the cluster epilogue or the stacked epilogue's sums, which
+  // also is the room that the MMA, reading 128 rows whatever R is, may run into
+  int landing = splits > 1 ? (BN + splits - 1) / splits * splits * BM * 4 : 0;
+  if (kstack > 1) landing = kstack * BN * rows_per_block * 4;
+  if (a.ahead.xw != nullptr) landing += BN * rows_per_block * 4;  // the squares of the new rows
+  const int over_read = (BM - kstack * rows_per_block) * BK * 2;
+  ra.landing_bytes = landing > over_read ? landing : over_read;
+  const int fixed = 16 + 8 * (2 * kRowsMaxStages + 1) + 1024 + ra.landing_bytes;
+  ra.n_stages = (kRowsSmemBytes - fixed) / stage;
+  if (ra.n_stages > kRowsMaxStages) ra.n_stages = kRowsMaxStages;
+  if (ra.n_stages < 2) return fail(kBadArgument, "gemm_tc_rows: stages of %d bytes do not fit twice", stage);
+  const int smem = fixed + ra.n_stages * stage;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_rows_kernel<BN, MODE, NORMB>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         kRowsSmemBytes);
+    if (e != cudaSuccess) return fail(kLaunchFailed, "gemm_tc_rows: cannot reserve shared memory: %s", cudaGetErrorString(e));
+    configured = true;
+  }
+  const dim3 grid((a.N + rows_per_block - 1) / rows_per_block, 1, splits);
+  if (splits > 1)
+    launch_overlapped_cluster(gemm_tc_rows_kernel<BN, MODE, NORMB>, grid, dim3(kThreads), (size_t)smem, stream,
+                              (unsigned)splits, mw, mx, a, ra);
+  else
+    launch_overlapped(gemm_tc_rows_kernel<BN, MODE, NORMB>, grid, dim3(kThreads), (size_t)smem, stream, mw, mx, a, ra);
+  return check_launch("gemm_tc_rows");
+}
+
 // ------------------------------------------------------------------ persistent, for prompts
 // Many tokens: the kernel is bound by the tensor cores, so the epilogue must not cost
 // tensor time.  One block per SM walks the output tiles (tile = blockIdx.x, += gridDim.x;
@@ -595,7 +1172,8 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
           if (!mbar_wait(empty_bar(s), phase ^ 1, &abort_flag, a.error_flag, 1)) { ok = false; break; }
           const uint32_t sa = base + s * C::kStageBytes, sb = sa + C::kABytes;
           mbar_expect_tx(full_bar(s), C::kStageBytes);
-          tma_load_2d(sa, &map_w, full_bar(s), kb * BK, f_tile * BM * C::kATiles);
+          tma_load_2d(sa, &map_w, full_bar(s), kb * BK, f_tile * BM);
+          if (MODE == kGluBf16) tma_load_2d(sa + BM * BK * 2, &map_w, full_bar(s), kb * BK, a.N + f_tile * BM);
           tma_load_2d(sb, &map_x, full_bar(s), kb * BK, t_tile * BN);
           armed |= 1u << s;
           armed_parity = (armed_parity & ~(1u << s)) | (phase << s);
@@ -779,13 +1357,29 @@ int launch_bn(int bn, const CUtensorMap& mw, const CUtensorMap& mx, const GemmAr
 
 // Fills a 128-byte tensor map for a row-major bfloat16 matrix [rows, cols] with
 // `ld` elements between rows; boxes are [box_rows x 64 columns], 128-byte swizzle.
+// box_kblocks > 1: a 3-D map (64 columns, rows, K blocks of 64 columns) whose boxes bring
+// box_kblocks K blocks of box_rows rows, one after the other in shared memory; cols must be a
+// multiple of 64 (a column past the end would be read from the next row, not filled with zero).
 extern "C" int skyla_tensor_map_bf16(void* out, const void* ptr, uint64_t rows, uint64_t cols, uint64_t ld,
-                                     uint32_t box_rows) {
+                                     uint32_t box_rows, uint32_t box_kblocks) {
   EncodeTiledFn fn = encode_fn();
   if (fn == nullptr) return fail(kLaunchFailed, "tensor map: the driver does not offer cuTensorMapEncodeTiled");
   if (((uintptr_t)ptr) % 16 || (ld * 2) % 16) return fail(kBadArgument, "tensor map: base or row stride is not a multiple of 16 bytes");
   if (box_rows == 0 || box_rows > 256) return fail(kBadArgument, "tensor map: box of %u rows", box_rows);
   alignas(64) CUtensorMap m;
+  if (box_kblocks > 1) {
+    if (cols % BK || box_kblocks > 256) return fail(kBadArgument, "tensor map: %u K blocks per box need columns in multiples of 64", box_kblocks);
+    const cuuint64_t dims3[3] = {BK, rows, cols / BK};
+    const cuuint64_t strides3[2] = {ld * 2, BK * 2};
+    const cuuint32_t box3[3] = {BK, box_rows, box_kblocks};
+    const cuuint32_t estr3[3] = {1, 1, 1};
+    CUresult r3 = fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims3, strides3, box3, estr3,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r3 != CUDA_SUCCESS) return fail(kLaunchFailed, "tensor map: cuTensorMapEncodeTiled (3-D) failed with %d", (int)r3);
+    memcpy(out, &m, sizeof(m));
+    return kOk;
+  }
   const cuuint64_t dims[2] = {cols, rows};
   const cuuint64_t strides[1] = {ld * 2};
   const cuuint32_t box[2] = {BK, box_rows};
@@ -899,4 +1493,82 @@ extern "C" int skyla_gemm_tc_norm(const void* map_w, const float* x, int64_t ldx
     default: SKYLA_NORM_LAUNCH(kStoreF32)
   }
 #undef SKYLA_NORM_LAUNCH
+}
+
+// Few tokens (at most 64): blocks of `rows_per_block` weight rows (a multiple of 8, at most 128), K cut
+// into `splits` (at most 8) that meet in a thread-block cluster.  map_w has boxes of rows_per_block rows
+// and `kkb` K blocks (kkb > 1: a 3-D map, see skyla_tensor_map_bf16), of which one MMA takes `kstack` at
+// once (stacked along its rows; one split then).  Either x comes by map_x (bf16
+// [M, K], boxes of bn rows and kkb K blocks), or -- norm_x set -- the token operand is
+// rmsnorm(norm_x + sum_s part[s]) * norm_w made in the kernel (M <= 16, bn = 16).
+// Modes: store bf16 / f32, accumulate into f32 y, gated (bf16, one split).
+// ahead_*: with the accumulate epilogue, also leave bf16(y_new * ahead_w) in ahead_xw [M, N] and this
+// launch's blocks' shares of the new rows' sums of squares in ahead_ssq [blocks, M].
+// scale_*: the result is multiplied by 1/sqrt(sum_p scale_ssq[p, tok] / K + scale_eps).
+extern "C" int skyla_gemm_tc_rows(const void* map_w, const void* map_x, const float* norm_x, int64_t norm_ldx,
+                                  const float* part, int n_part, int64_t part_split_stride, int64_t ldp,
+                                  const float* norm_w, float eps, void* y, int64_t ldy, int M, int N, int K, int bn,
+                                  int mode, int rows_per_block, int kkb, int kstack, int splits, int* error_flag,
+                                  const float* ahead_w, void* ahead_xw, int64_t ahead_ldxw, float* ahead_ssq,
+                                  const float* scale_ssq, int scale_parts, float scale_eps,
+                                  long long* timeline, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return kOk;
+  if (K <= 0 || K % 8) return fail(kBadArgument, "gemm_tc_rows: K=%d must be a positive multiple of 8", K);
+  if (rows_per_block < 8 || rows_per_block > BM || rows_per_block % 8)
+    return fail(kBadArgument, "gemm_tc_rows: %d rows per block (a multiple of 8 up to 128)", rows_per_block);
+  if (M > bn || (bn != 16 && bn != 32 && bn != 64)) return fail(kBadArgument, "gemm_tc_rows: %d tokens in a tile of %d", M, bn);
+  if (mode != kStoreBf16 && mode != kStoreF32 && mode != kAccumF32 && mode != kGluBf16)
+    return fail(kBadArgument, "gemm_tc_rows: epilogue %d is not offered", mode);
+  if (kkb < 1 || kkb > 16 || (kkb > 1 && K % BK))
+    return fail(kBadArgument, "gemm_tc_rows: %d K blocks per box need 1..16 and K=%d a multiple of 64", kkb, K);
+  if (kstack < 1 || kkb % kstack || kstack * rows_per_block > BM || kstack * bn > 256 ||
+      (kstack > 1 && (splits != 1 || mode == kGluBf16)))
+    return fail(kBadArgument, "gemm_tc_rows: stacking %d K blocks needs kstack | kkb, kstack * rows <= 128, kstack * tile <= 256, "
+                "one split and no gating", kstack);
+  const int total_kb = (K + BK - 1) / BK;
+  if (splits < 1 || splits > kRowsMaxSplits || splits > total_kb || (mode == kGluBf16 && splits != 1))
+    return fail(kBadArgument, "gemm_tc_rows: %d K splits (1..8, one for the gated product)", splits);
+  const bool normb = norm_x != nullptr;
+  if (normb && (bn != 16 || norm_ldx % 4 || ldp % 4 || part_split_stride % 4 || ((uintptr_t)norm_x) % 16 ||
+                ((uintptr_t)part) % 16 || ((uintptr_t)norm_w) % 16 || mode == kAccumF32))
+    return fail(kBadArgument, "gemm_tc_rows: the in-kernel norm takes at most 16 tokens, 16-byte aligned rows, and no accumulate epilogue");
+  alignas(64) CUtensorMap mw, mx;
+  memcpy(&mw, map_w, sizeof(mw));
+  if (map_x != nullptr) memcpy(&mx, map_x, sizeof(mx)); else memcpy(&mx, map_w, sizeof(mx));
+  int kps = (total_kb + splits - 1) / splits;
+  kps = (kps + kkb - 1) / kkb * kkb;  // whole boxes per split
+  if ((splits - 1) * kps >= total_kb) return fail(kBadArgument, "gemm_tc_rows: %d splits leave one without K blocks", splits);
+  GemmArgs a{y, ldy, 0, M, N, K, kps, error_flag, FoldJob{},
+             NormSource{norm_x, norm_ldx, part, part ? n_part : 0, part_split_stride, ldp, norm_w, eps, nullptr},
+             nullptr, nullptr};
+  if (ahead_xw != nullptr) {
+    if (mode != kAccumF32 || splits != 1 || ahead_w == nullptr || ahead_ssq == nullptr)
+      return fail(kBadArgument, "gemm_tc_rows: norm-ahead goes with the accumulate epilogue, one split, a norm weight and room for the sums");
+    a.ahead = NormAhead{ahead_w, (__nv_bfloat16*)ahead_xw, ahead_ldxw, ahead_ssq};
+  }
+  if (scale_ssq != nullptr) {
+    if (normb || splits != 1 || scale_parts < 1)
+      return fail(kBadArgument, "gemm_tc_rows: handed-in sums of squares go with a loaded token operand and one split");
+    a.scale = ScaleIn{scale_ssq, scale_parts, scale_eps, K};
+  }
+#define SKYLA_ROWS_BN(MODE_, NORMB_)                                                                  \
+  switch (bn) {                                                                                       \
+    case 16: return launch_rows<16, MODE_, NORMB_>(mw, mx, a, rows_per_block, kkb, kstack, splits, timeline, stream);   \
+    case 32: return launch_rows<32, MODE_, false>(mw, mx, a, rows_per_block, kkb, kstack, splits, timeline, stream);    \
+    default: return launch_rows<64, MODE_, false>(mw, mx, a, rows_per_block, kkb, kstack, splits, timeline, stream);    \
+  }
+  if (normb) {
+    switch (mode) {
+      case kStoreBf16: SKYLA_ROWS_BN(kStoreBf16, true)
+      case kStoreF32: SKYLA_ROWS_BN(kStoreF32, true)
+      default: SKYLA_ROWS_BN(kGluBf16, true)
+    }
+  }
+  switch (mode) {
+    case kStoreBf16: SKYLA_ROWS_BN(kStoreBf16, false)
+    case kStoreF32: SKYLA_ROWS_BN(kStoreF32, false)
+    case kAccumF32: SKYLA_ROWS_BN(kAccumF32, false)
+    default: SKYLA_ROWS_BN(kGluBf16, false)
+  }
+#undef SKYLA_ROWS_BN
 }

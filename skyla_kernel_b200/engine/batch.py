@@ -94,6 +94,13 @@ class StepContext:
     #: K-split partial sums [splits, tokens, hidden] that still have to be added to the
     #: residual stream; the next norm (or fold_pending) adds them in a fixed order
     pending: Optional[torch.Tensor] = None
+    #: hints for "norm ahead": the norm that reads the residual stream after the part now running
+    #: (set by the block), and the norm that reads it after the block now running (set by the model)
+    next_norm: Optional[object] = None
+    after_block_norm: Optional[object] = None
+    #: what the last writer of the residual stream left for its next reader:
+    #: (norm, x, x * norm.weight in bfloat16, shares of the rows' sums of squares)
+    ahead: Optional[tuple] = None
 
     @property
     def is_decode(self) -> bool:
@@ -102,6 +109,14 @@ class StepContext:
     def take_pending(self) -> Optional[torch.Tensor]:
         p, self.pending = self.pending, None
         return p
+
+    def take_ahead(self, norm, x: torch.Tensor):
+        """(x * norm.weight in bfloat16, shares of the sums of squares) if the last writer of ``x``
+        left them for this very norm, else ``None``; either way they are gone afterwards."""
+        a, self.ahead = self.ahead, None
+        if a is not None and a[0] is norm and a[1] is x:
+            return a[2], a[3]
+        return None
 
     def fold_pending(self, x: torch.Tensor) -> None:
         """Make ``x`` whole for a reader that is not a norm."""

@@ -112,7 +112,11 @@ class DecoderModel:
         x = ctx.buffer("model.x", (ctx.n_tokens, hidden), torch.float32)
         self.embedding.forward(ctx, ctx.tokens, x)
         ctx.mark("embedding")
-        for i, e in enumerate(self.spec.schedule):
+        schedule = self.spec.schedule
+        for i, e in enumerate(schedule):
+            # the norm that reads x after this run, for a product that can prepare its input
+            nxt = self.blocks[schedule[i + 1].layer] if i + 1 < len(schedule) else None
+            ctx.after_block_norm = getattr(nxt, "first_norm", None)
             self.blocks[e.layer].forward(ctx, x, self.entries[i])
             if taps is not None and i in taps:
                 ctx.fold_pending(x)
@@ -129,4 +133,5 @@ class DecoderModel:
             self.head.forward(ctx, h, logits)
             ctx.mark("matvec output")
         ctx.pending = None
+        ctx.ahead = ctx.next_norm = ctx.after_block_norm = None
         return logits

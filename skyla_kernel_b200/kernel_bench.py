@@ -38,7 +38,8 @@ def _time(fn, copies: int, reps: int) -> float:
     return a.elapsed_time(b) * 1e3 / reps / copies
 
 
-def linear(tokens: int, n_out: int, n_in: int, mode: str, copies: int = 0, reps: int = 5) -> dict:
+def linear(tokens: int, n_out: int, n_in: int, mode: str, copies: int = 0, reps: int = 5, rows_max: int = -1,
+           plan: str = "") -> dict:
     """The tensor-core product as the linear part would launch it for this many tokens."""
     from .parts.base import Runtime
     from .parts.feedforward import fuse_gate_up
@@ -51,7 +52,11 @@ def linear(tokens: int, n_out: int, n_in: int, mode: str, copies: int = 0, reps:
     for i in range(copies):
         w = torch.empty(rows, n_in, dtype=torch.bfloat16, device=DEV)
         ops.fill_normal(w, 0.0, 0.02, i)
-        lins.append(Linear(w, rt, gated_group=128 if gated else 0))
+        lins.append(Linear(w, rt, gated=gated))
+        if rows_max >= 0:
+            lins[-1].ROWS_MAX_TOKENS = lins[-1].STACKED_MAX_TOKENS = rows_max
+        if plan:
+            lins[-1].rows_plans = {bn: tuple(int(v) for v in plan.split(",")) for bn in (16, 32, 64)}
     x = torch.randn(tokens, n_in, device=DEV).to(torch.bfloat16)
     if mode == "accumulate":
         y = torch.zeros(tokens, n_out, device=DEV)
@@ -69,6 +74,7 @@ def linear(tokens: int, n_out: int, n_in: int, mode: str, copies: int = 0, reps:
     flops = 2.0 * tokens * rows * n_in
     return {"kernel": "linear", "tokens": tokens, "n_out": n_out, "n_in": n_in, "mode": mode, "us": us,
             "weight_GBps": rows * n_in * 2 / us / 1e3, "TFLOPs": flops / us / 1e6,
+            "rows_kernel": tokens <= (lins[0].ROWS_MAX_TOKENS if lins[0].streams_wide else lins[0].STACKED_MAX_TOKENS), "plan": lins[0].rows_plans[ops.token_tile(min(tokens, 64))],
             "splits": lins[0].choose_splits(tokens) if tokens <= 64 and not gated else 1}
 
 
@@ -126,7 +132,7 @@ def attention_prefill(tokens: int, nq: int = 32, nkv: int = 8, hd: int = 128, re
 
 def main(a) -> int:
     if a.kernel == "linear":
-        r = linear(a.tokens, a.n_out, a.n_in, a.mode, reps=a.reps)
+        r = linear(a.tokens, a.n_out, a.n_in, a.mode, reps=a.reps, rows_max=a.rows_max, plan=a.plan)
     elif a.kernel == "attention-decode":
         r = attention_decode(a.batch, a.context, reps=a.reps, splits=a.splits)
     else:

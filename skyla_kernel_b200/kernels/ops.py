@@ -173,7 +173,8 @@ def linear_plain(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, mode: int = 
     """y = x @ w.T (store), y += x @ w.T (accumulate, y float32) or the gated product.
 
     In gated mode ``w`` has ``2 * y.shape[1]`` rows in groups of ``glu_group``
-    gate rows followed by the ``glu_group`` up rows of the same outputs.
+    gate rows followed by the ``glu_group`` up rows of the same outputs (0: all
+    gate rows, then all up rows).
     """
     _cuda(x, w, y)
     if not w.is_contiguous() or w.dim() != 2:
@@ -217,11 +218,13 @@ def check_device_errors(device) -> None:
 
 
 class TensorMap:
-    """A TMA descriptor of a row-major bfloat16 matrix, boxes of [box_rows x 64]."""
+    """A TMA descriptor of a row-major bfloat16 matrix, boxes of [box_rows x 64]; with
+    ``box_kblocks`` > 1 a box brings that many 64-column blocks of its rows (the width must
+    then be a multiple of 64)."""
 
     __slots__ = ("buf", "key", "keep")
 
-    def __init__(self, t: torch.Tensor, box_rows: int):
+    def __init__(self, t: torch.Tensor, box_rows: int, box_kblocks: int = 1):
         _cuda(t)
         if t.dtype != torch.bfloat16 or t.dim() != 2:
             raise KernelError("tensor maps are built for 2-D bfloat16 tensors")
@@ -229,21 +232,21 @@ class TensorMap:
         self.buf = ctypes.create_string_buffer(128)
         self.keep = t
         f = _fn("gemm_tc", "skyla_tensor_map_bf16",
-                [c_void_p, c_void_p, c_uint64, c_uint64, c_uint64, ctypes.c_uint32])
-        _check_nolaunch("gemm_tc", f(self.buf, _ptr(t), t.shape[0], t.shape[1], ld, box_rows))
+                [c_void_p, c_void_p, c_uint64, c_uint64, c_uint64, ctypes.c_uint32, ctypes.c_uint32])
+        _check_nolaunch("gemm_tc", f(self.buf, _ptr(t), t.shape[0], t.shape[1], ld, box_rows, box_kblocks))
 
 
 _X_MAPS = {}
 
 
-def activation_map(x: torch.Tensor, box_rows: int) -> TensorMap:
+def activation_map(x: torch.Tensor, box_rows: int, box_kblocks: int = 1) -> TensorMap:
     """Tensor maps of workspace buffers are few (the buffers are reused) and cached."""
-    key = (x.data_ptr(), x.shape[0], x.shape[1], x.stride(0), box_rows)
+    key = (x.data_ptr(), x.shape[0], x.shape[1], x.stride(0), box_rows, box_kblocks)
     m = _X_MAPS.get(key)
     if m is None:
         if len(_X_MAPS) > 4096:
             _X_MAPS.clear()
-        m = _X_MAPS[key] = TensorMap(x, box_rows)
+        m = _X_MAPS[key] = TensorMap(x, box_rows, box_kblocks)
         m.keep = None  # do not pin workspace memory; the key holds the address
     return m
 
@@ -304,7 +307,8 @@ def accum_scratch(device, n: int) -> torch.Tensor:
 
 def gemm_tc(x: torch.Tensor, w_map: TensorMap, n_out: int, y: torch.Tensor, mode: int, splits: int = 1,
             bn: Optional[int] = None, fold=None, scratch: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """y = x W^T on the tensor cores.  ``w_map`` has boxes of 128 rows (256 when gated).
+    """y = x W^T on the tensor cores.  ``w_map`` has boxes of 128 rows; a gated weight holds
+    the ``n_out`` gate rows, then the up rows.
 
     ``mode``: TC_STORE_BF16 / TC_STORE_F32 / TC_ACCUM_F32 / TC_GLU_BF16, or
     TC_PARTIAL_F32 with ``y`` of shape [splits, tokens, n_out] float32, or
@@ -386,6 +390,124 @@ def gemm_tc_norm(x: torch.Tensor, partials: Optional[torch.Tensor], norm_weight:
     _check("gemm_tc", f(w_map.buf, _ptr(x), _rows(x, "x"), _ptr(partials), n_part, pstride, ldp, _ptr(norm_weight),
                         float(eps), _ptr(ssq_out), _ptr(y), ldy, sstride, m, n_out, k, bn, mode, splits,
                         _ptr(error_flag(x.device)), _stream()))
+    return y
+
+
+N_SMS = 148
+ROWS_TIMELINE = None  # {"buf": int64 [launches, blocks, 12], "n": 0, "log": []} while tuning
+ROWS_MAX_TOKENS = 64
+ROWS_MAX_SPLITS = 8
+
+
+def rows_plan(n_out: int, n_in: int, gated: bool = False, bn: int = 16):
+    """(rows per block, K splits, K blocks per box, K blocks per MMA) for the few-token product
+    of a weight [n_out (x2 when gated), n_in] with token tiles of ``bn``.
+
+    The tile height is the smallest multiple of 8 whose tiles fill the SMs in whole waves.
+    Tiles of at most 64 rows stack 128 / rows K blocks into one MMA, so that a block covers
+    all of K without a K split; a box brings about 32 KB of weights (a TMA load costs the
+    same 0.16 us whatever it brings).  K that is no multiple of 64 has to do with one K
+    block per box (two-dimensional tensor maps).
+    """
+    waves = -(-n_out // (N_SMS * 128))
+    rows = -(-n_out // (N_SMS * waves))
+    rows = min(128, max(8, -(-rows // 8) * 8))
+    if n_in % 64:
+        return rows, 1, 1, 1
+    if gated:
+        return rows, 1, 2, 1
+    n_kb = n_in // 64
+    kstack = max(1, min(128 // rows, 256 // bn, n_kb))
+    group = kstack * rows * 128                     # bytes of weights that one MMA takes
+    per_box = max(1, min(-(-28 * 1024 // group), 16 // kstack, -(-n_kb // kstack)))
+    if bn > 16:                                      # wide token tiles: leave room for three stages
+        while per_box > 1 and per_box * kstack * (rows + bn) * 128 > 56 * 1024:
+            per_box -= 1
+    return rows, 1, per_box * kstack, kstack
+
+
+def gemm_tc_rows(x: Optional[torch.Tensor], w_map: TensorMap, rows: int, n_out: int, y: torch.Tensor, mode: int,
+                 normed=None, kkb: int = 1, splits: int = 1, kstack: int = 1,
+                 norm_ahead=None, scale_in=None, timeline: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """y = x W^T for at most 64 tokens, streaming the weight: blocks of ``rows`` weight rows
+    (a multiple of 8 up to 128), K cut into ``splits`` that meet in a thread-block cluster.
+
+    ``w_map`` has boxes of ``rows`` rows and ``kkb`` K blocks, of which one MMA takes ``kstack``
+    at once (then ``kstack * rows <= 128``, one split, not gated); a gated weight holds the
+    ``n_out`` gate rows, then the up rows.  ``normed=(x32, partials or None, norm_weight, eps)``
+    instead of ``x``: the token operand is ``rmsnorm(x32 + sum partials) * norm_weight`` made
+    inside the kernel (at most 16 tokens).  Modes TC_STORE_BF16 / TC_STORE_F32 / TC_ACCUM_F32 /
+    TC_GLU_BF16 (one split).
+    ``norm_ahead=(w, xw, ssq_parts)`` with TC_ACCUM_F32: ``y`` being the residual stream, also leave
+    ``xw = bf16(y_new * w)`` [tokens, n_out] and ``ssq_parts`` [blocks, tokens], every block's share of
+    the new rows' sums of squares, for the RMSNorm (weight ``w``) that reads ``y`` next.
+    ``scale_in=(ssq_parts, eps)``: ``x`` is such an ``xw``; the result is multiplied by the rows'
+    ``1/sqrt(sum(ssq_parts) / K + eps)``.  ``timeline`` (int64 [blocks, 12], for tuning): every block leaves its SM's
+    number and clock readings at its phases (start, set up, dependency met, first data, last MMA
+    issued, accumulator complete, end).
+    """
+    want = {TC_STORE_BF16: torch.bfloat16, TC_GLU_BF16: torch.bfloat16}.get(mode, torch.float32)
+    if y.dtype != want:
+        raise KernelError(f"gemm_tc_rows: epilogue {mode} writes {want}, y is {y.dtype}")
+    if normed is not None:
+        x32, partials, norm_weight, eps = normed
+        _cuda(x32, partials, norm_weight, y)
+        m, k = x32.shape
+        if x32.dtype != torch.float32 or norm_weight.dtype != torch.float32 or norm_weight.numel() != k or m > 16:
+            raise KernelError("gemm_tc_rows: the in-kernel norm takes float32 rows, a float32 weight of their width, 16 tokens")
+        n_part, pstride, ldp = 0, 0, 0
+        if partials is not None:
+            if (partials.dtype != torch.float32 or partials.dim() != 3 or not partials.is_contiguous()
+                    or tuple(partials.shape[1:]) != (m, k)):
+                raise KernelError("gemm_tc_rows: partial sums must be contiguous float32 [splits, tokens, K]")
+            n_part, pstride, ldp = partials.shape[0], partials.stride(0), partials.stride(1)
+        bn, xm = 16, None
+        nargs = [_ptr(x32), _rows(x32, "x"), _ptr(partials), n_part, pstride, ldp, _ptr(norm_weight), float(eps)]
+        dev = x32.device
+    else:
+        _cuda(x, y)
+        m, k = x.shape
+        if m > ROWS_MAX_TOKENS:
+            raise KernelError(f"gemm_tc_rows: at most {ROWS_MAX_TOKENS} tokens")
+        bn = token_tile(m)
+        xm = activation_map(x, bn, kkb)
+        nargs = [c_void_p(0), 0, c_void_p(0), 0, 0, 0, c_void_p(0), 0.0]
+        dev = x.device
+    if tuple(y.shape) != (m, n_out):
+        raise KernelError(f"gemm_tc_rows: y {tuple(y.shape)} is not [{m}, {n_out}]")
+    blocks = -(-n_out // rows)
+    ahead_args = [c_void_p(0), c_void_p(0), 0, c_void_p(0)]
+    if norm_ahead is not None:
+        aw, axw, assq = norm_ahead
+        _cuda(aw, axw, assq)
+        if (aw.dtype != torch.float32 or aw.numel() != n_out or not aw.is_contiguous() or axw.dtype != torch.bfloat16
+                or tuple(axw.shape) != (m, n_out) or axw.stride(1) != 1 or assq.dtype != torch.float32
+                or tuple(assq.shape) != (blocks, m) or not assq.is_contiguous()):
+            raise KernelError(f"gemm_tc_rows: norm-ahead wants w [{n_out}] float32, xw [{m}, {n_out}] bfloat16, "
+                              f"ssq_parts [{blocks}, {m}] float32")
+        ahead_args = [_ptr(aw), _ptr(axw), axw.stride(0), _ptr(assq)]
+    scale_args = [c_void_p(0), 0, 0.0]
+    if scale_in is not None:
+        sssq, seps = scale_in
+        _cuda(sssq)
+        if sssq.dtype != torch.float32 or sssq.dim() != 2 or sssq.shape[1] != m or not sssq.is_contiguous():
+            raise KernelError(f"gemm_tc_rows: handed-in sums of squares are float32 [parts, {m}]")
+        scale_args = [_ptr(sssq), sssq.shape[0], float(seps)]
+    f = _fn("gemm_tc", "skyla_gemm_tc_rows",
+            [c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_int, c_int64, c_int64, c_void_p, c_float,
+             c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
+             c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_float, c_void_p, c_void_p])
+    if timeline is None and ROWS_TIMELINE is not None:  # tuning: every launch leaves its blocks' timeline
+        timeline = ROWS_TIMELINE["buf"][ROWS_TIMELINE["n"]]
+        ROWS_TIMELINE["log"].append((ROWS_TIMELINE["n"], mode, n_out, k, blocks, normed is not None))
+        ROWS_TIMELINE["n"] += 1
+    if timeline is not None:
+        _cuda(timeline)
+        if timeline.dtype != torch.int64 or timeline.numel() < 12 * blocks * splits or not timeline.is_contiguous():
+            raise KernelError("gemm_tc_rows: the timeline is int64 [blocks, 12]")
+    _check("gemm_tc", f(w_map.buf, xm.buf if xm is not None else None, *nargs, _ptr(y), _rows(y, "y"), m, n_out, k, bn,
+                        mode, rows, kkb, kstack, splits, _ptr(error_flag(dev)), *ahead_args, *scale_args,
+                        _ptr(timeline), _stream()))
     return y
 
 
@@ -518,12 +640,13 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, scratch: torch.Tensor, 
     _check("attention_mma", f(_ptr(q), _rows(q, "q"), _ptr(out), _rows(out, "out"), _ptr(scratch), n, nq, nkv, hd,
                               _ptr(k_pool), _ptr(v_pool), _ptr(pages), pages.shape[1], page_size, _ptr(tok_pos),
                               float(scale), int(window or 0), n_splits, pages_per_split, _ptr(pages_needed), _stream()))
-    global LAUNCHES
-    LAUNCHES += 1  # the merge kernel
+    if tok_pos.numel() * nkv > (1 << 16):
+        global LAUNCHES
+        LAUNCHES += 1  # the merge kernel, which otherwise is part of the attention kernel
     return out
 
 
-def attention_decode_fused(qkv_partials: torch.Tensor, row_ssq: torch.Tensor, norm_width: int, norm_eps: float,
+def attention_decode_fused(qkv_partials: torch.Tensor, row_ssq: Optional[torch.Tensor], norm_width: int, norm_eps: float,
                            q_off: int, k_off: int, v_off: int, q_norm: Optional[torch.Tensor],
                            k_norm: Optional[torch.Tensor], eps: float, cos: Optional[torch.Tensor],
                            sin: Optional[torch.Tensor], n_rot: int, out: torch.Tensor, scratch: torch.Tensor,
@@ -533,13 +656,15 @@ def attention_decode_fused(qkv_partials: torch.Tensor, row_ssq: torch.Tensor, no
                            pages_needed: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Decode attention that also finishes the new token's q, k and v (what
     ``qk_norm_rope_cache`` does) from the K-split partial sums of the QKV product and the
-    rows' sums of squares, and writes k and v to the cache."""
+    rows' sums of squares, and writes k and v to the cache.  ``row_ssq=None``: the rows of
+    ``qkv_partials`` carry their norm's scalar already."""
     _cuda(qkv_partials, row_ssq, q_norm, k_norm, cos, sin, out, scratch, k_pool, v_pool, pages, tok_pos, pages_needed)
     _i32(pages, "pages"); _i32(tok_pos, "tok_pos"); _i32(pages_needed, "pages_needed")
     n = tok_pos.numel()
     if (qkv_partials.dtype != torch.float32 or qkv_partials.dim() != 3 or not qkv_partials.is_contiguous()
-            or qkv_partials.shape[1] != n or row_ssq.dtype != torch.float32 or not row_ssq.is_contiguous()
-            or row_ssq.dim() != 2 or row_ssq.shape[1] != n):
+            or qkv_partials.shape[1] != n or (row_ssq is not None and (
+                row_ssq.dtype != torch.float32 or not row_ssq.is_contiguous() or row_ssq.dim() != 2
+                or row_ssq.shape[1] != n))):
         raise KernelError("attention_decode_fused: partial sums [splits, tokens, width] and sums of squares [splits, tokens], float32")
     if out.dtype != torch.bfloat16 or k_pool.dtype != torch.bfloat16 or tuple(k_pool.shape[1:]) != (nkv, page_size, hd) \
             or k_pool.shape != v_pool.shape or not k_pool.is_contiguous() or not v_pool.is_contiguous():
@@ -554,13 +679,15 @@ def attention_decode_fused(qkv_partials: torch.Tensor, row_ssq: torch.Tensor, no
              c_float, c_void_p, c_void_p, c_int, c_void_p, c_int64, c_void_p, c_int, c_int, c_int, c_int, c_void_p,
              c_void_p, c_void_p, c_int, c_int, c_void_p, c_float, c_int, c_int, c_int, c_void_p, c_void_p])
     _check("attention_mma", f(_ptr(qkv_partials), qkv_partials.shape[0], qkv_partials.stride(0), qkv_partials.stride(1),
-                              q_off, k_off, v_off, _ptr(row_ssq), row_ssq.shape[0], int(norm_width), float(norm_eps),
+                              q_off, k_off, v_off, _ptr(row_ssq), row_ssq.shape[0] if row_ssq is not None else 0,
+                              int(norm_width), float(norm_eps),
                               _ptr(q_norm), _ptr(k_norm), float(eps), _ptr(cos), _ptr(sin), n_rot if cos is not None else 0,
                               _ptr(out), _rows(out, "out"), _ptr(scratch), n, nq, nkv, hd, _ptr(k_pool), _ptr(v_pool),
                               _ptr(pages), pages.shape[1], page_size, _ptr(tok_pos), float(scale), int(window or 0),
                               n_splits, pages_per_split, _ptr(pages_needed), _stream()))
-    global LAUNCHES
-    LAUNCHES += 1  # the merge kernel
+    if tok_pos.numel() * nkv > (1 << 16):
+        global LAUNCHES
+        LAUNCHES += 1  # the merge kernel, which otherwise is part of the attention kernel
     return out
 
 

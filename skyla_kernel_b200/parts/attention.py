@@ -98,16 +98,17 @@ class GQAttention(Part):
     def decode_splits(self, n_seqs: int, max_pages: int):
         """Into how many blocks a decode step cuts each sequence's context: (splits, pages per split).
 
-        A block is alone on its SM and pays for about six pages' time before its first page
-        arrives; blocks run in waves of 148.  The count is fixed per (batch, page-list width) so
-        that a recorded launch keeps its grid; how many pages a split covers follows the step's
-        longest sequence, which the kernel reads from device memory.
+        Two blocks share an SM (296 at a time); a block costs about three pages' time beside its
+        pages, and the merge of the splits about 0.7 for every eight of them (measured: a page
+        takes 1.2 us, a block's start and end 3.5, a round of the merge 0.8).  The count is fixed
+        per (batch, page-list width) so that a recorded launch keeps its grid; how many pages a
+        split covers follows the step's longest sequence, which the kernel reads from device memory.
         """
         items = max(1, self.nkv * n_seqs)
         typical = max(1.0, 0.75 * max_pages)
         best, best_cost = 1, None
         for n in range(1, max(1, min(32, max_pages // 2)) + 1):
-            cost = -(-items * n // 148) * (6.0 + typical / n)
+            cost = -(-items * n // 296) * (3.0 + typical / n) + 0.7 * -(-n // 8)
             if best_cost is None or cost < best_cost:
                 best, best_cost = n, cost
         return best, -(-max_pages // best)
@@ -122,8 +123,15 @@ class GQAttention(Part):
     def forward(self, ctx, h, x: torch.Tensor, entry) -> None:
         n = ctx.n_tokens
         normed = None
+        # few tokens: the QKV product leaves whole float32 rows, which the kernels after it finish
+        few = (entry.owns_cache and n <= self.qkv.STACKED_MAX_TOKENS and self.qkv.tensor_cores
+               and self.rt.act_dtype == torch.bfloat16)
+        scale_in = None
         if isinstance(h, NormedInput):
-            if entry.owns_cache and self.qkv.can_fuse_norm(h):
+            if few and h.ahead is not None and ops.tc_linear_ok(h.ahead[0], self.qkv.weight):
+                scale_in = (h.ahead[1], h.norm.eps)  # the product that wrote x last left x * norm weight
+                h = h.ahead[0]
+            elif few and self.qkv.can_fuse_norm(h):
                 normed = h  # the norm is made inside the QKV product
             else:
                 h = h.tensor()
@@ -134,8 +142,12 @@ class GQAttention(Part):
         n_rot = 0
         if self.position is not None:
             cos, sin, n_rot = self.position.tables(ctx.max_position + 1)
-        if normed is not None:
-            part, ssq = self.qkv.forward_normed_partial(normed, ctx, "attn.qkv_partials")
+        if few:
+            whole = ctx.buffer("attn.qkv32", (1, n, (nq + 2 * nkv) * hd), torch.float32)
+            if normed is not None:
+                self.qkv.forward_normed(normed, ctx, whole[0])
+            else:
+                self.qkv.forward(h, whole[0], STORE, scale_in=scale_in)
             ctx.mark("matvec qkv")
             pend = ctx.take_pending()
             if (pend is None and self._fast == 2 and ctx.is_decode and k_pool.dtype == torch.bfloat16
@@ -144,20 +156,19 @@ class GQAttention(Part):
                 attn = ctx.buffer("attn.out", (n, nq * hd), self.rt.act_dtype)
                 n_splits, per = self.decode_splits(ctx.n_seqs, pages.shape[1])
                 scratch = ctx.buffer("attn.partials", (n * nq * n_splits * (hd + 2),), torch.float32)
-                ops.attention_decode_fused(part, ssq, self.hidden, normed.norm.eps, 0, nq * hd, (nq + nkv) * hd,
+                ops.attention_decode_fused(whole, None, 0, 0.0, 0, nq * hd, (nq + nkv) * hd,
                                            self.q_norm_w, self.k_norm_w, self.eps, cos, sin, n_rot, attn, scratch,
                                            nq, nkv, hd, k_pool, v_pool, pages, ctx.page_size, ctx.tok_pos,
                                            self.scale, self.window, n_splits, per, ctx.pages_needed)
                 ctx.mark("attention")
-                self.out.forward(attn, x, ACCUMULATE)
+                self.out.forward(attn, x, ACCUMULATE, ctx=ctx)
                 ctx.mark("matvec o")
                 return
             qkv = ctx.buffer("attn.q", (n, nq * hd), self.rt.act_dtype)
             # if sums are pending, the prep kernel also makes x whole, after the product read it
-            ops.qk_norm_rope_cache(part, 0, nq * hd, (nq + nkv) * hd, nq, nkv, hd, self.q_norm_w,
+            ops.qk_norm_rope_cache(whole, 0, nq * hd, (nq + nkv) * hd, nq, nkv, hd, self.q_norm_w,
                                    self.k_norm_w, self.eps, cos, sin, n_rot, ctx.tok_pos, ctx.tok_seq,
-                                   k_pool, v_pool, pages, ctx.page_size, q_out=qkv, row_ssq=ssq,
-                                   norm_width=self.hidden, norm_eps=normed.norm.eps,
+                                   k_pool, v_pool, pages, ctx.page_size, q_out=qkv,
                                    fold=(x, pend) if pend is not None else None)
         elif entry.owns_cache:
             part = self.qkv.forward_partial(h, ctx, "attn.qkv_partials")
@@ -196,7 +207,7 @@ class GQAttention(Part):
             ops.attention_plain(q, attn, nq, nkv, hd, k_pool, v_pool, pages, ctx.page_size, ctx.tok_pos,
                                 ctx.tok_seq, self.scale, self.window)
         ctx.mark("attention")
-        self.out.forward(attn, x, ACCUMULATE)
+        self.out.forward(attn, x, ACCUMULATE, ctx=ctx)
         ctx.mark("matvec o")
 
 

@@ -141,6 +141,10 @@ class NormedInput:
     def __init__(self, ctx, x: torch.Tensor, norm):
         self.ctx, self.x, self.norm = ctx, x, norm
         self._tensor = None
+        #: (x * norm.weight in bfloat16, shares of the rows' sums of squares) where the product that
+        #: wrote ``x`` last left them (``Linear.forward(..., ctx=ctx)``); a part may feed them to its
+        #: first product (``scale_in=``) instead of calling :meth:`tensor`
+        self.ahead = ctx.take_ahead(norm, x) if hasattr(ctx, "take_ahead") else None
 
     def tensor(self) -> torch.Tensor:
         if self._tensor is None:

@@ -57,11 +57,20 @@ class PrenormResidualBlock:
     def weight_bytes(self) -> int:
         return sum(p.weight_bytes() for p in self.parts())
 
+    @property
+    def first_norm(self):
+        """The norm that reads the residual stream first when this block runs."""
+        return self.mixer_norm
+
     def forward(self, ctx, x, entry: EntryBinding) -> None:
+        after = getattr(ctx, "after_block_norm", None)
         h = NormedInput(ctx, x, self.mixer_norm)
+        ctx.next_norm = self.ffn_norm  # who reads x after the mixer has added to it
         self.mixer.forward(ctx, h if getattr(self.mixer, "takes_normed_input", False) else h.tensor(), x, entry)
         h = NormedInput(ctx, x, self.ffn_norm)
+        ctx.next_norm = after          # who reads x after the feed-forward has added to it
         self.feed_forward.forward(ctx, h if getattr(self.feed_forward, "takes_normed_input", False) else h.tensor(), x)
+        ctx.next_norm = None
 
 
 register_block("prenorm_residual", PrenormResidualBlock)

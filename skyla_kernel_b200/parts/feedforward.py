@@ -18,14 +18,9 @@ from .base import NormedInput, Part, register_feed_forward
 from .linear import ACCUMULATE, GATED, Linear
 
 
-def fuse_gate_up(gate: torch.Tensor, up: torch.Tensor, group: int) -> torch.Tensor:
-    """Rows in groups: ``group`` gate rows, then the ``group`` up rows of the same outputs."""
-    n, k = gate.shape
-    if n % group:
-        raise ValueError(f"gate/up group {group} does not divide {n}")
-    g = gate.reshape(n // group, group, k)
-    u = up.reshape(n // group, group, k)
-    return torch.stack((g, u), dim=1).reshape(2 * n, k).contiguous()
+def fuse_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    """One matrix: all gate rows, then the up rows of the same outputs."""
+    return torch.cat((gate, up), dim=0).contiguous()
 
 
 class SwiGLU(Part):
@@ -52,8 +47,7 @@ class SwiGLU(Part):
         gate, up = tensors[t["gate_proj"]], tensors[t["up_proj"]]
         if gate.dtype != up.dtype:
             gate, up = gate.to(torch.float32), up.to(torch.float32)
-        group = Linear.gated_group_for(self.rt, gate)
-        self.gate_up = Linear(self.rt.matrix(fuse_gate_up(gate, up, group)), self.rt, gated_group=group)
+        self.gate_up = Linear(self.rt.matrix(fuse_gate_up(gate, up)), self.rt, gated=True)
         self.down = Linear(self.rt.matrix(tensors[t["down_proj"]]), self.rt)
 
     def weight_bytes(self) -> int:
@@ -62,8 +56,13 @@ class SwiGLU(Part):
     def forward(self, ctx, h, x: torch.Tensor) -> None:
         act = ctx.buffer("ffn.act", (ctx.n_tokens, self.inter), self.rt.act_dtype)
         fold = None
+        scale_in = None
         if isinstance(h, NormedInput):
-            if self.gate_up.can_fuse_norm(h):
+            if (h.ahead is not None and self.gate_up.streams(ctx.n_tokens)
+                    and ops.tc_linear_ok(h.ahead[0], self.gate_up.weight)):
+                scale_in = (h.ahead[1], h.norm.eps)  # the product that wrote x last left x * norm weight
+                h = h.ahead[0]
+            elif self.gate_up.can_fuse_norm(h):
                 self.gate_up.forward_normed(h, ctx, act)  # norm, both products and silu(g)*u in one kernel
                 pend = ctx.take_pending()                 # x still lacks these; the down product adds them on the side
                 fold = (x, pend) if pend is not None else None
@@ -71,11 +70,11 @@ class SwiGLU(Part):
             else:
                 h = h.tensor()
         if h is not None:
-            self.gate_up.forward(h, act, GATED)
+            self.gate_up.forward(h, act, GATED, scale_in=scale_in)
         ctx.mark("matvec gate+up, silu")
         if fold is not None:
             ops.fold_partials(*fold)
-        self.down.forward(act, x, ACCUMULATE)
+        self.down.forward(act, x, ACCUMULATE, ctx=ctx)
         ctx.mark("matvec down")
 
 

@@ -7,6 +7,8 @@ chosen here, never by the caller.
 """
 from __future__ import annotations
 
+import os
+
 import torch
 
 from ..kernels import ops
@@ -17,37 +19,83 @@ STORE, ACCUMULATE, GATED = ops.STORE, ops.ACCUMULATE, ops.GATED
 class Linear:
     kernel_modules = ("linear_plain", "gemm_tc")
 
-    #: rows of gate and of up that alternate in a fused gate/up matrix for the tensor-core kernel
-    TC_GATED_GROUP = 128
+    #: the weight-streaming kernel takes over up to this many tokens ...
+    ROWS_MAX_TOKENS = 64
+    #: ... but where its blocks each read every token's whole row (short tiles, no K split) only
+    #: up to this many: beyond, the token rows outweigh the block's weights
+    STACKED_MAX_TOKENS = 16
 
-    def __init__(self, weight: torch.Tensor, rt, gated_group: int = 0):
-        """``weight`` on the device; ``gated_group`` > 0 marks a fused gate/up matrix."""
+    def __init__(self, weight: torch.Tensor, rt, gated: bool = False):
+        """``weight`` on the device; ``gated`` marks a fused matrix: all gate rows, then all up rows."""
         self.weight = weight
         self.rt = rt
-        self.gated_group = gated_group
+        self.gated = gated
         self.n_in = weight.shape[1]
-        self.n_out = weight.shape[0] // 2 if gated_group else weight.shape[0]
+        self.n_out = weight.shape[0] // 2 if gated else weight.shape[0]
         self._map = None
+        self._rows_maps = {}
+        #: token tile -> (rows per block, K splits, K blocks per box, K blocks per MMA) of the weight-streaming kernel
+        self.rows_plans = {bn: ops.rows_plan(self.n_out, self.n_in, gated, bn) for bn in (16, 32, 64)}
+        self.streams_wide = self.rows_plans[64][0] > 64  # tall tiles: gated products, many-wave products
         self.tensor_cores = (not rt.full_precision and weight.dtype == torch.bfloat16 and self.n_in % 8 == 0
-                             and weight.is_contiguous() and weight.data_ptr() % 16 == 0
-                             and (not gated_group or gated_group == self.TC_GATED_GROUP))
-
-    @classmethod
-    def gated_group_for(cls, rt, gate: torch.Tensor) -> int:
-        """The gate/up grouping to fuse with: 128 where the tensor-core kernel will run, else one block."""
-        n, k = gate.shape
-        fast = not rt.full_precision and gate.dtype == torch.bfloat16 and n % cls.TC_GATED_GROUP == 0 and k % 8 == 0
-        return cls.TC_GATED_GROUP if fast else n
+                             and weight.is_contiguous() and weight.data_ptr() % 16 == 0)
 
     def weight_map(self):
         if self._map is None:
-            self._map = ops.TensorMap(self.weight, 256 if self.gated_group else 128)
+            self._map = ops.TensorMap(self.weight, 128)
         return self._map
 
-    def forward(self, x: torch.Tensor, y: torch.Tensor, mode: int = STORE) -> torch.Tensor:
-        if self.gated_group:
+    def streams(self, m: int) -> bool:
+        """Whether ``m`` tokens go to the weight-streaming kernel (given operands it takes)."""
+        return self.tensor_cores and m <= (self.ROWS_MAX_TOKENS if self.streams_wide else self.STACKED_MAX_TOKENS)
+
+    def _rows_map(self, m: int):
+        rows, splits, kkb, kstack = self.rows_plans[ops.token_tile(m)]
+        w_map = self._rows_maps.get((rows, kkb))
+        if w_map is None:
+            w_map = self._rows_maps[(rows, kkb)] = ops.TensorMap(self.weight, rows, kkb)
+        return w_map
+
+    def _stream(self, x, y, tc, normed=None, norm_ahead=None, scale_in=None):
+        m = x.shape[0] if x is not None else normed[0].shape[0]
+        rows, splits, kkb, kstack = self.rows_plans[ops.token_tile(m)]
+        return ops.gemm_tc_rows(x, self._rows_map(m), rows, self.n_out, y, tc, normed=normed, kkb=kkb, splits=splits,
+                                kstack=kstack, norm_ahead=norm_ahead, scale_in=scale_in)
+
+    def _norm_ahead(self, ctx, x, y):
+        """Buffers for "norm ahead" if this product adds into the residual stream ``y``, the norm
+        that reads it next is an RMSNorm of its width, and the weight-streaming kernel runs."""
+        norm = getattr(ctx, "next_norm", None) if ctx is not None else None
+        if ctx is not None:
+            ctx.next_norm = None
+        m = x.shape[0]
+        if (norm is None or type(norm).__name__ != "RMSNorm" or not self.NORM_AHEAD or y.dtype != torch.float32
+                or getattr(norm, "weight", None) is None or norm.weight.numel() != self.n_out
+                or self.n_out % 8 or self.rows_plans[ops.token_tile(m)][1] != 1):
+            return None, None
+        blocks = -(-self.n_out // self.rows_plans[ops.token_tile(m)][0])
+        xw = ctx.buffer("x.times_norm_weight", (m, self.n_out), torch.bfloat16)
+        ssq = ctx.buffer("x.ssq_shares", (blocks, m), torch.float32)
+        return norm, (norm.weight, xw, ssq)
+
+    def forward(self, x: torch.Tensor, y: torch.Tensor, mode: int = STORE, scale_in=None, ctx=None) -> torch.Tensor:
+        """``scale_in=(shares of the rows' sums of squares, eps)``: ``x`` is a residual stream times
+        its norm's weight (see ``NormedInput.ahead``); only where :meth:`streams` holds.
+        ``ctx`` with ``mode=ACCUMULATE``: ``y`` is the residual stream, and if ``ctx.next_norm``
+        names the RMSNorm that reads it next, its input is prepared on the way (``ctx.ahead``)."""
+        if self.gated:
             mode = GATED
         if self.tensor_cores and ops.tc_linear_ok(x, self.weight):
+            if self.streams(x.shape[0]):
+                tc = {GATED: ops.TC_GLU_BF16, ACCUMULATE: ops.TC_ACCUM_F32}.get(
+                    mode, ops.TC_STORE_BF16 if y.dtype == torch.bfloat16 else ops.TC_STORE_F32)
+                norm, ahead = self._norm_ahead(ctx, x, y) if mode == ACCUMULATE else (None, None)
+                self._stream(x, y, tc, norm_ahead=ahead, scale_in=scale_in)
+                if ahead is not None:
+                    ctx.ahead = (norm, y, ahead[1], ahead[2])
+                return y
+            if scale_in is not None:
+                raise ValueError("scale_in goes with the weight-streaming kernel only (Linear.streams)")
             if mode == GATED:
                 tc = ops.TC_GLU_BF16
             elif mode == ACCUMULATE:
@@ -62,7 +110,9 @@ class Linear:
             else:
                 tc = ops.TC_STORE_BF16 if y.dtype == torch.bfloat16 else ops.TC_STORE_F32
             return ops.gemm_tc(x, self.weight_map(), self.n_out, y, tc)
-        return ops.linear_plain(x, self.weight, y, mode, self.gated_group)
+        if scale_in is not None:
+            raise ValueError("scale_in goes with the weight-streaming kernel only (Linear.streams)")
+        return ops.linear_plain(x, self.weight, y, mode, 0)
 
     # ---- K-split products for small batches
     N_SMS = 148
@@ -98,7 +148,7 @@ class Linear:
         buffer, or ``None`` when splitting does not pay or the tensor-core kernel does not
         take these operands; the reader adds the splits up in ascending order.
         ``fold=(r, partials)`` rides along (``r += sum partials``) when the product is made."""
-        if self.gated_group or not self.tensor_cores or not ops.tc_linear_ok(x, self.weight):
+        if self.gated or not self.tensor_cores or not ops.tc_linear_ok(x, self.weight):
             return None
         m = x.shape[0]
         splits = self.choose_splits(m)
@@ -110,12 +160,14 @@ class Linear:
 
     # ---- the RMSNorm of the input made inside the product
     FUSED_NORM_MAX_TOKENS = 16  # every block re-reads the rows it normalises: only worth it for few
+    FUSE_NORM = os.environ.get("SKYLA_FUSE_NORM", "0") != "0"   # off: "norm ahead" is cheaper
+    NORM_AHEAD = os.environ.get("SKYLA_NORM_AHEAD", "1") != "0"
 
     def can_fuse_norm(self, normed) -> bool:
         """Whether ``norm(x + pending)`` can be made inside this product: RMSNorm, float32 rows
         with 16-byte alignment, few tokens, and a weight the tensor-core kernel takes."""
         x, norm, pend = normed.x, normed.norm, normed.ctx.pending
-        return (self.tensor_cores and type(norm).__name__ == "RMSNorm" and x.dtype == torch.float32
+        return (self.FUSE_NORM and self.tensor_cores and type(norm).__name__ == "RMSNorm" and x.dtype == torch.float32
                 and x.shape[0] <= self.FUSED_NORM_MAX_TOKENS and x.shape[1] == self.n_in
                 and x.stride(1) == 1 and x.stride(0) % 4 == 0 and x.data_ptr() % 16 == 0
                 and (pend is None or (pend.dim() == 3 and tuple(pend.shape[1:]) == tuple(x.shape))))
@@ -136,8 +188,8 @@ class Linear:
     def forward_normed(self, normed, ctx, y: torch.Tensor) -> torch.Tensor:
         """``y = f(norm(x + pending) W^T)`` in one kernel (gated or plain store)."""
         x, norm = normed.x, normed.norm
-        mode = ops.TC_GLU_BF16 if self.gated_group else (ops.TC_STORE_BF16 if y.dtype == torch.bfloat16 else ops.TC_STORE_F32)
-        return ops.gemm_tc_norm(x, ctx.pending, norm.weight, norm.eps, self.weight_map(), self.n_out, y, mode)
+        mode = ops.TC_GLU_BF16 if self.gated else (ops.TC_STORE_BF16 if y.dtype == torch.bfloat16 else ops.TC_STORE_F32)
+        return self._stream(None, y, mode, normed=(x, ctx.pending, norm.weight, norm.eps))
 
     def bytes(self) -> int:
         return self.weight.numel() * self.weight.element_size()

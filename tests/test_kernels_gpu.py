@@ -77,11 +77,10 @@ def test_linear_plain_store_and_accumulate(m, n, k, xdt, wdt):
 @pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
 def test_linear_plain_gated(group, dt):
     ops = _ops()
-    from skyla_kernel_b200.parts.feedforward import fuse_gate_up
     m, n, k = 37, 112, 80
     x, g, u = _rand(m, k, seed=7, dtype=dt), _rand(n, k, seed=8, dtype=dt, scale=0.2), _rand(n, k, seed=9, dtype=dt, scale=0.2)
     grp = group or n
-    w = fuse_gate_up(g, u, grp)
+    w = torch.stack((g.reshape(n // grp, grp, k), u.reshape(n // grp, grp, k)), dim=1).reshape(2 * n, k).contiguous()
     y = torch.empty(m, n, dtype=dt, device=DEV)
     ops.linear_plain(x, w, y, ops.GATED, grp)
     ref = plain.silu(x.double().cpu() @ g.double().cpu().T) * (x.double().cpu() @ u.double().cpu().T)
@@ -322,20 +321,21 @@ def test_gemm_tc_split_k(m, n, k, splits):
     ops.check_device_errors(DEV)
 
 
-@pytest.mark.parametrize("m,n,k", [(1, 128, 64), (9, 256, 80), (70, 384, 160), (200, 128, 520)])
+@pytest.mark.parametrize("m,n,k", [(1, 128, 64), (9, 256, 80), (70, 384, 160), (200, 128, 520), (33, 200, 72),
+                                   (300, 1000, 328)])
 def test_gemm_tc_gated(m, n, k):
     ops = _ops()
     from skyla_kernel_b200.parts.feedforward import fuse_gate_up
     x = _rand(m, k, seed=36, dtype=torch.bfloat16)
     g, u = _rand(n, k, seed=37, dtype=torch.bfloat16, scale=0.2), _rand(n, k, seed=38, dtype=torch.bfloat16, scale=0.2)
-    w = fuse_gate_up(g, u, 128)
+    w = fuse_gate_up(g, u)
     y = torch.empty(m, n, dtype=torch.bfloat16, device=DEV)
-    ops.gemm_tc(x, ops.TensorMap(w, 256), n, y, ops.TC_GLU_BF16)
+    ops.gemm_tc(x, ops.TensorMap(w, 128), n, y, ops.TC_GLU_BF16)
     gd, ud = x.double() @ g.double().T, x.double() @ u.double().T
     ref = gd / (1 + torch.exp(-gd)) * ud
     torch.testing.assert_close(y.double(), ref, rtol=1e-2, atol=1e-2 * ref.abs().max().item())
     plain_y = torch.empty_like(y)
-    ops.linear_plain(x, w, plain_y, ops.GATED, 128)  # the plain twin on the same fused matrix
+    ops.linear_plain(x, w, plain_y, ops.GATED)  # the plain twin on the same fused matrix
     torch.testing.assert_close(y.float(), plain_y.float(), rtol=2e-2, atol=1e-3)
     ops.check_device_errors(DEV)
 
@@ -491,6 +491,162 @@ def test_prep_adds_up_partial_sums():
     assert res[0][0].abs().sum() > 0 and res[0][1].abs().sum() > 0
 
 
+# ----------------------------------------------- few tokens: the weight-streaming product
+@pytest.mark.parametrize("m,n,k,rows,kkb,splits,kstack", [
+    (1, 128, 64, 128, 1, 1, 1), (8, 4096, 4096, 56, 2, 2, 1), (5, 1000, 264, 8, 1, 1, 1), (16, 300, 1032, 24, 1, 3, 1),
+    (11, 130, 8192, 16, 2, 8, 1), (33, 520, 704, 104, 2, 2, 1), (64, 392, 512, 40, 4, 2, 1), (64, 392, 520, 40, 1, 5, 1),
+    (8, 4096, 12288, 112, 2, 4, 1), (3, 200, 1536, 72, 3, 4, 1),
+    (8, 4096, 4096, 32, 8, 1, 4), (8, 6144, 4096, 48, 6, 1, 2), (16, 300, 1088, 24, 10, 1, 5), (1, 100, 704, 8, 16, 1, 16),
+    (33, 520, 704, 40, 6, 1, 3), (64, 392, 1536, 32, 4, 1, 4), (50, 200, 960, 56, 4, 1, 2), (8, 4096, 12288, 32, 8, 1, 4)])
+def test_gemm_tc_rows_store_accumulate_gated(m, n, k, rows, kkb, splits, kstack):
+    """Every epilogue of the weight-streaming product against float64, at tile heights that
+    divide nothing (the last block's rows run past the matrix), K cut into clusters of
+    splits of unequal length, boxes of one to sixteen K blocks, and K blocks stacked into
+    one MMA (with a last box that runs past K)."""
+    ops = _ops()
+    from skyla_kernel_b200.parts.feedforward import fuse_gate_up
+    x = _rand(m, k, seed=91, dtype=torch.bfloat16)
+    w = _rand(n, k, seed=92, dtype=torch.bfloat16, scale=0.1)
+    ref = x.double() @ w.double().T
+    tol = dict(rtol=1e-2, atol=1e-2 * ref.abs().max().item())
+    wm = ops.TensorMap(w, rows, kkb)
+    y = torch.full((m, n), float("nan"), device=DEV)
+    ops.gemm_tc_rows(x, wm, rows, n, y, ops.TC_STORE_F32, kkb=kkb, splits=splits, kstack=kstack)
+    assert (y.double() - ref).abs().max().item() <= 2e-5 * ref.abs().max().item() + 1e-6  # float32 sums of exact products
+    yb = torch.empty(m, n, dtype=torch.bfloat16, device=DEV)
+    ops.gemm_tc_rows(x, wm, rows, n, yb, ops.TC_STORE_BF16, kkb=kkb, splits=splits, kstack=kstack)
+    torch.testing.assert_close(yb.double(), ref, **tol)
+    base = _rand(m, n, seed=93)
+    acc = base.clone()
+    ops.gemm_tc_rows(x, wm, rows, n, acc, ops.TC_ACCUM_F32, kkb=kkb, splits=splits, kstack=kstack)
+    ops.gemm_tc_rows(x, wm, rows, n, acc, ops.TC_ACCUM_F32, kkb=kkb, splits=splits, kstack=kstack)
+    assert (acc.double() - (base.double() + 2 * ref)).abs().max().item() <= 1e-4 * ref.abs().max().item() + 1e-5
+    g, u = _rand(n, k, seed=94, dtype=torch.bfloat16, scale=0.1), _rand(n, k, seed=95, dtype=torch.bfloat16, scale=0.1)
+    act = torch.empty(m, n, dtype=torch.bfloat16, device=DEV)
+    kkb = min(kkb, 2)  # the gated product brings two tiles per K block
+    ops.gemm_tc_rows(x, ops.TensorMap(fuse_gate_up(g, u), rows, kkb), rows, n, act, ops.TC_GLU_BF16, kkb=kkb)
+    gd, ud = x.double() @ g.double().T, x.double() @ u.double().T
+    ref_act = gd / (1 + torch.exp(-gd)) * ud
+    torch.testing.assert_close(act.double(), ref_act, rtol=1e-2, atol=1e-2 * ref_act.abs().max().item())
+    ops.check_device_errors(DEV)
+
+
+@pytest.mark.parametrize("m,n,k,n_part,rows,kkb,splits,kstack", [
+    (1, 128, 64, 0, 128, 1, 1, 1), (8, 6144, 4096, 0, 48, 2, 1, 1), (5, 250, 264, 2, 16, 1, 2, 1), (16, 257, 1032, 3, 8, 1, 4, 1),
+    (11, 128, 8192, 1, 8, 2, 8, 1), (8, 6144, 4096, 0, 128, 2, 3, 1), (7, 264, 1536, 2, 40, 4, 3, 1),
+    (8, 6144, 4096, 0, 48, 6, 1, 2), (16, 257, 1088, 3, 8, 16, 1, 16), (3, 264, 1536, 2, 40, 9, 1, 3), (8, 4096, 4096, 1, 32, 8, 1, 4)])
+def test_gemm_tc_rows_with_the_norm_inside(m, n, k, n_part, rows, kkb, splits, kstack):
+    ops = _ops()
+    from skyla_kernel_b200.parts.feedforward import fuse_gate_up
+    x = _rand(m, k, seed=71, scale=1.5)
+    part = _rand(n_part, m, k, seed=72, scale=0.5) if n_part else None
+    nw = 1 + 0.2 * _rand(k, seed=73)
+    whole = x.double() + (part.double().sum(0) if n_part else 0)
+    h = plain.rmsnorm(whole.cpu(), nw.double().cpu(), 1e-5)
+    w = _rand(n, k, seed=74, dtype=torch.bfloat16, scale=0.1)
+    ref = h @ w.double().cpu().T
+    y = torch.full((m, n), float("nan"), dtype=torch.float32, device=DEV)
+    x_before = x.clone()
+    ops.gemm_tc_rows(None, ops.TensorMap(w, rows, kkb), rows, n, y, ops.TC_STORE_F32, normed=(x, part, nw, 1e-5),
+                     kkb=kkb, splits=splits, kstack=kstack)
+    assert torch.equal(x, x_before)
+    torch.testing.assert_close(y.double().cpu(), ref, rtol=2e-2, atol=2e-2 * ref.abs().max().item())
+    assert (y.double().cpu() - ref).abs().mean().item() < 4e-3 * ref.abs().max().item()
+    # the same rows through a separate norm kernel and the plain product of the rounded rows
+    hb = torch.empty(m, k, dtype=torch.bfloat16, device=DEV)
+    if n_part:
+        ops.add_rmsnorm(x.clone(), part, nw, 1e-5, hb)
+    else:
+        ops.rmsnorm(x, nw, 1e-5, hb)
+    y2 = torch.empty(m, n, device=DEV)
+    ops.linear_plain(hb, w, y2, ops.STORE)
+    assert (y - y2).abs().max().item() <= 1.2e-2 * ref.abs().max().item()
+    g, u = _rand(n, k, seed=75, dtype=torch.bfloat16, scale=0.1), _rand(n, k, seed=76, dtype=torch.bfloat16, scale=0.1)
+    act = torch.empty(m, n, dtype=torch.bfloat16, device=DEV)
+    kkb = min(kkb, 2)  # the gated product brings two tiles per K block
+    ops.gemm_tc_rows(None, ops.TensorMap(fuse_gate_up(g, u), rows, kkb), rows, n, act, ops.TC_GLU_BF16,
+                     normed=(x, part, nw, 1e-5), kkb=kkb)
+    gd, ud = h @ g.double().cpu().T, h @ u.double().cpu().T
+    ref_act = gd / (1 + torch.exp(-gd)) * ud
+    torch.testing.assert_close(act.double().cpu(), ref_act, rtol=3e-2, atol=3e-2 * ref_act.abs().max().item())
+    ops.check_device_errors(DEV)
+
+
+@pytest.mark.parametrize("m,n,k,rows,kkb,kstack,n2,rows2,kkb2,kstack2", [
+    (8, 4096, 4096, 32, 8, 4, 6144, 48, 6, 2), (5, 264, 520, 24, 1, 1, 200, 72, 1, 1), (16, 328, 704, 40, 6, 3, 136, 8, 16, 16),
+    (1, 128, 64, 128, 1, 1, 128, 128, 1, 1), (11, 1000, 1536, 56, 4, 2, 520, 88, 2, 1)])
+def test_gemm_tc_rows_norm_ahead_then_scale_in(m, n, k, rows, kkb, kstack, n2, rows2, kkb2, kstack2):
+    """x += a W^T leaves x * norm weight in bfloat16 and the blocks' shares of the rows' sums of
+    squares; the next product takes those and must equal the product of rmsnorm(x)."""
+    ops = _ops()
+    from skyla_kernel_b200.parts.feedforward import fuse_gate_up
+    a = _rand(m, k, seed=61, dtype=torch.bfloat16)
+    w = _rand(n, k, seed=62, dtype=torch.bfloat16, scale=0.1)
+    x0 = _rand(m, n, seed=63, scale=1.5)
+    nw = 1 + 0.2 * _rand(n, seed=64)
+    x = x0.clone()
+    blocks = -(-n // rows)
+    xw = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device=DEV)
+    shares = torch.full((blocks, m), float("nan"), device=DEV)
+    ops.gemm_tc_rows(a, ops.TensorMap(w, rows, kkb), rows, n, x, ops.TC_ACCUM_F32, kkb=kkb, kstack=kstack,
+                     norm_ahead=(nw, xw, shares))
+    want_x = x0.double() + a.double() @ w.double().T
+    assert (x.double() - want_x).abs().max().item() <= 1e-5 * want_x.abs().max().item() + 1e-6
+    assert torch.equal(xw, (x * nw).to(torch.bfloat16))                       # the very rows that were stored
+    ssq = shares.double().sum(0)
+    torch.testing.assert_close(ssq, (x.double() ** 2).sum(1), rtol=1e-5, atol=1e-6)
+    # the next product: plain, and gated
+    eps = 1e-5
+    h = plain.rmsnorm(x.double().cpu(), nw.double().cpu(), eps)
+    w2 = _rand(n2, n, seed=65, dtype=torch.bfloat16, scale=0.1)
+    ref = h @ w2.double().cpu().T
+    y = torch.full((m, n2), float("nan"), device=DEV)
+    ops.gemm_tc_rows(xw, ops.TensorMap(w2, rows2, kkb2 if n % 64 == 0 else 1), rows2, n2, y, ops.TC_STORE_F32,
+                     kkb=kkb2 if n % 64 == 0 else 1, kstack=kstack2 if n % 64 == 0 else 1, scale_in=(shares, eps))
+    torch.testing.assert_close(y.double().cpu(), ref, rtol=2e-2, atol=2e-2 * ref.abs().max().item())
+    assert (y.double().cpu() - ref).abs().mean().item() < 4e-3 * ref.abs().max().item()
+    g, u = _rand(n2, n, seed=66, dtype=torch.bfloat16, scale=0.1), _rand(n2, n, seed=67, dtype=torch.bfloat16, scale=0.1)
+    act = torch.empty(m, n2, dtype=torch.bfloat16, device=DEV)
+    kk = min(2, kkb2) if n % 64 == 0 else 1
+    ops.gemm_tc_rows(xw, ops.TensorMap(fuse_gate_up(g, u), rows2, kk), rows2, n2, act, ops.TC_GLU_BF16, kkb=kk,
+                     scale_in=(shares, eps))
+    gd, ud = h @ g.double().cpu().T, h @ u.double().cpu().T
+    ref_act = gd / (1 + torch.exp(-gd)) * ud
+    torch.testing.assert_close(act.double().cpu(), ref_act, rtol=3e-2, atol=3e-2 * ref_act.abs().max().item())
+    ops.check_device_errors(DEV)
+
+
+def test_rows_plan_fills_the_sms():
+    ops = _ops()
+    for n, k, gated in [(6144, 4096, False), (4096, 4096, False), (12288, 4096, True), (4096, 12288, False),
+                        (151936, 4096, False), (96, 80, False), (160, 80, True), (25600, 5120, True), (2560, 9728, False)]:
+        for bn in (16, 32, 64):
+            rows, splits, kkb, kstack = ops.rows_plan(n, k, gated, bn)
+            assert rows % 8 == 0 and 8 <= rows <= 128 and splits == 1 and kkb % kstack == 0 and 1 <= kkb <= 16
+            assert kstack * rows <= 128 and kstack * bn <= 256 and (kkb == 1 or k % 64 == 0) and (kstack == 1 or not gated)
+            blocks = -(-n // rows)
+            assert n < 148 * 8 or blocks / (-(-blocks // 148) * 148) >= 0.7  # the waves are nearly full
+            stage = kkb * (rows * (2 if gated else 1) + bn) * 128
+            assert 2 * stage + 40 * 1024 <= 212 * 1024  # at least two stages beside the epilogue's room
+
+
+def test_gemm_tc_rows_refuses():
+    ops = _ops()
+    from skyla_kernel_b200.kernels import KernelError
+    x = _rand(70, 64, seed=1, dtype=torch.bfloat16)
+    w = _rand(128, 64, seed=2, dtype=torch.bfloat16)
+    with pytest.raises(KernelError):  # too many tokens
+        ops.gemm_tc_rows(x, ops.TensorMap(w, 128), 128, 128, torch.empty(70, 128, device=DEV), ops.TC_STORE_F32)
+    with pytest.raises(KernelError):  # a tile height that is no multiple of 8
+        ops.gemm_tc_rows(x[:4], ops.TensorMap(w, 100), 100, 128, torch.empty(4, 128, device=DEV), ops.TC_STORE_F32)
+    with pytest.raises(KernelError):  # an epilogue it does not have
+        ops.gemm_tc_rows(x[:4], ops.TensorMap(w, 128), 128, 128, torch.empty(4, 128, device=DEV), ops.TC_PARTIAL_F32)
+    with pytest.raises(KernelError):  # more splits than K blocks
+        ops.gemm_tc_rows(x[:4], ops.TensorMap(w, 128), 128, 128, torch.empty(4, 128, device=DEV), ops.TC_STORE_F32, splits=2)
+    with pytest.raises(KernelError):  # boxes of several K blocks over a width that is no multiple of 64
+        ops.TensorMap(_rand(128, 72, seed=3, dtype=torch.bfloat16), 128, 2)
+
+
 # -------------------------------------------- RMSNorm made inside the matrix product
 @pytest.mark.parametrize("m,n,k,n_part", [(1, 128, 64, 0), (8, 384, 4096, 4), (5, 256, 264, 2), (16, 256, 1032, 3),
                                           (11, 128, 512, 1)])
@@ -513,7 +669,7 @@ def test_gemm_tc_norm_store_and_gated(m, n, k, n_part):
     assert (y.double().cpu() - ref).abs().mean().item() < 4e-3 * ref.abs().max().item()
     g, u = _rand(n, k, seed=75, dtype=torch.bfloat16, scale=0.1), _rand(n, k, seed=76, dtype=torch.bfloat16, scale=0.1)
     act = torch.empty(m, n, dtype=torch.bfloat16, device=DEV)
-    ops.gemm_tc_norm(x, part, nw, 1e-5, ops.TensorMap(fuse_gate_up(g, u, 128), 256), n, act, ops.TC_GLU_BF16)
+    ops.gemm_tc_norm(x, part, nw, 1e-5, ops.TensorMap(fuse_gate_up(g, u), 128), n, act, ops.TC_GLU_BF16)
     gd, ud = h @ g.double().cpu().T, h @ u.double().cpu().T
     ref_act = gd / (1 + torch.exp(-gd)) * ud
     torch.testing.assert_close(act.double().cpu(), ref_act, rtol=3e-2, atol=3e-2 * ref_act.abs().max().item())
