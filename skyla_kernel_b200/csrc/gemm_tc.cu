@@ -561,6 +561,12 @@ constexpr int kRowsMaxStages = 24;
 // Asking the L2 for the next product's first boxes (cp.async.bulk.prefetch.tensor) once a block's own
 // loads are issued also measured slower: a decode step of the 8B shape took 4.09, 4.18, 4.25 ms with
 // 64, 128, 256 KB per block against 4.07 without.
+// Running the four products between two attention kernels (O, gate/up, down, the next QKV) as the
+// phases of ONE launch, a grid-wide barrier between them and the loader running on into the next
+// phase's weights, was built and measured too: 93 against 80 us per layer.  A phase's end costs the
+// same as a launch's (the epilogue's stores have to be visible before the barrier: 3 to 5 us, and the
+// barrier 2.4), and the 192 KB ring is full again 3.7 us after a phase's last box was asked for, so the
+// memory idles through most of that just the same.
 constexpr int kRowsSmemBytes = 212 * 1024;
 constexpr int kRowsMaxSplits = 8;
 
@@ -1099,7 +1105,10 @@ int launch_rows(const CUtensorMap& mw, const CUtensorMap& mx, const GemmArgs& a,
 
 // ------------------------------------------------------------------ persistent, for prompts
 // Many tokens: the kernel is bound by the tensor cores, so the epilogue must not cost
-// tensor time.  One block per SM walks the output tiles (tile = blockIdx.x, += gridDim.x;
+// tensor time.  (A gated tile of 256 tokens, which fills TMEM with one accumulator and so
+// cannot hide its epilogue, measured slower than two of 128: 385 against 311 us for 2048
+// tokens of the 8B shape.  Under load an MMA of 256 columns takes about 220 cycles at the
+// clock the power cap leaves, not the 128 of an idle tensor pipe.)  One block per SM walks the output tiles (tile = blockIdx.x, += gridDim.x;
 // tiles of one weight tile are neighbours, so concurrent blocks share it through L2).  TMEM
 // holds two accumulators: while the four epilogue warps drain tile i, the MMA warp already
 // works on tile i+1.  The TMA ring runs on across tile boundaries.

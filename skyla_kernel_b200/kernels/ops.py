@@ -420,9 +420,8 @@ def rows_plan(n_out: int, n_in: int, gated: bool = False, bn: int = 16):
     kstack = max(1, min(128 // rows, 256 // bn, n_kb))
     group = kstack * rows * 128                     # bytes of weights that one MMA takes
     per_box = max(1, min(-(-28 * 1024 // group), 16 // kstack, -(-n_kb // kstack)))
-    if bn > 16:                                      # wide token tiles: leave room for three stages
-        while per_box > 1 and per_box * kstack * (rows + bn) * 128 > 56 * 1024:
-            per_box -= 1
+    while per_box > 1 and per_box * kstack * (rows + bn) * 128 > 48 * 1024:
+        per_box -= 1                                 # four stages or more in the ring
     return rows, 1, per_box * kstack, kstack
 
 

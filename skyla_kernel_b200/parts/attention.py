@@ -99,8 +99,8 @@ class GQAttention(Part):
         """Into how many blocks a decode step cuts each sequence's context: (splits, pages per split).
 
         Two blocks share an SM (296 at a time); a block costs about three pages' time beside its
-        pages, and the merge of the splits about 0.7 for every eight of them (measured: a page
-        takes 1.2 us, a block's start and end 3.5, a round of the merge 0.8).  The count is fixed
+        pages, and every split about 0.3 more in the merge (fitted to measurements at batch 1 to
+        64: a page takes about 1 us, a block's start and end 3.5, a split 0.3).  The count is fixed
         per (batch, page-list width) so that a recorded launch keeps its grid; how many pages a
         split covers follows the step's longest sequence, which the kernel reads from device memory.
         """
@@ -108,7 +108,7 @@ class GQAttention(Part):
         typical = max(1.0, 0.75 * max_pages)
         best, best_cost = 1, None
         for n in range(1, max(1, min(32, max_pages // 2)) + 1):
-            cost = -(-items * n // 296) * (3.0 + typical / n) + 0.7 * -(-n // 8)
+            cost = -(-items * n // 296) * (3.0 + typical / n) + 0.3 * n
             if best_cost is None or cost < best_cost:
                 best, best_cost = n, cost
         return best, -(-max_pages // best)
