@@ -112,68 +112,86 @@ __global__ void __launch_bounds__(kWarps * 32) prep_kernel(PrepArgs a) {
 // size is a multiple of 32.  A lane owns hd/32 consecutive elements, so lanes 0-15 hold the
 // first half of the head and lane l+16 holds the rotation partners of lane l: loads and stores
 // are contiguous and the partner comes by one shuffle.
+constexpr int kHeadsPerWarp = 4;  // a warp finishes this many heads of one token: their loads are in flight together
 template <int EPL>  // elements per lane
 __global__ void __launch_bounds__(kWarps * 32) prep_bf16_kernel(PrepArgs a) {
   allow_dependents();
   grid_dependency_wait();
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int head = blockIdx.x * kWarps + warp, t = blockIdx.y;
-  const int hd = a.hd;
-  if (head >= a.nq + 2 * a.nkv) return;
-  const bool is_q = head < a.nq, is_k = !is_q && head < a.nq + a.nkv;
-  const int kvh = is_q ? 0 : (is_k ? head - a.nq : head - a.nq - a.nkv);
   typedef __nv_bfloat16 bf16;
-  const bf16* src = (const bf16*)a.qkv + (int64_t)t * a.ld +
-                    (is_q ? a.q_off + head * hd : (is_k ? a.k_off : a.v_off) + kvh * hd) + lane * EPL;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int head0 = (blockIdx.x * kWarps + warp) * kHeadsPerWarp, t = blockIdx.y;
+  const int hd = a.hd, n_heads = a.nq + 2 * a.nkv;
+  if (head0 >= n_heads) return;
   const int pos = a.tok_pos[t];
-  bf16* dst;
-  if (is_q) {
-    dst = (bf16*)a.q_out + (int64_t)t * a.ldq + head * hd + lane * EPL;
-  } else {
-    if (a.k_pool == nullptr) return;
-    const int page = a.page_table[(int64_t)a.tok_slot[t] * a.max_pages + pos / a.page_size];
-    dst = (bf16*)(is_k ? a.k_pool : a.v_pool) +
-          (((int64_t)page * a.nkv + kvh) * a.page_size + pos % a.page_size) * hd + lane * EPL;
+  const int page = a.k_pool != nullptr
+                       ? a.page_table[(int64_t)a.tok_slot[t] * a.max_pages + pos / a.page_size] : 0;
+  const bf16* src[kHeadsPerWarp];
+  bf16* dst[kHeadsPerWarp];
+  int kind[kHeadsPerWarp];  // 0 query, 1 key, 2 value, 3 nothing to do
+  bf16 raw[kHeadsPerWarp][EPL];
+#pragma unroll
+  for (int h = 0; h < kHeadsPerWarp; ++h) {
+    const int head = head0 + h;
+    const bool is_q = head < a.nq, is_k = !is_q && head < a.nq + a.nkv;
+    const int kvh = is_q ? 0 : (is_k ? head - a.nq : head - a.nq - a.nkv);
+    kind[h] = head >= n_heads ? 3 : (is_q ? 0 : (a.k_pool == nullptr ? 3 : (is_k ? 1 : 2)));
+    src[h] = (const bf16*)a.qkv + (int64_t)t * a.ld +
+             (is_q ? a.q_off + head * hd : (is_k ? a.k_off : a.v_off) + kvh * hd) + lane * EPL;
+    dst[h] = is_q ? (bf16*)a.q_out + (int64_t)t * a.ldq + head * hd + lane * EPL
+                  : (bf16*)(is_k ? a.k_pool : a.v_pool) +
+                        (((int64_t)page * a.nkv + kvh) * a.page_size + pos % a.page_size) * hd + lane * EPL;
+    if (kind[h] == 3) continue;
+    if (EPL == 4) *reinterpret_cast<uint2*>(raw[h]) = *reinterpret_cast<const uint2*>(src[h]);
+    else if (EPL == 2) *reinterpret_cast<uint32_t*>(raw[h]) = *reinterpret_cast<const uint32_t*>(src[h]);
+    else if (EPL == 8) *reinterpret_cast<uint4*>(raw[h]) = *reinterpret_cast<const uint4*>(src[h]);
+    else
+#pragma unroll
+      for (int i = 0; i < EPL; ++i) raw[h][i] = src[h][i];
   }
-  bf16 raw[EPL];
-  if (EPL == 4) *reinterpret_cast<uint2*>(raw) = *reinterpret_cast<const uint2*>(src);
-  else if (EPL == 2) *reinterpret_cast<uint32_t*>(raw) = *reinterpret_cast<const uint32_t*>(src);
-  else if (EPL == 8) *reinterpret_cast<uint4*>(raw) = *reinterpret_cast<const uint4*>(src);
-  else
+  // the rotation of this lane's pairs, the same for every head of the token
+  float cs[EPL], sn[EPL];
+  if (a.cos_t != nullptr) {
+    const int half = hd / 2;
 #pragma unroll
-    for (int i = 0; i < EPL; ++i) raw[i] = src[i];
-  if (is_q || is_k) {
-    float u[EPL];
-    float ss = 0.f;
-#pragma unroll
-    for (int i = 0; i < EPL; ++i) { u[i] = __bfloat162float(raw[i]); ss = fmaf(u[i], u[i], ss); }
-    const float* nw = is_q ? a.q_norm : a.k_norm;
-    if (nw != nullptr) {
-      ss = warp_sum(ss);
-      const float inv = 1.0f / sqrtf(ss / (float)hd + a.eps);
-#pragma unroll
-      for (int i = 0; i < EPL; ++i) u[i] *= inv * nw[lane * EPL + i];
+    for (int i = 0; i < EPL; ++i) {
+      const int j = (lane & 15) * EPL + i;  // index of the pair
+      cs[i] = a.cos_t[(int64_t)pos * half + j];
+      sn[i] = a.sin_t[(int64_t)pos * half + j];
     }
-    if (a.cos_t != nullptr) {
-      const int half = hd / 2;
-      const bool low = lane < 16;
+  }
 #pragma unroll
-      for (int i = 0; i < EPL; ++i) {
-        const float other = __shfl_xor_sync(0xffffffffu, u[i], 16);
-        const int j = (lane & 15) * EPL + i;  // index of the pair
-        const float c = a.cos_t[(int64_t)pos * half + j], s = a.sin_t[(int64_t)pos * half + j];
-        u[i] = low ? u[i] * c - other * s : other * s + u[i] * c;
+  for (int h = 0; h < kHeadsPerWarp; ++h) {
+    if (kind[h] == 3) continue;
+    if (kind[h] < 2) {
+      float u[EPL];
+      float ss = 0.f;
+#pragma unroll
+      for (int i = 0; i < EPL; ++i) { u[i] = __bfloat162float(raw[h][i]); ss = fmaf(u[i], u[i], ss); }
+      const float* nw = kind[h] == 0 ? a.q_norm : a.k_norm;
+      if (nw != nullptr) {
+        ss = warp_sum(ss);
+        const float inv = 1.0f / sqrtf(ss / (float)hd + a.eps);
+#pragma unroll
+        for (int i = 0; i < EPL; ++i) u[i] *= inv * nw[lane * EPL + i];
       }
+      if (a.cos_t != nullptr) {
+        const bool low = lane < 16;
+#pragma unroll
+        for (int i = 0; i < EPL; ++i) {
+          const float other = __shfl_xor_sync(0xffffffffu, u[i], 16);
+          u[i] = low ? u[i] * cs[i] - other * sn[i] : other * sn[i] + u[i] * cs[i];
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < EPL; ++i) raw[h][i] = __float2bfloat16_rn(u[i]);
     }
+    if (EPL == 4) *reinterpret_cast<uint2*>(dst[h]) = *reinterpret_cast<uint2*>(raw[h]);
+    else if (EPL == 2) *reinterpret_cast<uint32_t*>(dst[h]) = *reinterpret_cast<uint32_t*>(raw[h]);
+    else if (EPL == 8) *reinterpret_cast<uint4*>(dst[h]) = *reinterpret_cast<uint4*>(raw[h]);
+    else
 #pragma unroll
-    for (int i = 0; i < EPL; ++i) raw[i] = __float2bfloat16_rn(u[i]);
+      for (int i = 0; i < EPL; ++i) dst[h][i] = raw[h][i];
   }
-  if (EPL == 4) *reinterpret_cast<uint2*>(dst) = *reinterpret_cast<uint2*>(raw);
-  else if (EPL == 2) *reinterpret_cast<uint32_t*>(dst) = *reinterpret_cast<uint32_t*>(raw);
-  else if (EPL == 8) *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<uint4*>(raw);
-  else
-#pragma unroll
-    for (int i = 0; i < EPL; ++i) dst[i] = raw[i];
 }
 }  // namespace
 
@@ -203,15 +221,16 @@ extern "C" int skyla_qk_norm_rope_cache(
       row_ssq == nullptr && fold_x == nullptr && hd % 32 == 0 && hd <= 256 && (cos_t == nullptr || n_rot == hd) &&
       ld % 8 == 0 && ldq % 8 == 0 && q_off % 8 == 0 && k_off % 8 == 0 && v_off % 8 == 0 &&
       ((uintptr_t)qkv) % 16 == 0 && ((uintptr_t)q_out) % 16 == 0) {
+    const dim3 gridf((nq + 2 * nkv + kWarps * kHeadsPerWarp - 1) / (kWarps * kHeadsPerWarp), n_tokens);
     switch (hd / 32) {
-      case 1: launch_overlapped(prep_bf16_kernel<1>, grid, dim3(kWarps * 32), 0, stream, a); break;
-      case 2: launch_overlapped(prep_bf16_kernel<2>, grid, dim3(kWarps * 32), 0, stream, a); break;
-      case 3: launch_overlapped(prep_bf16_kernel<3>, grid, dim3(kWarps * 32), 0, stream, a); break;
-      case 4: launch_overlapped(prep_bf16_kernel<4>, grid, dim3(kWarps * 32), 0, stream, a); break;
-      case 5: launch_overlapped(prep_bf16_kernel<5>, grid, dim3(kWarps * 32), 0, stream, a); break;
-      case 6: launch_overlapped(prep_bf16_kernel<6>, grid, dim3(kWarps * 32), 0, stream, a); break;
-      case 7: launch_overlapped(prep_bf16_kernel<7>, grid, dim3(kWarps * 32), 0, stream, a); break;
-      default: launch_overlapped(prep_bf16_kernel<8>, grid, dim3(kWarps * 32), 0, stream, a); break;
+      case 1: launch_overlapped(prep_bf16_kernel<1>, gridf, dim3(kWarps * 32), 0, stream, a); break;
+      case 2: launch_overlapped(prep_bf16_kernel<2>, gridf, dim3(kWarps * 32), 0, stream, a); break;
+      case 3: launch_overlapped(prep_bf16_kernel<3>, gridf, dim3(kWarps * 32), 0, stream, a); break;
+      case 4: launch_overlapped(prep_bf16_kernel<4>, gridf, dim3(kWarps * 32), 0, stream, a); break;
+      case 5: launch_overlapped(prep_bf16_kernel<5>, gridf, dim3(kWarps * 32), 0, stream, a); break;
+      case 6: launch_overlapped(prep_bf16_kernel<6>, gridf, dim3(kWarps * 32), 0, stream, a); break;
+      case 7: launch_overlapped(prep_bf16_kernel<7>, gridf, dim3(kWarps * 32), 0, stream, a); break;
+      default: launch_overlapped(prep_bf16_kernel<8>, gridf, dim3(kWarps * 32), 0, stream, a); break;
     }
     return check_launch("qk_norm_rope_cache");
   }

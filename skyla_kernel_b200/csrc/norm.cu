@@ -94,11 +94,13 @@ extern "C" int skyla_fold_partials(float* x, int64_t ldx, const float* part, int
   return check_launch("fold_partials");
 }
 
-// float32 rows whose width is a multiple of 4 and that start on 16 bytes: four elements per load.
-template <typename TO>
+// float32 rows whose width is a multiple of 4 and that start on 16 bytes: four elements per load,
+// kept in registers between the two passes (up to kKeep loads a thread; wider rows are read again),
+// four bfloat16 per store.
+constexpr int kKeep = 4;
 __global__ void rmsnorm_vec4_kernel(const float* __restrict__ x, int64_t ldx, const int32_t* __restrict__ rows,
-                                    int width, const float* __restrict__ w, float eps, TO* __restrict__ out,
-                                    int64_t ldo) {
+                                    int width, const float* __restrict__ w, float eps,
+                                    __nv_bfloat16* __restrict__ out, int64_t ldo) {
   __shared__ float scratch[32];
   allow_dependents();
   grid_dependency_wait();
@@ -106,21 +108,36 @@ __global__ void rmsnorm_vec4_kernel(const float* __restrict__ x, int64_t ldx, co
   const float4* xr = reinterpret_cast<const float4*>(x + (int64_t)(rows ? rows[r] : r) * ldx);
   const float4* wr = reinterpret_cast<const float4*>(w);
   const int n4 = width / 4;
+  float4 keep[kKeep];
   float ss = 0.f;
-  for (int i = threadIdx.x; i < n4; i += blockDim.x) {
+#pragma unroll
+  for (int j = 0; j < kKeep; ++j) {
+    const int i = threadIdx.x + j * blockDim.x;
+    if (i < n4) {
+      const float4 v = xr[i];
+      keep[j] = v;
+      ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
+    }
+  }
+  for (int i = threadIdx.x + kKeep * blockDim.x; i < n4; i += blockDim.x) {
     const float4 v = xr[i];
     ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
   }
   ss = block_sum(ss, scratch);
   const float inv = 1.0f / sqrtf(ss / (float)width + eps);
-  TO* o = out + (int64_t)r * ldo;
-  for (int i = threadIdx.x; i < n4; i += blockDim.x) {
-    const float4 v = xr[i], g = wr[i];
-    o[4 * i] = from_float<TO>(v.x * inv * g.x);
-    o[4 * i + 1] = from_float<TO>(v.y * inv * g.y);
-    o[4 * i + 2] = from_float<TO>(v.z * inv * g.z);
-    o[4 * i + 3] = from_float<TO>(v.w * inv * g.w);
+  uint2* o = reinterpret_cast<uint2*>(out + (int64_t)r * ldo);
+  auto put = [&](int i, const float4& v) {
+    const float4 g = wr[i];
+    __nv_bfloat162 lo = __floats2bfloat162_rn(v.x * inv * g.x, v.y * inv * g.y);
+    __nv_bfloat162 hi = __floats2bfloat162_rn(v.z * inv * g.z, v.w * inv * g.w);
+    o[i] = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+  };
+#pragma unroll
+  for (int j = 0; j < kKeep; ++j) {
+    const int i = threadIdx.x + j * blockDim.x;
+    if (i < n4) put(i, keep[j]);
   }
+  for (int i = threadIdx.x + kKeep * blockDim.x; i < n4; i += blockDim.x) put(i, xr[i]);
 }
 
 extern "C" int skyla_rmsnorm(const void* x, int x_dtype, int64_t ldx, const int32_t* rows,
@@ -133,9 +150,11 @@ extern "C" int skyla_rmsnorm(const void* x, int x_dtype, int64_t ldx, const int3
   const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
   // the vector kernel adds a row's squares in another order than the scalar one: it serves the
   // 16-bit path only, so that the 32-bit path keeps one order for every way of calling it
-  if (x_dtype == kF32 && out_dtype == kBF16 && width % 4 == 0 && ldx % 4 == 0 && ((uintptr_t)x) % 16 == 0 &&
-      ((uintptr_t)weight) % 16 == 0) {
-    launch_overlapped(rmsnorm_vec4_kernel<__nv_bfloat16>, dim3(n_rows), dim3(threads), 0, stream, (const float*)x, ldx,
+  if (x_dtype == kF32 && out_dtype == kBF16 && width % 4 == 0 && ldx % 4 == 0 && ldo % 4 == 0 &&
+      ((uintptr_t)x) % 16 == 0 && ((uintptr_t)weight) % 16 == 0 && ((uintptr_t)out) % 8 == 0) {
+    // few threads a row where the row is short, so that every thread has a load or two in flight
+    const int vthreads = width >= 4096 ? 256 : 128;
+    launch_overlapped(rmsnorm_vec4_kernel, dim3(n_rows), dim3(vthreads), 0, stream, (const float*)x, ldx,
                       rows, width, weight, eps, (__nv_bfloat16*)out, ldo);
     return check_launch("rmsnorm");
   }
