@@ -533,21 +533,24 @@ __global__ void __launch_bounds__(kDecodeWarps * 32, 2) attn_decode_kernel(Decod
   if (tl && threadIdx.x == 0) tl[6] = clock64();
   if (!merges) return;
   __threadfence();
-  // Every partial is a round trip to the L2, so they are asked for eight splits at a time, all
-  // at once, and then folded into the running (maximum, sum, row) in the order of the splits.
-  for (int idx = threadIdx.x; idx < G * HD; idx += NW * 32) {
-    const int r = idx / HD, c = idx % HD, h = kvh * G + r;
+  // Every partial is a round trip to the L2, so a thread asks for all of its own at once: two
+  // columns of one head, eight splits at a time, folded into the running (maximum, sum, row) in
+  // the order of the splits.
+  for (int idx = threadIdx.x; idx < G * (HD / 2); idx += NW * 32) {
+    const int r = idx / (HD / 2), c = 2 * (idx % (HD / 2)), h = kvh * G + r;
     const float* p = a.part + ((size_t)b * a.nq + h) * a.n_splits * (HD + 2);
-    float M = -INFINITY, total = 0.f, o = 0.f;
+    float M = -INFINITY, total = 0.f, o0 = 0.f, o1 = 0.f;
     for (int s0 = 0; s0 < a.n_splits; s0 += 8) {
-      float m8[8], l8[8], o8[8];
+      float m8[8], l8[8];
+      float2 o8[8];
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         const bool in = s0 + j < a.n_splits;
         const float* ps = p + (size_t)(s0 + j) * (HD + 2);
-        m8[j] = in ? __ldcg(ps) : -INFINITY;
-        l8[j] = in ? __ldcg(ps + 1) : 0.f;
-        o8[j] = in ? __ldcg(ps + 2 + c) : 0.f;
+        const float2 ml = in ? __ldcg(reinterpret_cast<const float2*>(ps)) : make_float2(-INFINITY, 0.f);
+        m8[j] = ml.x;
+        l8[j] = ml.y;
+        o8[j] = in ? __ldcg(reinterpret_cast<const float2*>(ps + 2 + c)) : make_float2(0.f, 0.f);
       }
       float Mn = M;
 #pragma unroll
@@ -555,16 +558,19 @@ __global__ void __launch_bounds__(kDecodeWarps * 32, 2) attn_decode_kernel(Decod
       if (Mn == -INFINITY) continue;
       const float keep = exp2f(M - Mn);  // 0 for the first chunk (M is -inf)
       total *= keep;
-      o *= keep;
+      o0 *= keep;
+      o1 *= keep;
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         const float f = exp2f(m8[j] - Mn);
         total += f * l8[j];
-        o += f * o8[j];
+        o0 += f * o8[j].x;
+        o1 += f * o8[j].y;
       }
       M = Mn;
     }
-    a.out[(int64_t)b * a.ldo + (int64_t)h * HD + c] = __float2bfloat16_rn(o / total);
+    *reinterpret_cast<__nv_bfloat162*>(a.out + (int64_t)b * a.ldo + (int64_t)h * HD + c) =
+        __floats2bfloat162_rn(o0 / total, o1 / total);
   }
   if (tl && threadIdx.x == 0) tl[7] = clock64();
 }

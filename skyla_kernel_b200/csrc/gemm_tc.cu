@@ -986,10 +986,16 @@ gemm_tc_rows_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     }
     if (ahead) {  // this block's share of the new rows' sums of squares, added up in a fixed order
       asm volatile("barrier.sync 1, 128;" ::: "memory");
-      if (ok && et < a.M) {
+      // a warp per token: lanes take the rows 32 apart, then a butterfly (one order whatever the batch)
+      for (int tok = warp - 2; ok && tok < a.M; tok += 4) {
         float v = 0.f;
-        for (int rr = 0; rr < R; ++rr) v += sqbuf[et * R + rr];
-        a.ahead.ssq_part[(int64_t)blockIdx.x * a.M + et] = v;
+        for (int rr = lane; rr < R; rr += 32) v += sqbuf[tok * R + rr];
+        v += __shfl_xor_sync(0xffffffffu, v, 16);
+        v += __shfl_xor_sync(0xffffffffu, v, 8);
+        v += __shfl_xor_sync(0xffffffffu, v, 4);
+        v += __shfl_xor_sync(0xffffffffu, v, 2);
+        v += __shfl_xor_sync(0xffffffffu, v, 1);
+        if (lane == 0) a.ahead.ssq_part[(int64_t)blockIdx.x * a.M + tok] = v;
       }
     }
   }
