@@ -125,7 +125,8 @@ struct RowState {
 
 // 16 keys starting at absolute position key0; k16/v16 point at their rows for one
 // key/value head, staged in shared memory.  Rows g and g+8 of the tile see positions lo..hi.
-template <int HD>
+// MASKED = false: every row sees all 16 keys (the caller has checked), so no position is compared.
+template <int HD, bool MASKED = true>
 __device__ __forceinline__ void attend16(const uint32_t (&qa)[Shape<HD>::NQ], const uint32_t (&qb)[Shape<HD>::NQ],
                                          const bf16* __restrict__ k16, const bf16* __restrict__ v16, int key0,
                                          int lo0, int hi0, int lo1, int hi1, float scale_log2, RowState<HD>& st,
@@ -156,11 +157,15 @@ __device__ __forceinline__ void attend16(const uint32_t (&qa)[Shape<HD>::NQ], co
   float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
   for (int j = 0; j < 2; ++j) {
-    const int p = key0 + 8 * j + 2 * t;
-    s[j][0] = (p >= lo0 && p <= hi0) ? s[j][0] * scale_log2 : -INFINITY;
-    s[j][1] = (p + 1 >= lo0 && p + 1 <= hi0) ? s[j][1] * scale_log2 : -INFINITY;
-    s[j][2] = (p >= lo1 && p <= hi1) ? s[j][2] * scale_log2 : -INFINITY;
-    s[j][3] = (p + 1 >= lo1 && p + 1 <= hi1) ? s[j][3] * scale_log2 : -INFINITY;
+    if (MASKED) {
+      const int p = key0 + 8 * j + 2 * t;
+      s[j][0] = (p >= lo0 && p <= hi0) ? s[j][0] * scale_log2 : -INFINITY;
+      s[j][1] = (p + 1 >= lo0 && p + 1 <= hi0) ? s[j][1] * scale_log2 : -INFINITY;
+      s[j][2] = (p >= lo1 && p <= hi1) ? s[j][2] * scale_log2 : -INFINITY;
+      s[j][3] = (p + 1 >= lo1 && p + 1 <= hi1) ? s[j][3] * scale_log2 : -INFINITY;
+    } else {
+      s[j][0] *= scale_log2; s[j][1] *= scale_log2; s[j][2] *= scale_log2; s[j][3] *= scale_log2;
+    }
     mx0 = fmaxf(mx0, fmaxf(s[j][0], s[j][1]));
     mx1 = fmaxf(mx1, fmaxf(s[j][2], s[j][3]));
   }
@@ -482,7 +487,10 @@ __global__ void __launch_bounds__(kDecodeWarps * 32, 2) attn_decode_kernel(Decod
     }
     const bf16* sk = stages + (size_t)(pg % kStages) * Stage<HD>::kElems;
     const int key0 = (page_begin + pg) * kPage + 16 * warp;  // this warp's 16 positions
-    if (key0 <= pos && key0 + 15 >= first)
+    if (key0 + 15 <= pos && key0 >= first)  // all 16 keys are visible: nothing to mask
+      attend16<HD, false>(qa, qb, sk + 16 * warp * RS, sk + (kPage + 16 * warp) * RS, key0, first, hi0, first, hi1,
+                          scale_log2, st, g, t);
+    else if (key0 <= pos && key0 + 15 >= first)
       attend16<HD>(qa, qb, sk + 16 * warp * RS, sk + (kPage + 16 * warp) * RS, key0, first, hi0, first, hi1,
                    scale_log2, st, g, t);
     __syncthreads();  // the stage is refilled in the next round
@@ -649,6 +657,7 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(PrefillArgs a) {
   const bool warp_live = warp * 16 < rows;
   const int w_first = pos_first + warp * 16, w_last = min(pos_last, w_first + 15);
   const int wlo = a.window > 0 ? max(0, w_first - a.window + 1) : 0, whi = w_last;
+  const int whi_lo = a.window > 0 ? max(0, w_first + 15 - a.window + 1) : 0;  // the lowest key the warp's last row sees
   const float scale_log2 = a.scale * kLog2e;
 
   RowState<HD> st;
@@ -664,7 +673,12 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(PrefillArgs a) {
         const int key0 = (page_begin + i) * kPage + off;
         if (key0 > whi) break;
         if (key0 + 15 < wlo) continue;
-        attend16<HD>(qa, qb, sk + off * RS, sk + (kPage + off) * RS, key0, lo0, hi0, lo1, hi1, scale_log2, st, g, t);
+        // all 16 keys lie before the warp's first row and inside the window of its last: nothing to mask
+        // (rows past the tile's end then compute on zeros; they are never stored)
+        if (key0 + 15 <= w_first && key0 >= whi_lo)
+          attend16<HD, false>(qa, qb, sk + off * RS, sk + (kPage + off) * RS, key0, lo0, hi0, lo1, hi1, scale_log2, st, g, t);
+        else
+          attend16<HD>(qa, qb, sk + off * RS, sk + (kPage + off) * RS, key0, lo0, hi0, lo1, hi1, scale_log2, st, g, t);
       }
     }
     __syncthreads();
