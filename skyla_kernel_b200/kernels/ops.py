@@ -694,8 +694,29 @@ def attention_prefill(q: torch.Tensor, out: torch.Tensor, nq: int, nkv: int, hd:
                       v_pool: torch.Tensor, pages: torch.Tensor, page_size: int, tok_pos: torch.Tensor,
                       tile_seq: torch.Tensor, tile_tok0: torch.Tensor, tile_rows: torch.Tensor, scale: float,
                       window: int = 0) -> torch.Tensor:
-    """Causal attention of new tokens in tiles of up to 64 tokens of one sequence."""
+    """Causal attention of new tokens in tiles of up to 64 tokens of one sequence.  Heads of 128 with an
+    even number of query heads per key/value head run on the tcgen05 kernel (``PREFILL_TC``), the
+    others on the mma.sync one."""
     _attn_common(q, out, k_pool, v_pool, nq, nkv, hd, page_size, pages, tok_pos, tile_seq, tile_tok0, tile_rows)
+    if (PREFILL_TC and hd == 128 and page_size == 64 and (nq // nkv) % 2 == 0 and q.dtype == torch.bfloat16
+            and q.stride(1) == 1 and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0 and q.shape[1] == nq * hd
+            and out.stride(0) % 8 == 0 and out.data_ptr() % 16 == 0):
+        key = (k_pool.data_ptr(), v_pool.data_ptr(), k_pool.numel())
+        maps = _POOL_MAPS.get(key)
+        if maps is None:
+            if len(_POOL_MAPS) > 1024:
+                _POOL_MAPS.clear()
+            maps = _POOL_MAPS[key] = (TensorMap(k_pool.view(-1, hd), 64, 2), TensorMap(v_pool.view(-1, hd), 64, 2))
+            maps[0].keep = maps[1].keep = None  # the key holds the addresses; do not pin the pools
+        q_map = activation_map(q, 64)
+        f = _fn("attention_tc", "skyla_attention_prefill_tc",
+                [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_void_p, c_int, c_int,
+                 c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_int, c_void_p, c_void_p])
+        _check("attention_tc", f(q_map.buf, maps[0].buf, maps[1].buf, _ptr(out), _rows(out, "out"), tile_seq.numel(), nq,
+                                 nkv, hd, _ptr(pages), pages.shape[1], page_size, _ptr(tok_pos), _ptr(tile_seq),
+                                 _ptr(tile_tok0), _ptr(tile_rows), float(scale), int(window or 0),
+                                 _ptr(error_flag(q.device)), _stream()))
+        return out
     f = _fn("attention_mma", "skyla_attention_prefill",
             [c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
              c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_int, c_void_p])
@@ -704,6 +725,10 @@ def attention_prefill(q: torch.Tensor, out: torch.Tensor, nq: int, nkv: int, hd:
                               _ptr(tile_seq), _ptr(tile_tok0), _ptr(tile_rows), float(scale), int(window or 0),
                               _stream()))
     return out
+
+
+PREFILL_TC = __import__("os").environ.get("SKYLA_PREFILL_TC", "1") != "0"
+_POOL_MAPS = {}
 
 
 # ------------------------------------------------------------------- sampling

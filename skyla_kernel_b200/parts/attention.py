@@ -32,7 +32,7 @@ from .linear import ACCUMULATE, STORE, Linear
 class GQAttention(Part):
     graph_safe = True
     takes_normed_input = True
-    kernel_modules = Linear.kernel_modules + ("attn_prep", "attention_plain", "attention_mma")
+    kernel_modules = Linear.kernel_modules + ("attn_prep", "attention_plain", "attention_mma", "attention_tc")
 
     def __init__(self, spec, rt):
         super().__init__(spec, rt)

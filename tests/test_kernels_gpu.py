@@ -407,6 +407,77 @@ def test_attention_prefill_mma(nq, nkv, hd, window):
         torch.testing.assert_close(out[i].float().cpu().view(nq, hd), ref.float(), rtol=2e-2, atol=2e-2)
 
 
+@pytest.mark.parametrize("nq,nkv,window", [(2, 1, 0), (4, 2, 0), (12, 2, 0), (16, 2, 130), (8, 8, 0), (6, 2, 0)])
+def test_attention_prefill_tcgen05_against_mma_sync_and_plain(nq, nkv, window):
+    """Heads of 128 with an even group run on the tcgen05 kernel (two heads a block, P V with V as it
+    lies in the cache); odd groups and (8, 8) stay on mma.sync.  Both against the plain kernel, on
+    prompts that start inside a page, end inside one, continue a cached prefix, and a lone token."""
+    ops = _ops()
+    dt, hd = torch.bfloat16, 128
+    spans = [(0, 200), (37, 64), (0, 1), (64, 129), (250, 70), (3, 5)]
+    lens = [s + n for s, n in spans]
+    k_pool, v_pool, table, ks, vs = _paged(len(lens), lens, nkv, hd, dt, seed=nq * 3 + nkv)
+    tok_pos, tok_seq, tile_seq, tile_tok0, tile_rows = [], [], [], [], []
+    for b, (s0, n) in enumerate(spans):
+        for j in range(0, n, 64):
+            tile_seq.append(b); tile_tok0.append(len(tok_pos) + j); tile_rows.append(min(64, n - j))
+        tok_pos += list(range(s0, s0 + n)); tok_seq += [b] * n
+    T = len(tok_pos)
+    q = _rand(T, nq * hd, seed=44, dtype=dt)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    scale = 1.0 / math.sqrt(hd)
+    args = (nq, nkv, hd, k_pool, v_pool, table, 64, i32(tok_pos), i32(tile_seq), i32(tile_tok0), i32(tile_rows), scale, window)
+    outs = {}
+    for tc in (True, False):
+        ops.PREFILL_TC = tc
+        try:
+            out = torch.full((T, nq * hd), float("nan"), dtype=dt, device=DEV)
+            before = ops.LAUNCHES
+            ops.attention_prefill(q, out, *args)
+            assert ops.LAUNCHES == before + 1
+            outs[tc] = out
+        finally:
+            ops.PREFILL_TC = True
+    plain_out = torch.empty_like(outs[True])
+    ops.attention_plain(q, plain_out, nq, nkv, hd, k_pool, v_pool, table, 64, i32(tok_pos), i32(tok_seq), scale, window)
+    for out in outs.values():
+        assert torch.isfinite(out.float()).all()
+        torch.testing.assert_close(out.float(), plain_out.float(), rtol=2e-2, atol=2e-2)
+    for i in (0, 199, 200, 263, T - 1, T - 6, T - 75):
+        ref = _attn_ref(q[i].cpu().view(nq, hd), ks[tok_seq[i]], vs[tok_seq[i]], tok_pos[i], nq, nkv, scale, window)
+        torch.testing.assert_close(outs[True][i].float().cpu().view(nq, hd), ref.float(), rtol=2e-2, atol=2e-2)
+    ops.check_device_errors(DEV)
+
+
+def test_attention_prefill_tcgen05_finds_one_far_key_and_respects_the_causal_edge():
+    """One key far back that dominates, and keys just past each row's own position that would dominate
+    if they were seen: the tcgen05 kernel's masks and its lazily rescaled accumulator."""
+    ops = _ops()
+    dt, nq, nkv, hd, L = torch.bfloat16, 4, 2, 128, 700
+    k_pool, v_pool, table, ks, vs = _paged(1, [L], nkv, hd, dt, seed=9)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    start = L - 150  # the last 150 tokens are new
+    tok_pos = list(range(start, L))
+    tile_seq, tile_tok0, tile_rows = [0, 0, 0], [0, 64, 128], [64, 64, 22]
+    q = _rand(len(tok_pos), nq * hd, seed=13, dtype=dt)
+    scale = 1.0 / math.sqrt(hd)
+    for target in (3, 63, 64, start - 1, start + 70):
+        kp = k_pool.clone()
+        page, off = int(table[0, target // 64]), target % 64
+        kp[page, :, off, :] = 6.0 * torch.sign(q[-1].view(nq, hd)[0]).to(dt)  # every query head leans on this key
+        out = torch.empty(len(tok_pos), nq * hd, dtype=dt, device=DEV)
+        ops.attention_prefill(q, out, nq, nkv, hd, kp, v_pool, table, 64, i32(tok_pos), i32(tile_seq), i32(tile_tok0),
+                              i32(tile_rows), scale, 0)
+        plain_out = torch.empty_like(out)
+        ops.attention_plain(q, plain_out, nq, nkv, hd, kp, v_pool, table, 64, i32(tok_pos), i32([0] * len(tok_pos)), scale, 0)
+        torch.testing.assert_close(out.float(), plain_out.float(), rtol=2e-2, atol=2e-2)
+        # rows before the target (when it is a new token) must not have seen it
+        if target >= start:
+            row = target - start - 1
+            assert (out[row].float() - plain_out[row].float()).abs().max().item() < 2e-2
+    ops.check_device_errors(DEV)
+
+
 def test_attention_mma_finds_one_far_key():
     ops = _ops()
     dt = torch.bfloat16
