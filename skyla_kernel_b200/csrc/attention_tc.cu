@@ -9,13 +9,17 @@
 //   S[128 x 64]  = Q K^T      8 MMAs (M 128, N 64, K 16): Q from shared memory (loaded once), the
 //                             page's K as it lies in the cache (keys are rows: K-major)
 //   softmax                   a thread owns a row: it reads its 64 scores from TMEM, masks, keeps the
-//                             running maximum and sum, and writes P (bfloat16) to shared memory
-//   O[128 x 128] += P V       4 MMAs (M 128, N 128, K 16): the page's V as it lies in the cache is an
-//                             "MN-major" operand (keys are the K dimension, a head's elements contiguous)
-// Warp 0 loads (TMA, a ring of four K+V pages), warp 1 issues the MMAs, warps 2-5 are the 128 rows.
-// S and P are double-buffered, so Q K^T of the next page and P V of the page before run while the
-// rows work on this one; O stays in TMEM and is rescaled there only when a row's maximum moved
-// (then the rows wait for P V of the page before).  Every wait is bounded.
+//                             running reference and sum, and writes P (bfloat16) back over them
+//   O[128 x 128] += P V       4 MMAs (M 128, N 128, K 16): P straight from TMEM; the page's V as it lies
+//                             in the cache is an "MN-major" operand (keys are the K dimension, a
+//                             head's elements contiguous)
+// Warp 0 loads (TMA, a ring of four tiles: K and V pages have slots and barriers of their own, so a
+// K page's slot is free as soon as Q K^T has read it), warp 1 issues the MMAs, warps 2-5 are the 128
+// rows.  S/P is double-buffered, so Q K^T of the next page and P V of the page before run while the
+// rows work on this one; O stays in TMEM and is rescaled there only when a score exceeds the
+// exponents' reference by more than kSlack (then the rows wait for P V of the page before).  Two
+// blocks share an SM (96 KB of shared memory and 256 TMEM columns each): one's waits are the
+// other's work.  Every wait is bounded.
 #include <cuda.h>
 
 #include <cstring>
@@ -31,14 +35,12 @@ typedef __nv_bfloat16 bf16;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kSlack = 8.f;  // log2 units a score may exceed the exponents' reference by before O is rescaled
 constexpr int kPage = 64, kHD = 128, kRows = 128;
-constexpr int kStages = 4;
+constexpr int kSlots = 4;                         // tiles (a page of K or a page of V) in flight
 constexpr int kQBytes = kRows * kHD * 2;          // [2 halves of the head][128 rows][128 bytes]
-constexpr int kPBytes = kRows * kPage * 2;        // [128 rows][64 keys]
 constexpr int kPageBytes = kPage * kHD * 2;       // one page of K or of V: [2 halves][64 keys][128 bytes]
-constexpr int kStageBytes = 2 * kPageBytes;       // K then V
 constexpr int kThreads = 192;
-constexpr int kSmemBytes = 1024 + kQBytes + 2 * kPBytes + kStages * kStageBytes + 256;
-constexpr uint32_t kTmemCols = 256;               // S twice (64 columns each), then O (128)
+constexpr int kSmemBytes = 1024 + kQBytes + kSlots * kPageBytes + 256;
+constexpr uint32_t kTmemCols = 256;               // S/P twice (64 columns each), then O (128)
 
 // 2^x by the hardware's approximation (x = -inf gives 0): one instruction a score
 __device__ __forceinline__ float fast_exp2(float x) {
@@ -54,26 +56,34 @@ struct PrefillTcArgs {
   float scale; int window; int* error_flag;
 };
 
-__global__ void __launch_bounds__(kThreads, 1)
+__device__ __forceinline__ void umma_bf16_tmem_a(uint32_t d_tmem, uint32_t a_tmem, uint64_t b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b), "r"(idesc), "r"(accumulate) : "memory");
+}
+
+__global__ void __launch_bounds__(kThreads, 2)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                        const __grid_constant__ CUtensorMap map_v, const PrefillTcArgs a) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ uint32_t tmem_base_slot;
   __shared__ volatile int abort_flag;
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const uint32_t q_smem = base, p_smem = base + kQBytes, ring = p_smem + 2 * kPBytes;  // P twice
-  const uint32_t bars = ring + kStages * kStageBytes;
+  const uint32_t q_smem = base, ring = base + kQBytes;
+  const uint32_t bars = ring + kSlots * kPageBytes;
   const uint32_t q_full = bars;
-  // Two barriers each for "P written" and "P V done", used by even and odd pages in turn.  The rows may
-  // be a page ahead of the MMAs and a warp of rows a page ahead of another; a parity wait can tell
-  // neither two phases ahead from none nor two behind from none, and a barrier counts arrivals, not who
-  // arrives.  With one barrier per buffer of P nobody is ever more than one phase away from it.
+  // "P written" and "P V done" have a barrier per buffer of S/P, used by even and odd pages in turn.
+  // A warp of rows may be a page ahead of another, and a barrier counts arrivals, not who arrives; and
+  // a parity wait cannot tell two phases ahead or behind from none.  With a barrier per buffer nobody
+  // is ever more than one phase away from it: the rows get page i's scores only after P V of page i-2
+  // is through (the tensor pipe runs Q K^T of page i behind it).
   auto o_done = [&](int b) { return bars + 8 + 8u * b; };
   auto p_full = [&](int b) { return bars + 24 + 8u * b; };
-  auto kv_full = [&](int s) { return bars + 40 + 8u * s; };
-  auto kv_empty = [&](int s) { return bars + 40 + 8u * (kStages + s); };
-  auto s_full = [&](int b) { return bars + 40 + 8u * (2 * kStages + b); };
-  auto s_free = [&](int b) { return bars + 40 + 8u * (2 * kStages + 2 + b); };
+  auto s_full = [&](int b) { return bars + 40 + 8u * b; };
+  auto t_full = [&](int s) { return bars + 56 + 8u * s; };            // tile ring: K0, V0, K1, V1, ..
+  auto t_empty = [&](int s) { return bars + 56 + 8u * (kSlots + s); };
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   // a sequence's later tiles see more keys: they go first, so that the short ones fill the end
@@ -87,11 +97,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   if (threadIdx.x == 0) {
     abort_flag = 0;
     mbar_init(q_full, 1);
-    for (int s = 0; s < kStages; ++s) { mbar_init(kv_full(s), 1); mbar_init(kv_empty(s), 1); }
+    for (int s = 0; s < kSlots; ++s) { mbar_init(t_full(s), 1); mbar_init(t_empty(s), 1); }
     for (int i = 0; i < 2; ++i) {
       mbar_init(s_full(i), 1);
-      mbar_init(s_free(i), 4);  // one arrival per warp of rows
-      mbar_init(p_full(i), 4);
+      mbar_init(p_full(i), 4);  // one arrival per warp of rows
       mbar_init(o_done(i), 1);
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -119,24 +128,23 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                       (h0 + head) * kHD + half * 64, tok0);
       uint32_t armed = 0, armed_parity = 0;
       bool ok = true;
-      for (int i = 0; i < n_pages; ++i) {
-        const int s = i % kStages;
-        const uint32_t round = (uint32_t)(i / kStages) & 1u;
-        if (!mbar_wait(kv_empty(s), round ^ 1u, &abort_flag, a.error_flag, 11)) { ok = false; break; }
-        const int row = (seq_pages[page_begin + i] * a.nkv + kvh) * kPage;
-        mbar_expect_tx(kv_full(s), kStageBytes);
+      for (int t = 0; t < 2 * n_pages; ++t) {  // tile t: K of page t/2 (even t) or V of it (odd t)
+        const int s = t % kSlots;
+        const uint32_t round = (uint32_t)(t / kSlots) & 1u;
+        if (!mbar_wait(t_empty(s), round ^ 1u, &abort_flag, a.error_flag, 11)) { ok = false; break; }
+        const int row = (seq_pages[page_begin + (t >> 1)] * a.nkv + kvh) * kPage;
+        mbar_expect_tx(t_full(s), kPageBytes);
         armed |= 1u << s;
         armed_parity = (armed_parity & ~(1u << s)) | (round << s);
-        tma_load_3d(ring + s * kStageBytes, &map_k, kv_full(s), 0, row, 0);
-        tma_load_3d(ring + s * kStageBytes + kPageBytes, &map_v, kv_full(s), 0, row, 0);
+        tma_load_3d(ring + s * kPageBytes, (t & 1) ? &map_v : &map_k, t_full(s), 0, row, 0);
       }
       if (!ok) {  // gave up: let the loads in flight land before the block's memory goes away
         const long long t0 = clock64();
         while (!mbar_try_wait(q_full, 0) && clock64() - t0 < kWaitCycles / 16) {}
-        for (int s = 0; s < kStages; ++s)
+        for (int s = 0; s < kSlots; ++s)
           if (armed & (1u << s)) {
             const long long t1 = clock64();
-            while (!mbar_try_wait(kv_full(s), (armed_parity >> s) & 1) && clock64() - t1 < kWaitCycles / 16) {}
+            while (!mbar_try_wait(t_full(s), (armed_parity >> s) & 1) && clock64() - t1 < kWaitCycles / 16) {}
           }
       }
     }
@@ -146,35 +154,37 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       const uint32_t idesc_qk = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kPage >> 3) << 17) | ((uint32_t)(kRows >> 4) << 24);
       const uint32_t idesc_pv = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) |  // B (the page of V) is MN-major
                                 ((uint32_t)(kHD >> 3) << 17) | ((uint32_t)(kRows >> 4) << 24);
+      const uint64_t q_desc0 = umma_desc(q_smem), q_desc1 = umma_desc(q_smem + kRows * 128);
       bool ok = mbar_wait(q_full, 0, &abort_flag, a.error_flag, 12);
       auto issue_qk = [&](int i) -> bool {
-        const int s = i % kStages, buf = i & 1;
-        if (!mbar_wait(kv_full(s), (uint32_t)(i / kStages) & 1u, &abort_flag, a.error_flag, 13)) return false;
-        // the rows must have read this buffer's scores of two pages ago
-        if (!mbar_wait(s_free(buf), ((uint32_t)(i >> 1) & 1u) ^ 1u, &abort_flag, a.error_flag, 14)) return false;
+        const int t = 2 * i, s = t % kSlots, buf = i & 1;
+        if (!mbar_wait(t_full(s), (uint32_t)(t / kSlots) & 1u, &abort_flag, a.error_flag, 13)) return false;
+        // S/P buffer `buf` held page i-2: its P V was issued before this, and the pipe keeps the order
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t k_smem = ring + s * kStageBytes;
+        const uint32_t k_smem = ring + s * kPageBytes;
+        const uint64_t k_desc0 = umma_desc(k_smem), k_desc1 = umma_desc(k_smem + kPage * 128);
 #pragma unroll
-        for (int half = 0; half < 2; ++half)
+        for (int k = 0; k < 4; ++k) umma_bf16(tmem + buf * kPage, q_desc0 + 2 * k, k_desc0 + 2 * k, idesc_qk, k ? 1u : 0u);
 #pragma unroll
-          for (int k = 0; k < 4; ++k)
-            umma_bf16(tmem + buf * kPage, umma_desc(q_smem + half * (kRows * 128)) + 2 * k,
-                      umma_desc(k_smem + half * (kPage * 128)) + 2 * k, idesc_qk, (half | k) ? 1u : 0u);
+        for (int k = 0; k < 4; ++k) umma_bf16(tmem + buf * kPage, q_desc1 + 2 * k, k_desc1 + 2 * k, idesc_qk, 1u);
+        umma_commit(t_empty(s));     // the page's K has been read
         umma_commit(s_full(buf));
         return true;
       };
       if (ok) ok = issue_qk(0);
       for (int i = 0; i < n_pages && ok; ++i) {
         if (i + 1 < n_pages && !issue_qk(i + 1)) { ok = false; break; }  // runs while the rows work on page i
-        if (!mbar_wait(p_full(i & 1), (uint32_t)(i >> 1) & 1u, &abort_flag, a.error_flag, 15)) { ok = false; break; }
+        const int t = 2 * i + 1, s = t % kSlots, buf = i & 1;
+        if (!mbar_wait(t_full(s), (uint32_t)(t / kSlots) & 1u, &abort_flag, a.error_flag, 14)) { ok = false; break; }
+        if (!mbar_wait(p_full(buf), (uint32_t)(i >> 1) & 1u, &abort_flag, a.error_flag, 15)) { ok = false; break; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t v_smem = ring + (i % kStages) * kStageBytes + kPageBytes;
+        const uint32_t v_smem = ring + s * kPageBytes;
 #pragma unroll
-        for (int k = 0; k < 4; ++k)  // 16 keys an instruction
-          umma_bf16(tmem_o, umma_desc(p_smem + (i & 1) * kPBytes) + 2 * k, umma_desc_mn(v_smem + k * 2048, kPage * 128, 1024), idesc_pv,
-                    (i | k) ? 1u : 0u);
-        umma_commit(kv_empty(i % kStages));  // the page's K and V have been read
-        umma_commit(o_done(i & 1));
+        for (int k = 0; k < 4; ++k)  // 16 keys an instruction: 8 packed columns of P, two 8-key groups of V
+          umma_bf16_tmem_a(tmem_o, tmem + buf * kPage + 8 * k, umma_desc_mn(v_smem + k * 2048, kPage * 128, 1024), idesc_pv,
+                           (i | k) ? 1u : 0u);
+        umma_commit(t_empty(s));     // the page's V has been read
+        umma_commit(o_done(buf));
       }
     }
   } else {
@@ -189,7 +199,6 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     const int lo_max = a.window > 0 ? max(0, pos_first + 63 - a.window + 1) : 0;  // the lowest key the last row sees
     const uint32_t t_lane = (uint32_t)(quad * 32) << 16;
     const float scale_log2 = a.scale * kLog2e;
-    uint8_t* p_row = smem_raw + (p_smem - smem_u32(smem_raw)) + row * 128;
     float m = -INFINITY, l = 0.f;
     bool ok = true;
     for (int i = 0; i < n_pages; ++i) {
@@ -200,9 +209,6 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 #pragma unroll
       for (int c0 = 0; c0 < 64; c0 += 16) tmem_ld16(tmem + t_lane + buf * kPage + c0, sr + c0);
       asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-      __syncwarp();
-      if (lane == 0) mbar_arrive(s_free(buf));  // the next page but one may overwrite these scores
       const int key0 = (page_begin + i) * kPage;
       const bool whole = key0 + 63 <= pos_first && key0 >= lo_max;  // every row sees the whole page (same for the block)
       // The maximum is taken over the raw scores (the scale is positive) on four chains, and the scale
@@ -246,31 +252,24 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       }
       const float sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
       l = l * alpha + sum;
-      // P V of the page before last has read this buffer of P
-      if (i > 1 && !mbar_wait(o_done(buf), (uint32_t)((i - 2) >> 1) & 1u, &abort_flag, a.error_flag, 17)) { ok = false; break; }
       if (i > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
-        // a maximum moved: rescale this warp's rows of O, once P V of the page before is through
+        // the reference moved: rescale this warp's rows of O, once P V of the page before is through
         if (!mbar_wait(o_done(buf ^ 1), (uint32_t)((i - 1) >> 1) & 1u, &abort_flag, a.error_flag, 19)) { ok = false; break; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        {
 #pragma unroll 1
-          for (int c0 = 0; c0 < kHD; c0 += 16) {
-            uint32_t o[16];
-            tmem_ld16(tmem_o + t_lane + c0, o);
-            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        for (int c0 = 0; c0 < kHD; c0 += 16) {
+          uint32_t o[16];
+          tmem_ld16(tmem_o + t_lane + c0, o);
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-            for (int j = 0; j < 16; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * alpha);
-            tmem_st16(tmem_o + t_lane + c0, o);
-          }
-          asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+          for (int j = 0; j < 16; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * alpha);
+          tmem_st16(tmem_o + t_lane + c0, o);
         }
       }
-      // this row of P: eight 16-byte chunks, swizzled like a TMA tile (chunk ^ (row & 7))
-#pragma unroll
-      for (int j = 0; j < 8; ++j)
-        *reinterpret_cast<uint4*>(p_row + buf * kPBytes + ((j ^ (row & 7)) << 4)) =
-            make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      // this row of P over its scores: 64 bfloat16 = 32 columns (keys 2c and 2c+1 in column c)
+      tmem_st16(tmem + t_lane + buf * kPage, pk);
+      tmem_st16(tmem + t_lane + buf * kPage + 16, pk + 16);
+      asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
       if (lane == 0) mbar_arrive(p_full(buf));
