@@ -209,7 +209,8 @@ def main(argv=None) -> int:
     p.add_argument("--tokens", type=int, default=8)
     p.add_argument("--n-out", type=int, default=4096)
     p.add_argument("--n-in", type=int, default=4096)
-    p.add_argument("--mode", choices=["store", "store-f32", "accumulate", "gated"], default="store")
+    p.add_argument("--mode", choices=["store", "store-f32", "accumulate", "gated", "ahead", "heads"], default="store",
+                   help="linear: the epilogue (ahead, heads: of the prompt kernel, 129 tokens or more)")
     p.add_argument("--batch", type=int, default=8)
     p.add_argument("--context", type=int, default=2048)
     p.add_argument("--reps", type=int, default=5)

@@ -64,6 +64,26 @@ def linear(tokens: int, n_out: int, n_in: int, mode: str, copies: int = 0, reps:
     elif gated:
         y = torch.empty(tokens, n_out, dtype=torch.bfloat16, device=DEV)
         fn = lambda i: lins[i].forward(x, y, GATED)
+    elif mode == "ahead":  # the prompt kernel's accumulate with the next norm's input prepared on the way
+        y = torch.zeros(tokens, n_out, device=DEV)
+        nw = torch.ones(n_out, device=DEV)
+        xw = torch.empty(tokens, n_out, dtype=torch.bfloat16, device=DEV)
+        shares = torch.empty(ops.prompt_ahead_parts(n_out), tokens, device=DEV)
+        fn = lambda i: ops.gemm_prompt(x, lins[i].weight_map(), n_out, y, ops.TC_ACCUM_F32, norm_ahead=(nw, xw, shares))
+    elif mode == "heads":  # the prompt kernel's q/k/v product: heads of 128 normed, rotated, written to q and the cache
+        hd = 128
+        nkv = max(1, n_out // hd // 6)
+        nq = n_out // hd - 2 * nkv
+        y = torch.empty(tokens, nq * hd, dtype=torch.bfloat16, device=DEV)
+        pages = -(-tokens // 64)
+        pools = [torch.zeros(pages, nkv, 64, hd, dtype=torch.bfloat16, device=DEV) for _ in range(2)]
+        ang = torch.arange(tokens, device=DEV, dtype=torch.float32)[:, None] * torch.rand(hd // 2, device=DEV)[None, :]
+        i32 = lambda t: t.to(torch.int32).to(DEV).contiguous()
+        prep = dict(nq=nq, nkv=nkv, hd=hd, q_norm=torch.ones(hd, device=DEV), k_norm=torch.ones(hd, device=DEV), eps=1e-6,
+                    cos=torch.cos(ang), sin=torch.sin(ang), tok_pos=i32(torch.arange(tokens)),
+                    tok_slot=i32(torch.zeros(tokens)), k_pool=pools[0], v_pool=pools[1],
+                    page_table=i32(torch.arange(pages)[None, :]), page_size=64)
+        fn = lambda i: lins[i].forward_heads(x, y, prep)
     elif mode == "store-f32":
         y = torch.empty(tokens, n_out, device=DEV)
         fn = lambda i: lins[i].forward(x, y, STORE)

@@ -8,6 +8,7 @@ launch.  Nothing here computes on the host or falls back to library code.
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import c_float, c_int, c_int64, c_size_t, c_uint64, c_void_p
 from typing import Optional
 
@@ -507,6 +508,122 @@ def gemm_tc_rows(x: Optional[torch.Tensor], w_map: TensorMap, rows: int, n_out: 
     _check("gemm_tc", f(w_map.buf, xm.buf if xm is not None else None, *nargs, _ptr(y), _rows(y, "y"), m, n_out, k, bn,
                         mode, rows, kkb, kstack, splits, _ptr(error_flag(dev)), *ahead_args, *scale_args,
                         _ptr(timeline), _stream()))
+    return y
+
+
+# ------------------------------------------------------- tensor-core linear, prompts
+TC_QKV_PREP = 4  # gemm_prompt only: the product's heads go through norm and rotation into q and the cache
+PROMPT_MIN_TOKENS = 129  # fewer tokens leave most of a 128-token tile empty: the weight-major kernels take them
+
+
+PROMPT_TMA_ADD = os.environ.get("SKYLA_PROMPT_TMA_ADD", "1") != "0"  # 0: the threads read, add and write y themselves
+_Y_MAPS = {}
+
+
+def _output_map(y: torch.Tensor):
+    """The tensor map through which ``gemm_prompt`` adds into ``y`` (cached: workspace buffers are few)."""
+    key = (y.data_ptr(), y.shape[0], y.shape[1], y.stride(0))
+    buf = _Y_MAPS.get(key)
+    if buf is None:
+        if len(_Y_MAPS) > 1024:
+            _Y_MAPS.clear()
+        buf = ctypes.create_string_buffer(128)
+        f = _fn("gemm_prompt", "skyla_output_map_f32", [c_void_p, c_void_p, c_uint64, c_uint64, c_uint64])
+        _check_nolaunch("gemm_prompt", f(buf, _ptr(y), y.shape[0], y.shape[1], _rows(y, "y")))
+        _Y_MAPS[key] = buf
+    return buf
+
+
+def prompt_ahead_parts(n_out: int) -> int:
+    """Shares of a row's sum of squares that ``gemm_prompt(..., norm_ahead=...)`` leaves: one per tile of 256 outputs."""
+    return -(-n_out // 256)
+
+
+def gemm_prompt(x: torch.Tensor, w_map: TensorMap, n_out: int, y: torch.Tensor, mode: int, scale_in=None,
+                norm_ahead=None, prep=None) -> torch.Tensor:
+    """y = x W^T for a prompt's tokens, a token's row of a tile in one thread of the epilogue.
+
+    ``w_map`` has boxes of 128 rows; a gated weight holds the ``n_out`` gate rows, then the up rows.
+    Modes TC_STORE_BF16 / TC_STORE_F32 / TC_ACCUM_F32 / TC_GLU_BF16 as in :func:`gemm_tc`.
+    ``scale_in=(ssq_parts [parts, tokens], eps)``: ``x`` is ``bf16(rows * norm weight)`` of rows whose
+    sums of squares lie in ``ssq_parts``; the result is multiplied by ``1/sqrt(sum / K + eps)``.
+    ``norm_ahead=(w, xw, ssq_parts)`` with TC_ACCUM_F32: also leave ``xw = bf16(y_new * w)`` and the
+    tiles' shares of the new rows' sums of squares, ``ssq_parts`` [prompt_ahead_parts(n_out), tokens].
+    Mode TC_QKV_PREP with ``prep=dict(nq, nkv, hd, q_norm, k_norm, eps, cos, sin, tok_pos, tok_slot, k_pool,
+    v_pool, page_table, page_size)``: the outputs are ``nq`` query, ``nkv`` key and ``nkv`` value heads of
+    ``hd``; q and k heads are RMS-normed (weights may be ``None``) and rotated whole (tables may be
+    ``None``), the queries go to ``y`` [tokens, nq * hd] bfloat16, keys and values to the tokens' places
+    in the pools (``None``: not written).
+    """
+    _cuda(x, y)
+    m, k = x.shape
+    want = {TC_STORE_BF16: torch.bfloat16, TC_GLU_BF16: torch.bfloat16, TC_QKV_PREP: torch.bfloat16}.get(mode, torch.float32)
+    if y.dtype != want:
+        raise KernelError(f"gemm_prompt: epilogue {mode} writes {want}, y is {y.dtype}")
+    scale_args = [c_void_p(0), 0, 0.0]
+    if scale_in is not None:
+        sssq, seps = scale_in
+        _cuda(sssq)
+        if sssq.dtype != torch.float32 or sssq.dim() != 2 or sssq.shape[1] != m or not sssq.is_contiguous():
+            raise KernelError(f"gemm_prompt: handed-in sums of squares are float32 [parts, {m}]")
+        scale_args = [_ptr(sssq), sssq.shape[0], float(seps)]
+    ahead_args = [c_void_p(0), c_void_p(0), 0, c_void_p(0)]
+    if norm_ahead is not None:
+        aw, axw, assq = norm_ahead
+        _cuda(aw, axw, assq)
+        parts = prompt_ahead_parts(n_out)
+        if (mode != TC_ACCUM_F32 or aw.dtype != torch.float32 or aw.numel() != n_out or not aw.is_contiguous()
+                or axw.dtype != torch.bfloat16 or tuple(axw.shape) != (m, n_out) or axw.stride(1) != 1
+                or assq.dtype != torch.float32 or tuple(assq.shape) != (parts, m) or not assq.is_contiguous()):
+            raise KernelError(f"gemm_prompt: norm-ahead goes with TC_ACCUM_F32 and wants w [{n_out}] float32, "
+                              f"xw [{m}, {n_out}] bfloat16, ssq_parts [{parts}, {m}] float32")
+        ahead_args = [_ptr(aw), _ptr(axw), axw.stride(0), _ptr(assq)]
+    prep_args = [0, 0, 0, c_void_p(0), c_void_p(0), 0.0, c_void_p(0), c_void_p(0), c_void_p(0), c_void_p(0),
+                 c_void_p(0), c_void_p(0), c_void_p(0), 0, 0]
+    if mode == TC_QKV_PREP:
+        if prep is None:
+            raise KernelError("gemm_prompt: TC_QKV_PREP needs prep")
+        nq, nkv, hd = int(prep["nq"]), int(prep["nkv"]), int(prep["hd"])
+        q_norm, k_norm, cos, sin = prep.get("q_norm"), prep.get("k_norm"), prep.get("cos"), prep.get("sin")
+        tok_pos, tok_slot, page_table = prep["tok_pos"], prep.get("tok_slot"), prep.get("page_table")
+        k_pool, v_pool, page_size = prep.get("k_pool"), prep.get("v_pool"), int(prep.get("page_size") or 0)
+        _cuda(q_norm, k_norm, cos, sin, tok_pos, tok_slot, page_table, k_pool, v_pool)
+        if (nq + 2 * nkv) * hd != n_out or tuple(y.shape) != (m, nq * hd):
+            raise KernelError(f"gemm_prompt: {nq} + 2 x {nkv} heads of {hd} against {n_out} outputs and y {tuple(y.shape)}")
+        for t, what in ((tok_pos, "tok_pos"), (tok_slot, "tok_slot"), (page_table, "page_table")):
+            if t is not None:
+                _i32(t, what)
+        if tok_pos.numel() != m:
+            raise KernelError("gemm_prompt: one position per token")
+        for t, what, shape in ((q_norm, "q_norm", (hd,)), (k_norm, "k_norm", (hd,)), (cos, "cos", None), (sin, "sin", None)):
+            if t is not None and (t.dtype != torch.float32 or not t.is_contiguous() or (shape and tuple(t.shape) != shape)):
+                raise KernelError(f"gemm_prompt: {what} must be a contiguous float32 tensor" + (f" {shape}" if shape else ""))
+        if cos is not None and (sin is None or cos.shape != sin.shape or cos.dim() != 2 or cos.shape[1] != hd // 2):
+            raise KernelError("gemm_prompt: the rotary tables must be [positions, head size / 2]: the whole head rotates")
+        max_pages = 0
+        if k_pool is not None:
+            if (v_pool is None or k_pool.shape != v_pool.shape or tuple(k_pool.shape[1:]) != (nkv, page_size, hd)
+                    or k_pool.dtype != torch.bfloat16 or v_pool.dtype != torch.bfloat16
+                    or not k_pool.is_contiguous() or not v_pool.is_contiguous() or tok_slot is None or page_table is None
+                    or page_table.dim() != 2 or tok_slot.numel() != m):
+                raise KernelError(f"gemm_prompt: bfloat16 cache pools [pages, {nkv}, {page_size}, {hd}] with slots and a page table")
+            max_pages = page_table.shape[1]
+        prep_args = [nq, nkv, hd, _ptr(q_norm), _ptr(k_norm), float(prep.get("eps") or 0.0), _ptr(cos), _ptr(sin),
+                     _ptr(tok_pos), _ptr(tok_slot), _ptr(k_pool), _ptr(v_pool), _ptr(page_table), max_pages, page_size]
+    elif tuple(y.shape) != (m, n_out):
+        raise KernelError(f"gemm_prompt: y {tuple(y.shape)} is not [{m}, {n_out}]")
+    xm = activation_map(x, 128)
+    ym = None
+    if (mode == TC_ACCUM_F32 and norm_ahead is None and PROMPT_TMA_ADD and y.data_ptr() % 16 == 0
+            and _rows(y, "y") % 4 == 0):
+        ym = _output_map(y)
+    f = _fn("gemm_prompt", "skyla_gemm_prompt",
+            [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_float,
+             c_void_p, c_void_p, c_int64, c_void_p,
+             c_int, c_int, c_int, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_void_p,
+             c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p])
+    _check("gemm_prompt", f(xm.buf, w_map.buf, ym, _ptr(y), _rows(y, "y"), m, n_out, k, mode, _ptr(error_flag(x.device)),
+                            *scale_args, *ahead_args, *prep_args, _stream()))
     return y
 
 

@@ -128,7 +128,8 @@ class GQAttention(Part):
                and self.rt.act_dtype == torch.bfloat16)
         scale_in = None
         if isinstance(h, NormedInput):
-            if few and h.ahead is not None and ops.tc_linear_ok(h.ahead[0], self.qkv.weight):
+            if ((few or (entry.owns_cache and self.qkv.prompts(n))) and h.ahead is not None
+                    and ops.tc_linear_ok(h.ahead[0], self.qkv.weight)):
                 scale_in = (h.ahead[1], h.norm.eps)  # the product that wrote x last left x * norm weight
                 h = h.ahead[0]
             elif few and self.qkv.can_fuse_norm(h):
@@ -170,8 +171,18 @@ class GQAttention(Part):
                                    self.k_norm_w, self.eps, cos, sin, n_rot, ctx.tok_pos, ctx.tok_seq,
                                    k_pool, v_pool, pages, ctx.page_size, q_out=qkv,
                                    fold=(x, pend) if pend is not None else None)
+        elif (entry.owns_cache and self.qkv.prompts(n) and ops.tc_linear_ok(h, self.qkv.weight)
+              and self.hd in (32, 64, 128, 256) and (cos is None or n_rot == self.hd)
+              and k_pool.dtype == torch.bfloat16 and self.rt.act_dtype == torch.bfloat16):
+            # a prompt: the heads are normed, rotated and put into the cache in the product's epilogue
+            qkv = ctx.buffer("attn.q", (n, nq * hd), self.rt.act_dtype)
+            self.qkv.forward_heads(h, qkv, dict(
+                nq=nq, nkv=nkv, hd=hd, q_norm=self.q_norm_w, k_norm=self.k_norm_w, eps=self.eps, cos=cos, sin=sin,
+                tok_pos=ctx.tok_pos, tok_slot=ctx.tok_seq, k_pool=k_pool, v_pool=v_pool, page_table=pages,
+                page_size=ctx.page_size), scale_in=scale_in)
+            ctx.mark("matvec qkv")
         elif entry.owns_cache:
-            part = self.qkv.forward_partial(h, ctx, "attn.qkv_partials")
+            part = self.qkv.forward_partial(h, ctx, "attn.qkv_partials") if scale_in is None else None
             if part is not None:  # a small batch: the product is K-split, the splits are added up here
                 ctx.mark("matvec qkv")
                 qkv = ctx.buffer("attn.q", (n, nq * hd), self.rt.act_dtype)
@@ -180,7 +191,7 @@ class GQAttention(Part):
                                        k_pool, v_pool, pages, ctx.page_size, q_out=qkv)
             else:
                 qkv = ctx.buffer("attn.qkv", (n, (nq + 2 * nkv) * hd), self.rt.act_dtype)
-                self.qkv.forward(h, qkv, STORE)
+                self.qkv.forward(h, qkv, STORE, scale_in=scale_in)
                 ctx.mark("matvec qkv")
                 ops.qk_norm_rope_cache(qkv, 0, nq * hd, (nq + nkv) * hd, nq, nkv, hd, self.q_norm_w,
                                        self.k_norm_w, self.eps, cos, sin, n_rot, ctx.tok_pos, ctx.tok_seq,

@@ -58,7 +58,7 @@ class SwiGLU(Part):
         fold = None
         scale_in = None
         if isinstance(h, NormedInput):
-            if (h.ahead is not None and self.gate_up.streams(ctx.n_tokens)
+            if (h.ahead is not None and self.gate_up.takes_scale_in(ctx.n_tokens)
                     and ops.tc_linear_ok(h.ahead[0], self.gate_up.weight)):
                 scale_in = (h.ahead[1], h.norm.eps)  # the product that wrote x last left x * norm weight
                 h = h.ahead[0]

@@ -17,7 +17,7 @@ STORE, ACCUMULATE, GATED = ops.STORE, ops.ACCUMULATE, ops.GATED
 
 
 class Linear:
-    kernel_modules = ("linear_plain", "gemm_tc")
+    kernel_modules = ("linear_plain", "gemm_tc", "gemm_prompt")
 
     #: the weight-streaming kernel takes over up to this many tokens ...
     ROWS_MAX_TOKENS = 64
@@ -49,6 +49,14 @@ class Linear:
         """Whether ``m`` tokens go to the weight-streaming kernel (given operands it takes)."""
         return self.tensor_cores and m <= (self.ROWS_MAX_TOKENS if self.streams_wide else self.STACKED_MAX_TOKENS)
 
+    def prompts(self, m: int) -> bool:
+        """Whether ``m`` tokens go to the prompt kernel (tokens are the tile's rows; given operands it takes)."""
+        return self.tensor_cores and self.PROMPT_KERNEL and m >= ops.PROMPT_MIN_TOKENS
+
+    def takes_scale_in(self, m: int) -> bool:
+        """Whether :meth:`forward` of ``m`` tokens accepts ``scale_in``."""
+        return self.streams(m) or self.prompts(m)
+
     def _rows_map(self, m: int):
         rows, splits, kkb, kstack = self.rows_plans[ops.token_tile(m)]
         w_map = self._rows_maps.get((rows, kkb))
@@ -62,57 +70,67 @@ class Linear:
         return ops.gemm_tc_rows(x, self._rows_map(m), rows, self.n_out, y, tc, normed=normed, kkb=kkb, splits=splits,
                                 kstack=kstack, norm_ahead=norm_ahead, scale_in=scale_in)
 
-    def _norm_ahead(self, ctx, x, y):
-        """Buffers for "norm ahead" if this product adds into the residual stream ``y``, the norm
-        that reads it next is an RMSNorm of its width, and the weight-streaming kernel runs."""
+    def _norm_ahead(self, ctx, x, y, parts: int):
+        """Buffers for "norm ahead" if this product adds into the residual stream ``y`` and the norm
+        that reads it next is an RMSNorm of its width; the kernel leaves ``parts`` shares of a row's
+        sum of squares (0: it cannot)."""
         norm = getattr(ctx, "next_norm", None) if ctx is not None else None
         if ctx is not None:
             ctx.next_norm = None
         m = x.shape[0]
         if (norm is None or type(norm).__name__ != "RMSNorm" or not self.NORM_AHEAD or y.dtype != torch.float32
                 or getattr(norm, "weight", None) is None or norm.weight.numel() != self.n_out
-                or self.n_out % 8 or self.rows_plans[ops.token_tile(m)][1] != 1):
+                or self.n_out % 8 or parts < 1):
             return None, None
-        blocks = -(-self.n_out // self.rows_plans[ops.token_tile(m)][0])
         xw = ctx.buffer("x.times_norm_weight", (m, self.n_out), torch.bfloat16)
-        ssq = ctx.buffer("x.ssq_shares", (blocks, m), torch.float32)
+        ssq = ctx.buffer("x.ssq_shares", (parts, m), torch.float32)
         return norm, (norm.weight, xw, ssq)
 
     def forward(self, x: torch.Tensor, y: torch.Tensor, mode: int = STORE, scale_in=None, ctx=None) -> torch.Tensor:
         """``scale_in=(shares of the rows' sums of squares, eps)``: ``x`` is a residual stream times
-        its norm's weight (see ``NormedInput.ahead``); only where :meth:`streams` holds.
+        its norm's weight (see ``NormedInput.ahead``); only where :meth:`takes_scale_in` holds.
         ``ctx`` with ``mode=ACCUMULATE``: ``y`` is the residual stream, and if ``ctx.next_norm``
         names the RMSNorm that reads it next, its input is prepared on the way (``ctx.ahead``)."""
         if self.gated:
             mode = GATED
         if self.tensor_cores and ops.tc_linear_ok(x, self.weight):
-            if self.streams(x.shape[0]):
-                tc = {GATED: ops.TC_GLU_BF16, ACCUMULATE: ops.TC_ACCUM_F32}.get(
-                    mode, ops.TC_STORE_BF16 if y.dtype == torch.bfloat16 else ops.TC_STORE_F32)
-                norm, ahead = self._norm_ahead(ctx, x, y) if mode == ACCUMULATE else (None, None)
+            m = x.shape[0]
+            tc = {GATED: ops.TC_GLU_BF16, ACCUMULATE: ops.TC_ACCUM_F32}.get(
+                mode, ops.TC_STORE_BF16 if y.dtype == torch.bfloat16 else ops.TC_STORE_F32)
+            if self.streams(m):
+                rows, splits = self.rows_plans[ops.token_tile(m)][:2]
+                norm, ahead = (self._norm_ahead(ctx, x, y, -(-self.n_out // rows) if splits == 1 else 0)
+                               if mode == ACCUMULATE else (None, None))
                 self._stream(x, y, tc, norm_ahead=ahead, scale_in=scale_in)
                 if ahead is not None:
                     ctx.ahead = (norm, y, ahead[1], ahead[2])
                 return y
+            if self.prompts(m):
+                norm, ahead = (self._norm_ahead(ctx, x, y, ops.prompt_ahead_parts(self.n_out) if self.PROMPT_NORM_AHEAD else 0)
+                               if mode == ACCUMULATE else (None, None))
+                ops.gemm_prompt(x, self.weight_map(), self.n_out, y, tc, scale_in=scale_in, norm_ahead=ahead)
+                if ahead is not None:
+                    ctx.ahead = (norm, y, ahead[1], ahead[2])
+                return y
             if scale_in is not None:
-                raise ValueError("scale_in goes with the weight-streaming kernel only (Linear.streams)")
-            if mode == GATED:
-                tc = ops.TC_GLU_BF16
-            elif mode == ACCUMULATE:
-                splits = self.choose_splits(x.shape[0])
+                raise ValueError("scale_in goes with the weight-streaming and the prompt kernel only (Linear.takes_scale_in)")
+            if mode == ACCUMULATE:
+                splits = self.choose_splits(m)
                 if splits > 8:  # more splits than a portable cluster holds: they meet through scratch
-                    scratch = ops.accum_scratch(x.device, splits * x.shape[0] * self.n_out)
+                    scratch = ops.accum_scratch(x.device, splits * m * self.n_out)
                     return ops.gemm_tc(x, self.weight_map(), self.n_out, y, ops.TC_ACCUM_LAST, splits=splits,
                                        scratch=scratch)
                 if splits > 1:  # few tokens: K is cut across a cluster of blocks so that every SM streams
                     return ops.gemm_tc(x, self.weight_map(), self.n_out, y, ops.TC_ACCUM_CLUSTER, splits=splits)
-                tc = ops.TC_ACCUM_F32
-            else:
-                tc = ops.TC_STORE_BF16 if y.dtype == torch.bfloat16 else ops.TC_STORE_F32
             return ops.gemm_tc(x, self.weight_map(), self.n_out, y, tc)
         if scale_in is not None:
-            raise ValueError("scale_in goes with the weight-streaming kernel only (Linear.streams)")
+            raise ValueError("scale_in goes with the weight-streaming and the prompt kernel only (Linear.takes_scale_in)")
         return ops.linear_plain(x, self.weight, y, mode, 0)
+
+    def forward_heads(self, x: torch.Tensor, q_out: torch.Tensor, prep: dict, scale_in=None) -> torch.Tensor:
+        """The product of a fused q/k/v weight whose heads are finished in its epilogue
+        (``ops.gemm_prompt`` with TC_QKV_PREP); only where :meth:`prompts` holds."""
+        return ops.gemm_prompt(x, self.weight_map(), self.n_out, q_out, ops.TC_QKV_PREP, scale_in=scale_in, prep=prep)
 
     # ---- K-split products for small batches
     N_SMS = 148
@@ -162,6 +180,11 @@ class Linear:
     FUSED_NORM_MAX_TOKENS = 16  # every block re-reads the rows it normalises: only worth it for few
     FUSE_NORM = os.environ.get("SKYLA_FUSE_NORM", "0") != "0"   # off: "norm ahead" is cheaper
     NORM_AHEAD = os.environ.get("SKYLA_NORM_AHEAD", "1") != "0"
+    # Prompts: the sums go into the residual stream by TMA reduce, which never reads it; preparing the
+    # next norm's input on the way would need the rows back in the threads (measured at 2,048 tokens of
+    # the 8B shape: 106 against 65 us for the O product, more than the norm kernel it saves)
+    PROMPT_NORM_AHEAD = os.environ.get("SKYLA_PROMPT_NORM_AHEAD", "0") != "0"
+    PROMPT_KERNEL = os.environ.get("SKYLA_PROMPT_KERNEL", "1") != "0"  # 0: prompts on the weight-major persistent kernel
 
     def can_fuse_norm(self, normed) -> bool:
         """Whether ``norm(x + pending)`` can be made inside this product: RMSNorm, float32 rows

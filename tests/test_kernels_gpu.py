@@ -884,3 +884,170 @@ def test_attention_decode_fused_prep(nq, nkv, hd, n_rot, window):
     torch.testing.assert_close(got.float(), want.float(), rtol=2e-2, atol=2e-2)
     assert torch.equal(kp2, kp1) and torch.equal(vp2, vp1)  # the same k and v reached the cache
     assert not torch.equal(kp2, k_pool)
+
+
+# ---------------------------------------------------------------- the prompt kernel (tokens are the tile's rows)
+@pytest.mark.parametrize("m,n,k", [(129, 256, 64), (130, 384, 1032), (300, 200, 264), (257, 203, 96), (1000, 640, 512),
+                                   (128, 1000, 328)])
+def test_gemm_prompt_store_accumulate_gated(m, n, k):
+    ops = _ops()
+    from skyla_kernel_b200.parts.feedforward import fuse_gate_up
+    x = _rand(m, k, seed=71, dtype=torch.bfloat16)
+    w = _rand(n, k, seed=72, dtype=torch.bfloat16, scale=0.1)
+    ref = x.double() @ w.double().T
+    scale = ref.abs().max().item()
+    wm = ops.TensorMap(w, 128)
+    y32 = torch.full((m, n), float("nan"), dtype=torch.float32, device=DEV)
+    ops.gemm_prompt(x, wm, n, y32, ops.TC_STORE_F32)
+    assert (y32.double() - ref).abs().max().item() <= 2e-5 * scale + 1e-6
+    y16 = torch.empty(m, n, dtype=torch.bfloat16, device=DEV)
+    ops.gemm_prompt(x, wm, n, y16, ops.TC_STORE_BF16)
+    assert torch.equal(y16, y32.to(torch.bfloat16))
+    acc = _rand(m, n, seed=73)
+    before = acc.clone()
+    ops.gemm_prompt(x, wm, n, acc, ops.TC_ACCUM_F32)
+    assert (acc.double() - before.double() - ref).abs().max().item() <= 2e-5 * scale + 1e-5
+    # rows of a wider buffer: what lies beside them stays
+    wide = torch.full((m, n + 24), 7.0, dtype=torch.float32, device=DEV)
+    ops.gemm_prompt(x, wm, n, wide[:, 8:8 + n], ops.TC_STORE_F32)
+    assert torch.equal(wide[:, 8:8 + n], y32) and (wide[:, :8] == 7).all() and (wide[:, 8 + n:] == 7).all()
+    g, u = _rand(n, k, seed=74, dtype=torch.bfloat16, scale=0.2), _rand(n, k, seed=75, dtype=torch.bfloat16, scale=0.2)
+    fused = fuse_gate_up(g, u)
+    act = torch.empty(m, n, dtype=torch.bfloat16, device=DEV)
+    ops.gemm_prompt(x, ops.TensorMap(fused, 128), n, act, ops.TC_GLU_BF16)
+    gd, ud = x.double() @ g.double().T, x.double() @ u.double().T
+    ref_act = gd / (1 + torch.exp(-gd)) * ud
+    torch.testing.assert_close(act.double(), ref_act, rtol=1e-2, atol=1e-2 * ref_act.abs().max().item())
+    plain_act = torch.empty_like(act)
+    ops.linear_plain(x, fused, plain_act, ops.GATED)
+    torch.testing.assert_close(act.float(), plain_act.float(), rtol=2e-2, atol=1e-3)
+    ops.check_device_errors(DEV)
+
+
+@pytest.mark.parametrize("m,n,k,n2", [(300, 512, 264, 384), (129, 264, 520, 200), (515, 1000, 128, 136)])
+def test_gemm_prompt_norm_ahead_then_scale_in(m, n, k, n2):
+    """x += a W^T leaves x * norm weight in bfloat16 and the tiles' shares of the rows' sums of
+    squares; the next product takes those and must equal the product of rmsnorm(x)."""
+    ops = _ops()
+    from skyla_kernel_b200.parts.feedforward import fuse_gate_up
+    a = _rand(m, k, seed=81, dtype=torch.bfloat16)
+    w = _rand(n, k, seed=82, dtype=torch.bfloat16, scale=0.1)
+    x0 = _rand(m, n, seed=83, scale=1.5)
+    nw = 1 + 0.2 * _rand(n, seed=84)
+    x = x0.clone()
+    parts = ops.prompt_ahead_parts(n)
+    xw = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device=DEV)
+    shares = torch.full((parts, m), float("nan"), device=DEV)
+    ops.gemm_prompt(a, ops.TensorMap(w, 128), n, x, ops.TC_ACCUM_F32, norm_ahead=(nw, xw, shares))
+    want_x = x0.double() + a.double() @ w.double().T
+    assert (x.double() - want_x).abs().max().item() <= 1e-5 * want_x.abs().max().item() + 1e-6
+    assert torch.equal(xw, (x * nw).to(torch.bfloat16))  # the very rows that were stored
+    torch.testing.assert_close(shares.double().sum(0), (x.double() ** 2).sum(1), rtol=1e-5, atol=1e-6)
+    eps = 1e-5
+    h = plain.rmsnorm(x.double().cpu(), nw.double().cpu(), eps)
+    w2 = _rand(n2, n, seed=85, dtype=torch.bfloat16, scale=0.1)
+    ref = h @ w2.double().cpu().T
+    y = torch.full((m, n2), float("nan"), device=DEV)
+    ops.gemm_prompt(xw, ops.TensorMap(w2, 128), n2, y, ops.TC_STORE_F32, scale_in=(shares, eps))
+    torch.testing.assert_close(y.double().cpu(), ref, rtol=2e-2, atol=2e-2 * ref.abs().max().item())
+    assert (y.double().cpu() - ref).abs().mean().item() < 4e-3 * ref.abs().max().item()
+    g, u = _rand(n2, n, seed=86, dtype=torch.bfloat16, scale=0.1), _rand(n2, n, seed=87, dtype=torch.bfloat16, scale=0.1)
+    act = torch.empty(m, n2, dtype=torch.bfloat16, device=DEV)
+    ops.gemm_prompt(xw, ops.TensorMap(fuse_gate_up(g, u), 128), n2, act, ops.TC_GLU_BF16, scale_in=(shares, eps))
+    gd, ud = h @ g.double().cpu().T, h @ u.double().cpu().T
+    ref_act = gd / (1 + torch.exp(-gd)) * ud
+    torch.testing.assert_close(act.double().cpu(), ref_act, rtol=3e-2, atol=3e-2 * ref_act.abs().max().item())
+    # shares left by the weight-streaming kernel are taken just as well (a producer of few rows, then many: not in
+    # one step, but the contract is the same): shares summed in another cut give the same scalars
+    one = shares.sum(0, keepdim=True).contiguous()
+    y1 = torch.empty_like(y)
+    ops.gemm_prompt(xw, ops.TensorMap(w2, 128), n2, y1, ops.TC_STORE_F32, scale_in=(one, eps))
+    torch.testing.assert_close(y1, y, rtol=1e-5, atol=1e-6)
+    ops.check_device_errors(DEV)
+
+
+@pytest.mark.parametrize("nq,nkv,hd,use_norm,use_rope,scaled", [
+    (4, 2, 128, True, True, True), (5, 1, 64, True, True, False), (3, 3, 32, False, True, False),
+    (2, 1, 256, True, False, True), (6, 2, 128, False, False, False)])
+def test_gemm_prompt_finishes_heads_into_queries_and_cache(nq, nkv, hd, use_norm, use_rope, scaled):
+    """The q/k/v product whose epilogue norms and rotates the heads and writes k and v into the
+    paged cache, against the plain steps on a float64 product; positions that start late in a
+    sequence, two sequences, shuffled pages."""
+    ops = _ops()
+    k = 264
+    lens, starts = [150, 70], [37, 64]  # new tokens of each sequence and the position of its first
+    T = sum(lens)
+    positions = [s + i for l, s in zip(lens, starts) for i in range(l)]
+    seqs = [b for b, l in enumerate(lens) for _ in range(l)]
+    g = torch.Generator().manual_seed(5)
+    table = torch.randperm(9, generator=g)[:8].view(2, 4).to(torch.int32).to(DEV)
+    n = (nq + 2 * nkv) * hd
+    x = _rand(T, k, seed=91, dtype=torch.bfloat16)
+    w = _rand(n, k, seed=92, dtype=torch.bfloat16, scale=0.1)
+    qn, kn = 1 + 0.2 * _rand(hd, seed=93), 1 + 0.2 * _rand(hd, seed=94)
+    freqs, _ = plain.rope_frequencies(hd, 10000.0)
+    ang = (torch.arange(300, dtype=torch.float32)[:, None] * freqs[None, :]).double()
+    cos, sin = torch.cos(ang).float().to(DEV), torch.sin(ang).float().to(DEV)
+    k_pool = torch.zeros(9, nkv, 64, hd, dtype=torch.bfloat16, device=DEV)
+    v_pool = torch.zeros_like(k_pool)
+    q_out = torch.full((T, nq * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+    shares, eps_in = None, 1e-5
+    if scaled:
+        shares = (0.5 + torch.rand(3, T, generator=g)).to(DEV)
+    ops.gemm_prompt(x, ops.TensorMap(w, 128), n, q_out, ops.TC_QKV_PREP,
+                    scale_in=(shares, eps_in) if scaled else None,
+                    prep=dict(nq=nq, nkv=nkv, hd=hd, q_norm=qn if use_norm else None, k_norm=kn if use_norm else None,
+                              eps=1e-6, cos=cos if use_rope else None, sin=sin if use_rope else None,
+                              tok_pos=torch.tensor(positions, dtype=torch.int32, device=DEV),
+                              tok_slot=torch.tensor(seqs, dtype=torch.int32, device=DEV),
+                              k_pool=k_pool, v_pool=v_pool, page_table=table, page_size=64))
+    ops.check_device_errors(DEV)
+    o = (x.double() @ w.double().T).cpu()
+    if scaled:
+        o = o * (1.0 / torch.sqrt(shares.double().cpu().sum(0) / k + eps_in))[:, None]
+    pos_t = torch.tensor(positions)
+    q = o[:, : nq * hd].reshape(T, nq, hd)
+    kk = o[:, nq * hd:(nq + nkv) * hd].reshape(T, nkv, hd)
+    v = o[:, (nq + nkv) * hd:].reshape(T, nkv, hd)
+    if use_norm:
+        q, kk = plain.rmsnorm(q, qn.double().cpu(), 1e-6), plain.rmsnorm(kk, kn.double().cpu(), 1e-6)
+    if use_rope:
+        q, kk = plain.rope_neox(q, pos_t, freqs, 1.0, hd), plain.rope_neox(kk, pos_t, freqs, 1.0, hd)
+    tol = dict(rtol=1e-2, atol=1e-2 * float(max(q.abs().max(), kk.abs().max(), v.abs().max())))
+    torch.testing.assert_close(q_out.double().cpu().view(T, nq, hd), q.double(), **tol)
+    pages = table.cpu()[torch.tensor(seqs), pos_t // 64].long()
+    torch.testing.assert_close(k_pool.cpu()[pages, :, pos_t % 64].double(), kk.double(), **tol)
+    torch.testing.assert_close(v_pool.cpu()[pages, :, pos_t % 64].double(), v.double(), **tol)
+    mask = torch.ones(9, 64, dtype=torch.bool)
+    mask[pages, pos_t % 64] = False
+    assert (k_pool.float().cpu().abs().sum((1, 3))[mask] == 0).all()  # nothing else was written
+    assert (v_pool.float().cpu().abs().sum((1, 3))[mask] == 0).all()
+    # and the same numbers as the two-kernel path leaves, beyond its extra rounding of the product
+    qkv = torch.empty(T, n, dtype=torch.bfloat16, device=DEV)
+    ops.gemm_prompt(x, ops.TensorMap(w, 128), n, qkv, ops.TC_STORE_BF16, scale_in=(shares, eps_in) if scaled else None)
+    k2, v2 = torch.zeros_like(k_pool), torch.zeros_like(v_pool)
+    ops.qk_norm_rope_cache(qkv, 0, nq * hd, (nq + nkv) * hd, nq, nkv, hd, qn if use_norm else None,
+                           kn if use_norm else None, 1e-6, cos if use_rope else None, sin if use_rope else None, hd,
+                           torch.tensor(positions, dtype=torch.int32, device=DEV),
+                           torch.tensor(seqs, dtype=torch.int32, device=DEV), k2, v2, table, 64)
+    torch.testing.assert_close(q_out.float(), qkv[:, : nq * hd].float(), rtol=3e-2, atol=3e-2 * tol["atol"] / 1e-2)
+    torch.testing.assert_close(k_pool.float(), k2.float(), rtol=3e-2, atol=3e-2 * tol["atol"] / 1e-2)
+    assert torch.equal(v_pool, v2)
+
+
+def test_gemm_prompt_refuses():
+    ops = _ops()
+    from skyla_kernel_b200.kernels import KernelError
+    x = _rand(200, 64, seed=95, dtype=torch.bfloat16)
+    w = _rand(6 * 48, 64, seed=96, dtype=torch.bfloat16)
+    wm = ops.TensorMap(w, 128)
+    pos = torch.arange(200, dtype=torch.int32, device=DEV)
+    with pytest.raises(KernelError, match="head sizes"):
+        ops.gemm_prompt(x, wm, 6 * 48, torch.empty(200, 4 * 48, dtype=torch.bfloat16, device=DEV), ops.TC_QKV_PREP,
+                        prep=dict(nq=4, nkv=1, hd=48, tok_pos=pos))
+    with pytest.raises(KernelError, match="writes"):
+        ops.gemm_prompt(x, wm, 6 * 48, torch.empty(200, 6 * 48, dtype=torch.float32, device=DEV), ops.TC_STORE_BF16)
+    with pytest.raises(KernelError, match="norm-ahead"):
+        y = torch.empty(200, 6 * 48, dtype=torch.bfloat16, device=DEV)
+        ops.gemm_prompt(x, wm, 6 * 48, y, ops.TC_STORE_BF16,
+                        norm_ahead=(torch.ones(6 * 48, device=DEV), torch.empty_like(y), torch.empty(2, 200, device=DEV)))
