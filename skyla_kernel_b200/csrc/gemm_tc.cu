@@ -6,8 +6,8 @@
 // and silu(gate)*up (skyla-shaders/shaders/silu_mul.comp:15-24).
 //
 // The weight is the 128-row operand of tcgen05.mma and the tokens are the N
-// operand (16..256 wide), so the same kernel serves a 2,048-token prompt and a
-// batch of a few decoded tokens that only has to stream the weight once:
+// operand (16..256 wide): a batch of decoded tokens only has to stream the weight
+// once (prompts of more than 128 tokens have a kernel of their own, gemm_prompt.cu):
 //   warp 0    one lane issues TMA loads (cp.async.bulk.tensor, 128-byte swizzle)
 //             of a [128 x 64] weight tile and a [BN x 64] token tile per stage;
 //   warp 1    allocates TMEM; one lane issues tcgen05.mma (M=128, N=BN, K=16),
@@ -1034,220 +1034,6 @@ int launch_rows(const CUtensorMap& mw, const CUtensorMap& mx, const GemmArgs& a,
   return check_launch("gemm_tc_rows");
 }
 
-// ------------------------------------------------------------------ persistent, for prompts
-// Many tokens: the kernel is bound by the tensor cores, so the epilogue must not cost
-// tensor time.  (A gated tile of 256 tokens, which fills TMEM with one accumulator and so
-// cannot hide its epilogue, measured slower than two of 128: 385 against 311 us for 2048
-// tokens of the 8B shape.  Under load an MMA of 256 columns takes about 220 cycles at the
-// clock the power cap leaves, not the 128 of an idle tensor pipe.)  One block per SM walks the output tiles (tile = blockIdx.x, += gridDim.x;
-// tiles of one weight tile are neighbours, so concurrent blocks share it through L2).  TMEM
-// holds two accumulators: while the four epilogue warps drain tile i, the MMA warp already
-// works on tile i+1.  The TMA ring runs on across tile boundaries.
-template <int BN, int MODE>
-struct PCfg {
-  static constexpr int kATiles = MODE == kGluBf16 ? 2 : 1;
-  static constexpr int kABytes = kATiles * BM * BK * 2;
-  static constexpr int kBBytes = BN * BK * 2;
-  static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kStages = kSmemBudget / kStageBytes;
-  static constexpr int kAccCols = kATiles * BN;
-  static constexpr int kTmemCols = 2 * kAccCols;
-  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256;
-  static_assert(kTmemCols <= 512 && (kTmemCols & (kTmemCols - 1)) == 0 && kTmemCols >= 32, "TMEM columns");
-  static_assert(kStages >= 2 && kStages <= 12, "pipeline depth");
-};
-
-template <int BN, int MODE>
-__global__ void __launch_bounds__(kThreads, 1)
-gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
-                          const GemmArgs a, int n_f_tiles, int n_t_tiles) {
-  using C = PCfg<BN, MODE>;
-  extern __shared__ uint8_t smem_raw[];
-  __shared__ uint32_t tmem_base_slot;
-  __shared__ volatile int abort_flag;
-  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const uint32_t bars = base + C::kStages * C::kStageBytes;
-  auto full_bar = [&](int s) { return bars + 8u * s; };
-  auto empty_bar = [&](int s) { return bars + 8u * (C::kStages + s); };
-  auto acc_full_bar = [&](int b) { return bars + 8u * (2 * C::kStages + b); };
-  auto acc_empty_bar = [&](int b) { return bars + 8u * (2 * C::kStages + 2 + b); };
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int total_kb = (a.K + BK - 1) / BK;
-  const int n_tiles = n_f_tiles * n_t_tiles;
-
-  if (threadIdx.x == 0) {
-    abort_flag = 0;
-    for (int s = 0; s < C::kStages; ++s) {
-      mbar_init(full_bar(s), 1);
-      mbar_init(empty_bar(s), 1);
-    }
-    for (int b = 0; b < 2; ++b) {
-      mbar_init(acc_full_bar(b), 1);
-      mbar_init(acc_empty_bar(b), 4);  // one arrival per epilogue warp
-    }
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-  }
-  if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
-                 ::"r"(smem_u32(&tmem_base_slot)), "r"((uint32_t)C::kTmemCols) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-  }
-  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-  __syncthreads();
-  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-  const uint32_t tmem_base = tmem_base_slot;
-  allow_dependents();
-
-  if (warp == 0) {
-    if (lane == 0) {
-      grid_dependency_wait();
-      uint32_t armed = 0, armed_parity = 0;
-      int kbg = 0;  // K blocks loaded so far, over all tiles
-      bool ok = true;
-      for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
-        const int f_tile = tile / n_t_tiles, t_tile = tile % n_t_tiles;
-        for (int kb = 0; kb < total_kb; ++kb, ++kbg) {
-          const int s = kbg % C::kStages;
-          const uint32_t phase = (kbg / C::kStages) & 1;
-          if (!mbar_wait(empty_bar(s), phase ^ 1, &abort_flag, a.error_flag, 1)) { ok = false; break; }
-          const uint32_t sa = base + s * C::kStageBytes, sb = sa + C::kABytes;
-          mbar_expect_tx(full_bar(s), C::kStageBytes);
-          tma_load_2d(sa, &map_w, full_bar(s), kb * BK, f_tile * BM);
-          if (MODE == kGluBf16) tma_load_2d(sa + BM * BK * 2, &map_w, full_bar(s), kb * BK, a.N + f_tile * BM);
-          tma_load_2d(sb, &map_x, full_bar(s), kb * BK, t_tile * BN);
-          armed |= 1u << s;
-          armed_parity = (armed_parity & ~(1u << s)) | (phase << s);
-        }
-      }
-      if (!ok)  // gave up: let the loads already issued land before the block's memory goes away
-        for (int s = 0; s < C::kStages; ++s)
-          if (armed & (1u << s)) {
-            const long long t0 = clock64();
-            while (!mbar_try_wait(full_bar(s), (armed_parity >> s) & 1) && clock64() - t0 < kWaitCycles) {}
-          }
-    }
-  } else if (warp == 1) {
-    if (lane == 0) {
-      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) |
-                             ((uint32_t)(BM >> 4) << 24);
-      int kbg = 0, it = 0;
-      bool ok = true;
-      for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++it) {
-        const int buf = it & 1;
-        // the epilogue must have drained this accumulator (two tiles ago)
-        if (!mbar_wait(acc_empty_bar(buf), ((it >> 1) & 1) ^ 1, &abort_flag, a.error_flag, 5)) break;
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t d = tmem_base + buf * C::kAccCols;
-        for (int kb = 0; kb < total_kb; ++kb, ++kbg) {
-          const int s = kbg % C::kStages;
-          const uint32_t phase = (kbg / C::kStages) & 1;
-          if (!mbar_wait(full_bar(s), phase, &abort_flag, a.error_flag, 2)) { ok = false; break; }
-          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          const uint32_t sa = base + s * C::kStageBytes, sb = sa + C::kABytes;
-          const uint64_t da = umma_desc(sa), db = umma_desc(sb);
-#pragma unroll
-          for (int k = 0; k < BK / 16; ++k) {
-            const uint32_t acc = (kb > 0 || k > 0) ? 1u : 0u;
-            umma_bf16(d, da + 2 * k, db + 2 * k, idesc, acc);
-            if (MODE == kGluBf16) umma_bf16(d + BN, umma_desc(sa + BM * BK * 2) + 2 * k, db + 2 * k, idesc, acc);
-          }
-          umma_commit(empty_bar(s));
-        }
-        umma_commit(acc_full_bar(buf));
-      }
-    }
-  } else {
-    grid_dependency_wait();
-    const int quad = warp & 3;
-    int it = 0;
-    for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++it) {
-      const int f_tile = tile / n_t_tiles, t_tile = tile % n_t_tiles, buf = it & 1;
-      if (!mbar_wait(acc_full_bar(buf), (it >> 1) & 1, &abort_flag, a.error_flag, 3)) break;
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const int f = f_tile * BM + quad * 32 + lane;
-      const uint32_t taddr = tmem_base + buf * C::kAccCols + ((uint32_t)(quad * 32) << 16);
-      const int tok0 = t_tile * BN;
-#pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 16) {
-        if (tok0 + c0 >= a.M) break;
-        uint32_t r[16], u[16];
-        tmem_ld16(taddr + c0, r);
-        if (MODE == kGluBf16) tmem_ld16(taddr + BN + c0, u);
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        if (f < a.N) {
-          float old[16];
-          if (MODE == kAccumF32) {
-#pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              const int tok = tok0 + c0 + j;
-              old[j] = tok < a.M ? ((const float*)a.y)[(int64_t)tok * a.ldy + f] : 0.f;
-            }
-          }
-#pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const int tok = tok0 + c0 + j;
-            if (tok >= a.M) break;
-            const float v = __uint_as_float(r[j]);
-            if (MODE == kStoreBf16) {
-              ((__nv_bfloat16*)a.y)[(int64_t)tok * a.ldy + f] = __float2bfloat16_rn(v);
-            } else if (MODE == kStoreF32) {
-              ((float*)a.y)[(int64_t)tok * a.ldy + f] = v;
-            } else if (MODE == kAccumF32) {
-              ((float*)a.y)[(int64_t)tok * a.ldy + f] = old[j] + v;
-            } else {
-              const float up = __uint_as_float(u[j]);
-              ((__nv_bfloat16*)a.y)[(int64_t)tok * a.ldy + f] = __float2bfloat16_rn(v / (1.0f + expf(-v)) * up);
-            }
-          }
-        }
-      }
-      // this warp has read its lanes of the accumulator: hand it back to the MMA warp
-      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-      __syncwarp();
-      if (lane == 0) mbar_arrive(acc_empty_bar(buf));
-    }
-  }
-  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-  __syncthreads();
-  if (warp == 1) {
-    if (lane == 0) {  // every accumulator must be idle before its columns are freed
-      const int my_tiles = (n_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
-      for (int b = 0; b < 2; ++b) {
-        const int uses = (my_tiles + 1 - b) / 2;  // tiles that used accumulator b
-        if (uses > 0) {
-          const long long t0 = clock64();
-          while (!mbar_try_wait(acc_full_bar(b), (uses - 1) & 1) && clock64() - t0 < kWaitCycles) {}
-        }
-      }
-    }
-    __syncwarp();
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)C::kTmemCols) : "memory");
-  }
-}
-
-template <int BN, int MODE>
-int launch_persistent(const CUtensorMap& mw, const CUtensorMap& mx, const GemmArgs& a, int n_f, int n_t, cudaStream_t stream) {
-  using C = PCfg<BN, MODE>;
-  static bool configured = false;
-  static int n_sms = 0;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tc_persistent_kernel<BN, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         C::kSmemBytes);
-    if (e != cudaSuccess) return fail(kLaunchFailed, "gemm_tc: cannot reserve %d bytes of shared memory: %s",
-                                      C::kSmemBytes, cudaGetErrorString(e));
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, dev);
-    if (n_sms <= 0) n_sms = 148;
-    configured = true;
-  }
-  const int tiles = n_f * n_t;
-  launch_overlapped(gemm_tc_persistent_kernel<BN, MODE>, dim3(tiles < n_sms ? tiles : n_sms), dim3(kThreads),
-                    C::kSmemBytes, stream, mw, mx, a, n_f, n_t);
-  return check_launch("gemm_tc_persistent");
-}
-
 template <int BN, int MODE, bool NORMB = false>
 int launch(const CUtensorMap& mw, const CUtensorMap& mx, const GemmArgs& a, dim3 grid, cudaStream_t stream) {
   using C = Cfg<BN, MODE>;
@@ -1352,16 +1138,6 @@ extern "C" int skyla_gemm_tc(const void* map_w, const void* map_x, void* y, int6
              scratch, counters};
   dim3 grid((N + BM - 1) / BM, (M + bn - 1) / bn, splits);
   if (grid.y > 65535 || grid.z > 65535) return fail(kBadArgument, "gemm_tc: grid too large");
-  if (splits == 1 && mode <= kGluBf16 && ((mode == kGluBf16 && bn == 128) || (mode != kGluBf16 && bn == 256))) {
-    // many tokens: the persistent kernel with two accumulators
-    const int n_f = (int)grid.x, n_t = (int)grid.y;
-    switch (mode) {
-      case kStoreBf16: return launch_persistent<256, kStoreBf16>(mw, mx, a, n_f, n_t, stream);
-      case kStoreF32: return launch_persistent<256, kStoreF32>(mw, mx, a, n_f, n_t, stream);
-      case kAccumF32: return launch_persistent<256, kAccumF32>(mw, mx, a, n_f, n_t, stream);
-      default: return launch_persistent<128, kGluBf16>(mw, mx, a, n_f, n_t, stream);
-    }
-  }
   switch (mode) {
     case kStoreBf16: return launch_bn<kStoreBf16>(bn, mw, mx, a, grid, stream);
     case kStoreF32: return launch_bn<kStoreF32>(bn, mw, mx, a, grid, stream);

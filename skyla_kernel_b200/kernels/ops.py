@@ -260,8 +260,8 @@ def tc_linear_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
 
 
 def token_tile(m: int, gated: bool = False) -> int:
-    """Tokens per tile.  From 129 tokens on the persistent kernel takes over: tiles of 256
-    (128 for the gated product, whose two accumulators are twice as wide)."""
+    """Tokens per tile of the weight-major kernels (128 at most for the gated product, whose two
+    accumulators are twice as wide).  From 129 tokens on the parts use :func:`gemm_prompt` instead."""
     for bn in TC_TOKEN_TILES:
         if m <= bn:
             return 128 if gated and bn == 256 else bn

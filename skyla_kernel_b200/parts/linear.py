@@ -51,7 +51,7 @@ class Linear:
 
     def prompts(self, m: int) -> bool:
         """Whether ``m`` tokens go to the prompt kernel (tokens are the tile's rows; given operands it takes)."""
-        return self.tensor_cores and self.PROMPT_KERNEL and m >= ops.PROMPT_MIN_TOKENS
+        return self.tensor_cores and m >= ops.PROMPT_MIN_TOKENS
 
     def takes_scale_in(self, m: int) -> bool:
         """Whether :meth:`forward` of ``m`` tokens accepts ``scale_in``."""
@@ -184,7 +184,6 @@ class Linear:
     # next norm's input on the way would need the rows back in the threads (measured at 2,048 tokens of
     # the 8B shape: 106 against 65 us for the O product, more than the norm kernel it saves)
     PROMPT_NORM_AHEAD = os.environ.get("SKYLA_PROMPT_NORM_AHEAD", "0") != "0"
-    PROMPT_KERNEL = os.environ.get("SKYLA_PROMPT_KERNEL", "1") != "0"  # 0: prompts on the weight-major persistent kernel
 
     def can_fuse_norm(self, normed) -> bool:
         """Whether ``norm(x + pending)`` can be made inside this product: RMSNorm, float32 rows
