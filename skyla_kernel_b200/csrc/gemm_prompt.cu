@@ -19,7 +19,12 @@
 //     lie within one tile (head sizes 32, 64, 128, 256).
 //
 // One block per SM walks the output tiles (tiles of one weight tile are neighbours, so blocks
-// that run together share it through L2):
+// that run together share it through L2).  Where the tiles are fewer than half the SMs (a batch
+// or a prompt of a few hundred tokens), they are cut along K into equal runs of K blocks, one run
+// per block: a block whose run starts inside a tile leaves its accumulator in scratch (a "share")
+// and raises a flag; the block that has the tile's first K blocks adds the shares into its own
+// accumulator in block order and runs the epilogue.  The sum order is fixed by the shapes alone.
+// Roles:
 //   warp 0    one lane issues TMA loads of a [128 tokens x 64] and two [128 outputs x 64] boxes
 //             a stage (a gated weight: 128 gate rows and the 128 up rows that go with them);
 //   warp 1    allocates TMEM (two accumulators of 256 columns); one lane issues tcgen05.mma
@@ -76,6 +81,8 @@ struct PromptArgs {
   int M, N, K;           // tokens, outputs (after gating), reduction length
   int vec;               // rows of y (and of ahead.xw) start on 16 bytes: whole chunks go as vectors
   int y_tma;             // kAccumF32: the kernel got a tensor map of y and adds by TMA reduce
+  float* share;          // [block][BF / 4][BT rows][4] accumulators of tiles that are cut along K; null: none are
+  int* share_flags;      // [block]: 1 while that block's share waits to be taken; zero between launches
   int* error_flag;
   ScaleIn scale;         // scale.ssq_part == nullptr: none
   NormAhead ahead;       // ahead.xw == nullptr: none
@@ -123,6 +130,47 @@ __device__ __forceinline__ void load16_f32(const float* src, float* v, int n, bo
   }
 }
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// ---- which work a block does, computed alike by its three roles: whole tiles (tile = blockIdx.x +
+// i * gridDim.x), or, where the tiles are cut along K, one run of units (unit = one K block of one tile)
+struct Plan {
+  int total_kb, n_whole;
+  long long u, u_end, units;
+};
+struct Segment { int tile, kb0, kb1; };
+
+__device__ __forceinline__ Plan make_plan(const PromptArgs& a, int n_tiles, int total_kb) {
+  Plan p;
+  const int G = (int)gridDim.x, b = (int)blockIdx.x;
+  p.total_kb = total_kb;
+  if (a.share == nullptr) {
+    p.n_whole = b < n_tiles ? (n_tiles - b + G - 1) / G : 0;
+    p.units = p.u = p.u_end = 0;
+  } else {
+    p.n_whole = 0;
+    p.units = (long long)n_tiles * total_kb;
+    p.u = p.units * b / G;
+    p.u_end = p.units * (b + 1) / G;
+  }
+  return p;
+}
+__device__ __forceinline__ bool next_segment(Plan& p, int& i, Segment& s) {
+  if (i < p.n_whole) {
+    s.tile = (int)blockIdx.x + i * (int)gridDim.x;
+    s.kb0 = 0;
+    s.kb1 = p.total_kb;
+    ++i;
+    return true;
+  }
+  if (p.u >= p.u_end) return false;
+  s.tile = (int)(p.u / p.total_kb);
+  s.kb0 = (int)(p.u % p.total_kb);
+  const long long left = p.u_end - p.u;
+  s.kb1 = (long long)(p.total_kb - s.kb0) <= left ? p.total_kb : s.kb0 + (int)left;
+  p.u += s.kb1 - s.kb0;
+  ++i;
+  return true;
+}
 
 // ---- the epilogues: one thread, one token's row of the tile.  tcgen05.ld is a warp's business:
 // every lane runs every load; only what touches global memory looks at `valid`.
@@ -361,13 +409,15 @@ gemm_prompt_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
     if (lane == 0) {
       grid_dependency_wait();
       uint32_t armed = 0, armed_parity = 0;
-      int kbg = 0;  // K blocks loaded so far, over all tiles
+      int kbg = 0;  // K blocks loaded so far, over all segments
       bool ok = true;
-      for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
-        const int f_tile = tile / n_t_tiles, t_tile = tile % n_t_tiles;
+      Plan plan = make_plan(a, n_tiles, total_kb);
+      Segment sg;
+      for (int i = 0; ok && next_segment(plan, i, sg);) {
+        const int f_tile = sg.tile / n_t_tiles, t_tile = sg.tile % n_t_tiles;
         const int row0 = f_tile * kTileOutputs;
         const int row1 = MODE == kGluBf16 ? a.N + row0 : row0 + BF / 2;
-        for (int kb = 0; kb < total_kb; ++kb, ++kbg) {
+        for (int kb = sg.kb0; kb < sg.kb1; ++kb, ++kbg) {
           const int s = kbg % kStages;
           const uint32_t phase = (kbg / kStages) & 1;
           if (!mbar_wait(empty_bar(s), phase ^ 1, &abort_flag, a.error_flag, 1)) { ok = false; break; }
@@ -391,15 +441,17 @@ gemm_prompt_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
     if (lane == 0) {
       const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BF >> 3) << 17) |
                              ((uint32_t)(BT >> 4) << 24);
-      int kbg = 0, it = 0;
+      int kbg = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++it) {
-        const int buf = it & 1;
-        // the epilogue must have drained this accumulator (two tiles ago)
+      Plan plan = make_plan(a, n_tiles, total_kb);
+      Segment sg;
+      for (int i = 0; ok && next_segment(plan, i, sg);) {
+        const int it = i - 1, buf = it & 1;
+        // the epilogue must have drained this accumulator (two segments ago)
         if (!mbar_wait(acc_empty_bar(buf), ((it >> 1) & 1) ^ 1, &abort_flag, a.error_flag, 5)) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t d = tmem_base + buf * BF;
-        for (int kb = 0; kb < total_kb; ++kb, ++kbg) {
+        for (int kb = sg.kb0; kb < sg.kb1; ++kb, ++kbg) {
           const int s = kbg % kStages;
           const uint32_t phase = (kbg / kStages) & 1;
           if (!mbar_wait(full_bar(s), phase, &abort_flag, a.error_flag, 2)) { ok = false; break; }
@@ -407,7 +459,7 @@ gemm_prompt_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
           const uint32_t sx = base + s * kStageBytes, sw = sx + kXBytes;
           const uint64_t dx = umma_desc(sx), dw = umma_desc(sw);
 #pragma unroll
-          for (int k = 0; k < BK / 16; ++k) umma_bf16(d, dx + 2 * k, dw + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          for (int k = 0; k < BK / 16; ++k) umma_bf16(d, dx + 2 * k, dw + 2 * k, idesc, (kb > sg.kb0 || k > 0) ? 1u : 0u);
           umma_commit(empty_bar(s));
         }
         umma_commit(acc_full_bar(buf));
@@ -415,26 +467,109 @@ gemm_prompt_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
     }
   } else {
     grid_dependency_wait();
-    const int quad = warp & 3;
+    const int quad = warp & 3, row = quad * 32 + lane;
     const bool by_tma = MODE == kAccumF32 && a.y_tma != 0;
     const bool sender = warp == 2 && lane == 0;
-    int it = 0, n_sent = 0;
-    for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++it) {
-      const int f_tile = tile / n_t_tiles, t_tile = tile % n_t_tiles, buf = it & 1;
-      const int tok = t_tile * BT + quad * 32 + lane;
+    const int G = (int)gridDim.x, me = (int)blockIdx.x;
+    constexpr int kShareVecs = BT * BF / 4;  // a share: [4 columns][row] as float4, a warp's 32 rows 512 bytes in a row
+    int n_sent = 0;
+    Plan plan = make_plan(a, n_tiles, total_kb);
+    const long long units = plan.units;
+    Segment sg;
+    for (int i = 0; next_segment(plan, i, sg);) {
+      const int it = i - 1, buf = it & 1;
+      const int f_tile = sg.tile / n_t_tiles, t_tile = sg.tile % n_t_tiles;
+      const int tok = t_tile * BT + row;
       const bool valid = tok < a.M;
+      const bool gives = sg.kb0 > 0;                        // another block has the tile's first K blocks
+      const bool takes = sg.kb0 == 0 && sg.kb1 < total_kb;  // this block finishes the tile from others' shares
       float s = 1.0f;
-      if (a.scale.ssq_part != nullptr && valid) {  // while the tile's products run
+      if (a.scale.ssq_part != nullptr && valid && !gives) {  // while the tile's products run
         float v = 0.f;
         for (int p = 0; p < a.scale.n_parts; ++p) v += a.scale.ssq_part[(int64_t)p * a.M + tok];
         s = 1.0f / sqrtf(v / (float)a.scale.width + a.scale.eps);
       }
+      int n_parts = 0;
+      if (takes) {  // the blocks after this one whose runs begin inside this tile
+        const long long tile_end = (long long)(sg.tile + 1) * total_kb;
+        while (me + 1 + n_parts < G && units * (me + 1 + n_parts) / G < tile_end) ++n_parts;
+      }
       if (!mbar_wait(acc_full_bar(buf), (it >> 1) & 1, &abort_flag, a.error_flag, 3)) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const uint32_t taddr = tmem_base + buf * BF + ((uint32_t)(quad * 32) << 16);
-      if (MODE == kQkvPrep) drain_qkv(a, taddr, tok, valid, f_tile * kTileOutputs, s);
-      else if (by_tma) drain_reduce(a, &map_y, taddr, out_smem, quad * 32 + lane, t_tile * BT, f_tile * kTileOutputs, s, sender, n_sent);
-      else drain_plain<MODE>(a, taddr, tok, valid, f_tile * kTileOutputs, s);
+      if (gives) {
+        // leave the accumulator for the block that has the tile's first K blocks
+        float4* sh = (float4*)a.share + (int64_t)me * kShareVecs + row;
+#pragma unroll 1
+        for (int c0 = 0; c0 < BF; c0 += 64) {
+          uint32_t r[64];
+          __syncwarp();
+#pragma unroll
+          for (int g = 0; g < 4; ++g) tmem_ld16(taddr + c0 + 16 * g, r + 16 * g);
+          tmem_wait_ld();
+#pragma unroll
+          for (int j = 0; j < 16; ++j)
+            __stcg(sh + (int64_t)(c0 / 4 + j) * BT, make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                                                                 __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3])));
+        }
+        __threadfence();
+        asm volatile("barrier.sync 1, 128;" ::: "memory");
+        if (sender) atomicExch(a.share_flags + me, 1);
+      } else {
+        if (takes) {
+          if (sender) {
+            for (int q = 0; q < n_parts && !abort_flag; ++q) {
+              const volatile int* flag = a.share_flags + me + 1 + q;
+              const long long t0 = clock64();
+              while (*flag == 0) {
+                if (clock64() - t0 > kWaitCycles) {
+                  abort_flag = 1;
+                  if (a.error_flag != nullptr) atomicCAS(a.error_flag, 0, 6);
+                  break;
+                }
+              }
+            }
+            __threadfence();
+          }
+          asm volatile("barrier.sync 1, 128;" ::: "memory");
+          if (abort_flag) break;  // the same for all four warps: written before the barrier
+          // add the shares into the accumulator where it lies, in block order; 64 columns' loads are
+          // in flight together (taken one by one with the epilogue's steps they cost a trip to L2 each)
+          const float4* sh = (const float4*)a.share + (int64_t)(me + 1) * kShareVecs + row;
+#pragma unroll 1
+          for (int c0 = 0; c0 < BF; c0 += 64) {
+#pragma unroll 1
+            for (int q = 0; q < n_parts; ++q) {
+              float4 v[16];
+#pragma unroll
+              for (int j = 0; j < 16; ++j) v[j] = __ldcg(sh + (int64_t)q * kShareVecs + (int64_t)(c0 / 4 + j) * BT);
+#pragma unroll
+              for (int g = 0; g < 4; ++g) {
+                uint32_t r[16];
+                __syncwarp();
+                tmem_ld16(taddr + c0 + 16 * g, r);
+                tmem_wait_ld();
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  r[4 * j] = __float_as_uint(__uint_as_float(r[4 * j]) + v[4 * g + j].x);
+                  r[4 * j + 1] = __float_as_uint(__uint_as_float(r[4 * j + 1]) + v[4 * g + j].y);
+                  r[4 * j + 2] = __float_as_uint(__uint_as_float(r[4 * j + 2]) + v[4 * g + j].z);
+                  r[4 * j + 3] = __float_as_uint(__uint_as_float(r[4 * j + 3]) + v[4 * g + j].w);
+                }
+                tmem_st16(taddr + c0 + 16 * g, r);
+              }
+              asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+            }
+          }
+          // the shares are read: their flags go back to zero for the next launch
+          asm volatile("barrier.sync 1, 128;" ::: "memory");
+          if (sender)
+            for (int q = 0; q < n_parts; ++q) a.share_flags[me + 1 + q] = 0;
+        }
+        if (MODE == kQkvPrep) drain_qkv(a, taddr, tok, valid, f_tile * kTileOutputs, s);
+        else if (by_tma) drain_reduce(a, &map_y, taddr, out_smem, row, t_tile * BT, f_tile * kTileOutputs, s, sender, n_sent);
+        else drain_plain<MODE>(a, taddr, tok, valid, f_tile * kTileOutputs, s);
+      }
       // this warp has read its lanes of the accumulator: hand it back to the MMA warp
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
@@ -446,9 +581,12 @@ gemm_prompt_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
   __syncthreads();
   if (warp == 1) {
     if (lane == 0) {  // every accumulator must be idle before its columns are freed
-      const int my_tiles = (n_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
+      Plan plan = make_plan(a, n_tiles, total_kb);
+      Segment sg;
+      int my_segments = 0;
+      while (next_segment(plan, my_segments, sg)) {}
       for (int b = 0; b < 2; ++b) {
-        const int uses = (my_tiles + 1 - b) / 2;  // tiles that used accumulator b
+        const int uses = (my_segments + 1 - b) / 2;  // segments that used accumulator b
         if (uses > 0) {
           const long long t0 = clock64();
           while (!mbar_try_wait(acc_full_bar(b), (uses - 1) & 1) && clock64() - t0 < kWaitCycles) {}
@@ -461,8 +599,22 @@ gemm_prompt_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
   }
 }
 
+// Whether `tiles` tiles of `total_kb` K blocks are cut along K, and over how many blocks: where the
+// tiles are at most half the SMs, every tile is cut into the same number of runs, at most four (the
+// tile's owner reads the other runs' accumulators through its one SM: about 3 us each) of at least
+// 8 K blocks.  0: whole tiles.  (Cutting only a last, partial round of many tiles measured slower
+// than leaving it: 63 against 57 us for 256 tiles of 64 K blocks.)
+int cut_blocks(long long tiles, long long total_kb, int n_sms) {
+  if (tiles <= 0 || tiles * 2 > n_sms) return 0;
+  long long runs = n_sms / tiles;
+  if (runs > 4) runs = 4;
+  if (runs > total_kb / 8) runs = total_kb / 8;
+  return runs < 2 ? 0 : (int)(tiles * runs);
+}
+
 template <int MODE>
-int launch(const CUtensorMap& mx, const CUtensorMap& mw, const CUtensorMap& my, const PromptArgs& a, cudaStream_t stream) {
+int launch(const CUtensorMap& mx, const CUtensorMap& mw, const CUtensorMap& my, const PromptArgs& a, int share_blocks,
+           cudaStream_t stream) {
   static bool configured = false;
   static int n_sms = 0;
   if (!configured) {
@@ -479,11 +631,20 @@ int launch(const CUtensorMap& mx, const CUtensorMap& mw, const CUtensorMap& my, 
   const int n_f = (a.N + per_tile - 1) / per_tile, n_t = (a.M + BT - 1) / BT;
   const long long tiles = (long long)n_f * n_t;
   if (tiles > 0x7fffffffLL) return fail(kBadArgument, "gemm_prompt: too many tiles");
-  launch_overlapped(gemm_prompt_kernel<MODE>, dim3((unsigned)(tiles < n_sms ? tiles : n_sms)), dim3(kThreads),
-                    (size_t)kSmemBytes, stream, mx, mw, my, a, n_t, n_f);
+  PromptArgs b = a;
+  const int cut = b.share != nullptr ? cut_blocks(tiles, (a.K + BK - 1) / BK, n_sms < share_blocks ? n_sms : share_blocks) : 0;
+  if (cut == 0) b.share = nullptr;
+  const unsigned grid = cut > 0 ? (unsigned)cut : (unsigned)(tiles < n_sms ? tiles : n_sms);
+  launch_overlapped(gemm_prompt_kernel<MODE>, dim3(grid), dim3(kThreads), (size_t)kSmemBytes, stream, mx, mw, my, b, n_t, n_f);
   return check_launch("gemm_prompt");
 }
 }  // namespace
+
+// Over how many blocks a product of these sizes is cut along K on a device of n_sms SMs (0: whole tiles).
+extern "C" int skyla_gemm_prompt_cut_blocks(int M, int N, int K, int gated, int n_sms) {
+  const long long n_f = (N + (gated ? BF / 2 : BF) - 1) / (gated ? BF / 2 : BF), n_t = (M + BT - 1) / BT;
+  return n_sms > 0 ? cut_blocks(n_f * n_t, (K + BK - 1) / BK, n_sms) : 0;
+}
 
 // How many shares of a row's sum of squares the "norm ahead" of a product with N outputs leaves.
 extern "C" int skyla_gemm_prompt_ahead_parts(int N) { return (N + BF - 1) / BF; }
@@ -515,6 +676,8 @@ extern "C" int skyla_output_map_f32(void* out, const void* ptr, uint64_t rows, u
 //   256) each; y [M, nq * hd] bfloat16 receives the prepared queries, the pools the keys and values;
 //   q_norm / k_norm [hd] or null; cos_t / sin_t [positions][hd / 2] or both null (the whole head rotates).
 // scale_ssq (or null): the result is multiplied by 1/sqrt(sum_p scale_ssq[p * M + tok] / K + scale_eps).
+// share, share_flags (or null): scratch of share_blocks x 128 x 256 floats and as many flags (zero between
+//   launches), with which few tiles are cut along K over up to share_blocks blocks.
 // ahead_xw (or null; mode 2): also leave bf16(y_new * ahead_w) in ahead_xw [M, N] and each tile's share
 //   of the rows' sums of squares in ahead_ssq [skyla_gemm_prompt_ahead_parts(N)][M].
 extern "C" int skyla_gemm_prompt(const void* map_x, const void* map_w, const void* map_y, void* y, int64_t ldy, int M, int N, int K, int mode,
@@ -523,7 +686,7 @@ extern "C" int skyla_gemm_prompt(const void* map_x, const void* map_w, const voi
                                  int nq, int nkv, int hd, const float* q_norm, const float* k_norm, float qk_eps,
                                  const float* cos_t, const float* sin_t, const int32_t* tok_pos, const int32_t* tok_slot,
                                  void* k_pool, void* v_pool, const int32_t* page_table, int max_pages, int page_size,
-                                 cudaStream_t stream) {
+                                 float* share, int* share_flags, int share_blocks, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return kOk;
   if (K <= 0 || K % 8) return fail(kBadArgument, "gemm_prompt: K=%d must be a positive multiple of 8", K);
   if (mode < 0 || mode > kQkvPrep) return fail(kBadArgument, "gemm_prompt: unknown epilogue %d", mode);
@@ -534,6 +697,7 @@ extern "C" int skyla_gemm_prompt(const void* map_x, const void* map_w, const voi
   else memcpy(&my, map_x, sizeof(my));  // not used; a valid map all the same
   PromptArgs a{};
   a.y = y; a.ldy = ldy; a.M = M; a.N = N; a.K = K; a.error_flag = error_flag;
+  if (share != nullptr && share_flags != nullptr && share_blocks > 1) { a.share = share; a.share_flags = share_flags; }
   const int per16 = (mode == kStoreF32 || mode == kAccumF32) ? 4 : 8;  // elements of y in 16 bytes
   a.vec = ((uintptr_t)y % 16 == 0 && ldy % per16 == 0) ? 1 : 0;
   if (scale_ssq != nullptr) {
@@ -567,10 +731,10 @@ extern "C" int skyla_gemm_prompt(const void* map_x, const void* map_w, const voi
                      (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, page_table, max_pages, page_size};
   }
   switch (mode) {
-    case kStoreBf16: return launch<kStoreBf16>(mx, mw, my, a, stream);
-    case kStoreF32: return launch<kStoreF32>(mx, mw, my, a, stream);
-    case kAccumF32: return launch<kAccumF32>(mx, mw, my, a, stream);
-    case kGluBf16: return launch<kGluBf16>(mx, mw, my, a, stream);
-    default: return launch<kQkvPrep>(mx, mw, my, a, stream);
+    case kStoreBf16: return launch<kStoreBf16>(mx, mw, my, a, share_blocks, stream);
+    case kStoreF32: return launch<kStoreF32>(mx, mw, my, a, share_blocks, stream);
+    case kAccumF32: return launch<kAccumF32>(mx, mw, my, a, share_blocks, stream);
+    case kGluBf16: return launch<kGluBf16>(mx, mw, my, a, share_blocks, stream);
+    default: return launch<kQkvPrep>(mx, mw, my, a, share_blocks, stream);
   }
 }

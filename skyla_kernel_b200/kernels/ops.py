@@ -215,6 +215,8 @@ def check_device_errors(device) -> None:
         code = int(t.item())
         if code:
             t.zero_()
+            for _, flags, _ in _PROMPT_SHARES.values():
+                flags.zero_()  # a kernel that gave up may have left some raised
             raise KernelError(f"a kernel's bounded wait ran out (code {code}); its results are not valid")
 
 
@@ -513,7 +515,10 @@ def gemm_tc_rows(x: Optional[torch.Tensor], w_map: TensorMap, rows: int, n_out: 
 
 # ------------------------------------------------------- tensor-core linear, prompts
 TC_QKV_PREP = 4  # gemm_prompt only: the product's heads go through norm and rotation into q and the cache
-PROMPT_MIN_TOKENS = 129  # fewer tokens leave most of a 128-token tile empty: the weight-major kernels take them
+# Fewer tokens leave most of a 128-token tile empty, and the weight-major kernels take them.  (At 96 and
+# 128 tokens of the 8B shape the two are about even: QKV 28 against 21 us, O 26 against 25, gate/up 48
+# against 48, down 41 against 60.)
+PROMPT_MIN_TOKENS = 129
 
 
 PROMPT_TMA_ADD = os.environ.get("SKYLA_PROMPT_TMA_ADD", "1") != "0"  # 0: the threads read, add and write y themselves
@@ -532,6 +537,27 @@ def _output_map(y: torch.Tensor):
         _check_nolaunch("gemm_prompt", f(buf, _ptr(y), y.shape[0], y.shape[1], _rows(y, "y")))
         _Y_MAPS[key] = buf
     return buf
+
+
+PROMPT_CUT_K = os.environ.get("SKYLA_PROMPT_CUT_K", "1") != "0"  # 0: few tiles stay whole tiles on few SMs
+_PROMPT_SHARES = {}
+
+
+def _prompt_shares(device):
+    """(scratch for one accumulator tile per SM, a flag per SM, SMs) for ``gemm_prompt``'s tiles that are cut along K."""
+    dev = torch.device(device)
+    t = _PROMPT_SHARES.get(dev)
+    if t is None:
+        n = torch.cuda.get_device_properties(dev).multi_processor_count
+        t = _PROMPT_SHARES[dev] = (torch.empty(n * 128 * 256, dtype=torch.float32, device=dev),
+                                   torch.zeros(n, dtype=torch.int32, device=dev), n)
+    return t
+
+
+def prompt_cut_blocks(m: int, n_out: int, k: int, gated: bool, device) -> int:
+    """Over how many blocks ``gemm_prompt`` cuts this product's tiles along K (0: whole tiles)."""
+    f = _fn("gemm_prompt", "skyla_gemm_prompt_cut_blocks", [c_int, c_int, c_int, c_int, c_int])
+    return int(f(m, n_out, k, int(gated), _prompt_shares(device)[2])) if PROMPT_CUT_K else 0
 
 
 def prompt_ahead_parts(n_out: int) -> int:
@@ -621,9 +647,10 @@ def gemm_prompt(x: torch.Tensor, w_map: TensorMap, n_out: int, y: torch.Tensor, 
             [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_float,
              c_void_p, c_void_p, c_int64, c_void_p,
              c_int, c_int, c_int, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_void_p,
-             c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p])
+             c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p])
+    share, flags, n_share = _prompt_shares(x.device) if PROMPT_CUT_K else (None, None, 0)
     _check("gemm_prompt", f(xm.buf, w_map.buf, ym, _ptr(y), _rows(y, "y"), m, n_out, k, mode, _ptr(error_flag(x.device)),
-                            *scale_args, *ahead_args, *prep_args, _stream()))
+                            *scale_args, *ahead_args, *prep_args, _ptr(share), _ptr(flags), n_share, _stream()))
     return y
 
 
