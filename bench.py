@@ -194,7 +194,7 @@ def e2e_decode(model, batch, prompt_len, steps, warmup, vocab):
             "ms_per_step": dt / steps * 1e3}
 
 
-def prefill_once(model, cfg, length, reps=3, warmup=1):
+def prefill_once(model, cfg, length, reps=5, warmup=3):
     import torch
     from skyla_kernel_b200.engine import StepItem
     eng = model.engine
