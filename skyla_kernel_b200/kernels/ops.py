@@ -76,6 +76,8 @@ def _fn(module: str, name: str, argtypes):
 
 #: kernel launches made through this module since import (bench.py reports the difference)
 LAUNCHES = 0
+#: the same per kernel library, for tests that want to know which kernels a step went through
+LAUNCHES_BY_MODULE = {}
 
 
 def _check_nolaunch(module: str, rc: int):
@@ -87,6 +89,7 @@ def _check_nolaunch(module: str, rc: int):
 def _check(module: str, rc: int):
     global LAUNCHES
     LAUNCHES += 1
+    LAUNCHES_BY_MODULE[module] = LAUNCHES_BY_MODULE.get(module, 0) + 1
     if rc != 0:
         msg = build.load(module).skyla_error_message().decode("utf-8", "replace")
         raise KernelError(msg or f"{module}: error {rc}")

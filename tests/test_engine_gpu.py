@@ -8,7 +8,7 @@ from helpers import TINY, assert_close, make_folder, random_tokens
 pytestmark = pytest.mark.gpu
 
 DTYPES = ["float32", "bfloat16"]
-NAMES = ["A", "B", "C"]
+NAMES = ["A", "B", "C", "D"]
 
 
 @pytest.fixture(scope="module")
@@ -39,7 +39,7 @@ def test_whole_sequence_alone(folders, name, dtype):
     from skyla_kernel_b200.engine import StepItem
     eng = _engine(folders[name], dtype)
     V = TINY[name][0]["vocab_size"]
-    for n, seed in ((1, 3), (5, 4), (70, 5), (150, 6)):
+    for n, seed in ((1, 3), (5, 4), (70, 5), (150, 6), (300, 7)):
         toks = random_tokens(n, V, seed)
         s = eng.alloc_slot()
         got = eng.step([StepItem(s, toks, list(range(n)))])
@@ -100,3 +100,23 @@ def test_unequal_batches_with_slot_reuse(folders, name, dtype):
             _check(folders[name], seqs[i], torch.cat(got[i]), dtype, f"{name} {dtype} round {round_} request {i}")
         eng.cache.check()
         assert eng.cache.slots.n_held == 0 and all(g.pages.n_held == 0 for g in eng.cache.groups)
+
+
+def test_the_wide_configuration_reaches_the_blackwell_kernels(folders):
+    """Configuration D is there for the kernels that small sizes never reach: a prompt of 150 tokens
+    must go through the token-major product (with its tiles cut along K) and the tcgen05 attention."""
+    from skyla_kernel_b200.engine import StepItem
+    from skyla_kernel_b200.kernels import ops
+    base = TINY["D"][0]
+    eng = _engine(folders["D"], "bfloat16")
+    before = dict(ops.LAUNCHES_BY_MODULE)
+    s = eng.alloc_slot()
+    eng.step([StepItem(s, random_tokens(150, base["vocab_size"], 1), [149])])
+    eng.free_slot(s)
+    made = {m: n - before.get(m, 0) for m, n in ops.LAUNCHES_BY_MODULE.items()}
+    L = base["num_hidden_layers"]
+    assert made.get("gemm_prompt", 0) == 4 * L, made   # q/k/v, o, gate+up, down
+    assert made.get("attention_tc", 0) == L, made
+    assert made.get("attn_prep", 0) == 0, made          # the heads are finished in the q/k/v product
+    if torch.cuda.get_device_properties(0).multi_processor_count >= 64:
+        assert ops.prompt_cut_blocks(150, base["hidden_size"], base["hidden_size"], False, "cuda:0") > 0
