@@ -30,7 +30,7 @@ def _read(out, step, vocab):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("name", ["A", "B", "D"])
 def test_replay_three_ways(tmp_path, name, dtype):
     folder = make_folder(tmp_path, name)
     cfg, w = plain.read_folder(folder)
