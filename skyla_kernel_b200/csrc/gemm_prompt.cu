@@ -19,9 +19,9 @@
 //     lie within one tile (head sizes 32, 64, 128, 256).
 //
 // One block per SM walks the output tiles (tiles of one weight tile are neighbours, so blocks
-// that run together share it through L2).  Where the tiles are fewer than half the SMs (a batch
-// or a prompt of a few hundred tokens), they are cut along K into equal runs of K blocks, one run
-// per block: a block whose run starts inside a tile leaves its accumulator in scratch (a "share")
+// that run together share it through L2).  Where the tiles are at most half the SMs (a prompt of
+// a few hundred tokens), each is cut along K into up to four equal runs of K blocks, one run per
+// block: a block whose run starts inside a tile leaves its accumulator in scratch (a "share")
 // and raises a flag; the block that has the tile's first K blocks adds the shares into its own
 // accumulator in block order and runs the epilogue.  The sum order is fixed by the shapes alone.
 // Roles:
