@@ -19,6 +19,8 @@ STORE, ACCUMULATE, GATED = ops.STORE, ops.ACCUMULATE, ops.GATED
 class Linear:
     kernel_modules = ("linear_plain", "gemm_tc", "gemm_prompt")
 
+    #: inputs from which a product of 65 to 128 tokens goes to the prompt kernel
+    PROMPT_LONG_K = 8192
     #: the weight-streaming kernel takes over up to this many tokens ...
     ROWS_MAX_TOKENS = 64
     #: ... but where its blocks each read every token's whole row (short tiles, no K split) only
@@ -51,7 +53,12 @@ class Linear:
 
     def prompts(self, m: int) -> bool:
         """Whether ``m`` tokens go to the prompt kernel (tokens are the tile's rows; given operands it takes)."""
-        return self.tensor_cores and m >= ops.PROMPT_MIN_TOKENS
+        if not self.tensor_cores:
+            return False
+        # from 65 tokens already where the reduction is long: the weight-major kernel cuts K for at most 64
+        # tokens, the prompt kernel for few tiles of any height (down product of the 8B shape at 96 and 128
+        # tokens: 41 against 60 us; the products with 4,096 inputs are even or lose)
+        return m >= ops.PROMPT_MIN_TOKENS or (m > self.ROWS_MAX_TOKENS and self.n_in >= self.PROMPT_LONG_K and not self.gated)
 
     def takes_scale_in(self, m: int) -> bool:
         """Whether :meth:`forward` of ``m`` tokens accepts ``scale_in``."""
