@@ -19,9 +19,10 @@ TINY_C = dict(hidden_size=80, num_hidden_layers=1, num_attention_heads=3, num_ke
               rms_norm_eps=3e-6, max_position_embeddings=512, tie_word_embeddings=False,
               rope_scaling={"rope_type": "yarn", "factor": 4.0,
                             "original_max_position_embeddings": 64, "attn_factor": 1.0})
-# Not tiny in width: heads of 128 in pairs and a width of 1024 bring in the kernels that the small
-# ones never reach (tcgen05 attention, heads finished in the q/k/v product, tiles cut along K).
-WIDE_D = dict(hidden_size=1024, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+# Not tiny in width: heads of 128 in pairs and a width of 2048 bring in the kernels that the small
+# ones never reach (tcgen05 attention, heads finished in the q/k/v product, tiles cut along K,
+# K-split products of mid-size batches).
+WIDE_D = dict(hidden_size=2048, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
               head_dim=128, intermediate_size=1280, vocab_size=300, rope_theta=20000.0,
               rms_norm_eps=2e-6, max_position_embeddings=1024, tie_word_embeddings=False)
 TINY = {"A": (TINY_A, "float32", 0), "B": (TINY_B, "bfloat16", 1), "C": (TINY_C, "bfloat16", 2),

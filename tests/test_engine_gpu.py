@@ -102,6 +102,32 @@ def test_unequal_batches_with_slot_reuse(folders, name, dtype):
         assert eng.cache.slots.n_held == 0 and all(g.pages.n_held == 0 for g in eng.cache.groups)
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["B", "D"])
+def test_a_batch_of_twenty_decodes(folders, name, dtype):
+    """Twenty unequal prompts in one step, then six tokens each: the batch sizes between the few
+    tokens of the other tests and a prompt's many have kernels of their own."""
+    from skyla_kernel_b200.engine import StepItem
+    V = TINY[name][0]["vocab_size"]
+    eng = _engine(folders[name], dtype, max_tokens=20 * 128)
+    lens = [3 + (7 * i) % 38 for i in range(20)]
+    seqs = [random_tokens(p + 6, V, 300 + i) for i, p in enumerate(lens)]
+    slots = [eng.alloc_slot() for _ in seqs]
+    out = eng.step([StepItem(slots[i], seqs[i][:p], list(range(p))) for i, p in enumerate(lens)])
+    got, o = [], 0
+    for p in lens:
+        got.append([out[o:o + p]]); o += p
+    for t in range(6):
+        out = eng.step([StepItem(slots[i], [seqs[i][p + t]], [0]) for i, p in enumerate(lens)])
+        for i in range(len(seqs)):
+            got[i].append(out[i:i + 1])
+    for i in range(len(seqs)):
+        _check(folders[name], seqs[i], torch.cat(got[i]), dtype, f"{name} {dtype} batch of twenty, request {i}")
+    for sl in slots:
+        eng.free_slot(sl)
+    eng.cache.check()
+
+
 def test_the_wide_configuration_reaches_the_blackwell_kernels(folders):
     """Configuration D is there for the kernels that small sizes never reach: a prompt of 150 tokens
     must go through the token-major product (with its tiles cut along K) and the tcgen05 attention."""
