@@ -8,7 +8,7 @@ a random-weights writer and the replay program.
     skyla bench MODEL [--batch 8] [--prompt-len 512] [-n 64]
     skyla bench-bw [--mib 512] [--reps 9]
     skyla random --config CONFIG.json --out DIR [--seed S] [--dtype bfloat16|float32]
-    skyla kernel-bench linear|attention-decode|attention-prefill [sizes]
+    skyla kernel-bench linear|attention-decode|attention-prefill|step [sizes]
     skyla replay --model DIR --dtype D --out DIR --max-tokens N   (same as bin/trace_run)
 """
 from __future__ import annotations
@@ -205,7 +205,8 @@ def main(argv=None) -> int:
     p.add_argument("--norm-std", type=float, default=0.02)
     p.set_defaults(fn=cmd_random)
     p = sub.add_parser("kernel-bench", help="time one kernel on its own (also the target of profiler captures)")
-    p.add_argument("kernel", choices=["linear", "attention-decode", "attention-prefill"])
+    p.add_argument("kernel", choices=["linear", "attention-decode", "attention-prefill", "step"])
+    p.add_argument("--layers", type=int, default=4, help="step: layers of the 8B-shaped model")
     p.add_argument("--tokens", type=int, default=8)
     p.add_argument("--n-out", type=int, default=4096)
     p.add_argument("--n-in", type=int, default=4096)

@@ -5,6 +5,8 @@ dispatch (skyla-vk/src/submit.rs:31-76).  Also the target of profiler captures:
     skyla kernel-bench linear --tokens 8 --n-out 4096 --n-in 12288 --mode accumulate
     skyla kernel-bench attention-decode --batch 8 --context 2048
     skyla kernel-bench attention-prefill --tokens 2048
+    skyla kernel-bench step --tokens 2048 --batch 1 --layers 4      (a prompt step of the 8B layer sizes)
+    skyla kernel-bench step --tokens 1 --batch 8 --context 2048 --layers 4   (a decode step)
 """
 from __future__ import annotations
 
@@ -150,8 +152,65 @@ def attention_prefill(tokens: int, nq: int = 32, nkv: int = 8, hd: int = 128, re
     return {"kernel": "attention-prefill", "tokens": tokens, "us": us, "TFLOPs": flops / us / 1e6}
 
 
+def step(tokens: int, batch: int, context: int, layers: int, reps: int = 3) -> dict:
+    """Whole steps of a model with the Qwen3-8B layer sizes and ``layers`` layers, random weights drawn on
+    the device: ``batch`` prompts of ``tokens`` tokens in one step (``tokens`` > 1), or one token for each
+    of ``batch`` sequences that hold ``context`` positions (``tokens`` == 1).  With an event after each
+    stage on the last repetition (for a decode step that repetition is launched kernel by kernel, not as
+    its graph, so its stage times are those of the host).  The launches of the last repetition are what a
+    profiler's launch list should look at."""
+    from .config import Qwen3Config
+    from .engine import Engine, StepItem, declared_tensors
+    cfg = Qwen3Config(hidden_size=4096, num_hidden_layers=layers, num_attention_heads=32, num_key_value_heads=8,
+                      head_dim=128, intermediate_size=12288, vocab_size=151936, rope_theta=1000000.0, rms_norm_eps=1e-6,
+                      max_position_embeddings=40960, tie_word_embeddings=False)
+    tensors = {}
+    for i, (name, d) in enumerate(declared_tensors(cfg.to_spec()).items()):
+        t = torch.empty(d.shape, dtype=torch.bfloat16, device=DEV)
+        ops.fill_normal(t, 1.0 if d.init == "norm" else 0.0, 0.02, i)
+        tensors[name] = t
+    length = tokens if tokens > 1 else context
+    eng = Engine(cfg, tensors, "bfloat16", max_tokens=batch * (length + 128), max_slots=batch)
+    del tensors
+    g = torch.Generator().manual_seed(1)
+    prompts = [torch.randint(0, cfg.vocab_size, (length,), generator=g).tolist() for _ in range(batch)]
+    times = []
+    if tokens > 1:
+        for r in range(reps + 2):  # one untimed, `reps` timed, one with stage events
+            slots = [eng.alloc_slot() for _ in range(batch)]
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            eng.step([StepItem(s, p, [length - 1]) for s, p in zip(slots, prompts)], profile=(r == reps + 1))
+            b.record()
+            torch.cuda.synchronize()
+            times.append(a.elapsed_time(b))
+            for s in slots:
+                eng.free_slot(s)
+    else:
+        slots = [eng.alloc_slot() for _ in range(batch)]
+        per = max(1, 16384 // length)
+        for i in range(0, batch, per):
+            eng.step([StepItem(s, p, [length - 1]) for s, p in zip(slots[i:i + per], prompts[i:i + per])])
+        for r in range(reps + 4):  # three untimed (the first records the graph), `reps` timed, one with stage events
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            eng.step([StepItem(s, [5], [0]) for s in slots], profile=(r == reps + 3))
+            b.record()
+            torch.cuda.synchronize()
+            times.append(a.elapsed_time(b))
+    stages = {}
+    for label, ns in eng.last_step_profile():
+        stages[label] = stages.get(label, 0.0) + ns / 1e3
+    timed = sorted(times[-1 - reps:-1])
+    return {"kernel": "step", "tokens": tokens, "batch": batch, "context": length, "layers": layers,
+            "ms": timed[len(timed) // 2], "ms_with_stage_events": times[-1],
+            "stage_us": {k: round(v, 1) for k, v in stages.items()}}
+
+
 def main(a) -> int:
-    if a.kernel == "linear":
+    if a.kernel == "step":
+        r = step(a.tokens, a.batch, a.context, a.layers, reps=a.reps)
+    elif a.kernel == "linear":
         r = linear(a.tokens, a.n_out, a.n_in, a.mode, reps=a.reps, rows_max=a.rows_max, plan=a.plan)
     elif a.kernel == "attention-decode":
         r = attention_decode(a.batch, a.context, reps=a.reps, splits=a.splits)
