@@ -521,6 +521,7 @@ gemm_tc_rows_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
   __shared__ uint32_t tmem_base_slot;
   __shared__ volatile int abort_flag;
   __shared__ float row_ssq[BN];  // the rows' sums of squares: over this block's K range (NORMB), or handed in
+  __shared__ float row_inv[BN];  // 1/sqrt(mean square + eps) of the rows (not where the K splits of a cluster meet)
   __shared__ float warp_ssq[NORMB ? 4 : 1][NORMB ? BN : 1];
   __shared__ float rank_ssq[NORMB ? kRowsMaxSplits : 1][NORMB ? BN : 1];  // every split's share, pushed by the splits
 
@@ -772,6 +773,14 @@ gemm_tc_rows_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     const bool scaled = NORMB || scale_in;
     const float norm_width = NORMB ? (float)a.K : (float)a.scale.width;
     const float norm_eps = NORMB ? a.norm.eps : a.scale.eps;
+    // The epilogue below runs once per block with one warp per scheduler: nothing hides an
+    // instruction's latency there, so whatever can be done while the main loop runs is done here
+    // (the rows' scalars: 1.6 to 1.0 us for the q/k/v product's epilogue).  (Running the token loops
+    // without their early exit, so that the tokens' chains interleave, measured slower for 8 tokens.)
+    if (scaled) {
+      if (et < BN) row_inv[et] = 1.0f / sqrtf(row_ssq[et] / norm_width + norm_eps);
+      asm volatile("barrier.sync 1, 128;" ::: "memory");
+    }
     const bool ahead = MODE == kAccumF32 && a.ahead.xw != nullptr && !clustered;
     const int kstack = ra.kstack, R = ra.rows_per_block;
     float* red = reinterpret_cast<float*>(smem_raw + (landing - smem_u32(smem_raw)));
@@ -822,8 +831,10 @@ gemm_tc_rows_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         }
       }
       asm volatile("barrier.sync 1, 128;" ::: "memory");
+      const float inv_R = 1.0f / (float)R;
       for (int idx = et; ok && idx < a.M * R; idx += 128) {
-        const int tok = idx / R, rr = idx - tok * R;
+        // idx / R without the integer division: (idx + 0.5) / R is at least 1 / (2 R) away from an integer
+        const int tok = (int)(((float)idx + 0.5f) * inv_R), rr = idx - tok * R;
         const int ff = f0 + rr;
         if (ff >= a.N) {
           if (ahead) sqbuf[idx] = 0.f;
@@ -831,7 +842,7 @@ gemm_tc_rows_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         }
         float v = 0.f;
         for (int q = 0; q < kstack; ++q) v += red[(q * BN + tok) * R + rr];
-        if (scaled) v *= 1.0f / sqrtf(row_ssq[tok] / norm_width + norm_eps);
+        if (scaled) v *= row_inv[tok];
         if (MODE == kStoreBf16) ((__nv_bfloat16*)a.y)[(int64_t)tok * a.ldy + ff] = __float2bfloat16_rn(v);
         else if (MODE == kStoreF32) ((float*)a.y)[(int64_t)tok * a.ldy + ff] = v;
         else if (MODE == kAccumF32) {
@@ -886,12 +897,8 @@ gemm_tc_rows_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
       for (int j = 0; j < 16; ++j) {
         const int tok = c0 + j;
         if (tok >= a.M) break;
-        float v = __uint_as_float(r[j]);
-        float inv = 1.f;
-        if (scaled) {
-          inv = 1.0f / sqrtf(row_ssq[tok] / norm_width + norm_eps);
-          v *= inv;
-        }
+        const float inv = scaled ? row_inv[tok] : 1.f;
+        const float v = __uint_as_float(r[j]) * inv;
         if (MODE == kStoreBf16) {
           ((__nv_bfloat16*)a.y)[(int64_t)tok * a.ldy + f] = __float2bfloat16_rn(v);
         } else if (MODE == kStoreF32) {
