@@ -1,0 +1,66 @@
+"""Which kernel a matrix product goes to is decided from shapes alone (``parts/linear.py``): these
+decisions are checked here without a GPU, at the layer sizes of the benchmark model."""
+import torch
+
+from skyla_kernel_b200.kernels import ops
+from skyla_kernel_b200.parts.base import Runtime
+from skyla_kernel_b200.parts.linear import Linear
+
+H, QKV, INTER = 4096, 6144, 12288
+
+
+def _lin(n_out, n_in, gated=False, dtype="bfloat16"):
+    # a meta tensor: only its shape, dtype and (absent) address are looked at
+    rows = 2 * n_out if gated else n_out
+    w = torch.empty(rows, n_in, dtype=torch.bfloat16 if dtype == "bfloat16" else torch.float32, device="meta")
+    return Linear(w, Runtime(torch.device("cpu"), dtype), gated=gated)
+
+
+def test_few_tokens_stream_the_weight_and_many_go_to_the_prompt_kernel():
+    qkv, o, gate_up, down = _lin(QKV, H), _lin(H, H), _lin(INTER, H, gated=True), _lin(H, INTER)
+    for lin in (qkv, o, gate_up, down):
+        assert lin.tensor_cores
+        assert all(lin.streams(m) for m in (1, 8, 16))
+        assert all(lin.prompts(m) and not lin.streams(m) for m in (129, 2048))
+        assert all(lin.takes_scale_in(m) for m in (1, 16, 129, 4096))
+    # 17 to 64 tokens: only the tall tiles of the gated product still stream
+    assert gate_up.streams(17) and gate_up.streams(64) and not gate_up.streams(65)
+    assert not any(lin.streams(17) for lin in (qkv, o, down))
+    # 65 to 128 tokens: only the product with the long reduction goes to the prompt kernel
+    assert down.prompts(65) and down.prompts(128)
+    assert not any(lin.prompts(m) for lin in (qkv, o, gate_up) for m in (65, 128))
+    assert not down.prompts(64)
+
+
+def test_the_32_bit_path_never_takes_a_tensor_core_kernel():
+    lin = _lin(H, H, dtype="float32")
+    assert not lin.tensor_cores
+    assert not any(lin.streams(m) or lin.prompts(m) or lin.takes_scale_in(m) for m in (1, 16, 64, 129, 4096))
+
+
+def test_widths_that_are_no_multiple_of_eight_stay_on_the_plain_kernel():
+    lin = _lin(200, 84)
+    assert not lin.tensor_cores and not lin.streams(4) and not lin.prompts(500)
+
+
+def test_k_splits_of_small_batches():
+    qkv, o, down = _lin(QKV, H), _lin(H, H), _lin(H, INTER)
+    for lin in (qkv, o, down):
+        total = -(-lin.n_in // 64)
+        for m in (1, 17, 32, 64):
+            s = lin.choose_splits(m)
+            assert 1 <= s <= total // 16
+            per = -(-total // s)
+            assert (s - 1) * per < total          # no split is empty
+        assert lin.choose_splits(65) == 1 and lin.choose_splits(4096) == 1
+    assert down.choose_splits(32) >= o.choose_splits(32) > 1  # both fill the SMs: 32 tiles, four splits each
+
+
+def test_rows_plans_fill_the_sms_with_one_wave():
+    for n_out, n_in, gated in ((QKV, H, False), (H, H, False), (INTER, H, True), (H, INTER, False), (151936, H, False)):
+        rows, splits, kkb, kstack = ops.rows_plan(n_out, n_in, gated, 16)
+        assert rows % 8 == 0 and 8 <= rows <= 128 and splits == 1
+        blocks = -(-n_out // rows)
+        if n_out <= 148 * 128:
+            assert blocks <= 148, (n_out, rows, blocks)   # one block per SM at most: a single wave
+        assert kstack * rows <= 128 and kkb % kstack == 0
