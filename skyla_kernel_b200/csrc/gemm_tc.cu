@@ -787,6 +787,7 @@ gemm_tc_rows_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     const int kstack = ra.kstack, R = ra.rows_per_block;
     float* red = reinterpret_cast<float*>(smem_raw + (landing - smem_u32(smem_raw)));
     float* sqbuf = red + (kstack > 1 ? kstack * BN * R : 0);  // [tok][row of the tile]: squares of the new x
+    bool ssq_in_warp = false;
     // the old values of y do not depend on the product: fetch them while the main loop runs
     float old_pre[4] = {0.f, 0.f, 0.f, 0.f}, wn_pre[4] = {0.f, 0.f, 0.f, 0.f}, old16[16];
     if (MODE == kAccumF32 && kstack > 1) {
@@ -834,6 +835,9 @@ gemm_tc_rows_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
       }
       asm volatile("barrier.sync 1, 128;" ::: "memory");
       const float inv_R = 1.0f / (float)R;
+      // tiles of 32 whole rows: a warp's 32 items are one token's row, so its share of the row's sum of
+      // squares is a butterfly in the warp (the same order as below) and needs neither memory nor a barrier
+      ssq_in_warp = ahead && R == 32 && f0 + 32 <= a.N;
       for (int idx = et; ok && idx < a.M * R; idx += 128) {
         // idx / R without the integer division: (idx + 0.5) / R is at least 1 / (2 R) away from an integer
         const int tok = (int)(((float)idx + 0.5f) * inv_R), rr = idx - tok * R;
@@ -855,7 +859,17 @@ gemm_tc_rows_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
           if (ahead) {
             const float wn = n == 0 ? wn_pre[0] : n == 1 ? wn_pre[1] : n == 2 ? wn_pre[2] : n == 3 ? wn_pre[3] : a.ahead.w[ff];
             a.ahead.xw[(int64_t)tok * a.ahead.ldxw + ff] = __float2bfloat16_rn(nv * wn);
-            sqbuf[idx] = nv * nv;
+            if (ssq_in_warp) {
+              float sq = nv * nv;
+              sq += __shfl_xor_sync(0xffffffffu, sq, 16);
+              sq += __shfl_xor_sync(0xffffffffu, sq, 8);
+              sq += __shfl_xor_sync(0xffffffffu, sq, 4);
+              sq += __shfl_xor_sync(0xffffffffu, sq, 2);
+              sq += __shfl_xor_sync(0xffffffffu, sq, 1);
+              if (lane == 0) a.ahead.ssq_part[(int64_t)blockIdx.x * a.M + tok] = sq;
+            } else {
+              sqbuf[idx] = nv * nv;
+            }
           }
         }
       }
@@ -920,7 +934,7 @@ gemm_tc_rows_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         }
       }
     }
-    if (ahead) {  // this block's share of the new rows' sums of squares, added up in a fixed order
+    if (ahead && !ssq_in_warp) {  // this block's share of the new rows' sums of squares, added up in a fixed order
       asm volatile("barrier.sync 1, 128;" ::: "memory");
       // a warp per token: lanes take the rows 32 apart, then a butterfly (one order whatever the batch)
       for (int tok = warp - 2; ok && tok < a.M; tok += 4) {
