@@ -146,3 +146,168 @@ def test_the_wide_configuration_reaches_the_blackwell_kernels(folders):
     assert made.get("attn_prep", 0) == 0, made          # the heads are finished in the q/k/v product
     if torch.cuda.get_device_properties(0).multi_processor_count >= 64:
         assert ops.prompt_cut_blocks(150, base["hidden_size"], base["hidden_size"], False, "cuda:0") > 0
+
+
+def _feed(eng, slot, toks, cuts):
+    """Feed ``toks`` to ``slot`` in steps of the sizes ``cuts`` (their sum is the length); all logits."""
+    from skyla_kernel_b200.engine import StepItem
+    rows, o = [], 0
+    for c in cuts:
+        rows.append(eng.step([StepItem(slot, toks[o:o + c], list(range(c)))]))
+        o += c
+    assert o == len(toks)
+    return torch.cat(rows)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["B", "D"])
+def test_mixed_chunks_of_one_request(folders, name, dtype):
+    """A request cut into chunks of many tokens that land on a filled cache (the reference cuts its
+    prompts at 128, skyla-engine/src/engine.rs:144-152): 50, 30, 1, 140 (from 129 tokens on the
+    token-major product finishes the heads and the tcgen05 attention starts inside a sequence), a few
+    single tokens, a chunk that starts inside a page, single tokens again."""
+    from skyla_kernel_b200.kernels import ops
+    V = TINY[name][0]["vocab_size"]
+    eng = _engine(folders[name], dtype)
+    cuts = [50, 30, 1, 140, 1, 1, 1, 37, 1, 1]
+    toks = random_tokens(sum(cuts), V, 41)
+    s = eng.alloc_slot()
+    before = dict(ops.LAUNCHES_BY_MODULE)
+    got = _feed(eng, s, toks, cuts)
+    eng.free_slot(s)
+    _check(folders[name], toks, got, dtype, f"{name} {dtype} mixed chunks {cuts}")
+    if name == "D" and dtype == "bfloat16":
+        made = {m: n - before.get(m, 0) for m, n in ops.LAUNCHES_BY_MODULE.items()}
+        L = TINY[name][0]["num_hidden_layers"]
+        assert made.get("gemm_prompt", 0) >= 4 * L and made.get("attention_tc", 0) >= L, made
+    eng.cache.check()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["B", "D"])
+def test_steps_that_mix_chunks_and_single_tokens(folders, name, dtype):
+    """Steps in which one sequence brings a chunk on a filled cache while its neighbours bring one
+    token each: few tokens in all (the weight-streaming products), 17 to 64, and 129 and more."""
+    from skyla_kernel_b200.engine import StepItem
+    V = TINY[name][0]["vocab_size"]
+    eng = _engine(folders[name], dtype, max_tokens=4 * 320)
+    # per step, the tokens each of the four sequences brings
+    plan = [(60, 7, 33, 90), (40, 1, 1, 1), (1, 130, 1, 1), (1, 1, 1, 1), (1, 1, 17, 20), (3, 1, 2, 1),
+            (1, 1, 1, 1), (1, 64, 1, 65), (1, 1, 1, 1)]
+    total = [sum(p[i] for p in plan) for i in range(4)]
+    seqs = [random_tokens(total[i], V, 500 + i) for i in range(4)]
+    slots = [eng.alloc_slot() for _ in seqs]
+    got = [[] for _ in seqs]
+    at = [0] * 4
+    for p in plan:
+        out = eng.step([StepItem(slots[i], seqs[i][at[i]:at[i] + p[i]], list(range(p[i]))) for i in range(4)])
+        o = 0
+        for i in range(4):
+            got[i].append(out[o:o + p[i]]); o += p[i]; at[i] += p[i]
+        assert o == out.shape[0]
+    for i in range(4):
+        _check(folders[name], seqs[i], torch.cat(got[i]), dtype, f"{name} {dtype} mixed steps, request {i}")
+        eng.free_slot(slots[i])
+    eng.cache.check()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["B", "D"])
+@pytest.mark.parametrize("prompt", [500, 1010])
+def test_decoding_across_a_page_list_bucket(folders, name, dtype, prompt):
+    """Decode steps replay graphs recorded per (batch, width of the page lists); at 512 and 1,024
+    positions a sequence moves to a wider list, a new graph, other context splits and longer rotary
+    tables.  A long request decodes across that edge beside a short neighbour; every row is compared."""
+    from skyla_kernel_b200.engine import StepItem
+    V = TINY[name][0]["vocab_size"]
+    eng = _engine(folders[name], dtype, max_tokens=1280)
+    n_dec = 40
+    long_, short = random_tokens(prompt + n_dec, V, 61), random_tokens(9 + n_dec, V, 62)
+    a, b = eng.alloc_slot(), eng.alloc_slot()
+    out = eng.step([StepItem(a, long_[:prompt], [prompt - 2, prompt - 1]), StepItem(b, short[:9], list(range(9)))])
+    got_a, got_b = [out[:2]], [out[2:]]
+    keys = set()
+    for t in range(n_dec):
+        out = eng.step([StepItem(a, [long_[prompt + t]], [0]), StepItem(b, [short[9 + t]], [0])])
+        got_a.append(out[:1]); got_b.append(out[1:])
+        if eng.graphs is not None:
+            keys.add(eng.graphs.last_key)
+    if eng.graphs is not None:
+        assert len(keys) == 2, f"the decode crossed no bucket: {keys}"
+    if folders[name] not in _MODELS:
+        _MODELS[folders[name]] = plain.read_folder(folders[name])
+    cfg, w = _MODELS[folders[name]]
+    ref = plain.forward(cfg, w, long_)
+    assert_close(torch.cat(got_a), ref[prompt - 2:], dtype, f"{name} {dtype} long request across position {prompt}")
+    _check(folders[name], short, torch.cat(got_b), dtype, f"{name} {dtype} the short neighbour")
+    eng.free_slot(a); eng.free_slot(b)
+    eng.cache.check()
+
+
+@pytest.mark.parametrize("name", NAMES)
+def test_float32_logits_are_the_same_bits_in_every_cut(folders, name):
+    """In the 32-bit path every output element is summed in one order that the batch does not change:
+    whole, in chunks, token by token, and beside other requests give equal bits, not close ones."""
+    from skyla_kernel_b200.engine import StepItem
+    V = TINY[name][0]["vocab_size"]
+    eng = _engine(folders[name], "float32", max_tokens=2048)
+    n = 150
+    toks = random_tokens(n, V, 77)
+    others = [random_tokens(m, V, 78 + i) for i, m in enumerate((140, 20, 66))]
+    s = eng.alloc_slot()
+    whole = _feed(eng, s, toks, [n]); eng.free_slot(s)
+    s = eng.alloc_slot()
+    chunks = _feed(eng, s, toks, [50, 30, 1, 37, 32]); eng.free_slot(s)
+    s = eng.alloc_slot()
+    single = _feed(eng, s, toks, [n - 32] + [1] * 32); eng.free_slot(s)
+    # beside others: the prompt in a batch of unequal prompts, then tokens beside a chunk and single tokens
+    slots = [eng.alloc_slot() for _ in range(4)]
+    out = eng.step([StepItem(slots[1], others[0][:100], [99]), StepItem(slots[0], toks[:90], list(range(90))),
+                    StepItem(slots[2], others[1][:5], [4]), StepItem(slots[3], others[2][:66], [65])])
+    rows = [out[1:91]]
+    for t in range(90, n):
+        j = t - 90
+        items = [StepItem(slots[0], [toks[t]], [0])]
+        if j < 15:
+            items.insert(0, StepItem(slots[2], [others[1][5 + j]], [0]))
+        if j == 3:
+            items.append(StepItem(slots[1], others[0][100:140], [39]))
+        out = eng.step(items)
+        rows.append(out[1:2] if j < 15 else out[0:1])
+    batched = torch.cat(rows)
+    for sl in slots:
+        eng.free_slot(sl)
+    for what, got in (("chunks", chunks), ("token by token", single), ("beside other requests", batched)):
+        assert torch.equal(whole, got), (f"{name} float32 {what}: differs from the whole run in "
+                                         f"{int((whole != got).any(-1).sum())} rows, first row "
+                                         f"{int((whole != got).any(-1).nonzero()[0])}, "
+                                         f"largest difference {float((whole - got).abs().max()):.3e}")
+    eng.cache.check()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_layer_taps(folders, name, dtype):
+    """The residual stream after every layer, read through ``Engine.step(taps=...)`` (the reference's
+    ``Engine::residuals``, skyla-engine/src/taps.rs:7-46), against the plain implementation's: the
+    tool for finding the layer in which a difference starts."""
+    from skyla_kernel_b200.engine import StepItem
+    base = TINY[name][0]
+    V, L, H = base["vocab_size"], base["num_hidden_layers"], base["hidden_size"]
+    eng = _engine(folders[name], dtype)
+    toks = random_tokens(70, V, 91)
+    s = eng.alloc_slot()
+    # a prompt, then two single tokens (with taps a decode step runs eagerly, not as a graph)
+    got = {i: [] for i in range(L)}
+    for lo, hi in ((0, 68), (68, 69), (69, 70)):
+        taps = {i: torch.empty(hi - lo, H, dtype=torch.float32, device="cuda:0") for i in range(L)}
+        eng.step([StepItem(s, toks[lo:hi], [hi - lo - 1])], taps=taps)
+        for i in range(L):
+            got[i].append(taps[i].cpu())
+    eng.free_slot(s)
+    cfg, w = plain.read_folder(folders[name])
+    ref = []
+    plain.forward(cfg, w, toks, taps=ref)
+    assert len(ref) == L
+    for i in range(L):
+        assert_close(torch.cat(got[i]), ref[i], dtype, f"{name} {dtype} residual stream after layer {i}")

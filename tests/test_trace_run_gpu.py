@@ -1,5 +1,5 @@
 """bin/trace_run replays the same requests whole, with the last 32 tokens one by one,
-and in batches of unequal lengths, in both precisions, against the plain implementation."""
+in batches of unequal lengths and in mixed chunks, in both precisions, against the plain implementation."""
 import json
 import os
 import subprocess
@@ -31,7 +31,7 @@ def _read(out, step, vocab):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", ["A", "B", "D"])
-def test_replay_three_ways(tmp_path, name, dtype):
+def test_replay_every_way(tmp_path, name, dtype):
     folder = make_folder(tmp_path, name)
     cfg, w = plain.read_folder(folder)
     V = cfg["vocab_size"]
@@ -70,6 +70,37 @@ def test_replay_three_ways(tmp_path, name, dtype):
             steps.append({"step": n, "entries": [{"id": k + "b", "tokens": [reqs[k][cut[k] + t]], "want": [0]} for k in live], "end": ending})
             expect[n] = [(k, cut[k] + t, 1) for k in live]; n += 1
             t += 1
+    # 4) mixed chunks: 50 / 30 / 1 on a filled cache, a chunk of 15 for two requests at once, the rest one by one
+    #    (the program passes any cut on to the step function; the reference cuts its prompts at 128,
+    #    skyla-engine/src/engine.rs:144-152)
+    chunk_step = n
+    chunked = ["r1", "r2", "r4"]   # 2 + 1 + 3 pages: they are live together
+    cut = {}
+    for k in chunked:
+        toks = reqs[k]
+        o = 0
+        for c in (50, 30, 1):
+            c = min(c, len(toks) - 1 - o)
+            if c <= 0:
+                break
+            steps.append({"step": n, "entries": [{"id": k + "c", "tokens": toks[o:o + c], "want": list(range(c))}], "end": []})
+            expect[n] = [(k, o, c)]; n += 1
+            o += c
+        cut[k] = o
+    pair = ["r1", "r4"]
+    steps.append({"step": n, "entries": [{"id": k + "c", "tokens": reqs[k][cut[k]:cut[k] + 15], "want": list(range(15))} for k in pair], "end": []})
+    expect[n] = [(k, cut[k], 15) for k in pair]; n += 1
+    for k in pair:
+        cut[k] += 15
+    t = 0
+    while True:
+        live = [k for k in chunked if cut[k] + t < len(reqs[k])]
+        if not live:
+            break
+        ending = [k + "c" for k in live if cut[k] + t == len(reqs[k]) - 1]
+        steps.append({"step": n, "entries": [{"id": k + "c", "tokens": [reqs[k][cut[k] + t]], "want": [0]} for k in live], "end": ending})
+        expect[n] = [(k, cut[k] + t, 1) for k in live]; n += 1
+        t += 1
     # one step that wants nothing writes no file
     steps.append({"step": n, "entries": [{"id": "q", "tokens": [1, 2, 3], "want": []}], "end": ["q"]})
     out = str(tmp_path / f"out_{dtype}")
@@ -81,13 +112,18 @@ def test_replay_three_ways(tmp_path, name, dtype):
         got = _read(out, s, V)
         o = 0
         for k, first, count in parts:
-            mode = 0 if s < len(reqs) else (1 if s < first_batch_step else 2 + (s >= second_batch_step))
+            mode = (0 if s < len(reqs) else 1 if s < first_batch_step else 2 if s < second_batch_step
+                    else 3 if s < chunk_step else 4)
             blocks.setdefault((mode, k), []).append((first, got[o:o + count]))
             o += count
         assert o == got.shape[0]
-    assert len(blocks) == 5 + 5 + 6
+    assert len(blocks) == 5 + 5 + 6 + 3
+    whole = {k: torch.cat([g for _, g in blocks[(0, k)]]) for k in reqs}
     for (mode, k), rows in blocks.items():
         places = [f + i for f, g in rows for i in range(g.shape[0])]
         assert places == list(range(places[0], places[0] + len(places)))
-        assert_close(torch.cat([g for _, g in rows]), refs[k][places[0]:places[-1] + 1], dtype,
-                     f"{name} {dtype} way {mode} request {k}")
+        got = torch.cat([g for _, g in rows])
+        assert_close(got, refs[k][places[0]:places[-1] + 1], dtype, f"{name} {dtype} way {mode} request {k}")
+        if dtype == "float32":  # the 32-bit path sums every element in one order, however the tokens are cut
+            assert torch.equal(got, whole[k][places[0]:places[-1] + 1]), \
+                f"{name} float32 way {mode} request {k}: not the bits of the whole run"
