@@ -21,14 +21,8 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-# layer sizes of the Qwen3-8B shape (the third benchmark configuration)
-QWEN3_8B = dict(hidden_size=4096, num_hidden_layers=36, num_attention_heads=32, num_key_value_heads=8,
-                head_dim=128, intermediate_size=12288, vocab_size=151936, rope_theta=1000000.0,
-                rms_norm_eps=1e-6, max_position_embeddings=40960, tie_word_embeddings=False)
-# the other two shapes of the benchmark list, for --shape
-QWEN3_4B = dict(QWEN3_8B, hidden_size=2560, intermediate_size=9728, tie_word_embeddings=True)
-QWEN3_32B = dict(QWEN3_8B, num_hidden_layers=64, hidden_size=5120, num_attention_heads=64, intermediate_size=25600)
-SHAPES = {"8b": QWEN3_8B, "4b": QWEN3_4B, "32b": QWEN3_32B}
+from skyla_kernel_b200.measure import SHAPES  # layer sizes of the Qwen3-8B (default), -4B and -32B shapes
+
 PROMPT_LEN = 2048
 CONTEXT = 4096
 FALLBACK_HBM_GBS = 6650.0       # an earlier measurement on this pool, used when no peaks file exists
@@ -91,26 +85,11 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def build_model(layers: int, max_tokens: int, max_slots: int, seed: int = 0, shape: dict = None):
-    """The 8B-shaped (or ``shape``d) model with seeded random weights drawn on the device."""
-    import torch
+def build_model(layers: int, max_tokens: int, max_slots: int, seed: int = 0, shape: str = "8b"):
+    """The model of ``shape``'s layer sizes with seeded random weights drawn on the device."""
     import skyla_kernel_b200 as skyla
-    from skyla_kernel_b200.config import Qwen3Config
-    from skyla_kernel_b200.engine import Engine, declared_tensors
-    from skyla_kernel_b200.kernels import ops
-    cfg = Qwen3Config(**dict(shape or QWEN3_8B, num_hidden_layers=layers))
-    decl = declared_tensors(cfg.to_spec())
-    tensors = {}
-    for i, (name, d) in enumerate(decl.items()):
-        t = torch.empty(d.shape, dtype=torch.bfloat16, device="cuda:0")
-        if d.init == "norm":
-            ops.fill_normal(t, 1.0, 0.02, seed * 100003 + i)
-        else:
-            ops.fill_normal(t, 0.0, 0.02, seed * 100003 + i)
-        tensors[name] = t
-    engine = Engine(cfg, tensors, "bfloat16", max_tokens=max_tokens, max_slots=max_slots)
-    del tensors
-    torch.cuda.empty_cache()
+    from skyla_kernel_b200.measure import random_engine
+    engine, cfg = random_engine(shape, layers, max_tokens=max_tokens, max_slots=max_slots, seed=seed)
     return skyla.Model(engine), cfg
 
 
@@ -243,7 +222,7 @@ def main() -> int:
     batches = [args.batch] + ([] if args.no_points else [b for b in (1, 64) if b != args.batch])
     max_tokens = max(batches) * (-(-CONTEXT // 64) * 64)
     t_build = time.time()
-    model, cfg = build_model(args.layers, max_tokens=max_tokens, max_slots=max(batches), shape=shape)
+    model, cfg = build_model(args.layers, max_tokens=max_tokens, max_slots=max(batches), shape=args.shape)
     print(f"[bench] model built in {time.time() - t_build:.1f} s: {args.layers} layers, "
           f"{model.engine.weight_bytes() / 1e9:.2f} GB of weights per step", file=sys.stderr, flush=True)
     V = cfg.vocab_size

@@ -71,7 +71,7 @@ class Model:
         params = SamplingParams(temperature, top_k, top_p, seed)
         sampler = self._samplers.get(params)
         if sampler is None:
-            sampler = self._samplers[params] = Sampler(params, self.engine.rt.device)
+            sampler = self._samplers[params] = Sampler(params, self.engine.rt.device, self.engine.rt.kernel_state)
         if stop_ids is None:
             stop_ids = self.engine.spec.stop_token_ids
         if isinstance(max_new_tokens, int):
@@ -100,26 +100,36 @@ class _Backend:
         return self.m.engine.step(items, borrow=True)  # sampled at once, before the next step
 
     def sample(self, logits, req_ids, steps) -> List[int]:
-        return self.sampler(logits, req_ids, steps).cpu().tolist()
+        tokens = self.sampler(logits, req_ids, steps).cpu().tolist()
+        self.m.engine.check_errors()  # the copy above has waited for the step
+        return tokens
 
     def step_async(self, items, req_ids, steps) -> "_Tokens":
         """Step and sample without waiting: the tokens stay on the device for the next step and
-        travel to pinned host memory on the side."""
+        travel to pinned host memory on the side, the kernels' error word with them."""
         logits = self.m.engine.step(items, borrow=True)
-        return _Tokens(self.sampler(logits, req_ids, steps))
+        return _Tokens(self.sampler(logits, req_ids, steps), self.m.engine.rt.kernel_state)
 
 
 class _Tokens:
-    def __init__(self, device_tokens: torch.Tensor):
+    """A step's sampled tokens: on the device for the next step, and on their way to the host."""
+
+    def __init__(self, device_tokens: torch.Tensor, state):
         self.device_tokens = device_tokens
-        self._host = torch.empty(device_tokens.shape, dtype=device_tokens.dtype, pin_memory=True)
-        self._host.copy_(device_tokens, non_blocking=True)
+        self._state = state
+        n = device_tokens.numel()
+        self._host = torch.empty(n + 1, dtype=torch.int32, pin_memory=True)
+        self._host[:n].copy_(device_tokens, non_blocking=True)
+        self._host[n:].copy_(state.error_flag, non_blocking=True)
         self._ready = torch.cuda.Event()
         self._ready.record()
 
     def tokens(self) -> List[int]:
+        """Waits for this step; raises ``KernelError`` if a kernel reported a fault up to it."""
         self._ready.synchronize()
-        return self._host.tolist()
+        host = self._host.tolist()
+        self._state.raise_if(host[-1])
+        return host[:-1]
 
 
 def load(model: Union[str, dict, object], dtype: str = "bfloat16", max_tokens: int = 4096,

@@ -8,7 +8,7 @@ layers in regions that are zeroed together on reset
 (skyla-engine/src/arena.rs:114-142, engine.rs:82-89).  Here many sequences share
 the memory, so positions live in pages:
 
-* layers whose mixers have the same need (key/value heads, head size, window)
+* layers whose mixers have the same need (key/value heads, head size, window, precision)
   form a *group* with one pool ``[layer, page, kv_head, position_in_page, head_dim]``
   for keys and one for values, and a page list per slot;
 * a group with a window gives back the pages that no later token can see;
@@ -37,6 +37,9 @@ class KVNeed:
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None  # None: every earlier position stays visible
+    #: precision of the stored keys and values; None: the runtime's (bfloat16, or float32 in the 32-bit
+    #: path).  Mixers with different precisions fall into different groups, like any other difference.
+    dtype: Optional[torch.dtype] = None
 
 
 @dataclass(frozen=True)
@@ -57,7 +60,7 @@ class KVGroup:
         self.page_size = page_size
         self.n_pages = n_pages
         self.pages = FreeList(n_pages, "cache page")
-        self.dtype = dtype
+        self.dtype = dtype = need.dtype or dtype
         shape = (n_layers, n_pages, need.num_kv_heads, page_size, need.head_dim)
         self.k = torch.zeros(shape, dtype=dtype, device=device) if device is not None else None
         self.v = torch.zeros(shape, dtype=dtype, device=device) if device is not None else None

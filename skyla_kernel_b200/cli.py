@@ -66,14 +66,37 @@ def cmd_run(a) -> int:
     return 0
 
 
+NEAR_TIE = 0.02  # probability: "top-2 margin under 2 points" (docs/roadmap.md:89-92 of the reference)
+
+
+def near_tie(logits) -> bool:
+    """Whether the two most likely tokens of a row of logits are within 2 points of probability,
+    the reference's rule for a top-1 disagreement that rounding alone explains."""
+    import torch
+    p = torch.softmax(logits.double(), dim=-1)
+    top = torch.topk(p, 2).values
+    return bool(top[0] - top[1] < NEAR_TIE)
+
+
+def judge(logits, oracle):
+    """One step of the lockstep: (top of ``logits``, top of ``oracle``, largest difference, verdict);
+    the verdict is "" when the tops agree, "near tie" when they differ at a near tie of the oracle,
+    else "DISAGREE"."""
+    ta, tb = int(logits.argmax()), int(oracle.argmax())
+    diff = float((logits - oracle).abs().max())
+    return ta, tb, diff, "" if ta == tb else ("near tie" if near_tie(oracle) else "DISAGREE")
+
+
 def _check(a, prompts, out) -> int:
     """Lockstep against the true 32-bit path: top token of each and the largest logit
-    difference at every step (the reference's ``run --check``, README.md:206-208)."""
+    difference at every step (the reference's ``run --check``, README.md:206-208).
+    Returns 1 (the command's exit code) if the top tokens disagree anywhere but at a near
+    tie of the 32-bit path, else 0."""
     import torch
 
     from . import load
     from .engine import StepItem
-    worst_all, mismatches = 0.0, 0
+    worst_all, mismatches, real = 0.0, 0, 0
     engines = [load(a.model, dtype=d, max_tokens=64 * (-(-(max(map(len, prompts)) + a.n) // 64))).engine
                for d in (a.dtype, "float32")]
     for p, o in zip(prompts, out):
@@ -82,19 +105,20 @@ def _check(a, prompts, out) -> int:
         for step, tok in enumerate(o + [None]):
             want = [len(feed) - 1]
             la, lb = (e.step([StepItem(s, feed, want)]) for e, s in zip(engines, slots))
-            ta, tb = int(la[0].argmax()), int(lb[0].argmax())
-            diff = float((la[0] - lb[0]).abs().max())
+            ta, tb, diff, verdict = judge(la[0], lb[0])
             worst_all = max(worst_all, diff)
-            mismatches += ta != tb
-            print(f"# check step {step}: {a.dtype} top {ta}, float32 top {tb}, largest logit difference {diff:.4f}",
-                  file=sys.stderr)
+            mismatches += verdict != ""
+            real += verdict == "DISAGREE"
+            print(f"# check step {step}: {a.dtype} top {ta}, float32 top {tb}, largest logit difference {diff:.4f}"
+                  + (f" ({verdict})" if verdict else ""), file=sys.stderr)
             if tok is None:
                 break
             feed = [tok]
         for e, s in zip(engines, slots):
             e.free_slot(s)
-    print(f"# check: {mismatches} top-1 disagreements, worst logit difference {worst_all:.4f}", file=sys.stderr)
-    return 0
+    print(f"# check: {mismatches} top-1 disagreements ({real} outside near ties), worst logit difference {worst_all:.4f}",
+          file=sys.stderr)
+    return 1 if real else 0
 
 
 def cmd_bench(a) -> int:
@@ -215,10 +239,6 @@ def main(argv=None) -> int:
     p.add_argument("--batch", type=int, default=8)
     p.add_argument("--context", type=int, default=2048)
     p.add_argument("--reps", type=int, default=5)
-    p.add_argument("--splits", type=int, default=0, help="attention-decode: override the number of context splits")
-    p.add_argument("--plan", default="", help="linear: rows,splits,kkb,kstack of the weight-streaming kernel instead of the part's choice")
-    p.add_argument("--rows-max", type=int, default=-1,
-                   help="linear: up to how many tokens the rows-per-SM kernel runs (default: the part's own limit)")
     p.set_defaults(fn=lambda a: __import__("skyla_kernel_b200.kernel_bench", fromlist=["main"]).main(a))
     p = sub.add_parser("replay", help="replay a token trace from standard input (bin/trace_run)")
     p.add_argument("--model", required=True)

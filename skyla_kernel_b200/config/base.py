@@ -41,18 +41,27 @@ class PartSpec:
 
 @dataclass(frozen=True)
 class LayerSpec:
-    """One layer: its weight-name prefix and the parts it is assembled from.
+    """One layer: its weight-name prefix, the arrangement of its parts and the parts themselves.
 
-    ``block`` names the arrangement of the parts (for the Qwen3 decoder:
-    ``x += mixer(norm1(x)); x += ffn(norm2(x))``, skyla-ref/src/model.rs:104-115).
+    ``block`` names the arrangement (a registry key) and ``parts`` the parts by the names that this
+    arrangement gives them.  For the Qwen3 decoder the arrangement is ``"prenorm_residual"``,
+    ``x += mixer(mixer_norm(x)); x += feed_forward(ffn_norm(x))`` (skyla-ref/src/model.rs:104-115),
+    with the four parts ``mixer_norm, mixer, ffn_norm, feed_forward``.  Which names an arrangement
+    wants, and to which registry each belongs, is the block class's business: one with a norm after
+    each sub-layer too, or without a feed-forward, asks for other names and needs no change here.
     """
 
     prefix: str
     block: str
-    mixer_norm: PartSpec
-    mixer: PartSpec
-    ffn_norm: PartSpec
-    feed_forward: PartSpec
+    parts: Dict[str, PartSpec]
+
+    def part(self, name: str) -> PartSpec:
+        try:
+            return self.parts[name]
+        except KeyError:
+            have = ", ".join(sorted(self.parts)) or "(none)"
+            raise ConfigError(f"layer {self.prefix!r}: the {self.block!r} block needs a part named {name!r}; "
+                              f"the layer has {have}") from None
 
 
 @dataclass(frozen=True)

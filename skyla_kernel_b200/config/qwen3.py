@@ -221,10 +221,9 @@ class Qwen3Config:
                 "up_proj": f"{p}.mlp.up_proj.weight",
                 "down_proj": f"{p}.mlp.down_proj.weight",
             })
-            layers.append(LayerSpec(prefix=p, block="prenorm_residual",
-                                    mixer_norm=norm(f"{p}.input_layernorm.weight"), mixer=mixer,
-                                    ffn_norm=norm(f"{p}.post_attention_layernorm.weight"),
-                                    feed_forward=ffn))
+            layers.append(LayerSpec(prefix=p, block="prenorm_residual", parts={
+                "mixer_norm": norm(f"{p}.input_layernorm.weight"), "mixer": mixer,
+                "ffn_norm": norm(f"{p}.post_attention_layernorm.weight"), "feed_forward": ffn}))
         schedule = [ScheduleEntry(layer=i) for i in range(self.num_hidden_layers)]
         return ModelSpec(
             architecture=ARCHITECTURE,

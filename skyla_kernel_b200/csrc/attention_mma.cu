@@ -347,14 +347,11 @@ struct DecodeArgs {
   // if set: the split of a (sequence, kv head) that finishes last merges the splits itself and
   // writes the heads' rows here; else attn_merge_kernel does that in a launch of its own
   bf16* out; int64_t ldo;
-  long long* timeline;  // optional [blocks][8] clock readings of each block's phases (for tuning)
+  // one zeroed counter per (sequence, kv head) for "who finishes last"; the last arriver puts it back to
+  // zero.  They belong to whoever launches (an engine's kernel state): launches that share them must not
+  // overlap on the device
+  int* counters;
 };
-
-// One counter per (sequence, kv head) for "who finishes last"; zero between launches (the last
-// arriver puts it back).  Shared by all launches of this module: they must not overlap, which
-// holds for launches on one stream.
-constexpr int kMergeCounters = 1 << 16;
-__device__ int g_merge_counters[kMergeCounters];
 
 constexpr int kDecodeWarps = 4;
 
@@ -366,8 +363,6 @@ __global__ void __launch_bounds__(kDecodeWarps * 32, 2) attn_decode_kernel(Decod
   bf16* stages = reinterpret_cast<bf16*>(smem_raw);
   float* smem = reinterpret_cast<float*>(smem_raw);  // after the loop: [NW][16 rows][HD], [NW][16] m, [NW][16] l
   __shared__ int merges;
-  long long* tl = a.timeline ? a.timeline + 8 * ((size_t)(blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) : nullptr;
-  if (tl && threadIdx.x == 0) { uint32_t smid; asm volatile("mov.u32 %0, %%smid;" : "=r"(smid)); tl[0] = smid; tl[1] = clock64(); }
   allow_dependents();
   // What the kernel before this one wrote: the unfinished q, k, v (fused) or q and the new
   // token's row of the cache (not fused).  Positions, page lists and the pages of earlier
@@ -398,7 +393,6 @@ __global__ void __launch_bounds__(kDecodeWarps * 32, 2) attn_decode_kernel(Decod
 #pragma unroll
   for (int i = 0; i < kAhead; ++i) issue(i);
   if (fused) grid_dependency_wait();
-  if (tl && threadIdx.x == 0) tl[2] = clock64();
 
   uint32_t qa[S::NQ], qb[S::NQ];
 #pragma unroll
@@ -467,7 +461,6 @@ __global__ void __launch_bounds__(kDecodeWarps * 32, 2) attn_decode_kernel(Decod
 
   RowState<HD> st;
   st.init();
-  if (tl && threadIdx.x == 0) tl[3] = clock64();
   for (int pg = 0; pg < n_pages; ++pg) {
     issue(pg + kAhead);  // into the stage that the round before this one read
     cp_async_wait<kAhead>();
@@ -497,7 +490,6 @@ __global__ void __launch_bounds__(kDecodeWarps * 32, 2) attn_decode_kernel(Decod
   }
   cp_async_wait<0>();
   __syncthreads();
-  if (tl && threadIdx.x == 0) tl[4] = clock64();
   // this thread's shares of the row sums -> whole rows
   st.l[0] += __shfl_xor_sync(0xffffffffu, st.l[0], 1); st.l[0] += __shfl_xor_sync(0xffffffffu, st.l[0], 2);
   st.l[1] += __shfl_xor_sync(0xffffffffu, st.l[1], 1); st.l[1] += __shfl_xor_sync(0xffffffffu, st.l[1], 2);
@@ -526,19 +518,17 @@ __global__ void __launch_bounds__(kDecodeWarps * 32, 2) attn_decode_kernel(Decod
     out[2 + c] = acc;
     if (c == 0) { out[0] = M; out[1] = L; }
   }
-  if (tl && threadIdx.x == 0) tl[5] = clock64();
   if (a.out == nullptr) return;
   // who finishes last of this (sequence, kv head) merges its splits, in the order of the splits
   __threadfence();
   __syncthreads();
   if (threadIdx.x == 0) {
-    int* counter = &g_merge_counters[b * a.nkv + kvh];
+    int* counter = &a.counters[b * a.nkv + kvh];
     const int before = atomicAdd(counter, 1);
     merges = before == a.n_splits - 1;
     if (merges) *counter = 0;  // all are in: ready for the next launch
   }
   __syncthreads();
-  if (tl && threadIdx.x == 0) tl[6] = clock64();
   if (!merges) return;
   __threadfence();
   // Every partial is a round trip to the L2, so a thread asks for all of its own at once: two
@@ -580,7 +570,6 @@ __global__ void __launch_bounds__(kDecodeWarps * 32, 2) attn_decode_kernel(Decod
     *reinterpret_cast<__nv_bfloat162*>(a.out + (int64_t)b * a.ldo + (int64_t)h * HD + c) =
         __floats2bfloat162_rn(o0 / total, o1 / total);
   }
-  if (tl && threadIdx.x == 0) tl[7] = clock64();
 }
 
 struct MergeArgs { const float* part; bf16* out; int64_t ldo; int nq, n_splits, hd; };
@@ -695,12 +684,9 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(PrefillArgs a) {
   store_rows_bf16<HD>(p0, p1, st.o, t, inv0, inv1);
 }
 
-long long* g_decode_timeline = nullptr;  // see skyla_attention_decode_timeline
-
 template <int HD>
 int launch_decode(const DecodeArgs& a_in, int n_seqs, cudaStream_t stream) {
-  DecodeArgs a = a_in;
-  a.timeline = g_decode_timeline;
+  const DecodeArgs& a = a_in;
   size_t smem = (size_t)(kDecodeWarps * 16 * HD + 2 * kDecodeWarps * 16) * sizeof(float);
   if (smem < (size_t)Stage<HD>::kDecodeStages * Stage<HD>::kPageBytes) smem = (size_t)Stage<HD>::kDecodeStages * Stage<HD>::kPageBytes;
   // after the stages: up to 18 finished heads (bf16) and a float scratch row per warp
@@ -750,14 +736,6 @@ int check_common(const void* q, int64_t ldq, int nq, int nkv, int page_size, con
 }
 }  // namespace
 
-// For tuning: from now on every decode launch leaves, per block, its SM's number and clock readings
-// (start, pages asked for and dependency met, loop start, loop end, partial written, counted in,
-// merged) in `buffer` (int64 [blocks][8]; null: stop).
-extern "C" int skyla_attention_decode_timeline(long long* buffer) {
-  g_decode_timeline = buffer;
-  return kOk;
-}
-
 // 1 when the tensor-core kernels take this head size.
 extern "C" int skyla_attention_mma_supports(int hd, int group) {
   return (hd % 16 == 0 && hd >= 16 && hd <= 128) ? (group <= 16 ? 2 : 1) : 0;
@@ -765,11 +743,15 @@ extern "C" int skyla_attention_mma_supports(int hd, int group) {
 
 // Decode: token b of the step is the one new token of sequence b.  `part` holds
 // n_seqs * nq * n_splits * (hd + 2) floats of scratch; out is [n_seqs, nq*hd] bf16.
+// `counters`: n_counters zeroed ints that stay the caller's between launches (they are zero again
+// when a launch ends); with n_seqs * nkv of them the split that finishes last merges the splits
+// inside the kernel, with fewer (or none) a merge kernel follows.
 extern "C" int skyla_attention_decode(const void* q, int64_t ldq, void* out, int64_t ldo, float* part, int n_seqs,
                                       int nq, int nkv, int hd, const void* k_pool, const void* v_pool,
                                       const int32_t* pages, int max_pages, int page_size, const int32_t* tok_pos,
                                       float scale, int window, int n_splits, int pages_per_split,
-                                      const int32_t* pages_needed, cudaStream_t stream) {
+                                      const int32_t* pages_needed, int* counters, int n_counters,
+                                      cudaStream_t stream) {
   if (n_seqs <= 0) return kOk;
   int rc = check_common(q, ldq, nq, nkv, page_size, k_pool, v_pool);
   if (rc) return rc;
@@ -778,8 +760,8 @@ extern "C" int skyla_attention_decode(const void* q, int64_t ldq, void* out, int
     return fail(kBadArgument, "attention_decode: bad split of the context");
   DecodeArgs a{(const bf16*)q, ldq, part, n_splits, pages_per_split, nq, nkv,
                PagedKV{(const bf16*)k_pool, (const bf16*)v_pool, pages, max_pages, page_size, nkv}, tok_pos, scale, window,
-               FusedPrep{}, pages_needed, nullptr, 0, nullptr};
-  const bool merge_inside = (int64_t)n_seqs * nkv <= kMergeCounters;
+               FusedPrep{}, pages_needed, nullptr, 0, counters};
+  const bool merge_inside = counters != nullptr && (int64_t)n_seqs * nkv <= n_counters;
   if (merge_inside) { a.out = (bf16*)out; a.ldo = ldo; }
   SKYLA_HD_SWITCH(hd, { rc = launch_decode<HD>(a, n_seqs, stream); break; });
   if (rc || merge_inside) return rc;
@@ -798,7 +780,7 @@ extern "C" int skyla_attention_decode_fused(
     float eps, const float* cos_t, const float* sin_t, int n_rot, void* out, int64_t ldo, float* part, int n_seqs,
     int nq, int nkv, int hd, void* k_pool, void* v_pool, const int32_t* pages, int max_pages, int page_size,
     const int32_t* tok_pos, float scale, int window, int n_splits, int pages_per_split,
-    const int32_t* pages_needed, cudaStream_t stream) {
+    const int32_t* pages_needed, int* counters, int n_counters, cudaStream_t stream) {
   if (n_seqs <= 0) return kOk;
   int rc = check_common(k_pool, 8, nq, nkv, page_size, k_pool, v_pool);
   if (rc) return rc;
@@ -811,8 +793,8 @@ extern "C" int skyla_attention_decode_fused(
                PagedKV{(const bf16*)k_pool, (const bf16*)v_pool, pages, max_pages, page_size, nkv}, tok_pos, scale, window,
                FusedPrep{qkv, qkv_splits, qkv_split_stride, ld, q_off, k_off, v_off, ssq, n_ssq, norm_width, norm_eps,
                          q_norm, k_norm, eps, cos_t, sin_t, cos_t ? n_rot : 0, (bf16*)k_pool, (bf16*)v_pool, n_seqs},
-               pages_needed, nullptr, 0, nullptr};
-  const bool merge_inside = (int64_t)n_seqs * nkv <= kMergeCounters;
+               pages_needed, nullptr, 0, counters};
+  const bool merge_inside = counters != nullptr && (int64_t)n_seqs * nkv <= n_counters;
   if (merge_inside) { a.out = (bf16*)out; a.ldo = ldo; }
   SKYLA_HD_SWITCH(hd, { rc = launch_decode<HD>(a, n_seqs, stream); break; });
   if (rc || merge_inside) return rc;
@@ -845,13 +827,18 @@ extern "C" int skyla_attention_prefill(const void* q, int64_t ldq, void* out, in
 // GPU that loads it.  Host code may not use this name as an address; it asks the
 // runtime for the device address once per device (see scratch_address()).
 static __device__ __align__(256) float g_no_alloc_scratch[SKYLA_NO_ALLOC_SCRATCH_FLOATS];
+// Its "who finishes last" counters, one per (sequence, kv head): the entry point's own, so that it
+// shares nothing with an engine that runs on the same device.  They start at zero (the image is
+// zero-filled) and every launch leaves them at zero.
+static __device__ __align__(256) int g_no_alloc_counters[SKYLA_NO_ALLOC_COUNTERS];
 
 namespace {
 constexpr int kMaxDevices = 64;
 float* g_scratch_address[kMaxDevices] = {nullptr};
+int* g_counters_address[kMaxDevices] = {nullptr};
 
-// Device address of g_no_alloc_scratch on the current device, looked up on first use.
-int scratch_address(float** out) {
+// Device addresses of g_no_alloc_scratch and g_no_alloc_counters on the current device, looked up on first use.
+int scratch_address(float** out, int** counters) {
   int dev = -1;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return fail(kLaunchFailed, "attention_decode_no_alloc: cudaGetDevice: %s", cudaGetErrorString(e));
@@ -861,9 +848,15 @@ int scratch_address(float** out) {
     e = cudaGetSymbolAddress(&p, g_no_alloc_scratch);
     if (e != cudaSuccess || p == nullptr)
       return fail(kLaunchFailed, "attention_decode_no_alloc: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+    void* c = nullptr;
+    e = cudaGetSymbolAddress(&c, g_no_alloc_counters);
+    if (e != cudaSuccess || c == nullptr)
+      return fail(kLaunchFailed, "attention_decode_no_alloc: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+    g_counters_address[dev] = static_cast<int*>(c);
     g_scratch_address[dev] = static_cast<float*>(p);
   }
   *out = g_scratch_address[dev];
+  *counters = g_counters_address[dev];
   return kOk;
 }
 }  // namespace
@@ -882,8 +875,11 @@ extern "C" int skyla_attention_decode_no_alloc(const void* q, int64_t ldq, void*
                 "the built-in array holds %u; use fewer splits or skyla_attention_decode with a buffer of your own",
                 need, n_seqs, nq, n_splits, hd + 2, (unsigned)SKYLA_NO_ALLOC_SCRATCH_FLOATS);
   float* scratch = nullptr;
-  const int rc = scratch_address(&scratch);
+  int* counters = nullptr;
+  const int rc = scratch_address(&scratch, &counters);
   if (rc) return rc;
+  // more (sequence, kv head) pairs than counters: the splits are merged by a second kernel instead
   return skyla_attention_decode(q, ldq, out, ldo, scratch, n_seqs, nq, nkv, hd, k_pool, v_pool, pages, max_pages,
-                                page_size, tok_pos, scale, window, n_splits, pages_per_split, nullptr, stream);
+                                page_size, tok_pos, scale, window, n_splits, pages_per_split, nullptr, counters,
+                                SKYLA_NO_ALLOC_COUNTERS, stream);
 }

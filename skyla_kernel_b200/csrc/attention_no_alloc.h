@@ -12,8 +12,12 @@
 // buffer from its caller for the per-split partial results; this variant brings its
 // own: one fixed array of SKYLA_NO_ALLOC_SCRATCH_FLOATS floats that lives in the
 // library's device image (so every GPU that loads the library holds those 8 MiB
-// until the process exits).  It calls no cudaMalloc, no cudaFree and no other
-// routine that allocates, on the host or on the device.
+// until the process exits), and beside it SKYLA_NO_ALLOC_COUNTERS small counters
+// (16 KiB) with which the blocks of one launch find out which of them finishes
+// last.  Both are this entry point's own: an engine of this library that runs on
+// the same GPU brings its own scratch and counters and shares nothing with it.
+// It calls no cudaMalloc, no cudaFree and no other routine that allocates, on the
+// host or on the device.
 //
 // Rules for callers:
 //  * The problem must fit: n_seqs * nq * n_splits * (hd + 2) floats of scratch must
@@ -23,10 +27,14 @@
 //    (cudaGetSymbolAddress, with that device current) and remembers it.  Make that
 //    first call outside any stream capture.
 //  * All calls on a device share the one array, and it keeps whatever the last call
-//    left in it.  Nothing in it has to start at zero -- each call writes every slot
-//    that its merge step reads -- but two calls that overlap on the GPU (different
-//    streams, or one stream capture replayed concurrently with another call) race on
-//    it.  Order them on one stream or with events.
+//    left in it.  Nothing in the float array has to start at zero -- each call writes
+//    every slot that its merge step reads -- and the counters are back at zero when a
+//    call's kernel ends.  But two calls that overlap on the GPU (different streams, or
+//    one stream capture replayed concurrently with another call) race on both.  Order
+//    them on one stream or with events.
+//  * With more than SKYLA_NO_ALLOC_COUNTERS (sequence, key/value head) pairs the
+//    splits are merged by a second small kernel instead of inside the first; the
+//    result is the same.
 //  * Inputs and outputs are still the caller's: q, out, the cache pools, the page
 //    lists and the positions, exactly as for skyla_attention_decode().
 #pragma once
@@ -34,6 +42,7 @@
 #include <stdint.h>
 
 #define SKYLA_NO_ALLOC_SCRATCH_FLOATS (2u * 1024u * 1024u) /* 8 MiB */
+#define SKYLA_NO_ALLOC_COUNTERS 4096 /* 16 KiB */
 
 #ifdef __cplusplus
 extern "C" {

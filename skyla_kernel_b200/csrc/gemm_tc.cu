@@ -72,16 +72,6 @@ struct FoldJob {
   float* x; int64_t ldx; const float* part; int n_splits; int64_t split_stride, ldp; int M, H;
 };
 
-// The token operand made inside the kernel instead of loaded: rmsnorm(x + sum_s part[s]).
-// RMSNorm is x * r * w with one scalar r per row, and a row's scalar commutes with
-// the product, so the operand is bf16((x + sum part) * w) and r = 1/sqrt(mean(.^2) + eps)
-// is applied to the accumulator (or, for K-split partial output, handed on as the
-// split's share of the row's sum of squares in ssq_out[split][row]).
-struct NormSource {
-  const float* x; int64_t ldx; const float* part; int n_splits; int64_t split_stride, ldp;
-  const float* w; float eps; float* ssq_out;
-};
-
 // "Norm ahead": the product that writes the residual stream last (y += x W^T) also leaves, for the
 // RMSNorm that reads it next, the rows times that norm's weight in bfloat16 (the next product's
 // token operand) and each block's share of the rows' sums of squares (ssq_part[block * M + tok]).
@@ -98,14 +88,13 @@ struct GemmArgs {
   int k_blocks_per_split;
   int* error_flag;
   FoldJob fold;           // fold.x == nullptr: none
-  NormSource norm;        // used by the NORMB kernels only
   float* scratch;         // kAccumLast: [splits][M][N] tiles of the K splits
   int* counters;          // kAccumLast: one per output tile, zero between launches
   NormAhead ahead;        // weight-streaming kernel, accumulate epilogue: ahead.xw == nullptr: none
   ScaleIn scale;          // weight-streaming kernel: scale.ssq_part == nullptr: none
 };
 
-template <int BN, int MODE, bool NORMB>
+template <int BN, int MODE>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                const GemmArgs a) {
@@ -114,8 +103,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   __shared__ uint32_t tmem_base_slot;
   __shared__ volatile int abort_flag;
   __shared__ int last_split;                 // kAccumLast: this block counted in last
-  __shared__ float row_ssq[NORMB ? BN : 1];  // sum of squares of each token row over this block's K range
-  __shared__ float warp_ssq[NORMB ? 4 : 1][NORMB ? BN : 1];
 
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t bars = base + C::kStages * C::kStageBytes;
@@ -133,7 +120,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   if (threadIdx.x == 0) {
     abort_flag = 0;
     for (int s = 0; s < C::kStages; ++s) {
-      mbar_init(full_bar(s), NORMB ? 2 : 1);  // the loader, and with NORMB the warp that makes the stage's token tile
+      mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), 1);
     }
     mbar_init(tmem_full_bar, 1);
@@ -157,7 +144,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       // Weights are written by no kernel: the first stages' weight tiles are requested
       // before this grid waits for its predecessor, the token tiles after.
       const int n_pre = min(n_kb, C::kStages);
-      constexpr uint32_t kTxBytes = NORMB ? C::kABytes : C::kStageBytes;
+      constexpr uint32_t kTxBytes = C::kStageBytes;
       for (int kb = 0; kb < n_pre; ++kb) {
         mbar_expect_tx(full_bar(kb), kTxBytes);
         tma_load_2d(base + kb * C::kStageBytes, &map_w, full_bar(kb), (kb0 + kb) * BK, f_tile * BM);
@@ -165,11 +152,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
           tma_load_2d(base + kb * C::kStageBytes + BM * BK * 2, &map_w, full_bar(kb), (kb0 + kb) * BK, a.N + f_tile * BM);
         armed |= 1u << kb;
       }
-      if (!NORMB) {
-        grid_dependency_wait();
-        for (int kb = 0; kb < n_pre; ++kb)
-          tma_load_2d(base + kb * C::kStageBytes + C::kABytes, &map_x, full_bar(kb), (kb0 + kb) * BK, t_tile * BN);
-      }
+      grid_dependency_wait();
+      for (int kb = 0; kb < n_pre; ++kb)
+        tma_load_2d(base + kb * C::kStageBytes + C::kABytes, &map_x, full_bar(kb), (kb0 + kb) * BK, t_tile * BN);
       int kb = n_pre;
       for (; kb < n_kb; ++kb) {
         const int s = kb % C::kStages;
@@ -179,7 +164,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         mbar_expect_tx(full_bar(s), kTxBytes);
         tma_load_2d(sa, &map_w, full_bar(s), (kb0 + kb) * BK, f_tile * BM);
         if (MODE == kGluBf16) tma_load_2d(sa + BM * BK * 2, &map_w, full_bar(s), (kb0 + kb) * BK, a.N + f_tile * BM);
-        if (!NORMB) tma_load_2d(sb, &map_x, full_bar(s), (kb0 + kb) * BK, t_tile * BN);
+        tma_load_2d(sb, &map_x, full_bar(s), (kb0 + kb) * BK, t_tile * BN);
         armed |= 1u << s;
         armed_parity = (armed_parity & ~(1u << s)) | (phase << s);
       }
@@ -239,84 +224,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
           a.fold.x[(int64_t)r * a.fold.ldx + c] = v;
         }
     }
-    if (NORMB) {
-      // Make the token tiles (BN = 16): each of the four warps takes every fourth stage, so four
-      // stages' loads are in flight at once.  Lane l handles chunk l%8 (8 elements) of rows
-      // l/8, l/8+4, l/8+8, l/8+12.
-      static_assert(!NORMB || BN == 16, "the in-kernel norm is written for token tiles of 16");
-      // No more producing warps than stages: a warp that has finished block kb then knows that
-      // block kb - stages has been consumed, so the stage of its next block, kb + producers, is
-      // at most one phase behind -- the most a parity wait can tell apart.
-      constexpr int kProducers = C::kStages < 4 ? C::kStages : 4;
-      const int ew = warp - 2, chunk = lane & 7;
-      float ssq[4] = {0.f, 0.f, 0.f, 0.f};
-      for (int kb = ew; kb < n_kb && ew < kProducers; kb += kProducers) {
-        const int s = kb % C::kStages;
-        const uint32_t phase = (kb / C::kStages) & 1;
-        if (!mbar_wait(empty_bar(s), phase ^ 1, &abort_flag, a.error_flag, 4)) break;
-        const int k = (kb0 + kb) * BK + chunk * 8;
-        uint8_t* sb = smem_raw + (base - smem_u32(smem_raw)) + s * C::kStageBytes + C::kABytes;
-        float4 v0[4], v1[4];
-        bool live[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {  // all loads first
-          const int tok = t_tile * BN + (lane >> 3) + 4 * i;
-          live[i] = tok < a.M && k < a.K;
-          v0[i] = v1[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-          if (live[i]) {
-            const float* xp = a.norm.x + (int64_t)tok * a.norm.ldx + k;
-            v0[i] = *reinterpret_cast<const float4*>(xp);
-            v1[i] = *reinterpret_cast<const float4*>(xp + 4);
-          }
-        }
-        float4 w0 = make_float4(0.f, 0.f, 0.f, 0.f), w1 = w0;
-        if (k < a.K) {
-          w0 = *reinterpret_cast<const float4*>(a.norm.w + k);
-          w1 = *reinterpret_cast<const float4*>(a.norm.w + k + 4);
-        }
-        for (int sp = 0; sp < a.norm.n_splits; ++sp)  // pending partial sums, if any (ascending order)
-#pragma unroll
-          for (int i = 0; i < 4; ++i)
-            if (live[i]) {
-              const int tok = t_tile * BN + (lane >> 3) + 4 * i;
-              const float* pp = a.norm.part + (int64_t)sp * a.norm.split_stride + (int64_t)tok * a.norm.ldp + k;
-              const float4 p0 = *reinterpret_cast<const float4*>(pp), p1 = *reinterpret_cast<const float4*>(pp + 4);
-              v0[i].x += p0.x; v0[i].y += p0.y; v0[i].z += p0.z; v0[i].w += p0.w;
-              v1[i].x += p1.x; v1[i].y += p1.y; v1[i].z += p1.z; v1[i].w += p1.w;
-            }
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int r = (lane >> 3) + 4 * i;
-          ssq[i] += v0[i].x * v0[i].x + v0[i].y * v0[i].y + v0[i].z * v0[i].z + v0[i].w * v0[i].w +
-                    v1[i].x * v1[i].x + v1[i].y * v1[i].y + v1[i].z * v1[i].z + v1[i].w * v1[i].w;
-          __nv_bfloat162 b0 = __floats2bfloat162_rn(v0[i].x * w0.x, v0[i].y * w0.y);
-          __nv_bfloat162 b1 = __floats2bfloat162_rn(v0[i].z * w0.z, v0[i].w * w0.w);
-          __nv_bfloat162 b2 = __floats2bfloat162_rn(v1[i].x * w1.x, v1[i].y * w1.y);
-          __nv_bfloat162 b3 = __floats2bfloat162_rn(v1[i].z * w1.z, v1[i].w * w1.w);
-          // the layout TMA's 128-byte swizzle would have written: chunk ^ (row mod 8)
-          *reinterpret_cast<uint4*>(sb + r * 128 + ((chunk ^ (r & 7)) << 4)) =
-              make_uint4(*reinterpret_cast<uint32_t*>(&b0), *reinterpret_cast<uint32_t*>(&b1),
-                         *reinterpret_cast<uint32_t*>(&b2), *reinterpret_cast<uint32_t*>(&b3));
-        }
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic writes -> visible to the MMA's reads
-        __syncwarp();
-        if (lane == 0) mbar_arrive(full_bar(s));
-      }
-      // whole rows: a row's 8 chunks sit in consecutive lanes; then the four warps, in order
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        float v = ssq[i];
-        v += __shfl_xor_sync(0xffffffffu, v, 1);
-        v += __shfl_xor_sync(0xffffffffu, v, 2);
-        v += __shfl_xor_sync(0xffffffffu, v, 4);
-        if (chunk == 0) warp_ssq[ew][(lane >> 3) + 4 * i] = v;
-      }
-      asm volatile("barrier.sync 1, 128;" ::: "memory");  // the four epilogue warps
-      if (et < BN) row_ssq[et] = warp_ssq[0][et] + warp_ssq[1][et] + warp_ssq[2][et] + warp_ssq[3][et];
-      asm volatile("barrier.sync 1, 128;" ::: "memory");
-      if (a.norm.ssq_out != nullptr && f_tile == 0 && et < BN && t_tile * BN + et < a.M)
-        a.norm.ssq_out[(int64_t)split * a.M + t_tile * BN + et] = row_ssq[et];
-    }
     if (n_kb > 0 && mbar_wait(tmem_full_bar, 0, &abort_flag, a.error_flag, 3)) {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16);
@@ -341,12 +248,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
           for (int j = 0; j < 16; ++j) {
             const int tok = tok0 + c0 + j;
             if (tok >= a.M) break;
-            float v = __uint_as_float(r[j]);
-            float inv = 1.f;
-            if (NORMB && MODE != kPartialF32) {  // one block sees the whole row: apply the norm's scalar here
-              inv = 1.0f / sqrtf(row_ssq[c0 + j] / (float)a.K + a.norm.eps);
-              v *= inv;
-            }
+            const float v = __uint_as_float(r[j]);
             if (MODE == kStoreBf16) {
               ((__nv_bfloat16*)a.y)[(int64_t)tok * a.ldy + f] = __float2bfloat16_rn(v);
             } else if (MODE == kStoreF32) {
@@ -363,7 +265,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
               asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(col % n_ranks));
               asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
             } else if (MODE == kGluBf16) {
-              const float up = __uint_as_float(u[j]) * inv;
+              const float up = __uint_as_float(u[j]);
               ((__nv_bfloat16*)a.y)[(int64_t)tok * a.ldy + f] = __float2bfloat16_rn(v / (1.0f + expf(-v)) * up);
             } else if (MODE == kAccumLast) {
               a.scratch[((int64_t)split * a.M + tok) * a.N + f] = v;
@@ -507,11 +409,10 @@ struct RowsArgs {
   int kstack;           // K blocks that one MMA takes at once, stacked along its rows (see below); divides kkb
   int tmem_cols;        // accumulator columns to allocate: a power of two >= 32
   int landing_bytes;    // behind the ring: the cluster's landing zone, at least the 16 KB the MMA may over-read
-  long long* timeline;  // optional [blocks][12]: SM id and clock64 at the phases of each block (for tuning)
 };
 
 
-template <int BN, int MODE, bool NORMB>
+template <int BN, int MODE>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tc_rows_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                     const GemmArgs a, const RowsArgs ra) {
@@ -520,22 +421,10 @@ gemm_tc_rows_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
   extern __shared__ uint8_t smem_raw[];
   __shared__ uint32_t tmem_base_slot;
   __shared__ volatile int abort_flag;
-  __shared__ float row_ssq[BN];  // the rows' sums of squares: over this block's K range (NORMB), or handed in
+  __shared__ float row_ssq[BN];  // the rows' sums of squares, handed in as shares
   __shared__ float row_inv[BN];  // 1/sqrt(mean square + eps) of the rows (not where the K splits of a cluster meet)
-  __shared__ float warp_ssq[NORMB ? 4 : 1][NORMB ? BN : 1];
-  __shared__ float rank_ssq[NORMB ? kRowsMaxSplits : 1][NORMB ? BN : 1];  // every split's share, pushed by the splits
 
   const int n_stages = ra.n_stages, kkb = ra.kkb;
-  long long* tl = ra.timeline ? ra.timeline + 12 * ((size_t)blockIdx.z * gridDim.x + blockIdx.x) : nullptr;
-  if (tl && threadIdx.x == 0) {
-    uint32_t smid;
-    asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
-    tl[0] = smid;
-    tl[1] = clock64();
-    unsigned long long g;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g));
-    tl[11] = (long long)g;
-  }
   const int a_tile = ra.rows_per_block * BK * 2;  // R rows of 128 bytes: a multiple of 1024
   const uint32_t stage_bytes = (uint32_t)(kkb * (kATiles * a_tile + kBBytes));
   const uint32_t bars = (smem_u32(smem_raw) + 15u) & ~15u;                       // barriers first
@@ -557,7 +446,7 @@ gemm_tc_rows_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
   // read different lines of the token rows, which they all share, not all the same L2 line
   const int st_start = n_st > 0 ? (int)(((unsigned)blockIdx.x * 5u) % (unsigned)n_st) : 0;
   auto st_of = [&](int i) { int t = i + st_start; return t >= n_st ? t - n_st : t; };
-  const uint32_t tx_bytes = (uint32_t)(kkb * kATiles * a_tile) + (NORMB ? 0u : (uint32_t)(kkb * kBBytes));
+  const uint32_t tx_bytes = (uint32_t)(kkb * kATiles * a_tile) + (uint32_t)(kkb * kBBytes);
 
   auto load_weights = [&](int i, int s) {
     const uint32_t sa = base + s * stage_bytes;
@@ -575,7 +464,7 @@ gemm_tc_rows_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
   if (threadIdx.x == 0) {
     abort_flag = 0;
     for (int s = 0; s < n_stages; ++s) {
-      mbar_init(full_bar(s), NORMB ? 1 + kkb : 1);  // the loader, and with NORMB one arrival per token tile made
+      mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), 1);
     }
     mbar_init(tmem_full_bar, 1);
@@ -594,7 +483,6 @@ gemm_tc_rows_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = tmem_base_slot;
   allow_dependents();
-  if (tl && threadIdx.x == 0) tl[2] = clock64();
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
@@ -606,17 +494,14 @@ gemm_tc_rows_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         else tma_load_3d(sb, &map_x, full_bar(s), 0, 0, kb);
       };
       // (the ring's first filling of weights was asked for during the set-up)
-      if (!NORMB) {
-        grid_dependency_wait();
-        if (tl) tl[3] = clock64();
-        for (int i = 0; i < n_pre; ++i) load_tokens(i, i);
-      }
+      grid_dependency_wait();
+      for (int i = 0; i < n_pre; ++i) load_tokens(i, i);
       int i = n_pre, s = 0;
       uint32_t phase = 1;
       for (; i < n_st; ++i) {
         if (!mbar_wait(empty_bar(s), phase ^ 1, &abort_flag, a.error_flag, 1)) break;
         load_weights(i, s);
-        if (!NORMB) load_tokens(i, s);
+        load_tokens(i, s);
         if (++s == n_stages) { s = 0; phase ^= 1; }
       }
       if (i < n_st) {  // gave up: let the loads in flight land before the block's memory goes away
@@ -636,10 +521,9 @@ gemm_tc_rows_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
       uint32_t phase = 0, started = 0;
       for (int i = 0; i < n_st; ++i) {
         if (!mbar_wait(full_bar(s), phase, &abort_flag, a.error_flag, 2)) break;
-        if (tl && i == 0) tl[4] = clock64();
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t sa = base + s * stage_bytes, sb = sa + kkb * kATiles * a_tile;
-        // K blocks past the end of K hold zeros (the loads fill them, the norm's producers write them)
+        // K blocks past the end of K hold zeros (the loads fill them)
         for (int j = 0; j < kkb; j += kstack) {
           const uint64_t da = umma_desc(sa + j * a_tile), db = umma_desc(sb + j * kBBytes);
           const uint64_t du = umma_desc(sa + (kkb + j) * a_tile);
@@ -654,7 +538,6 @@ gemm_tc_rows_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         if (++s == n_stages) { s = 0; phase ^= 1; }
       }
       umma_commit(tmem_full_bar);
-      if (tl) tl[5] = clock64();
     }
   } else {
     // ------------------------------------------------------------ epilogue warps
@@ -669,100 +552,7 @@ gemm_tc_rows_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
       asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(my_rank));
       asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(n_ranks));
     }
-    if (NORMB) {
-      static_assert(!NORMB || BN == 16, "the in-kernel norm is written for token tiles of 16");
-      // Warp w makes the tiles j with j % 4 == w of every stage, so it visits every ring slot in
-      // every round and is never two phases ahead of a slot's barrier.  The rows of the next
-      // tile are fetched before the current one is written: the fetch does not depend on the ring.
-      const int ew = warp - 2, chunk = lane & 7;
-      float ssq[4] = {0.f, 0.f, 0.f, 0.f};
-      struct Rows { float4 v0[4], v1[4], w0, w1; };
-      auto fetch = [&](int unit, Rows& t) {  // unit = stage index * kkb + tile of the stage
-        const int i = unit / kkb, j = unit - i * kkb;
-        const int k = (kb0 + st_of(i) * kkb + j) * BK + chunk * 8;  // past K: a tile of zeros
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          const int tok = (lane >> 3) + 4 * q;
-          t.v0[q] = t.v1[q] = make_float4(0.f, 0.f, 0.f, 0.f);
-          if (tok < a.M && k < a.K) {
-            const float* xp = a.norm.x + (int64_t)tok * a.norm.ldx + k;
-            t.v0[q] = *reinterpret_cast<const float4*>(xp);
-            t.v1[q] = *reinterpret_cast<const float4*>(xp + 4);
-            for (int sp = 0; sp < a.norm.n_splits; ++sp) {
-              const float* pp = a.norm.part + (int64_t)sp * a.norm.split_stride + (int64_t)tok * a.norm.ldp + k;
-              const float4 p0 = *reinterpret_cast<const float4*>(pp), p1 = *reinterpret_cast<const float4*>(pp + 4);
-              t.v0[q].x += p0.x; t.v0[q].y += p0.y; t.v0[q].z += p0.z; t.v0[q].w += p0.w;
-              t.v1[q].x += p1.x; t.v1[q].y += p1.y; t.v1[q].z += p1.z; t.v1[q].w += p1.w;
-            }
-          }
-        }
-        t.w0 = t.w1 = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (k < a.K) {
-          t.w0 = *reinterpret_cast<const float4*>(a.norm.w + k);
-          t.w1 = *reinterpret_cast<const float4*>(a.norm.w + k + 4);
-        }
-      };
-      // this warp's units in order: (stage 0, tiles ew, ew+4, ..), (stage 1, ..), ..
-      auto next_unit = [&](int unit) {
-        int i = unit / kkb, j = unit - i * kkb + 4;
-        if (j >= kkb) { ++i; j = ew; }
-        return i * kkb + j;
-      };
-      const int end_unit = n_st * kkb;
-      int unit = ew < kkb ? ew : end_unit;
-      Rows cur, nxt;
-      if (unit < end_unit) fetch(unit, cur);
-      while (unit < end_unit) {
-        const int following = next_unit(unit);
-        if (following < end_unit) fetch(following, nxt);
-        const int i = unit / kkb, j = unit - i * kkb;
-        const int s = i % n_stages;
-        const uint32_t phase = (i / n_stages) & 1;
-        if (!mbar_wait(empty_bar(s), phase ^ 1, &abort_flag, a.error_flag, 4)) break;
-        uint8_t* sb = smem_raw + (base - smem_u32(smem_raw)) + s * stage_bytes + kkb * kATiles * a_tile + j * kBBytes;
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          const int r = (lane >> 3) + 4 * q;
-          const float4 v0 = cur.v0[q], v1 = cur.v1[q];
-          ssq[q] += v0.x * v0.x + v0.y * v0.y + v0.z * v0.z + v0.w * v0.w +
-                    v1.x * v1.x + v1.y * v1.y + v1.z * v1.z + v1.w * v1.w;
-          __nv_bfloat162 b0 = __floats2bfloat162_rn(v0.x * cur.w0.x, v0.y * cur.w0.y);
-          __nv_bfloat162 b1 = __floats2bfloat162_rn(v0.z * cur.w0.z, v0.w * cur.w0.w);
-          __nv_bfloat162 b2 = __floats2bfloat162_rn(v1.x * cur.w1.x, v1.y * cur.w1.y);
-          __nv_bfloat162 b3 = __floats2bfloat162_rn(v1.z * cur.w1.z, v1.w * cur.w1.w);
-          *reinterpret_cast<uint4*>(sb + r * 128 + ((chunk ^ (r & 7)) << 4)) =
-              make_uint4(*reinterpret_cast<uint32_t*>(&b0), *reinterpret_cast<uint32_t*>(&b1),
-                         *reinterpret_cast<uint32_t*>(&b2), *reinterpret_cast<uint32_t*>(&b3));
-        }
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        __syncwarp();
-        if (lane == 0) mbar_arrive(full_bar(s));  // one arrival per tile of the stage
-        cur = nxt;
-        unit = following;
-      }
-#pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        float v = ssq[q];
-        v += __shfl_xor_sync(0xffffffffu, v, 1);
-        v += __shfl_xor_sync(0xffffffffu, v, 2);
-        v += __shfl_xor_sync(0xffffffffu, v, 4);
-        if (chunk == 0) warp_ssq[ew][(lane >> 3) + 4 * q] = v;
-      }
-      asm volatile("barrier.sync 1, 128;" ::: "memory");
-      if (et < BN) {
-        const float v = warp_ssq[0][et] + warp_ssq[1][et] + warp_ssq[2][et] + warp_ssq[3][et];
-        row_ssq[et] = v;
-        if (clustered) {  // every split needs every split's share
-          for (uint32_t r = 0; r < n_ranks; ++r) {
-            uint32_t remote;
-            asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(&rank_ssq[my_rank][et])), "r"(r));
-            asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
-          }
-        }
-      }
-      asm volatile("barrier.sync 1, 128;" ::: "memory");
-    }
-    const bool scale_in = !NORMB && a.scale.ssq_part != nullptr;
+    const bool scale_in = a.scale.ssq_part != nullptr;
     if (scale_in) {  // while the main loop runs: add up the shares of the rows' sums of squares
       if (et < BN) {
         float v = 0.f;
@@ -772,9 +562,9 @@ gemm_tc_rows_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
       }
       asm volatile("barrier.sync 1, 128;" ::: "memory");
     }
-    const bool scaled = NORMB || scale_in;
-    const float norm_width = NORMB ? (float)a.K : (float)a.scale.width;
-    const float norm_eps = NORMB ? a.norm.eps : a.scale.eps;
+    const bool scaled = scale_in;
+    const float norm_width = (float)a.scale.width;
+    const float norm_eps = a.scale.eps;
     // The epilogue below runs once per block with one warp per scheduler: nothing hides an
     // instruction's latency there, so whatever can be done while the main loop runs is done here
     // (the rows' scalars: 1.6 to 1.0 us for the q/k/v product's epilogue).  (Running the token loops
@@ -806,10 +596,7 @@ gemm_tc_rows_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
       for (int j = 0; j < 16; ++j) old16[j] = j < a.M ? ((const float*)a.y)[(int64_t)j * a.ldy + f] : 0.f;
     }
     const bool ok = n_kb > 0 && mbar_wait(tmem_full_bar, 0, &abort_flag, a.error_flag, 3);
-    if (ok) {
-      if (tl && threadIdx.x == 64) tl[6] = clock64();
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    }
+    if (ok) asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16);
     if (kstack > 1) {
       // lane L of the accumulator is row L % R of K-block group L / R; its partial products are the
@@ -950,7 +737,7 @@ gemm_tc_rows_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     }
   }
   if (clustered) {
-    // All splits have pushed their tiles (and their shares of the rows' sums of squares); each
+    // All splits have pushed their tiles; each
     // block owns the token columns c with c % n_ranks == its rank and adds the splits' values
     // in rank order.  A block that gave up on a wait still arrives, so that its peers go on.
     uint32_t rank, n_ranks;
@@ -969,19 +756,12 @@ gemm_tc_rows_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
       }
     }
     __syncwarp();
-    if (tl && threadIdx.x == 64) tl[8] = clock64();
     asm volatile("barrier.cluster.arrive.release;\n\tbarrier.cluster.wait.acquire;" ::: "memory");
-    if (tl && threadIdx.x == 64) tl[9] = clock64();
     if (worker && !abort_flag) {
       const float* land = reinterpret_cast<const float*>(smem_raw + (landing - smem_u32(smem_raw)));
       auto finish = [&](int i, int col, float before) {
         float sum = 0.f;
         for (uint32_t src = 0; src < n_ranks; ++src) sum += land[((int)src * per_rank + i) * BM + r_local];
-        if (NORMB) {
-          float ssq = 0.f;
-          for (uint32_t src = 0; src < n_ranks; ++src) ssq += rank_ssq[src][col];
-          sum *= 1.0f / sqrtf(ssq / (float)a.K + a.norm.eps);
-        }
         if (MODE == kStoreBf16) ((__nv_bfloat16*)a.y)[(int64_t)col * a.ldy + f] = __float2bfloat16_rn(sum);
         else ((float*)a.y)[(int64_t)col * a.ldy + f] = before + sum;
       };
@@ -998,7 +778,6 @@ gemm_tc_rows_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     }
   }
   // ------------------------------------------------------------------ teardown
-  if (tl && threadIdx.x == 64) tl[10] = clock64();
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   if (warp == 1) {
@@ -1010,20 +789,13 @@ gemm_tc_rows_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)ra.tmem_cols) : "memory");
   }
-  if (tl && threadIdx.x == 0) {
-    tl[7] = clock64();
-    unsigned long long g;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g));
-    if (!clustered) tl[8] = (long long)g;
-  }
 }
 
-template <int BN, int MODE, bool NORMB>
+template <int BN, int MODE>
 int launch_rows(const CUtensorMap& mw, const CUtensorMap& mx, const GemmArgs& a, int rows_per_block, int kkb, int kstack,
-                int splits, long long* timeline, cudaStream_t stream) {
+                int splits, cudaStream_t stream) {
   constexpr int kATiles = MODE == kGluBf16 ? 2 : 1;
   RowsArgs ra;
-  ra.timeline = timeline;
   ra.rows_per_block = rows_per_block;
   ra.kkb = kkb;
   ra.kstack = kstack;
@@ -1045,35 +817,35 @@ int launch_rows(const CUtensorMap& mw, const CUtensorMap& mx, const GemmArgs& a,
   const int smem = fixed + ra.n_stages * stage;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tc_rows_kernel<BN, MODE, NORMB>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_rows_kernel<BN, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          kRowsSmemBytes);
     if (e != cudaSuccess) return fail(kLaunchFailed, "gemm_tc_rows: cannot reserve shared memory: %s", cudaGetErrorString(e));
     configured = true;
   }
   const dim3 grid((a.N + rows_per_block - 1) / rows_per_block, 1, splits);
   if (splits > 1)
-    launch_overlapped_cluster(gemm_tc_rows_kernel<BN, MODE, NORMB>, grid, dim3(kThreads), (size_t)smem, stream,
+    launch_overlapped_cluster(gemm_tc_rows_kernel<BN, MODE>, grid, dim3(kThreads), (size_t)smem, stream,
                               (unsigned)splits, mw, mx, a, ra);
   else
-    launch_overlapped(gemm_tc_rows_kernel<BN, MODE, NORMB>, grid, dim3(kThreads), (size_t)smem, stream, mw, mx, a, ra);
+    launch_overlapped(gemm_tc_rows_kernel<BN, MODE>, grid, dim3(kThreads), (size_t)smem, stream, mw, mx, a, ra);
   return check_launch("gemm_tc_rows");
 }
 
-template <int BN, int MODE, bool NORMB = false>
+template <int BN, int MODE>
 int launch(const CUtensorMap& mw, const CUtensorMap& mx, const GemmArgs& a, dim3 grid, cudaStream_t stream) {
   using C = Cfg<BN, MODE>;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, MODE, NORMB>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          C::kSmemBytes);
     if (e != cudaSuccess) return fail(kLaunchFailed, "gemm_tc: cannot reserve %d bytes of shared memory: %s",
                                       C::kSmemBytes, cudaGetErrorString(e));
     configured = true;
   }
   if (MODE == kAccumCluster)
-    launch_overlapped_cluster(gemm_tc_kernel<BN, MODE, NORMB>, grid, dim3(kThreads), C::kSmemBytes, stream, grid.z, mw, mx, a);
+    launch_overlapped_cluster(gemm_tc_kernel<BN, MODE>, grid, dim3(kThreads), C::kSmemBytes, stream, grid.z, mw, mx, a);
   else
-    launch_overlapped(gemm_tc_kernel<BN, MODE, NORMB>, grid, dim3(kThreads), C::kSmemBytes, stream, mw, mx, a);
+    launch_overlapped(gemm_tc_kernel<BN, MODE>, grid, dim3(kThreads), C::kSmemBytes, stream, mw, mx, a);
   return check_launch("gemm_tc");
 }
 
@@ -1159,7 +931,7 @@ extern "C" int skyla_gemm_tc(const void* map_w, const void* map_x, void* y, int6
   memcpy(&mw, map_w, sizeof(mw));
   memcpy(&mx, map_x, sizeof(mx));
   GemmArgs a{y, ldy, split_stride, M, N, K, per, error_flag,
-             FoldJob{fold_x, fold_ldx, fold_part, fold_splits, fold_split_stride, fold_ldp, M, fold_h}, NormSource{},
+             FoldJob{fold_x, fold_ldx, fold_part, fold_splits, fold_split_stride, fold_ldp, M, fold_h},
              scratch, counters};
   dim3 grid((N + BM - 1) / BM, (M + bn - 1) / bn, splits);
   if (grid.y > 65535 || grid.z > 65535) return fail(kBadArgument, "gemm_tc: grid too large");
@@ -1184,59 +956,19 @@ extern "C" int skyla_gemm_tc(const void* map_w, const void* map_x, void* y, int6
   }
 }
 
-// The same product with the token operand made in the kernel: rmsnorm(x + sum_s part[s]) * w.
-// x [M, K] float, part [n_part][M][K] float or null, w [K] float.  Modes: gated (bf16 out),
-// store bf16/f32 (one K split only: the norm's scalar is applied in the epilogue), or partial
-// with ssq_out [splits][M] receiving each split's share of the rows' sums of squares.
-// Token tiles of 16, 32 or 64; x is not changed.
-extern "C" int skyla_gemm_tc_norm(const void* map_w, const float* x, int64_t ldx, const float* part, int n_part,
-                                  int64_t part_split_stride, int64_t ldp, const float* w, float eps, float* ssq_out,
-                                  void* y, int64_t ldy, int64_t split_stride, int M, int N, int K, int bn, int mode,
-                                  int splits, int* error_flag, cudaStream_t stream) {
-  if (M <= 0 || N <= 0) return kOk;
-  if (K <= 0 || K % 8) return fail(kBadArgument, "gemm_tc_norm: K=%d must be a positive multiple of 8", K);
-  if (bn != 16 || M > 16) return fail(kBadArgument, "gemm_tc_norm: at most 16 tokens (token tile 16), got %d", M);
-  if (ldx % 4 || ldp % 4 || part_split_stride % 4 || ((uintptr_t)x) % 16 || ((uintptr_t)part) % 16 || ((uintptr_t)w) % 16)
-    return fail(kBadArgument, "gemm_tc_norm: x, the partial sums and the weight must be 16-byte aligned");
-  if (mode == kPartialF32 ? ssq_out == nullptr : splits != 1)
-    return fail(kBadArgument, "gemm_tc_norm: K splits go with the partial epilogue and a place for the sums of squares");
-  if (mode != kPartialF32 && mode != kGluBf16 && mode != kStoreBf16 && mode != kStoreF32)
-    return fail(kBadArgument, "gemm_tc_norm: epilogue %d is not offered", mode);
-  const int total_kb = (K + BK - 1) / BK;
-  const int per = (total_kb + splits - 1) / splits;
-  if (splits < 1 || (splits - 1) * per >= total_kb) return fail(kBadArgument, "gemm_tc_norm: %d K splits leave one empty (K=%d)", splits, K);
-  alignas(64) CUtensorMap mw;
-  memcpy(&mw, map_w, sizeof(mw));
-  GemmArgs a{y, ldy, split_stride, M, N, K, per, error_flag, FoldJob{},
-             NormSource{x, ldx, part, part ? n_part : 0, part_split_stride, ldp, w, eps, ssq_out}, nullptr, nullptr};
-  dim3 grid((N + BM - 1) / BM, (M + bn - 1) / bn, splits);
-#define SKYLA_NORM_LAUNCH(MODE_) return launch<16, MODE_, true>(mw, mw, a, grid, stream);
-  switch (mode) {
-    case kPartialF32: SKYLA_NORM_LAUNCH(kPartialF32)
-    case kGluBf16: SKYLA_NORM_LAUNCH(kGluBf16)
-    case kStoreBf16: SKYLA_NORM_LAUNCH(kStoreBf16)
-    default: SKYLA_NORM_LAUNCH(kStoreF32)
-  }
-#undef SKYLA_NORM_LAUNCH
-}
-
 // Few tokens (at most 64): blocks of `rows_per_block` weight rows (a multiple of 8, at most 128), K cut
 // into `splits` (at most 8) that meet in a thread-block cluster.  map_w has boxes of rows_per_block rows
 // and `kkb` K blocks (kkb > 1: a 3-D map, see skyla_tensor_map_bf16), of which one MMA takes `kstack` at
-// once (stacked along its rows; one split then).  Either x comes by map_x (bf16
-// [M, K], boxes of bn rows and kkb K blocks), or -- norm_x set -- the token operand is
-// rmsnorm(norm_x + sum_s part[s]) * norm_w made in the kernel (M <= 16, bn = 16).
+// once (stacked along its rows; one split then).  x comes by map_x (bf16 [M, K], boxes of bn rows
+// and kkb K blocks).
 // Modes: store bf16 / f32, accumulate into f32 y, gated (bf16, one split).
 // ahead_*: with the accumulate epilogue, also leave bf16(y_new * ahead_w) in ahead_xw [M, N] and this
 // launch's blocks' shares of the new rows' sums of squares in ahead_ssq [blocks, M].
 // scale_*: the result is multiplied by 1/sqrt(sum_p scale_ssq[p, tok] / K + scale_eps).
-extern "C" int skyla_gemm_tc_rows(const void* map_w, const void* map_x, const float* norm_x, int64_t norm_ldx,
-                                  const float* part, int n_part, int64_t part_split_stride, int64_t ldp,
-                                  const float* norm_w, float eps, void* y, int64_t ldy, int M, int N, int K, int bn,
+extern "C" int skyla_gemm_tc_rows(const void* map_w, const void* map_x, void* y, int64_t ldy, int M, int N, int K, int bn,
                                   int mode, int rows_per_block, int kkb, int kstack, int splits, int* error_flag,
                                   const float* ahead_w, void* ahead_xw, int64_t ahead_ldxw, float* ahead_ssq,
-                                  const float* scale_ssq, int scale_parts, float scale_eps,
-                                  long long* timeline, cudaStream_t stream) {
+                                  const float* scale_ssq, int scale_parts, float scale_eps, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return kOk;
   if (K <= 0 || K % 8) return fail(kBadArgument, "gemm_tc_rows: K=%d must be a positive multiple of 8", K);
   if (rows_per_block < 8 || rows_per_block > BM || rows_per_block % 8)
@@ -1253,47 +985,35 @@ extern "C" int skyla_gemm_tc_rows(const void* map_w, const void* map_x, const fl
   const int total_kb = (K + BK - 1) / BK;
   if (splits < 1 || splits > kRowsMaxSplits || splits > total_kb || (mode == kGluBf16 && splits != 1))
     return fail(kBadArgument, "gemm_tc_rows: %d K splits (1..8, one for the gated product)", splits);
-  const bool normb = norm_x != nullptr;
-  if (normb && (bn != 16 || norm_ldx % 4 || ldp % 4 || part_split_stride % 4 || ((uintptr_t)norm_x) % 16 ||
-                ((uintptr_t)part) % 16 || ((uintptr_t)norm_w) % 16 || mode == kAccumF32))
-    return fail(kBadArgument, "gemm_tc_rows: the in-kernel norm takes at most 16 tokens, 16-byte aligned rows, and no accumulate epilogue");
+  if (map_w == nullptr || map_x == nullptr) return fail(kBadArgument, "gemm_tc_rows: both operands come by tensor maps");
   alignas(64) CUtensorMap mw, mx;
   memcpy(&mw, map_w, sizeof(mw));
-  if (map_x != nullptr) memcpy(&mx, map_x, sizeof(mx)); else memcpy(&mx, map_w, sizeof(mx));
+  memcpy(&mx, map_x, sizeof(mx));
   int kps = (total_kb + splits - 1) / splits;
   kps = (kps + kkb - 1) / kkb * kkb;  // whole boxes per split
   if ((splits - 1) * kps >= total_kb) return fail(kBadArgument, "gemm_tc_rows: %d splits leave one without K blocks", splits);
-  GemmArgs a{y, ldy, 0, M, N, K, kps, error_flag, FoldJob{},
-             NormSource{norm_x, norm_ldx, part, part ? n_part : 0, part_split_stride, ldp, norm_w, eps, nullptr},
-             nullptr, nullptr};
+  GemmArgs a{y, ldy, 0, M, N, K, kps, error_flag, FoldJob{}, nullptr, nullptr};
   if (ahead_xw != nullptr) {
     if (mode != kAccumF32 || splits != 1 || ahead_w == nullptr || ahead_ssq == nullptr)
       return fail(kBadArgument, "gemm_tc_rows: norm-ahead goes with the accumulate epilogue, one split, a norm weight and room for the sums");
     a.ahead = NormAhead{ahead_w, (__nv_bfloat16*)ahead_xw, ahead_ldxw, ahead_ssq};
   }
   if (scale_ssq != nullptr) {
-    if (normb || splits != 1 || scale_parts < 1)
+    if (splits != 1 || scale_parts < 1)
       return fail(kBadArgument, "gemm_tc_rows: handed-in sums of squares go with a loaded token operand and one split");
     a.scale = ScaleIn{scale_ssq, scale_parts, scale_eps, K};
   }
-#define SKYLA_ROWS_BN(MODE_, NORMB_)                                                                  \
+#define SKYLA_ROWS_BN(MODE_)                                                                          \
   switch (bn) {                                                                                       \
-    case 16: return launch_rows<16, MODE_, NORMB_>(mw, mx, a, rows_per_block, kkb, kstack, splits, timeline, stream);   \
-    case 32: return launch_rows<32, MODE_, false>(mw, mx, a, rows_per_block, kkb, kstack, splits, timeline, stream);    \
-    default: return launch_rows<64, MODE_, false>(mw, mx, a, rows_per_block, kkb, kstack, splits, timeline, stream);    \
-  }
-  if (normb) {
-    switch (mode) {
-      case kStoreBf16: SKYLA_ROWS_BN(kStoreBf16, true)
-      case kStoreF32: SKYLA_ROWS_BN(kStoreF32, true)
-      default: SKYLA_ROWS_BN(kGluBf16, true)
-    }
+    case 16: return launch_rows<16, MODE_>(mw, mx, a, rows_per_block, kkb, kstack, splits, stream);   \
+    case 32: return launch_rows<32, MODE_>(mw, mx, a, rows_per_block, kkb, kstack, splits, stream);   \
+    default: return launch_rows<64, MODE_>(mw, mx, a, rows_per_block, kkb, kstack, splits, stream);   \
   }
   switch (mode) {
-    case kStoreBf16: SKYLA_ROWS_BN(kStoreBf16, false)
-    case kStoreF32: SKYLA_ROWS_BN(kStoreF32, false)
-    case kAccumF32: SKYLA_ROWS_BN(kAccumF32, false)
-    default: SKYLA_ROWS_BN(kGluBf16, false)
+    case kStoreBf16: SKYLA_ROWS_BN(kStoreBf16)
+    case kStoreF32: SKYLA_ROWS_BN(kStoreF32)
+    case kAccumF32: SKYLA_ROWS_BN(kAccumF32)
+    default: SKYLA_ROWS_BN(kGluBf16)
   }
 #undef SKYLA_ROWS_BN
 }

@@ -59,10 +59,20 @@ __device__ Best block_argmax(Best b, Best* scratch) {
 }
 __device__ float block_sum_f(float v, float* scratch) { return block_sum(v, scratch); }
 
+// A row in which no logit compares (all NaN) leaves no candidate: the token is then 0, never an
+// index outside the vocabulary (the next step would read the embedding table there), and the
+// device's error word is raised (code 31) for the host to find.
+constexpr int kNoTokenCode = 31;
+__device__ __forceinline__ int checked(int token, int vocab, int* error_flag) {
+  if (token >= 0 && token < vocab) return token;
+  if (error_flag != nullptr) atomicCAS(error_flag, 0, kNoTokenCode);
+  return 0;
+}
+
 __global__ void __launch_bounds__(kThreads)
 sample_kernel(const float* __restrict__ logits, int64_t ld, int vocab, float temperature, int top_k,
               float top_p, uint32_t seed_lo, uint32_t seed_hi, const int32_t* __restrict__ req_ids,
-              const int32_t* __restrict__ steps, int32_t* __restrict__ out) {
+              const int32_t* __restrict__ steps, int32_t* __restrict__ out, int* error_flag) {
   __shared__ Best bscratch[32];
   __shared__ float fscratch[32];
   const int r = blockIdx.x;
@@ -73,7 +83,7 @@ sample_kernel(const float* __restrict__ logits, int64_t ld, int vocab, float tem
     Best b{-INFINITY, 0x7fffffff};
     for (int i = tid; i < vocab; i += kThreads) b = better(b, Best{row[i], i});
     b = block_argmax(b, bscratch);
-    if (tid == 0) out[r] = b.i;
+    if (tid == 0) out[r] = checked(b.i, vocab, error_flag);
     return;
   }
   uint32_t tau = 0;  // keep ordered(z_i) >= tau
@@ -117,13 +127,13 @@ sample_kernel(const float* __restrict__ logits, int64_t ld, int vocab, float tem
     b = better(b, Best{z - logf(-logf(u)), i});
   }
   b = block_argmax(b, bscratch);
-  if (tid == 0) out[r] = b.i;
+  if (tid == 0) out[r] = checked(b.i, vocab, error_flag);
 }
 }  // namespace
 
 extern "C" int skyla_sample(const float* logits, int64_t ld, int n_rows, int vocab, float temperature,
                             int top_k, float top_p, uint64_t seed, const int32_t* req_ids,
-                            const int32_t* steps, int32_t* out, cudaStream_t stream) {
+                            const int32_t* steps, int32_t* out, int* error_flag, cudaStream_t stream) {
   if (n_rows <= 0) return kOk;
   if (vocab <= 0 || ld < vocab) return fail(kBadArgument, "sample: bad vocabulary %d", vocab);
   if (vocab > (1 << 24)) return fail(kBadArgument, "sample: vocabulary %d above 2^24", vocab);
@@ -132,6 +142,6 @@ extern "C" int skyla_sample(const float* logits, int64_t ld, int n_rows, int voc
     return fail(kBadArgument, "sample: a random draw needs request ids and steps");
   sample_kernel<<<n_rows, kThreads, 0, stream>>>(logits, ld, vocab, temperature, top_k, top_p,
                                                 (uint32_t)seed, (uint32_t)(seed >> 32), req_ids,
-                                                steps, out);
+                                                steps, out, error_flag);
   return check_launch("sample");
 }

@@ -12,8 +12,9 @@ pinned host buffer and sent with one copy per step:
   seq_slot[B]  cache slot of each sequence (for parts with per-slot state)
   seq_start[B] positions already cached, seq_n[B] new tokens, cu[B+1] packed offsets
   want[R]      rows (packed token indices) whose logits are asked for
-  tile_seq/tile_tok0/tile_rows[Q]  tiles of up to 64 consecutive new tokens of one
-               sequence, the units the prefill attention kernel works in
+  tiles[h] = (tile_seq, tile_tok0, tile_rows)[Q]  for every tile height h that a mixer of the
+               model asked for (``Part.token_tiles``): tiles of up to h consecutive new tokens of
+               one sequence, the units a prompt attention kernel works in
   pages[G][B,P] for each cache group the page list of each sequence
 """
 from __future__ import annotations
@@ -83,10 +84,9 @@ class StepContext:
     want: torch.Tensor
     pages: List[torch.Tensor]
     pages_needed: Optional[torch.Tensor] = None  # one int32: pages of the longest sequence after this step
-    n_tiles: int = 0
-    tile_seq: Optional[torch.Tensor] = None
-    tile_tok0: Optional[torch.Tensor] = None
-    tile_rows: Optional[torch.Tensor] = None
+    #: tile height -> (sequence row, first packed token, rows) of every tile, for the heights the
+    #: model's mixers asked for
+    tiles: Dict[int, Tuple[torch.Tensor, torch.Tensor, torch.Tensor]] = field(default_factory=dict)
     host: Dict[str, np.ndarray] = field(default_factory=dict)
     #: when profiling: (label, event) pairs, an event after each stage
     #: (the reference's timestamp marks, skyla-engine/src/graph.rs:54-57)
@@ -156,9 +156,11 @@ class BatchBuilder:
             idx = torch.tensor(rows, dtype=torch.int64).to(self.rt.device, non_blocking=True)
             dev_tokens.copy_(src.index_select(0, idx))
 
-    def __init__(self, rt, cache):
+    def __init__(self, rt, cache, tile_heights: Sequence[int] = ()):
+        """``tile_heights``: the heights of token tiles that the model's mixers want listed every step."""
         self.rt = rt
         self.cache = cache
+        self.tile_heights = tuple(sorted(set(int(h) for h in tile_heights)))
         self.workspace = Workspace(rt.device)
         self._pinned: Optional[torch.Tensor] = None
         self._device: Optional[torch.Tensor] = None
@@ -186,9 +188,8 @@ class BatchBuilder:
             if pages_width < P:
                 raise ValueError(f"page lists need {P} columns, {pages_width} were given")
             P = pages_width
-        TILE = 64
-        Q = sum(-(-n // TILE) for n in ns)
-        total = 3 * T + 3 * B + (B + 1) + R + 3 * Q + 1 + G * B * P
+        n_tiles = {th: sum(-(-n // th) for n in ns) for th in self.tile_heights}
+        total = 3 * T + 3 * B + (B + 1) + R + 3 * sum(n_tiles.values()) + 1 + G * B * P
         if self._copied is not None:
             self._copied.synchronize()  # the last step's copy has left the pinned buffer
         host, dev = self._staging(total)
@@ -209,12 +210,10 @@ class BatchBuilder:
         seq_n, r_n = take(B)
         cu, r_cu = take(B + 1)
         want, r_want = take(R)
-        tile_seq, r_tseq = take(Q)
-        tile_tok0, r_ttok = take(Q)
-        tile_rows, r_trows = take(Q)
+        tiles = {th: [take(q) for _ in range(3)] for th, q in n_tiles.items()}
         needed, r_needed = take(1)
         needed[0] = max(1, max(-(-(s + n) // cache.page_size) for s, n in zip(starts, ns)))
-        q = 0
+        q = {th: 0 for th in tiles}
         t = 0
         w = 0
         cu[0] = 0
@@ -229,9 +228,10 @@ class BatchBuilder:
                     raise IndexError(f"wanted place {j} is outside the {n} tokens of this step")
                 want[w] = t + j
                 w += 1
-            for j in range(0, n, TILE):
-                tile_seq[q], tile_tok0[q], tile_rows[q] = b, t + j, min(TILE, n - j)
-                q += 1
+            for th, ((tile_seq, _), (tile_tok0, _), (tile_rows, _)) in tiles.items():
+                for j in range(0, n, th):
+                    tile_seq[q[th]], tile_tok0[q[th]], tile_rows[q[th]] = b, t + j, min(th, n - j)
+                    q[th] += 1
             t += n
             cu[b + 1] = t
         r_pages = []
@@ -260,6 +260,6 @@ class BatchBuilder:
             page_size=cache.page_size, tokens=view(r_tokens), tok_pos=view(r_pos),
             tok_seq=view(r_seq), seq_slot=view(r_slot), seq_start=view(r_start), seq_n=view(r_n),
             cu=view(r_cu), want=view(r_want), pages=[view(r).view(B, P) for r in r_pages],
-            pages_needed=view(r_needed), n_tiles=Q, tile_seq=view(r_tseq), tile_tok0=view(r_ttok), tile_rows=view(r_trows),
+            pages_needed=view(r_needed), tiles={th: tuple(view(r) for _, r in three) for th, three in tiles.items()},
             host={"starts": np.asarray(starts), "ns": np.asarray(ns)},
         )

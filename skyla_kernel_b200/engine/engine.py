@@ -58,7 +58,7 @@ class Engine:
         self.model.load(tensors)
         self.cache = SequenceCache(self.model.kv_needs, self.model.state_needs, max_tokens, max_slots,
                                    self.rt.cache_dtype, self.rt.device)
-        self.batcher = BatchBuilder(self.rt, self.cache)
+        self.batcher = BatchBuilder(self.rt, self.cache, self.model.tile_heights())
         self.vocab_size = self.spec.vocab_size
         if cuda_graphs is None:
             cuda_graphs = os.environ.get("SKYLA_CUDA_GRAPHS", "1") != "0"
@@ -140,6 +140,13 @@ class Engine:
         """``[(label, nanoseconds)]`` of the last step run with ``profile=True``, largest first
         (the reference's ``Engine::last_step_profile``, skyla-engine/src/engine.rs:91-96)."""
         return list(getattr(self, "_profile", []))
+
+    def check_errors(self) -> None:
+        """Raise ``KernelError`` if one of this engine's kernels reported a fault since the last check:
+        a bounded wait that ran out, a row of logits without a token, a token outside the embedding
+        table.  It waits for the device.  The generation loop reads the same word with every step's
+        tokens; callers of :meth:`step` who never synchronize otherwise call this when they read results."""
+        self.rt.kernel_state.check()
 
     # ------------------------------------------------------------------ facts
     def weight_bytes(self) -> int:

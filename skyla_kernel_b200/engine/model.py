@@ -54,19 +54,19 @@ class DecoderModel:
         for i, e in enumerate(spec.schedule):
             if not 0 <= e.layer < len(self.blocks):
                 raise ConfigError(f"schedule entry {i} names layer {e.layer}, the model has {len(self.blocks)}")
-            mixer = self.blocks[e.layer].mixer
+            block = self.blocks[e.layer]
             if e.reads_cache_of is None:
                 owner_entry[i] = len(self.kv_needs)
                 self.entries.append(EntryBinding(len(self.kv_needs), True))
-                self.kv_needs.append(mixer.cache_need())
-                self.state_needs.append(mixer.state_need())
+                self.kv_needs.append(block.cache_need())
+                self.state_needs.append(block.state_need())
             else:
                 j = e.reads_cache_of
                 if j not in owner_entry or j >= i:
                     raise ConfigError(f"schedule entry {i} reads the cache of entry {j}, which is not "
                                       f"an earlier entry with a cache of its own")
-                src = self.blocks[spec.schedule[j].layer].mixer
-                if src.cache_need() != mixer.cache_need():
+                src = self.blocks[spec.schedule[j].layer]
+                if src.cache_need() != block.cache_need():
                     raise ConfigError(f"schedule entry {i} cannot read the cache of entry {j}: "
                                       f"their mixers need different caches")
                 self.entries.append(EntryBinding(owner_entry[j], False))
@@ -78,6 +78,14 @@ class DecoderModel:
         for b in self.blocks:
             parts.extend(b.parts())
         return all(getattr(p, "graph_safe", False) for p in parts)
+
+    def tile_heights(self):
+        """The heights of token tiles that the mixers want listed in every step's batch."""
+        hs = []
+        for b in self.blocks:
+            for p in b.parts():
+                hs.extend(getattr(p, "token_tiles", ()))
+        return tuple(sorted(set(hs)))
 
     def kernels_needed(self):
         mods = list(self.embedding.kernels_needed())

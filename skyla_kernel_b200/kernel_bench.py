@@ -40,8 +40,7 @@ def _time(fn, copies: int, reps: int) -> float:
     return a.elapsed_time(b) * 1e3 / reps / copies
 
 
-def linear(tokens: int, n_out: int, n_in: int, mode: str, copies: int = 0, reps: int = 5, rows_max: int = -1,
-           plan: str = "") -> dict:
+def linear(tokens: int, n_out: int, n_in: int, mode: str, copies: int = 0, reps: int = 5) -> dict:
     """The tensor-core product as the linear part would launch it for this many tokens."""
     from .parts.base import Runtime
     from .parts.feedforward import fuse_gate_up
@@ -55,10 +54,6 @@ def linear(tokens: int, n_out: int, n_in: int, mode: str, copies: int = 0, reps:
         w = torch.empty(rows, n_in, dtype=torch.bfloat16, device=DEV)
         ops.fill_normal(w, 0.0, 0.02, i)
         lins.append(Linear(w, rt, gated=gated))
-        if rows_max >= 0:
-            lins[-1].ROWS_MAX_TOKENS = lins[-1].STACKED_MAX_TOKENS = rows_max
-        if plan:
-            lins[-1].rows_plans = {bn: tuple(int(v) for v in plan.split(",")) for bn in (16, 32, 64)}
     x = torch.randn(tokens, n_in, device=DEV).to(torch.bfloat16)
     if mode == "accumulate":
         y = torch.zeros(tokens, n_out, device=DEV)
@@ -112,10 +107,8 @@ def _paged(batch: int, context: int, nkv: int, hd: int):
     return k, v, table, width
 
 
-def attention_decode(batch: int, context: int, nq: int = 32, nkv: int = 8, hd: int = 128, reps: int = 5,
-                     splits: int = 0) -> dict:
-    """Split-context decode attention plus its merge, cut as the attention part would cut it
-    (``splits`` > 0 overrides the number of splits)."""
+def attention_decode(batch: int, context: int, nq: int = 32, nkv: int = 8, hd: int = 128, reps: int = 5) -> dict:
+    """Split-context decode attention plus its merge, cut as the attention part would cut it."""
     from .config import PartSpec
     from .parts.attention import GQAttention
     from .parts.base import Runtime
@@ -126,8 +119,6 @@ def attention_decode(batch: int, context: int, nq: int = 32, nkv: int = 8, hd: i
     part = GQAttention(PartSpec("gqa_attention", {"hidden_size": nq * hd, "num_heads": nq, "num_kv_heads": nkv,
                                                   "head_dim": hd}), Runtime(torch.device(DEV), "bfloat16"))
     n_splits, per = part.decode_splits(batch, width)
-    if splits:
-        n_splits, per = splits, -(-width // splits)
     needed = torch.tensor([-(-context // 64)], dtype=torch.int32, device=DEV)
     scratch = torch.empty(batch * nq * n_splits * (hd + 2), device=DEV)
     us = _time(lambda i: ops.attention_decode(q, out, scratch, nq, nkv, hd, k, v, table, 64, pos, 1 / math.sqrt(hd), 0,
@@ -159,19 +150,10 @@ def step(tokens: int, batch: int, context: int, layers: int, reps: int = 3) -> d
     stage on the last repetition (for a decode step that repetition is launched kernel by kernel, not as
     its graph, so its stage times are those of the host).  The launches of the last repetition are what a
     profiler's launch list should look at."""
-    from .config import Qwen3Config
-    from .engine import Engine, StepItem, declared_tensors
-    cfg = Qwen3Config(hidden_size=4096, num_hidden_layers=layers, num_attention_heads=32, num_key_value_heads=8,
-                      head_dim=128, intermediate_size=12288, vocab_size=151936, rope_theta=1000000.0, rms_norm_eps=1e-6,
-                      max_position_embeddings=40960, tie_word_embeddings=False)
-    tensors = {}
-    for i, (name, d) in enumerate(declared_tensors(cfg.to_spec()).items()):
-        t = torch.empty(d.shape, dtype=torch.bfloat16, device=DEV)
-        ops.fill_normal(t, 1.0 if d.init == "norm" else 0.0, 0.02, i)
-        tensors[name] = t
+    from .engine import StepItem
+    from .measure import random_engine
     length = tokens if tokens > 1 else context
-    eng = Engine(cfg, tensors, "bfloat16", max_tokens=batch * (length + 128), max_slots=batch)
-    del tensors
+    eng, cfg = random_engine("8b", layers, max_tokens=batch * (length + 128), max_slots=batch, device=DEV)
     g = torch.Generator().manual_seed(1)
     prompts = [torch.randint(0, cfg.vocab_size, (length,), generator=g).tolist() for _ in range(batch)]
     times = []
@@ -211,9 +193,9 @@ def main(a) -> int:
     if a.kernel == "step":
         r = step(a.tokens, a.batch, a.context, a.layers, reps=a.reps)
     elif a.kernel == "linear":
-        r = linear(a.tokens, a.n_out, a.n_in, a.mode, reps=a.reps, rows_max=a.rows_max, plan=a.plan)
+        r = linear(a.tokens, a.n_out, a.n_in, a.mode, reps=a.reps)
     elif a.kernel == "attention-decode":
-        r = attention_decode(a.batch, a.context, reps=a.reps, splits=a.splits)
+        r = attention_decode(a.batch, a.context, reps=a.reps)
     else:
         r = attention_prefill(a.tokens, reps=a.reps)
     print(json.dumps(r))

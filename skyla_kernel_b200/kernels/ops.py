@@ -8,7 +8,6 @@ launch.  Nothing here computes on the host or falls back to library code.
 from __future__ import annotations
 
 import ctypes
-import os
 from ctypes import c_float, c_int, c_int64, c_size_t, c_uint64, c_void_p
 from typing import Optional
 
@@ -96,8 +95,10 @@ def _check(module: str, rc: int):
 
 
 # ------------------------------------------------------------------ embedding
-def embed_gather(tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
-    """out[t, :] = table[tokens[t], :]; tokens were checked against the vocabulary on the host."""
+def embed_gather(tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor,
+                 state: Optional["KernelState"] = None) -> torch.Tensor:
+    """out[t, :] = table[tokens[t], :].  A token outside the table gets a row of zeros and raises the
+    state's error word (the host checks the tokens it feeds; a sampler's output is checked here)."""
     _cuda(tokens, table, out)
     _i32(tokens, "tokens")
     if not table.is_contiguous():
@@ -106,9 +107,9 @@ def embed_gather(tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor) -
     if out.shape[0] < n or out.shape[1] != hidden:
         raise KernelError(f"embed_gather: out {tuple(out.shape)} does not hold [{n}, {hidden}]")
     f = _fn("embed", "skyla_embed_gather",
-            [c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int64, c_void_p])
-    _check("embed", f(_ptr(tokens), n, _ptr(table), dtype_code(table), hidden, _ptr(out),
-                      dtype_code(out), _rows(out, "out"), _stream()))
+            [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_int64, c_void_p, c_void_p])
+    _check("embed", f(_ptr(tokens), n, _ptr(table), dtype_code(table), table.shape[0], hidden, _ptr(out),
+                      dtype_code(out), _rows(out, "out"), _ptr(_state(state, out).error_flag), _stream()))
     return out
 
 
@@ -199,28 +200,116 @@ def linear_plain(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, mode: int = 
 TC_STORE_BF16, TC_STORE_F32, TC_ACCUM_F32, TC_GLU_BF16, TC_PARTIAL_F32, TC_ACCUM_CLUSTER, TC_ACCUM_LAST = 0, 1, 2, 3, 4, 5, 6
 TC_TOKEN_TILES = (16, 32, 64, 128, 256)
 
-_ERROR_FLAGS = {}
+
+class KernelState:
+    """Device memory that the kernels of ONE engine keep between their launches.
+
+    * ``error_flag``: one int32 that a kernel raises when a bounded wait ran out (codes 1 to 19),
+      when the sampler found no token in a row of logits (31: every logit NaN) or when a token fed
+      on the device lies outside the embedding table (32);
+    * counters with which the blocks of a launch find out which of them finishes last (the context
+      splits of decode attention, the K splits of a small product): zero between launches;
+    * scratch in which K splits meet, and the flags of the prompt product's tiles that are cut
+      along K.
+
+    An engine owns one (``Runtime.kernel_state``) and hands it to every launch, so two engines on
+    two streams share nothing.  The launches of one state must not overlap on the device: one
+    engine runs its steps on one stream.  Launches that name no state (kernel tests, the kernel
+    benchmark) use the device's default state.  Buffers that had to grow stay alive, because a
+    recorded CUDA graph may still point at the old ones.
+    """
+
+    MERGE_COUNTERS = 1 << 16
+
+    def __init__(self, device):
+        self.device = torch.device(device)
+        self.error_flag = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self._merge = None
+        self._tiles = []
+        self._accum = []
+        self._shares = None
+
+    @property
+    def sm_count(self) -> int:
+        return torch.cuda.get_device_properties(self.device).multi_processor_count
+
+    def merge_counters(self) -> torch.Tensor:
+        """One zeroed int32 per (sequence, key/value head) of a decode step."""
+        if self._merge is None:
+            self._merge = torch.zeros(self.MERGE_COUNTERS, dtype=torch.int32, device=self.device)
+        return self._merge
+
+    def tile_counters(self, n: int) -> torch.Tensor:
+        """Zeroed int32 counters, one per output tile, that the last-arriver epilogue leaves zeroed."""
+        if not self._tiles or self._tiles[-1].numel() < n:
+            self._tiles.append(torch.zeros(max(4096, n), dtype=torch.int32, device=self.device))
+        return self._tiles[-1]
+
+    def accum_scratch(self, n: int) -> torch.Tensor:
+        """Float32 scratch for the K splits' tiles, shared by the products of this state (they run
+        one after another)."""
+        if not self._accum or self._accum[-1].numel() < n:
+            self._accum.append(torch.empty(max(n, 1 << 22), dtype=torch.float32, device=self.device))
+        return self._accum[-1]
+
+    def prompt_shares(self):
+        """(scratch for one accumulator tile per SM, a flag per SM, SMs) for ``gemm_prompt``'s tiles
+        that are cut along K."""
+        if self._shares is None:
+            n = self.sm_count
+            self._shares = (torch.empty(n * 128 * 256, dtype=torch.float32, device=self.device),
+                            torch.zeros(n, dtype=torch.int32, device=self.device), n)
+        return self._shares
+
+    def reset(self) -> None:
+        """Everything that has to be zero between launches is zero again (after a kernel gave up,
+        any of it may have been left raised)."""
+        self.error_flag.zero_()
+        if self._merge is not None:
+            self._merge.zero_()
+        for t in self._tiles:
+            t.zero_()
+        if self._shares is not None:
+            self._shares[1].zero_()
+
+    def raise_if(self, code: int) -> None:
+        """``code`` is the error word as read on the host (0: nothing happened)."""
+        if not code:
+            return
+        self.reset()
+        if code == 31:
+            what = "the sampler found no token in a row of logits (all NaN?) and gave token 0"
+        elif code == 32:
+            what = "a token fed on the device lies outside the embedding table; its row was zero-filled"
+        else:
+            what = f"a kernel's bounded wait ran out (code {code})"
+        raise KernelError(f"{what}; the results since the last check are not valid")
+
+    def check(self) -> None:
+        """Raise if a kernel reported an error since the last check (synchronizes)."""
+        self.raise_if(int(self.error_flag.item()))
 
 
-def error_flag(device) -> torch.Tensor:
-    """One int32 per device that kernels with bounded waits set when a wait ran out."""
+_DEFAULT_STATES = {}
+
+
+def default_state(device) -> KernelState:
     dev = torch.device(device)
-    t = _ERROR_FLAGS.get(dev)
-    if t is None:
-        t = _ERROR_FLAGS[dev] = torch.zeros(1, dtype=torch.int32, device=dev)
-    return t
+    if dev.index is None:
+        dev = torch.device(dev.type, torch.cuda.current_device())
+    st = _DEFAULT_STATES.get(dev)
+    if st is None:
+        st = _DEFAULT_STATES[dev] = KernelState(dev)
+    return st
+
+
+def _state(state: Optional[KernelState], t: torch.Tensor) -> KernelState:
+    return state if state is not None else default_state(t.device)
 
 
 def check_device_errors(device) -> None:
-    """Raise if a kernel gave up on a wait since the last check (synchronizes)."""
-    t = _ERROR_FLAGS.get(torch.device(device))
-    if t is not None:
-        code = int(t.item())
-        if code:
-            t.zero_()
-            for _, flags, _ in _PROMPT_SHARES.values():
-                flags.zero_()  # a kernel that gave up may have left some raised
-            raise KernelError(f"a kernel's bounded wait ran out (code {code}); its results are not valid")
+    """Raise if a kernel launched without a state of its own gave up since the last check."""
+    default_state(device).check()
 
 
 class TensorMap:
@@ -285,34 +374,8 @@ def _fold_args(fold, m: int):
     return [_ptr(x), _rows(x, "x"), _ptr(part), part.shape[0], part.stride(0), part.stride(1), x.shape[1]]
 
 
-_TILE_COUNTERS = {}
-
-
-def tile_counters(device, n: int) -> torch.Tensor:
-    """Zeroed int32 counters, one per output tile, that the last-arriver epilogue leaves zeroed."""
-    dev = torch.device(device)
-    t = _TILE_COUNTERS.get(dev)
-    if t is None or t.numel() < n:
-        t = _TILE_COUNTERS[dev] = torch.zeros(max(4096, n), dtype=torch.int32, device=dev)
-    return t
-
-
-_ACCUM_SCRATCH = {}
-
-
-def accum_scratch(device, n: int) -> torch.Tensor:
-    """Float32 scratch for the K splits' tiles, shared by all products of a device (they run one
-    after another on one stream).  A larger request gets a new buffer; the old ones stay alive
-    for recorded launches that still point at them."""
-    dev = torch.device(device)
-    bufs = _ACCUM_SCRATCH.setdefault(dev, [])
-    if not bufs or bufs[-1].numel() < n:
-        bufs.append(torch.empty(max(n, 1 << 22), dtype=torch.float32, device=dev))
-    return bufs[-1]
-
-
 def gemm_tc(x: torch.Tensor, w_map: TensorMap, n_out: int, y: torch.Tensor, mode: int, splits: int = 1,
-            bn: Optional[int] = None, fold=None, scratch: Optional[torch.Tensor] = None) -> torch.Tensor:
+            bn: Optional[int] = None, fold=None, state: Optional[KernelState] = None) -> torch.Tensor:
     """y = x W^T on the tensor cores.  ``w_map`` has boxes of 128 rows; a gated weight holds
     the ``n_out`` gate rows, then the up rows.
 
@@ -320,8 +383,8 @@ def gemm_tc(x: torch.Tensor, w_map: TensorMap, n_out: int, y: torch.Tensor, mode
     TC_PARTIAL_F32 with ``y`` of shape [splits, tokens, n_out] float32, or
     TC_ACCUM_CLUSTER: ``y += x W^T`` with the product cut into ``splits`` (at most 8) along K,
     the splits running as one thread-block cluster and added up in a fixed order; or
-    TC_ACCUM_LAST: the same sum, but every split leaves its tile in ``scratch`` (float32,
-    ``splits * tokens * n_out`` elements) and the split that finishes last adds them up.
+    TC_ACCUM_LAST: the same sum, but every split leaves its tile in the state's scratch and the
+    split that finishes last adds them up.
     ``fold=(r, partials)``: on the side, ``r += sum_s partials[s]`` (``r`` must not be an
     operand of this product).
     """
@@ -339,84 +402,35 @@ def gemm_tc(x: torch.Tensor, w_map: TensorMap, n_out: int, y: torch.Tensor, mode
             raise KernelError(f"gemm_tc: y {tuple(y.shape)} is not [{m}, {n_out}]")
         ldy, sstride = _rows(y, "y"), 0
     xm = activation_map(x, bn)
-    counters = None
+    st = _state(state, x)
+    counters = scratch = None
     if mode == TC_ACCUM_LAST:
-        _cuda(scratch)
-        if scratch is None or scratch.dtype != torch.float32 or scratch.numel() < splits * m * n_out:
-            raise KernelError("gemm_tc: the last-arriver epilogue needs float32 scratch of splits * tokens * n_out")
-        counters = tile_counters(x.device, -(-n_out // 128) * -(-m // bn))
+        scratch = st.accum_scratch(splits * m * n_out)
+        counters = st.tile_counters(-(-n_out // 128) * -(-m // bn))
     f = _fn("gemm_tc", "skyla_gemm_tc",
             [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int, c_int, c_int, c_int, c_int, c_int,
              c_void_p, c_void_p, c_int64, c_void_p, c_int, c_int64, c_int64, c_int, c_void_p, c_void_p, c_void_p])
     _check("gemm_tc", f(w_map.buf, xm.buf, _ptr(y), ldy, sstride, m, n_out, k, bn, mode, splits,
-                        _ptr(error_flag(x.device)), *_fold_args(fold, m), _ptr(scratch), _ptr(counters), _stream()))
+                        _ptr(st.error_flag), *_fold_args(fold, m), _ptr(scratch), _ptr(counters), _stream()))
     return y
 
 
-def gemm_tc_norm(x: torch.Tensor, partials: Optional[torch.Tensor], norm_weight: torch.Tensor, eps: float,
-                 w_map: TensorMap, n_out: int, y: torch.Tensor, mode: int, splits: int = 1,
-                 ssq_out: Optional[torch.Tensor] = None, bn: Optional[int] = None) -> torch.Tensor:
-    """y = rmsnorm(x + sum_s partials[s]) W^T with the norm made inside the product.
-
-    ``x`` float32 [tokens, K] (not changed), ``partials`` float32 [s, tokens, K] or ``None``.
-    Modes TC_GLU_BF16 / TC_STORE_*: one K split, the norm's scalar is applied to the result.
-    Mode TC_PARTIAL_F32: ``y`` [splits, tokens, n_out] holds products of the rows *before*
-    their scalar, and ``ssq_out`` [splits, tokens] each split's share of the rows' sums of
-    squares, for the reader to finish (``qk_norm_rope_cache(..., row_ssq=...)``).
-    """
-    _cuda(x, partials, norm_weight, y, ssq_out)
-    m, k = x.shape
-    bn = bn or token_tile(m)
-    if bn > 64:
-        raise KernelError("gemm_tc_norm: at most 64 tokens")
-    if x.dtype != torch.float32 or norm_weight.dtype != torch.float32 or norm_weight.numel() != k:
-        raise KernelError("gemm_tc_norm: float32 x and a float32 norm weight of its width")
-    n_part, pstride, ldp = 0, 0, 0
-    if partials is not None:
-        if (partials.dtype != torch.float32 or partials.dim() != 3 or not partials.is_contiguous()
-                or tuple(partials.shape[1:]) != (m, k)):
-            raise KernelError("gemm_tc_norm: partial sums must be contiguous float32 [splits, tokens, K]")
-        n_part, pstride, ldp = partials.shape[0], partials.stride(0), partials.stride(1)
-    want = {TC_STORE_BF16: torch.bfloat16, TC_GLU_BF16: torch.bfloat16}.get(mode, torch.float32)
-    if y.dtype != want:
-        raise KernelError(f"gemm_tc_norm: epilogue {mode} writes {want}, y is {y.dtype}")
-    if mode == TC_PARTIAL_F32:
-        if tuple(y.shape) != (splits, m, n_out) or not y.is_contiguous():
-            raise KernelError(f"gemm_tc_norm: partial output must be contiguous [{splits}, {m}, {n_out}]")
-        if ssq_out is None or ssq_out.dtype != torch.float32 or tuple(ssq_out.shape) != (splits, m) or not ssq_out.is_contiguous():
-            raise KernelError(f"gemm_tc_norm: ssq_out must be contiguous float32 [{splits}, {m}]")
-        ldy, sstride = n_out, m * n_out
-    else:
-        if tuple(y.shape) != (m, n_out):
-            raise KernelError(f"gemm_tc_norm: y {tuple(y.shape)} is not [{m}, {n_out}]")
-        ldy, sstride = _rows(y, "y"), 0
-    f = _fn("gemm_tc", "skyla_gemm_tc_norm",
-            [c_void_p, c_void_p, c_int64, c_void_p, c_int, c_int64, c_int64, c_void_p, c_float, c_void_p,
-             c_void_p, c_int64, c_int64, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
-    _check("gemm_tc", f(w_map.buf, _ptr(x), _rows(x, "x"), _ptr(partials), n_part, pstride, ldp, _ptr(norm_weight),
-                        float(eps), _ptr(ssq_out), _ptr(y), ldy, sstride, m, n_out, k, bn, mode, splits,
-                        _ptr(error_flag(x.device)), _stream()))
-    return y
-
-
-N_SMS = 148
-ROWS_TIMELINE = None  # {"buf": int64 [launches, blocks, 12], "n": 0, "log": []} while tuning
 ROWS_MAX_TOKENS = 64
 ROWS_MAX_SPLITS = 8
 
 
-def rows_plan(n_out: int, n_in: int, gated: bool = False, bn: int = 16):
+def rows_plan(n_out: int, n_in: int, gated: bool = False, bn: int = 16, n_sms: int = 148):
     """(rows per block, K splits, K blocks per box, K blocks per MMA) for the few-token product
     of a weight [n_out (x2 when gated), n_in] with token tiles of ``bn``.
 
-    The tile height is the smallest multiple of 8 whose tiles fill the SMs in whole waves.
+    The tile height is the smallest multiple of 8 whose tiles fill the ``n_sms`` SMs in whole waves.
     Tiles of at most 64 rows stack 128 / rows K blocks into one MMA, so that a block covers
     all of K without a K split; a box brings about 32 KB of weights (a TMA load costs the
     same 0.16 us whatever it brings).  K that is no multiple of 64 has to do with one K
     block per box (two-dimensional tensor maps).
     """
-    waves = -(-n_out // (N_SMS * 128))
-    rows = -(-n_out // (N_SMS * waves))
+    waves = -(-n_out // (n_sms * 128))
+    rows = -(-n_out // (n_sms * waves))
     rows = min(128, max(8, -(-rows // 8) * 8))
     if n_in % 64:
         return rows, 1, 1, 1
@@ -431,53 +445,31 @@ def rows_plan(n_out: int, n_in: int, gated: bool = False, bn: int = 16):
     return rows, 1, per_box * kstack, kstack
 
 
-def gemm_tc_rows(x: Optional[torch.Tensor], w_map: TensorMap, rows: int, n_out: int, y: torch.Tensor, mode: int,
-                 normed=None, kkb: int = 1, splits: int = 1, kstack: int = 1,
-                 norm_ahead=None, scale_in=None, timeline: Optional[torch.Tensor] = None) -> torch.Tensor:
+def gemm_tc_rows(x: torch.Tensor, w_map: TensorMap, rows: int, n_out: int, y: torch.Tensor, mode: int,
+                 kkb: int = 1, splits: int = 1, kstack: int = 1, norm_ahead=None, scale_in=None,
+                 state: Optional[KernelState] = None) -> torch.Tensor:
     """y = x W^T for at most 64 tokens, streaming the weight: blocks of ``rows`` weight rows
     (a multiple of 8 up to 128), K cut into ``splits`` that meet in a thread-block cluster.
 
     ``w_map`` has boxes of ``rows`` rows and ``kkb`` K blocks, of which one MMA takes ``kstack``
     at once (then ``kstack * rows <= 128``, one split, not gated); a gated weight holds the
-    ``n_out`` gate rows, then the up rows.  ``normed=(x32, partials or None, norm_weight, eps)``
-    instead of ``x``: the token operand is ``rmsnorm(x32 + sum partials) * norm_weight`` made
-    inside the kernel (at most 16 tokens).  Modes TC_STORE_BF16 / TC_STORE_F32 / TC_ACCUM_F32 /
+    ``n_out`` gate rows, then the up rows.  Modes TC_STORE_BF16 / TC_STORE_F32 / TC_ACCUM_F32 /
     TC_GLU_BF16 (one split).
     ``norm_ahead=(w, xw, ssq_parts)`` with TC_ACCUM_F32: ``y`` being the residual stream, also leave
     ``xw = bf16(y_new * w)`` [tokens, n_out] and ``ssq_parts`` [blocks, tokens], every block's share of
     the new rows' sums of squares, for the RMSNorm (weight ``w``) that reads ``y`` next.
     ``scale_in=(ssq_parts, eps)``: ``x`` is such an ``xw``; the result is multiplied by the rows'
-    ``1/sqrt(sum(ssq_parts) / K + eps)``.  ``timeline`` (int64 [blocks, 12], for tuning): every block leaves its SM's
-    number and clock readings at its phases (start, set up, dependency met, first data, last MMA
-    issued, accumulator complete, end).
+    ``1/sqrt(sum(ssq_parts) / K + eps)``.
     """
     want = {TC_STORE_BF16: torch.bfloat16, TC_GLU_BF16: torch.bfloat16}.get(mode, torch.float32)
     if y.dtype != want:
         raise KernelError(f"gemm_tc_rows: epilogue {mode} writes {want}, y is {y.dtype}")
-    if normed is not None:
-        x32, partials, norm_weight, eps = normed
-        _cuda(x32, partials, norm_weight, y)
-        m, k = x32.shape
-        if x32.dtype != torch.float32 or norm_weight.dtype != torch.float32 or norm_weight.numel() != k or m > 16:
-            raise KernelError("gemm_tc_rows: the in-kernel norm takes float32 rows, a float32 weight of their width, 16 tokens")
-        n_part, pstride, ldp = 0, 0, 0
-        if partials is not None:
-            if (partials.dtype != torch.float32 or partials.dim() != 3 or not partials.is_contiguous()
-                    or tuple(partials.shape[1:]) != (m, k)):
-                raise KernelError("gemm_tc_rows: partial sums must be contiguous float32 [splits, tokens, K]")
-            n_part, pstride, ldp = partials.shape[0], partials.stride(0), partials.stride(1)
-        bn, xm = 16, None
-        nargs = [_ptr(x32), _rows(x32, "x"), _ptr(partials), n_part, pstride, ldp, _ptr(norm_weight), float(eps)]
-        dev = x32.device
-    else:
-        _cuda(x, y)
-        m, k = x.shape
-        if m > ROWS_MAX_TOKENS:
-            raise KernelError(f"gemm_tc_rows: at most {ROWS_MAX_TOKENS} tokens")
-        bn = token_tile(m)
-        xm = activation_map(x, bn, kkb)
-        nargs = [c_void_p(0), 0, c_void_p(0), 0, 0, 0, c_void_p(0), 0.0]
-        dev = x.device
+    _cuda(x, y)
+    m, k = x.shape
+    if m > ROWS_MAX_TOKENS:
+        raise KernelError(f"gemm_tc_rows: at most {ROWS_MAX_TOKENS} tokens")
+    bn = token_tile(m)
+    xm = activation_map(x, bn, kkb)
     if tuple(y.shape) != (m, n_out):
         raise KernelError(f"gemm_tc_rows: y {tuple(y.shape)} is not [{m}, {n_out}]")
     blocks = -(-n_out // rows)
@@ -499,20 +491,10 @@ def gemm_tc_rows(x: Optional[torch.Tensor], w_map: TensorMap, rows: int, n_out: 
             raise KernelError(f"gemm_tc_rows: handed-in sums of squares are float32 [parts, {m}]")
         scale_args = [_ptr(sssq), sssq.shape[0], float(seps)]
     f = _fn("gemm_tc", "skyla_gemm_tc_rows",
-            [c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_int, c_int64, c_int64, c_void_p, c_float,
-             c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
-             c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_float, c_void_p, c_void_p])
-    if timeline is None and ROWS_TIMELINE is not None:  # tuning: every launch leaves its blocks' timeline
-        timeline = ROWS_TIMELINE["buf"][ROWS_TIMELINE["n"]]
-        ROWS_TIMELINE["log"].append((ROWS_TIMELINE["n"], mode, n_out, k, blocks, normed is not None))
-        ROWS_TIMELINE["n"] += 1
-    if timeline is not None:
-        _cuda(timeline)
-        if timeline.dtype != torch.int64 or timeline.numel() < 12 * blocks * splits or not timeline.is_contiguous():
-            raise KernelError("gemm_tc_rows: the timeline is int64 [blocks, 12]")
-    _check("gemm_tc", f(w_map.buf, xm.buf if xm is not None else None, *nargs, _ptr(y), _rows(y, "y"), m, n_out, k, bn,
-                        mode, rows, kkb, kstack, splits, _ptr(error_flag(dev)), *ahead_args, *scale_args,
-                        _ptr(timeline), _stream()))
+            [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+             c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_float, c_void_p])
+    _check("gemm_tc", f(w_map.buf, xm.buf, _ptr(y), _rows(y, "y"), m, n_out, k, bn, mode, rows, kkb, kstack, splits,
+                        _ptr(_state(state, x).error_flag), *ahead_args, *scale_args, _stream()))
     return y
 
 
@@ -524,7 +506,6 @@ TC_QKV_PREP = 4  # gemm_prompt only: the product's heads go through norm and rot
 PROMPT_MIN_TOKENS = 129
 
 
-PROMPT_TMA_ADD = os.environ.get("SKYLA_PROMPT_TMA_ADD", "1") != "0"  # 0: the threads read, add and write y themselves
 _Y_MAPS = {}
 
 
@@ -542,25 +523,10 @@ def _output_map(y: torch.Tensor):
     return buf
 
 
-PROMPT_CUT_K = os.environ.get("SKYLA_PROMPT_CUT_K", "1") != "0"  # 0: few tiles stay whole tiles on few SMs
-_PROMPT_SHARES = {}
-
-
-def _prompt_shares(device):
-    """(scratch for one accumulator tile per SM, a flag per SM, SMs) for ``gemm_prompt``'s tiles that are cut along K."""
-    dev = torch.device(device)
-    t = _PROMPT_SHARES.get(dev)
-    if t is None:
-        n = torch.cuda.get_device_properties(dev).multi_processor_count
-        t = _PROMPT_SHARES[dev] = (torch.empty(n * 128 * 256, dtype=torch.float32, device=dev),
-                                   torch.zeros(n, dtype=torch.int32, device=dev), n)
-    return t
-
-
 def prompt_cut_blocks(m: int, n_out: int, k: int, gated: bool, device) -> int:
     """Over how many blocks ``gemm_prompt`` cuts this product's tiles along K (0: whole tiles)."""
     f = _fn("gemm_prompt", "skyla_gemm_prompt_cut_blocks", [c_int, c_int, c_int, c_int, c_int])
-    return int(f(m, n_out, k, int(gated), _prompt_shares(device)[2])) if PROMPT_CUT_K else 0
+    return int(f(m, n_out, k, int(gated), torch.cuda.get_device_properties(device).multi_processor_count))
 
 
 def prompt_ahead_parts(n_out: int) -> int:
@@ -569,7 +535,8 @@ def prompt_ahead_parts(n_out: int) -> int:
 
 
 def gemm_prompt(x: torch.Tensor, w_map: TensorMap, n_out: int, y: torch.Tensor, mode: int, scale_in=None,
-                norm_ahead=None, prep=None) -> torch.Tensor:
+                norm_ahead=None, prep=None, tma_add: bool = True, cut_k: bool = True,
+                state: Optional[KernelState] = None) -> torch.Tensor:
     """y = x W^T for a prompt's tokens, a token's row of a tile in one thread of the epilogue.
 
     ``w_map`` has boxes of 128 rows; a gated weight holds the ``n_out`` gate rows, then the up rows.
@@ -583,6 +550,8 @@ def gemm_prompt(x: torch.Tensor, w_map: TensorMap, n_out: int, y: torch.Tensor, 
     ``hd``; q and k heads are RMS-normed (weights may be ``None``) and rotated whole (tables may be
     ``None``), the queries go to ``y`` [tokens, nq * hd] bfloat16, keys and values to the tokens' places
     in the pools (``None``: not written).
+    ``tma_add=False``: the accumulate epilogue's threads read, add and write ``y`` themselves (the path
+    that ``y`` without 16-byte rows takes anyway); ``cut_k=False``: few tiles stay whole tiles on few SMs.
     """
     _cuda(x, y)
     m, k = x.shape
@@ -643,7 +612,7 @@ def gemm_prompt(x: torch.Tensor, w_map: TensorMap, n_out: int, y: torch.Tensor, 
         raise KernelError(f"gemm_prompt: y {tuple(y.shape)} is not [{m}, {n_out}]")
     xm = activation_map(x, 128)
     ym = None
-    if (mode == TC_ACCUM_F32 and norm_ahead is None and PROMPT_TMA_ADD and y.data_ptr() % 16 == 0
+    if (mode == TC_ACCUM_F32 and norm_ahead is None and tma_add and y.data_ptr() % 16 == 0
             and _rows(y, "y") % 4 == 0):
         ym = _output_map(y)
     f = _fn("gemm_prompt", "skyla_gemm_prompt",
@@ -651,8 +620,9 @@ def gemm_prompt(x: torch.Tensor, w_map: TensorMap, n_out: int, y: torch.Tensor, 
              c_void_p, c_void_p, c_int64, c_void_p,
              c_int, c_int, c_int, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_void_p,
              c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p])
-    share, flags, n_share = _prompt_shares(x.device) if PROMPT_CUT_K else (None, None, 0)
-    _check("gemm_prompt", f(xm.buf, w_map.buf, ym, _ptr(y), _rows(y, "y"), m, n_out, k, mode, _ptr(error_flag(x.device)),
+    st = _state(state, x)
+    share, flags, n_share = st.prompt_shares() if cut_k else (None, None, 0)
+    _check("gemm_prompt", f(xm.buf, w_map.buf, ym, _ptr(y), _rows(y, "y"), m, n_out, k, mode, _ptr(st.error_flag),
                             *scale_args, *ahead_args, *prep_args, _ptr(share), _ptr(flags), n_share, _stream()))
     return y
 
@@ -767,7 +737,8 @@ def _attn_common(q, out, k_pool, v_pool, nq, nkv, hd, page_size, *ints):
 def attention_decode(q: torch.Tensor, out: torch.Tensor, scratch: torch.Tensor, nq: int, nkv: int, hd: int,
                      k_pool: torch.Tensor, v_pool: torch.Tensor, pages: torch.Tensor, page_size: int,
                      tok_pos: torch.Tensor, scale: float, window: int, n_splits: int,
-                     pages_per_split: int, pages_needed: Optional[torch.Tensor] = None) -> torch.Tensor:
+                     pages_per_split: int, pages_needed: Optional[torch.Tensor] = None,
+                     state: Optional[KernelState] = None) -> torch.Tensor:
     """One new token per sequence (token b belongs to sequence b): split-context attention
     over the cache for all query heads of a key/value head at once, then the merge.
 
@@ -782,11 +753,13 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, scratch: torch.Tensor, 
         raise KernelError("attention_decode: scratch too small")
     f = _fn("attention_mma", "skyla_attention_decode",
             [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
-             c_void_p, c_int, c_int, c_void_p, c_float, c_int, c_int, c_int, c_void_p, c_void_p])
+             c_void_p, c_int, c_int, c_void_p, c_float, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p])
+    counters = _state(state, q).merge_counters()
     _check("attention_mma", f(_ptr(q), _rows(q, "q"), _ptr(out), _rows(out, "out"), _ptr(scratch), n, nq, nkv, hd,
                               _ptr(k_pool), _ptr(v_pool), _ptr(pages), pages.shape[1], page_size, _ptr(tok_pos),
-                              float(scale), int(window or 0), n_splits, pages_per_split, _ptr(pages_needed), _stream()))
-    if tok_pos.numel() * nkv > (1 << 16):
+                              float(scale), int(window or 0), n_splits, pages_per_split, _ptr(pages_needed),
+                              _ptr(counters), counters.numel(), _stream()))
+    if tok_pos.numel() * nkv > counters.numel():
         global LAUNCHES
         LAUNCHES += 1  # the merge kernel, which otherwise is part of the attention kernel
     return out
@@ -799,7 +772,8 @@ def attention_decode_fused(qkv_partials: torch.Tensor, row_ssq: Optional[torch.T
                            nq: int, nkv: int, hd: int, k_pool: torch.Tensor, v_pool: torch.Tensor,
                            pages: torch.Tensor, page_size: int, tok_pos: torch.Tensor, scale: float, window: int,
                            n_splits: int, pages_per_split: int,
-                           pages_needed: Optional[torch.Tensor] = None) -> torch.Tensor:
+                           pages_needed: Optional[torch.Tensor] = None,
+                           state: Optional[KernelState] = None) -> torch.Tensor:
     """Decode attention that also finishes the new token's q, k and v (what
     ``qk_norm_rope_cache`` does) from the K-split partial sums of the QKV product and the
     rows' sums of squares, and writes k and v to the cache.  ``row_ssq=None``: the rows of
@@ -823,15 +797,16 @@ def attention_decode_fused(qkv_partials: torch.Tensor, row_ssq: Optional[torch.T
     f = _fn("attention_mma", "skyla_attention_decode_fused",
             [c_void_p, c_int, c_int64, c_int64, c_int, c_int, c_int, c_void_p, c_int, c_int, c_float, c_void_p, c_void_p,
              c_float, c_void_p, c_void_p, c_int, c_void_p, c_int64, c_void_p, c_int, c_int, c_int, c_int, c_void_p,
-             c_void_p, c_void_p, c_int, c_int, c_void_p, c_float, c_int, c_int, c_int, c_void_p, c_void_p])
+             c_void_p, c_void_p, c_int, c_int, c_void_p, c_float, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p])
+    counters = _state(state, out).merge_counters()
     _check("attention_mma", f(_ptr(qkv_partials), qkv_partials.shape[0], qkv_partials.stride(0), qkv_partials.stride(1),
                               q_off, k_off, v_off, _ptr(row_ssq), row_ssq.shape[0] if row_ssq is not None else 0,
                               int(norm_width), float(norm_eps),
                               _ptr(q_norm), _ptr(k_norm), float(eps), _ptr(cos), _ptr(sin), n_rot if cos is not None else 0,
                               _ptr(out), _rows(out, "out"), _ptr(scratch), n, nq, nkv, hd, _ptr(k_pool), _ptr(v_pool),
                               _ptr(pages), pages.shape[1], page_size, _ptr(tok_pos), float(scale), int(window or 0),
-                              n_splits, pages_per_split, _ptr(pages_needed), _stream()))
-    if tok_pos.numel() * nkv > (1 << 16):
+                              n_splits, pages_per_split, _ptr(pages_needed), _ptr(counters), counters.numel(), _stream()))
+    if tok_pos.numel() * nkv > counters.numel():
         global LAUNCHES
         LAUNCHES += 1  # the merge kernel, which otherwise is part of the attention kernel
     return out
@@ -840,12 +815,12 @@ def attention_decode_fused(qkv_partials: torch.Tensor, row_ssq: Optional[torch.T
 def attention_prefill(q: torch.Tensor, out: torch.Tensor, nq: int, nkv: int, hd: int, k_pool: torch.Tensor,
                       v_pool: torch.Tensor, pages: torch.Tensor, page_size: int, tok_pos: torch.Tensor,
                       tile_seq: torch.Tensor, tile_tok0: torch.Tensor, tile_rows: torch.Tensor, scale: float,
-                      window: int = 0) -> torch.Tensor:
-    """Causal attention of new tokens in tiles of up to 64 tokens of one sequence.  Heads of 128 with an
-    even number of query heads per key/value head run on the tcgen05 kernel (``PREFILL_TC``), the
-    others on the mma.sync one."""
+                      window: int = 0, tcgen05: bool = True, state: Optional[KernelState] = None) -> torch.Tensor:
+    """Causal attention of new tokens in tiles of up to ``PREFILL_TILE`` tokens of one sequence.  Heads of
+    128 with an even number of query heads per key/value head run on the tcgen05 kernel (unless
+    ``tcgen05=False``), the others on the mma.sync one."""
     _attn_common(q, out, k_pool, v_pool, nq, nkv, hd, page_size, pages, tok_pos, tile_seq, tile_tok0, tile_rows)
-    if (PREFILL_TC and hd == 128 and page_size == 64 and (nq // nkv) % 2 == 0 and q.dtype == torch.bfloat16
+    if (tcgen05 and hd == 128 and page_size == 64 and (nq // nkv) % 2 == 0 and q.dtype == torch.bfloat16
             and q.stride(1) == 1 and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0 and q.shape[1] == nq * hd
             and out.stride(0) % 8 == 0 and out.data_ptr() % 16 == 0):
         key = (k_pool.data_ptr(), v_pool.data_ptr(), k_pool.numel())
@@ -862,7 +837,7 @@ def attention_prefill(q: torch.Tensor, out: torch.Tensor, nq: int, nkv: int, hd:
         _check("attention_tc", f(q_map.buf, maps[0].buf, maps[1].buf, _ptr(out), _rows(out, "out"), tile_seq.numel(), nq,
                                  nkv, hd, _ptr(pages), pages.shape[1], page_size, _ptr(tok_pos), _ptr(tile_seq),
                                  _ptr(tile_tok0), _ptr(tile_rows), float(scale), int(window or 0),
-                                 _ptr(error_flag(q.device)), _stream()))
+                                 _ptr(_state(state, q).error_flag), _stream()))
         return out
     f = _fn("attention_mma", "skyla_attention_prefill",
             [c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
@@ -874,15 +849,17 @@ def attention_prefill(q: torch.Tensor, out: torch.Tensor, nq: int, nkv: int, hd:
     return out
 
 
-PREFILL_TC = __import__("os").environ.get("SKYLA_PREFILL_TC", "1") != "0"
+#: the prefill attention kernels work on tiles of this many consecutive new tokens of one sequence
+PREFILL_TILE = 64
 _POOL_MAPS = {}
 
 
 # ------------------------------------------------------------------- sampling
 def sample(logits: torch.Tensor, out: torch.Tensor, temperature: float = 0.0, top_k: int = 0,
            top_p: float = 1.0, seed: int = 0, req_ids: Optional[torch.Tensor] = None,
-           steps: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """One token per row of float32 logits: argmax when ``temperature`` is 0, else a seeded draw."""
+           steps: Optional[torch.Tensor] = None, state: Optional[KernelState] = None) -> torch.Tensor:
+    """One token per row of float32 logits: argmax when ``temperature`` is 0, else a seeded draw.
+    A row in which nothing compares (all NaN) gives token 0 and raises the state's error word."""
     _cuda(logits, out, req_ids, steps)
     _i32(out, "out"); _i32(req_ids, "req_ids"); _i32(steps, "steps")
     if logits.dtype != torch.float32:
@@ -892,10 +869,10 @@ def sample(logits: torch.Tensor, out: torch.Tensor, temperature: float = 0.0, to
         raise KernelError("sample: output too small")
     f = _fn("sampling", "skyla_sample",
             [c_void_p, c_int64, c_int, c_int, c_float, c_int, c_float, c_uint64, c_void_p, c_void_p,
-             c_void_p, c_void_p])
+             c_void_p, c_void_p, c_void_p])
     _check("sampling", f(_ptr(logits), _rows(logits, "logits"), n, vocab, float(temperature),
                          int(top_k), float(top_p), int(seed) & 0xFFFFFFFFFFFFFFFF, _ptr(req_ids),
-                         _ptr(steps), _ptr(out), _stream()))
+                         _ptr(steps), _ptr(out), _ptr(_state(state, logits).error_flag), _stream()))
     return out
 
 

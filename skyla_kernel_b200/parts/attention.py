@@ -55,6 +55,9 @@ class GQAttention(Part):
         self._fast = 0
         if not rt.full_precision and self.hd % 16 == 0 and 16 <= self.hd <= 128:
             self._fast = 2 if self.nq // self.nkv <= 16 else 1
+        #: the prompt attention kernels work on tiles of consecutive new tokens of one sequence; the step's
+        #: batch builder makes the tile lists that the model's mixers ask for here
+        self.token_tiles = (ops.PREFILL_TILE,) if self._fast else ()
         self.qkv: Optional[Linear] = None
         self.q_only: Optional[Linear] = None
         self.out: Optional[Linear] = None
@@ -98,17 +101,18 @@ class GQAttention(Part):
     def decode_splits(self, n_seqs: int, max_pages: int):
         """Into how many blocks a decode step cuts each sequence's context: (splits, pages per split).
 
-        Two blocks share an SM (296 at a time); a block costs about three pages' time beside its
+        Two blocks share an SM; a block costs about three pages' time beside its
         pages, and every split about 0.3 more in the merge (fitted to measurements at batch 1 to
         64: a page takes about 1 us, a block's start and end 3.5, a split 0.3).  The count is fixed
         per (batch, page-list width) so that a recorded launch keeps its grid; how many pages a
         split covers follows the step's longest sequence, which the kernel reads from device memory.
         """
         items = max(1, self.nkv * n_seqs)
+        resident = 2 * self.rt.sm_count
         typical = max(1.0, 0.75 * max_pages)
         best, best_cost = 1, None
         for n in range(1, max(1, min(32, max_pages // 2)) + 1):
-            cost = -(-items * n // 296) * (3.0 + typical / n) + 0.3 * n
+            cost = -(-items * n // resident) * (3.0 + typical / n) + 0.3 * n
             if best_cost is None or cost < best_cost:
                 best, best_cost = n, cost
         return best, -(-max_pages // best)
@@ -122,7 +126,7 @@ class GQAttention(Part):
     # --------------------------------------------------------------------- step
     def forward(self, ctx, h, x: torch.Tensor, entry) -> None:
         n = ctx.n_tokens
-        normed = None
+        state = self.rt.kernel_state
         # few tokens: the QKV product leaves whole float32 rows, which the kernels after it finish
         few = (entry.owns_cache and n <= self.qkv.STACKED_MAX_TOKENS and self.qkv.tensor_cores
                and self.rt.act_dtype == torch.bfloat16)
@@ -130,10 +134,8 @@ class GQAttention(Part):
         if isinstance(h, NormedInput):
             if ((few or (entry.owns_cache and self.qkv.prompts(n))) and h.ahead is not None
                     and ops.tc_linear_ok(h.ahead[0], self.qkv.weight)):
-                scale_in = (h.ahead[1], h.norm.eps)  # the product that wrote x last left x * norm weight
+                scale_in = (h.ahead[1], h.norm.rms_scale_form()[1])  # the product that wrote x last left x * norm weight
                 h = h.ahead[0]
-            elif few and self.qkv.can_fuse_norm(h):
-                normed = h  # the norm is made inside the QKV product
             else:
                 h = h.tensor()
         nq, nkv, hd = self.nq, self.nkv, self.hd
@@ -145,10 +147,7 @@ class GQAttention(Part):
             cos, sin, n_rot = self.position.tables(ctx.max_position + 1)
         if few:
             whole = ctx.buffer("attn.qkv32", (1, n, (nq + 2 * nkv) * hd), torch.float32)
-            if normed is not None:
-                self.qkv.forward_normed(normed, ctx, whole[0])
-            else:
-                self.qkv.forward(h, whole[0], STORE, scale_in=scale_in)
+            self.qkv.forward(h, whole[0], STORE, scale_in=scale_in)
             ctx.mark("matvec qkv")
             pend = ctx.take_pending()
             if (pend is None and self._fast == 2 and ctx.is_decode and k_pool.dtype == torch.bfloat16
@@ -160,7 +159,7 @@ class GQAttention(Part):
                 ops.attention_decode_fused(whole, None, 0, 0.0, 0, nq * hd, (nq + nkv) * hd,
                                            self.q_norm_w, self.k_norm_w, self.eps, cos, sin, n_rot, attn, scratch,
                                            nq, nkv, hd, k_pool, v_pool, pages, ctx.page_size, ctx.tok_pos,
-                                           self.scale, self.window, n_splits, per, ctx.pages_needed)
+                                           self.scale, self.window, n_splits, per, ctx.pages_needed, state=state)
                 ctx.mark("attention")
                 self.out.forward(attn, x, ACCUMULATE, ctx=ctx)
                 ctx.mark("matvec o")
@@ -210,10 +209,11 @@ class GQAttention(Part):
             n_splits, per = self.decode_splits(ctx.n_seqs, pages.shape[1])
             scratch = ctx.buffer("attn.partials", (n * nq * n_splits * (hd + 2),), torch.float32)
             ops.attention_decode(q, attn, scratch, nq, nkv, hd, k_pool, v_pool, pages, ctx.page_size,
-                                 ctx.tok_pos, self.scale, self.window, n_splits, per, ctx.pages_needed)
+                                 ctx.tok_pos, self.scale, self.window, n_splits, per, ctx.pages_needed, state=state)
         elif fast:
+            tile_seq, tile_tok0, tile_rows = ctx.tiles[ops.PREFILL_TILE]
             ops.attention_prefill(q, attn, nq, nkv, hd, k_pool, v_pool, pages, ctx.page_size, ctx.tok_pos,
-                                  ctx.tile_seq, ctx.tile_tok0, ctx.tile_rows, self.scale, self.window)
+                                  tile_seq, tile_tok0, tile_rows, self.scale, self.window, state=state)
         else:
             ops.attention_plain(q, attn, nq, nkv, hd, k_pool, v_pool, pages, ctx.page_size, ctx.tok_pos,
                                 ctx.tok_seq, self.scale, self.window)

@@ -47,6 +47,9 @@ class Runtime:
 
     device: torch.device
     dtype: str = "bfloat16"
+    #: streaming multiprocessors of the device; asked from the device when not given (a runtime on
+    #: a device without them, as the dispatch tests build, has to say which machine it stands for)
+    n_sms: Optional[int] = None
 
     def __post_init__(self):
         if self.dtype in ("fp32", "float"):
@@ -58,6 +61,24 @@ class Runtime:
         self.device = torch.device(self.device)
         self._placed = {}
         self.shared_parts = {}
+        self._kernel_state = None
+
+    @property
+    def sm_count(self) -> int:
+        if self.n_sms is None:
+            if self.device.type != "cuda":
+                raise ValueError("a runtime that is not on a CUDA device must be given its number of SMs")
+            self.n_sms = torch.cuda.get_device_properties(self.device).multi_processor_count
+        return self.n_sms
+
+    @property
+    def kernel_state(self):
+        """What this runtime's kernels keep between launches (error word, counters, scratch): one per
+        runtime, that is per engine, so that two engines on one device share nothing."""
+        if self._kernel_state is None:
+            from ..kernels.ops import KernelState
+            self._kernel_state = KernelState(self.device)
+        return self._kernel_state
 
     def forget_host_tensors(self) -> None:
         """Drop the host-to-device placement table once a model is loaded."""

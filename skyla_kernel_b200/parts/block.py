@@ -1,6 +1,13 @@
 """Arrangements of a layer's parts.
 
-``prenorm_residual``: ``x += mixer(norm_a(x)); x += feed_forward(norm_b(x))``
+A block class takes a :class:`~skyla_kernel_b200.config.LayerSpec`, reads from its ``parts`` the
+names it wants (each from the registry it chooses) and runs them on the residual stream.  What the
+model asks of a block: ``declare(layer_spec)``, ``load(tensors)``, ``forward(ctx, x, entry)``,
+``parts()``, ``kernels_needed()``, ``weight_bytes()``, ``cache_need()`` and ``state_need()`` (what a
+run of the layer keeps in the cache: ``None`` for a block without a mixer), and optionally
+``first_norm`` (the norm that reads ``x`` first, for the block before it).
+
+``prenorm_residual``: ``x += mixer(mixer_norm(x)); x += feed_forward(ffn_norm(x))``
 (skyla-ref/src/model.rs:104-115).  The residual stream ``x`` is 32-bit in every
 precision; the mixer and the feed-forward add into it themselves, in the epilogue
 of their last matrix product.
@@ -24,24 +31,29 @@ class EntryBinding:
     owns_cache: bool = True
 
 
-class PrenormResidualBlock:
+class Block:
+    """Base of the arrangements: builds the parts that ``PARTS`` names from the layer's spec and does
+    the housekeeping; a subclass says which parts it wants and how a step runs through them."""
+
+    #: (name in ``LayerSpec.parts``, registry it comes from) of every part, in the order they load
+    PARTS = ()
+    #: name of the part whose cache and state needs are the layer's (``None``: the layer keeps nothing)
+    CACHING_PART = "mixer"
+
     def __init__(self, layer_spec, rt):
         self.spec = layer_spec
         self.rt = rt
-        self.mixer_norm = build_part("norm", layer_spec.mixer_norm, rt)
-        self.mixer = build_part("mixer", layer_spec.mixer, rt)
-        self.ffn_norm = build_part("norm", layer_spec.ffn_norm, rt)
-        self.feed_forward = build_part("feed_forward", layer_spec.feed_forward, rt)
+        for name, category in self.PARTS:
+            setattr(self, name, build_part(category, layer_spec.part(name), rt))
 
     def parts(self):
-        return (self.mixer_norm, self.mixer, self.ffn_norm, self.feed_forward)
+        return tuple(getattr(self, name) for name, _ in self.PARTS)
 
     @classmethod
     def declare(cls, layer_spec):
         d = {}
-        for cat, spec in (("norm", layer_spec.mixer_norm), ("mixer", layer_spec.mixer),
-                          ("norm", layer_spec.ffn_norm), ("feed_forward", layer_spec.feed_forward)):
-            d.update(declare_part(cat, spec))
+        for name, category in cls.PARTS:
+            d.update(declare_part(category, layer_spec.part(name)))
         return d
 
     def load(self, tensors) -> None:
@@ -56,6 +68,21 @@ class PrenormResidualBlock:
 
     def weight_bytes(self) -> int:
         return sum(p.weight_bytes() for p in self.parts())
+
+    def cache_need(self):
+        part = getattr(self, self.CACHING_PART, None) if self.CACHING_PART else None
+        return part.cache_need() if part is not None else None
+
+    def state_need(self):
+        part = getattr(self, self.CACHING_PART, None) if self.CACHING_PART else None
+        return part.state_need() if part is not None else None
+
+    def forward(self, ctx, x, entry: EntryBinding) -> None:
+        raise NotImplementedError
+
+
+class PrenormResidualBlock(Block):
+    PARTS = (("mixer_norm", "norm"), ("mixer", "mixer"), ("ffn_norm", "norm"), ("feed_forward", "feed_forward"))
 
     @property
     def first_norm(self):

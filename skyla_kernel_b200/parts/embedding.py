@@ -39,7 +39,7 @@ class TokenEmbedding(Part):
         return self.weight.numel() * self.weight.element_size()
 
     def forward(self, ctx, tokens: torch.Tensor, x: torch.Tensor) -> None:
-        ops.embed_gather(tokens, self.weight, x)
+        ops.embed_gather(tokens, self.weight, x, state=self.rt.kernel_state)
 
 
 class LinearHead(Part):

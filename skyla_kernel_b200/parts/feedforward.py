@@ -55,25 +55,16 @@ class SwiGLU(Part):
 
     def forward(self, ctx, h, x: torch.Tensor) -> None:
         act = ctx.buffer("ffn.act", (ctx.n_tokens, self.inter), self.rt.act_dtype)
-        fold = None
         scale_in = None
         if isinstance(h, NormedInput):
             if (h.ahead is not None and self.gate_up.takes_scale_in(ctx.n_tokens)
                     and ops.tc_linear_ok(h.ahead[0], self.gate_up.weight)):
-                scale_in = (h.ahead[1], h.norm.eps)  # the product that wrote x last left x * norm weight
+                scale_in = (h.ahead[1], h.norm.rms_scale_form()[1])  # the product that wrote x last left x * norm weight
                 h = h.ahead[0]
-            elif self.gate_up.can_fuse_norm(h):
-                self.gate_up.forward_normed(h, ctx, act)  # norm, both products and silu(g)*u in one kernel
-                pend = ctx.take_pending()                 # x still lacks these; the down product adds them on the side
-                fold = (x, pend) if pend is not None else None
-                h = None
             else:
                 h = h.tensor()
-        if h is not None:
-            self.gate_up.forward(h, act, GATED, scale_in=scale_in)
+        self.gate_up.forward(h, act, GATED, scale_in=scale_in)
         ctx.mark("matvec gate+up, silu")
-        if fold is not None:
-            ops.fold_partials(*fold)
         self.down.forward(act, x, ACCUMULATE, ctx=ctx)
         ctx.mark("matvec down")
 

@@ -7,8 +7,6 @@ chosen here, never by the caller.
 """
 from __future__ import annotations
 
-import os
-
 import torch
 
 from ..kernels import ops
@@ -37,7 +35,7 @@ class Linear:
         self._map = None
         self._rows_maps = {}
         #: token tile -> (rows per block, K splits, K blocks per box, K blocks per MMA) of the weight-streaming kernel
-        self.rows_plans = {bn: ops.rows_plan(self.n_out, self.n_in, gated, bn) for bn in (16, 32, 64)}
+        self.rows_plans = {bn: ops.rows_plan(self.n_out, self.n_in, gated, bn, rt.sm_count) for bn in (16, 32, 64)}
         self.streams_wide = self.rows_plans[64][0] > 64  # tall tiles: gated products, many-wave products
         self.tensor_cores = (not rt.full_precision and weight.dtype == torch.bfloat16 and self.n_in % 8 == 0
                              and weight.is_contiguous() and weight.data_ptr() % 16 == 0)
@@ -71,27 +69,28 @@ class Linear:
             w_map = self._rows_maps[(rows, kkb)] = ops.TensorMap(self.weight, rows, kkb)
         return w_map
 
-    def _stream(self, x, y, tc, normed=None, norm_ahead=None, scale_in=None):
-        m = x.shape[0] if x is not None else normed[0].shape[0]
+    def _stream(self, x, y, tc, norm_ahead=None, scale_in=None):
+        m = x.shape[0]
         rows, splits, kkb, kstack = self.rows_plans[ops.token_tile(m)]
-        return ops.gemm_tc_rows(x, self._rows_map(m), rows, self.n_out, y, tc, normed=normed, kkb=kkb, splits=splits,
-                                kstack=kstack, norm_ahead=norm_ahead, scale_in=scale_in)
+        return ops.gemm_tc_rows(x, self._rows_map(m), rows, self.n_out, y, tc, kkb=kkb, splits=splits, kstack=kstack,
+                                norm_ahead=norm_ahead, scale_in=scale_in, state=self.rt.kernel_state)
 
     def _norm_ahead(self, ctx, x, y, parts: int):
         """Buffers for "norm ahead" if this product adds into the residual stream ``y`` and the norm
-        that reads it next is an RMSNorm of its width; the kernel leaves ``parts`` shares of a row's
-        sum of squares (0: it cannot)."""
+        that reads it next says that it has the form ``x * w / sqrt(mean(x^2) + eps)`` over this
+        width (``norm.rms_scale_form()``); the kernel leaves ``parts`` shares of a row's sum of
+        squares (0: it cannot)."""
         norm = getattr(ctx, "next_norm", None) if ctx is not None else None
         if ctx is not None:
             ctx.next_norm = None
         m = x.shape[0]
-        if (norm is None or type(norm).__name__ != "RMSNorm" or not self.NORM_AHEAD or y.dtype != torch.float32
-                or getattr(norm, "weight", None) is None or norm.weight.numel() != self.n_out
-                or self.n_out % 8 or parts < 1):
+        form = getattr(norm, "rms_scale_form", None)
+        form = form() if form is not None else None
+        if form is None or y.dtype != torch.float32 or form[0].numel() != self.n_out or self.n_out % 8 or parts < 1:
             return None, None
         xw = ctx.buffer("x.times_norm_weight", (m, self.n_out), torch.bfloat16)
         ssq = ctx.buffer("x.ssq_shares", (parts, m), torch.float32)
-        return norm, (norm.weight, xw, ssq)
+        return norm, (form[0], xw, ssq)
 
     def forward(self, x: torch.Tensor, y: torch.Tensor, mode: int = STORE, scale_in=None, ctx=None) -> torch.Tensor:
         """``scale_in=(shares of the rows' sums of squares, eps)``: ``x`` is a residual stream times
@@ -113,23 +112,24 @@ class Linear:
                     ctx.ahead = (norm, y, ahead[1], ahead[2])
                 return y
             if self.prompts(m):
-                norm, ahead = (self._norm_ahead(ctx, x, y, ops.prompt_ahead_parts(self.n_out) if self.PROMPT_NORM_AHEAD else 0)
-                               if mode == ACCUMULATE else (None, None))
-                ops.gemm_prompt(x, self.weight_map(), self.n_out, y, tc, scale_in=scale_in, norm_ahead=ahead)
-                if ahead is not None:
-                    ctx.ahead = (norm, y, ahead[1], ahead[2])
+                # (Prompts add into the residual stream by TMA reduce, which never reads it; preparing the next
+                # norm's input on the way would need the rows back in the threads: 106 against 65 us for the O
+                # product of 2,048 tokens of the 8B shape, more than the norm kernel it saves.)
+                if ctx is not None:
+                    ctx.next_norm = None
+                ops.gemm_prompt(x, self.weight_map(), self.n_out, y, tc, scale_in=scale_in, state=self.rt.kernel_state)
                 return y
             if scale_in is not None:
                 raise ValueError("scale_in goes with the weight-streaming and the prompt kernel only (Linear.takes_scale_in)")
             if mode == ACCUMULATE:
                 splits = self.choose_splits(m)
                 if splits > 8:  # more splits than a portable cluster holds: they meet through scratch
-                    scratch = ops.accum_scratch(x.device, splits * m * self.n_out)
                     return ops.gemm_tc(x, self.weight_map(), self.n_out, y, ops.TC_ACCUM_LAST, splits=splits,
-                                       scratch=scratch)
+                                       state=self.rt.kernel_state)
                 if splits > 1:  # few tokens: K is cut across a cluster of blocks so that every SM streams
-                    return ops.gemm_tc(x, self.weight_map(), self.n_out, y, ops.TC_ACCUM_CLUSTER, splits=splits)
-            return ops.gemm_tc(x, self.weight_map(), self.n_out, y, tc)
+                    return ops.gemm_tc(x, self.weight_map(), self.n_out, y, ops.TC_ACCUM_CLUSTER, splits=splits,
+                                       state=self.rt.kernel_state)
+            return ops.gemm_tc(x, self.weight_map(), self.n_out, y, tc, state=self.rt.kernel_state)
         if scale_in is not None:
             raise ValueError("scale_in goes with the weight-streaming and the prompt kernel only (Linear.takes_scale_in)")
         return ops.linear_plain(x, self.weight, y, mode, 0)
@@ -137,10 +137,10 @@ class Linear:
     def forward_heads(self, x: torch.Tensor, q_out: torch.Tensor, prep: dict, scale_in=None) -> torch.Tensor:
         """The product of a fused q/k/v weight whose heads are finished in its epilogue
         (``ops.gemm_prompt`` with TC_QKV_PREP); only where :meth:`prompts` holds."""
-        return ops.gemm_prompt(x, self.weight_map(), self.n_out, q_out, ops.TC_QKV_PREP, scale_in=scale_in, prep=prep)
+        return ops.gemm_prompt(x, self.weight_map(), self.n_out, q_out, ops.TC_QKV_PREP, scale_in=scale_in, prep=prep,
+                               state=self.rt.kernel_state)
 
     # ---- K-split products for small batches
-    N_SMS = 148
     # How the K splits of "y += x W^T" meet: up to 8 splits form a thread-block cluster and add up
     # through distributed shared memory (ops.TC_ACCUM_CLUSTER); more than 8 leave their tiles in
     # scratch and the one that finishes last adds them up (ops.TC_ACCUM_LAST).  Measured at the
@@ -163,7 +163,7 @@ class Linear:
             per = -(-total // s)
             if (s - 1) * per >= total:
                 continue
-            cost = -(-tiles * s // self.N_SMS) * (per + 6)
+            cost = -(-tiles * s // self.rt.sm_count) * (per + 6)
             if best_cost is None or cost < best_cost:
                 best, best_cost = s, cost
         return best
@@ -180,45 +180,9 @@ class Linear:
         if splits <= 1:
             return None
         part = ctx.buffer(name, (splits, m, self.n_out), torch.float32)
-        ops.gemm_tc(x, self.weight_map(), self.n_out, part, ops.TC_PARTIAL_F32, splits=splits, fold=fold)
+        ops.gemm_tc(x, self.weight_map(), self.n_out, part, ops.TC_PARTIAL_F32, splits=splits, fold=fold,
+                    state=self.rt.kernel_state)
         return part
-
-    # ---- the RMSNorm of the input made inside the product
-    FUSED_NORM_MAX_TOKENS = 16  # every block re-reads the rows it normalises: only worth it for few
-    FUSE_NORM = os.environ.get("SKYLA_FUSE_NORM", "0") != "0"   # off: "norm ahead" is cheaper
-    NORM_AHEAD = os.environ.get("SKYLA_NORM_AHEAD", "1") != "0"
-    # Prompts: the sums go into the residual stream by TMA reduce, which never reads it; preparing the
-    # next norm's input on the way would need the rows back in the threads (measured at 2,048 tokens of
-    # the 8B shape: 106 against 65 us for the O product, more than the norm kernel it saves)
-    PROMPT_NORM_AHEAD = os.environ.get("SKYLA_PROMPT_NORM_AHEAD", "0") != "0"
-
-    def can_fuse_norm(self, normed) -> bool:
-        """Whether ``norm(x + pending)`` can be made inside this product: RMSNorm, float32 rows
-        with 16-byte alignment, few tokens, and a weight the tensor-core kernel takes."""
-        x, norm, pend = normed.x, normed.norm, normed.ctx.pending
-        return (self.FUSE_NORM and self.tensor_cores and type(norm).__name__ == "RMSNorm" and x.dtype == torch.float32
-                and x.shape[0] <= self.FUSED_NORM_MAX_TOKENS and x.shape[1] == self.n_in
-                and x.stride(1) == 1 and x.stride(0) % 4 == 0 and x.data_ptr() % 16 == 0
-                and (pend is None or (pend.dim() == 3 and tuple(pend.shape[1:]) == tuple(x.shape))))
-
-    def forward_normed_partial(self, normed, ctx, name: str):
-        """(partial sums [splits, tokens, n_out], row sums of squares [splits, tokens]) of the
-        product of the *un-scaled* normed input; the reader applies the rows' scalars.
-        ``x`` and ``ctx.pending`` are left as they are."""
-        x, norm = normed.x, normed.norm
-        m = x.shape[0]
-        splits = self.choose_splits(m)
-        part = ctx.buffer(name, (splits, m, self.n_out), torch.float32)
-        ssq = ctx.buffer(name + ".ssq", (splits, m), torch.float32)
-        ops.gemm_tc_norm(x, ctx.pending, norm.weight, norm.eps, self.weight_map(), self.n_out, part,
-                         ops.TC_PARTIAL_F32, splits=splits, ssq_out=ssq)
-        return part, ssq
-
-    def forward_normed(self, normed, ctx, y: torch.Tensor) -> torch.Tensor:
-        """``y = f(norm(x + pending) W^T)`` in one kernel (gated or plain store)."""
-        x, norm = normed.x, normed.norm
-        mode = ops.TC_GLU_BF16 if self.gated else (ops.TC_STORE_BF16 if y.dtype == torch.bfloat16 else ops.TC_STORE_F32)
-        return self._stream(None, y, mode, normed=(x, ctx.pending, norm.weight, norm.eps))
 
     def bytes(self) -> int:
         return self.weight.numel() * self.weight.element_size()

@@ -40,6 +40,13 @@ class RMSNorm(Part):
             return ops.add_rmsnorm(x, pending, self.weight, self.eps, out, rows)
         return ops.rmsnorm(x, self.weight, self.eps, out, rows)
 
+    def rms_scale_form(self):
+        """``(weight, eps)``: this norm is ``x * weight / sqrt(mean(x^2) + eps)``, one scalar per row times a
+        fixed vector.  A matrix product may use that: the scalar commutes with the product, so whoever
+        writes ``x`` last can leave ``x * weight`` and the rows' sums of squares for the product that
+        follows the norm ("norm ahead").  A norm of another form does not define this method."""
+        return self.weight, self.eps
+
     def weight_bytes(self) -> int:
         return self.weight.numel() * self.weight.element_size()
 

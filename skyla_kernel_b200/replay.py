@@ -23,8 +23,6 @@ def replay(model: str, dtype: str, out: str, max_tokens: int, device: str = "cud
     import torch
 
     from .engine import Engine, StepItem
-    from .kernels import ops
-
     os.makedirs(out, exist_ok=True)
     engine = Engine.from_folder(model, dtype=dtype, max_tokens=max_tokens, device=device)
     print("[skyla] model ready", file=sys.stderr, flush=True)
@@ -48,7 +46,7 @@ def replay(model: str, dtype: str, out: str, max_tokens: int, device: str = "cud
             arr.tofile(tmp)
             os.replace(tmp, os.path.join(out, f"{step}.f32"))
         torch.cuda.synchronize()  # a fault shows at the step that caused it
-        ops.check_device_errors(engine.rt.device)
+        engine.check_errors()
         for rid in rec.get("end", []):
             if rid in slots:
                 engine.free_slot(slots.pop(rid))

@@ -41,9 +41,12 @@ CHAT_DEFAULTS = SamplingParams(temperature=0.6, top_k=40, top_p=0.95)
 class Sampler:
     kernel_modules = ("sampling",)
 
-    def __init__(self, params: SamplingParams, device):
+    def __init__(self, params: SamplingParams, device, state: Optional["ops.KernelState"] = None):
+        """``state``: the kernel state whose error word is raised when a row of logits offers no token
+        (every logit NaN); the engine's own when an engine samples."""
         self.params = params
         self.device = torch.device(device)
+        self.state = state
 
     def __call__(self, logits: torch.Tensor, req_ids: Sequence[int], steps: Sequence[int]) -> torch.Tensor:
         """int32 tokens ``[rows]`` on the device."""
@@ -51,7 +54,7 @@ class Sampler:
         out = torch.empty(n, dtype=torch.int32, device=self.device)
         p = self.params
         if p.greedy:
-            return ops.sample(logits, out)
+            return ops.sample(logits, out, state=self.state)
         keys = torch.tensor([list(req_ids), list(steps)], dtype=torch.int32).to(self.device)
         return ops.sample(logits, out, p.temperature, p.top_k, p.top_p, p.seed, keys[0].contiguous(),
-                          keys[1].contiguous())
+                          keys[1].contiguous(), state=self.state)

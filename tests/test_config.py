@@ -75,7 +75,7 @@ def test_round_trip_and_folder(tmp_path):
 def test_spec_is_data():
     spec = config_from_dict(config_dict(TINY_B)).to_spec()
     assert len(spec.layers) == 3 and [e.layer for e in spec.schedule] == [0, 1, 2]
-    m = spec.layers[1].mixer
+    m = spec.layers[1].part("mixer")
     assert m.kind == "gqa_attention" and m.params["num_kv_heads"] == 1 and m.params["head_dim"] == 32
     assert m.tensors["q_proj"] == "model.layers.1.self_attn.q_proj.weight"
     assert spec.head.tensors["weight"] == "lm_head.weight"

@@ -198,3 +198,26 @@ def test_pipelined_loop_batches_zero_tokens_and_failures():
     with pytest.raises(RuntimeError, match="boom"):
         generate(f, [Request([1], 9), Request([2], 9)])
     assert f.free == [0, 1, 2, 3] and not f.seqs
+
+
+def test_lockstep_check_tells_a_near_tie_from_a_disagreement():
+    """``skyla run --check`` fails on a top-1 disagreement unless the oracle's two most likely tokens are
+    within two points of probability (the reference's rule, docs/roadmap.md:89-92 and 206-212: "France"
+    0.1799 against "Italy" 0.1680 counted as a near tie)."""
+    import math
+
+    import torch
+
+    from skyla_kernel_b200.cli import judge, near_tie
+    base = torch.full((50,), -4.0)
+    prob = torch.full((50,), (1.0 - 0.1799 - 0.1680) / 48)
+    prob[3], prob[7] = 0.1799, 0.1680
+    tie = torch.log(prob)
+    assert near_tie(tie)
+    moved = tie.clone(); moved[7] += 0.2
+    assert judge(moved, tie)[3] == "near tie" and judge(moved, tie)[:2] == (7, 3)
+    clear = base.clone(); clear[3], clear[7] = 2.0, 1.0
+    assert not near_tie(clear)
+    wrong = clear.clone(); wrong[7] = 2.5
+    assert judge(wrong, clear)[3] == "DISAGREE"
+    assert judge(clear + 0.01, clear)[3] == "" and abs(judge(clear + 0.01, clear)[2] - 0.01) < 1e-6

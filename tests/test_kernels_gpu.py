@@ -429,15 +429,13 @@ def test_attention_prefill_tcgen05_against_mma_sync_and_plain(nq, nkv, window):
     args = (nq, nkv, hd, k_pool, v_pool, table, 64, i32(tok_pos), i32(tile_seq), i32(tile_tok0), i32(tile_rows), scale, window)
     outs = {}
     for tc in (True, False):
-        ops.PREFILL_TC = tc
-        try:
-            out = torch.full((T, nq * hd), float("nan"), dtype=dt, device=DEV)
-            before = ops.LAUNCHES
-            ops.attention_prefill(q, out, *args)
-            assert ops.LAUNCHES == before + 1
-            outs[tc] = out
-        finally:
-            ops.PREFILL_TC = True
+        out = torch.full((T, nq * hd), float("nan"), dtype=dt, device=DEV)
+        before = dict(ops.LAUNCHES_BY_MODULE)
+        ops.attention_prefill(q, out, *args, tcgen05=tc)
+        made = {m: n - before.get(m, 0) for m, n in ops.LAUNCHES_BY_MODULE.items() if n != before.get(m, 0)}
+        tc_takes_it = (nq // nkv) % 2 == 0
+        assert made == ({"attention_tc": 1} if tc and tc_takes_it else {"attention_mma": 1}), made
+        outs[tc] = out
     plain_out = torch.empty_like(outs[True])
     ops.attention_plain(q, plain_out, nq, nkv, hd, k_pool, v_pool, table, 64, i32(tok_pos), i32(tok_seq), scale, window)
     for out in outs.values():
@@ -602,47 +600,6 @@ def test_gemm_tc_rows_store_accumulate_gated(m, n, k, rows, kkb, splits, kstack)
     ops.check_device_errors(DEV)
 
 
-@pytest.mark.parametrize("m,n,k,n_part,rows,kkb,splits,kstack", [
-    (1, 128, 64, 0, 128, 1, 1, 1), (8, 6144, 4096, 0, 48, 2, 1, 1), (5, 250, 264, 2, 16, 1, 2, 1), (16, 257, 1032, 3, 8, 1, 4, 1),
-    (11, 128, 8192, 1, 8, 2, 8, 1), (8, 6144, 4096, 0, 128, 2, 3, 1), (7, 264, 1536, 2, 40, 4, 3, 1),
-    (8, 6144, 4096, 0, 48, 6, 1, 2), (16, 257, 1088, 3, 8, 16, 1, 16), (3, 264, 1536, 2, 40, 9, 1, 3), (8, 4096, 4096, 1, 32, 8, 1, 4)])
-def test_gemm_tc_rows_with_the_norm_inside(m, n, k, n_part, rows, kkb, splits, kstack):
-    ops = _ops()
-    from skyla_kernel_b200.parts.feedforward import fuse_gate_up
-    x = _rand(m, k, seed=71, scale=1.5)
-    part = _rand(n_part, m, k, seed=72, scale=0.5) if n_part else None
-    nw = 1 + 0.2 * _rand(k, seed=73)
-    whole = x.double() + (part.double().sum(0) if n_part else 0)
-    h = plain.rmsnorm(whole.cpu(), nw.double().cpu(), 1e-5)
-    w = _rand(n, k, seed=74, dtype=torch.bfloat16, scale=0.1)
-    ref = h @ w.double().cpu().T
-    y = torch.full((m, n), float("nan"), dtype=torch.float32, device=DEV)
-    x_before = x.clone()
-    ops.gemm_tc_rows(None, ops.TensorMap(w, rows, kkb), rows, n, y, ops.TC_STORE_F32, normed=(x, part, nw, 1e-5),
-                     kkb=kkb, splits=splits, kstack=kstack)
-    assert torch.equal(x, x_before)
-    torch.testing.assert_close(y.double().cpu(), ref, rtol=2e-2, atol=2e-2 * ref.abs().max().item())
-    assert (y.double().cpu() - ref).abs().mean().item() < 4e-3 * ref.abs().max().item()
-    # the same rows through a separate norm kernel and the plain product of the rounded rows
-    hb = torch.empty(m, k, dtype=torch.bfloat16, device=DEV)
-    if n_part:
-        ops.add_rmsnorm(x.clone(), part, nw, 1e-5, hb)
-    else:
-        ops.rmsnorm(x, nw, 1e-5, hb)
-    y2 = torch.empty(m, n, device=DEV)
-    ops.linear_plain(hb, w, y2, ops.STORE)
-    assert (y - y2).abs().max().item() <= 1.2e-2 * ref.abs().max().item()
-    g, u = _rand(n, k, seed=75, dtype=torch.bfloat16, scale=0.1), _rand(n, k, seed=76, dtype=torch.bfloat16, scale=0.1)
-    act = torch.empty(m, n, dtype=torch.bfloat16, device=DEV)
-    kkb = min(kkb, 2)  # the gated product brings two tiles per K block
-    ops.gemm_tc_rows(None, ops.TensorMap(fuse_gate_up(g, u), rows, kkb), rows, n, act, ops.TC_GLU_BF16,
-                     normed=(x, part, nw, 1e-5), kkb=kkb)
-    gd, ud = h @ g.double().cpu().T, h @ u.double().cpu().T
-    ref_act = gd / (1 + torch.exp(-gd)) * ud
-    torch.testing.assert_close(act.double().cpu(), ref_act, rtol=3e-2, atol=3e-2 * ref_act.abs().max().item())
-    ops.check_device_errors(DEV)
-
-
 @pytest.mark.parametrize("m,n,k,rows,kkb,kstack,n2,rows2,kkb2,kstack2", [
     (8, 4096, 4096, 32, 8, 4, 6144, 48, 6, 2), (5, 264, 520, 24, 1, 1, 200, 72, 1, 1), (16, 328, 704, 40, 6, 3, 136, 8, 16, 16),
     (1, 128, 64, 128, 1, 1, 128, 128, 1, 1), (11, 1000, 1536, 56, 4, 2, 520, 88, 2, 1)])
@@ -718,80 +675,6 @@ def test_gemm_tc_rows_refuses():
         ops.TensorMap(_rand(128, 72, seed=3, dtype=torch.bfloat16), 128, 2)
 
 
-# -------------------------------------------- RMSNorm made inside the matrix product
-@pytest.mark.parametrize("m,n,k,n_part", [(1, 128, 64, 0), (8, 384, 4096, 4), (5, 256, 264, 2), (16, 256, 1032, 3),
-                                          (11, 128, 512, 1)])
-def test_gemm_tc_norm_store_and_gated(m, n, k, n_part):
-    ops = _ops()
-    from skyla_kernel_b200.parts.feedforward import fuse_gate_up
-    x = _rand(m, k, seed=71, scale=1.5)
-    part = _rand(n_part, m, k, seed=72, scale=0.5) if n_part else None
-    nw = 1 + 0.2 * _rand(k, seed=73)
-    whole = x.double() + (part.double().sum(0) if n_part else 0)
-    h = plain.rmsnorm(whole.cpu(), nw.double().cpu(), 1e-5)
-    w = _rand(n, k, seed=74, dtype=torch.bfloat16, scale=0.1)
-    ref = h @ w.double().cpu().T
-    y = torch.full((m, n), float("nan"), dtype=torch.float32, device=DEV)
-    x_before = x.clone()
-    ops.gemm_tc_norm(x, part, nw, 1e-5, ops.TensorMap(w, 128), n, y, ops.TC_STORE_F32)
-    assert torch.equal(x, x_before)  # the residual stream is read, not written
-    # the operand is rounded to bfloat16 once (as a separate norm kernel would round it)
-    torch.testing.assert_close(y.double().cpu(), ref, rtol=2e-2, atol=2e-2 * ref.abs().max().item())
-    assert (y.double().cpu() - ref).abs().mean().item() < 4e-3 * ref.abs().max().item()
-    g, u = _rand(n, k, seed=75, dtype=torch.bfloat16, scale=0.1), _rand(n, k, seed=76, dtype=torch.bfloat16, scale=0.1)
-    act = torch.empty(m, n, dtype=torch.bfloat16, device=DEV)
-    ops.gemm_tc_norm(x, part, nw, 1e-5, ops.TensorMap(fuse_gate_up(g, u), 128), n, act, ops.TC_GLU_BF16)
-    gd, ud = h @ g.double().cpu().T, h @ u.double().cpu().T
-    ref_act = gd / (1 + torch.exp(-gd)) * ud
-    torch.testing.assert_close(act.double().cpu(), ref_act, rtol=3e-2, atol=3e-2 * ref_act.abs().max().item())
-    ops.check_device_errors(DEV)
-
-
-@pytest.mark.parametrize("m,k,splits,n_part", [(8, 4096, 3, 4), (3, 264, 2, 0), (16, 1032, 4, 2)])
-def test_gemm_tc_norm_partial_then_prep_and_fold(m, k, splits, n_part):
-    """K-split product of un-scaled rows + shares of the sums of squares, finished by the prep
-    kernel, which also makes the residual stream whole."""
-    ops = _ops()
-    nq, nkv, hd = 4, 2, 32
-    n = (nq + 2 * nkv) * hd
-    x = _rand(m, k, seed=81, scale=1.5)
-    part = _rand(n_part, m, k, seed=82, scale=0.5) if n_part else None
-    nw = 1 + 0.2 * _rand(k, seed=83)
-    w = _rand(n, k, seed=84, dtype=torch.bfloat16, scale=0.1)
-    whole = x.double() + (part.double().sum(0) if n_part else 0)
-    qkv_ref = (plain.rmsnorm(whole.cpu(), nw.double().cpu(), 1e-5) @ w.double().cpu().T).float()
-    y = torch.empty(splits, m, n, dtype=torch.float32, device=DEV)
-    ssq = torch.empty(splits, m, dtype=torch.float32, device=DEV)
-    ops.gemm_tc_norm(x, part, nw, 1e-5, ops.TensorMap(w, 128), n, y, ops.TC_PARTIAL_F32, splits=splits, ssq_out=ssq)
-    torch.testing.assert_close(ssq.sum(0).double().cpu(), (whole.cpu() ** 2).sum(1), rtol=1e-4, atol=1e-4)
-    qn, kn = 1 + 0.2 * _rand(hd, seed=85), 1 + 0.2 * _rand(hd, seed=86)
-    freqs, _ = plain.rope_frequencies(hd, 10000.0)
-    ang = (torch.arange(64, dtype=torch.float32)[:, None] * freqs[None, :]).double()
-    cos, sin = torch.cos(ang).float().to(DEV), torch.sin(ang).float().to(DEV)
-    pos = torch.arange(m, dtype=torch.int32, device=DEV)
-    seq = torch.zeros(m, dtype=torch.int32, device=DEV)
-    table = torch.tensor([[1]], dtype=torch.int32, device=DEV)
-    out = {}
-    for name, src, kw in (("fused", y, dict(row_ssq=ssq, norm_width=k, norm_eps=1e-5,
-                                           fold=(x, part) if n_part else None)),
-                          ("plain", qkv_ref.to(DEV), {})):
-        kp = torch.zeros(2, nkv, 64, hd, dtype=torch.bfloat16, device=DEV)
-        vp = torch.zeros_like(kp)
-        q = torch.zeros(m, nq * hd, dtype=torch.bfloat16, device=DEV)
-        ops.qk_norm_rope_cache(src, 0, nq * hd, (nq + nkv) * hd, nq, nkv, hd, qn, kn, 1e-6, cos, sin, hd, pos, seq,
-                               kp, vp, table, 64, q_out=q, **kw)
-        out[name] = (q, kp, vp)
-    for a, b in zip(out["fused"], out["plain"]):
-        torch.testing.assert_close(a.float(), b.float(), rtol=3e-2, atol=3e-2)
-    if n_part:  # the side job added the partial sums to x, in ascending order
-        want = x_whole = None
-        ref_x = _rand(m, k, seed=81, scale=1.5)
-        for s_ in range(n_part):
-            ref_x += part[s_]
-        assert torch.equal(x, ref_x)
-    ops.check_device_errors(DEV)
-
-
 def test_gemm_tc_fold_side_job():
     ops = _ops()
     m, n, k, hidden = 8, 256, 512, 4096
@@ -818,15 +701,14 @@ def test_gemm_tc_last_arriver_accumulate(m, n, k, splits):
     w = _rand(n, k, seed=96, dtype=torch.bfloat16, scale=0.1)
     acc0 = _rand(m, n, seed=97)
     ref = acc0.double() + x.double() @ w.double().T
-    scratch = torch.full((splits * m * n,), float("nan"), device=DEV)
     runs = []
     for _ in range(3):  # the counters must come back to zero by themselves
         acc = acc0.clone()
-        ops.gemm_tc(x, ops.TensorMap(w, 128), n, acc, ops.TC_ACCUM_LAST, splits=splits, scratch=scratch)
+        ops.gemm_tc(x, ops.TensorMap(w, 128), n, acc, ops.TC_ACCUM_LAST, splits=splits)
         runs.append(acc)
     assert (runs[0].double() - ref).abs().max().item() <= 3e-5 * ref.abs().max().item() + 1e-5
     assert torch.equal(runs[0], runs[1]) and torch.equal(runs[0], runs[2])  # split order, whoever finishes last
-    assert int(ops.tile_counters(DEV, 1).abs().sum()) == 0
+    assert int(ops.default_state(DEV).tile_counters(1).abs().sum()) == 0
     ops.check_device_errors(DEV)
 
 
@@ -930,7 +812,7 @@ def test_gemm_prompt_store_accumulate_gated(m, n, k, cut):
     ops.linear_plain(x, fused, plain_act, ops.GATED)
     torch.testing.assert_close(act.float(), plain_act.float(), rtol=2e-2, atol=1e-3 * max(1.0, k / 512))
     ops.check_device_errors(DEV)
-    assert int(ops._prompt_shares(DEV)[1].abs().sum()) == 0  # every share that was left was taken
+    assert int(ops.default_state(DEV).prompt_shares()[1].abs().sum()) == 0  # every share that was left was taken
 
 
 @pytest.mark.parametrize("m,n,k,n2", [(300, 512, 264, 384), (129, 264, 520, 200), (515, 1000, 128, 136), (300, 512, 12800, 384)])

@@ -13,7 +13,7 @@ def _lin(n_out, n_in, gated=False, dtype="bfloat16"):
     # a meta tensor: only its shape, dtype and (absent) address are looked at
     rows = 2 * n_out if gated else n_out
     w = torch.empty(rows, n_in, dtype=torch.bfloat16 if dtype == "bfloat16" else torch.float32, device="meta")
-    return Linear(w, Runtime(torch.device("cpu"), dtype), gated=gated)
+    return Linear(w, Runtime(torch.device("cpu"), dtype, n_sms=148), gated=gated)  # the machine the decisions are checked for
 
 
 def test_few_tokens_stream_the_weight_and_many_go_to_the_prompt_kernel():
@@ -58,7 +58,7 @@ def test_k_splits_of_small_batches():
 
 def test_rows_plans_fill_the_sms_with_one_wave():
     for n_out, n_in, gated in ((QKV, H, False), (H, H, False), (INTER, H, True), (H, INTER, False), (151936, H, False)):
-        rows, splits, kkb, kstack = ops.rows_plan(n_out, n_in, gated, 16)
+        rows, splits, kkb, kstack = ops.rows_plan(n_out, n_in, gated, 16, 148)
         assert rows % 8 == 0 and 8 <= rows <= 128 and splits == 1
         blocks = -(-n_out // rows)
         if n_out <= 148 * 128:

@@ -24,11 +24,11 @@ def _tensors(decl, seed, std=0.08, sharp=1.0):
     return out
 
 
-def _ctx(rt, needs, states, items, max_tokens=1024):
+def _ctx(rt, needs, states, items, max_tokens=1024, tiles=(64,)):
     from skyla_kernel_b200.cache import SequenceCache
     from skyla_kernel_b200.engine.batch import BatchBuilder
     cache = SequenceCache(needs, states, max_tokens, None, rt.cache_dtype, rt.device)
-    return cache, BatchBuilder(rt, cache)
+    return cache, BatchBuilder(rt, cache, tiles)   # the token tiles that a mixer asks for (Part.token_tiles)
 
 
 def _tol(dtype):
@@ -247,9 +247,10 @@ def test_block_alone(dtype):
     rt = _rt(dtype)
     H, nq, nkv, hd, I = 96, 6, 2, 32, 256
     norm = lambda n: PartSpec("rmsnorm", {"width": H, "eps": 2e-5}, {"weight": n})
-    spec = LayerSpec("l", "prenorm_residual", norm("l.n1"), _attention_spec(H, nq, nkv, hd), norm("l.n2"),
-                     PartSpec("swiglu", {"hidden_size": H, "intermediate_size": I},
-                              {k: f"l.{k}" for k in ("gate_proj", "up_proj", "down_proj")}))
+    spec = LayerSpec("l", "prenorm_residual", {
+        "mixer_norm": norm("l.n1"), "mixer": _attention_spec(H, nq, nkv, hd), "ffn_norm": norm("l.n2"),
+        "feed_forward": PartSpec("swiglu", {"hidden_size": H, "intermediate_size": I},
+                                 {k: f"l.{k}" for k in ("gate_proj", "up_proj", "down_proj")})})
     cls = part_class("block", spec.block)
     w = _tensors(cls.declare(spec), 21, std=0.08, sharp=2.0)
     if dtype == "bfloat16":  # stored in 16 bits, as a served model would be: the tensor-core kernels run
@@ -263,7 +264,7 @@ def test_block_alone(dtype):
     ref = x0 + plain.attention(plain.rmsnorm(x0, wf["l.n1"], 2e-5), wf["a.q_proj"], wf["a.k_proj"], wf["a.v_proj"],
                                wf["a.o_proj"], wf["a.q_norm"], wf["a.k_norm"], nq, nkv, hd, 1e-5, freqs, m, hd)
     ref = ref + plain.swiglu(plain.rmsnorm(ref, wf["l.n2"], 2e-5), wf["l.gate_proj"], wf["l.up_proj"], wf["l.down_proj"])
-    cache, batcher = _ctx(rt, [block.mixer.cache_need()], [None], None)
+    cache, batcher = _ctx(rt, [block.cache_need()], [None], None)
     slot = cache.alloc_slot()
     got = []
     for a, b in ((0, 70), (70, 71), (71, 90)):  # a prompt, one token (the few-token kernels), a second chunk

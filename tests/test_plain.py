@@ -99,3 +99,31 @@ def test_sampling_twin_filters():
         counts[int(np.argmax(s))] += 1
     p = torch.softmax(logits, 0).numpy()
     assert np.abs(counts / 4000 - p).max() < 0.03
+
+
+import pytest
+
+
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_two_independent_restatements_agree(tmp_path, name):
+    """``plain_qwen3`` (whole sequences, torch, a mask) against ``plain_numpy64`` (token by token with
+    a growing cache, 64-bit NumPy, loops), written apart from the same cited lines of the reference:
+    logits and the residual stream after every layer."""
+    import plain_numpy64 as second
+    folder = make_folder(tmp_path, name)
+    cfg, w = plain.read_folder(folder)
+    toks = random_tokens(70 if name != "C" else 90, cfg["vocab_size"], 5)   # C: past YaRN's original 64 positions
+    taps = []
+    ref = plain.forward(cfg, w, toks, dtype=torch.float64, taps=taps)
+    dec = second.Decoder(cfg, {k: v.numpy() for k, v in w.items()})
+    taps2 = []
+    got = np.stack([dec.step(t, taps2) for t in toks])
+    scale = ref.abs().max().item()
+    assert np.abs(got - ref.numpy()).max() / scale < 3e-6     # 32-bit frequencies and angles on both sides
+    L = cfg["num_hidden_layers"]
+    for pos, l, x in taps2:
+        assert np.abs(x - taps[l][pos].numpy()).max() < 3e-6 * max(1.0, taps[l].abs().max().item())
+    assert len(taps2) == L * len(toks)
+    # and the 32-bit run of the first stays within rounding of the 64-bit run of the second
+    ref32 = plain.forward(cfg, w, toks)
+    assert np.abs(got - ref32.numpy().astype(np.float64)).max() / scale < 2e-5

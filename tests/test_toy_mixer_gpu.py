@@ -71,12 +71,13 @@ def _register():
             layers = []
             for i in range(self.num_layers):
                 p = f"layers.{i}"
-                layers.append(LayerSpec(p, "prenorm_residual", norm(f"{p}.n1"),
-                                        PartSpec("toy_decay", {"hidden_size": self.hidden_size, "state_size": self.state_size,
-                                                               "decay": self.decay}, {"w_in": f"{p}.w_in", "w_out": f"{p}.w_out"}),
-                                        norm(f"{p}.n2"),
-                                        PartSpec("swiglu", {"hidden_size": self.hidden_size, "intermediate_size": 2 * self.hidden_size},
-                                                 {k: f"{p}.{k}" for k in ("gate_proj", "up_proj", "down_proj")})))
+                layers.append(LayerSpec(p, "prenorm_residual", {
+                    "mixer_norm": norm(f"{p}.n1"),
+                    "mixer": PartSpec("toy_decay", {"hidden_size": self.hidden_size, "state_size": self.state_size,
+                                                    "decay": self.decay}, {"w_in": f"{p}.w_in", "w_out": f"{p}.w_out"}),
+                    "ffn_norm": norm(f"{p}.n2"),
+                    "feed_forward": PartSpec("swiglu", {"hidden_size": self.hidden_size, "intermediate_size": 2 * self.hidden_size},
+                                             {k: f"{p}.{k}" for k in ("gate_proj", "up_proj", "down_proj")})}))
             return ModelSpec("ToyDecayLM", self.vocab_size, self.hidden_size, 1 << 20,
                              PartSpec("token_embedding", {"vocab_size": self.vocab_size, "hidden_size": self.hidden_size}, {"weight": "embed"}),
                              layers, [ScheduleEntry(i) for i in range(self.num_layers)], norm("final"),

@@ -114,3 +114,34 @@ def test_integer_tables_and_float_kinds(tmp_path):
     assert w["t"].dtype == torch.int32 and w["h"].dtype == torch.bfloat16
     with pytest.raises(WeightError, match="integer table"):
         load_weights(str(tmp_path), {"h": TensorDecl((2,), "int"), "t": TensorDecl((4,), "int")})
+
+
+def test_sharded_folder_with_an_index(tmp_path):
+    """A checkpoint in several files: ``model.safetensors.index.json`` names, for every tensor, the
+    file that holds it; the loader reads the files the index lists and checks the union."""
+    folder, cfg = _folder(tmp_path, TINY_B, "bfloat16", 2)
+    decl = declared_tensors(cfg.to_spec())
+    whole = load_weights(folder, decl)
+    names = sorted(whole)
+    shards = {"model-00001-of-00003.safetensors": names[0::3], "model-00002-of-00003.safetensors": names[1::3],
+              "model-00003-of-00003.safetensors": names[2::3]}
+    sharded = tmp_path / "sharded"
+    os.makedirs(sharded)
+    with open(os.path.join(folder, "config.json")) as f, open(sharded / "config.json", "w") as g:
+        g.write(f.read())
+    weight_map = {}
+    for fname, ns in shards.items():
+        write_safetensors(str(sharded / fname), {n: whole[n] for n in ns})
+        weight_map.update({n: fname for n in ns})
+    with open(sharded / "model.safetensors.index.json", "w") as f:
+        json.dump({"metadata": {}, "weight_map": weight_map}, f)
+    # a stray file that the index does not list is not read
+    write_safetensors(str(sharded / "stray.safetensors"), {"not.a.weight": torch.zeros(2)})
+    got = load_weights(str(sharded), decl)
+    assert sorted(got) == names and all(torch.equal(got[n], whole[n]) for n in names)
+    # a tensor lost with its shard is reported by name, among all the missing ones
+    os.remove(sharded / "model-00002-of-00003.safetensors")
+    write_safetensors(str(sharded / "model-00002-of-00003.safetensors"), {n: whole[n] for n in names[1::3][1:]})
+    with pytest.raises(WeightError) as e:
+        load_weights(str(sharded), decl)
+    assert names[1] in str(e.value) and "missing tensors (1)" in str(e.value)

@@ -45,25 +45,36 @@ def test_no_alloc_entry_point_matches_the_ordinary_one_twice_in_a_row():
     lib, f = _lib()
     stream = c_void_p(torch.cuda.current_stream().cuda_stream)
     # two different problems in a row: the second must not be disturbed by what the first left in the array
-    for call, (B, nq, nkv, hd, lens, n_splits, per) in enumerate([
-            (5, 8, 2, 128, [1, 64, 65, 300, 777], 4, 4),
-            (3, 6, 1, 32, [500, 17, 129], 2, 4)]):
+    # (the third looks back over a window only; the fourth has more (sequence, head) pairs than the entry
+    # point has counters, so its splits are merged by the second kernel)
+    for call, (B, nq, nkv, hd, lens, n_splits, per, window) in enumerate([
+            (5, 8, 2, 128, [1, 64, 65, 300, 777], 4, 4, 0),
+            (3, 6, 1, 32, [500, 17, 129], 2, 4, 0),
+            (4, 4, 2, 64, [700, 90, 257, 64], 3, 4, 130),
+            (700, 8, 8, 16, [1 + (37 * i) % 190 for i in range(700)], 2, 2, 0)]):
         q, k_pool, v_pool, pages, tok_pos, width = _problem(B, nq, nkv, hd, lens, 90 + call)
         scale = 1.0 / math.sqrt(hd)
         want = torch.empty(B, nq * hd, dtype=torch.bfloat16, device=DEV)
         scratch = torch.empty(B * nq * n_splits * (hd + 2), dtype=torch.float32, device=DEV)
-        ops.attention_decode(q, want, scratch, nq, nkv, hd, k_pool, v_pool, pages, 64, tok_pos, scale, 0, n_splits, per)
+        ops.attention_decode(q, want, scratch, nq, nkv, hd, k_pool, v_pool, pages, 64, tok_pos, scale, window, n_splits, per)
         got = torch.full_like(want, float("nan"))
+        args = (q.data_ptr(), q.stride(0), got.data_ptr(), got.stride(0), B, nq, nkv, hd, k_pool.data_ptr(),
+                v_pool.data_ptr(), pages.data_ptr(), width, 64, tok_pos.data_ptr(), scale, window, n_splits, per, stream)
+        # one warm call: the first call on a device looks up the array's address, and the driver loads a
+        # kernel's code when it is first launched; memory is compared around the call after it
+        assert f(*args) == 0, lib.skyla_error_message().decode()
+        got.fill_(float("nan"))
         torch.cuda.synchronize()
-        before = torch.cuda.memory_allocated()
-        rc = f(q.data_ptr(), q.stride(0), got.data_ptr(), got.stride(0), B, nq, nkv, hd, k_pool.data_ptr(),
-               v_pool.data_ptr(), pages.data_ptr(), width, 64, tok_pos.data_ptr(), scale, 0, n_splits, per, stream)
+        # the driver's own count of free memory sees every allocation on the device, whoever makes it
+        before, before_torch = torch.cuda.mem_get_info()[0], torch.cuda.memory_allocated()
+        rc = f(*args)
         assert rc == 0, lib.skyla_error_message().decode()
         torch.cuda.synchronize()
-        assert torch.cuda.memory_allocated() == before
+        assert torch.cuda.mem_get_info()[0] == before and torch.cuda.memory_allocated() == before_torch
         # the same kernels on the same inputs: the same bits; the suite's bf16 tolerance is the stated bound
         torch.testing.assert_close(got.float(), want.float(), rtol=2e-2, atol=2e-2)
-        assert torch.equal(got, want)
+        if B * nkv <= 4096:  # merged inside the kernel on both sides: the same arithmetic
+            assert torch.equal(got, want)
 
 
 def test_no_alloc_entry_point_refuses_what_does_not_fit():
