@@ -31,10 +31,15 @@ class _Captured:
 
 
 class DecodeGraphs:
+    #: graphs kept at a time; each owns its arrays, its workspace and a [batch, vocabulary] logits
+    #: buffer, so a batch that shrinks from 64 to 1 across several widths must not keep them all for ever
+    MAX_GRAPHS = 24
+
     def __init__(self, model, rt, cache):
         self.model, self.rt, self.cache = model, rt, cache
-        self._graphs: Dict[Tuple[int, int], _Captured] = {}
+        self._graphs: Dict[Tuple[int, int], _Captured] = {}  # in order of last use
         self.replays = 0
+        self.captures = 0
 
     def run(self, items: List[StepItem]) -> torch.Tensor:
         """``items``: one token each, logits wanted for it.  Returns the graph's own
@@ -44,10 +49,15 @@ class DecodeGraphs:
         pages = max(-(-(self.cache.length(it.slot) + 1) // self.cache.page_size) for it in items)
         width = page_bucket(pages)
         key = (B, width)
-        cap = self._graphs.get(key)
+        cap = self._graphs.pop(key, None)
         if cap is None:
+            while len(self._graphs) >= self.MAX_GRAPHS:  # the one used longest ago goes
+                old = self._graphs.pop(next(iter(self._graphs)))
+                torch.cuda.synchronize(self.rt.device)    # it may still be running
+                del old
             cap = self._capture(items, width)
-            self._graphs[key] = cap
+            self.captures += 1
+        self._graphs[key] = cap
         cap.batcher.build(items, pages_width=width)  # refills the static arrays
         cap.graph.replay()
         self.replays += 1

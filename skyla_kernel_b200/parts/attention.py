@@ -11,7 +11,10 @@ does with its ACCUM matvec, skyla-engine/src/graph.rs:110-112).
 
 Parameters: ``hidden_size``, ``num_heads``, ``num_kv_heads``, ``head_dim``,
 ``qk_norm``, ``qk_norm_eps``, ``scale`` (``None``: ``1/sqrt(head_dim)``),
-``window`` (``None``: all earlier positions), ``position`` (a position part spec).
+``window`` (``None``: all earlier positions), ``position`` (a position part spec),
+``cache_dtype`` (``None``: the runtime's; ``"float32"`` keeps this mixer's keys and values
+in 32-bit even where activations are 16-bit: its layers then form a cache group of
+their own and run on the plain kernels).
 The three input projections are stored as one matrix so that a step needs one
 product for them.
 """
@@ -47,6 +50,10 @@ class GQAttention(Part):
         self.eps = float(p.get("qk_norm_eps", 0.0))
         self.scale = float(p["scale"]) if p.get("scale") is not None else 1.0 / math.sqrt(self.hd)
         self.window = int(p["window"]) if p.get("window") else 0
+        cdt = p.get("cache_dtype")
+        if cdt not in (None, "float32", "bfloat16"):
+            raise ValueError(f"cache_dtype must be float32 or bfloat16, not {cdt!r}")
+        self.cache_dtype = None if cdt is None else getattr(torch, cdt)
         pos = p.get("position")
         self.position = build_part("position", pos, rt) if pos is not None else None
         self.q_norm_w = self.k_norm_w = None
@@ -118,7 +125,7 @@ class GQAttention(Part):
         return best, -(-max_pages // best)
 
     def cache_need(self) -> Optional[KVNeed]:
-        return KVNeed(self.nkv, self.hd, self.window or None)
+        return KVNeed(self.nkv, self.hd, self.window or None, self.cache_dtype)
 
     def state_need(self):
         return None

@@ -118,3 +118,13 @@ def test_state_area_is_zeroed_on_alloc():
     c.free_slot(s)
     assert c.alloc_slot() == s
     assert torch.equal(c.state_of_entry(0)[s], torch.zeros(4))
+
+
+def test_needs_that_differ_only_in_precision_get_storage_of_their_own():
+    import torch
+    needs = [KVNeed(2, 16), KVNeed(2, 16, None, torch.float32), KVNeed(2, 16)]
+    c = SequenceCache(needs, [None] * 3, 256, None, torch.bfloat16, "cpu")
+    assert len(c.groups) == 2 and sorted(g.n_layers for g in c.groups) == [1, 2]
+    assert {g.k.dtype for g in c.groups} == {torch.bfloat16, torch.float32}
+    assert c.entry_group[0][0] == c.entry_group[2][0] != c.entry_group[1][0]
+    assert c.bytes_per_token() == 2 * 2 * 16 * (2 * 2 + 1 * 4)

@@ -66,26 +66,27 @@ def test_rotary_tables(scaling):
     torch.testing.assert_close(sin.cpu(), (torch.sin(ang) * m).float(), rtol=0, atol=1e-6)
 
 
-def _attention_spec(hidden, nq, nkv, hd, n_rot=None, window=None, qk_norm=True, scale=None):
+def _attention_spec(hidden, nq, nkv, hd, n_rot=None, window=None, qk_norm=True, scale=None, cache_dtype=None):
     from skyla_kernel_b200.config import PartSpec
     rope = PartSpec("rotary_neox", {"n_rot": n_rot or hd, "theta": 10000.0, "max_positions": 64, "scaling": None})
     return PartSpec("gqa_attention", {"hidden_size": hidden, "num_heads": nq, "num_kv_heads": nkv, "head_dim": hd,
                                       "qk_norm": qk_norm, "qk_norm_eps": 1e-5, "scale": scale, "window": window,
-                                      "position": rope},
+                                      "position": rope, "cache_dtype": cache_dtype},
                     {k: f"a.{k}" for k in ("q_proj", "k_proj", "v_proj", "o_proj", "q_norm", "k_norm")})
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("hidden,nq,nkv,hd,n_rot,window,qk_norm,scale", [
-    (80, 5, 5, 16, 16, None, True, None),
-    (96, 6, 2, 48, 24, None, True, 0.3),     # partial rotation, own scale
-    (64, 4, 1, 32, 32, 40, False, None),      # a window, no q/k norm
+@pytest.mark.parametrize("hidden,nq,nkv,hd,n_rot,window,qk_norm,scale,cache_dtype", [
+    (80, 5, 5, 16, 16, None, True, None, None),
+    (96, 6, 2, 48, 24, None, True, 0.3, None),     # partial rotation, own scale
+    (64, 4, 1, 32, 32, 40, False, None, None),      # a window, no q/k norm
+    (96, 6, 2, 32, 32, None, True, None, "float32"),  # keys and values kept in 32-bit whatever the activations are
 ])
-def test_attention_part_whole_then_one_by_one(dtype, hidden, nq, nkv, hd, n_rot, window, qk_norm, scale):
+def test_attention_part_whole_then_one_by_one(dtype, hidden, nq, nkv, hd, n_rot, window, qk_norm, scale, cache_dtype):
     from skyla_kernel_b200.engine.batch import StepItem
     from skyla_kernel_b200.parts import EntryBinding, build_part, declare_part
     rt = _rt(dtype)
-    spec = _attention_spec(hidden, nq, nkv, hd, n_rot, window, qk_norm, scale)
+    spec = _attention_spec(hidden, nq, nkv, hd, n_rot, window, qk_norm, scale, cache_dtype)
     part = build_part("mixer", spec, rt)
     w = _tensors(declare_part("mixer", spec), 3, sharp=2.0)
     part.load(w)
@@ -96,6 +97,7 @@ def test_attention_part_whole_then_one_by_one(dtype, hidden, nq, nkv, hd, n_rot,
                           w["a.q_norm"] if qk_norm else None, w["a.k_norm"] if qk_norm else None,
                           nq, nkv, hd, 1e-5, freqs, m, n_rot, scale=scale, window=window)
     cache, batcher = _ctx(rt, [part.cache_need()], [None], None)
+    assert cache.groups[0].k.dtype == (torch.float32 if cache_dtype == "float32" else rt.cache_dtype)
     slot = cache.alloc_slot()
     got = []
     for a, b in [(0, 100)] + [(i, i + 1) for i in range(100, T)]:
