@@ -1,12 +1,15 @@
 """Decode and prefill throughput of the Qwen3-8B-shaped model with random weights.
 
-    python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--layers L]
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--layers L] [--shape 8b|4b|32b]
+    python bench.py --shape 4b --workload unequal16     (16 unequal prompts, 256 sampled tokens, checked)
 
 One "step" is one decode step of the batch.  Prints ONE JSON line: decoded tokens
 per second on the device (`value`), the same through the Python entry point with
 host tokens in and out (`e2e`), a 2,048-token prefill, the decode step's HBM
-roofline fraction, and decode at batch 1 and 64 (`points`).  The library runs on
-one GPU only; for --gpus N > 1 it says so and exits with 2.
+roofline fraction, and in `points` decode at batch 1 and 64 from 2,048-token prompts and
+at batch 1, 8 and 64 at the far end of the 4,096-token context, each with its own
+fraction of the roofline (`frac_*`).  The library runs on one GPU only; for
+--gpus N > 1 it says so and exits with 2.
 """
 from __future__ import annotations
 
@@ -16,6 +19,7 @@ import os
 import statistics
 import subprocess
 import sys
+import threading
 import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
@@ -42,26 +46,61 @@ def peaks():
 
 
 class ClockSampler:
-    """nvidia-smi in the background during the timed region (reads only)."""
+    """SM clock and throttle reasons during the timed region (reads only): NVML from a thread every
+    few milliseconds, so that short regions are seen too; nvidia-smi in the background where the
+    NVML binding is missing."""
+    NAMES = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
     FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
               "clocks_event_reasons.sw_power_cap")
 
-    def __init__(self, index=0):
-        self.proc = None
-        self.index = index
+    def __init__(self, index=0, period_s=0.004):
+        self.index, self.period = index, period_s
+        self.proc = self.thread = None
+        self.samples, self.max_mhz, self.reasons = [], None, set()
+        self._stop = threading.Event()
+
+    def _nvml_loop(self, nvml, handle):
+        masks = {"hw_slowdown": nvml.nvmlClocksThrottleReasonHwSlowdown,
+                 "hw_thermal_slowdown": nvml.nvmlClocksThrottleReasonHwThermalSlowdown,
+                 "sw_thermal_slowdown": nvml.nvmlClocksThrottleReasonSwThermalSlowdown,
+                 "sw_power_cap": nvml.nvmlClocksThrottleReasonSwPowerCap}
+        while not self._stop.is_set():
+            try:
+                self.samples.append(float(nvml.nvmlDeviceGetClockInfo(handle, nvml.NVML_CLOCK_SM)))
+                bits = nvml.nvmlDeviceGetCurrentClocksThrottleReasons(handle)
+                self.reasons.update(n for n, m in masks.items() if bits & m)
+            except Exception:
+                pass
+            self._stop.wait(self.period)
 
     def start(self):
         try:
+            import pynvml as nvml
+            nvml.nvmlInit()
+            handle = nvml.nvmlDeviceGetHandleByIndex(self.index)
+            self.max_mhz = float(nvml.nvmlDeviceGetMaxClockInfo(handle, nvml.NVML_CLOCK_SM))
+            self.thread = threading.Thread(target=self._nvml_loop, args=(nvml, handle), daemon=True)
+            self.thread.start()
+            return
+        except Exception:
+            self.thread = None
+        try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "20",
                  "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
 
     def stop(self):
+        if self.thread is not None:
+            self._stop.set()
+            self.thread.join(timeout=2)
+            sm = self.samples
+            return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": self.max_mhz,
+                    "reasons": sorted(self.reasons), "samples": len(sm), "how": "nvml"}
         if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no clock reading available"]}
         self.proc.terminate()
         try:
             out, _ = self.proc.communicate(timeout=5)
@@ -69,7 +108,6 @@ class ClockSampler:
             self.proc.kill()
             out, _ = self.proc.communicate()
         sm, mx, reasons = [], [], set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         for line in out.strip().splitlines():
             parts = [p.strip() for p in line.split(",")]
             if len(parts) < 6:
@@ -78,11 +116,11 @@ class ClockSampler:
                 sm.append(float(parts[0])); mx.append(float(parts[1]))
             except ValueError:
                 continue
-            for n, v in zip(names, parts[2:6]):
+            for n, v in zip(self.NAMES, parts[2:6]):
                 if v.lower().startswith("active"):
                     reasons.add(n)
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": sorted(reasons), "samples": len(sm)}
+                "reasons": sorted(reasons), "samples": len(sm), "how": "nvidia-smi"}
 
 
 def build_model(layers: int, max_tokens: int, max_slots: int, seed: int = 0, shape: str = "8b"):
@@ -142,8 +180,10 @@ def device_decode(model, batch, prompt_len, steps, warmup, vocab, sampler):
     ctx_end = eng.cache.length(slots[0])
     for sl in slots:
         eng.free_slot(sl)
+    step_bytes = eng.weight_bytes() + kv_bytes / steps
     return {"ms_per_step": ms / steps, "tok_s": batch * steps / (ms / 1e3), "kv_bytes_per_step": kv_bytes / steps,
-            "launches": launches, "clocks": clocks, "context_end": ctx_end}
+            "launches": launches, "clocks": clocks, "context_end": ctx_end,
+            "GBps": step_bytes / (ms / steps / 1e3) / 1e9}
 
 
 class _NoSampler:
@@ -151,9 +191,18 @@ class _NoSampler:
     def stop(self): return None
 
 
+#: After a long prompt step the GPU runs at about half its clock for the next 80 to 100 ms (it has just been
+#: capped at its power limit and takes that long to come back: decode steps of the 8B shape take 5.2 ms
+#: there instead of 3.7).  `value` never sees this, because recording the decode graph idles the GPU right
+#: after the prompts; the end-to-end loop, whose graph exists by then, would be timed inside it.  Both
+#: numbers are meant as steady decoding, so the end-to-end loop warms up for at least this many steps.
+E2E_MIN_WARMUP = 40
+
+
 def e2e_decode(model, batch, prompt_len, steps, warmup, vocab):
     """The same through model.generate: host token ids in, host token ids out every step."""
     import torch
+    warmup = max(warmup, E2E_MIN_WARMUP)
     prompts = random_prompts(batch, prompt_len, vocab, 23 + batch)
     marks = {}
 
@@ -169,8 +218,8 @@ def e2e_decode(model, batch, prompt_len, steps, warmup, vocab):
     pages = -(-(prompt_len + warmup + steps) // model.page_size)
     groups = len(model.engine.cache.groups)
     h2d = 4 * (3 * batch + 3 * batch + (batch + 1) + batch + groups * batch * pages)
-    return {"value": batch * steps / dt, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4 * batch,
-            "ms_per_step": dt / steps * 1e3}
+    return {"value": batch * steps / dt, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4 * (batch + 1),
+            "ms_per_step": dt / steps * 1e3, "warmup_steps": warmup}
 
 
 def prefill_once(model, cfg, length, reps=5, warmup=3):
@@ -193,6 +242,57 @@ def prefill_once(model, cfg, length, reps=5, warmup=3):
     return statistics.median(times)
 
 
+def unequal16(args, hbm_gbs) -> dict:
+    """The 4B benchmark configuration: 16 sequences that start together with prompts uniform in
+    [64, 1536], 256 decode steps at temperature 0.7 through the Python entry point; then the
+    bfloat16 path's logits at each sequence's last position against the 32-bit path on the same
+    tokens (the reference's lockstep check at model size, README.md:206-208, docs/roadmap.md:264-265)."""
+    import torch
+    import skyla_kernel_b200 as skyla
+    from skyla_kernel_b200.engine import Engine, StepItem
+    from skyla_kernel_b200.measure import random_config, random_tensors_on_device
+    n_seq, n_new, tail = 16, 256, 8
+    cfg = random_config(args.shape, args.layers)
+    g = torch.Generator().manual_seed(16)
+    lens = torch.randint(64, 1537, (n_seq,), generator=g).tolist()
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in lens]
+    max_tokens = sum(-(-(n + n_new) // 64) * 64 for n in lens)
+    tensors = random_tensors_on_device(cfg, seed=0)
+    model = skyla.Model(Engine(cfg, dict(tensors), "bfloat16", max_tokens=max_tokens, max_slots=n_seq))
+    kw = dict(max_new_tokens=n_new, temperature=0.7, seed=7, stop_ids=[], max_batch=n_seq)
+    model.generate(prompts, **kw)  # the workload once untimed: kernels are loaded and the decode graphs recorded
+    marks = []
+    t0 = time.perf_counter()
+    out = model.generate(prompts, on_step=lambda s, live: marks.append(time.perf_counter()), **kw)
+    decode_s = marks[-1] - marks[0]
+    # the check: all but the last `tail` tokens as a prompt, then `tail` single tokens (the decode kernels, as
+    # graphs), in bfloat16; the whole sequence at once in 32-bit; logits after the last token of both
+    seqs = [p + o for p, o in zip(prompts, out)]
+    eng = model.engine
+    slots = [eng.alloc_slot() for _ in seqs]
+    eng.step([StepItem(s, q[:-tail], []) for s, q in zip(slots, seqs)])
+    for t in range(tail, 0, -1):
+        low = eng.step([StepItem(s, [q[-t]], [0]) for s, q in zip(slots, seqs)])
+    eng.check_errors()
+    for s in slots:
+        eng.free_slot(s)
+    ref_eng = Engine(cfg, tensors, "float32", max_tokens=max_tokens, max_slots=n_seq)
+    del tensors
+    rows = []
+    for q in seqs:  # one at a time: the 32-bit path's activations of a step are wide
+        s = ref_eng.alloc_slot()
+        rows.append(ref_eng.step([StepItem(s, q, [len(q) - 1])]))
+        ref_eng.free_slot(s)
+    ref = torch.cat(rows)
+    diff = (low - ref).abs()
+    scale = float(ref.abs().max())
+    return {"tok_s": n_seq * (len(marks) - 1) / decode_s, "ms_per_step": decode_s / (len(marks) - 1) * 1e3,
+            "prompt_lens": [min(lens), max(lens)], "prompt_tokens": sum(lens), "prefill_s": marks[0] - t0,
+            "logit_diff_abs": float(diff.max()), "logit_diff_rel": float(diff.max()) / scale,
+            "logit_diff_mean_rel": float(diff.mean()) / scale, "largest_logit": scale,
+            "top1_agree": int((low.argmax(-1) == ref.argmax(-1)).sum()), "of": n_seq, "layers": cfg.num_hidden_layers}
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -202,7 +302,9 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--shape", choices=sorted(SHAPES), default="8b", help="layer sizes: Qwen3-8B (the default), -4B or -32B")
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the shape has (0: all)")
-    ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
+    ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64 and at the long context")
+    ap.add_argument("--workload", choices=["decode", "unequal16"], default="decode",
+                    help="unequal16: 16 unequal prompts, 256 sampled tokens, bfloat16 logits checked against 32-bit")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -219,6 +321,12 @@ def main() -> int:
 
     import torch
     hbm_gbs, bf16_tflops, peak_kind = peaks()
+    if args.workload == "unequal16":
+        r = unequal16(args, hbm_gbs)
+        print(json.dumps({"metric": "decode tokens/s through the entry point, Qwen3-%s shape bf16, 16 unequal prompts, "
+                                    "256 tokens at temperature 0.7" % args.shape.upper(), "value": r["tok_s"],
+                          "unit": "tokens/s", "n_gpus": 1, "dtype": "bf16", "workload": r}))
+        return 0
     batches = [args.batch] + ([] if args.no_points else [b for b in (1, 64) if b != args.batch])
     max_tokens = max(batches) * (-(-CONTEXT // 64) * 64)
     t_build = time.time()
@@ -242,11 +350,21 @@ def main() -> int:
     for b in batches[1:]:
         r = device_decode(model, b, PROMPT_LEN, args.steps, args.warmup, V, _NoSampler())
         points[f"decode_b{b}"] = r["tok_s"]
+        points[f"frac_b{b}"] = r["GBps"] / hbm_gbs
         print(f"[bench] decode batch {b}: {r['ms_per_step']:.3f} ms/step", file=sys.stderr, flush=True)
     points[f"decode_b{args.batch}"] = main_run["tok_s"]
+    points[f"frac_b{args.batch}"] = main_run["GBps"] / hbm_gbs
+    if not args.no_points:
+        # the far end of the context: the timed steps end just under CONTEXT positions
+        long_prompt = max(64, CONTEXT - args.warmup - args.steps - 2)
+        for b in sorted(set(batches)):
+            r = device_decode(model, b, long_prompt, args.steps, args.warmup, V, _NoSampler())
+            points[f"decode_b{b}_ctx{CONTEXT}"] = r["tok_s"]
+            points[f"frac_b{b}_ctx{CONTEXT}"] = r["GBps"] / hbm_gbs
+            print(f"[bench] decode batch {b} at context {r['context_end']}: {r['ms_per_step']:.3f} ms/step",
+                  file=sys.stderr, flush=True)
 
-    step_bytes = model.engine.weight_bytes() + main_run["kv_bytes_per_step"]
-    achieved = step_bytes / (main_run["ms_per_step"] / 1e3) / 1e9
+    achieved = main_run["GBps"]
     line = {
         "metric": "decode tokens/s, Qwen3-%s shape bf16, batch %d, 2048-token prompts" % (args.shape.upper(), args.batch),
         "value": main_run["tok_s"], "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,

@@ -43,7 +43,9 @@ class Engine:
 
     ``max_tokens`` counts the positions held by live sequences, each sequence
     rounded up to a whole page of 64.  ``max_slots`` bounds the live sequences
-    (default: one per page).
+    (default: one per page).  ``tensors`` (checkpoint name -> tensor) is consumed:
+    parts take out of it what they copy into matrices of their own, so that a
+    caller who keeps no other reference keeps no second copy of the weights.
     """
 
     def __init__(self, config, tensors: Dict[str, torch.Tensor], dtype: str = "bfloat16",

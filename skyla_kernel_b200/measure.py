@@ -19,20 +19,20 @@ QWEN3_32B = dict(QWEN3_8B, num_hidden_layers=64, hidden_size=5120, num_attention
 SHAPES = {"8b": QWEN3_8B, "4b": QWEN3_4B, "32b": QWEN3_32B}
 
 
-def random_engine(shape: Union[str, dict], layers: Optional[int] = None, max_tokens: int = 4096,
-                  max_slots: Optional[int] = None, seed: int = 0, dtype: str = "bfloat16", device="cuda:0",
-                  linear_std: float = 0.02, norm_std: float = 0.02):
-    """(engine, configuration) of a model with the layer sizes of ``shape`` (a key of ``SHAPES`` or a
-    config.json-style dict) and ``layers`` layers (default: the shape's own), weights N(0, linear_std),
-    norm weights 1 + N(0, norm_std), drawn on the device tensor by tensor."""
+def random_config(shape: Union[str, dict], layers: Optional[int] = None):
     from .config import Qwen3Config
-    from .engine import Engine, declared_tensors
-    from .kernels import ops
     base = dict(SHAPES[shape] if isinstance(shape, str) else shape)
     if layers:
         base["num_hidden_layers"] = layers
-    cfg = Qwen3Config(**base)
-    store = torch.float32 if dtype in ("float32", "fp32") else torch.bfloat16
+    return Qwen3Config(**base)
+
+
+def random_tensors_on_device(cfg, seed: int = 0, store: torch.dtype = torch.bfloat16, device="cuda:0",
+                             linear_std: float = 0.02, norm_std: float = 0.02):
+    """The model's tensors by checkpoint name, drawn on the device: N(0, linear_std), norm weights
+    1 + N(0, norm_std), each tensor from a stream of its own."""
+    from .engine import declared_tensors
+    from .kernels import ops
     tensors = {}
     for i, (name, d) in enumerate(declared_tensors(cfg.to_spec()).items()):
         t = torch.empty(d.shape, dtype=store, device=device)
@@ -41,6 +41,18 @@ def random_engine(shape: Union[str, dict], layers: Optional[int] = None, max_tok
         else:
             ops.fill_normal(t, 0.0, linear_std, seed * 100003 + i)
         tensors[name] = t
+    return tensors
+
+
+def random_engine(shape: Union[str, dict], layers: Optional[int] = None, max_tokens: int = 4096,
+                  max_slots: Optional[int] = None, seed: int = 0, dtype: str = "bfloat16", device="cuda:0",
+                  linear_std: float = 0.02, norm_std: float = 0.02):
+    """(engine, configuration) of a model with the layer sizes of ``shape`` (a key of ``SHAPES`` or a
+    config.json-style dict) and ``layers`` layers (default: the shape's own), with random weights."""
+    from .engine import Engine
+    cfg = random_config(shape, layers)
+    store = torch.float32 if dtype in ("float32", "fp32") else torch.bfloat16
+    tensors = random_tensors_on_device(cfg, seed, store, device, linear_std, norm_std)
     engine = Engine(cfg, tensors, dtype, max_tokens=max_tokens, max_slots=max_slots, device=device)
     del tensors
     torch.cuda.empty_cache()

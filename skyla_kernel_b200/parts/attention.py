@@ -87,10 +87,13 @@ class GQAttention(Part):
 
     def load(self, tensors) -> None:
         t = self.spec.tensors
-        parts = [tensors[t[k]] for k in ("q_proj", "k_proj", "v_proj")]
+        # the three matrices become one of this part's own: they are taken OUT of the table, so that
+        # whoever filled it keeps no second copy of them alive (a 32B model and its cache share one GPU)
+        parts = [tensors.pop(t[k]) for k in ("q_proj", "k_proj", "v_proj")]
         if len({w.dtype for w in parts}) > 1:
             parts = [w.to(torch.float32) for w in parts]
         fused = self.rt.matrix(torch.cat(parts, dim=0))
+        del parts
         self.qkv = Linear(fused, self.rt)
         self.q_only = Linear(fused[: self.nq * self.hd], self.rt)
         self.out = Linear(self.rt.matrix(tensors[t["o_proj"]]), self.rt)

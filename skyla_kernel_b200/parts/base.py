@@ -140,7 +140,10 @@ class Part:
         return {}
 
     def load(self, tensors: Dict[str, torch.Tensor]) -> None:
-        """Take the declared tensors (CPU, as stored) and keep what the kernels need."""
+        """Take the declared tensors (as stored, on the host or already on the device) and keep what
+        the kernels need.  A part that copies tensors into a fused matrix of its own may remove them
+        from ``tensors`` (``pop``) so that the originals can be freed; a tensor that another part may
+        also declare (a tied head) stays."""
 
     def kernels_needed(self):
         return tuple(self.kernel_modules)

@@ -44,10 +44,12 @@ class SwiGLU(Part):
 
     def load(self, tensors) -> None:
         t = self.spec.tensors
-        gate, up = tensors[t["gate_proj"]], tensors[t["up_proj"]]
+        gate, up = tensors.pop(t["gate_proj"]), tensors.pop(t["up_proj"])  # taken out: they live on fused
         if gate.dtype != up.dtype:
             gate, up = gate.to(torch.float32), up.to(torch.float32)
-        self.gate_up = Linear(self.rt.matrix(fuse_gate_up(gate, up)), self.rt, gated=True)
+        fused = fuse_gate_up(gate, up)
+        del gate, up
+        self.gate_up = Linear(self.rt.matrix(fused), self.rt, gated=True)
         self.down = Linear(self.rt.matrix(tensors[t["down_proj"]]), self.rt)
 
     def weight_bytes(self) -> int:

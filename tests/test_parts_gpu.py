@@ -43,7 +43,7 @@ def test_rmsnorm_part(dtype):
     rt = _rt(dtype)
     part = build_part("norm", spec, rt)
     w = _tensors(declare_part("norm", spec), 1)
-    part.load(w)
+    part.load(dict(w))  # a part may take out of the table what it fuses
     x = torch.randn(6, 80, device=DEV) * 2
     out = torch.empty(6, 80, dtype=rt.act_dtype, device=DEV)
     part.forward(None, x, out)
@@ -89,7 +89,7 @@ def test_attention_part_whole_then_one_by_one(dtype, hidden, nq, nkv, hd, n_rot,
     spec = _attention_spec(hidden, nq, nkv, hd, n_rot, window, qk_norm, scale, cache_dtype)
     part = build_part("mixer", spec, rt)
     w = _tensors(declare_part("mixer", spec), 3, sharp=2.0)
-    part.load(w)
+    part.load(dict(w))  # a part may take out of the table what it fuses
     T = 150
     h_all = torch.randn(T, hidden, generator=torch.Generator().manual_seed(4))
     freqs, m = plain.rope_frequencies(n_rot, 10000.0)
@@ -124,7 +124,7 @@ def test_swiglu_part(dtype):
                     {k: f"f.{k}" for k in ("gate_proj", "up_proj", "down_proj")})
     part = build_part("feed_forward", spec, rt)
     w = _tensors(declare_part("feed_forward", spec), 5, std=0.15)
-    part.load(w)
+    part.load(dict(w))  # a part may take out of the table what it fuses
     cache, batcher = _ctx(rt, [], [], None)
     slot = cache.alloc_slot()
     ctx = batcher.build([StepItem(slot, [0] * 9, [])])
@@ -151,7 +151,7 @@ def _two_layer_engine(schedule, dtype="float32"):
 
     cfg = Scheduled(**TINY_A)
     w = _tensors(declared_tensors(cfg.to_spec()), 9, std=0.05, sharp=2.0)
-    return Engine(cfg, w, dtype, max_tokens=512), cfg, w
+    return Engine(cfg, dict(w), dtype, max_tokens=512), cfg, w  # the engine consumes the table it is given
 
 
 def _plain_scheduled(cfg, w, tokens, schedule):
@@ -258,7 +258,7 @@ def test_block_alone(dtype):
     if dtype == "bfloat16":  # stored in 16 bits, as a served model would be: the tensor-core kernels run
         w = {k: v.to(torch.bfloat16) for k, v in w.items()}
     block = cls(spec, rt)
-    block.load(w)
+    block.load(dict(w))
     wf = {k: v.float() for k, v in w.items()}
     T = 90
     x0 = torch.randn(T, H, generator=torch.Generator().manual_seed(3)) * 0.5
@@ -292,7 +292,7 @@ def test_wide_groups_decode_through_the_prompt_kernel():
     part = build_part("mixer", spec, rt)
     assert part._fast == 1
     w = {k: v.to(torch.bfloat16) for k, v in _tensors(declare_part("mixer", spec), 5, sharp=2.0).items()}
-    part.load(w)
+    part.load(dict(w))  # a part may take out of the table what it fuses
     wf = {k: v.float() for k, v in w.items()}
     T = 80
     h_all = torch.randn(T, hidden, generator=torch.Generator().manual_seed(6))

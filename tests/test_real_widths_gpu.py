@@ -82,7 +82,7 @@ def test_two_layers_of_the_real_widths(shape):
     ref = plain.forward(d, {k: v.float() for k, v in tensors.items()}, main)[-33:]
     got = {}
     for dtype in ("float32", "bfloat16"):
-        eng = Engine(cfg, tensors, dtype, max_tokens=1024)
+        eng = Engine(cfg, dict(tensors), dtype, max_tokens=1024)  # the engine consumes the table it is given
         got[dtype] = _cuts(eng, main, others)
         del eng
         torch.cuda.empty_cache()
