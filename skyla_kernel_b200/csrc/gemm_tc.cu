@@ -428,11 +428,13 @@ gemm_tc_rows_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
   const int a_tile = ra.rows_per_block * BK * 2;  // R rows of 128 bytes: a multiple of 1024
   const uint32_t stage_bytes = (uint32_t)(kkb * (kATiles * a_tile + kBBytes));
   const uint32_t bars = (smem_u32(smem_raw) + 15u) & ~15u;                       // barriers first
-  const uint32_t base = (bars + 8u * (2 * kRowsMaxStages + 1) + 1023u) & ~1023u;  // then the ring
+  const uint32_t base = (bars + 8u * (2 * kRowsMaxStages + 3) + 1023u) & ~1023u;  // then the ring
   const uint32_t landing = base + (uint32_t)n_stages * stage_bytes;               // then the landing zone
   auto full_bar = [&](int s) { return bars + 8u * s; };
   auto empty_bar = [&](int s) { return bars + 8u * (kRowsMaxStages + s); };
   const uint32_t tmem_full_bar = bars + 8u * (2 * kRowsMaxStages);
+  const uint32_t land_bar = bars + 8u * (2 * kRowsMaxStages + 1);  // the peers' tiles have landed (K splits as a cluster)
+  const uint32_t sent_bar = bars + 8u * (2 * kRowsMaxStages + 2);  // the peers have taken what this block sent them
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int f0 = blockIdx.x * ra.rows_per_block;  // first output feature of this block
@@ -468,6 +470,17 @@ gemm_tc_rows_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
       mbar_init(empty_bar(s), 1);
     }
     mbar_init(tmem_full_bar, 1);
+    mbar_init(land_bar, 1);
+    if (clustered) {  // one arrival from every peer that this block sends tokens to (rank r owns ceil(M / ranks) tokens from r * that on)
+      uint32_t ranks;
+      asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(ranks));
+      const int per = (a.M + (int)ranks - 1) / (int)ranks;
+      const int owners = (a.M + per - 1) / per;  // ranks that own tokens: the first ones
+      uint32_t rank;
+      asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+      const int n_dst = owners - ((int)rank < owners ? 1 : 0);
+      mbar_init(sent_bar, n_dst > 0 ? n_dst : 1);
+    }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     // weights are written by no kernel: this thread, which is the loader, asks for the ring's first
     // filling at once, while the other warps allocate TMEM and the block meets (0.35 us earlier)
@@ -483,6 +496,10 @@ gemm_tc_rows_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = tmem_base_slot;
   allow_dependents();
+  // K splits as a cluster: nobody may send into a peer's landing zone before that peer's barrier exists.
+  // Every thread arrives here (it costs nothing); who sends waits for the others just before sending.
+  if (clustered) asm volatile("barrier.cluster.arrive.release;" ::: "memory");
+  bool met_cluster = false;  // this thread has waited for that first meeting
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
@@ -573,7 +590,7 @@ gemm_tc_rows_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
       if (et < BN) row_inv[et] = 1.0f / sqrtf(row_ssq[et] / norm_width + norm_eps);
       asm volatile("barrier.sync 1, 128;" ::: "memory");
     }
-    const bool ahead = MODE == kAccumF32 && a.ahead.xw != nullptr && !clustered;
+    const bool ahead = MODE == kAccumF32 && a.ahead.xw != nullptr;
     const int kstack = ra.kstack, R = ra.rows_per_block;
     float* red = reinterpret_cast<float*>(smem_raw + (landing - smem_u32(smem_raw)));
     float* sqbuf = red + (kstack > 1 ? kstack * BN * R : 0);  // [tok][row of the tile]: squares of the new x
@@ -598,7 +615,139 @@ gemm_tc_rows_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     const bool ok = n_kb > 0 && mbar_wait(tmem_full_bar, 0, &abort_flag, a.error_flag, 3);
     if (ok) asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16);
-    if (kstack > 1) {
+    if (clustered) {
+      // The K splits of a tile form a cluster.  Rank r owns the tokens [r * per, r * per + per): every
+      // split writes its accumulator, token by token, into shared memory of its own (the ring, idle by
+      // now), one region per owner, and sends each region to its owner's landing zone with ONE bulk
+      // copy through distributed shared memory (cp.async.bulk.shared::cluster), which the owner's
+      // barrier counts in.  (Element-wise remote stores, tried first, take 70 ns each and cannot be
+      // overlapped: 4.4 us for 64 tokens, more than streaming the block's weights.)  The owner then
+      // adds the splits' values in rank order: one order whatever the batch.
+      const int per = (a.M + (int)n_ranks - 1) / (int)n_ranks;
+      const int my_n = max(0, min(per, a.M - (int)my_rank * per));
+      const uint32_t kRowBytes = BM * 4;  // a token's 128 features of the tile
+      if (et == 0 && my_n > 0 && n_ranks > 1) mbar_expect_tx(land_bar, (n_ranks - 1) * (uint32_t)my_n * kRowBytes);
+      float old[16];
+      const float w_next = (ahead && mine) ? a.ahead.w[f] : 0.f;
+      if (MODE == kAccumF32 && mine) {  // the old values do not depend on the product: fetch them while the main loop runs
+#pragma unroll
+        for (int i = 0; i < 16; ++i)
+          old[i] = i < my_n ? ((const float*)a.y)[(int64_t)((int)my_rank * per + i) * a.ldy + f] : 0.f;
+      }
+      const bool warp_reads = ok && quad * 32 < R;  // uniform for the warp
+      // token col lies at slot col of the travelling regions (owner col / per, place col % per: the regions
+      // follow one another), except my own tokens, which go straight to my landing zone
+      const int mine_lo = (int)my_rank * per, mine_hi = mine_lo + my_n;
+      const uint32_t travel = base + 4u * (uint32_t)r_local, home = landing + 4u * (uint32_t)r_local;
+      if (warp_reads) {
+        // all of the tile's columns are asked for at once (a load and its wait take 0.2 us one after the other)
+        uint32_t r[BN];
+#pragma unroll
+        for (int c0 = 0; c0 < BN; c0 += 16)
+          if (c0 < a.M) tmem_ld16(taddr + c0, r + c0);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+        for (int col = 0; col < BN; ++col) {
+          if (col < a.M) {
+            const uint32_t at = (col >= mine_lo && col < mine_hi ? home : travel) + (uint32_t)col * kRowBytes;
+            asm volatile("st.shared.b32 [%0], %1;" ::"r"(at), "r"(r[col]) : "memory");
+          }
+        }
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // these writes, as the bulk copies will read them
+      asm volatile("barrier.sync 1, 128;" ::: "memory");
+      // every peer's barrier exists from here on.  (Whole warps wait together: one lane of a warp waiting
+      // for the cluster alone is held until the rest of its warp waits too.)
+      asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
+      met_cluster = true;
+      if (et == 0) {
+        for (uint32_t d = 1; ok && d < n_ranks; ++d) {
+          const uint32_t dst = (my_rank + d) % n_ranks;
+          const int dst_n = max(0, min(per, a.M - (int)dst * per));
+          if (dst_n == 0) continue;
+          uint32_t remote_zone, remote_bar;
+          asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote_zone) : "r"(landing + my_rank * (uint32_t)per * kRowBytes), "r"(dst));
+          asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote_bar) : "r"(land_bar), "r"(dst));
+          asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                       ::"r"(remote_zone), "r"(base + dst * (uint32_t)per * kRowBytes), "r"((uint32_t)dst_n * kRowBytes), "r"(remote_bar)
+                       : "memory");
+        }
+      }
+      bool landed = ok;
+      if (landed && my_n > 0 && n_ranks > 1) landed = mbar_wait(land_bar, 0, &abort_flag, a.error_flag, 7);
+      if (et == 0 && landed && my_n > 0) {  // what the peers sent has been taken: they may leave
+        for (uint32_t d = 1; d < n_ranks; ++d) {
+          uint32_t remote_bar;
+          asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote_bar) : "r"(sent_bar), "r"((my_rank + d) % n_ranks));
+          asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(remote_bar) : "memory");
+        }
+      }
+      __shared__ float warp_sq[4][64];  // norm ahead: the warps' shares of the owned tokens' sums of squares
+      // The epilogue runs with one warp per scheduler, so nothing hides a load's latency but more loads: four
+      // tokens' values of all splits are asked for before any is used, then added in rank order.
+      const uint32_t zone = landing + 4u * (uint32_t)r_local;
+      const uint32_t rank_stride = (uint32_t)per * kRowBytes;
+      auto finish4 = [&](int i0, const float* before) {
+        float v[4][kRowsMaxSplits];
+#pragma unroll
+        for (int t = 0; t < 4; ++t)
+#pragma unroll
+          for (int src = 0; src < kRowsMaxSplits; ++src) {
+            v[t][src] = 0.f;
+            if (i0 + t < my_n && src < (int)n_ranks)
+              asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v[t][src]) : "r"(zone + (uint32_t)src * rank_stride + (uint32_t)(i0 + t) * kRowBytes));
+          }
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          const int i = i0 + t;
+          if (i >= my_n) break;
+          const int col = (int)my_rank * per + i;
+          float nv = 0.f;
+          if (landed && mine) {
+            float sum = 0.f;
+#pragma unroll
+            for (int src = 0; src < kRowsMaxSplits; ++src) sum += v[t][src];  // the ranks beyond the cluster add zeros
+            if (scaled) sum *= row_inv[col];
+            if (MODE == kStoreBf16) {
+              ((__nv_bfloat16*)a.y)[(int64_t)col * a.ldy + f] = __float2bfloat16_rn(sum);
+            } else if (MODE == kStoreF32) {
+              ((float*)a.y)[(int64_t)col * a.ldy + f] = sum;
+            } else {
+              nv = before[t] + sum;
+              ((float*)a.y)[(int64_t)col * a.ldy + f] = nv;
+              if (ahead) a.ahead.xw[(int64_t)col * a.ahead.ldxw + f] = __float2bfloat16_rn(nv * w_next);
+            }
+          }
+          if (ahead) {  // uniform for the block
+            float sq = nv * nv;
+            sq += __shfl_xor_sync(0xffffffffu, sq, 16);
+            sq += __shfl_xor_sync(0xffffffffu, sq, 8);
+            sq += __shfl_xor_sync(0xffffffffu, sq, 4);
+            sq += __shfl_xor_sync(0xffffffffu, sq, 2);
+            sq += __shfl_xor_sync(0xffffffffu, sq, 1);
+            if (lane == 0) warp_sq[quad][i] = sq;
+          }
+        }
+      };
+#pragma unroll
+      for (int i0 = 0; i0 < 16; i0 += 4)
+        if (i0 < my_n) finish4(i0, old + i0);
+      for (int i0 = 16; i0 < my_n; i0 += 4) {  // a block that owns more than 16 tokens (two splits of a wide tile)
+        float before[4] = {0.f, 0.f, 0.f, 0.f};
+        if (MODE == kAccumF32 && landed && mine) {
+#pragma unroll
+          for (int t = 0; t < 4; ++t)
+            if (i0 + t < my_n) before[t] = ((const float*)a.y)[(int64_t)((int)my_rank * per + i0 + t) * a.ldy + f];
+        }
+        finish4(i0, before);
+      }
+      if (ahead) {
+        asm volatile("barrier.sync 1, 128;" ::: "memory");
+        if (et < my_n && landed)
+          a.ahead.ssq_part[(int64_t)blockIdx.x * a.M + (int)my_rank * per + et] =
+              warp_sq[0][et] + warp_sq[1][et] + warp_sq[2][et] + warp_sq[3][et];
+      }
+    } else if (kstack > 1) {
       // lane L of the accumulator is row L % R of K-block group L / R; its partial products are the
       // columns [q*BN, q*BN + BN) of its own group q.  red[(q*BN + tok)*R + r], then a sum over q.
       if (ok) {
@@ -661,7 +810,7 @@ gemm_tc_rows_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         }
       }
     }
-    const bool warp_has_rows = ok && kstack == 1 && quad * 32 < R;  // uniform for the warp
+    const bool warp_has_rows = ok && kstack == 1 && !clustered && quad * 32 < R;  // uniform for the warp
 #pragma unroll 1
     for (int c0 = 0; c0 < BN && warp_has_rows; c0 += 16) {
       if (c0 >= a.M) break;
@@ -672,21 +821,6 @@ gemm_tc_rows_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
       if (!mine) {
         if (ahead && r_local < R)
           for (int j = 0; j < 16 && c0 + j < a.M; ++j) sqbuf[(c0 + j) * R + r_local] = 0.f;
-        continue;
-      }
-      if (clustered) {
-        // token column c belongs to rank c % n_ranks: push this split's value into that
-        // block's landing zone, slot [my rank][c / n_ranks][row of the tile]
-        const uint32_t per_rank = ((uint32_t)BN + n_ranks - 1) / n_ranks;
-#pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          const uint32_t col = (uint32_t)(c0 + j);
-          if ((int)col >= a.M) break;
-          const uint32_t local = landing + 4u * ((my_rank * per_rank + col / n_ranks) * BM + (uint32_t)r_local);
-          uint32_t remote;
-          asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(col % n_ranks));
-          asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "r"(r[j]) : "memory");
-        }
         continue;
       }
       float old[16];
@@ -721,7 +855,7 @@ gemm_tc_rows_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         }
       }
     }
-    if (ahead && !ssq_in_warp) {  // this block's share of the new rows' sums of squares, added up in a fixed order
+    if (ahead && !ssq_in_warp && !clustered) {  // this block's share of the new rows' sums of squares, added up in a fixed order
       asm volatile("barrier.sync 1, 128;" ::: "memory");
       // a warp per token: lanes take the rows 32 apart, then a butterfly (one order whatever the batch)
       for (int tok = warp - 2; ok && tok < a.M; tok += 4) {
@@ -737,44 +871,17 @@ gemm_tc_rows_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     }
   }
   if (clustered) {
-    // All splits have pushed their tiles; each
-    // block owns the token columns c with c % n_ranks == its rank and adds the splits' values
-    // in rank order.  A block that gave up on a wait still arrives, so that its peers go on.
-    uint32_t rank, n_ranks;
-    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
-    asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(n_ranks));
-    const int r_local = (warp & 3) * 32 + lane;
-    const int f = f0 + r_local;
-    const int per_rank = (BN + (int)n_ranks - 1) / (int)n_ranks;
-    const bool worker = warp >= 2 && r_local < ra.rows_per_block && f < a.N;
-    float old[16];
-    if (worker && MODE == kAccumF32) {  // the old values do not depend on the peers: fetch them while waiting
-#pragma unroll
-      for (int i = 0; i < 16; ++i) {
-        const int col = i * (int)n_ranks + (int)rank;
-        old[i] = (i < per_rank && col < a.M) ? ((const float*)a.y)[(int64_t)col * a.ldy + f] : 0.f;
-      }
-    }
-    __syncwarp();
-    asm volatile("barrier.cluster.arrive.release;\n\tbarrier.cluster.wait.acquire;" ::: "memory");
-    if (worker && !abort_flag) {
-      const float* land = reinterpret_cast<const float*>(smem_raw + (landing - smem_u32(smem_raw)));
-      auto finish = [&](int i, int col, float before) {
-        float sum = 0.f;
-        for (uint32_t src = 0; src < n_ranks; ++src) sum += land[((int)src * per_rank + i) * BM + r_local];
-        if (MODE == kStoreBf16) ((__nv_bfloat16*)a.y)[(int64_t)col * a.ldy + f] = __float2bfloat16_rn(sum);
-        else ((float*)a.y)[(int64_t)col * a.ldy + f] = before + sum;
-      };
-#pragma unroll
-      for (int i = 0; i < 16; ++i) {
-        const int col = i * (int)n_ranks + (int)rank;
-        if (i < per_rank && col < a.M) finish(i, col, MODE == kAccumF32 ? old[i] : 0.f);
-      }
-      for (int i = 16; i < per_rank; ++i) {  // a block that owns more than 16 columns (few splits, wide tile)
-        const int col = i * (int)n_ranks + (int)rank;
-        if (col >= a.M) break;
-        finish(i, col, MODE == kAccumF32 ? ((const float*)a.y)[(int64_t)col * a.ldy + f] : 0.f);
-      }
+    // A block's shared memory has to outlive the copies that read it: it leaves when every peer it sent to has
+    // told it so (the copies INTO this block were over when its own barrier let it go on).  A peer that gave up
+    // never tells; the wait is bounded like every other.
+    if (!met_cluster) asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
+    if (threadIdx.x == 64) {
+      uint32_t rank, ranks;
+      asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+      asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(ranks));
+      const int per = (a.M + (int)ranks - 1) / (int)ranks;
+      const int owners = (a.M + per - 1) / per;
+      if (owners - ((int)rank < owners ? 1 : 0) > 0 && !abort_flag) mbar_wait(sent_bar, 0, &abort_flag, a.error_flag, 8);
     }
   }
   // ------------------------------------------------------------------ teardown
@@ -805,15 +912,17 @@ int launch_rows(const CUtensorMap& mw, const CUtensorMap& mx, const GemmArgs& a,
   const int stage = kkb * (kATiles * rows_per_block * BK * 2 + BN * BK * 2);
   // behind the ring: the landing zone of the cluster epilogue or the stacked epilogue's sums, which
   // also is the room that the MMA, reading 128 rows whatever R is, may run into
-  int landing = splits > 1 ? (BN + splits - 1) / splits * splits * BM * 4 : 0;
+  int landing = splits > 1 ? (BN + splits - 1) / splits * splits * BM * 4 : 0;  // [source rank][owned token][128]
   if (kstack > 1) landing = kstack * BN * rows_per_block * 4;
   if (a.ahead.xw != nullptr) landing += BN * rows_per_block * 4;  // the squares of the new rows
   const int over_read = (BM - kstack * rows_per_block) * BK * 2;
   ra.landing_bytes = landing > over_read ? landing : over_read;
-  const int fixed = 16 + 8 * (2 * kRowsMaxStages + 1) + 1024 + ra.landing_bytes;
+  const int fixed = 16 + 8 * (2 * kRowsMaxStages + 3) + 1024 + ra.landing_bytes;
   ra.n_stages = (kRowsSmemBytes - fixed) / stage;
   if (ra.n_stages > kRowsMaxStages) ra.n_stages = kRowsMaxStages;
   if (ra.n_stages < 2) return fail(kBadArgument, "gemm_tc_rows: stages of %d bytes do not fit twice", stage);
+  if (splits > 1 && ra.n_stages * stage < landing)  // the splits' tiles wait in the idle ring for their bulk copies
+    return fail(kBadArgument, "gemm_tc_rows: a ring of %d bytes is too small for the K splits' tiles", ra.n_stages * stage);
   const int smem = fixed + ra.n_stages * stage;
   static bool configured = false;
   if (!configured) {
@@ -994,13 +1103,12 @@ extern "C" int skyla_gemm_tc_rows(const void* map_w, const void* map_x, void* y,
   if ((splits - 1) * kps >= total_kb) return fail(kBadArgument, "gemm_tc_rows: %d splits leave one without K blocks", splits);
   GemmArgs a{y, ldy, 0, M, N, K, kps, error_flag, FoldJob{}, nullptr, nullptr};
   if (ahead_xw != nullptr) {
-    if (mode != kAccumF32 || splits != 1 || ahead_w == nullptr || ahead_ssq == nullptr)
-      return fail(kBadArgument, "gemm_tc_rows: norm-ahead goes with the accumulate epilogue, one split, a norm weight and room for the sums");
+    if (mode != kAccumF32 || ahead_w == nullptr || ahead_ssq == nullptr)
+      return fail(kBadArgument, "gemm_tc_rows: norm-ahead goes with the accumulate epilogue, a norm weight and room for the sums");
     a.ahead = NormAhead{ahead_w, (__nv_bfloat16*)ahead_xw, ahead_ldxw, ahead_ssq};
   }
   if (scale_ssq != nullptr) {
-    if (splits != 1 || scale_parts < 1)
-      return fail(kBadArgument, "gemm_tc_rows: handed-in sums of squares go with a loaded token operand and one split");
+    if (scale_parts < 1) return fail(kBadArgument, "gemm_tc_rows: handed-in sums of squares come in one share at least");
     a.scale = ScaleIn{scale_ssq, scale_parts, scale_eps, K};
   }
 #define SKYLA_ROWS_BN(MODE_)                                                                          \

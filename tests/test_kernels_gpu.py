@@ -602,11 +602,19 @@ def test_gemm_tc_rows_store_accumulate_gated(m, n, k, rows, kkb, splits, kstack)
 
 @pytest.mark.parametrize("m,n,k,rows,kkb,kstack,n2,rows2,kkb2,kstack2", [
     (8, 4096, 4096, 32, 8, 4, 6144, 48, 6, 2), (5, 264, 520, 24, 1, 1, 200, 72, 1, 1), (16, 328, 704, 40, 6, 3, 136, 8, 16, 16),
-    (1, 128, 64, 128, 1, 1, 128, 128, 1, 1), (11, 1000, 1536, 56, 4, 2, 520, 88, 2, 1)])
+    (1, 128, 64, 128, 1, 1, 128, 128, 1, 1), (11, 1000, 1536, 56, 4, 2, 520, 88, 2, 1),
+    # K cut into a cluster of splits on either side (kstack = -splits): 17 to 64 tokens are served so
+    (64, 4096, 4096, 128, 2, -4, 6144, 96, 2, -2), (40, 520, 1088, 104, 1, -3, 200, 72, 2, -2), (17, 328, 704, 40, 2, -2, 136, 128, 1, -8),
+    (3, 264, 640, 24, 1, -4, 264, 24, 1, -5)])
 def test_gemm_tc_rows_norm_ahead_then_scale_in(m, n, k, rows, kkb, kstack, n2, rows2, kkb2, kstack2):
     """x += a W^T leaves x * norm weight in bfloat16 and the blocks' shares of the rows' sums of
     squares; the next product takes those and must equal the product of rmsnorm(x)."""
     ops = _ops()
+    splits = splits2 = 1
+    if kstack < 0:
+        splits, kstack = -kstack, 1
+    if kstack2 < 0:
+        splits2, kstack2 = -kstack2, 1
     from skyla_kernel_b200.parts.feedforward import fuse_gate_up
     a = _rand(m, k, seed=61, dtype=torch.bfloat16)
     w = _rand(n, k, seed=62, dtype=torch.bfloat16, scale=0.1)
@@ -616,7 +624,7 @@ def test_gemm_tc_rows_norm_ahead_then_scale_in(m, n, k, rows, kkb, kstack, n2, r
     blocks = -(-n // rows)
     xw = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device=DEV)
     shares = torch.full((blocks, m), float("nan"), device=DEV)
-    ops.gemm_tc_rows(a, ops.TensorMap(w, rows, kkb), rows, n, x, ops.TC_ACCUM_F32, kkb=kkb, kstack=kstack,
+    ops.gemm_tc_rows(a, ops.TensorMap(w, rows, kkb), rows, n, x, ops.TC_ACCUM_F32, kkb=kkb, kstack=kstack, splits=splits,
                      norm_ahead=(nw, xw, shares))
     want_x = x0.double() + a.double() @ w.double().T
     assert (x.double() - want_x).abs().max().item() <= 1e-5 * want_x.abs().max().item() + 1e-6
@@ -630,7 +638,8 @@ def test_gemm_tc_rows_norm_ahead_then_scale_in(m, n, k, rows, kkb, kstack, n2, r
     ref = h @ w2.double().cpu().T
     y = torch.full((m, n2), float("nan"), device=DEV)
     ops.gemm_tc_rows(xw, ops.TensorMap(w2, rows2, kkb2 if n % 64 == 0 else 1), rows2, n2, y, ops.TC_STORE_F32,
-                     kkb=kkb2 if n % 64 == 0 else 1, kstack=kstack2 if n % 64 == 0 else 1, scale_in=(shares, eps))
+                     kkb=kkb2 if n % 64 == 0 else 1, kstack=kstack2 if n % 64 == 0 else 1, splits=splits2,
+                     scale_in=(shares, eps))
     torch.testing.assert_close(y.double().cpu(), ref, rtol=2e-2, atol=2e-2 * ref.abs().max().item())
     assert (y.double().cpu() - ref).abs().mean().item() < 4e-3 * ref.abs().max().item()
     g, u = _rand(n2, n, seed=66, dtype=torch.bfloat16, scale=0.1), _rand(n2, n, seed=67, dtype=torch.bfloat16, scale=0.1)
