@@ -20,6 +20,7 @@
 #include <cuda.h>
 
 #include <cstring>
+#include <type_traits>
 
 #include "common.cuh"
 #include "tc_common.cuh"
@@ -412,7 +413,10 @@ struct RowsArgs {
 };
 
 
-template <int BN, int MODE>
+// CLUSTER: the K splits of a tile form a thread-block cluster (gridDim.z blocks).  A kernel of its own, so that
+// the kernels of a decode step, which run one after the other with cold instruction caches, do not carry its
+// epilogue: with it inside, every launch of a step took 1.7 us longer although nothing of it ran.
+template <int BN, int MODE, bool CLUSTER>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tc_rows_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                     const GemmArgs a, const RowsArgs ra) {
@@ -439,7 +443,7 @@ gemm_tc_rows_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int f0 = blockIdx.x * ra.rows_per_block;  // first output feature of this block
   const int split = blockIdx.z;
-  const bool clustered = gridDim.z > 1;
+  constexpr bool clustered = CLUSTER;
   const int total_kb = (a.K + BK - 1) / BK;
   const int kb0 = split * a.k_blocks_per_split;
   const int n_kb = max(0, min(a.k_blocks_per_split, total_kb - kb0));
@@ -612,6 +616,27 @@ gemm_tc_rows_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 #pragma unroll
       for (int j = 0; j < 16; ++j) old16[j] = j < a.M ? ((const float*)a.y)[(int64_t)j * a.ldy + f] : 0.f;
     }
+    // K splits as a cluster: rank r owns the tokens [r * per, r * per + per) of the tile (see below)
+    const int per = (a.M + (int)n_ranks - 1) / (int)n_ranks;
+    const int my_n = max(0, min(per, a.M - (int)my_rank * per));
+    constexpr uint32_t kRowBytes = BM * 4;  // a token's 128 features of the tile
+    // ... and in the owner a warp takes every fourth token and a lane four neighbouring features of the tile
+    const int f4 = f0 + 4 * lane;
+    const bool mine4 = 4 * lane < ra.rows_per_block && f4 < a.N;  // (rows and N are multiples of 4 here)
+    float4 old4[4];
+    float4 w_next4 = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (clustered) {  // what does not depend on the product is fetched while the main loop runs
+      if (et == 0 && my_n > 0) mbar_expect_tx(land_bar, (n_ranks - 1) * (uint32_t)my_n * kRowBytes);
+      if (ahead && mine4) w_next4 = *reinterpret_cast<const float4*>(a.ahead.w + f4);
+      if (MODE == kAccumF32) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int i = quad + 4 * j;
+          old4[j] = (mine4 && i < my_n) ? *reinterpret_cast<const float4*>((const float*)a.y + (int64_t)((int)my_rank * per + i) * a.ldy + f4)
+                                        : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+      }
+    }
     const bool ok = n_kb > 0 && mbar_wait(tmem_full_bar, 0, &abort_flag, a.error_flag, 3);
     if (ok) asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16);
@@ -623,36 +648,24 @@ gemm_tc_rows_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
       // barrier counts in.  (Element-wise remote stores, tried first, take 70 ns each and cannot be
       // overlapped: 4.4 us for 64 tokens, more than streaming the block's weights.)  The owner then
       // adds the splits' values in rank order: one order whatever the batch.
-      const int per = (a.M + (int)n_ranks - 1) / (int)n_ranks;
-      const int my_n = max(0, min(per, a.M - (int)my_rank * per));
-      const uint32_t kRowBytes = BM * 4;  // a token's 128 features of the tile
-      if (et == 0 && my_n > 0 && n_ranks > 1) mbar_expect_tx(land_bar, (n_ranks - 1) * (uint32_t)my_n * kRowBytes);
-      float old[16];
-      const float w_next = (ahead && mine) ? a.ahead.w[f] : 0.f;
-      if (MODE == kAccumF32 && mine) {  // the old values do not depend on the product: fetch them while the main loop runs
-#pragma unroll
-        for (int i = 0; i < 16; ++i)
-          old[i] = i < my_n ? ((const float*)a.y)[(int64_t)((int)my_rank * per + i) * a.ldy + f] : 0.f;
-      }
       const bool warp_reads = ok && quad * 32 < R;  // uniform for the warp
-      // token col lies at slot col of the travelling regions (owner col / per, place col % per: the regions
-      // follow one another), except my own tokens, which go straight to my landing zone
-      const int mine_lo = (int)my_rank * per, mine_hi = mine_lo + my_n;
-      const uint32_t travel = base + 4u * (uint32_t)r_local, home = landing + 4u * (uint32_t)r_local;
-      if (warp_reads) {
-        // all of the tile's columns are asked for at once (a load and its wait take 0.2 us one after the other)
-        uint32_t r[BN];
-#pragma unroll
-        for (int c0 = 0; c0 < BN; c0 += 16)
-          if (c0 < a.M) tmem_ld16(taddr + c0, r + c0);
+      // Token col lies at slot col of the travelling regions (owner col / per, place col % per: the regions
+      // follow one another); this block's own tokens stay there and are read from there.  The epilogue runs
+      // with one warp per scheduler, where every instruction costs its latency, so it is kept to one store per
+      // element at a constant offset: columns past the last token are written too (nobody reads them).
+      const uint32_t travel = base + 4u * (uint32_t)r_local;
+      // (Compact code matters as much as short code here: a kernel of a decode step starts with cold
+      // instruction caches, and every line of straight-line code is a miss of its own.  So: loops.)
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN && warp_reads; c0 += 16) {
+        if (c0 >= a.M) break;
+        uint32_t r[16];
+        tmem_ld16(taddr + c0, r);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        const uint32_t at = travel + (uint32_t)c0 * kRowBytes;
 #pragma unroll
-        for (int col = 0; col < BN; ++col) {
-          if (col < a.M) {
-            const uint32_t at = (col >= mine_lo && col < mine_hi ? home : travel) + (uint32_t)col * kRowBytes;
-            asm volatile("st.shared.b32 [%0], %1;" ::"r"(at), "r"(r[col]) : "memory");
-          }
-        }
+        for (int j = 0; j < 16; ++j)
+          asm volatile("st.shared.b32 [%0], %1;" ::"r"(at + (uint32_t)j * kRowBytes), "r"(r[j]) : "memory");
       }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // these writes, as the bulk copies will read them
       asm volatile("barrier.sync 1, 128;" ::: "memory");
@@ -675,77 +688,65 @@ gemm_tc_rows_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
       }
       bool landed = ok;
       if (landed && my_n > 0 && n_ranks > 1) landed = mbar_wait(land_bar, 0, &abort_flag, a.error_flag, 7);
-      if (et == 0 && landed && my_n > 0) {  // what the peers sent has been taken: they may leave
+      if (et == 32 && landed && my_n > 0) {  // what the peers sent has arrived: they may leave
+        // (relaxed: nothing this thread wrote has to be seen by them, only the copies' end, which the barrier
+        // that let it pass has vouched for; with release semantics each arrival costs 0.35 us)
         for (uint32_t d = 1; d < n_ranks; ++d) {
           uint32_t remote_bar;
           asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote_bar) : "r"(sent_bar), "r"((my_rank + d) % n_ranks));
-          asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(remote_bar) : "memory");
+          asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(remote_bar) : "memory");
         }
       }
-      __shared__ float warp_sq[4][64];  // norm ahead: the warps' shares of the owned tokens' sums of squares
-      // The epilogue runs with one warp per scheduler, so nothing hides a load's latency but more loads: four
-      // tokens' values of all splits are asked for before any is used, then added in rank order.
-      const uint32_t zone = landing + 4u * (uint32_t)r_local;
+      // The owner adds the splits' values in rank order: a warp per token (every fourth), a lane per four
+      // neighbouring features, so that a token's share of a row's sum of squares (norm ahead) is a butterfly in
+      // the warp.  Kept small: this code runs once per block from cold instruction caches.
       const uint32_t rank_stride = (uint32_t)per * kRowBytes;
-      auto finish4 = [&](int i0, const float* before) {
-        float v[4][kRowsMaxSplits];
-#pragma unroll
-        for (int t = 0; t < 4; ++t)
-#pragma unroll
-          for (int src = 0; src < kRowsMaxSplits; ++src) {
-            v[t][src] = 0.f;
-            if (i0 + t < my_n && src < (int)n_ranks)
-              asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v[t][src]) : "r"(zone + (uint32_t)src * rank_stride + (uint32_t)(i0 + t) * kRowBytes));
+      const uint32_t zone = landing + 16u * (uint32_t)lane;                    // [source rank][owned token][feature]
+      const uint32_t own = base + my_rank * rank_stride + 16u * (uint32_t)lane;  // this block's own share of its tokens
+      const bool live = landed && mine4;
+#pragma unroll 1
+      for (int j = 0; quad + 4 * j < my_n; ++j) {
+        const int i = quad + 4 * j, col = (int)my_rank * per + i;
+        float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (live) {
+          for (uint32_t src = 0; src < n_ranks; ++src) {
+            float4 v;
+            asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+                         : "r"((src == my_rank ? own : zone + src * rank_stride) + (uint32_t)i * kRowBytes));
+            sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
           }
-#pragma unroll
-        for (int t = 0; t < 4; ++t) {
-          const int i = i0 + t;
-          if (i >= my_n) break;
-          const int col = (int)my_rank * per + i;
-          float nv = 0.f;
-          if (landed && mine) {
-            float sum = 0.f;
-#pragma unroll
-            for (int src = 0; src < kRowsMaxSplits; ++src) sum += v[t][src];  // the ranks beyond the cluster add zeros
-            if (scaled) sum *= row_inv[col];
-            if (MODE == kStoreBf16) {
-              ((__nv_bfloat16*)a.y)[(int64_t)col * a.ldy + f] = __float2bfloat16_rn(sum);
-            } else if (MODE == kStoreF32) {
-              ((float*)a.y)[(int64_t)col * a.ldy + f] = sum;
-            } else {
-              nv = before[t] + sum;
-              ((float*)a.y)[(int64_t)col * a.ldy + f] = nv;
-              if (ahead) a.ahead.xw[(int64_t)col * a.ahead.ldxw + f] = __float2bfloat16_rn(nv * w_next);
+          if (scaled) { const float r = row_inv[col]; sum.x *= r; sum.y *= r; sum.z *= r; sum.w *= r; }
+        }
+        float sq = 0.f;
+        if (live) {
+          if (MODE == kStoreBf16) {
+            __nv_bfloat162 lo = __floats2bfloat162_rn(sum.x, sum.y), hi = __floats2bfloat162_rn(sum.z, sum.w);
+            *reinterpret_cast<uint2*>((__nv_bfloat16*)a.y + (int64_t)col * a.ldy + f4) =
+                make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+          } else if (MODE == kStoreF32) {
+            *reinterpret_cast<float4*>((float*)a.y + (int64_t)col * a.ldy + f4) = sum;
+          } else {
+            float* p = (float*)a.y + (int64_t)col * a.ldy + f4;
+            const float4 before = j == 0 ? old4[0] : j == 1 ? old4[1] : j == 2 ? old4[2] : j == 3 ? old4[3] : *reinterpret_cast<const float4*>(p);
+            const float4 nv = make_float4(before.x + sum.x, before.y + sum.y, before.z + sum.z, before.w + sum.w);
+            *reinterpret_cast<float4*>(p) = nv;
+            if (ahead) {
+              __nv_bfloat162 lo = __floats2bfloat162_rn(nv.x * w_next4.x, nv.y * w_next4.y);
+              __nv_bfloat162 hi = __floats2bfloat162_rn(nv.z * w_next4.z, nv.w * w_next4.w);
+              *reinterpret_cast<uint2*>(a.ahead.xw + (int64_t)col * a.ahead.ldxw + f4) =
+                  make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+              sq = nv.x * nv.x + nv.y * nv.y + nv.z * nv.z + nv.w * nv.w;
             }
           }
-          if (ahead) {  // uniform for the block
-            float sq = nv * nv;
-            sq += __shfl_xor_sync(0xffffffffu, sq, 16);
-            sq += __shfl_xor_sync(0xffffffffu, sq, 8);
-            sq += __shfl_xor_sync(0xffffffffu, sq, 4);
-            sq += __shfl_xor_sync(0xffffffffu, sq, 2);
-            sq += __shfl_xor_sync(0xffffffffu, sq, 1);
-            if (lane == 0) warp_sq[quad][i] = sq;
-          }
         }
-      };
-#pragma unroll
-      for (int i0 = 0; i0 < 16; i0 += 4)
-        if (i0 < my_n) finish4(i0, old + i0);
-      for (int i0 = 16; i0 < my_n; i0 += 4) {  // a block that owns more than 16 tokens (two splits of a wide tile)
-        float before[4] = {0.f, 0.f, 0.f, 0.f};
-        if (MODE == kAccumF32 && landed && mine) {
-#pragma unroll
-          for (int t = 0; t < 4; ++t)
-            if (i0 + t < my_n) before[t] = ((const float*)a.y)[(int64_t)((int)my_rank * per + i0 + t) * a.ldy + f];
+        if (ahead) {  // uniform for the block: this tile's share of the token's sum of squares, in one fixed order
+          sq += __shfl_xor_sync(0xffffffffu, sq, 16);
+          sq += __shfl_xor_sync(0xffffffffu, sq, 8);
+          sq += __shfl_xor_sync(0xffffffffu, sq, 4);
+          sq += __shfl_xor_sync(0xffffffffu, sq, 2);
+          sq += __shfl_xor_sync(0xffffffffu, sq, 1);
+          if (lane == 0 && landed) a.ahead.ssq_part[(int64_t)blockIdx.x * a.M + col] = sq;
         }
-        finish4(i0, before);
-      }
-      if (ahead) {
-        asm volatile("barrier.sync 1, 128;" ::: "memory");
-        if (et < my_n && landed)
-          a.ahead.ssq_part[(int64_t)blockIdx.x * a.M + (int)my_rank * per + et] =
-              warp_sq[0][et] + warp_sq[1][et] + warp_sq[2][et] + warp_sq[3][et];
       }
     } else if (kstack > 1) {
       // lane L of the accumulator is row L % R of K-block group L / R; its partial products are the
@@ -912,7 +913,8 @@ int launch_rows(const CUtensorMap& mw, const CUtensorMap& mx, const GemmArgs& a,
   const int stage = kkb * (kATiles * rows_per_block * BK * 2 + BN * BK * 2);
   // behind the ring: the landing zone of the cluster epilogue or the stacked epilogue's sums, which
   // also is the room that the MMA, reading 128 rows whatever R is, may run into
-  int landing = splits > 1 ? (BN + splits - 1) / splits * splits * BM * 4 : 0;  // [source rank][owned token][128]
+  // [source rank][owned token][128 features], and four tokens' room behind it: the owner reads four at a time
+  int landing = splits > 1 ? ((BN + splits - 1) / splits * splits + 4) * BM * 4 : 0;
   if (kstack > 1) landing = kstack * BN * rows_per_block * 4;
   if (a.ahead.xw != nullptr) landing += BN * rows_per_block * 4;  // the squares of the new rows
   const int over_read = (BM - kstack * rows_per_block) * BK * 2;
@@ -924,19 +926,35 @@ int launch_rows(const CUtensorMap& mw, const CUtensorMap& mx, const GemmArgs& a,
   if (splits > 1 && ra.n_stages * stage < landing)  // the splits' tiles wait in the idle ring for their bulk copies
     return fail(kBadArgument, "gemm_tc_rows: a ring of %d bytes is too small for the K splits' tiles", ra.n_stages * stage);
   const int smem = fixed + ra.n_stages * stage;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tc_rows_kernel<BN, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         kRowsSmemBytes);
-    if (e != cudaSuccess) return fail(kLaunchFailed, "gemm_tc_rows: cannot reserve shared memory: %s", cudaGetErrorString(e));
-    configured = true;
-  }
   const dim3 grid((a.N + rows_per_block - 1) / rows_per_block, 1, splits);
-  if (splits > 1)
-    launch_overlapped_cluster(gemm_tc_rows_kernel<BN, MODE>, grid, dim3(kThreads), (size_t)smem, stream,
+  if (splits > 1) {
+    if (MODE == kGluBf16) return fail(kBadArgument, "gemm_tc_rows: the gated product takes one K split");
+    // the owners of a cluster write four neighbouring outputs of a token at once
+    const int ybytes = MODE == kStoreBf16 ? 2 : 4;
+    if (a.N % 4 || a.ldy % 4 || ((uintptr_t)a.y) % (4 * ybytes) ||
+        (a.ahead.xw != nullptr && (a.ahead.ldxw % 4 || ((uintptr_t)a.ahead.xw) % 8 || ((uintptr_t)a.ahead.w) % 16)))
+      return fail(kBadArgument, "gemm_tc_rows: K splits want the outputs in fours: N=%d, rows of y and of the norm-ahead "
+                  "buffer in multiples of 4 elements, 16-byte aligned (8 for bfloat16)", a.N);
+    constexpr int M2 = MODE == kGluBf16 ? kStoreBf16 : MODE;  // (the gated instance is never built)
+    static bool configured = false;
+    if (!configured) {
+      cudaError_t e = cudaFuncSetAttribute(gemm_tc_rows_kernel<BN, M2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           kRowsSmemBytes);
+      if (e != cudaSuccess) return fail(kLaunchFailed, "gemm_tc_rows: cannot reserve shared memory: %s", cudaGetErrorString(e));
+      configured = true;
+    }
+    launch_overlapped_cluster(gemm_tc_rows_kernel<BN, M2, true>, grid, dim3(kThreads), (size_t)smem, stream,
                               (unsigned)splits, mw, mx, a, ra);
-  else
-    launch_overlapped(gemm_tc_rows_kernel<BN, MODE>, grid, dim3(kThreads), (size_t)smem, stream, mw, mx, a, ra);
+  } else {
+    static bool configured = false;
+    if (!configured) {
+      cudaError_t e = cudaFuncSetAttribute(gemm_tc_rows_kernel<BN, MODE, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           kRowsSmemBytes);
+      if (e != cudaSuccess) return fail(kLaunchFailed, "gemm_tc_rows: cannot reserve shared memory: %s", cudaGetErrorString(e));
+      configured = true;
+    }
+    launch_overlapped(gemm_tc_rows_kernel<BN, MODE, false>, grid, dim3(kThreads), (size_t)smem, stream, mw, mx, a, ra);
+  }
   return check_launch("gemm_tc_rows");
 }
 
@@ -1006,6 +1024,31 @@ extern "C" int skyla_tensor_map_bf16(void* out, const void* ptr, uint64_t rows, 
   if (r != CUDA_SUCCESS) return fail(kLaunchFailed, "tensor map: cuTensorMapEncodeTiled failed with %d", (int)r);
   memcpy(out, &m, sizeof(m));
   return kOk;
+}
+
+// How many clusters of `cluster` blocks of the weight-streaming kernel the current device holds at a time
+// (one block per SM, clusters inside a GPC): a product whose tiles x K splits exceed it runs in two waves.
+// Returns the count, or a negative error code.
+extern "C" int skyla_gemm_tc_rows_max_clusters(int cluster) {
+  if (cluster < 1 || cluster > kRowsMaxSplits) return fail(kBadArgument, "gemm_tc_rows: clusters of %d blocks", cluster);
+  auto kernel = gemm_tc_rows_kernel<64, kAccumF32, true>;
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kRowsSmemBytes);
+  if (e != cudaSuccess) return fail(kLaunchFailed, "gemm_tc_rows: cannot reserve shared memory: %s", cudaGetErrorString(e));
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(1024, 1, cluster);
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = kRowsSmemBytes - 4096;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = cluster;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  int n = 0;
+  e = cudaOccupancyMaxActiveClusters(&n, kernel, &cfg);
+  if (e != cudaSuccess) return fail(kLaunchFailed, "gemm_tc_rows: cudaOccupancyMaxActiveClusters: %s", cudaGetErrorString(e));
+  return n;
 }
 
 extern "C" int skyla_gemm_tc_stages(int bn, int mode) {

@@ -419,6 +419,50 @@ ROWS_MAX_TOKENS = 64
 ROWS_MAX_SPLITS = 8
 
 
+_CLUSTER_ROOM = {}
+
+
+def rows_cluster_room(device) -> dict:
+    """{blocks per cluster: clusters that the device holds at a time} for the weight-streaming kernel,
+    asked from the occupancy calculator once per device (clusters stay inside a GPC, so it is less
+    than SMs / size: on a B200 33 clusters of four)."""
+    dev = torch.device(device)
+    room = _CLUSTER_ROOM.get(dev)
+    if room is None:
+        f = _fn("gemm_tc", "skyla_gemm_tc_rows_max_clusters", [c_int])
+        room = {}
+        with torch.cuda.device(dev):
+            for size in (2, 4):
+                n = int(f(size))
+                if n < 0:
+                    _check_nolaunch("gemm_tc", n)
+                room[size] = n
+        _CLUSTER_ROOM[dev] = room
+    return room
+
+
+def rows_cluster_plan(n_out: int, n_in: int, bn: int, room: dict):
+    """The plan for 17 to 64 tokens of a product that is not gated: tiles of up to 128 rows whose K is
+    cut into a cluster of 2 or 4 splits, chosen so that all blocks run at once (``room``: clusters of
+    each size that fit) and a block moves as few bytes as possible (its share of the weight and of the
+    tokens' rows, which every tile reads whole).  ``None`` where K is too short to cut."""
+    if n_in % 64 or n_out % 4:  # (the owners of a cluster write four neighbouring outputs at once)
+        return None
+    n_kb = n_in // 64
+    best, best_cost = None, None
+    for splits in (2, 4):
+        if n_kb < 8 * splits or room.get(splits, 0) < 1:
+            continue
+        rows = -(-n_out // room[splits])              # the fewest rows whose tiles fit at once
+        rows = max(8, -(-rows // 8) * 8)
+        if rows > 128:
+            continue
+        cost = (rows + bn) * -(-n_kb // splits)
+        if best_cost is None or cost < best_cost:
+            best, best_cost = (rows, splits, 2, 1), cost
+    return best
+
+
 def rows_plan(n_out: int, n_in: int, gated: bool = False, bn: int = 16, n_sms: int = 148):
     """(rows per block, K splits, K blocks per box, K blocks per MMA) for the few-token product
     of a weight [n_out (x2 when gated), n_in] with token tiles of ``bn``.

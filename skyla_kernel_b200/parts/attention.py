@@ -137,9 +137,9 @@ class GQAttention(Part):
     def forward(self, ctx, h, x: torch.Tensor, entry) -> None:
         n = ctx.n_tokens
         state = self.rt.kernel_state
-        # few tokens: the QKV product leaves whole float32 rows, which the kernels after it finish
-        few = (entry.owns_cache and n <= self.qkv.STACKED_MAX_TOKENS and self.qkv.tensor_cores
-               and self.rt.act_dtype == torch.bfloat16)
+        # few tokens (the weight-streaming product takes them): it leaves whole float32 rows, which the
+        # kernels after it finish
+        few = entry.owns_cache and self.qkv.streams(n) and self.rt.act_dtype == torch.bfloat16
         scale_in = None
         if isinstance(h, NormedInput):
             if ((few or (entry.owns_cache and self.qkv.prompts(n))) and h.ahead is not None
@@ -160,8 +160,10 @@ class GQAttention(Part):
             self.qkv.forward(h, whole[0], STORE, scale_in=scale_in)
             ctx.mark("matvec qkv")
             pend = ctx.take_pending()
-            if (pend is None and self._fast == 2 and ctx.is_decode and k_pool.dtype == torch.bfloat16
-                    and self.rt.act_dtype == torch.bfloat16):
+            # (up to 16 sequences; with more, every block's repeating the preparation costs more than the
+            # kernel it saves: 7,560 against 7,800 to 7,980 tokens/s at batch 64)
+            if (pend is None and self._fast == 2 and ctx.is_decode and n <= self.qkv.STACKED_MAX_TOKENS
+                    and k_pool.dtype == torch.bfloat16 and self.rt.act_dtype == torch.bfloat16):
                 # one new token per sequence: its q, k and v are finished inside the attention kernel
                 attn = ctx.buffer("attn.out", (n, nq * hd), self.rt.act_dtype)
                 n_splits, per = self.decode_splits(ctx.n_seqs, pages.shape[1])

@@ -50,6 +50,9 @@ class Runtime:
     #: streaming multiprocessors of the device; asked from the device when not given (a runtime on
     #: a device without them, as the dispatch tests build, has to say which machine it stands for)
     n_sms: Optional[int] = None
+    #: {blocks per cluster: clusters of the weight-streaming kernel that run at a time}; asked from the device
+    #: when not given
+    cluster_room: Optional[dict] = None
 
     def __post_init__(self):
         if self.dtype in ("fp32", "float"):
@@ -70,6 +73,15 @@ class Runtime:
                 raise ValueError("a runtime that is not on a CUDA device must be given its number of SMs")
             self.n_sms = torch.cuda.get_device_properties(self.device).multi_processor_count
         return self.n_sms
+
+    @property
+    def clusters(self) -> dict:
+        if self.cluster_room is None:
+            if self.device.type != "cuda":
+                raise ValueError("a runtime that is not on a CUDA device must be given its room for clusters")
+            from ..kernels.ops import rows_cluster_room
+            self.cluster_room = rows_cluster_room(self.device)
+        return self.cluster_room
 
     @property
     def kernel_state(self):

@@ -19,10 +19,11 @@ class Linear:
 
     #: inputs from which a product of 65 to 128 tokens goes to the prompt kernel
     PROMPT_LONG_K = 8192
-    #: the weight-streaming kernel takes over up to this many tokens ...
+    #: the weight-streaming kernel takes over up to this many tokens: with tall tiles (gated products,
+    #: products of many waves) or with tiles whose K is cut into a cluster of splits ...
     ROWS_MAX_TOKENS = 64
-    #: ... but where its blocks each read every token's whole row (short tiles, no K split) only
-    #: up to this many: beyond, the token rows outweigh the block's weights
+    #: ... but where its blocks each read every token's whole row (short tiles, K blocks stacked, no K
+    #: split) only up to this many: beyond, the token rows outweigh the block's weights
     STACKED_MAX_TOKENS = 16
 
     def __init__(self, weight: torch.Tensor, rt, gated: bool = False):
@@ -34,11 +35,20 @@ class Linear:
         self.n_out = weight.shape[0] // 2 if gated else weight.shape[0]
         self._map = None
         self._rows_maps = {}
+        self.tensor_cores = (not rt.full_precision and weight.dtype == torch.bfloat16 and self.n_in % 8 == 0
+                             and weight.is_contiguous() and weight.data_ptr() % 16 == 0)
         #: token tile -> (rows per block, K splits, K blocks per box, K blocks per MMA) of the weight-streaming kernel
         self.rows_plans = {bn: ops.rows_plan(self.n_out, self.n_in, gated, bn, rt.sm_count) for bn in (16, 32, 64)}
         self.streams_wide = self.rows_plans[64][0] > 64  # tall tiles: gated products, many-wave products
-        self.tensor_cores = (not rt.full_precision and weight.dtype == torch.bfloat16 and self.n_in % 8 == 0
-                             and weight.is_contiguous() and weight.data_ptr() % 16 == 0)
+        if self.tensor_cores and not self.streams_wide and not gated:
+            # 17 to 64 tokens: tiles whose K is cut into a cluster of splits, where K is long enough to cut
+            for bn in (32, 64):
+                plan = ops.rows_cluster_plan(self.n_out, self.n_in, bn, rt.clusters)
+                if plan is not None:
+                    self.rows_plans[bn] = plan
+        #: the most tokens that the weight-streaming kernel takes for this weight
+        self.rows_limit = (self.ROWS_MAX_TOKENS if self.streams_wide or all(self.rows_plans[bn][1] > 1 for bn in (32, 64))
+                           else self.STACKED_MAX_TOKENS)
 
     def weight_map(self):
         if self._map is None:
@@ -47,7 +57,7 @@ class Linear:
 
     def streams(self, m: int) -> bool:
         """Whether ``m`` tokens go to the weight-streaming kernel (given operands it takes)."""
-        return self.tensor_cores and m <= (self.ROWS_MAX_TOKENS if self.streams_wide else self.STACKED_MAX_TOKENS)
+        return self.tensor_cores and m <= self.rows_limit
 
     def prompts(self, m: int) -> bool:
         """Whether ``m`` tokens go to the prompt kernel (tokens are the tile's rows; given operands it takes)."""
@@ -104,9 +114,8 @@ class Linear:
             tc = {GATED: ops.TC_GLU_BF16, ACCUMULATE: ops.TC_ACCUM_F32}.get(
                 mode, ops.TC_STORE_BF16 if y.dtype == torch.bfloat16 else ops.TC_STORE_F32)
             if self.streams(m):
-                rows, splits = self.rows_plans[ops.token_tile(m)][:2]
-                norm, ahead = (self._norm_ahead(ctx, x, y, -(-self.n_out // rows) if splits == 1 else 0)
-                               if mode == ACCUMULATE else (None, None))
+                rows = self.rows_plans[ops.token_tile(m)][0]
+                norm, ahead = self._norm_ahead(ctx, x, y, -(-self.n_out // rows)) if mode == ACCUMULATE else (None, None)
                 self._stream(x, y, tc, norm_ahead=ahead, scale_in=scale_in)
                 if ahead is not None:
                     ctx.ahead = (norm, y, ahead[1], ahead[2])

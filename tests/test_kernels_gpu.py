@@ -563,7 +563,7 @@ def test_prep_adds_up_partial_sums():
 # ----------------------------------------------- few tokens: the weight-streaming product
 @pytest.mark.parametrize("m,n,k,rows,kkb,splits,kstack", [
     (1, 128, 64, 128, 1, 1, 1), (8, 4096, 4096, 56, 2, 2, 1), (5, 1000, 264, 8, 1, 1, 1), (16, 300, 1032, 24, 1, 3, 1),
-    (11, 130, 8192, 16, 2, 8, 1), (33, 520, 704, 104, 2, 2, 1), (64, 392, 512, 40, 4, 2, 1), (64, 392, 520, 40, 1, 5, 1),
+    (11, 132, 8192, 16, 2, 8, 1), (33, 520, 704, 104, 2, 2, 1), (64, 392, 512, 40, 4, 2, 1), (64, 392, 520, 40, 1, 5, 1),
     (8, 4096, 12288, 112, 2, 4, 1), (3, 200, 1536, 72, 3, 4, 1),
     (8, 4096, 4096, 32, 8, 1, 4), (8, 6144, 4096, 48, 6, 1, 2), (16, 300, 1088, 24, 10, 1, 5), (1, 100, 704, 8, 16, 1, 16),
     (33, 520, 704, 40, 6, 1, 3), (64, 392, 1536, 32, 4, 1, 4), (50, 200, 960, 56, 4, 1, 2), (8, 4096, 12288, 32, 8, 1, 4)])
@@ -680,6 +680,9 @@ def test_gemm_tc_rows_refuses():
         ops.gemm_tc_rows(x[:4], ops.TensorMap(w, 128), 128, 128, torch.empty(4, 128, device=DEV), ops.TC_PARTIAL_F32)
     with pytest.raises(KernelError):  # more splits than K blocks
         ops.gemm_tc_rows(x[:4], ops.TensorMap(w, 128), 128, 128, torch.empty(4, 128, device=DEV), ops.TC_STORE_F32, splits=2)
+    with pytest.raises(KernelError, match="outputs in fours"):  # K splits of a width that is no multiple of four
+        ops.gemm_tc_rows(_rand(4, 256, seed=4, dtype=torch.bfloat16), ops.TensorMap(_rand(130, 256, seed=5, dtype=torch.bfloat16), 128),
+                         128, 130, torch.empty(4, 130, device=DEV), ops.TC_STORE_F32, splits=2)
     with pytest.raises(KernelError):  # boxes of several K blocks over a width that is no multiple of 64
         ops.TensorMap(_rand(128, 72, seed=3, dtype=torch.bfloat16), 128, 2)
 

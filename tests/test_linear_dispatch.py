@@ -13,7 +13,8 @@ def _lin(n_out, n_in, gated=False, dtype="bfloat16"):
     # a meta tensor: only its shape, dtype and (absent) address are looked at
     rows = 2 * n_out if gated else n_out
     w = torch.empty(rows, n_in, dtype=torch.bfloat16 if dtype == "bfloat16" else torch.float32, device="meta")
-    return Linear(w, Runtime(torch.device("cpu"), dtype, n_sms=148), gated=gated)  # the machine the decisions are checked for
+    # the machine the decisions are checked for: a B200's SMs and its room for clusters of two and four blocks
+    return Linear(w, Runtime(torch.device("cpu"), dtype, n_sms=148, cluster_room={2: 72, 4: 33}), gated=gated)
 
 
 def test_few_tokens_stream_the_weight_and_many_go_to_the_prompt_kernel():
@@ -23,9 +24,20 @@ def test_few_tokens_stream_the_weight_and_many_go_to_the_prompt_kernel():
         assert all(lin.streams(m) for m in (1, 8, 16))
         assert all(lin.prompts(m) and not lin.streams(m) for m in (129, 2048))
         assert all(lin.takes_scale_in(m) for m in (1, 16, 129, 4096))
-    # 17 to 64 tokens: only the tall tiles of the gated product still stream
+    # 17 to 64 tokens: the tall tiles of the gated product still stream; the others stream as tiles whose K is
+    # cut into a cluster of splits, all of whose blocks run at once
     assert gate_up.streams(17) and gate_up.streams(64) and not gate_up.streams(65)
-    assert not any(lin.streams(17) for lin in (qkv, o, down))
+    for lin in (qkv, o, down):
+        assert lin.streams(17) and lin.streams(64) and not lin.streams(65)
+        for bn in (32, 64):
+            rows, splits, kkb, kstack = lin.rows_plans[bn]
+            assert splits in (2, 4) and kstack == 1 and rows % 8 == 0 and rows <= 128
+            assert -(-lin.n_out // rows) <= {2: 72, 4: 33}[splits]
+        assert lin.rows_plans[16][1] == 1          # up to 16 tokens: short tiles, K blocks stacked, no split
+    assert o.rows_plans[64][:2] == (128, 4) and down.rows_plans[64][:2] == (128, 4) and qkv.rows_plans[64][1] == 2
+    # a reduction too short to cut stays with the kernels it had
+    short = _lin(H, 512)
+    assert short.streams(16) and not short.streams(17)
     # 65 to 128 tokens: only the product with the long reduction goes to the prompt kernel
     assert down.prompts(65) and down.prompts(128)
     assert not any(lin.prompts(m) for lin in (qkv, o, gate_up) for m in (65, 128))
