@@ -413,10 +413,13 @@ struct RowsArgs {
 };
 
 
-// CLUSTER: the K splits of a tile form a thread-block cluster (gridDim.z blocks).  A kernel of its own, so that
-// the kernels of a decode step, which run one after the other with cold instruction caches, do not carry its
-// epilogue: with it inside, every launch of a step took 1.7 us longer although nothing of it ran.
-template <int BN, int MODE, bool CLUSTER>
+// KIND: kPlain (whole K in one block, one K block an MMA), kCluster (the K splits of a tile form a thread-block
+// cluster of gridDim.z blocks) or kStacked (whole K, several K blocks stacked into one MMA).  Kernels of their
+// own, so that the kernels of a decode step, which run one after the other with cold instruction caches, carry
+// one epilogue each: with the cluster's epilogue inside, every launch of a step took 1.7 us longer although
+// nothing of it ran.
+enum RowsKind : int { kPlain = 0, kCluster = 1, kStacked = 2 };
+template <int BN, int MODE, int KIND>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tc_rows_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                     const GemmArgs a, const RowsArgs ra) {
@@ -443,7 +446,8 @@ gemm_tc_rows_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int f0 = blockIdx.x * ra.rows_per_block;  // first output feature of this block
   const int split = blockIdx.z;
-  constexpr bool clustered = CLUSTER;
+  constexpr bool clustered = KIND == kCluster;
+  constexpr bool stacked = KIND == kStacked;
   const int total_kb = (a.K + BK - 1) / BK;
   const int kb0 = split * a.k_blocks_per_split;
   const int n_kb = max(0, min(a.k_blocks_per_split, total_kb - kb0));
@@ -535,7 +539,7 @@ gemm_tc_rows_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      const int kstack = ra.kstack;
+      const int kstack = stacked ? ra.kstack : 1;
       const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)((kstack * BN) >> 3) << 17) |
                              ((uint32_t)(BM >> 4) << 24);
       int s = 0;
@@ -595,13 +599,13 @@ gemm_tc_rows_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
       asm volatile("barrier.sync 1, 128;" ::: "memory");
     }
     const bool ahead = MODE == kAccumF32 && a.ahead.xw != nullptr;
-    const int kstack = ra.kstack, R = ra.rows_per_block;
+    const int kstack = stacked ? ra.kstack : 1, R = ra.rows_per_block;
     float* red = reinterpret_cast<float*>(smem_raw + (landing - smem_u32(smem_raw)));
-    float* sqbuf = red + (kstack > 1 ? kstack * BN * R : 0);  // [tok][row of the tile]: squares of the new x
+    float* sqbuf = red + (stacked ? kstack * BN * R : 0);  // [tok][row of the tile]: squares of the new x
     bool ssq_in_warp = false;
     // the old values of y do not depend on the product: fetch them while the main loop runs
     float old_pre[4] = {0.f, 0.f, 0.f, 0.f}, wn_pre[4] = {0.f, 0.f, 0.f, 0.f}, old16[16];
-    if (MODE == kAccumF32 && kstack > 1) {
+    if (MODE == kAccumF32 && stacked) {
 #pragma unroll
       for (int n = 0; n < 4; ++n) {
         const int idx = et + 128 * n;
@@ -612,7 +616,7 @@ gemm_tc_rows_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         }
       }
     }
-    if (MODE == kAccumF32 && kstack == 1 && !clustered && mine) {
+    if (MODE == kAccumF32 && !stacked && !clustered && mine) {
 #pragma unroll
       for (int j = 0; j < 16; ++j) old16[j] = j < a.M ? ((const float*)a.y)[(int64_t)j * a.ldy + f] : 0.f;
     }
@@ -748,7 +752,7 @@ gemm_tc_rows_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
           if (lane == 0 && landed) a.ahead.ssq_part[(int64_t)blockIdx.x * a.M + col] = sq;
         }
       }
-    } else if (kstack > 1) {
+    } else if (stacked) {
       // lane L of the accumulator is row L % R of K-block group L / R; its partial products are the
       // columns [q*BN, q*BN + BN) of its own group q.  red[(q*BN + tok)*R + r], then a sum over q.
       if (ok) {
@@ -811,7 +815,7 @@ gemm_tc_rows_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         }
       }
     }
-    const bool warp_has_rows = ok && kstack == 1 && !clustered && quad * 32 < R;  // uniform for the warp
+    const bool warp_has_rows = ok && !stacked && !clustered && quad * 32 < R;  // uniform for the warp
 #pragma unroll 1
     for (int c0 = 0; c0 < BN && warp_has_rows; c0 += 16) {
       if (c0 >= a.M) break;
@@ -927,6 +931,7 @@ int launch_rows(const CUtensorMap& mw, const CUtensorMap& mx, const GemmArgs& a,
     return fail(kBadArgument, "gemm_tc_rows: a ring of %d bytes is too small for the K splits' tiles", ra.n_stages * stage);
   const int smem = fixed + ra.n_stages * stage;
   const dim3 grid((a.N + rows_per_block - 1) / rows_per_block, 1, splits);
+  constexpr int M2 = MODE == kGluBf16 ? kStoreBf16 : MODE;  // (no gated instance of the cluster and stacked kernels is built)
   if (splits > 1) {
     if (MODE == kGluBf16) return fail(kBadArgument, "gemm_tc_rows: the gated product takes one K split");
     // the owners of a cluster write four neighbouring outputs of a token at once
@@ -935,25 +940,34 @@ int launch_rows(const CUtensorMap& mw, const CUtensorMap& mx, const GemmArgs& a,
         (a.ahead.xw != nullptr && (a.ahead.ldxw % 4 || ((uintptr_t)a.ahead.xw) % 8 || ((uintptr_t)a.ahead.w) % 16)))
       return fail(kBadArgument, "gemm_tc_rows: K splits want the outputs in fours: N=%d, rows of y and of the norm-ahead "
                   "buffer in multiples of 4 elements, 16-byte aligned (8 for bfloat16)", a.N);
-    constexpr int M2 = MODE == kGluBf16 ? kStoreBf16 : MODE;  // (the gated instance is never built)
     static bool configured = false;
     if (!configured) {
-      cudaError_t e = cudaFuncSetAttribute(gemm_tc_rows_kernel<BN, M2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+      cudaError_t e = cudaFuncSetAttribute(gemm_tc_rows_kernel<BN, M2, kCluster>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                            kRowsSmemBytes);
       if (e != cudaSuccess) return fail(kLaunchFailed, "gemm_tc_rows: cannot reserve shared memory: %s", cudaGetErrorString(e));
       configured = true;
     }
-    launch_overlapped_cluster(gemm_tc_rows_kernel<BN, M2, true>, grid, dim3(kThreads), (size_t)smem, stream,
+    launch_overlapped_cluster(gemm_tc_rows_kernel<BN, M2, kCluster>, grid, dim3(kThreads), (size_t)smem, stream,
                               (unsigned)splits, mw, mx, a, ra);
+  } else if (kstack > 1) {
+    if (MODE == kGluBf16) return fail(kBadArgument, "gemm_tc_rows: the gated product does not stack K blocks");
+    static bool configured = false;
+    if (!configured) {
+      cudaError_t e = cudaFuncSetAttribute(gemm_tc_rows_kernel<BN, M2, kStacked>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           kRowsSmemBytes);
+      if (e != cudaSuccess) return fail(kLaunchFailed, "gemm_tc_rows: cannot reserve shared memory: %s", cudaGetErrorString(e));
+      configured = true;
+    }
+    launch_overlapped(gemm_tc_rows_kernel<BN, M2, kStacked>, grid, dim3(kThreads), (size_t)smem, stream, mw, mx, a, ra);
   } else {
     static bool configured = false;
     if (!configured) {
-      cudaError_t e = cudaFuncSetAttribute(gemm_tc_rows_kernel<BN, MODE, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+      cudaError_t e = cudaFuncSetAttribute(gemm_tc_rows_kernel<BN, MODE, kPlain>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                            kRowsSmemBytes);
       if (e != cudaSuccess) return fail(kLaunchFailed, "gemm_tc_rows: cannot reserve shared memory: %s", cudaGetErrorString(e));
       configured = true;
     }
-    launch_overlapped(gemm_tc_rows_kernel<BN, MODE, false>, grid, dim3(kThreads), (size_t)smem, stream, mw, mx, a, ra);
+    launch_overlapped(gemm_tc_rows_kernel<BN, MODE, kPlain>, grid, dim3(kThreads), (size_t)smem, stream, mw, mx, a, ra);
   }
   return check_launch("gemm_tc_rows");
 }
@@ -1031,7 +1045,7 @@ extern "C" int skyla_tensor_map_bf16(void* out, const void* ptr, uint64_t rows, 
 // Returns the count, or a negative error code.
 extern "C" int skyla_gemm_tc_rows_max_clusters(int cluster) {
   if (cluster < 1 || cluster > kRowsMaxSplits) return fail(kBadArgument, "gemm_tc_rows: clusters of %d blocks", cluster);
-  auto kernel = gemm_tc_rows_kernel<64, kAccumF32, true>;
+  auto kernel = gemm_tc_rows_kernel<64, kAccumF32, kCluster>;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kRowsSmemBytes);
   if (e != cudaSuccess) return fail(kLaunchFailed, "gemm_tc_rows: cannot reserve shared memory: %s", cudaGetErrorString(e));
   cudaLaunchConfig_t cfg = {};

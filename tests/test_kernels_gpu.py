@@ -604,7 +604,7 @@ def test_gemm_tc_rows_store_accumulate_gated(m, n, k, rows, kkb, splits, kstack)
     (8, 4096, 4096, 32, 8, 4, 6144, 48, 6, 2), (5, 264, 520, 24, 1, 1, 200, 72, 1, 1), (16, 328, 704, 40, 6, 3, 136, 8, 16, 16),
     (1, 128, 64, 128, 1, 1, 128, 128, 1, 1), (11, 1000, 1536, 56, 4, 2, 520, 88, 2, 1),
     # K cut into a cluster of splits on either side (kstack = -splits): 17 to 64 tokens are served so
-    (64, 4096, 4096, 128, 2, -4, 6144, 96, 2, -2), (40, 520, 1088, 104, 1, -3, 200, 72, 2, -2), (17, 328, 704, 40, 2, -2, 136, 128, 1, -8),
+    (64, 4096, 4096, 128, 2, -4, 6144, 96, 2, -2), (40, 520, 1088, 104, 1, -3, 200, 72, 2, -2), (17, 328, 704, 40, 2, -2, 136, 128, 1, -3),
     (3, 264, 640, 24, 1, -4, 264, 24, 1, -5)])
 def test_gemm_tc_rows_norm_ahead_then_scale_in(m, n, k, rows, kkb, kstack, n2, rows2, kkb2, kstack2):
     """x += a W^T leaves x * norm weight in bfloat16 and the blocks' shares of the rows' sums of
