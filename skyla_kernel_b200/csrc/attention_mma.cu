@@ -325,14 +325,12 @@ __device__ __forceinline__ void stage_page(bf16* stage, const bf16* __restrict__
 
 // ------------------------------------------------------------------------ decode
 // The new token's q, k and v made inside the decode kernel instead of by a kernel before it:
-// `qkv` holds K-split partial sums [n_splits][tokens][ld] of the QKV product of un-scaled
-// rows and `ssq` each split's share of the rows' sums of squares (see gemm_tc.cu); every
+// `qkv` holds the rows [tokens][ld] of the QKV product in 32-bit; every
 // block finishes the q heads of its group (row scalar, per-head RMSNorm, rotation), and the
 // block whose pages end at the token's own position also finishes k and v, writes them to
 // the cache and patches them into the page it has staged.
 struct FusedPrep {
-  const float* qkv; int n_splits; int64_t split_stride, ld; int q_off, k_off, v_off;
-  const float* ssq; int n_ssq; int norm_width; float norm_eps;
+  const float* qkv; int64_t ld; int q_off, k_off, v_off;
   const float* q_norm; const float* k_norm; float eps; const float* cos_t; const float* sin_t; int n_rot;
   bf16* k_pool; bf16* v_pool; int n_tokens;
 };
@@ -403,12 +401,6 @@ __global__ void __launch_bounds__(kDecodeWarps * 32, 2) attn_decode_kernel(Decod
   if (fused) {
     float* u = reinterpret_cast<float*>(fresh + (size_t)(G + 2) * HD) + (size_t)warp * HD;
     const FusedPrep& p = a.prep;
-    float row_scale = 1.0f;  // no sums of squares: the rows came finished
-    if (p.ssq != nullptr) {
-      float ssq = 0.f;
-      for (int sp = 0; sp < p.n_ssq; ++sp) ssq += p.ssq[(int64_t)sp * p.n_tokens + b];
-      row_scale = 1.0f / sqrtf(ssq / (float)p.norm_width + p.norm_eps);
-    }
     for (int job = warp; job < G + 2; job += NW) {  // q heads of the group, then k, then v
       if (job >= G && !owner) continue;
       const bool is_q = job < G, is_k = job == G;
@@ -416,9 +408,7 @@ __global__ void __launch_bounds__(kDecodeWarps * 32, 2) attn_decode_kernel(Decod
                          (is_q ? p.q_off + (kvh * G + job) * HD : (is_k ? p.k_off : p.v_off) + kvh * HD);
       float ss = 0.f;
       for (int e = lane; e < HD; e += 32) {
-        float v = src[e];
-        for (int sp = 1; sp < p.n_splits; ++sp) v += src[(int64_t)sp * p.split_stride + e];
-        v *= row_scale;
+        const float v = src[e];
         u[e] = v;
         ss = fmaf(v, v, ss);
       }
@@ -770,13 +760,11 @@ extern "C" int skyla_attention_decode(const void* q, int64_t ldq, void* out, int
   return check_launch("attention_merge");
 }
 
-// Decode with the new token's q, k and v finished inside the kernel: `qkv` are the K-split
-// partial sums [qkv_splits][n_seqs][ld] (float) of the QKV product of un-scaled rows, `ssq`
-// [n_ssq][n_seqs] the splits' shares of the rows' sums of squares over `norm_width` inputs.
-// k and v of the new token are written to the pools (which this call therefore changes).
+// Decode with the new token's q, k and v finished inside the kernel: `qkv` are the rows [n_seqs][ld]
+// (float) of the QKV product.  k and v of the new token are written to the pools (which this call
+// therefore changes).
 extern "C" int skyla_attention_decode_fused(
-    const float* qkv, int qkv_splits, int64_t qkv_split_stride, int64_t ld, int q_off, int k_off, int v_off,
-    const float* ssq, int n_ssq, int norm_width, float norm_eps, const float* q_norm, const float* k_norm,
+    const float* qkv, int64_t ld, int q_off, int k_off, int v_off, const float* q_norm, const float* k_norm,
     float eps, const float* cos_t, const float* sin_t, int n_rot, void* out, int64_t ldo, float* part, int n_seqs,
     int nq, int nkv, int hd, void* k_pool, void* v_pool, const int32_t* pages, int max_pages, int page_size,
     const int32_t* tok_pos, float scale, int window, int n_splits, int pages_per_split,
@@ -787,11 +775,11 @@ extern "C" int skyla_attention_decode_fused(
   if (nq / nkv > 16) return fail(kBadArgument, "attention_decode: groups of %d query heads exceed 16", nq / nkv);
   if (n_splits < 1 || pages_per_split < 1 || n_seqs > 65535 || n_splits > 65535)
     return fail(kBadArgument, "attention_decode: bad split of the context");
-  if (qkv == nullptr || qkv_splits < 1 || (ssq != nullptr && (n_ssq < 1 || norm_width <= 0)) || n_rot < 0 || n_rot > hd || n_rot % 2)
+  if (qkv == nullptr || n_rot < 0 || n_rot > hd || n_rot % 2)
     return fail(kBadArgument, "attention_decode_fused: bad description of the unfinished q, k and v");
   DecodeArgs a{nullptr, 0, part, n_splits, pages_per_split, nq, nkv,
                PagedKV{(const bf16*)k_pool, (const bf16*)v_pool, pages, max_pages, page_size, nkv}, tok_pos, scale, window,
-               FusedPrep{qkv, qkv_splits, qkv_split_stride, ld, q_off, k_off, v_off, ssq, n_ssq, norm_width, norm_eps,
+               FusedPrep{qkv, ld, q_off, k_off, v_off,
                          q_norm, k_norm, eps, cos_t, sin_t, cos_t ? n_rot : 0, (bf16*)k_pool, (bf16*)v_pool, n_seqs},
                pages_needed, nullptr, 0, counters};
   const bool merge_inside = counters != nullptr && (int64_t)n_seqs * nkv <= n_counters;

@@ -19,13 +19,7 @@ constexpr int kMaxHeadDim = 512;
 
 struct PrepArgs {
   const void* qkv; int64_t ld; int q_off, k_off, v_off;
-  int n_splits; int64_t split_stride;  // the input may be K-split partial sums: [split][token][width]
   void* q_out; int64_t ldq;            // where the prepared queries go (may be the input itself)
-  // the input may lack a per-token scalar: a product that ran on un-normed rows hands on each
-  // K split's share of the row's sum of squares; the row is scaled by 1/sqrt(sum/width + eps)
-  const float* row_ssq; int n_ssq; int norm_width; float norm_eps;
-  // side job: x[t] += sum_s part[s][t] (the residual stream made whole), done by the blocks of column 0
-  float* fold_x; int64_t fold_ldx; const float* fold_part; int fold_splits; int64_t fold_split_stride, fold_ldp; int fold_h;
   int n_tokens, nq, nkv, hd;
   const float* q_norm; const float* k_norm; float eps;
   const float* cos_t; const float* sin_t; int n_rot;
@@ -41,15 +35,6 @@ __global__ void __launch_bounds__(kWarps * 32) prep_kernel(PrepArgs a) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int head = blockIdx.x * kWarps + warp;
   const int t = blockIdx.y;
-  if (a.fold_x != nullptr && blockIdx.x == 0) {
-    float* xr = a.fold_x + (int64_t)t * a.fold_ldx;
-    const float* pr = a.fold_part + (int64_t)t * a.fold_ldp;
-    for (int c = threadIdx.x; c < a.fold_h; c += kWarps * 32) {
-      float v = xr[c];
-      for (int s = 0; s < a.fold_splits; ++s) v += pr[(int64_t)s * a.fold_split_stride + c];
-      xr[c] = v;
-    }
-  }
   const int n_heads = a.nq + 2 * a.nkv;
   if (head >= n_heads) return;
   float* u = smem + warp * a.hd;
@@ -58,17 +43,7 @@ __global__ void __launch_bounds__(kWarps * 32) prep_kernel(PrepArgs a) {
   const int kvh = is_q ? 0 : (is_k ? head - a.nq : head - a.nq - a.nkv);
   const TI* src = (const TI*)a.qkv + (int64_t)t * a.ld +
                   (is_q ? a.q_off + head * hd : (is_k ? a.k_off : a.v_off) + kvh * hd);
-  float row_scale = 1.f;
-  if (a.row_ssq != nullptr) {
-    float ssq = 0.f;
-    for (int s = 0; s < a.n_ssq; ++s) ssq += a.row_ssq[(int64_t)s * a.n_tokens + t];
-    row_scale = 1.0f / sqrtf(ssq / (float)a.norm_width + a.norm_eps);
-  }
-  auto load = [&](int e) {  // splits are summed in ascending order
-    float v = to_float(src[e]);
-    for (int s = 1; s < a.n_splits; ++s) v += to_float(src[(int64_t)s * a.split_stride + e]);
-    return v * row_scale;
-  };
+  auto load = [&](int e) { return to_float(src[e]); };
   const int pos = a.tok_pos[t];
 
   TC* dst = nullptr;
@@ -195,30 +170,24 @@ __global__ void __launch_bounds__(kWarps * 32) prep_bf16_kernel(PrepArgs a) {
 }
 }  // namespace
 
-// qkv: [n_splits][tokens][ld] (n_splits = 1: plain activations); the prepared queries go
-// to q_out [tokens][ldq] (heads contiguous), which may alias the q columns of qkv.
+// qkv: [tokens][ld]; the prepared queries go to q_out [tokens][ldq] (heads contiguous), which may
+// alias the q columns of qkv.
 extern "C" int skyla_qk_norm_rope_cache(
-    const void* qkv, int in_dtype, int64_t ld, int n_splits, int64_t split_stride, void* q_out,
+    const void* qkv, int in_dtype, int64_t ld, void* q_out,
     int act_dtype, int64_t ldq, int q_off, int k_off, int v_off, int n_tokens, int nq,
     int nkv, int hd, const float* q_norm, const float* k_norm, float eps, const float* cos_t,
     const float* sin_t, int n_rot, const int32_t* tok_pos, const int32_t* tok_slot, void* k_pool,
     void* v_pool, int cache_dtype, const int32_t* page_table, int max_pages, int page_size,
-    const float* row_ssq, int n_ssq, int norm_width, float norm_eps,
-    float* fold_x, int64_t fold_ldx, const float* fold_part, int fold_splits, int64_t fold_split_stride,
-    int64_t fold_ldp, int fold_h, cudaStream_t stream) {
+    cudaStream_t stream) {
   if (n_tokens <= 0) return kOk;
   if (hd <= 0 || hd > kMaxHeadDim) return fail(kBadArgument, "qk_norm_rope_cache: head size %d is outside 1..%d", hd, kMaxHeadDim);
   if (n_rot < 0 || n_rot > hd || n_rot % 2) return fail(kBadArgument, "qk_norm_rope_cache: rotary width %d does not fit head size %d", n_rot, hd);
   if (n_tokens > 65535) return fail(kBadArgument, "qk_norm_rope_cache: %d tokens exceed the grid", n_tokens);
-  if (n_splits < 1) return fail(kBadArgument, "qk_norm_rope_cache: bad split count");
-  PrepArgs a{qkv, ld, q_off, k_off, v_off, n_splits, split_stride, q_out, ldq,
-             row_ssq, n_ssq, norm_width, norm_eps,
-             fold_x, fold_ldx, fold_part, fold_splits, fold_split_stride, fold_ldp, fold_h, n_tokens, nq, nkv, hd, q_norm, k_norm, eps, cos_t, sin_t,
+  PrepArgs a{qkv, ld, q_off, k_off, v_off, q_out, ldq, n_tokens, nq, nkv, hd, q_norm, k_norm, eps, cos_t, sin_t,
              n_rot, tok_pos, tok_slot, k_pool, v_pool, page_table, max_pages, page_size};
   dim3 grid((nq + 2 * nkv + kWarps - 1) / kWarps, n_tokens);
   const size_t smem = (size_t)kWarps * hd * sizeof(float);
-  if (in_dtype == kBF16 && act_dtype == kBF16 && (k_pool == nullptr || cache_dtype == kBF16) && n_splits == 1 &&
-      row_ssq == nullptr && fold_x == nullptr && hd % 32 == 0 && hd <= 256 && (cos_t == nullptr || n_rot == hd) &&
+  if (in_dtype == kBF16 && act_dtype == kBF16 && (k_pool == nullptr || cache_dtype == kBF16) && hd % 32 == 0 && hd <= 256 && (cos_t == nullptr || n_rot == hd) &&
       ld % 8 == 0 && ldq % 8 == 0 && q_off % 8 == 0 && k_off % 8 == 0 && v_off % 8 == 0 &&
       ((uintptr_t)qkv) % 16 == 0 && ((uintptr_t)q_out) % 16 == 0) {
     const dim3 gridf((nq + 2 * nkv + kWarps * kHeadsPerWarp - 1) / (kWarps * kHeadsPerWarp), n_tokens);

@@ -14,9 +14,10 @@
 //             accumulating in TMEM, and commits each stage back to the loader;
 //   warps 2-5 read the accumulator with tcgen05.ld (lane = output feature,
 //             column = token) and write the epilogue.
-// grid = (feature tiles, token tiles, K splits).  Every mbarrier wait is bounded:
-// on a timeout the CTA records an error code, drains what it started, frees its
-// TMEM and returns.
+// Two kernels: gemm_tc_kernel (grid = feature tiles x token tiles, whole K in a block:
+// 65 to 128 tokens) and gemm_tc_rows_kernel (up to 64 tokens: every SM streams its
+// share of the weight; see there).  Every mbarrier wait is bounded: on a timeout the
+// CTA records an error code, drains what it started, frees its TMEM and returns.
 #include <cuda.h>
 
 #include <cstring>
@@ -35,11 +36,6 @@ enum Mode : int {
   kStoreF32 = 1,    // y[tok, f] = acc                     (float)
   kAccumF32 = 2,    // y[tok, f] += acc                    (float: the residual sum)
   kGluBf16 = 3,     // y[tok, f] = silu(gate) * up         (bfloat16; W = N gate rows, then the N up rows)
-  kPartialF32 = 4,  // y[split, tok, f] = acc of this K split (float scratch)
-  kAccumCluster = 5,  // y[tok, f] += sum over the K splits, which form one thread-block cluster: the
-                      // splits' tiles meet in rank 0 through distributed shared memory, in rank order
-  kAccumLast = 6,     // y[tok, f] += sum over the K splits: every split leaves its tile in scratch and
-                      // counts itself in; the one that counts last adds them up in split order
 };
 
 constexpr int BM = 128;  // weight rows per tile
@@ -56,21 +52,13 @@ struct Cfg {
   static constexpr int kABytes = kATiles * BM * BK * 2;
   static constexpr int kBBytes = BN * BK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
-  // cluster epilogue: a landing zone of BN x 128 floats that the K splits push their tiles into
-  static constexpr int kLandingBytes = MODE == kAccumCluster ? (BN + 8) * BM * 4 : 0;  // ranks x ceil(BN/ranks) columns
-  static constexpr int kStagesRaw = (kSmemBudget - kLandingBytes) / kStageBytes;
+  static constexpr int kStagesRaw = kSmemBudget / kStageBytes;
   static constexpr int kStages = kStagesRaw > 12 ? 12 : kStagesRaw;
   static constexpr int kTmemColsRaw = kATiles * BN;
   static constexpr int kTmemCols = kTmemColsRaw < 32 ? 32 : kTmemColsRaw;
-  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 256 /*barriers*/ + kLandingBytes;
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 256 /*barriers*/;
   static_assert(kTmemCols <= 512 && (kTmemCols & (kTmemCols - 1)) == 0, "TMEM columns");
   static_assert(kStages >= 2, "pipeline depth");
-};
-
-// "Make the residual stream whole": x[r] += sum_s part[s][r], rows 0..M-1, width H.
-// A side job for warps that would otherwise idle; it runs after the dependency wait.
-struct FoldJob {
-  float* x; int64_t ldx; const float* part; int n_splits; int64_t split_stride, ldp; int M, H;
 };
 
 // "Norm ahead": the product that writes the residual stream last (y += x W^T) also leaves, for the
@@ -84,13 +72,9 @@ struct ScaleIn { const float* ssq_part; int n_parts; float eps; int width; };
 struct GemmArgs {
   void* y;
   int64_t ldy;            // elements between token rows of y
-  int64_t split_stride;   // elements between K splits of y (partial mode)
   int M, N, K;            // tokens, output features (after gating), reduction length
-  int k_blocks_per_split;
+  int k_blocks_per_split; // weight-streaming kernel: the K blocks of each split of a cluster
   int* error_flag;
-  FoldJob fold;           // fold.x == nullptr: none
-  float* scratch;         // kAccumLast: [splits][M][N] tiles of the K splits
-  int* counters;          // kAccumLast: one per output tile, zero between launches
   NormAhead ahead;        // weight-streaming kernel, accumulate epilogue: ahead.xw == nullptr: none
   ScaleIn scale;          // weight-streaming kernel: scale.ssq_part == nullptr: none
 };
@@ -103,20 +87,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   extern __shared__ uint8_t smem_raw[];
   __shared__ uint32_t tmem_base_slot;
   __shared__ volatile int abort_flag;
-  __shared__ int last_split;                 // kAccumLast: this block counted in last
 
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t bars = base + C::kStages * C::kStageBytes;
   auto full_bar = [&](int s) { return bars + 8u * s; };
   auto empty_bar = [&](int s) { return bars + 8u * (C::kStages + s); };
   const uint32_t tmem_full_bar = bars + 8u * (2 * C::kStages);
-  const uint32_t landing = bars + 256u;  // [source rank][owned token][128 features] floats (cluster epilogue)
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int f_tile = blockIdx.x, t_tile = blockIdx.y, split = blockIdx.z;
-  const int total_kb = (a.K + BK - 1) / BK;
-  const int kb0 = split * a.k_blocks_per_split;
-  const int n_kb = min(a.k_blocks_per_split, total_kb - kb0);
+  const int f_tile = blockIdx.x, t_tile = blockIdx.y;
+  const int n_kb = (a.K + BK - 1) / BK;
 
   if (threadIdx.x == 0) {
     abort_flag = 0;
@@ -148,14 +128,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       constexpr uint32_t kTxBytes = C::kStageBytes;
       for (int kb = 0; kb < n_pre; ++kb) {
         mbar_expect_tx(full_bar(kb), kTxBytes);
-        tma_load_2d(base + kb * C::kStageBytes, &map_w, full_bar(kb), (kb0 + kb) * BK, f_tile * BM);
+        tma_load_2d(base + kb * C::kStageBytes, &map_w, full_bar(kb), kb * BK, f_tile * BM);
         if (MODE == kGluBf16)  // the up rows of the same outputs follow the a.N gate rows
-          tma_load_2d(base + kb * C::kStageBytes + BM * BK * 2, &map_w, full_bar(kb), (kb0 + kb) * BK, a.N + f_tile * BM);
+          tma_load_2d(base + kb * C::kStageBytes + BM * BK * 2, &map_w, full_bar(kb), kb * BK, a.N + f_tile * BM);
         armed |= 1u << kb;
       }
       grid_dependency_wait();
       for (int kb = 0; kb < n_pre; ++kb)
-        tma_load_2d(base + kb * C::kStageBytes + C::kABytes, &map_x, full_bar(kb), (kb0 + kb) * BK, t_tile * BN);
+        tma_load_2d(base + kb * C::kStageBytes + C::kABytes, &map_x, full_bar(kb), kb * BK, t_tile * BN);
       int kb = n_pre;
       for (; kb < n_kb; ++kb) {
         const int s = kb % C::kStages;
@@ -163,9 +143,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         if (!mbar_wait(empty_bar(s), phase ^ 1, &abort_flag, a.error_flag, 1)) break;
         const uint32_t sa = base + s * C::kStageBytes, sb = sa + C::kABytes;
         mbar_expect_tx(full_bar(s), kTxBytes);
-        tma_load_2d(sa, &map_w, full_bar(s), (kb0 + kb) * BK, f_tile * BM);
-        if (MODE == kGluBf16) tma_load_2d(sa + BM * BK * 2, &map_w, full_bar(s), (kb0 + kb) * BK, a.N + f_tile * BM);
-        tma_load_2d(sb, &map_x, full_bar(s), (kb0 + kb) * BK, t_tile * BN);
+        tma_load_2d(sa, &map_w, full_bar(s), kb * BK, f_tile * BM);
+        if (MODE == kGluBf16) tma_load_2d(sa + BM * BK * 2, &map_w, full_bar(s), kb * BK, a.N + f_tile * BM);
+        tma_load_2d(sb, &map_x, full_bar(s), kb * BK, t_tile * BN);
         armed |= 1u << s;
         armed_parity = (armed_parity & ~(1u << s)) | (phase << s);
       }
@@ -207,24 +187,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     grid_dependency_wait();                      // the epilogue reads and writes what earlier kernels touch
     const int quad = warp & 3;                   // the TMEM lanes this warp may read
     const int f = f_tile * BM + quad * 32 + lane;  // output feature of this thread
-    const int et = threadIdx.x - 64;             // 0..127 among the four epilogue warps
-    uint32_t my_rank = 0, n_ranks = 1;
-    if (MODE == kAccumCluster) {
-      asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(my_rank));
-      asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(n_ranks));
-    }
-    if (a.fold.x != nullptr && f_tile == 0 && t_tile == 0) {
-      // side job while the main loop runs: this split's share of the columns of x
-      const int per = (a.fold.H + (int)gridDim.z - 1) / (int)gridDim.z;
-      const int c0 = split * per, c1 = min(a.fold.H, c0 + per);
-      for (int r = 0; r < a.fold.M; ++r)
-        for (int c = c0 + et; c < c1; c += 128) {
-          float v = a.fold.x[(int64_t)r * a.fold.ldx + c];
-          for (int sp = 0; sp < a.fold.n_splits; ++sp)
-            v += a.fold.part[(int64_t)sp * a.fold.split_stride + (int64_t)r * a.fold.ldp + c];
-          a.fold.x[(int64_t)r * a.fold.ldx + c] = v;
-        }
-    }
     if (n_kb > 0 && mbar_wait(tmem_full_bar, 0, &abort_flag, a.error_flag, 3)) {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16);
@@ -256,99 +218,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
               ((float*)a.y)[(int64_t)tok * a.ldy + f] = v;
             } else if (MODE == kAccumF32) {
               ((float*)a.y)[(int64_t)tok * a.ldy + f] = old[j] + v;
-            } else if (MODE == kAccumCluster) {
-              // token column c0+j belongs to rank (c0+j) % n_ranks: push this split's value into
-              // that block's landing zone, slot [my rank][(c0+j) / n_ranks][feature]
-              const uint32_t col = (uint32_t)(c0 + j);
-              const uint32_t local = landing + 4u * ((my_rank * ((BN + n_ranks - 1) / n_ranks) + col / n_ranks) * BM +
-                                                     quad * 32 + lane);
-              uint32_t remote;
-              asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(col % n_ranks));
-              asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
-            } else if (MODE == kGluBf16) {
+            } else {
               const float up = __uint_as_float(u[j]);
               ((__nv_bfloat16*)a.y)[(int64_t)tok * a.ldy + f] = __float2bfloat16_rn(v / (1.0f + expf(-v)) * up);
-            } else if (MODE == kAccumLast) {
-              a.scratch[((int64_t)split * a.M + tok) * a.N + f] = v;
-            } else {
-              ((float*)a.y)[(int64_t)split * a.split_stride + (int64_t)tok * a.ldy + f] = v;
             }
           }
         }
-      }
-    }
-    if (MODE == kAccumLast) {
-      // count this split in; whoever counts last has every split's tile in reach and adds them up
-      __threadfence();
-      asm volatile("barrier.sync 1, 128;" ::: "memory");
-      if (et == 0) {
-        const int tile_id = f_tile * (int)gridDim.y + t_tile;
-        const int before = atomicAdd(&a.counters[tile_id], 1);
-        last_split = before == (int)gridDim.z - 1;
-        if (last_split) a.counters[tile_id] = 0;  // ready for the next launch
-      }
-      asm volatile("barrier.sync 1, 128;" ::: "memory");
-      if (last_split && f < a.N && !abort_flag) {
-        __threadfence();
-        const int tok0 = t_tile * BN;
-        const int n_tok = min(BN, a.M - tok0);
-        for (int j0 = 0; j0 < n_tok; j0 += 8) {
-          float sum[8], old[8];
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            sum[j] = 0.f;
-            old[j] = j0 + j < n_tok ? ((const float*)a.y)[(int64_t)(tok0 + j0 + j) * a.ldy + f] : 0.f;
-          }
-          for (int sp = 0; sp < (int)gridDim.z; ++sp)
-#pragma unroll
-            for (int j = 0; j < 8; ++j)
-              if (j0 + j < n_tok) sum[j] += __ldcg(&a.scratch[((int64_t)sp * a.M + tok0 + j0 + j) * a.N + f]);
-#pragma unroll
-          for (int j = 0; j < 8; ++j)
-            if (j0 + j < n_tok) ((float*)a.y)[(int64_t)(tok0 + j0 + j) * a.ldy + f] = old[j] + sum[j];
-        }
-      }
-    }
-  }
-  if (MODE == kAccumCluster) {
-    // All splits have pushed their tiles; each block now owns the token columns c with
-    // c % n_ranks == its rank, adds the splits' values in rank order and updates y.
-    uint32_t rank, n_ranks;
-    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
-    asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(n_ranks));
-    const int f = f_tile * BM + (warp & 3) * 32 + lane;
-    const int tok0 = t_tile * BN;
-    const int n_tok = min(BN, a.M - tok0);
-    constexpr int kMaxOwned = BN;  // with one rank a block owns every column
-    const int per_rank = (BN + (int)n_ranks - 1) / (int)n_ranks;
-    float old[kMaxOwned > 16 ? 16 : kMaxOwned];
-    const bool worker = warp >= 2 && f < a.N;
-    if (worker) {  // the old values do not depend on the peers: fetch them while waiting
-#pragma unroll
-      for (int i = 0; i < (kMaxOwned > 16 ? 16 : kMaxOwned); ++i) {
-        const int col = i * (int)n_ranks + (int)rank;
-        old[i] = (i < per_rank && col < n_tok) ? ((const float*)a.y)[(int64_t)(tok0 + col) * a.ldy + f] : 0.f;
-      }
-    }
-    __syncwarp();
-    asm volatile("barrier.cluster.arrive.release;\n\tbarrier.cluster.wait.acquire;" ::: "memory");
-    if (worker && !abort_flag) {
-      const float* land = reinterpret_cast<const float*>(smem_raw + (landing - smem_u32(smem_raw)));
-#pragma unroll
-      for (int i = 0; i < (kMaxOwned > 16 ? 16 : kMaxOwned); ++i) {
-        const int col = i * (int)n_ranks + (int)rank;
-        if (i >= per_rank || col >= n_tok) continue;
-        float sum = 0.f;
-        for (uint32_t src = 0; src < n_ranks; ++src) sum += land[((int)src * per_rank + i) * BM + (warp & 3) * 32 + lane];
-        ((float*)a.y)[(int64_t)(tok0 + col) * a.ldy + f] = old[i] + sum;
-      }
-      for (int i = 16; i < per_rank; ++i) {  // a block that owns more than 16 columns (few splits, wide tile)
-        const int col = i * (int)n_ranks + (int)rank;
-        if (col >= n_tok) break;
-        float sum = 0.f;
-        for (uint32_t src = 0; src < n_ranks; ++src) sum += land[((int)src * per_rank + i) * BM + (warp & 3) * 32 + lane];
-        float* p = (float*)a.y + (int64_t)(tok0 + col) * a.ldy + f;
-        *p += sum;
       }
     }
   }
@@ -983,10 +858,7 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, const GemmArgs& a, dim3
                                       C::kSmemBytes, cudaGetErrorString(e));
     configured = true;
   }
-  if (MODE == kAccumCluster)
-    launch_overlapped_cluster(gemm_tc_kernel<BN, MODE>, grid, dim3(kThreads), C::kSmemBytes, stream, grid.z, mw, mx, a);
-  else
-    launch_overlapped(gemm_tc_kernel<BN, MODE>, grid, dim3(kThreads), C::kSmemBytes, stream, mw, mx, a);
+  launch_overlapped(gemm_tc_kernel<BN, MODE>, grid, dim3(kThreads), C::kSmemBytes, stream, mw, mx, a);
   return check_launch("gemm_tc");
 }
 
@@ -1073,52 +945,25 @@ extern "C" int skyla_gemm_tc_stages(int bn, int mode) {
        : bn == 128 ? Cfg<128, 0>::kStages : Cfg<256, 0>::kStages;
 }
 
-// map_w: weight [rows, K] with boxes of 128 rows (256 in gated mode); map_x: tokens [M, K] with boxes of bn rows.
-// fold_x (may be null): a residual stream [M, fold_h] to which fold_part [fold_splits][M][fold_h]
-// is added on the side, after this kernel's dependency wait.
-extern "C" int skyla_gemm_tc(const void* map_w, const void* map_x, void* y, int64_t ldy, int64_t split_stride,
-                             int M, int N, int K, int bn, int mode, int splits, int* error_flag,
-                             float* fold_x, int64_t fold_ldx, const float* fold_part, int fold_splits,
-                             int64_t fold_split_stride, int64_t fold_ldp, int fold_h, float* scratch, int* counters,
-                             cudaStream_t stream) {
+// map_w: weight [rows, K] with boxes of 128 rows (a gated weight: the N gate rows, then the N up rows);
+// map_x: tokens [M, K] with boxes of bn rows.  Whole K in every block: the products of 65 to 128 tokens, and
+// the fewer tokens of weights whose K is too short (or whose width too odd) for the weight-streaming kernel.
+extern "C" int skyla_gemm_tc(const void* map_w, const void* map_x, void* y, int64_t ldy, int M, int N, int K, int bn,
+                             int mode, int* error_flag, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return kOk;
   if (K <= 0 || K % 8) return fail(kBadArgument, "gemm_tc: K=%d must be a positive multiple of 8", K);
-  if (mode < 0 || mode > 6) return fail(kBadArgument, "gemm_tc: unknown epilogue %d", mode);
-  if (splits < 1 || (splits > 1 && mode != kPartialF32 && mode != kAccumCluster && mode != kAccumLast))
-    return fail(kBadArgument, "gemm_tc: %d K splits need the partial, the cluster or the last-arriver epilogue", splits);
-  if (mode == kAccumLast && (scratch == nullptr || counters == nullptr || bn > 64))
-    return fail(kBadArgument, "gemm_tc: the last-arriver epilogue needs scratch, counters and at most 64 tokens per tile");
-  if (mode == kAccumCluster && (splits > 8 || bn > 64))
-    return fail(kBadArgument, "gemm_tc: the cluster epilogue takes at most 8 K splits and 64 tokens per tile");
-  const int total_kb = (K + BK - 1) / BK;
-  const int per = (total_kb + splits - 1) / splits;
-  if ((splits - 1) * per >= total_kb) return fail(kBadArgument, "gemm_tc: %d K splits leave one empty (K=%d)", splits, K);
+  if (mode < 0 || mode > kGluBf16) return fail(kBadArgument, "gemm_tc: unknown epilogue %d", mode);
   alignas(64) CUtensorMap mw, mx;
   memcpy(&mw, map_w, sizeof(mw));
   memcpy(&mx, map_x, sizeof(mx));
-  GemmArgs a{y, ldy, split_stride, M, N, K, per, error_flag,
-             FoldJob{fold_x, fold_ldx, fold_part, fold_splits, fold_split_stride, fold_ldp, M, fold_h},
-             scratch, counters};
-  dim3 grid((N + BM - 1) / BM, (M + bn - 1) / bn, splits);
-  if (grid.y > 65535 || grid.z > 65535) return fail(kBadArgument, "gemm_tc: grid too large");
+  GemmArgs a{y, ldy, M, N, K, (K + BK - 1) / BK, error_flag};
+  dim3 grid((N + BM - 1) / BM, (M + bn - 1) / bn, 1);
+  if (grid.y > 65535) return fail(kBadArgument, "gemm_tc: grid too large");
   switch (mode) {
     case kStoreBf16: return launch_bn<kStoreBf16>(bn, mw, mx, a, grid, stream);
     case kStoreF32: return launch_bn<kStoreF32>(bn, mw, mx, a, grid, stream);
     case kAccumF32: return launch_bn<kAccumF32>(bn, mw, mx, a, grid, stream);
-    case kGluBf16: return launch_bn<kGluBf16>(bn, mw, mx, a, grid, stream);
-    case kAccumCluster:
-      switch (bn) {
-        case 16: return launch<16, kAccumCluster>(mw, mx, a, grid, stream);
-        case 32: return launch<32, kAccumCluster>(mw, mx, a, grid, stream);
-        default: return launch<64, kAccumCluster>(mw, mx, a, grid, stream);
-      }
-    case kAccumLast:
-      switch (bn) {
-        case 16: return launch<16, kAccumLast>(mw, mx, a, grid, stream);
-        case 32: return launch<32, kAccumLast>(mw, mx, a, grid, stream);
-        default: return launch<64, kAccumLast>(mw, mx, a, grid, stream);
-      }
-    default: return launch_bn<kPartialF32>(bn, mw, mx, a, grid, stream);
+    default: return launch_bn<kGluBf16>(bn, mw, mx, a, grid, stream);
   }
 }
 
@@ -1158,7 +1003,7 @@ extern "C" int skyla_gemm_tc_rows(const void* map_w, const void* map_x, void* y,
   int kps = (total_kb + splits - 1) / splits;
   kps = (kps + kkb - 1) / kkb * kkb;  // whole boxes per split
   if ((splits - 1) * kps >= total_kb) return fail(kBadArgument, "gemm_tc_rows: %d splits leave one without K blocks", splits);
-  GemmArgs a{y, ldy, 0, M, N, K, kps, error_flag, FoldJob{}, nullptr, nullptr};
+  GemmArgs a{y, ldy, M, N, K, kps, error_flag};
   if (ahead_xw != nullptr) {
     if (mode != kAccumF32 || ahead_w == nullptr || ahead_ssq == nullptr)
       return fail(kBadArgument, "gemm_tc_rows: norm-ahead goes with the accumulate epilogue, a norm weight and room for the sums");

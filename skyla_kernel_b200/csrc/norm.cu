@@ -28,72 +28,6 @@ __global__ void rmsnorm_kernel(const TI* __restrict__ x, int64_t ldx, const int3
     o[i] = from_float<TO>(to_float(xr[i]) * inv * w[i]);
 }
 
-// The same with the residual stream completed first: x[r] += sum over K splits of
-// partial[s][r] (ascending s, a fixed order), written back, then normed.  It folds
-// the split-K partial sums that the tensor-core matrix product leaves for a small
-// batch into the kernel that reads x next, and is the fused "residual add + norm".
-template <typename TO>
-__global__ void add_rmsnorm_kernel(float* __restrict__ x, int64_t ldx, const float* __restrict__ part,
-                                   int n_splits, int64_t split_stride, int64_t ldp,
-                                   const int32_t* __restrict__ rows, int width, const float* __restrict__ w,
-                                   float eps, TO* __restrict__ out, int64_t ldo) {
-  __shared__ float scratch[32];
-  allow_dependents();
-  grid_dependency_wait();
-  const int r = blockIdx.x;
-  const int64_t src = rows ? rows[r] : r;
-  float* xr = x + src * ldx;
-  const float* pr = part + src * ldp;
-  float ss = 0.f;
-  for (int i = threadIdx.x; i < width; i += blockDim.x) {
-    float v = xr[i];
-    for (int s = 0; s < n_splits; ++s) v += pr[(int64_t)s * split_stride + i];
-    xr[i] = v;
-    ss = fmaf(v, v, ss);
-  }
-  ss = block_sum(ss, scratch);
-  const float inv = 1.0f / sqrtf(ss / (float)width + eps);
-  TO* o = out + (int64_t)r * ldo;
-  for (int i = threadIdx.x; i < width; i += blockDim.x) o[i] = from_float<TO>(xr[i] * inv * w[i]);
-}
-
-// x[r] += sum_s partial[s][r] for all rows, no norm (for readers of x that are not norms).
-__global__ void fold_partials_kernel(float* __restrict__ x, int64_t ldx, const float* __restrict__ part,
-                                     int n_splits, int64_t split_stride, int64_t ldp, int width) {
-  allow_dependents();
-  grid_dependency_wait();
-  const int r = blockIdx.x;
-  for (int i = threadIdx.x; i < width; i += blockDim.x) {
-    float v = x[(int64_t)r * ldx + i];
-    for (int s = 0; s < n_splits; ++s) v += part[(int64_t)s * split_stride + (int64_t)r * ldp + i];
-    x[(int64_t)r * ldx + i] = v;
-  }
-}
-
-extern "C" int skyla_add_rmsnorm(float* x, int64_t ldx, const float* part, int n_splits, int64_t split_stride,
-                                 int64_t ldp, const int32_t* rows, int n_rows, int width, const float* weight,
-                                 float eps, void* out, int out_dtype, int64_t ldo, cudaStream_t stream) {
-  if (n_rows <= 0) return kOk;
-  if (width <= 0 || ldx < width || ldo < width || ldp < width || n_splits < 1)
-    return fail(kBadArgument, "add_rmsnorm: bad width %d, stride or split count", width);
-  const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
-  SKYLA_DISPATCH(out_dtype, TO, {
-    launch_overlapped(add_rmsnorm_kernel<TO>, dim3(n_rows), dim3(threads), 0, stream, x, ldx, part, n_splits,
-                      split_stride, ldp, rows, width, weight, eps, (TO*)out, ldo);
-  });
-  return check_launch("add_rmsnorm");
-}
-
-extern "C" int skyla_fold_partials(float* x, int64_t ldx, const float* part, int n_splits, int64_t split_stride,
-                                   int64_t ldp, int n_rows, int width, cudaStream_t stream) {
-  if (n_rows <= 0) return kOk;
-  if (width <= 0 || ldx < width || ldp < width || n_splits < 1)
-    return fail(kBadArgument, "fold_partials: bad width %d, stride or split count", width);
-  launch_overlapped(fold_partials_kernel, dim3(n_rows), dim3(256), 0, stream, x, ldx, part, n_splits, split_stride,
-                    ldp, width);
-  return check_launch("fold_partials");
-}
-
 // float32 rows whose width is a multiple of 4 and that start on 16 bytes: four elements per load,
 // kept in registers between the two passes (up to kKeep loads a thread; wider rows are read again),
 // four bfloat16 per store.

@@ -91,9 +91,6 @@ class StepContext:
     #: when profiling: (label, event) pairs, an event after each stage
     #: (the reference's timestamp marks, skyla-engine/src/graph.rs:54-57)
     marks: Optional[list] = None
-    #: K-split partial sums [splits, tokens, hidden] that still have to be added to the
-    #: residual stream; the next norm (or fold_pending) adds them in a fixed order
-    pending: Optional[torch.Tensor] = None
     #: hints for "norm ahead": the norm that reads the residual stream after the part now running
     #: (set by the block), and the norm that reads it after the block now running (set by the model)
     next_norm: Optional[object] = None
@@ -106,10 +103,6 @@ class StepContext:
     def is_decode(self) -> bool:
         return self.max_new == 1
 
-    def take_pending(self) -> Optional[torch.Tensor]:
-        p, self.pending = self.pending, None
-        return p
-
     def take_ahead(self, norm, x: torch.Tensor):
         """(x * norm.weight in bfloat16, shares of the sums of squares) if the last writer of ``x``
         left them for this very norm, else ``None``; either way they are gone afterwards."""
@@ -117,13 +110,6 @@ class StepContext:
         if a is not None and a[0] is norm and a[1] is x:
             return a[2], a[3]
         return None
-
-    def fold_pending(self, x: torch.Tensor) -> None:
-        """Make ``x`` whole for a reader that is not a norm."""
-        p = self.take_pending()
-        if p is not None:
-            from ..kernels import ops
-            ops.fold_partials(x, p)
 
     def mark(self, label: str) -> None:
         """End of a stage; a no-op unless the step is profiled."""

@@ -127,19 +127,13 @@ class DecoderModel:
             ctx.after_block_norm = getattr(nxt, "first_norm", None)
             self.blocks[e.layer].forward(ctx, x, self.entries[i])
             if taps is not None and i in taps:
-                ctx.fold_pending(x)
                 taps[i].copy_(x)
         logits = ctx.buffer("model.logits", (ctx.n_want, self.spec.vocab_size), torch.float32)
         if ctx.n_want:
             h = ctx.buffer("model.final", (ctx.n_want, hidden), self.rt.act_dtype)
-            if ctx.pending is not None and getattr(self.final_norm, "fuses_pending", False):
-                self.final_norm.forward(ctx, x, h, rows=ctx.want, pending=ctx.take_pending())
-            else:
-                ctx.fold_pending(x)
-                self.final_norm.forward(ctx, x, h, rows=ctx.want)
+            self.final_norm.forward(ctx, x, h, rows=ctx.want)
             ctx.mark("take wanted rows + rmsnorm")
             self.head.forward(ctx, h, logits)
             ctx.mark("matvec output")
-        ctx.pending = None
         ctx.ahead = ctx.next_norm = ctx.after_block_norm = None
         return logits

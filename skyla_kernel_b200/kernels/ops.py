@@ -133,42 +133,6 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor
     return out
 
 
-def add_rmsnorm(x: torch.Tensor, partials: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,
-                rows: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """x[r] += sum_s partials[s, r] (written back), then out = rmsnorm(x[r]) * weight.
-
-    ``partials``: float32 [splits, tokens, width], the K-split sums a matrix product left.
-    """
-    _cuda(x, partials, weight, out, rows)
-    _i32(rows, "rows")
-    if x.dtype != torch.float32 or partials.dtype != torch.float32 or partials.dim() != 3 or not partials.is_contiguous():
-        raise KernelError("add_rmsnorm: x and the contiguous [splits, tokens, width] partials must be float32")
-    width = weight.numel()
-    n = rows.numel() if rows is not None else x.shape[0]
-    if x.shape[1] != width or partials.shape[2] != width or partials.shape[1] != x.shape[0] or out.shape[0] < n:
-        raise KernelError(f"add_rmsnorm: shapes x {tuple(x.shape)} partials {tuple(partials.shape)} out {tuple(out.shape)}")
-    f = _fn("norm", "skyla_add_rmsnorm",
-            [c_void_p, c_int64, c_void_p, c_int, c_int64, c_int64, c_void_p, c_int, c_int, c_void_p, c_float,
-             c_void_p, c_int, c_int64, c_void_p])
-    _check("norm", f(_ptr(x), _rows(x, "x"), _ptr(partials), partials.shape[0], partials.stride(0), partials.stride(1),
-                     _ptr(rows), n, width, _ptr(weight), float(eps), _ptr(out), dtype_code(out), _rows(out, "out"),
-                     _stream()))
-    return out
-
-
-def fold_partials(x: torch.Tensor, partials: torch.Tensor) -> torch.Tensor:
-    """x += sum_s partials[s] in ascending s."""
-    _cuda(x, partials)
-    if x.dtype != torch.float32 or partials.dtype != torch.float32 or partials.dim() != 3 or not partials.is_contiguous():
-        raise KernelError("fold_partials: float32 x and contiguous [splits, tokens, width] partials")
-    if tuple(partials.shape[1:]) != tuple(x.shape):
-        raise KernelError("fold_partials: shapes differ")
-    f = _fn("norm", "skyla_fold_partials", [c_void_p, c_int64, c_void_p, c_int, c_int64, c_int64, c_int, c_int, c_void_p])
-    _check("norm", f(_ptr(x), _rows(x, "x"), _ptr(partials), partials.shape[0], partials.stride(0), partials.stride(1),
-                     x.shape[0], x.shape[1], _stream()))
-    return x
-
-
 # --------------------------------------------------------------------- linear
 STORE, ACCUMULATE, GATED = 0, 1, 2
 
@@ -197,7 +161,7 @@ def linear_plain(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, mode: int = 
 
 
 # ---------------------------------------------------------- tensor-core linear
-TC_STORE_BF16, TC_STORE_F32, TC_ACCUM_F32, TC_GLU_BF16, TC_PARTIAL_F32, TC_ACCUM_CLUSTER, TC_ACCUM_LAST = 0, 1, 2, 3, 4, 5, 6
+TC_STORE_BF16, TC_STORE_F32, TC_ACCUM_F32, TC_GLU_BF16 = 0, 1, 2, 3
 TC_TOKEN_TILES = (16, 32, 64, 128, 256)
 
 
@@ -208,9 +172,8 @@ class KernelState:
       when the sampler found no token in a row of logits (31: every logit NaN) or when a token fed
       on the device lies outside the embedding table (32);
     * counters with which the blocks of a launch find out which of them finishes last (the context
-      splits of decode attention, the K splits of a small product): zero between launches;
-    * scratch in which K splits meet, and the flags of the prompt product's tiles that are cut
-      along K.
+      splits of decode attention): zero between launches;
+    * the scratch and the flags of the prompt product's tiles that are cut along K.
 
     An engine owns one (``Runtime.kernel_state``) and hands it to every launch, so two engines on
     two streams share nothing.  The launches of one state must not overlap on the device: one
@@ -225,8 +188,6 @@ class KernelState:
         self.device = torch.device(device)
         self.error_flag = torch.zeros(1, dtype=torch.int32, device=self.device)
         self._merge = None
-        self._tiles = []
-        self._accum = []
         self._shares = None
 
     @property
@@ -238,19 +199,6 @@ class KernelState:
         if self._merge is None:
             self._merge = torch.zeros(self.MERGE_COUNTERS, dtype=torch.int32, device=self.device)
         return self._merge
-
-    def tile_counters(self, n: int) -> torch.Tensor:
-        """Zeroed int32 counters, one per output tile, that the last-arriver epilogue leaves zeroed."""
-        if not self._tiles or self._tiles[-1].numel() < n:
-            self._tiles.append(torch.zeros(max(4096, n), dtype=torch.int32, device=self.device))
-        return self._tiles[-1]
-
-    def accum_scratch(self, n: int) -> torch.Tensor:
-        """Float32 scratch for the K splits' tiles, shared by the products of this state (they run
-        one after another)."""
-        if not self._accum or self._accum[-1].numel() < n:
-            self._accum.append(torch.empty(max(n, 1 << 22), dtype=torch.float32, device=self.device))
-        return self._accum[-1]
 
     def prompt_shares(self):
         """(scratch for one accumulator tile per SM, a flag per SM, SMs) for ``gemm_prompt``'s tiles
@@ -267,8 +215,6 @@ class KernelState:
         self.error_flag.zero_()
         if self._merge is not None:
             self._merge.zero_()
-        for t in self._tiles:
-            t.zero_()
         if self._shares is not None:
             self._shares[1].zero_()
 
@@ -362,56 +308,24 @@ def token_tile(m: int, gated: bool = False) -> int:
     return 128 if gated else 256
 
 
-def _fold_args(fold, m: int):
-    """(x, partials) -> the seven launcher arguments of a fold side job (all zero for none)."""
-    if fold is None:
-        return [c_void_p(0), 0, c_void_p(0), 0, 0, 0, 0]
-    x, part = fold
-    _cuda(x, part)
-    if (x.dtype != torch.float32 or part.dtype != torch.float32 or part.dim() != 3 or not part.is_contiguous()
-            or tuple(part.shape[1:]) != tuple(x.shape) or x.shape[0] != m):
-        raise KernelError("fold job: float32 x [tokens, width] and contiguous partial sums [splits, tokens, width]")
-    return [_ptr(x), _rows(x, "x"), _ptr(part), part.shape[0], part.stride(0), part.stride(1), x.shape[1]]
-
-
-def gemm_tc(x: torch.Tensor, w_map: TensorMap, n_out: int, y: torch.Tensor, mode: int, splits: int = 1,
-            bn: Optional[int] = None, fold=None, state: Optional[KernelState] = None) -> torch.Tensor:
-    """y = x W^T on the tensor cores.  ``w_map`` has boxes of 128 rows; a gated weight holds
-    the ``n_out`` gate rows, then the up rows.
-
-    ``mode``: TC_STORE_BF16 / TC_STORE_F32 / TC_ACCUM_F32 / TC_GLU_BF16, or
-    TC_PARTIAL_F32 with ``y`` of shape [splits, tokens, n_out] float32, or
-    TC_ACCUM_CLUSTER: ``y += x W^T`` with the product cut into ``splits`` (at most 8) along K,
-    the splits running as one thread-block cluster and added up in a fixed order; or
-    TC_ACCUM_LAST: the same sum, but every split leaves its tile in the state's scratch and the
-    split that finishes last adds them up.
-    ``fold=(r, partials)``: on the side, ``r += sum_s partials[s]`` (``r`` must not be an
-    operand of this product).
+def gemm_tc(x: torch.Tensor, w_map: TensorMap, n_out: int, y: torch.Tensor, mode: int, bn: Optional[int] = None,
+            state: Optional[KernelState] = None) -> torch.Tensor:
+    """y = x W^T on the tensor cores, whole K in every block.  ``w_map`` has boxes of 128 rows; a gated
+    weight holds the ``n_out`` gate rows, then the up rows.
+    ``mode``: TC_STORE_BF16 / TC_STORE_F32 / TC_ACCUM_F32 (``y += x W^T``, the residual add) / TC_GLU_BF16.
     """
     m, k = x.shape
     bn = bn or token_tile(m, mode == TC_GLU_BF16)
     want = {TC_STORE_BF16: torch.bfloat16, TC_GLU_BF16: torch.bfloat16}.get(mode, torch.float32)
     if y.dtype != want:
         raise KernelError(f"gemm_tc: epilogue {mode} writes {want}, y is {y.dtype}")
-    if mode == TC_PARTIAL_F32:
-        if y.dim() != 3 or tuple(y.shape) != (splits, m, n_out) or not y.is_contiguous():
-            raise KernelError(f"gemm_tc: partial output must be contiguous [{splits}, {m}, {n_out}]")
-        ldy, sstride = n_out, m * n_out
-    else:
-        if y.shape[0] != m or y.shape[1] != n_out:
-            raise KernelError(f"gemm_tc: y {tuple(y.shape)} is not [{m}, {n_out}]")
-        ldy, sstride = _rows(y, "y"), 0
+    if y.shape[0] != m or y.shape[1] != n_out:
+        raise KernelError(f"gemm_tc: y {tuple(y.shape)} is not [{m}, {n_out}]")
     xm = activation_map(x, bn)
-    st = _state(state, x)
-    counters = scratch = None
-    if mode == TC_ACCUM_LAST:
-        scratch = st.accum_scratch(splits * m * n_out)
-        counters = st.tile_counters(-(-n_out // 128) * -(-m // bn))
     f = _fn("gemm_tc", "skyla_gemm_tc",
-            [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int, c_int, c_int, c_int, c_int, c_int,
-             c_void_p, c_void_p, c_int64, c_void_p, c_int, c_int64, c_int64, c_int, c_void_p, c_void_p, c_void_p])
-    _check("gemm_tc", f(w_map.buf, xm.buf, _ptr(y), ldy, sstride, m, n_out, k, bn, mode, splits,
-                        _ptr(st.error_flag), *_fold_args(fold, m), _ptr(scratch), _ptr(counters), _stream()))
+            [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
+    _check("gemm_tc", f(w_map.buf, xm.buf, _ptr(y), _rows(y, "y"), m, n_out, k, bn, mode,
+                        _ptr(_state(state, x).error_flag), _stream()))
     return y
 
 
@@ -677,35 +591,23 @@ def qk_norm_rope_cache(qkv: torch.Tensor, q_off: int, k_off: int, v_off: int, nq
                        eps: float, cos: Optional[torch.Tensor], sin: Optional[torch.Tensor],
                        n_rot: int, tok_pos: torch.Tensor, tok_slot: torch.Tensor,
                        k_pool: Optional[torch.Tensor], v_pool: Optional[torch.Tensor],
-                       page_table: torch.Tensor, page_size: int, q_out: Optional[torch.Tensor] = None,
-                       row_ssq: Optional[torch.Tensor] = None, norm_width: int = 0, norm_eps: float = 0.0,
-                       fold=None) -> None:
+                       page_table: torch.Tensor, page_size: int, q_out: Optional[torch.Tensor] = None) -> None:
     """Per-head norm and rotation of the new tokens; q to ``q_out`` (default: in place), k and
     v into the cache.
 
-    ``qkv``: [tokens, width] activations, or float32 [splits, tokens, width] K-split partial
-    sums that are added up on the way in (then ``q_out`` is required).  ``k_pool``/``v_pool``
-    of shape [pages, nkv, page_size, hd]; ``None`` skips the cache write (a run that reads
-    another entry's cache).  ``row_ssq`` [splits, tokens]: the rows still lack the scalar of an
-    RMSNorm over ``norm_width`` inputs, given as each split's share of the sum of squares
-    (``gemm_tc_norm``).  ``fold=(x, partials)``: on the side, ``x += sum_s partials[s]``.
+    ``qkv``: [tokens, width] rows of the q/k/v product in any precision (32-bit rows go with a
+    ``q_out`` of the activations' precision).  ``k_pool``/``v_pool`` of shape
+    [pages, nkv, page_size, hd]; ``None`` skips the cache write (a run that reads another
+    entry's cache).
     """
-    _cuda(qkv, q_norm, k_norm, cos, sin, tok_pos, tok_slot, k_pool, v_pool, page_table, q_out, row_ssq)
-    if row_ssq is not None and (row_ssq.dtype != torch.float32 or row_ssq.dim() != 2 or not row_ssq.is_contiguous()
-                                or row_ssq.shape[1] != tok_pos.numel() or norm_width <= 0):
-        raise KernelError("qk_norm_rope_cache: row_ssq must be contiguous float32 [splits, tokens] with a norm width")
+    _cuda(qkv, q_norm, k_norm, cos, sin, tok_pos, tok_slot, k_pool, v_pool, page_table, q_out)
     for t, what in ((tok_pos, "tok_pos"), (tok_slot, "tok_slot"), (page_table, "page_table")):
         _i32(t, what)
     for t, what in ((q_norm, "q_norm"), (k_norm, "k_norm"), (cos, "cos"), (sin, "sin")):
         if t is not None and (t.dtype != torch.float32 or not t.is_contiguous()):
             raise KernelError(f"{what}: expected a contiguous float32 tensor")
     n = tok_pos.numel()
-    if qkv.dim() == 3:
-        if q_out is None or not qkv.is_contiguous():
-            raise KernelError("qk_norm_rope_cache: partial sums need a separate, contiguous layout and q_out")
-        n_splits, split_stride, ld = qkv.shape[0], qkv.stride(0), qkv.stride(1)
-    else:
-        n_splits, split_stride, ld = 1, 0, _rows(qkv, "qkv")
+    ld = _rows(qkv, "qkv")
     if q_out is None:
         q_ptr, q_dt, ldq = c_void_p(qkv.data_ptr() + q_off * qkv.element_size()), dtype_code(qkv), ld
     else:
@@ -722,16 +624,14 @@ def qk_norm_rope_cache(qkv: torch.Tensor, q_off: int, k_off: int, v_off: int, nq
     if cos is not None and (cos.shape != sin.shape or cos.shape[1] != n_rot // 2):
         raise KernelError("rotary table does not match the rotary width")
     f = _fn("attn_prep", "skyla_qk_norm_rope_cache",
-            [c_void_p, c_int, c_int64, c_int, c_int64, c_void_p, c_int, c_int64, c_int, c_int, c_int, c_int, c_int,
+            [c_void_p, c_int, c_int64, c_void_p, c_int, c_int64, c_int, c_int, c_int, c_int, c_int,
              c_int, c_int, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
-             c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_float,
-             c_void_p, c_int64, c_void_p, c_int, c_int64, c_int64, c_int, c_void_p])
-    _check("attn_prep", f(_ptr(qkv), dtype_code(qkv), ld, n_splits, split_stride, q_ptr, q_dt, ldq, q_off, k_off,
+             c_void_p, c_int, c_void_p, c_int, c_int, c_void_p])
+    _check("attn_prep", f(_ptr(qkv), dtype_code(qkv), ld, q_ptr, q_dt, ldq, q_off, k_off,
                           v_off, n, nq, nkv, hd, _ptr(q_norm), _ptr(k_norm), float(eps), _ptr(cos), _ptr(sin),
                           n_rot if cos is not None else 0, _ptr(tok_pos), _ptr(tok_slot),
                           _ptr(k_pool), _ptr(v_pool), cdt, _ptr(page_table), page_table.shape[1],
-                          page_size, _ptr(row_ssq), row_ssq.shape[0] if row_ssq is not None else 0,
-                          int(norm_width), float(norm_eps), *_fold_args(fold, n), _stream()))
+                          page_size, _stream()))
 
 
 def attention_plain(q: torch.Tensor, out: torch.Tensor, nq: int, nkv: int, hd: int,
@@ -809,8 +709,7 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, scratch: torch.Tensor, 
     return out
 
 
-def attention_decode_fused(qkv_partials: torch.Tensor, row_ssq: Optional[torch.Tensor], norm_width: int, norm_eps: float,
-                           q_off: int, k_off: int, v_off: int, q_norm: Optional[torch.Tensor],
+def attention_decode_fused(qkv: torch.Tensor, q_off: int, k_off: int, v_off: int, q_norm: Optional[torch.Tensor],
                            k_norm: Optional[torch.Tensor], eps: float, cos: Optional[torch.Tensor],
                            sin: Optional[torch.Tensor], n_rot: int, out: torch.Tensor, scratch: torch.Tensor,
                            nq: int, nkv: int, hd: int, k_pool: torch.Tensor, v_pool: torch.Tensor,
@@ -819,17 +718,13 @@ def attention_decode_fused(qkv_partials: torch.Tensor, row_ssq: Optional[torch.T
                            pages_needed: Optional[torch.Tensor] = None,
                            state: Optional[KernelState] = None) -> torch.Tensor:
     """Decode attention that also finishes the new token's q, k and v (what
-    ``qk_norm_rope_cache`` does) from the K-split partial sums of the QKV product and the
-    rows' sums of squares, and writes k and v to the cache.  ``row_ssq=None``: the rows of
-    ``qkv_partials`` carry their norm's scalar already."""
-    _cuda(qkv_partials, row_ssq, q_norm, k_norm, cos, sin, out, scratch, k_pool, v_pool, pages, tok_pos, pages_needed)
+    ``qk_norm_rope_cache`` does) from the float32 rows ``qkv`` [tokens, width] of the q/k/v
+    product, and writes k and v to the cache."""
+    _cuda(qkv, q_norm, k_norm, cos, sin, out, scratch, k_pool, v_pool, pages, tok_pos, pages_needed)
     _i32(pages, "pages"); _i32(tok_pos, "tok_pos"); _i32(pages_needed, "pages_needed")
     n = tok_pos.numel()
-    if (qkv_partials.dtype != torch.float32 or qkv_partials.dim() != 3 or not qkv_partials.is_contiguous()
-            or qkv_partials.shape[1] != n or (row_ssq is not None and (
-                row_ssq.dtype != torch.float32 or not row_ssq.is_contiguous() or row_ssq.dim() != 2
-                or row_ssq.shape[1] != n))):
-        raise KernelError("attention_decode_fused: partial sums [splits, tokens, width] and sums of squares [splits, tokens], float32")
+    if qkv.dtype != torch.float32 or qkv.dim() != 2 or qkv.shape[0] != n or qkv.stride(1) != 1:
+        raise KernelError("attention_decode_fused: the q/k/v rows are float32 [tokens, width]")
     if out.dtype != torch.bfloat16 or k_pool.dtype != torch.bfloat16 or tuple(k_pool.shape[1:]) != (nkv, page_size, hd) \
             or k_pool.shape != v_pool.shape or not k_pool.is_contiguous() or not v_pool.is_contiguous():
         raise KernelError("attention_decode_fused: bfloat16 output and cache pools [pages, kv heads, page, head]")
@@ -839,13 +734,11 @@ def attention_decode_fused(qkv_partials: torch.Tensor, row_ssq: Optional[torch.T
     if scratch.dtype != torch.float32 or scratch.numel() < n * nq * n_splits * (hd + 2):
         raise KernelError("attention_decode_fused: scratch too small")
     f = _fn("attention_mma", "skyla_attention_decode_fused",
-            [c_void_p, c_int, c_int64, c_int64, c_int, c_int, c_int, c_void_p, c_int, c_int, c_float, c_void_p, c_void_p,
+            [c_void_p, c_int64, c_int, c_int, c_int, c_void_p, c_void_p,
              c_float, c_void_p, c_void_p, c_int, c_void_p, c_int64, c_void_p, c_int, c_int, c_int, c_int, c_void_p,
              c_void_p, c_void_p, c_int, c_int, c_void_p, c_float, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p])
     counters = _state(state, out).merge_counters()
-    _check("attention_mma", f(_ptr(qkv_partials), qkv_partials.shape[0], qkv_partials.stride(0), qkv_partials.stride(1),
-                              q_off, k_off, v_off, _ptr(row_ssq), row_ssq.shape[0] if row_ssq is not None else 0,
-                              int(norm_width), float(norm_eps),
+    _check("attention_mma", f(_ptr(qkv), _rows(qkv, "qkv"), q_off, k_off, v_off,
                               _ptr(q_norm), _ptr(k_norm), float(eps), _ptr(cos), _ptr(sin), n_rot if cos is not None else 0,
                               _ptr(out), _rows(out, "out"), _ptr(scratch), n, nq, nkv, hd, _ptr(k_pool), _ptr(v_pool),
                               _ptr(pages), pages.shape[1], page_size, _ptr(tok_pos), float(scale), int(window or 0),

@@ -156,19 +156,18 @@ class GQAttention(Part):
         if self.position is not None:
             cos, sin, n_rot = self.position.tables(ctx.max_position + 1)
         if few:
-            whole = ctx.buffer("attn.qkv32", (1, n, (nq + 2 * nkv) * hd), torch.float32)
-            self.qkv.forward(h, whole[0], STORE, scale_in=scale_in)
+            whole = ctx.buffer("attn.qkv32", (n, (nq + 2 * nkv) * hd), torch.float32)
+            self.qkv.forward(h, whole, STORE, scale_in=scale_in)
             ctx.mark("matvec qkv")
-            pend = ctx.take_pending()
             # (up to 16 sequences; with more, every block's repeating the preparation costs more than the
             # kernel it saves: 7,560 against 7,800 to 7,980 tokens/s at batch 64)
-            if (pend is None and self._fast == 2 and ctx.is_decode and n <= self.qkv.STACKED_MAX_TOKENS
+            if (self._fast == 2 and ctx.is_decode and n <= self.qkv.STACKED_MAX_TOKENS
                     and k_pool.dtype == torch.bfloat16 and self.rt.act_dtype == torch.bfloat16):
                 # one new token per sequence: its q, k and v are finished inside the attention kernel
                 attn = ctx.buffer("attn.out", (n, nq * hd), self.rt.act_dtype)
                 n_splits, per = self.decode_splits(ctx.n_seqs, pages.shape[1])
                 scratch = ctx.buffer("attn.partials", (n * nq * n_splits * (hd + 2),), torch.float32)
-                ops.attention_decode_fused(whole, None, 0, 0.0, 0, nq * hd, (nq + nkv) * hd,
+                ops.attention_decode_fused(whole, 0, nq * hd, (nq + nkv) * hd,
                                            self.q_norm_w, self.k_norm_w, self.eps, cos, sin, n_rot, attn, scratch,
                                            nq, nkv, hd, k_pool, v_pool, pages, ctx.page_size, ctx.tok_pos,
                                            self.scale, self.window, n_splits, per, ctx.pages_needed, state=state)
@@ -177,11 +176,9 @@ class GQAttention(Part):
                 ctx.mark("matvec o")
                 return
             qkv = ctx.buffer("attn.q", (n, nq * hd), self.rt.act_dtype)
-            # if sums are pending, the prep kernel also makes x whole, after the product read it
             ops.qk_norm_rope_cache(whole, 0, nq * hd, (nq + nkv) * hd, nq, nkv, hd, self.q_norm_w,
                                    self.k_norm_w, self.eps, cos, sin, n_rot, ctx.tok_pos, ctx.tok_seq,
-                                   k_pool, v_pool, pages, ctx.page_size, q_out=qkv,
-                                   fold=(x, pend) if pend is not None else None)
+                                   k_pool, v_pool, pages, ctx.page_size, q_out=qkv)
         elif (entry.owns_cache and self.qkv.prompts(n) and ops.tc_linear_ok(h, self.qkv.weight)
               and self.hd in (32, 64, 128, 256) and (cos is None or n_rot == self.hd)
               and k_pool.dtype == torch.bfloat16 and self.rt.act_dtype == torch.bfloat16):
@@ -193,20 +190,12 @@ class GQAttention(Part):
                 page_size=ctx.page_size), scale_in=scale_in)
             ctx.mark("matvec qkv")
         elif entry.owns_cache:
-            part = self.qkv.forward_partial(h, ctx, "attn.qkv_partials") if scale_in is None else None
-            if part is not None:  # a small batch: the product is K-split, the splits are added up here
-                ctx.mark("matvec qkv")
-                qkv = ctx.buffer("attn.q", (n, nq * hd), self.rt.act_dtype)
-                ops.qk_norm_rope_cache(part, 0, nq * hd, (nq + nkv) * hd, nq, nkv, hd, self.q_norm_w,
-                                       self.k_norm_w, self.eps, cos, sin, n_rot, ctx.tok_pos, ctx.tok_seq,
-                                       k_pool, v_pool, pages, ctx.page_size, q_out=qkv)
-            else:
-                qkv = ctx.buffer("attn.qkv", (n, (nq + 2 * nkv) * hd), self.rt.act_dtype)
-                self.qkv.forward(h, qkv, STORE, scale_in=scale_in)
-                ctx.mark("matvec qkv")
-                ops.qk_norm_rope_cache(qkv, 0, nq * hd, (nq + nkv) * hd, nq, nkv, hd, self.q_norm_w,
-                                       self.k_norm_w, self.eps, cos, sin, n_rot, ctx.tok_pos, ctx.tok_seq,
-                                       k_pool, v_pool, pages, ctx.page_size)
+            qkv = ctx.buffer("attn.qkv", (n, (nq + 2 * nkv) * hd), self.rt.act_dtype)
+            self.qkv.forward(h, qkv, STORE, scale_in=scale_in)
+            ctx.mark("matvec qkv")
+            ops.qk_norm_rope_cache(qkv, 0, nq * hd, (nq + nkv) * hd, nq, nkv, hd, self.q_norm_w,
+                                   self.k_norm_w, self.eps, cos, sin, n_rot, ctx.tok_pos, ctx.tok_seq,
+                                   k_pool, v_pool, pages, ctx.page_size)
         else:  # reads the cache another run wrote: only queries are needed
             qkv = ctx.buffer("attn.q", (n, nq * hd), self.rt.act_dtype)
             self.q_only.forward(h, qkv, STORE)

@@ -11,15 +11,13 @@ mixer, feed-forward, norm, position encoding or block is one ``register_*`` call
 Interfaces (``ctx`` is the step's :class:`~skyla_kernel_b200.engine.batch.StepContext`;
 ``x`` the float32 residual stream ``[tokens, hidden]``):
 
-* norm           ``forward(ctx, x, out, rows=None)``: ``out[r] = norm(x[rows[r]])``; a norm
-                 with ``fuses_pending = True`` also takes ``pending=`` (see below)
+* norm           ``forward(ctx, x, out, rows=None)``: ``out[r] = norm(x[rows[r]])``; a norm of
+                 the form "one scalar per row times a fixed vector" may say so with
+                 ``rms_scale_form()`` (see ``parts/norm.py``), which lets the product before
+                 it prepare its input
 * mixer          ``cache_need()``, ``state_need()``, ``forward(ctx, h, x, entry)``:
                  adds its output to ``x``; ``entry`` says which cache it uses
 * feed-forward   ``forward(ctx, h, x)``: adds its output to ``x``
-                 A mixer or feed-forward may instead leave its output in ``ctx.pending``
-                 as float32 partial sums ``[splits, tokens, hidden]``; the block hands
-                 them to the next norm, which adds them to ``x`` in ascending order, or
-                 calls ``ctx.fold_pending(x)`` for any other reader of ``x``.
 * position       whatever the mixers that accept it read (rotary: ``tables()``)
 * block          ``forward(ctx, x, entry)`` with the four parts above inside
 * embedding      ``forward(ctx, tokens, x)``;  head: ``forward(ctx, h, logits)``
@@ -165,12 +163,11 @@ class Part:
 
 
 class NormedInput:
-    """The input of a mixer or feed-forward before it is computed: ``norm(x + pending)``.
+    """The input of a mixer or feed-forward before it is computed: ``norm(x)``.
 
     A block hands this to parts that set ``takes_normed_input = True``; such a part either
-    calls :meth:`tensor` (the norm runs as a kernel of its own, the pending sums are added
-    to ``x``) or does the norm inside its first product (``parts.linear.Linear`` knows how
-    for RMSNorm and few tokens) and then sees to it that ``x`` is made whole later.
+    calls :meth:`tensor` (the norm runs as a kernel of its own) or, where the product that
+    wrote ``x`` last prepared the norm's input (:attr:`ahead`), feeds that to its first product.
     Parts without the flag get ``tensor()``.
     """
 
@@ -186,11 +183,7 @@ class NormedInput:
         if self._tensor is None:
             ctx, x = self.ctx, self.x
             h = ctx.buffer("block.normed", (ctx.n_tokens, x.shape[1]), ctx.rt.act_dtype)
-            if ctx.pending is not None and getattr(self.norm, "fuses_pending", False):
-                self.norm.forward(ctx, x, h, pending=ctx.take_pending())
-            else:
-                ctx.fold_pending(x)
-                self.norm.forward(ctx, x, h)
+            self.norm.forward(ctx, x, h)
             ctx.mark("rmsnorm")
             self._tensor = h
         return self._tensor

@@ -130,14 +130,6 @@ class Linear:
                 return y
             if scale_in is not None:
                 raise ValueError("scale_in goes with the weight-streaming and the prompt kernel only (Linear.takes_scale_in)")
-            if mode == ACCUMULATE:
-                splits = self.choose_splits(m)
-                if splits > 8:  # more splits than a portable cluster holds: they meet through scratch
-                    return ops.gemm_tc(x, self.weight_map(), self.n_out, y, ops.TC_ACCUM_LAST, splits=splits,
-                                       state=self.rt.kernel_state)
-                if splits > 1:  # few tokens: K is cut across a cluster of blocks so that every SM streams
-                    return ops.gemm_tc(x, self.weight_map(), self.n_out, y, ops.TC_ACCUM_CLUSTER, splits=splits,
-                                       state=self.rt.kernel_state)
             return ops.gemm_tc(x, self.weight_map(), self.n_out, y, tc, state=self.rt.kernel_state)
         if scale_in is not None:
             raise ValueError("scale_in goes with the weight-streaming and the prompt kernel only (Linear.takes_scale_in)")
@@ -148,50 +140,6 @@ class Linear:
         (``ops.gemm_prompt`` with TC_QKV_PREP); only where :meth:`prompts` holds."""
         return ops.gemm_prompt(x, self.weight_map(), self.n_out, q_out, ops.TC_QKV_PREP, scale_in=scale_in, prep=prep,
                                state=self.rt.kernel_state)
-
-    # ---- K-split products for small batches
-    # How the K splits of "y += x W^T" meet: up to 8 splits form a thread-block cluster and add up
-    # through distributed shared memory (ops.TC_ACCUM_CLUSTER); more than 8 leave their tiles in
-    # scratch and the one that finishes last adds them up (ops.TC_ACCUM_LAST).  Measured at the
-    # 8B shape the two cost the same for 8 tokens (10.7 and 21.8 us for the O and down
-    # products); the cluster is faster for 64 (15.4 against 23.5 us, 28.0 against 35.8).
-
-    def choose_splits(self, m: int) -> int:
-        """How many K splits make a small batch's product fill the GPU (1: do not split).
-
-        One block per SM is resident; a block costs its K blocks plus about six more
-        for filling and draining its pipeline; at least 16 K blocks stay per split.
-        """
-        if m > 64:
-            return 1
-        bn = ops.token_tile(m)
-        tiles = -(-self.n_out // 128) * -(-m // bn)
-        total = -(-self.n_in // 64)
-        best, best_cost = 1, None
-        for s in range(1, max(1, total // 16) + 1):
-            per = -(-total // s)
-            if (s - 1) * per >= total:
-                continue
-            cost = -(-tiles * s // self.rt.sm_count) * (per + 6)
-            if best_cost is None or cost < best_cost:
-                best, best_cost = s, cost
-        return best
-
-    def forward_partial(self, x: torch.Tensor, ctx, name: str, fold=None):
-        """The product as K-split partial sums [splits, tokens, n_out] (float32) in a workspace
-        buffer, or ``None`` when splitting does not pay or the tensor-core kernel does not
-        take these operands; the reader adds the splits up in ascending order.
-        ``fold=(r, partials)`` rides along (``r += sum partials``) when the product is made."""
-        if self.gated or not self.tensor_cores or not ops.tc_linear_ok(x, self.weight):
-            return None
-        m = x.shape[0]
-        splits = self.choose_splits(m)
-        if splits <= 1:
-            return None
-        part = ctx.buffer(name, (splits, m, self.n_out), torch.float32)
-        ops.gemm_tc(x, self.weight_map(), self.n_out, part, ops.TC_PARTIAL_F32, splits=splits, fold=fold,
-                    state=self.rt.kernel_state)
-        return part
 
     def bytes(self) -> int:
         return self.weight.numel() * self.weight.element_size()

@@ -31,13 +31,7 @@ class RMSNorm(Part):
     def load(self, tensors) -> None:
         self.weight = self.rt.vector(tensors[self.spec.tensors["weight"]])
 
-    #: forward() accepts ``pending`` partial sums and adds them to x on the way
-    fuses_pending = True
-
-    def forward(self, ctx, x: torch.Tensor, out: torch.Tensor, rows: Optional[torch.Tensor] = None,
-                pending: Optional[torch.Tensor] = None):
-        if pending is not None:
-            return ops.add_rmsnorm(x, pending, self.weight, self.eps, out, rows)
+    def forward(self, ctx, x: torch.Tensor, out: torch.Tensor, rows: Optional[torch.Tensor] = None):
         return ops.rmsnorm(x, self.weight, self.eps, out, rows)
 
     def rms_scale_form(self):

@@ -309,18 +309,6 @@ def test_gemm_tc_store_and_accumulate(m, n, k):
     ops.check_device_errors(DEV)
 
 
-@pytest.mark.parametrize("m,n,k,splits", [(8, 128, 4096, 4), (3, 300, 1032, 3), (64, 256, 512, 8), (20, 96, 160, 2)])
-def test_gemm_tc_split_k(m, n, k, splits):
-    ops = _ops()
-    x = _rand(m, k, seed=34, dtype=torch.bfloat16)
-    w = _rand(n, k, seed=35, dtype=torch.bfloat16, scale=0.1)
-    ref = (x.double() @ w.double().T)
-    part = torch.full((splits, m, n), float("nan"), dtype=torch.float32, device=DEV)
-    ops.gemm_tc(x, ops.TensorMap(w, 128), n, part, ops.TC_PARTIAL_F32, splits=splits)
-    assert (part.double().sum(0) - ref).abs().max().item() <= 2e-5 * ref.abs().max().item() + 1e-6
-    ops.check_device_errors(DEV)
-
-
 @pytest.mark.parametrize("m,n,k", [(1, 128, 64), (9, 256, 80), (70, 384, 160), (200, 128, 520), (33, 200, 72),
                                    (300, 1000, 328)])
 def test_gemm_tc_gated(m, n, k):
@@ -502,44 +490,12 @@ def test_attention_mma_finds_one_far_key():
                 torch.testing.assert_close(got, vs[0][target, kvh].float(), rtol=2e-2, atol=2e-2)
 
 
-# ------------------------------------------------- folding of K-split partial sums
-@pytest.mark.parametrize("width,splits", [(80, 2), (4096, 4)])
-def test_add_rmsnorm_and_fold(width, splits):
+def test_prep_takes_32_bit_rows_and_writes_bfloat16():
+    """Few tokens: the product leaves 32-bit rows; queries and cache are bfloat16."""
     ops = _ops()
-    x0 = _rand(9, width, seed=51, scale=2.0)
-    part = _rand(splits, 9, width, seed=52)
-    w = 1 + 0.1 * _rand(width, seed=53)
-    whole = x0.clone()
-    for s_ in range(splits):
-        whole += part[s_]
-    for out_dtype in (torch.float32, torch.bfloat16):
-        x = x0.clone()
-        out = torch.empty(9, width, dtype=out_dtype, device=DEV)
-        ops.add_rmsnorm(x, part, w, 1e-5, out)
-        assert torch.equal(x, whole)  # ascending order, the same bits
-        ref = torch.empty_like(out)
-        ops.rmsnorm(whole, w, 1e-5, ref)
-        assert torch.equal(out, ref)
-    rows = torch.tensor([8, 2], dtype=torch.int32, device=DEV)
-    x = x0.clone()
-    out = torch.empty(2, width, device=DEV)
-    ops.add_rmsnorm(x, part, w, 1e-5, out, rows)
-    ref = torch.empty(9, width, device=DEV)
-    ops.rmsnorm(whole, w, 1e-5, ref)
-    assert torch.equal(out, ref[rows.long()]) and torch.equal(x[8], whole[8]) and torch.equal(x[0], x0[0])
-    x = x0.clone()
-    ops.fold_partials(x, part)
-    assert torch.equal(x, whole)
-
-
-def test_prep_adds_up_partial_sums():
-    ops = _ops()
-    nq, nkv, hd, T, S = 4, 2, 32, 5, 3
+    nq, nkv, hd, T = 4, 2, 32, 5
     width = (nq + 2 * nkv) * hd
-    part = _rand(S, T, width, seed=61)
-    whole = part[0].clone()
-    for s_ in range(1, S):
-        whole += part[s_]
+    whole = _rand(T, width, seed=61)
     qn, kn = 1 + 0.2 * _rand(hd, seed=62), 1 + 0.2 * _rand(hd, seed=63)
     freqs, _ = plain.rope_frequencies(hd, 10000.0)
     ang = (torch.arange(100, dtype=torch.float32)[:, None] * freqs[None, :]).double()
@@ -548,14 +504,14 @@ def test_prep_adds_up_partial_sums():
     seq = torch.tensor([0, 0, 0, 0, 1], dtype=torch.int32, device=DEV)
     table = torch.tensor([[1, 2], [0, 3]], dtype=torch.int32, device=DEV)
     res = []
-    for src in (part, whole.to(torch.bfloat16)):
+    for src in (whole, whole.to(torch.bfloat16)):
         kp = torch.zeros(4, nkv, 64, hd, dtype=torch.bfloat16, device=DEV)
         vp = torch.zeros_like(kp)
         q = torch.zeros(T, nq * hd, dtype=torch.bfloat16, device=DEV)
         ops.qk_norm_rope_cache(src, 0, nq * hd, (nq + nkv) * hd, nq, nkv, hd, qn, kn, 1e-6, cos, sin, hd, pos, seq,
                                kp, vp, table, 64, q_out=q)
         res.append((q, kp, vp))
-    for a, b in zip(res[0], res[1]):  # from 32-bit sums against from the rounded whole: bf16 apart at most
+    for a, b in zip(res[0], res[1]):  # from 32-bit rows against from the rounded rows: bf16 apart at most
         torch.testing.assert_close(a.float(), b.float(), rtol=2e-2, atol=2e-2)
     assert res[0][0].abs().sum() > 0 and res[0][1].abs().sum() > 0
 
@@ -677,7 +633,7 @@ def test_gemm_tc_rows_refuses():
     with pytest.raises(KernelError):  # a tile height that is no multiple of 8
         ops.gemm_tc_rows(x[:4], ops.TensorMap(w, 100), 100, 128, torch.empty(4, 128, device=DEV), ops.TC_STORE_F32)
     with pytest.raises(KernelError):  # an epilogue it does not have
-        ops.gemm_tc_rows(x[:4], ops.TensorMap(w, 128), 128, 128, torch.empty(4, 128, device=DEV), ops.TC_PARTIAL_F32)
+        ops.gemm_tc_rows(x[:4], ops.TensorMap(w, 128), 128, 128, torch.empty(4, 128, device=DEV), 4)
     with pytest.raises(KernelError):  # more splits than K blocks
         ops.gemm_tc_rows(x[:4], ops.TensorMap(w, 128), 128, 128, torch.empty(4, 128, device=DEV), ops.TC_STORE_F32, splits=2)
     with pytest.raises(KernelError, match="outputs in fours"):  # K splits of a width that is no multiple of four
@@ -687,73 +643,16 @@ def test_gemm_tc_rows_refuses():
         ops.TensorMap(_rand(128, 72, seed=3, dtype=torch.bfloat16), 128, 2)
 
 
-def test_gemm_tc_fold_side_job():
-    ops = _ops()
-    m, n, k, hidden = 8, 256, 512, 4096
-    x = _rand(m, k, seed=91, dtype=torch.bfloat16)
-    w = _rand(n, k, seed=92, dtype=torch.bfloat16, scale=0.1)
-    r0 = _rand(m, hidden, seed=93)
-    part = _rand(4, m, hidden, seed=94)
-    r = r0.clone()
-    y = torch.empty(2, m, n, dtype=torch.float32, device=DEV)
-    ops.gemm_tc(x, ops.TensorMap(w, 128), n, y, ops.TC_PARTIAL_F32, splits=2, fold=(r, part))
-    want = r0.clone()
-    for s_ in range(4):
-        want += part[s_]
-    assert torch.equal(r, want)
-    ref = x.double() @ w.double().T
-    assert (y.double().sum(0) - ref).abs().max().item() <= 2e-5 * ref.abs().max().item() + 1e-6
-
-
-@pytest.mark.parametrize("m,n,k,splits", [(8, 4096, 4096, 4), (1, 131, 520, 2), (33, 384, 12288, 12), (64, 200, 1032, 3)])
-def test_gemm_tc_last_arriver_accumulate(m, n, k, splits):
-    """K cut across blocks; each leaves its tile in scratch and the last one to finish adds them up."""
-    ops = _ops()
-    x = _rand(m, k, seed=95, dtype=torch.bfloat16)
-    w = _rand(n, k, seed=96, dtype=torch.bfloat16, scale=0.1)
-    acc0 = _rand(m, n, seed=97)
-    ref = acc0.double() + x.double() @ w.double().T
-    runs = []
-    for _ in range(3):  # the counters must come back to zero by themselves
-        acc = acc0.clone()
-        ops.gemm_tc(x, ops.TensorMap(w, 128), n, acc, ops.TC_ACCUM_LAST, splits=splits)
-        runs.append(acc)
-    assert (runs[0].double() - ref).abs().max().item() <= 3e-5 * ref.abs().max().item() + 1e-5
-    assert torch.equal(runs[0], runs[1]) and torch.equal(runs[0], runs[2])  # split order, whoever finishes last
-    assert int(ops.default_state(DEV).tile_counters(1).abs().sum()) == 0
-    ops.check_device_errors(DEV)
-
-
-@pytest.mark.parametrize("m,n,k,splits", [(8, 4096, 4096, 4), (1, 131, 520, 2), (33, 384, 12288, 8), (64, 200, 1032, 3)])
-def test_gemm_tc_cluster_accumulate(m, n, k, splits):
-    """K cut across a cluster of blocks; the splits meet in distributed shared memory."""
-    ops = _ops()
-    x = _rand(m, k, seed=95, dtype=torch.bfloat16)
-    w = _rand(n, k, seed=96, dtype=torch.bfloat16, scale=0.1)
-    acc0 = _rand(m, n, seed=97)
-    ref = acc0.double() + x.double() @ w.double().T
-    runs = []
-    for _ in range(2):
-        acc = acc0.clone()
-        ops.gemm_tc(x, ops.TensorMap(w, 128), n, acc, ops.TC_ACCUM_CLUSTER, splits=splits)
-        runs.append(acc)
-    assert (runs[0].double() - ref).abs().max().item() <= 3e-5 * ref.abs().max().item() + 1e-5
-    assert torch.equal(runs[0], runs[1])  # a fixed order of summation: the same bits every time
-    ops.check_device_errors(DEV)
-
-
 @pytest.mark.parametrize("nq,nkv,hd,n_rot,window", [(32, 8, 128, 128, 0), (6, 1, 32, 32, 0), (3, 3, 48, 24, 70), (8, 2, 64, 64, 0)])
 def test_attention_decode_fused_prep(nq, nkv, hd, n_rot, window):
     """The decode kernel finishing q, k and v itself against prep kernel + decode kernel."""
     ops = _ops()
     dt = torch.bfloat16
     lens = [1, 64, 65, 200, 333, 128]   # lengths after the new token
-    B, S = len(lens), 3
+    B = len(lens)
     width = (nq + 2 * nkv) * hd
     k_pool, v_pool, table, ks, vs = _paged(B, lens, nkv, hd, dt, seed=nq + hd)
-    part = _rand(S, B, width, seed=101)
-    hidden = 777
-    ssq = (_rand(S, B, seed=102).abs() + 0.5) * hidden
+    rows = _rand(B, width, seed=101)
     qn, kn = 1 + 0.2 * _rand(hd, seed=103), 1 + 0.2 * _rand(hd, seed=104)
     freqs, _ = plain.rope_frequencies(n_rot, 10000.0)
     ang = (torch.arange(512, dtype=torch.float32)[:, None] * freqs[None, :]).double()
@@ -765,15 +664,15 @@ def test_attention_decode_fused_prep(nq, nkv, hd, n_rot, window):
     # two kernels
     kp1, vp1 = k_pool.clone(), v_pool.clone()
     q = torch.empty(B, nq * hd, dtype=dt, device=DEV)
-    ops.qk_norm_rope_cache(part, 0, nq * hd, (nq + nkv) * hd, nq, nkv, hd, qn, kn, 1e-6, cos, sin, n_rot, tok_pos, seq,
-                           kp1, vp1, table, 64, q_out=q, row_ssq=ssq, norm_width=hidden, norm_eps=1e-5)
+    ops.qk_norm_rope_cache(rows, 0, nq * hd, (nq + nkv) * hd, nq, nkv, hd, qn, kn, 1e-6, cos, sin, n_rot, tok_pos, seq,
+                           kp1, vp1, table, 64, q_out=q)
     want = torch.empty(B, nq * hd, dtype=dt, device=DEV)
     scratch = torch.empty(B * nq * n_splits * (hd + 2), dtype=torch.float32, device=DEV)
     ops.attention_decode(q, want, scratch, nq, nkv, hd, kp1, vp1, table, 64, tok_pos, scale, window, n_splits, per)
     # one kernel
     kp2, vp2 = k_pool.clone(), v_pool.clone()
     got = torch.full_like(want, float("nan"))
-    ops.attention_decode_fused(part, ssq, hidden, 1e-5, 0, nq * hd, (nq + nkv) * hd, qn, kn, 1e-6, cos, sin, n_rot, got,
+    ops.attention_decode_fused(rows, 0, nq * hd, (nq + nkv) * hd, qn, kn, 1e-6, cos, sin, n_rot, got,
                                scratch, nq, nkv, hd, kp2, vp2, table, 64, tok_pos, scale, window, n_splits, per)
     torch.testing.assert_close(got.float(), want.float(), rtol=2e-2, atol=2e-2)
     assert torch.equal(kp2, kp1) and torch.equal(vp2, vp1)  # the same k and v reached the cache

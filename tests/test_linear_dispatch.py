@@ -55,19 +55,6 @@ def test_widths_that_are_no_multiple_of_eight_stay_on_the_plain_kernel():
     assert not lin.tensor_cores and not lin.streams(4) and not lin.prompts(500)
 
 
-def test_k_splits_of_small_batches():
-    qkv, o, down = _lin(QKV, H), _lin(H, H), _lin(H, INTER)
-    for lin in (qkv, o, down):
-        total = -(-lin.n_in // 64)
-        for m in (1, 17, 32, 64):
-            s = lin.choose_splits(m)
-            assert 1 <= s <= total // 16
-            per = -(-total // s)
-            assert (s - 1) * per < total          # no split is empty
-        assert lin.choose_splits(65) == 1 and lin.choose_splits(4096) == 1
-    assert down.choose_splits(32) >= o.choose_splits(32) > 1  # both fill the SMs: 32 tiles, four splits each
-
-
 def test_rows_plans_fill_the_sms_with_one_wave():
     for n_out, n_in, gated in ((QKV, H, False), (H, H, False), (INTER, H, True), (H, INTER, False), (151936, H, False)):
         rows, splits, kkb, kstack = ops.rows_plan(n_out, n_in, gated, 16, 148)

@@ -105,7 +105,6 @@ def test_attention_part_whole_then_one_by_one(dtype, hidden, nq, nkv, hd, n_rot,
         ctx = batcher.build([StepItem(slot, [0] * (b - a), [])])
         x = torch.zeros(b - a, hidden, device=DEV)
         part.forward(ctx, h_all[a:b].to(DEV).to(rt.act_dtype), x, EntryBinding(0, True))
-        ctx.fold_pending(x)  # a small batch may leave its last product as split sums
         cache.advance([(slot, b - a)])
         got.append(x.cpu())
     from helpers import assert_close
@@ -132,7 +131,6 @@ def test_swiglu_part(dtype):
     x0 = torch.randn(9, 80, generator=torch.Generator().manual_seed(7))
     x = x0.clone().to(DEV)
     part.forward(ctx, h.to(DEV).to(rt.act_dtype), x)
-    ctx.fold_pending(x)
     ref = x0 + plain.swiglu(h, w["f.gate_proj"], w["f.up_proj"], w["f.down_proj"])
     torch.testing.assert_close(x.cpu(), ref, **_tol(dtype))
 
@@ -274,7 +272,6 @@ def test_block_alone(dtype):
         ctx = batcher.build([StepItem(slot, [0] * (b - a), [])])
         x = x0[a:b].clone().to(DEV)
         block.forward(ctx, x, EntryBinding(0, True))
-        ctx.fold_pending(x)
         cache.advance([(slot, b - a)])
         got.append(x.cpu())
     assert_close(torch.cat(got), ref, dtype, f"block alone {dtype}")
@@ -307,7 +304,6 @@ def test_wide_groups_decode_through_the_prompt_kernel():
         ctx = batcher.build([StepItem(slot, [0] * (b - a), [])])
         x = torch.zeros(b - a, hidden, device=DEV)
         part.forward(ctx, h_all[a:b].to(DEV).to(torch.bfloat16), x, EntryBinding(0, True))
-        ctx.fold_pending(x)
         cache.advance([(slot, b - a)])
         got.append(x.cpu())
     assert_close(torch.cat(got), ref, "bfloat16", "34 query heads over 2 key/value heads")
