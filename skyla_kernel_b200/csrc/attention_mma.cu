@@ -19,12 +19,14 @@
 // chunks of a row swizzled (or the rows padded) so that the fragment reads spread
 // over the banks; the warps read their fragments from there, 16 bytes at a time.
 //
-// Decode: one CTA per (key/value head, sequence, split of the context); the 16 rows
-// are the query heads that share the key/value head (grouped-query attention), so
-// the cache is read once for all of them, as the reference does with N_REP
-// (attention.comp:60-79).  The CTA's eight warps work on two pages at a time, 16 of
-// a page's 64 positions each; the warps are merged in shared memory; splits are aligned to absolute positions and merged by a
-// second kernel in fixed order (skyla-shaders/shaders/attention_merge.comp:17-41).
+// Decode: the 16 rows of a tile are the query heads that share a key/value head (grouped-query
+// attention), so the cache is read once for all of them, as the reference does with N_REP
+// (attention.comp:60-79).  The pages of all (sequence, key/value head) pairs of the step are laid end
+// to end and dealt to the CTAs in equal runs (see kPlanInts), so that every CTA reads the same amount
+// whatever the lengths are; a CTA's four warps take 16 of a page's 64 positions each and are merged in
+// shared memory; the pieces of a pair that different CTAs read are merged, in the order of the
+// positions, by the CTA that finishes last (skyla-shaders/shaders/attention_merge.comp:17-41 is the
+// reference's merge, a pass of its own).
 // Prefill: one CTA per (64 new tokens of one sequence, query head), a warp per 16
 // tokens, causal by row.
 #include "common.cuh"
@@ -335,20 +337,35 @@ struct FusedPrep {
   bf16* k_pool; bf16* v_pool; int n_tokens;
 };
 
+// How a decode step's pages are dealt to the blocks.  The items of a step are its (sequence, key/value
+// head) pairs, item = sequence * nkv + head, each with the pages of its sequence that the window still
+// sees.  A block takes a run of consecutive pages of consecutive items: a run may end one item and begin
+// the next.  Row j of the plan says where block j starts: (sequence, head, page of that item, pages of the
+// run, position of that sequence's new token, first block and number of pieces of that item, 0).  After
+// the rows the plan holds (first block, pieces) of every item: the blocks that read one item are
+// consecutive.  Who cuts the runs is free in how: a host that knows the positions may give every item
+// equal pieces, or lay all pages end to end and cut them evenly (attn_decode_plan_kernel does the
+// latter); the kernel only follows the rows.
+// The piece of an item that block j reads has the slot j + item for its partial result, which no other
+// piece has (from one piece to the next, j or the item grows); the pieces of one item lie in consecutive
+// slots.
+constexpr int kPlanInts = 8;
+
 struct DecodeArgs {
-  const bf16* q; int64_t ldq; float* part; int n_splits, pages_per_split;
+  const bf16* q; int64_t ldq; float* part;
   int nq, nkv; PagedKV kv; const int32_t* tok_pos; float scale; int window;
   FusedPrep prep;  // prep.qkv == nullptr: q comes prepared in `q`, k and v are in the cache
-  // if set: the pages the longest sequence of this step needs; the splits then share those
-  // evenly (pages_per_split is ignored), so a launch recorded once fits every context length
-  const int32_t* pages_needed;
-  // if set: the split of a (sequence, kv head) that finishes last merges the splits itself and
-  // writes the heads' rows here; else attn_merge_kernel does that in a launch of its own
+  const int32_t* plan;   // [blocks][kPlanInts]
+  const int32_t* items;  // [items][2]: first block, pieces
+  // if set: the part of an item that finishes last merges the parts itself and writes the heads' rows
+  // here (an item that is one part is written straight away); else every part leaves its partial result,
+  // `meta` gets (first slot, parts) of every item, and attn_merge_kernel follows in a launch of its own
   bf16* out; int64_t ldo;
-  // one zeroed counter per (sequence, kv head) for "who finishes last"; the last arriver puts it back to
+  // one zeroed counter per item for "who finishes last"; the last arriver puts it back to
   // zero.  They belong to whoever launches (an engine's kernel state): launches that share them must not
   // overlap on the device
   int* counters;
+  int32_t* meta;
 };
 
 constexpr int kDecodeWarps = 4;
@@ -363,220 +380,323 @@ __global__ void __launch_bounds__(kDecodeWarps * 32, 2) attn_decode_kernel(Decod
   __shared__ int merges;
   allow_dependents();
   // What the kernel before this one wrote: the unfinished q, k, v (fused) or q and the new
-  // token's row of the cache (not fused).  Positions, page lists and the pages of earlier
+  // token's row of the cache (not fused).  Positions, page lists, the plan and the pages of earlier
   // tokens are older than that, so the fused kernel starts fetching pages right away.
   const bool fused = a.prep.qkv != nullptr;
+  bool waited = !fused;
   if (!fused) grid_dependency_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
-  const int kvh = blockIdx.x, b = blockIdx.y, split = blockIdx.z;
   const int G = a.nq / a.nkv;
-  const int pos = a.tok_pos[b];
-  const int first = a.window > 0 ? max(0, pos - a.window + 1) : 0;
-  const int per_split = a.pages_needed != nullptr
-                            ? max(1, (a.pages_needed[0] + a.n_splits - 1) / a.n_splits) : a.pages_per_split;
-  const int page_begin = max(split * per_split, first / kPage);
-  const int page_end = min((split + 1) * per_split, pos / kPage + 1);
-  const int n_pages = max(0, page_end - page_begin);
-  const int32_t* seq_pages = a.kv.pages + (int64_t)b * a.kv.max_pages;
-
-  auto issue = [&](int i) {
-    if (i < n_pages) {
-      const size_t row0 = ((size_t)seq_pages[page_begin + i] * a.kv.nkv + kvh) * kPage;
-      stage_page<HD, NW * 32>(stages + (size_t)(i % kStages) * Stage<HD>::kElems, a.kv.k + row0 * HD, a.kv.v + row0 * HD,
-                              threadIdx.x);
-    }
-    cp_async_commit();  // an empty group keeps the count the same for every thread
-  };
-  constexpr int kAhead = kStages - 1;
-#pragma unroll
-  for (int i = 0; i < kAhead; ++i) issue(i);
-  if (fused) grid_dependency_wait();
-
-  uint32_t qa[S::NQ], qb[S::NQ];
-#pragma unroll
-  for (int i = 0; i < S::NQ; ++i) qa[i] = qb[i] = 0u;
+  const int4 row0v = reinterpret_cast<const int4*>(a.plan)[2 * blockIdx.x];
+  const int4 row1v = reinterpret_cast<const int4*>(a.plan)[2 * blockIdx.x + 1];
+  int b = row0v.x, kvh = row0v.y, page0 = row0v.z, left = row0v.w;
+  int pos = row1v.x, j_first = row1v.y, n_parts = row1v.z;
+  const float scale_log2 = a.scale * kLog2e;
   // after the page stages: [G+2][HD] bf16 finished heads (q heads, then k, then v), [NW][HD] float scratch
   bf16* fresh = stages + (size_t)kStages * Stage<HD>::kElems;
-  const bool owner = fused && page_end == pos / kPage + 1 && n_pages > 0;  // this block's pages end at the new token
-  if (fused) {
-    float* u = reinterpret_cast<float*>(fresh + (size_t)(G + 2) * HD) + (size_t)warp * HD;
-    const FusedPrep& p = a.prep;
-    for (int job = warp; job < G + 2; job += NW) {  // q heads of the group, then k, then v
-      if (job >= G && !owner) continue;
-      const bool is_q = job < G, is_k = job == G;
-      const float* src = p.qkv + (int64_t)b * p.ld +
-                         (is_q ? p.q_off + (kvh * G + job) * HD : (is_k ? p.k_off : p.v_off) + kvh * HD);
-      float ss = 0.f;
-      for (int e = lane; e < HD; e += 32) {
-        const float v = src[e];
-        u[e] = v;
-        ss = fmaf(v, v, ss);
-      }
-      const float* nw = is_q ? p.q_norm : (is_k ? p.k_norm : nullptr);
-      if (nw != nullptr) {
-        ss = warp_sum(ss);
-        const float inv = 1.0f / sqrtf(ss / (float)HD + p.eps);
-        for (int e = lane; e < HD; e += 32) u[e] *= inv * nw[e];
-      }
-      __syncwarp();
-      const int half = p.n_rot / 2;
-      bf16* dst = fresh + (size_t)job * HD;
-      for (int e = lane; e < HD; e += 32) {
-        float v = u[e];
-        if ((is_q || is_k) && p.cos_t != nullptr && e < p.n_rot) {
-          const int i = e < half ? e : e - half;
-          const float c = p.cos_t[(int64_t)pos * half + i], sn = p.sin_t[(int64_t)pos * half + i];
-          const float x0 = u[i], x1 = u[i + half];
-          v = e < half ? x0 * c - x1 * sn : x0 * sn + x1 * c;
-        }
-        dst[e] = __float2bfloat16_rn(v);
-      }
-      __syncwarp();
-      if (!is_q) {  // the token's place in the cache, for the steps to come
-        const size_t row = ((size_t)seq_pages[pos / kPage] * a.kv.nkv + kvh) * kPage + pos % kPage;
-        bf16* pool = is_k ? p.k_pool : p.v_pool;
-        for (int e = lane; e < HD; e += 32) pool[row * HD + e] = dst[e];
-      }
-    }
-    __syncthreads();
-    if (g < G) load_row<HD>(fresh + (size_t)g * HD, t, qa);
-    if (g + 8 < G) load_row<HD>(fresh + (size_t)(g + 8) * HD, t, qb);
-  } else {
-    const bf16* qrow = a.q + (int64_t)b * a.ldq + (int64_t)kvh * G * HD;
-    if (g < G) load_row<HD>(qrow + g * HD, t, qa);
-    if (g + 8 < G) load_row<HD>(qrow + (g + 8) * HD, t, qb);
-  }
-  const int hi0 = g < G ? pos : -1, hi1 = g + 8 < G ? pos : -1;
-  const float scale_log2 = a.scale * kLog2e;
+  constexpr int kAhead = kStages - 1;
 
-  RowState<HD> st;
-  st.init();
-  for (int pg = 0; pg < n_pages; ++pg) {
-    issue(pg + kAhead);  // into the stage that the round before this one read
-    cp_async_wait<kAhead>();
-    __syncthreads();
-    if (owner && pg == n_pages - 1) {
-      // the staged copy of the token's page was read before k and v were written: put them in
-      bf16* page = stages + (size_t)(pg % kStages) * Stage<HD>::kElems;
-      const int r = pos % kPage;
-      for (int c = threadIdx.x; c < 2 * (HD / 8); c += NW * 32) {
-        const bool is_v = c >= HD / 8;
-        const int chunk = is_v ? c - HD / 8 : c;
-        const int x = is_v ? Swz<HD>::v(r) : Swz<HD>::k(r);
-        *reinterpret_cast<uint4*>(page + (is_v ? kPage * RS : 0) + r * RS + 8 * (chunk ^ x)) =
-            *reinterpret_cast<const uint4*>(fresh + (size_t)(G + (is_v ? 1 : 0)) * HD + 8 * chunk);
+  while (left > 0) {  // one piece after the other
+    const int first = a.window > 0 ? max(0, pos - a.window + 1) : 0;
+    const int item_pages = pos / kPage + 1 - first / kPage;
+    const int n_pages = min(left, item_pages - page0);
+    const int page_begin = first / kPage + page0;
+    const int32_t* seq_pages = a.kv.pages + (int64_t)b * a.kv.max_pages;
+
+    auto issue = [&](int i) {
+      if (i < n_pages) {
+        const size_t row0 = ((size_t)seq_pages[page_begin + i] * a.kv.nkv + kvh) * kPage;
+        stage_page<HD, NW * 32>(stages + (size_t)(i % kStages) * Stage<HD>::kElems, a.kv.k + row0 * HD, a.kv.v + row0 * HD,
+                                threadIdx.x);
+      }
+      cp_async_commit();  // an empty group keeps the count the same for every thread
+    };
+#pragma unroll
+    for (int i = 0; i < kAhead; ++i) issue(i);
+    if (!waited) {
+      grid_dependency_wait();
+      waited = true;
+    }
+
+    uint32_t qa[S::NQ], qb[S::NQ];
+#pragma unroll
+    for (int i = 0; i < S::NQ; ++i) qa[i] = qb[i] = 0u;
+    const bool owner = fused && page0 + n_pages == item_pages;  // this part ends at the new token
+    if (fused) {
+      float* uu = reinterpret_cast<float*>(fresh + (size_t)(G + 2) * HD) + (size_t)warp * HD;
+      const FusedPrep& p = a.prep;
+      for (int job = warp; job < G + 2; job += NW) {  // q heads of the group, then k, then v
+        if (job >= G && !owner) continue;
+        const bool is_q = job < G, is_k = job == G;
+        const float* src = p.qkv + (int64_t)b * p.ld +
+                           (is_q ? p.q_off + (kvh * G + job) * HD : (is_k ? p.k_off : p.v_off) + kvh * HD);
+        float ss = 0.f;
+        for (int e = lane; e < HD; e += 32) {
+          const float v = src[e];
+          uu[e] = v;
+          ss = fmaf(v, v, ss);
+        }
+        const float* nw = is_q ? p.q_norm : (is_k ? p.k_norm : nullptr);
+        if (nw != nullptr) {
+          ss = warp_sum(ss);
+          const float inv = 1.0f / sqrtf(ss / (float)HD + p.eps);
+          for (int e = lane; e < HD; e += 32) uu[e] *= inv * nw[e];
+        }
+        __syncwarp();
+        const int half = p.n_rot / 2;
+        bf16* dst = fresh + (size_t)job * HD;
+        for (int e = lane; e < HD; e += 32) {
+          float v = uu[e];
+          if ((is_q || is_k) && p.cos_t != nullptr && e < p.n_rot) {
+            const int i = e < half ? e : e - half;
+            const float c = p.cos_t[(int64_t)pos * half + i], sn = p.sin_t[(int64_t)pos * half + i];
+            const float x0 = uu[i], x1 = uu[i + half];
+            v = e < half ? x0 * c - x1 * sn : x0 * sn + x1 * c;
+          }
+          dst[e] = __float2bfloat16_rn(v);
+        }
+        __syncwarp();
+        if (!is_q) {  // the token's place in the cache, for the steps to come
+          const size_t row = ((size_t)seq_pages[pos / kPage] * a.kv.nkv + kvh) * kPage + pos % kPage;
+          bf16* pool = is_k ? p.k_pool : p.v_pool;
+          for (int e = lane; e < HD; e += 32) pool[row * HD + e] = dst[e];
+        }
       }
       __syncthreads();
+      if (g < G) load_row<HD>(fresh + (size_t)g * HD, t, qa);
+      if (g + 8 < G) load_row<HD>(fresh + (size_t)(g + 8) * HD, t, qb);
+    } else {
+      const bf16* qrow = a.q + (int64_t)b * a.ldq + (int64_t)kvh * G * HD;
+      if (g < G) load_row<HD>(qrow + g * HD, t, qa);
+      if (g + 8 < G) load_row<HD>(qrow + (g + 8) * HD, t, qb);
     }
-    const bf16* sk = stages + (size_t)(pg % kStages) * Stage<HD>::kElems;
-    const int key0 = (page_begin + pg) * kPage + 16 * warp;  // this warp's 16 positions
-    if (key0 + 15 <= pos && key0 >= first)  // all 16 keys are visible: nothing to mask
-      attend16<HD, false>(qa, qb, sk + 16 * warp * RS, sk + (kPage + 16 * warp) * RS, key0, first, hi0, first, hi1,
-                          scale_log2, st, g, t);
-    else if (key0 <= pos && key0 + 15 >= first)
-      attend16<HD>(qa, qb, sk + 16 * warp * RS, sk + (kPage + 16 * warp) * RS, key0, first, hi0, first, hi1,
-                   scale_log2, st, g, t);
-    __syncthreads();  // the stage is refilled in the next round
-  }
-  cp_async_wait<0>();
-  __syncthreads();
-  // this thread's shares of the row sums -> whole rows
-  st.l[0] += __shfl_xor_sync(0xffffffffu, st.l[0], 1); st.l[0] += __shfl_xor_sync(0xffffffffu, st.l[0], 2);
-  st.l[1] += __shfl_xor_sync(0xffffffffu, st.l[1], 1); st.l[1] += __shfl_xor_sync(0xffffffffu, st.l[1], 2);
+    const int hi0 = g < G ? pos : -1, hi1 = g + 8 < G ? pos : -1;
 
-  float* so = smem + (size_t)warp * 16 * HD;
-  float* sm = smem + (size_t)NW * 16 * HD + warp * 16;
-  float* sl = sm + NW * 16;
-  stage_rows<HD>(so, st.o, g, t, g < G, g + 8 < G, 1.f, 1.f);
-  if (t == 0) { sm[g] = st.m[0]; sm[g + 8] = st.m[1]; sl[g] = st.l[0]; sl[g + 8] = st.l[1]; }
-  __syncthreads();
-  // merge the warps in fixed order; one partial per (head, split): m, l, acc[HD]
-  const float* am = smem + (size_t)NW * 16 * HD;
-  const float* al = am + NW * 16;
-  for (int idx = threadIdx.x; idx < G * HD; idx += NW * 32) {
-    const int r = idx / HD, c = idx % HD;
-    float M = -INFINITY;
-    for (int w = 0; w < NW; ++w) M = fmaxf(M, am[w * 16 + r]);
-    const float ref = M == -INFINITY ? 0.f : M;
-    float acc = 0.f, L = 0.f;
-    for (int w = 0; w < NW; ++w) {
-      const float f = exp2f(am[w * 16 + r] - ref);
-      acc += f * smem[(size_t)w * 16 * HD + staged_index<HD>(r, c)];
-      L += f * al[w * 16 + r];
-    }
-    float* out = a.part + (((size_t)b * a.nq + kvh * G + r) * a.n_splits + split) * (HD + 2);
-    out[2 + c] = acc;
-    if (c == 0) { out[0] = M; out[1] = L; }
-  }
-  if (a.out == nullptr) return;
-  // who finishes last of this (sequence, kv head) merges its splits, in the order of the splits
-  __threadfence();
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    int* counter = &a.counters[b * a.nkv + kvh];
-    const int before = atomicAdd(counter, 1);
-    merges = before == a.n_splits - 1;
-    if (merges) *counter = 0;  // all are in: ready for the next launch
-  }
-  __syncthreads();
-  if (!merges) return;
-  __threadfence();
-  // Every partial is a round trip to the L2, so a thread asks for all of its own at once: two
-  // columns of one head, eight splits at a time, folded into the running (maximum, sum, row) in
-  // the order of the splits.
-  for (int idx = threadIdx.x; idx < G * (HD / 2); idx += NW * 32) {
-    const int r = idx / (HD / 2), c = 2 * (idx % (HD / 2)), h = kvh * G + r;
-    const float* p = a.part + ((size_t)b * a.nq + h) * a.n_splits * (HD + 2);
-    float M = -INFINITY, total = 0.f, o0 = 0.f, o1 = 0.f;
-    for (int s0 = 0; s0 < a.n_splits; s0 += 8) {
-      float m8[8], l8[8];
-      float2 o8[8];
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const bool in = s0 + j < a.n_splits;
-        const float* ps = p + (size_t)(s0 + j) * (HD + 2);
-        const float2 ml = in ? __ldcg(reinterpret_cast<const float2*>(ps)) : make_float2(-INFINITY, 0.f);
-        m8[j] = ml.x;
-        l8[j] = ml.y;
-        o8[j] = in ? __ldcg(reinterpret_cast<const float2*>(ps + 2 + c)) : make_float2(0.f, 0.f);
+    RowState<HD> st;
+    st.init();
+    for (int pg = 0; pg < n_pages; ++pg) {
+      issue(pg + kAhead);  // into the stage that the round before this one read
+      cp_async_wait<kAhead>();
+      __syncthreads();
+      if (owner && pg == n_pages - 1) {
+        // the staged copy of the token's page was read before k and v were written: put them in
+        bf16* page = stages + (size_t)(pg % kStages) * Stage<HD>::kElems;
+        const int r = pos % kPage;
+        for (int c = threadIdx.x; c < 2 * (HD / 8); c += NW * 32) {
+          const bool is_v = c >= HD / 8;
+          const int chunk = is_v ? c - HD / 8 : c;
+          const int x = is_v ? Swz<HD>::v(r) : Swz<HD>::k(r);
+          *reinterpret_cast<uint4*>(page + (is_v ? kPage * RS : 0) + r * RS + 8 * (chunk ^ x)) =
+              *reinterpret_cast<const uint4*>(fresh + (size_t)(G + (is_v ? 1 : 0)) * HD + 8 * chunk);
+        }
+        __syncthreads();
       }
-      float Mn = M;
-#pragma unroll
-      for (int j = 0; j < 8; ++j) Mn = fmaxf(Mn, m8[j]);
-      if (Mn == -INFINITY) continue;
-      const float keep = exp2f(M - Mn);  // 0 for the first chunk (M is -inf)
-      total *= keep;
-      o0 *= keep;
-      o1 *= keep;
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const float f = exp2f(m8[j] - Mn);
-        total += f * l8[j];
-        o0 += f * o8[j].x;
-        o1 += f * o8[j].y;
-      }
-      M = Mn;
+      const bf16* sk = stages + (size_t)(pg % kStages) * Stage<HD>::kElems;
+      const int key0 = (page_begin + pg) * kPage + 16 * warp;  // this warp's 16 positions
+      if (key0 + 15 <= pos && key0 >= first)  // all 16 keys are visible: nothing to mask
+        attend16<HD, false>(qa, qb, sk + 16 * warp * RS, sk + (kPage + 16 * warp) * RS, key0, first, hi0, first, hi1,
+                            scale_log2, st, g, t);
+      else if (key0 <= pos && key0 + 15 >= first)
+        attend16<HD>(qa, qb, sk + 16 * warp * RS, sk + (kPage + 16 * warp) * RS, key0, first, hi0, first, hi1,
+                     scale_log2, st, g, t);
+      __syncthreads();  // the stage is refilled in the next round
     }
-    *reinterpret_cast<__nv_bfloat162*>(a.out + (int64_t)b * a.ldo + (int64_t)h * HD + c) =
-        __floats2bfloat162_rn(o0 / total, o1 / total);
+    cp_async_wait<0>();
+    __syncthreads();
+    // this thread's shares of the row sums -> whole rows
+    st.l[0] += __shfl_xor_sync(0xffffffffu, st.l[0], 1); st.l[0] += __shfl_xor_sync(0xffffffffu, st.l[0], 2);
+    st.l[1] += __shfl_xor_sync(0xffffffffu, st.l[1], 1); st.l[1] += __shfl_xor_sync(0xffffffffu, st.l[1], 2);
+
+    float* so = smem + (size_t)warp * 16 * HD;
+    float* sm = smem + (size_t)NW * 16 * HD + warp * 16;
+    float* sl = sm + NW * 16;
+    stage_rows<HD>(so, st.o, g, t, g < G, g + 8 < G, 1.f, 1.f);
+    if (t == 0) { sm[g] = st.m[0]; sm[g + 8] = st.m[1]; sl[g] = st.l[0]; sl[g + 8] = st.l[1]; }
+    __syncthreads();
+
+    const int item = b * a.nkv + kvh;
+    const bool alone = n_parts == 1 && a.out != nullptr;
+    // merge the warps in fixed order, two columns of a head per thread
+    const float* am = smem + (size_t)NW * 16 * HD;
+    const float* al = am + NW * 16;
+    float* mine = a.part + (size_t)(blockIdx.x + item) * G * (HD + 2);
+    for (int idx = threadIdx.x; idx < G * (HD / 2); idx += NW * 32) {
+      const int r = idx / (HD / 2), c = 2 * (idx % (HD / 2));
+      float M = -INFINITY;
+      for (int w = 0; w < NW; ++w) M = fmaxf(M, am[w * 16 + r]);
+      const float ref = M == -INFINITY ? 0.f : M;
+      float acc0 = 0.f, acc1 = 0.f, L = 0.f;
+      for (int w = 0; w < NW; ++w) {
+        const float f = exp2f(am[w * 16 + r] - ref);
+        const float2 o = *reinterpret_cast<const float2*>(smem + (size_t)w * 16 * HD + staged_index<HD>(r, c));
+        acc0 += f * o.x;
+        acc1 += f * o.y;
+        L += f * al[w * 16 + r];
+      }
+      if (alone) {  // the whole item: its heads' rows are final
+        *reinterpret_cast<__nv_bfloat162*>(a.out + (int64_t)b * a.ldo + (int64_t)(kvh * G + r) * HD + c) =
+            __floats2bfloat162_rn(acc0 / L, acc1 / L);
+      } else {      // one partial per (slot, head): m, l, acc[HD]
+        float* out = mine + (size_t)r * (HD + 2);
+        *reinterpret_cast<float2*>(out + 2 + c) = make_float2(acc0, acc1);
+        if (c == 0) { out[0] = M; out[1] = L; }
+      }
+    }
+    if (a.out == nullptr) {
+      if (page0 == 0 && threadIdx.x == 0) { a.meta[2 * item] = j_first + item; a.meta[2 * item + 1] = n_parts; }
+    } else if (!alone) {
+      // who finishes last of this item merges its parts, in the order of the parts
+      __threadfence();
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        int* counter = &a.counters[item];
+        const int before = atomicAdd(counter, 1);
+        merges = before == n_parts - 1;
+        if (merges) *counter = 0;  // all are in: ready for the next launch
+      }
+      __syncthreads();
+      if (merges) {
+        __threadfence();
+        // Every partial is a round trip to the L2, so a thread asks for all of its own at once: two
+        // columns of one head, eight parts at a time, folded into the running (maximum, sum, row) in
+        // the order of the parts.
+        const float* base = a.part + (size_t)(j_first + item) * G * (HD + 2);
+        const size_t stride = (size_t)G * (HD + 2);
+        for (int idx = threadIdx.x; idx < G * (HD / 2); idx += NW * 32) {
+          const int r = idx / (HD / 2), c = 2 * (idx % (HD / 2)), h = kvh * G + r;
+          const float* p = base + (size_t)r * (HD + 2);
+          float M = -INFINITY, total = 0.f, o0 = 0.f, o1 = 0.f;
+          for (int s0 = 0; s0 < n_parts; s0 += 8) {
+            float m8[8], l8[8];
+            float2 o8[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const bool in = s0 + j < n_parts;
+              const float* ps = p + (size_t)(s0 + j) * stride;
+              const float2 ml = in ? __ldcg(reinterpret_cast<const float2*>(ps)) : make_float2(-INFINITY, 0.f);
+              m8[j] = ml.x;
+              l8[j] = ml.y;
+              o8[j] = in ? __ldcg(reinterpret_cast<const float2*>(ps + 2 + c)) : make_float2(0.f, 0.f);
+            }
+            float Mn = M;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) Mn = fmaxf(Mn, m8[j]);
+            if (Mn == -INFINITY) continue;
+            const float keep = exp2f(M - Mn);  // 0 for the first chunk (M is -inf)
+            total *= keep;
+            o0 *= keep;
+            o1 *= keep;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const float f = exp2f(m8[j] - Mn);
+              total += f * l8[j];
+              o0 += f * o8[j].x;
+              o1 += f * o8[j].y;
+            }
+            M = Mn;
+          }
+          *reinterpret_cast<__nv_bfloat162*>(a.out + (int64_t)b * a.ldo + (int64_t)h * HD + c) =
+              __floats2bfloat162_rn(o0 / total, o1 / total);
+        }
+      }
+    }
+    // the next part of this block: the next head of the sequence, or the next sequence's first
+    left -= n_pages;
+    page0 = 0;
+    if (++kvh == a.nkv) { kvh = 0; ++b; }
+    if (left > 0) {
+      pos = a.tok_pos[b];
+      const int2 info = reinterpret_cast<const int2*>(a.items)[b * a.nkv + kvh];
+      j_first = info.x;
+      n_parts = info.y;
+    }
+    __syncthreads();  // the staged rows are read; the stages are free for the next part's pages
   }
 }
 
-struct MergeArgs { const float* part; bf16* out; int64_t ldo; int nq, n_splits, hd; };
+struct MergeArgs { const float* part; const int32_t* meta; bf16* out; int64_t ldo; int nq, nkv, hd; };
 
 __global__ void __launch_bounds__(128) attn_merge_kernel(MergeArgs a) {
   allow_dependents();
   grid_dependency_wait();
-  const int h = blockIdx.x, b = blockIdx.y;
-  const float* p = a.part + ((size_t)b * a.nq + h) * a.n_splits * (a.hd + 2);
+  const int h = blockIdx.x, b = blockIdx.y, G = a.nq / a.nkv, item = b * a.nkv + h / G;
+  const int n_parts = a.meta[2 * item + 1];
+  const size_t stride = (size_t)G * (a.hd + 2);
+  const float* p = a.part + ((size_t)a.meta[2 * item] * G + h % G) * (a.hd + 2);
   float M = -INFINITY;
-  for (int s = 0; s < a.n_splits; ++s) M = fmaxf(M, p[(size_t)s * (a.hd + 2)]);
+  for (int s = 0; s < n_parts; ++s) M = fmaxf(M, p[s * stride]);
   float total = 0.f;
-  for (int s = 0; s < a.n_splits; ++s) total += exp2f(p[(size_t)s * (a.hd + 2)] - M) * p[(size_t)s * (a.hd + 2) + 1];
+  for (int s = 0; s < n_parts; ++s) total += exp2f(p[s * stride] - M) * p[s * stride + 1];
   for (int c = threadIdx.x; c < a.hd; c += blockDim.x) {
     float o = 0.f;
-    for (int s = 0; s < a.n_splits; ++s) o += exp2f(p[(size_t)s * (a.hd + 2)] - M) * p[(size_t)s * (a.hd + 2) + 2 + c];
+    for (int s = 0; s < n_parts; ++s) o += exp2f(p[s * stride] - M) * p[s * stride + 2 + c];
     a.out[(int64_t)b * a.ldo + (int64_t)h * a.hd + c] = __float2bfloat16_rn(o / total);
+  }
+}
+
+// The plan of a decode step (see kPlanInts) from the positions of its new tokens: all pages laid end to
+// end, T in all, and block j gets the run [j * per, (j+1) * per), per = ceil(T / blocks).  One block.
+struct PlanArgs { const int32_t* tok_pos; int n_seqs, nkv, window, n_blocks; int32_t* plan; };
+
+__global__ void __launch_bounds__(256) attn_decode_plan_kernel(PlanArgs a) {
+  __shared__ long long warp_sum_s[8];
+  __shared__ long long carry_s;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  int32_t* table = a.plan + (size_t)a.n_blocks * kPlanInts;
+  auto pages_of = [&](int b) -> long long {
+    if (b >= a.n_seqs) return 0;
+    const int pos = a.tok_pos[b];
+    const int first = a.window > 0 ? max(0, pos - a.window + 1) : 0;
+    return pos / kPage + 1 - first / kPage;
+  };
+  // all pages
+  long long mine = 0;
+  for (int b = tid; b < a.n_seqs; b += 256) mine += pages_of(b);
+  for (int o = 16; o > 0; o >>= 1) mine += __shfl_xor_sync(0xffffffffu, mine, o);
+  if (lane == 0) warp_sum_s[warp] = mine;
+  __syncthreads();
+  long long total = 0;
+  for (int w = 0; w < 8; ++w) total += warp_sum_s[w];
+  total *= a.nkv;
+  const long long per = max(1LL, (total + a.n_blocks - 1) / a.n_blocks);
+  if (tid == 0) carry_s = 0;
+  __syncthreads();
+  // every sequence writes its items' lines of the table and the rows of the blocks that start inside it
+  for (int base = 0; base < a.n_seqs; base += 256) {
+    const int b = base + tid;
+    const long long n = pages_of(b);
+    long long incl = n;
+    for (int o = 1; o < 32; o <<= 1) {
+      const long long v = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += v;
+    }
+    __syncthreads();  // warp_sum_s and carry_s of the round before are read
+    if (lane == 31) warp_sum_s[warp] = incl;
+    __syncthreads();
+    long long before = carry_s;
+    for (int w = 0; w < warp; ++w) before += warp_sum_s[w];
+    const long long lo = (before + incl - n) * a.nkv, hi = lo + n * a.nkv;
+    if (b < a.n_seqs && n > 0) {
+      const int pos = a.tok_pos[b];
+      for (int h = 0; h < a.nkv; ++h) {
+        const long long item_lo = lo + h * n, jf = item_lo / per;
+        table[2 * (b * a.nkv + h)] = (int)jf;
+        table[2 * (b * a.nkv + h) + 1] = (int)((item_lo + n - 1) / per - jf + 1);
+      }
+      for (long long j = (lo + per - 1) / per; j * per < hi && j < a.n_blocks; ++j) {
+        const long long r = j * per - lo, h = r / n, item_lo = lo + h * n, jf = item_lo / per;
+        int32_t* row = a.plan + j * kPlanInts;
+        row[0] = b; row[1] = (int)h; row[2] = (int)(r % n); row[3] = (int)min(per, total - j * per);
+        row[4] = pos; row[5] = (int)jf; row[6] = (int)((item_lo + n - 1) / per - jf + 1); row[7] = 0;
+      }
+    }
+    __syncthreads();
+    if (tid == 255) carry_s = before + incl;
+  }
+  __syncthreads();
+  for (long long j = (total + per - 1) / per + tid; j < a.n_blocks; j += 256) {  // blocks that get nothing
+    int32_t* row = a.plan + j * kPlanInts;
+    for (int i = 0; i < kPlanInts; ++i) row[i] = 0;
   }
 }
 
@@ -675,8 +795,7 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(PrefillArgs a) {
 }
 
 template <int HD>
-int launch_decode(const DecodeArgs& a_in, int n_seqs, cudaStream_t stream) {
-  const DecodeArgs& a = a_in;
+int launch_decode(const DecodeArgs& a, int n_blocks, cudaStream_t stream) {
   size_t smem = (size_t)(kDecodeWarps * 16 * HD + 2 * kDecodeWarps * 16) * sizeof(float);
   if (smem < (size_t)Stage<HD>::kDecodeStages * Stage<HD>::kPageBytes) smem = (size_t)Stage<HD>::kDecodeStages * Stage<HD>::kPageBytes;
   // after the stages: up to 18 finished heads (bf16) and a float scratch row per warp
@@ -687,7 +806,7 @@ int launch_decode(const DecodeArgs& a_in, int n_seqs, cudaStream_t stream) {
     if (e != cudaSuccess) return fail(kLaunchFailed, "attention_decode: shared memory: %s", cudaGetErrorString(e));
   }
   configured = true;
-  launch_overlapped(attn_decode_kernel<HD>, dim3(a.nkv, n_seqs, a.n_splits), dim3(kDecodeWarps * 32), smem, stream, a);
+  launch_overlapped(attn_decode_kernel<HD>, dim3(n_blocks), dim3(kDecodeWarps * 32), smem, stream, a);
   return check_launch("attention_decode");
 }
 template <int HD>
@@ -731,64 +850,91 @@ extern "C" int skyla_attention_mma_supports(int hd, int group) {
   return (hd % 16 == 0 && hd >= 16 && hd <= 128) ? (group <= 16 ? 2 : 1) : 0;
 }
 
-// Decode: token b of the step is the one new token of sequence b.  `part` holds
-// n_seqs * nq * n_splits * (hd + 2) floats of scratch; out is [n_seqs, nq*hd] bf16.
+// Floats of scratch that a decode launch of `n_blocks` blocks needs: a partial result per part and head
+// (slots 0 .. blocks + items - 1), and two ints per item for the merge kernel.
+extern "C" int64_t skyla_attention_decode_scratch_floats(int n_seqs, int nq, int nkv, int hd, int n_blocks) {
+  if (n_seqs <= 0 || nkv <= 0) return 0;
+  const int64_t items = (int64_t)n_seqs * nkv;
+  return (n_blocks + items) * (nq / nkv) * (hd + 2) + 2 * items;
+}
+
+// The plan of a decode step, made on the device from the positions of its new tokens (a host that knows
+// the positions can write a plan itself): [n_blocks][8] ints of rows, then [n_seqs * nkv][2] ints of items.
+extern "C" int skyla_attention_decode_plan(const int32_t* tok_pos, int n_seqs, int nkv, int window, int n_blocks,
+                                           int32_t* plan, cudaStream_t stream) {
+  if (n_seqs <= 0 || n_blocks <= 0 || nkv <= 0) return fail(kBadArgument, "attention_decode_plan: bad sizes");
+  PlanArgs a{tok_pos, n_seqs, nkv, window, n_blocks, plan};
+  attn_decode_plan_kernel<<<1, 256, 0, stream>>>(a);
+  return check_launch("attention_decode_plan");
+}
+
+namespace {
+int run_decode(DecodeArgs& a, void* out, int64_t ldo, float* part, int64_t part_floats, int n_seqs, int hd, int max_pages,
+               int n_blocks, int* counters, int n_counters, cudaStream_t stream) {
+  if (a.nq / a.nkv > 16) return fail(kBadArgument, "attention_decode: groups of %d query heads exceed 16", a.nq / a.nkv);
+  if (n_blocks < 1 || a.plan == nullptr) return fail(kBadArgument, "attention_decode: no plan");
+  const int64_t items = (int64_t)n_seqs * a.nkv;
+  if (items * max_pages >= (1LL << 31)) return fail(kBadArgument, "attention_decode: too many pages to number");
+  const int64_t need = skyla_attention_decode_scratch_floats(n_seqs, a.nq, a.nkv, hd, n_blocks);
+  if (part == nullptr || part_floats < need)
+    return fail(kBadArgument, "attention_decode: %lld floats of scratch needed, %lld given", (long long)need, (long long)part_floats);
+  a.part = part;
+  a.items = a.plan + (size_t)n_blocks * kPlanInts;
+  a.meta = reinterpret_cast<int32_t*>(part + (need - 2 * items));
+  const bool merge_inside = counters != nullptr && items <= n_counters;
+  a.counters = counters;
+  if (merge_inside) { a.out = (bf16*)out; a.ldo = ldo; }
+  int rc = kOk;
+  SKYLA_HD_SWITCH(hd, { rc = launch_decode<HD>(a, n_blocks, stream); break; });
+  if (rc || merge_inside) return rc;
+  MergeArgs m{part, a.meta, (bf16*)out, ldo, a.nq, a.nkv, hd};
+  launch_overlapped(attn_merge_kernel, dim3(a.nq, n_seqs), dim3(128), 0, stream, m);
+  return check_launch("attention_merge");
+}
+}  // namespace
+
+// Decode: token b of the step is the one new token of sequence b.  `plan` deals the step's pages to
+// `n_blocks` blocks (skyla_attention_decode_plan); `part` holds `part_floats` floats of scratch
+// (skyla_attention_decode_scratch_floats); out is [n_seqs, nq*hd] bf16.
 // `counters`: n_counters zeroed ints that stay the caller's between launches (they are zero again
-// when a launch ends); with n_seqs * nkv of them the split that finishes last merges the splits
+// when a launch ends); with n_seqs * nkv of them the part that finishes last merges an item's parts
 // inside the kernel, with fewer (or none) a merge kernel follows.
-extern "C" int skyla_attention_decode(const void* q, int64_t ldq, void* out, int64_t ldo, float* part, int n_seqs,
-                                      int nq, int nkv, int hd, const void* k_pool, const void* v_pool,
+extern "C" int skyla_attention_decode(const void* q, int64_t ldq, void* out, int64_t ldo, float* part, int64_t part_floats,
+                                      int n_seqs, int nq, int nkv, int hd, const void* k_pool, const void* v_pool,
                                       const int32_t* pages, int max_pages, int page_size, const int32_t* tok_pos,
-                                      float scale, int window, int n_splits, int pages_per_split,
-                                      const int32_t* pages_needed, int* counters, int n_counters,
-                                      cudaStream_t stream) {
+                                      float scale, int window, const int32_t* plan, int n_blocks, int* counters,
+                                      int n_counters, cudaStream_t stream) {
   if (n_seqs <= 0) return kOk;
   int rc = check_common(q, ldq, nq, nkv, page_size, k_pool, v_pool);
   if (rc) return rc;
-  if (nq / nkv > 16) return fail(kBadArgument, "attention_decode: groups of %d query heads exceed 16", nq / nkv);
-  if (n_splits < 1 || pages_per_split < 1 || n_seqs > 65535 || n_splits > 65535)
-    return fail(kBadArgument, "attention_decode: bad split of the context");
-  DecodeArgs a{(const bf16*)q, ldq, part, n_splits, pages_per_split, nq, nkv,
+  DecodeArgs a{(const bf16*)q, ldq, nullptr, nq, nkv,
                PagedKV{(const bf16*)k_pool, (const bf16*)v_pool, pages, max_pages, page_size, nkv}, tok_pos, scale, window,
-               FusedPrep{}, pages_needed, nullptr, 0, counters};
-  const bool merge_inside = counters != nullptr && (int64_t)n_seqs * nkv <= n_counters;
-  if (merge_inside) { a.out = (bf16*)out; a.ldo = ldo; }
-  SKYLA_HD_SWITCH(hd, { rc = launch_decode<HD>(a, n_seqs, stream); break; });
-  if (rc || merge_inside) return rc;
-  MergeArgs m{part, (bf16*)out, ldo, nq, n_splits, hd};
-  launch_overlapped(attn_merge_kernel, dim3(nq, n_seqs), dim3(128), 0, stream, m);
-  return check_launch("attention_merge");
+               FusedPrep{}, plan, nullptr, nullptr, 0, nullptr, nullptr};
+  return run_decode(a, out, ldo, part, part_floats, n_seqs, hd, max_pages, n_blocks, counters, n_counters, stream);
 }
 
 // Decode with the new token's q, k and v finished inside the kernel: `qkv` are the rows [n_seqs][ld]
 // (float) of the QKV product.  k and v of the new token are written to the pools (which this call
-// therefore changes).
+// therefore changes).  The plan must be older than the kernel that runs before this one (the kernel
+// reads it while that one may still be running): written by the host, or by a kernel the stream has
+// been waited for.
 extern "C" int skyla_attention_decode_fused(
     const float* qkv, int64_t ld, int q_off, int k_off, int v_off, const float* q_norm, const float* k_norm,
-    float eps, const float* cos_t, const float* sin_t, int n_rot, void* out, int64_t ldo, float* part, int n_seqs,
-    int nq, int nkv, int hd, void* k_pool, void* v_pool, const int32_t* pages, int max_pages, int page_size,
-    const int32_t* tok_pos, float scale, int window, int n_splits, int pages_per_split,
-    const int32_t* pages_needed, int* counters, int n_counters, cudaStream_t stream) {
+    float eps, const float* cos_t, const float* sin_t, int n_rot, void* out, int64_t ldo, float* part, int64_t part_floats,
+    int n_seqs, int nq, int nkv, int hd, void* k_pool, void* v_pool, const int32_t* pages, int max_pages, int page_size,
+    const int32_t* tok_pos, float scale, int window, const int32_t* plan, int n_blocks, int* counters, int n_counters,
+    cudaStream_t stream) {
   if (n_seqs <= 0) return kOk;
   int rc = check_common(k_pool, 8, nq, nkv, page_size, k_pool, v_pool);
   if (rc) return rc;
-  if (nq / nkv > 16) return fail(kBadArgument, "attention_decode: groups of %d query heads exceed 16", nq / nkv);
-  if (n_splits < 1 || pages_per_split < 1 || n_seqs > 65535 || n_splits > 65535)
-    return fail(kBadArgument, "attention_decode: bad split of the context");
   if (qkv == nullptr || n_rot < 0 || n_rot > hd || n_rot % 2)
     return fail(kBadArgument, "attention_decode_fused: bad description of the unfinished q, k and v");
-  DecodeArgs a{nullptr, 0, part, n_splits, pages_per_split, nq, nkv,
+  DecodeArgs a{nullptr, 0, nullptr, nq, nkv,
                PagedKV{(const bf16*)k_pool, (const bf16*)v_pool, pages, max_pages, page_size, nkv}, tok_pos, scale, window,
                FusedPrep{qkv, ld, q_off, k_off, v_off,
                          q_norm, k_norm, eps, cos_t, sin_t, cos_t ? n_rot : 0, (bf16*)k_pool, (bf16*)v_pool, n_seqs},
-               pages_needed, nullptr, 0, counters};
-  const bool merge_inside = counters != nullptr && (int64_t)n_seqs * nkv <= n_counters;
-  if (merge_inside) { a.out = (bf16*)out; a.ldo = ldo; }
-  SKYLA_HD_SWITCH(hd, { rc = launch_decode<HD>(a, n_seqs, stream); break; });
-  if (rc || merge_inside) return rc;
-  MergeArgs m{part, (bf16*)out, ldo, nq, n_splits, hd};
-  launch_overlapped(attn_merge_kernel, dim3(nq, n_seqs), dim3(128), 0, stream, m);
-  return check_launch("attention_merge");
+               plan, nullptr, nullptr, 0, nullptr, nullptr};
+  return run_decode(a, out, ldo, part, part_floats, n_seqs, hd, max_pages, n_blocks, counters, n_counters, stream);
 }
 
 // Prefill: tiles of up to 64 consecutive new tokens of one sequence.
@@ -819,14 +965,18 @@ static __device__ __align__(256) float g_no_alloc_scratch[SKYLA_NO_ALLOC_SCRATCH
 // shares nothing with an engine that runs on the same device.  They start at zero (the image is
 // zero-filled) and every launch leaves them at zero.
 static __device__ __align__(256) int g_no_alloc_counters[SKYLA_NO_ALLOC_COUNTERS];
+// And the plan of its launch: which pages each block reads.
+static __device__ __align__(256) int32_t g_no_alloc_plan[8 * SKYLA_NO_ALLOC_BLOCKS + 2 * SKYLA_NO_ALLOC_ITEMS];
 
 namespace {
 constexpr int kMaxDevices = 64;
 float* g_scratch_address[kMaxDevices] = {nullptr};
 int* g_counters_address[kMaxDevices] = {nullptr};
+int32_t* g_plan_address[kMaxDevices] = {nullptr};
 
-// Device addresses of g_no_alloc_scratch and g_no_alloc_counters on the current device, looked up on first use.
-int scratch_address(float** out, int** counters) {
+// Device addresses of g_no_alloc_scratch, g_no_alloc_counters and g_no_alloc_plan on the current device,
+// looked up on first use.
+int scratch_address(float** out, int** counters, int32_t** plan) {
   int dev = -1;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return fail(kLaunchFailed, "attention_decode_no_alloc: cudaGetDevice: %s", cudaGetErrorString(e));
@@ -840,11 +990,17 @@ int scratch_address(float** out, int** counters) {
     e = cudaGetSymbolAddress(&c, g_no_alloc_counters);
     if (e != cudaSuccess || c == nullptr)
       return fail(kLaunchFailed, "attention_decode_no_alloc: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+    void* pl = nullptr;
+    e = cudaGetSymbolAddress(&pl, g_no_alloc_plan);
+    if (e != cudaSuccess || pl == nullptr)
+      return fail(kLaunchFailed, "attention_decode_no_alloc: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+    g_plan_address[dev] = static_cast<int32_t*>(pl);
     g_counters_address[dev] = static_cast<int*>(c);
     g_scratch_address[dev] = static_cast<float*>(p);
   }
   *out = g_scratch_address[dev];
   *counters = g_counters_address[dev];
+  *plan = g_plan_address[dev];
   return kOk;
 }
 }  // namespace
@@ -852,22 +1008,30 @@ int scratch_address(float** out, int** counters) {
 extern "C" int skyla_attention_decode_no_alloc(const void* q, int64_t ldq, void* out, int64_t ldo, int n_seqs, int nq,
                                                int nkv, int hd, const void* k_pool, const void* v_pool,
                                                const int32_t* pages, int max_pages, int page_size,
-                                               const int32_t* tok_pos, float scale, int window, int n_splits,
-                                               int pages_per_split, cudaStream_t stream) {
+                                               const int32_t* tok_pos, float scale, int window, int n_blocks,
+                                               cudaStream_t stream) {
   if (n_seqs <= 0) return kOk;
-  if (nq <= 0 || hd <= 0 || n_splits <= 0) return fail(kBadArgument, "attention_decode_no_alloc: bad sizes");
-  const unsigned long long need = (unsigned long long)n_seqs * nq * n_splits * (hd + 2);
-  if (need > SKYLA_NO_ALLOC_SCRATCH_FLOATS)
+  if (nq <= 0 || hd <= 0 || nkv <= 0 || nq % nkv || n_blocks <= 0) return fail(kBadArgument, "attention_decode_no_alloc: bad sizes");
+  if (n_blocks > SKYLA_NO_ALLOC_BLOCKS)
+    return fail(kBadArgument, "attention_decode_no_alloc: %d blocks, the built-in plan holds %d", n_blocks, SKYLA_NO_ALLOC_BLOCKS);
+  if ((long long)n_seqs * nkv > SKYLA_NO_ALLOC_ITEMS)
+    return fail(kBadArgument, "attention_decode_no_alloc: %d sequences x %d key/value heads, the built-in plan holds %d such pairs",
+                n_seqs, nkv, SKYLA_NO_ALLOC_ITEMS);
+  const long long need = skyla_attention_decode_scratch_floats(n_seqs, nq, nkv, hd, n_blocks);
+  if (need > (long long)SKYLA_NO_ALLOC_SCRATCH_FLOATS)
     return fail(kBadArgument,
-                "attention_decode_no_alloc: %llu floats of scratch needed (%d sequences x %d heads x %d splits x %d), "
-                "the built-in array holds %u; use fewer splits or skyla_attention_decode with a buffer of your own",
-                need, n_seqs, nq, n_splits, hd + 2, (unsigned)SKYLA_NO_ALLOC_SCRATCH_FLOATS);
+                "attention_decode_no_alloc: %lld floats of scratch needed ((%d blocks + %d sequences x %d key/value heads) x "
+                "%d heads x %d), the built-in array holds %u; use fewer blocks or skyla_attention_decode with a buffer of "
+                "your own", need, n_blocks, n_seqs, nkv, nq / nkv, hd + 2, (unsigned)SKYLA_NO_ALLOC_SCRATCH_FLOATS);
   float* scratch = nullptr;
   int* counters = nullptr;
-  const int rc = scratch_address(&scratch, &counters);
+  int32_t* plan = nullptr;
+  int rc = scratch_address(&scratch, &counters, &plan);
   if (rc) return rc;
-  // more (sequence, kv head) pairs than counters: the splits are merged by a second kernel instead
-  return skyla_attention_decode(q, ldq, out, ldo, scratch, n_seqs, nq, nkv, hd, k_pool, v_pool, pages, max_pages,
-                                page_size, tok_pos, scale, window, n_splits, pages_per_split, nullptr, counters,
+  rc = skyla_attention_decode_plan(tok_pos, n_seqs, nkv, window, n_blocks, plan, stream);
+  if (rc) return rc;
+  // more (sequence, kv head) pairs than counters: the parts are merged by a second kernel instead
+  return skyla_attention_decode(q, ldq, out, ldo, scratch, SKYLA_NO_ALLOC_SCRATCH_FLOATS, n_seqs, nq, nkv, hd, k_pool,
+                                v_pool, pages, max_pages, page_size, tok_pos, scale, window, plan, n_blocks, counters,
                                 SKYLA_NO_ALLOC_COUNTERS, stream);
 }

@@ -16,6 +16,9 @@ pinned host buffer and sent with one copy per step:
                model asked for (``Part.token_tiles``): tiles of up to h consecutive new tokens of
                one sequence, the units a prompt attention kernel works in
   pages[G][B,P] for each cache group the page list of each sequence
+  plans[key]   what a part of the model asked to have worked out on the host from the step's
+               positions (``parts.base.StepPlan``), e.g. which pages each block of a decode
+               attention launch reads
 """
 from __future__ import annotations
 
@@ -83,7 +86,8 @@ class StepContext:
     cu: torch.Tensor
     want: torch.Tensor
     pages: List[torch.Tensor]
-    pages_needed: Optional[torch.Tensor] = None  # one int32: pages of the longest sequence after this step
+    #: key of a part's :class:`~skyla_kernel_b200.parts.base.StepPlan` -> its ints on the device
+    plans: Dict[object, torch.Tensor] = field(default_factory=dict)
     #: tile height -> (sequence row, first packed token, rows) of every tile, for the heights the
     #: model's mixers asked for
     tiles: Dict[int, Tuple[torch.Tensor, torch.Tensor, torch.Tensor]] = field(default_factory=dict)
@@ -142,9 +146,11 @@ class BatchBuilder:
             idx = torch.tensor(rows, dtype=torch.int64).to(self.rt.device, non_blocking=True)
             dev_tokens.copy_(src.index_select(0, idx))
 
-    def __init__(self, rt, cache, tile_heights: Sequence[int] = ()):
-        """``tile_heights``: the heights of token tiles that the model's mixers want listed every step."""
+    def __init__(self, rt, cache, tile_heights: Sequence[int] = (), plans: Sequence[object] = ()):
+        """``tile_heights``: the heights of token tiles that the model's mixers want listed every step;
+        ``plans``: the ``StepPlan`` objects of its parts."""
         self.rt = rt
+        self.plans = tuple(plans)
         self.cache = cache
         self.tile_heights = tuple(sorted(set(int(h) for h in tile_heights)))
         self.workspace = Workspace(rt.device)
@@ -175,7 +181,8 @@ class BatchBuilder:
                 raise ValueError(f"page lists need {P} columns, {pages_width} were given")
             P = pages_width
         n_tiles = {th: sum(-(-n // th) for n in ns) for th in self.tile_heights}
-        total = 3 * T + 3 * B + (B + 1) + R + 3 * sum(n_tiles.values()) + 1 + G * B * P
+        plan_sizes = [int(p.size(B, P, max(ns) == 1)) for p in self.plans]
+        total = 3 * T + 3 * B + (B + 1) + R + 3 * sum(n_tiles.values()) + G * B * P + sum(s + 3 for s in plan_sizes if s)
         if self._copied is not None:
             self._copied.synchronize()  # the last step's copy has left the pinned buffer
         host, dev = self._staging(total)
@@ -197,8 +204,6 @@ class BatchBuilder:
         cu, r_cu = take(B + 1)
         want, r_want = take(R)
         tiles = {th: [take(q) for _ in range(3)] for th, q in n_tiles.items()}
-        needed, r_needed = take(1)
-        needed[0] = max(1, max(-(-(s + n) // cache.page_size) for s, n in zip(starts, ns)))
         q = {th: 0 for th in tiles}
         t = 0
         w = 0
@@ -230,6 +235,13 @@ class BatchBuilder:
                 m = min(len(lst), P)
                 pg[b, :m] = np.maximum(np.asarray(lst[:m], dtype=np.int64), 0)
             r_pages.append(r)
+        r_plans = {}
+        for plan, size in zip(self.plans, plan_sizes):
+            if size:
+                o = -(-o // 4) * 4  # 16-byte aligned: kernels read plan rows as vectors
+                arr, r = take(size)
+                plan.fill(arr, np.asarray(starts), np.asarray(ns), cache.page_size)
+                r_plans[plan.key] = r
         dev[:total].copy_(host[:total], non_blocking=True)
         if self.rt.device.type == "cuda":
             self._copied = torch.cuda.Event()
@@ -246,6 +258,7 @@ class BatchBuilder:
             page_size=cache.page_size, tokens=view(r_tokens), tok_pos=view(r_pos),
             tok_seq=view(r_seq), seq_slot=view(r_slot), seq_start=view(r_start), seq_n=view(r_n),
             cu=view(r_cu), want=view(r_want), pages=[view(r).view(B, P) for r in r_pages],
-            pages_needed=view(r_needed), tiles={th: tuple(view(r) for _, r in three) for th, three in tiles.items()},
+            tiles={th: tuple(view(r) for _, r in three) for th, three in tiles.items()},
+            plans={k: view(r) for k, r in r_plans.items()},
             host={"starts": np.asarray(starts), "ns": np.asarray(ns)},
         )

@@ -60,7 +60,7 @@ class Engine:
         self.model.load(tensors)
         self.cache = SequenceCache(self.model.kv_needs, self.model.state_needs, max_tokens, max_slots,
                                    self.rt.cache_dtype, self.rt.device)
-        self.batcher = BatchBuilder(self.rt, self.cache, self.model.tile_heights())
+        self.batcher = BatchBuilder(self.rt, self.cache, self.model.tile_heights(), self.model.step_plans())
         self.vocab_size = self.spec.vocab_size
         if cuda_graphs is None:
             cuda_graphs = os.environ.get("SKYLA_CUDA_GRAPHS", "1") != "0"

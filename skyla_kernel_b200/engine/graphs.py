@@ -67,7 +67,8 @@ class DecodeGraphs:
 
     def _capture(self, items: List[StepItem], width: int) -> _Captured:
         from ..kernels import ops
-        batcher = BatchBuilder(self.rt, self.cache, self.model.tile_heights())  # arrays and workspace of this graph alone
+        # arrays and workspace of this graph alone
+        batcher = BatchBuilder(self.rt, self.cache, self.model.tile_heights(), self.model.step_plans())
         ctx = batcher.build(items, pages_width=width)
         ctx.max_position = width * self.cache.page_size - 1  # position tables must cover the bucket
         ctx.max_context = width * self.cache.page_size

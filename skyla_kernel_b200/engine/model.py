@@ -87,6 +87,15 @@ class DecoderModel:
                 hs.extend(getattr(p, "token_tiles", ()))
         return tuple(sorted(set(hs)))
 
+    def step_plans(self):
+        """The host-made plans that the parts want in every step's batch, one per key."""
+        plans = {}
+        for b in self.blocks:
+            for p in b.parts():
+                for plan in getattr(p, "step_plans", ()):
+                    plans.setdefault(plan.key, plan)
+        return tuple(plans.values())
+
     def kernels_needed(self):
         mods = list(self.embedding.kernels_needed())
         for b in self.blocks:

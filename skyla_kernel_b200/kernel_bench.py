@@ -117,13 +117,13 @@ def attention_decode(batch: int, context: int, nq: int = 32, nkv: int = 8, hd: i
     pos = torch.full((batch,), context - 1, dtype=torch.int32, device=DEV)
     part = GQAttention(PartSpec("gqa_attention", {"hidden_size": nq * hd, "num_heads": nq, "num_kv_heads": nkv,
                                                   "head_dim": hd}), Runtime(torch.device(DEV), "bfloat16"))
-    n_splits, per = part.decode_splits(batch, width)
-    needed = torch.tensor([-(-context // 64)], dtype=torch.int32, device=DEV)
-    scratch = torch.empty(batch * nq * n_splits * (hd + 2), device=DEV)
+    n_blocks = part.step_plans[0].blocks(batch, width)
+    plan = torch.from_numpy(ops.decode_plan([context - 1] * batch, nkv, 0, 64, n_blocks)).to(DEV)
+    scratch = torch.empty(ops.attention_decode_scratch(batch, nq, nkv, hd, n_blocks), device=DEV)
     us = _time(lambda i: ops.attention_decode(q, out, scratch, nq, nkv, hd, k, v, table, 64, pos, 1 / math.sqrt(hd), 0,
-                                              n_splits, per, needed), 8, reps)
+                                              n_blocks, plan), 8, reps)
     kv_bytes = 2 * batch * context * nkv * hd * 2
-    return {"kernel": "attention-decode", "batch": batch, "context": context, "us": us, "splits": n_splits,
+    return {"kernel": "attention-decode", "batch": batch, "context": context, "us": us, "blocks": n_blocks,
             "kv_GBps": kv_bytes / us / 1e3}
 
 

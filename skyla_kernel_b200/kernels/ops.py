@@ -678,30 +678,166 @@ def _attn_common(q, out, k_pool, v_pool, nq, nkv, hd, page_size, *ints):
         raise KernelError(f"cache pools {tuple(k_pool.shape)} do not match [pages, {nkv}, {page_size}, {hd}]")
 
 
+#: ints per row of a decode plan
+DECODE_PLAN_INTS = 8
+#: what starting another item costs a block, and what a block costs beside its pages, in pages' time
+#: (a page of 64 positions of one key/value head takes about a microsecond)
+_PIECE_COST, _BLOCK_COST = 3, 3
+_plan_memo: dict = {}
+
+
+def decode_plan_ints(n_seqs: int, nkv: int, n_blocks: int) -> int:
+    """Ints of a decode plan: a row per block, then (first block, pieces) per item."""
+    return DECODE_PLAN_INTS * n_blocks + 2 * n_seqs * nkv
+
+
+def _plan_layout(n_pages, nkv: int, n_blocks: int, even_only: bool):
+    """Rows (without the positions) and item table of :func:`decode_plan` for sequences of ``n_pages[b]`` pages."""
+    import numpy as np
+    B = len(n_pages)
+    items = B * nkv
+    rows = np.zeros((n_blocks, DECODE_PLAN_INTS), dtype=np.int32)
+    table = np.zeros((items, 2), dtype=np.int32)
+    total = int(n_pages.sum()) * nkv
+    per = max(1, -(-total // n_blocks))
+    # even runs: cost of the slowest block
+    ends = np.cumsum(n_pages) * nkv                       # where each sequence's items end
+    starts = ends - n_pages * nkv
+    u0 = np.arange(n_blocks, dtype=np.int64) * per
+    live = u0 < total
+    u0 = np.where(live, u0, 0)
+    u1 = np.minimum(u0 + per, total) - 1                  # a block's last page
+
+    def item_of(u):
+        b = np.minimum(np.searchsorted(ends, u, side="right"), B - 1)
+        r = u - starts[b]
+        return b, r // n_pages[b], r % n_pages[b]
+    b0, h0, p0 = item_of(u0)
+    b1, h1, _ = item_of(np.maximum(u1, u0))
+    pieces = (b1 * nkv + h1) - (b0 * nkv + h0) + 1
+    even_cost = _BLOCK_COST + per + _PIECE_COST * (int(pieces[live].max()) - 1)
+    # runs that end with their item: every item in k equal pieces, as few pages a piece as the blocks allow
+    m = n_blocks // nkv
+    if m >= B and not even_only:
+        size = max(1, -(-int(n_pages.sum()) // m))
+        while int((-(-n_pages // size)).sum()) > m:
+            size += 1
+        k = -(-n_pages // size)
+        if _BLOCK_COST + int((-(-n_pages // k)).max()) <= even_cost:
+            first_block = (np.cumsum(k) - k) * nkv       # of each sequence's first item
+            # piece c of an item of n pages and k pieces starts at page c * n // k
+            seq = np.repeat(np.arange(B), k * nkv)
+            head = np.concatenate([np.repeat(np.arange(nkv), kb) for kb in k])
+            piece = np.concatenate([np.tile(np.arange(kb), nkv) for kb in k])
+            n_of, k_of = n_pages[seq], k[seq]
+            lo = piece * n_of // k_of
+            used = len(seq)
+            rows[:used, 0], rows[:used, 1], rows[:used, 2] = seq, head, lo
+            rows[:used, 3] = (piece + 1) * n_of // k_of - lo
+            rows[:used, 5] = first_block[seq] + head * k_of
+            rows[:used, 6] = k_of
+            item_seq = np.repeat(np.arange(B), nkv)
+            table[:, 0] = first_block[item_seq] + np.tile(np.arange(nkv), B) * k[item_seq]
+            table[:, 1] = k[item_seq]
+            return rows, table
+    rows[:, 0], rows[:, 1], rows[:, 2] = np.where(live, b0, 0), np.where(live, h0, 0), np.where(live, p0, 0)
+    rows[:, 3] = np.where(live, u1 - u0 + 1, 0)
+    item_seq = np.repeat(np.arange(B), nkv)
+    lo = starts[item_seq] + np.tile(np.arange(nkv), B) * n_pages[item_seq]
+    table[:, 0] = lo // per
+    table[:, 1] = (lo + n_pages[item_seq] - 1) // per - lo // per + 1
+    first_item = b0 * nkv + h0
+    rows[:, 5] = np.where(live, table[first_item, 0], 0)
+    rows[:, 6] = np.where(live, table[first_item, 1], 0)
+    return rows, table
+
+
+def decode_plan(positions, nkv: int, window: int, page_size: int, n_blocks: int, out=None, even_only: bool = False):
+    """Which pages each block of a decode launch reads, made on the host: int32, :func:`decode_plan_ints` long.
+
+    ``positions[b]`` is the position of sequence b's new token.  The items of the step are its
+    (sequence, key/value head) pairs, item = sequence * nkv + head, each with the pages from the
+    window's first to the new token's.  Blocks take runs of consecutive pages of consecutive items:
+    row j = (sequence, head, page of that item where the run starts, pages of the run, position of that
+    sequence's new token, first block and number of pieces of that item, 0).  After the rows, for every
+    item, (first block, pieces): the blocks that read pieces of one item are consecutive.
+    Two ways of cutting, whichever makes the slowest block faster: every item in equal pieces, so that no
+    block has to start a second item (few long sequences); or all pages laid end to end and cut into
+    even runs, whatever the lengths are (more items than blocks, unequal lengths).
+    ``attn_decode_plan_kernel`` writes a plan of the second kind (``even_only``) from positions that only
+    the device has.
+    """
+    import numpy as np
+    pos = np.asarray(positions, dtype=np.int64)
+    first = np.maximum(pos - window + 1, 0) if window and window > 0 else np.zeros_like(pos)
+    n_pages = pos // page_size + 1 - first // page_size
+    key = (nkv, n_blocks, even_only, n_pages.tobytes())
+    got = _plan_memo.get(key)
+    if got is None:                                       # the cuts change only when a sequence gains a page
+        if len(_plan_memo) > 256:
+            _plan_memo.clear()
+        got = _plan_memo[key] = _plan_layout(n_pages, nkv, n_blocks, even_only)
+    rows, table = got
+    if out is None:
+        out = np.empty(decode_plan_ints(len(pos), nkv, n_blocks), dtype=np.int32)
+    out_rows = out[: rows.size].reshape(rows.shape)
+    out_rows[:] = rows
+    out_rows[:, 4] = np.where(rows[:, 3] > 0, pos[rows[:, 0]], 0)
+    out[rows.size:] = table.reshape(-1)
+    return out
+
+
+def attention_decode_plan(tok_pos: torch.Tensor, nkv: int, window: int, n_blocks: int,
+                          plan: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """:func:`decode_plan` by a kernel, from positions on the device (pages of 64 positions)."""
+    _cuda(tok_pos, plan); _i32(tok_pos, "tok_pos")
+    need = decode_plan_ints(tok_pos.numel(), nkv, n_blocks)
+    if plan is None:
+        plan = torch.empty(need, dtype=torch.int32, device=tok_pos.device)
+    _i32(plan, "plan")
+    if plan.numel() < need:
+        raise KernelError("attention_decode_plan: plan too small")
+    f = _fn("attention_mma", "skyla_attention_decode_plan", [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
+    _check("attention_mma", f(_ptr(tok_pos), tok_pos.numel(), nkv, int(window or 0), n_blocks, _ptr(plan), _stream()))
+    return plan
+
+
+def attention_decode_scratch(n_seqs: int, nq: int, nkv: int, hd: int, n_blocks: int) -> int:
+    """Floats of scratch that a decode launch needs: a partial result for every piece of an item that a
+    block reads, and two ints per item for the merge kernel."""
+    return (n_blocks + n_seqs * nkv) * (nq // nkv) * (hd + 2) + 2 * n_seqs * nkv
+
+
+def _decode_plan_arg(plan, n_seqs, nkv, n_blocks, what):
+    _cuda(plan); _i32(plan, "plan")
+    if plan.numel() < decode_plan_ints(n_seqs, nkv, n_blocks) or plan.data_ptr() % 16:
+        raise KernelError(f"{what}: a plan of {n_blocks} rows of {DECODE_PLAN_INTS} ints and two ints per item, 16-byte aligned")
+
+
 def attention_decode(q: torch.Tensor, out: torch.Tensor, scratch: torch.Tensor, nq: int, nkv: int, hd: int,
                      k_pool: torch.Tensor, v_pool: torch.Tensor, pages: torch.Tensor, page_size: int,
-                     tok_pos: torch.Tensor, scale: float, window: int, n_splits: int,
-                     pages_per_split: int, pages_needed: Optional[torch.Tensor] = None,
-                     state: Optional[KernelState] = None) -> torch.Tensor:
-    """One new token per sequence (token b belongs to sequence b): split-context attention
-    over the cache for all query heads of a key/value head at once, then the merge.
+                     tok_pos: torch.Tensor, scale: float, window: int, n_blocks: int,
+                     plan: Optional[torch.Tensor] = None, state: Optional[KernelState] = None) -> torch.Tensor:
+    """One new token per sequence (token b belongs to sequence b): attention over the cache for all
+    query heads of a key/value head at once, the step's pages dealt evenly to ``n_blocks`` blocks.
 
-    ``scratch``: float32, at least ``n_seqs * nq * n_splits * (hd + 2)`` elements.
-    ``pages_needed`` (one int32 on the device): the pages the longest sequence needs; the splits
-    then share those evenly and ``pages_per_split`` is ignored.
+    ``scratch``: float32, at least :func:`attention_decode_scratch` elements.
+    ``plan``: :func:`decode_plan` on the device (default: made here by :func:`attention_decode_plan`).
     """
     _attn_common(q, out, k_pool, v_pool, nq, nkv, hd, page_size, pages, tok_pos)
-    _cuda(pages_needed); _i32(pages_needed, "pages_needed")
     n = tok_pos.numel()
-    if scratch.dtype != torch.float32 or scratch.numel() < n * nq * n_splits * (hd + 2):
+    if plan is None:
+        plan = attention_decode_plan(tok_pos, nkv, window, n_blocks)
+    _decode_plan_arg(plan, n, nkv, n_blocks, "attention_decode")
+    if scratch.dtype != torch.float32 or scratch.numel() < attention_decode_scratch(n, nq, nkv, hd, n_blocks):
         raise KernelError("attention_decode: scratch too small")
     f = _fn("attention_mma", "skyla_attention_decode",
-            [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
-             c_void_p, c_int, c_int, c_void_p, c_float, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p])
+            [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
+             c_void_p, c_int, c_int, c_void_p, c_float, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p])
     counters = _state(state, q).merge_counters()
-    _check("attention_mma", f(_ptr(q), _rows(q, "q"), _ptr(out), _rows(out, "out"), _ptr(scratch), n, nq, nkv, hd,
-                              _ptr(k_pool), _ptr(v_pool), _ptr(pages), pages.shape[1], page_size, _ptr(tok_pos),
-                              float(scale), int(window or 0), n_splits, pages_per_split, _ptr(pages_needed),
+    _check("attention_mma", f(_ptr(q), _rows(q, "q"), _ptr(out), _rows(out, "out"), _ptr(scratch), scratch.numel(),
+                              n, nq, nkv, hd, _ptr(k_pool), _ptr(v_pool), _ptr(pages), pages.shape[1], page_size,
+                              _ptr(tok_pos), float(scale), int(window or 0), _ptr(plan), n_blocks,
                               _ptr(counters), counters.numel(), _stream()))
     if tok_pos.numel() * nkv > counters.numel():
         global LAUNCHES
@@ -714,15 +850,18 @@ def attention_decode_fused(qkv: torch.Tensor, q_off: int, k_off: int, v_off: int
                            sin: Optional[torch.Tensor], n_rot: int, out: torch.Tensor, scratch: torch.Tensor,
                            nq: int, nkv: int, hd: int, k_pool: torch.Tensor, v_pool: torch.Tensor,
                            pages: torch.Tensor, page_size: int, tok_pos: torch.Tensor, scale: float, window: int,
-                           n_splits: int, pages_per_split: int,
-                           pages_needed: Optional[torch.Tensor] = None,
-                           state: Optional[KernelState] = None) -> torch.Tensor:
+                           n_blocks: int, plan: torch.Tensor, state: Optional[KernelState] = None) -> torch.Tensor:
     """Decode attention that also finishes the new token's q, k and v (what
     ``qk_norm_rope_cache`` does) from the float32 rows ``qkv`` [tokens, width] of the q/k/v
-    product, and writes k and v to the cache."""
-    _cuda(qkv, q_norm, k_norm, cos, sin, out, scratch, k_pool, v_pool, pages, tok_pos, pages_needed)
-    _i32(pages, "pages"); _i32(tok_pos, "tok_pos"); _i32(pages_needed, "pages_needed")
+    product, and writes k and v to the cache.
+
+    The kernel reads ``plan`` while the kernel launched before it may still run, so the plan must
+    be older than that one: copied from the host (:func:`decode_plan`), or written by
+    :func:`attention_decode_plan` and waited for."""
+    _cuda(qkv, q_norm, k_norm, cos, sin, out, scratch, k_pool, v_pool, pages, tok_pos)
+    _i32(pages, "pages"); _i32(tok_pos, "tok_pos")
     n = tok_pos.numel()
+    _decode_plan_arg(plan, n, nkv, n_blocks, "attention_decode_fused")
     if qkv.dtype != torch.float32 or qkv.dim() != 2 or qkv.shape[0] != n or qkv.stride(1) != 1:
         raise KernelError("attention_decode_fused: the q/k/v rows are float32 [tokens, width]")
     if out.dtype != torch.bfloat16 or k_pool.dtype != torch.bfloat16 or tuple(k_pool.shape[1:]) != (nkv, page_size, hd) \
@@ -731,18 +870,19 @@ def attention_decode_fused(qkv: torch.Tensor, q_off: int, k_off: int, v_off: int
     for t_, what in ((q_norm, "q_norm"), (k_norm, "k_norm"), (cos, "cos"), (sin, "sin")):
         if t_ is not None and (t_.dtype != torch.float32 or not t_.is_contiguous()):
             raise KernelError(f"{what}: expected a contiguous float32 tensor")
-    if scratch.dtype != torch.float32 or scratch.numel() < n * nq * n_splits * (hd + 2):
+    if scratch.dtype != torch.float32 or scratch.numel() < attention_decode_scratch(n, nq, nkv, hd, n_blocks):
         raise KernelError("attention_decode_fused: scratch too small")
     f = _fn("attention_mma", "skyla_attention_decode_fused",
             [c_void_p, c_int64, c_int, c_int, c_int, c_void_p, c_void_p,
-             c_float, c_void_p, c_void_p, c_int, c_void_p, c_int64, c_void_p, c_int, c_int, c_int, c_int, c_void_p,
-             c_void_p, c_void_p, c_int, c_int, c_void_p, c_float, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p])
+             c_float, c_void_p, c_void_p, c_int, c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_void_p,
+             c_void_p, c_void_p, c_int, c_int, c_void_p, c_float, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p])
     counters = _state(state, out).merge_counters()
     _check("attention_mma", f(_ptr(qkv), _rows(qkv, "qkv"), q_off, k_off, v_off,
                               _ptr(q_norm), _ptr(k_norm), float(eps), _ptr(cos), _ptr(sin), n_rot if cos is not None else 0,
-                              _ptr(out), _rows(out, "out"), _ptr(scratch), n, nq, nkv, hd, _ptr(k_pool), _ptr(v_pool),
-                              _ptr(pages), pages.shape[1], page_size, _ptr(tok_pos), float(scale), int(window or 0),
-                              n_splits, pages_per_split, _ptr(pages_needed), _ptr(counters), counters.numel(), _stream()))
+                              _ptr(out), _rows(out, "out"), _ptr(scratch), scratch.numel(), n, nq, nkv, hd,
+                              _ptr(k_pool), _ptr(v_pool), _ptr(pages), pages.shape[1], page_size, _ptr(tok_pos),
+                              float(scale), int(window or 0), _ptr(plan), n_blocks, _ptr(counters), counters.numel(),
+                              _stream()))
     if tok_pos.numel() * nkv > counters.numel():
         global LAUNCHES
         LAUNCHES += 1  # the merge kernel, which otherwise is part of the attention kernel

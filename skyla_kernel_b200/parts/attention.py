@@ -28,8 +28,46 @@ import torch
 from ..cache.kv import KVNeed
 from ..kernels import ops
 from ..weights.loader import TensorDecl
-from .base import NormedInput, Part, build_part, register_mixer
+from .base import NormedInput, Part, StepPlan, build_part, register_mixer
 from .linear import ACCUMULATE, STORE, Linear
+
+
+class DecodePages(StepPlan):
+    """Which pages each block of a decode attention launch reads (``ops.decode_plan``): the same for
+    every layer with these key/value heads and this window, so it is made once a step, on the host."""
+
+    def __init__(self, nkv: int, window: int, n_sms: int):
+        self.nkv, self.window, self.n_sms = nkv, window, n_sms
+        self.key = ("decode pages", nkv, window)
+        self._blocks = {}
+
+    def blocks(self, n_seqs: int, pages_width: int) -> int:
+        """How many blocks share a decode step's pages.
+
+        Two blocks share an SM, and all of them run at once.  A block costs about three pages' time
+        beside its pages (a page takes about 1 us), each further item that it starts about as much
+        again, and every piece that an item is read in about 0.3 more in the merge (fitted to
+        measurements at batch 1 to 64).  The count is fixed per (batch, width of the page lists), so
+        that a recorded launch keeps its grid; which pages a block reads follows the step's lengths.
+        """
+        got = self._blocks.get((n_seqs, pages_width))
+        if got is None:
+            items = max(1, self.nkv * n_seqs)
+            total = items * max(1.0, 0.75 * pages_width)
+            best_cost = None
+            for n in range(1, 2 * self.n_sms + 1):
+                cost = 3.0 + -(-total // n) + 0.3 * (n / items + 1) + 2.5 * max(0.0, items / n - 1)
+                if best_cost is None or cost < best_cost:
+                    got, best_cost = n, cost
+            self._blocks[(n_seqs, pages_width)] = got
+        return got
+
+    def size(self, n_seqs: int, pages_width: int, decode: bool) -> int:
+        return ops.decode_plan_ints(n_seqs, self.nkv, self.blocks(n_seqs, pages_width)) if decode else 0
+
+    def fill(self, out, starts, ns, page_size: int) -> None:
+        n_blocks = (out.size - 2 * len(starts) * self.nkv) // ops.DECODE_PLAN_INTS
+        ops.decode_plan(starts, self.nkv, self.window, page_size, n_blocks, out)
 
 
 class GQAttention(Part):
@@ -65,6 +103,9 @@ class GQAttention(Part):
         #: the prompt attention kernels work on tiles of consecutive new tokens of one sequence; the step's
         #: batch builder makes the tile lists that the model's mixers ask for here
         self.token_tiles = (ops.PREFILL_TILE,) if self._fast else ()
+        #: and, for steps of one token per sequence, which pages each block of the decode kernel reads
+        self._pages_plan = DecodePages(self.nkv, self.window, rt.sm_count) if self._fast == 2 else None
+        self.step_plans = (self._pages_plan,) if self._pages_plan is not None else ()
         self.qkv: Optional[Linear] = None
         self.q_only: Optional[Linear] = None
         self.out: Optional[Linear] = None
@@ -108,24 +149,17 @@ class GQAttention(Part):
         return self.kernel_modules
 
     # -------------------------------------------------------------------- cache
-    def decode_splits(self, n_seqs: int, max_pages: int):
-        """Into how many blocks a decode step cuts each sequence's context: (splits, pages per split).
-
-        Two blocks share an SM; a block costs about three pages' time beside its
-        pages, and every split about 0.3 more in the merge (fitted to measurements at batch 1 to
-        64: a page takes about 1 us, a block's start and end 3.5, a split 0.3).  The count is fixed
-        per (batch, page-list width) so that a recorded launch keeps its grid; how many pages a
-        split covers follows the step's longest sequence, which the kernel reads from device memory.
-        """
-        items = max(1, self.nkv * n_seqs)
-        resident = 2 * self.rt.sm_count
-        typical = max(1.0, 0.75 * max_pages)
-        best, best_cost = 1, None
-        for n in range(1, max(1, min(32, max_pages // 2)) + 1):
-            cost = -(-items * n // resident) * (3.0 + typical / n) + 0.3 * n
-            if best_cost is None or cost < best_cost:
-                best, best_cost = n, cost
-        return best, -(-max_pages // best)
+    def _decode_plan(self, ctx, pages):
+        """(plan, blocks, from the host): the step's plan if its builder made one, else one made here by
+        a kernel (which the kernel that finishes q, k and v itself must not be given: it reads the plan
+        before it waits for the kernels ahead of it)."""
+        plan = ctx.plans.get(self._pages_plan.key) if getattr(ctx, "plans", None) else None
+        if plan is not None:
+            return plan, (plan.numel() - 2 * ctx.n_seqs * self.nkv) // ops.DECODE_PLAN_INTS, True
+        n_blocks = self._pages_plan.blocks(ctx.n_seqs, pages.shape[1])
+        plan = ctx.buffer("attn.decode_plan", (ops.decode_plan_ints(ctx.n_seqs, self.nkv, n_blocks),), torch.int32)
+        ops.attention_decode_plan(ctx.tok_pos, self.nkv, self.window, n_blocks, plan)
+        return plan, n_blocks, False
 
     def cache_need(self) -> Optional[KVNeed]:
         return KVNeed(self.nkv, self.hd, self.window or None, self.cache_dtype)
@@ -161,16 +195,18 @@ class GQAttention(Part):
             ctx.mark("matvec qkv")
             # (up to 16 sequences; with more, every block's repeating the preparation costs more than the
             # kernel it saves: 7,560 against 7,800 to 7,980 tokens/s at batch 64)
+            plan = None
             if (self._fast == 2 and ctx.is_decode and n <= self.qkv.STACKED_MAX_TOKENS
                     and k_pool.dtype == torch.bfloat16 and self.rt.act_dtype == torch.bfloat16):
+                plan, n_blocks, from_host = self._decode_plan(ctx, pages)
+            if plan is not None and from_host:
                 # one new token per sequence: its q, k and v are finished inside the attention kernel
                 attn = ctx.buffer("attn.out", (n, nq * hd), self.rt.act_dtype)
-                n_splits, per = self.decode_splits(ctx.n_seqs, pages.shape[1])
-                scratch = ctx.buffer("attn.partials", (n * nq * n_splits * (hd + 2),), torch.float32)
+                scratch = ctx.buffer("attn.partials", (ops.attention_decode_scratch(n, nq, nkv, hd, n_blocks),), torch.float32)
                 ops.attention_decode_fused(whole, 0, nq * hd, (nq + nkv) * hd,
                                            self.q_norm_w, self.k_norm_w, self.eps, cos, sin, n_rot, attn, scratch,
                                            nq, nkv, hd, k_pool, v_pool, pages, ctx.page_size, ctx.tok_pos,
-                                           self.scale, self.window, n_splits, per, ctx.pages_needed, state=state)
+                                           self.scale, self.window, n_blocks, plan, state=state)
                 ctx.mark("attention")
                 self.out.forward(attn, x, ACCUMULATE, ctx=ctx)
                 ctx.mark("matvec o")
@@ -207,10 +243,10 @@ class GQAttention(Part):
         q = qkv[:, : nq * hd]
         fast = self._fast if k_pool.dtype == torch.bfloat16 and q.dtype == torch.bfloat16 else 0
         if fast == 2 and ctx.is_decode:
-            n_splits, per = self.decode_splits(ctx.n_seqs, pages.shape[1])
-            scratch = ctx.buffer("attn.partials", (n * nq * n_splits * (hd + 2),), torch.float32)
+            plan, n_blocks, _ = self._decode_plan(ctx, pages)
+            scratch = ctx.buffer("attn.partials", (ops.attention_decode_scratch(n, nq, nkv, hd, n_blocks),), torch.float32)
             ops.attention_decode(q, attn, scratch, nq, nkv, hd, k_pool, v_pool, pages, ctx.page_size,
-                                 ctx.tok_pos, self.scale, self.window, n_splits, per, ctx.pages_needed, state=state)
+                                 ctx.tok_pos, self.scale, self.window, n_blocks, plan, state=state)
         elif fast:
             tile_seq, tile_tok0, tile_rows = ctx.tiles[ops.PREFILL_TILE]
             ops.attention_prefill(q, attn, nq, nkv, hd, k_pool, v_pool, pages, ctx.page_size, ctx.tok_pos,

@@ -139,6 +139,8 @@ class Part:
     #: True if forward() only launches kernels on the current stream and never reads
     #: device memory on the host, so that a step may be captured in a CUDA graph
     graph_safe = False
+    #: :class:`StepPlan` objects: what the part wants worked out on the host once a step
+    step_plans = ()
 
     def __init__(self, spec: PartSpec, rt: Runtime):
         self.spec = spec
@@ -160,6 +162,27 @@ class Part:
 
     def weight_bytes(self) -> int:
         return 0
+
+
+class StepPlan:
+    """Integers that a part wants worked out on the host once a step, from the positions of the step's
+    sequences, and sent to the device with the step's other arrays (one copy): work lists and the like
+    that are the same for every layer with the same need.  A part lists its plans in ``step_plans``;
+    plans with equal ``key`` are one plan, which the parts find as ``ctx.plans[key]`` (int32, on the
+    device, 16-byte aligned; absent where the step's builder was not given the plan).
+    """
+
+    key = None
+
+    def size(self, n_seqs: int, pages_width: int, decode: bool) -> int:
+        """Ints the plan takes for a step of ``n_seqs`` sequences whose page lists have ``pages_width``
+        columns (0: none for such a step); ``decode``: every sequence brings one token.  The size may
+        depend on nothing else, so that a recorded step keeps its layout."""
+        return 0
+
+    def fill(self, out, starts, ns, page_size: int) -> None:
+        """Write the plan into ``out`` (int32 NumPy, ``size`` ints) for sequences that hold ``starts[b]``
+        positions and bring ``ns[b]`` new tokens."""
 
 
 class NormedInput:

@@ -1,5 +1,6 @@
 """The step's packed arrays, built on the host (no GPU): tokens, positions, wanted rows, token tiles
-of the heights the mixers asked for, page lists of a fixed width."""
+of the heights the mixers asked for, page lists of a fixed width, and the plans that parts asked for."""
+import numpy as np
 import torch
 
 from skyla_kernel_b200.cache import KVNeed, SequenceCache
@@ -26,7 +27,7 @@ def test_packed_arrays_of_an_unequal_batch():
     assert (seq, tok0, rows) == ([0, 0, 0, 1, 2], [0, 64, 128, 130, 131], [64, 64, 2, 1, 3])
     seq, tok0, rows = (t.tolist() for t in ctx.tiles[16])
     assert seq == [0] * 9 + [1, 2] and tok0[:9] == list(range(0, 130, 16)) and rows[8:] == [2, 1, 3]
-    assert int(ctx.pages_needed) == 3 and all(p.shape == (3, 3) for p in ctx.pages)
+    assert all(p.shape == (3, 3) for p in ctx.pages)
     for g in range(2):
         for row, slot in enumerate((a, b, c)):
             held = cache.pages_of(g, slot)
@@ -39,3 +40,91 @@ def test_packed_arrays_of_an_unequal_batch():
     assert [t.tolist() for t in d.tiles[64]] == [[0, 1, 2], [0, 1, 2], [1, 1, 1]]
     # no mixer asked for tiles: none are made
     assert BatchBuilder(rt, cache).build([StepItem(a, [9], [0])]).tiles == {}
+
+
+def _walk(plan, positions, nkv, window, n_blocks, page_size=64):
+    """Follow a decode plan the way the kernel does: {(sequence, head): [(block, first page, pages)]}."""
+    first = [max(0, p - window + 1) if window else 0 for p in positions]
+    n_pages = [p // page_size + 1 - f // page_size for p, f in zip(positions, first)]
+    rows, table = plan[: 8 * n_blocks].reshape(n_blocks, 8), plan[8 * n_blocks:].reshape(-1, 2)
+    pieces = {}
+    for j, (b, kvh, page0, left, pos, j_first, n_parts, _) in enumerate(rows.tolist()):
+        if left:  # what the row says of the item it starts in is what the table says
+            assert pos == positions[b] and [j_first, n_parts] == table[b * nkv + kvh].tolist()
+        while left > 0:
+            n = min(left, n_pages[b] - page0)
+            assert n > 0
+            pieces.setdefault((b, kvh), []).append((j, page0, n))
+            left -= n
+            page0 = 0
+            kvh += 1
+            if kvh == nkv:
+                kvh, b = 0, b + 1
+    return pieces, n_pages, rows, table
+
+
+def test_decode_plan_deals_every_page_once_and_evenly():
+    from skyla_kernel_b200.kernels import ops
+    rng = np.random.default_rng(3)
+    for nkv, window, n_seqs, n_blocks in ((8, 0, 64, 296), (2, 0, 5, 7), (1, 130, 9, 40), (3, 0, 1, 50), (4, 70, 16, 3),
+                                          (8, 0, 16, 296), (2, 0, 3, 1), (8, 0, 8, 296)):
+        positions = rng.integers(0, 3000, n_seqs).tolist()
+        for even_only in (False, True):
+            plan = ops.decode_plan(positions, nkv, window, 64, n_blocks, even_only=even_only)
+            assert plan.shape == (ops.decode_plan_ints(n_seqs, nkv, n_blocks),) and plan.dtype == np.int32
+            pieces, n_pages, rows, table = _walk(plan, positions, nkv, window, n_blocks)
+            total = nkv * sum(n_pages)
+            assert rows[:, 3].sum() == total
+            assert sorted(pieces) == [(b, h) for b in range(n_seqs) for h in range(nkv)]
+            for (b, h), got in pieces.items():
+                # an item's pieces follow one another, page after page, in consecutive blocks, as the table says
+                assert [p[1] for p in got] == [0] + list(np.cumsum([p[2] for p in got])[:-1])
+                assert sum(p[2] for p in got) == n_pages[b]
+                assert [p[0] for p in got] == list(range(got[0][0], got[0][0] + len(got)))
+                assert table[b * nkv + h].tolist() == [got[0][0], len(got)]
+            # slot = block + item is a piece's own
+            slots = [j + b * nkv + h for (b, h), got in pieces.items() for j, _, _ in got]
+            assert len(set(slots)) == len(slots) and max(slots) < n_blocks + n_seqs * nkv
+            if even_only:  # nobody reads more than an even share
+                assert rows[:, 3].max() <= -(-total // n_blocks)
+            else:          # never slower than even runs, by the planner's own measure
+                even = _walk(ops.decode_plan(positions, nkv, window, 64, n_blocks, even_only=True), positions, nkv,
+                             window, n_blocks)[0]
+                def cost(pc):
+                    per_block = {}
+                    for got in pc.values():
+                        for j, _, n in got:
+                            per_block[j] = per_block.get(j, 0) + n + 3
+                    return max(per_block.values())
+                assert cost(pieces) <= cost(even)
+    # eight equal sequences and room for all: every item in equal pieces, no block starts a second item
+    plan = ops.decode_plan([2100] * 8, 8, 0, 64, 296)
+    pieces, _, rows, _ = _walk(plan, [2100] * 8, 8, 0, 296)
+    assert all(len(got) == 4 and [n for _, _, n in got] == [8, 8, 8, 9] for got in pieces.values())
+    assert (rows[:, 3] > 0).sum() == 256
+    # sixty-four: more items than blocks, so the pages are cut evenly and a block reads into the next item
+    plan = ops.decode_plan([2100] * 64, 8, 0, 64, 296)
+    pieces, _, rows, _ = _walk(plan, [2100] * 64, 8, 0, 296)
+    assert rows[:, 3].max() == -(-64 * 8 * 33 // 296) and max(len(got) for got in pieces.values()) == 2
+
+
+def test_a_parts_plan_travels_with_the_step():
+    from skyla_kernel_b200.parts.attention import DecodePages
+    rt = Runtime(torch.device("cpu"), "float32", n_sms=4)
+    cache = SequenceCache([KVNeed(2, 16)], [None], 64 * 12, 4, torch.float32, None)
+    a, b = cache.alloc_slot(), cache.alloc_slot()
+    cache.reserve([(a, 200), (b, 70)]); cache.advance([(a, 200), (b, 70)])
+    plan = DecodePages(nkv=2, window=0, n_sms=4)
+    builder = BatchBuilder(rt, cache, plans=(plan,))
+    cache.reserve([(a, 1), (b, 1)])
+    ctx = builder.build([StepItem(a, [5], [0]), StepItem(b, [6], [0])], pages_width=8)
+    got = ctx.plans[plan.key]
+    n_blocks = plan.blocks(2, 8)
+    from skyla_kernel_b200.kernels import ops
+    assert 1 <= n_blocks <= 8 and got.numel() == ops.decode_plan_ints(2, 2, n_blocks) and got.data_ptr() % 16 == 0
+    assert np.array_equal(got.numpy(), ops.decode_plan([200, 70], 2, 0, 64, n_blocks))
+    assert ctx.pages[0].shape == (2, 8) and ctx.tok_pos.tolist() == [200, 70]   # the arrays beside it are whole
+    # a step that is no decode step has no such plan
+    cache.advance([(a, 1), (b, 1)])
+    cache.reserve([(a, 3)])
+    assert builder.build([StepItem(a, [1, 2, 3], [])]).plans == {}

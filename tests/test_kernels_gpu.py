@@ -357,13 +357,24 @@ def test_attention_decode_mma(nq, nkv, hd, window):
     plain_out = torch.empty(B, nq * hd, dtype=dt, device=DEV)
     ops.attention_plain(q, plain_out, nq, nkv, hd, k_pool, v_pool, table, 64, tok_pos,
                         torch.arange(B, dtype=torch.int32, device=DEV), scale, window)
-    for n_splits, per in ((1, 16), (4, 4), (16, 1), (3, 6)):
+    # the pages of all (sequence, head) pairs dealt to one block, to a few (a block then reads several pairs),
+    # to about as many as there are pairs, and to more than there are pages (a page each, the rest idle)
+    for n_blocks in (1, 3, B * nkv, 29, 64 * nkv):
         out = torch.full((B, nq * hd), float("nan"), dtype=dt, device=DEV)
-        scratch = torch.full((B * nq * n_splits * (hd + 2),), float("nan"), dtype=torch.float32, device=DEV)
-        ops.attention_decode(q, out, scratch, nq, nkv, hd, k_pool, v_pool, table, 64, tok_pos, scale, window,
-                             n_splits, per)
+        scratch = torch.full((ops.attention_decode_scratch(B, nq, nkv, hd, n_blocks),), float("nan"),
+                             dtype=torch.float32, device=DEV)
+        ops.attention_decode(q, out, scratch, nq, nkv, hd, k_pool, v_pool, table, 64, tok_pos, scale, window, n_blocks)
         torch.testing.assert_close(out.float().cpu().view(B, nq, hd), ref, rtol=2e-2, atol=2e-2)
         torch.testing.assert_close(out.float(), plain_out.float(), rtol=2e-2, atol=2e-2)
+        # the kernel's plan is the host's plan of even runs
+        host = ops.decode_plan([l - 1 for l in lens], nkv, window, 64, n_blocks, even_only=True)
+        assert np.array_equal(ops.attention_decode_plan(tok_pos, nkv, window, n_blocks).cpu().numpy(), host)
+        # and with the plan the host likes best (items in equal pieces where the blocks allow) the same comes out
+        out2 = torch.full_like(out, float("nan"))
+        best = torch.from_numpy(ops.decode_plan([l - 1 for l in lens], nkv, window, 64, n_blocks)).to(DEV)
+        ops.attention_decode(q, out2, scratch, nq, nkv, hd, k_pool, v_pool, table, 64, tok_pos, scale, window, n_blocks, best)
+        torch.testing.assert_close(out2.float(), plain_out.float(), rtol=2e-2, atol=2e-2)
+        ops.check_device_errors(DEV)
 
 
 @pytest.mark.parametrize("nq,nkv,hd", [(4, 2, 16), (6, 1, 32), (3, 3, 48), (8, 2, 64), (2, 1, 112), (8, 2, 128)])
@@ -480,8 +491,8 @@ def test_attention_mma_finds_one_far_key():
         for mode in ("decode", "prefill"):
             out = torch.empty(1, nq * hd, dtype=dt, device=DEV)
             if mode == "decode":
-                scratch = torch.empty(nq * 5 * (hd + 2), dtype=torch.float32, device=DEV)
-                ops.attention_decode(q, out, scratch, nq, nkv, hd, kp, v_pool, table, 64, i32([L - 1]), 1.0, 0, 5, 5)
+                scratch = torch.empty(ops.attention_decode_scratch(1, nq, nkv, hd, 10), dtype=torch.float32, device=DEV)
+                ops.attention_decode(q, out, scratch, nq, nkv, hd, kp, v_pool, table, 64, i32([L - 1]), 1.0, 0, 10)
             else:
                 ops.attention_prefill(q, out, nq, nkv, hd, kp, v_pool, table, 64, i32([L - 1]), i32([0]), i32([0]),
                                       i32([1]), 1.0, 0)
@@ -660,20 +671,21 @@ def test_attention_decode_fused_prep(nq, nkv, hd, n_rot, window):
     tok_pos = torch.tensor([l - 1 for l in lens], dtype=torch.int32, device=DEV)
     seq = torch.arange(B, dtype=torch.int32, device=DEV)
     scale = 1.0 / math.sqrt(hd)
-    n_splits, per = 3, 2
+    n_blocks = 3 * nkv + 1
+    plan = torch.from_numpy(ops.decode_plan([l - 1 for l in lens], nkv, window, 64, n_blocks)).to(DEV)
     # two kernels
     kp1, vp1 = k_pool.clone(), v_pool.clone()
     q = torch.empty(B, nq * hd, dtype=dt, device=DEV)
     ops.qk_norm_rope_cache(rows, 0, nq * hd, (nq + nkv) * hd, nq, nkv, hd, qn, kn, 1e-6, cos, sin, n_rot, tok_pos, seq,
                            kp1, vp1, table, 64, q_out=q)
     want = torch.empty(B, nq * hd, dtype=dt, device=DEV)
-    scratch = torch.empty(B * nq * n_splits * (hd + 2), dtype=torch.float32, device=DEV)
-    ops.attention_decode(q, want, scratch, nq, nkv, hd, kp1, vp1, table, 64, tok_pos, scale, window, n_splits, per)
+    scratch = torch.empty(ops.attention_decode_scratch(B, nq, nkv, hd, n_blocks), dtype=torch.float32, device=DEV)
+    ops.attention_decode(q, want, scratch, nq, nkv, hd, kp1, vp1, table, 64, tok_pos, scale, window, n_blocks, plan)
     # one kernel
     kp2, vp2 = k_pool.clone(), v_pool.clone()
     got = torch.full_like(want, float("nan"))
     ops.attention_decode_fused(rows, 0, nq * hd, (nq + nkv) * hd, qn, kn, 1e-6, cos, sin, n_rot, got,
-                               scratch, nq, nkv, hd, kp2, vp2, table, 64, tok_pos, scale, window, n_splits, per)
+                               scratch, nq, nkv, hd, kp2, vp2, table, 64, tok_pos, scale, window, n_blocks, plan)
     torch.testing.assert_close(got.float(), want.float(), rtol=2e-2, atol=2e-2)
     assert torch.equal(kp2, kp1) and torch.equal(vp2, vp1)  # the same k and v reached the cache
     assert not torch.equal(kp2, k_pool)

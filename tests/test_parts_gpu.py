@@ -24,11 +24,12 @@ def _tensors(decl, seed, std=0.08, sharp=1.0):
     return out
 
 
-def _ctx(rt, needs, states, items, max_tokens=1024, tiles=(64,)):
+def _ctx(rt, needs, states, items, max_tokens=1024, tiles=(64,), plans=()):
     from skyla_kernel_b200.cache import SequenceCache
     from skyla_kernel_b200.engine.batch import BatchBuilder
     cache = SequenceCache(needs, states, max_tokens, None, rt.cache_dtype, rt.device)
-    return cache, BatchBuilder(rt, cache, tiles)   # the token tiles that a mixer asks for (Part.token_tiles)
+    # the token tiles and the host-made plans that a mixer asks for (Part.token_tiles, Part.step_plans)
+    return cache, BatchBuilder(rt, cache, tiles, plans)
 
 
 def _tol(dtype):
@@ -96,7 +97,7 @@ def test_attention_part_whole_then_one_by_one(dtype, hidden, nq, nkv, hd, n_rot,
     ref = plain.attention(h_all, w["a.q_proj"], w["a.k_proj"], w["a.v_proj"], w["a.o_proj"],
                           w["a.q_norm"] if qk_norm else None, w["a.k_norm"] if qk_norm else None,
                           nq, nkv, hd, 1e-5, freqs, m, n_rot, scale=scale, window=window)
-    cache, batcher = _ctx(rt, [part.cache_need()], [None], None)
+    cache, batcher = _ctx(rt, [part.cache_need()], [None], None, plans=part.step_plans)
     assert cache.groups[0].k.dtype == (torch.float32 if cache_dtype == "float32" else rt.cache_dtype)
     slot = cache.alloc_slot()
     got = []
@@ -264,7 +265,7 @@ def test_block_alone(dtype):
     ref = x0 + plain.attention(plain.rmsnorm(x0, wf["l.n1"], 2e-5), wf["a.q_proj"], wf["a.k_proj"], wf["a.v_proj"],
                                wf["a.o_proj"], wf["a.q_norm"], wf["a.k_norm"], nq, nkv, hd, 1e-5, freqs, m, hd)
     ref = ref + plain.swiglu(plain.rmsnorm(ref, wf["l.n2"], 2e-5), wf["l.gate_proj"], wf["l.up_proj"], wf["l.down_proj"])
-    cache, batcher = _ctx(rt, [block.cache_need()], [None], None)
+    cache, batcher = _ctx(rt, [block.cache_need()], [None], None, plans=block.mixer.step_plans)
     slot = cache.alloc_slot()
     got = []
     for a, b in ((0, 70), (70, 71), (71, 90)):  # a prompt, one token (the few-token kernels), a second chunk
@@ -296,7 +297,7 @@ def test_wide_groups_decode_through_the_prompt_kernel():
     freqs, m = plain.rope_frequencies(hd, 10000.0)
     ref = plain.attention(plain.bf16_round(h_all), wf["a.q_proj"], wf["a.k_proj"], wf["a.v_proj"], wf["a.o_proj"],
                           wf["a.q_norm"], wf["a.k_norm"], nq, nkv, hd, 1e-5, freqs, m, hd)
-    cache, batcher = _ctx(rt, [part.cache_need()], [None], None)
+    cache, batcher = _ctx(rt, [part.cache_need()], [None], None, plans=part.step_plans)
     slot = cache.alloc_slot()
     got = []
     for a, b in [(0, 66)] + [(i, i + 1) for i in range(66, T)]:
