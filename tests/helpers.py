@@ -105,11 +105,16 @@ def random_tokens(n: int, vocab: int, seed: int):
 #     scales -- attention weights relative to a running maximum -- so every stored
 #     value draws its rounding anew and the two differ by as much as either differs
 #     from the 32-bit run.)
-TOL = {"float32": 1e-4, "bfloat16": 1.5e-1}
-TOL_MEAN = {"float32": 2e-5, "bfloat16": 1e-2}
+#   "bfloat16 flat": the same comparison on models made with sharp=1.0 (unit q/k norm weights: flatter
+#     attention, less rounding noise).  There the rounded plain run differs from the 32-bit one by up to
+#     1.14e-2 (worst) and 1.91e-3 (mean) over the four configurations, and the engine by 1.06e-2 and
+#     1.90e-3: the limits are about twice that, six times tighter than for the sharp models.
+TOL = {"float32": 1e-4, "bfloat16": 1.5e-1, "bfloat16 flat": 2.5e-2}
+TOL_MEAN = {"float32": 2e-5, "bfloat16": 1e-2, "bfloat16 flat": 4e-3}
 
 
 def assert_close(got: torch.Tensor, ref: torch.Tensor, dtype: str, what: str = ""):
+    """``dtype`` names the limits: "float32", "bfloat16" or "bfloat16 flat"."""
     got, ref = got.detach().cpu().to(torch.float64), ref.detach().cpu().to(torch.float64)
     assert got.shape == ref.shape, f"{what}: shape {tuple(got.shape)} vs {tuple(ref.shape)}"
     assert torch.isfinite(got).all(), f"{what}: non-finite logits"
