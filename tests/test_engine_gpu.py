@@ -128,6 +128,44 @@ def test_a_batch_of_twenty_decodes(folders, name, dtype):
     eng.cache.check()
 
 
+def test_more_sequences_than_attention_blocks(folders):
+    """With more (sequence, key/value head) pairs than the decode attention has blocks, the step's pages are cut
+    into even runs and a block reads the end of one pair and the beginning of the next: 120 sequences of
+    unequal lengths (three key/value heads each) decode together, some of them across a page's end."""
+    from skyla_kernel_b200.engine import StepItem
+    from skyla_kernel_b200.kernels import ops
+    name, dtype = "C", "bfloat16"
+    V = TINY[name][0]["vocab_size"]
+    eng = _engine(folders[name], dtype, max_tokens=120 * 192)
+    lens = [2 + (37 * i) % 150 for i in range(120)]
+    lens[5], lens[77] = 63, 127                       # their second new token opens a page
+    seqs = [random_tokens(p + 3, V, 700 + i) for i, p in enumerate(lens)]
+    slots = [eng.alloc_slot() for _ in seqs]
+    got = [[] for _ in seqs]
+    for i in range(0, 120, 30):                       # the prompts, thirty a step
+        out = eng.step([StepItem(slots[j], seqs[j][:lens[j]], [lens[j] - 1]) for j in range(i, i + 30)])
+        for k, j in enumerate(range(i, i + 30)):
+            got[j].append(out[k:k + 1])
+    for t in range(3):
+        out = eng.step([StepItem(slots[j], [seqs[j][lens[j] + t]], [0]) for j in range(120)])
+        for j in range(120):
+            got[j].append(out[j:j + 1])
+    # what the attention part asked for: fewer blocks than pairs, so even runs
+    plan = eng.model.step_plans()[0]
+    n_blocks = plan.blocks(120, 8)
+    assert n_blocks < 120 * plan.nkv
+    rows = ops.decode_plan([p + 2 for p in lens], plan.nkv, plan.window, 64, n_blocks)[: 8 * n_blocks].reshape(-1, 8)
+    assert rows[:, 3].max() <= -(-sum(-(-(p + 3) // 64) for p in lens) * plan.nkv // n_blocks)
+    cfg, w = plain.read_folder(folders[name])
+    for j in range(0, 120, 7):
+        ref = plain.forward(cfg, w, seqs[j])[lens[j] - 1:]
+        assert_close(torch.cat(got[j]), ref, dtype, f"request {j} of 120")
+    for sl in slots:
+        eng.free_slot(sl)
+    eng.cache.check()
+    eng.check_errors()
+
+
 def test_the_wide_configuration_reaches_the_blackwell_kernels(folders):
     """Configuration D is there for the kernels that small sizes never reach: a prompt of 150 tokens
     must go through the token-major product (with its tiles cut along K) and the tcgen05 attention."""
