@@ -716,8 +716,9 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(PrefillArgs a) {
   allow_dependents();
   grid_dependency_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
-  // a sequence's later tiles see more keys: they go first, so that the short ones fill the end
-  const int tile = (int)gridDim.x - 1 - (int)blockIdx.x, h = blockIdx.y, kvh = h / (a.nq / a.nkv);
+  // a sequence's later tiles see more keys: they go first, so that the short ones fill the end; blocks
+  // start in the order of their numbers, so the heads are the fast index: all heads of the longest tile first
+  const int tile = (int)(gridDim.x / a.nq) - 1 - (int)(blockIdx.x / a.nq), h = (int)(blockIdx.x % a.nq), kvh = h / (a.nq / a.nkv);
   const int b = a.tile_seq[tile], tok0 = a.tile_tok0[tile], rows = a.tile_rows[tile];
   // the tile's rows are consecutive positions of one sequence
   const int pos_first = a.tok_pos[tok0], pos_last = pos_first + rows - 1;
@@ -819,7 +820,7 @@ int launch_prefill(const PrefillArgs& a, int n_tiles, cudaStream_t stream) {
     if (e != cudaSuccess) return fail(kLaunchFailed, "attention_prefill: shared memory: %s", cudaGetErrorString(e));
   }
   configured = true;
-  launch_overlapped(attn_prefill_kernel<HD>, dim3(n_tiles, a.nq), dim3(128), smem, stream, a);
+  launch_overlapped(attn_prefill_kernel<HD>, dim3(n_tiles * a.nq), dim3(128), smem, stream, a);
   return check_launch("attention_prefill");
 }
 
@@ -946,7 +947,7 @@ extern "C" int skyla_attention_prefill(const void* q, int64_t ldq, void* out, in
   if (n_tiles <= 0) return kOk;
   int rc = check_common(q, ldq, nq, nkv, page_size, k_pool, v_pool);
   if (rc) return rc;
-  if (nq > 65535) return fail(kBadArgument, "attention_prefill: too many heads");
+  if ((int64_t)n_tiles * nq >= (1LL << 31)) return fail(kBadArgument, "attention_prefill: too many tiles");
   PrefillArgs a{(const bf16*)q, ldq, (bf16*)out, ldo, nq, nkv,
                 PagedKV{(const bf16*)k_pool, (const bf16*)v_pool, pages, max_pages, page_size, nkv},
                 tok_pos, tile_seq, tile_tok0, tile_rows, scale, window};

@@ -86,8 +86,13 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   auto t_empty = [&](int s) { return bars + 56 + 8u * (kSlots + s); };
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-  // a sequence's later tiles see more keys: they go first, so that the short ones fill the end
-  const int tile = (int)gridDim.x - 1 - (int)blockIdx.x, h0 = 2 * blockIdx.y, kvh = h0 / (a.nq / a.nkv);
+  // A sequence's later tiles see more keys: they go first, so that the short ones fill the end.  Blocks
+  // start in the order of their numbers, so the head pairs are the fast index: all pairs of the longest
+  // tile, then all of the next (with the tiles as the fast index every pair's longest tile but the first
+  // few started late, and the launch ended with long blocks running alone).
+  const int n_pairs = a.nq / 2;
+  const int tile = (int)(gridDim.x / n_pairs) - 1 - (int)(blockIdx.x / n_pairs), h0 = 2 * (int)(blockIdx.x % n_pairs);
+  const int kvh = h0 / (a.nq / a.nkv);
   const int b = a.tile_seq[tile], tok0 = a.tile_tok0[tile], rows = a.tile_rows[tile];
   const int pos_first = a.tok_pos[tok0], pos_last = pos_first + rows - 1;
   const int tile_lo = a.window > 0 ? max(0, pos_first - a.window + 1) : 0;
@@ -330,7 +335,7 @@ extern "C" int skyla_attention_prefill_tc(const void* map_q, const void* map_k, 
     return fail(kBadArgument, "attention_prefill_tc: heads of 128, pages of 64 and an even group of query heads only");
   if (map_q == nullptr || map_k == nullptr || map_v == nullptr || out == nullptr || ldo % 8 || ((uintptr_t)out) % 16)
     return fail(kBadArgument, "attention_prefill_tc: missing tensor maps or an output that is not 16-byte aligned");
-  if (nq / 2 > 65535) return fail(kBadArgument, "attention_prefill_tc: too many heads");
+  if ((int64_t)n_tiles * (nq / 2) >= (1LL << 31)) return fail(kBadArgument, "attention_prefill_tc: too many tiles");
   alignas(64) CUtensorMap mq, mk, mv;
   memcpy(&mq, map_q, sizeof(mq));
   memcpy(&mk, map_k, sizeof(mk));
@@ -342,6 +347,6 @@ extern "C" int skyla_attention_prefill_tc(const void* map_q, const void* map_k, 
     configured = true;
   }
   PrefillTcArgs a{(bf16*)out, ldo, nq, nkv, pages, max_pages, tok_pos, tile_seq, tile_tok0, tile_rows, scale, window, error_flag};
-  launch_overlapped(attn_prefill_tc_kernel, dim3(n_tiles, nq / 2), dim3(kThreads), (size_t)kSmemBytes, stream, mq, mk, mv, a);
+  launch_overlapped(attn_prefill_tc_kernel, dim3(n_tiles * (nq / 2)), dim3(kThreads), (size_t)kSmemBytes, stream, mq, mk, mv, a);
   return check_launch("attention_prefill_tc");
 }
