@@ -14,7 +14,8 @@ pinned host buffer and sent with one copy per step:
   want[R]      rows (packed token indices) whose logits are asked for
   tiles[h] = (tile_seq, tile_tok0, tile_rows)[Q]  for every tile height h that a mixer of the
                model asked for (``Part.token_tiles``): tiles of up to h consecutive new tokens of
-               one sequence, the units a prompt attention kernel works in
+               one sequence, the units a prompt attention kernel works in, in ascending order of
+               the last position they see
   pages[G][B,P] for each cache group the page list of each sequence
   plans[key]   what a part of the model asked to have worked out on the host from the step's
                positions (``parts.base.StepPlan``), e.g. which pages each block of a decode
@@ -225,6 +226,13 @@ class BatchBuilder:
                     q[th] += 1
             t += n
             cu[b + 1] = t
+        # The prompt attention kernels start the tiles from the list's end: the tiles that see the most keys go
+        # last in the list, so that the longest blocks start first whichever sequences they belong to.
+        for th, ((tile_seq, _), (tile_tok0, _), (tile_rows, _)) in tiles.items():
+            if len(tile_seq) > 1:
+                ends = np.asarray(starts)[tile_seq] + (tile_tok0 - cu[tile_seq]) + tile_rows
+                order = np.argsort(ends, kind="stable")
+                tile_seq[:], tile_tok0[:], tile_rows[:] = tile_seq[order], tile_tok0[order], tile_rows[order]
         r_pages = []
         for g in range(G):
             pg, r = take(B * P)

@@ -24,9 +24,11 @@ def test_packed_arrays_of_an_unequal_batch():
     assert ctx.seq_slot.tolist() == [a, b, c] and ctx.seq_start.tolist() == [0, 70, 0] and ctx.seq_n.tolist() == [130, 1, 3]
     assert ctx.cu.tolist() == [0, 130, 131, 134] and ctx.want.tolist() == [0, 129, 130]
     seq, tok0, rows = (t.tolist() for t in ctx.tiles[64])
-    assert (seq, tok0, rows) == ([0, 0, 0, 1, 2], [0, 64, 128, 130, 131], [64, 64, 2, 1, 3])
+    # in ascending order of the last position a tile sees (the kernels start from the list's end): sequence c's
+    # three tokens, a's first 64, b's token at position 70, a's next 64, a's last two
+    assert (seq, tok0, rows) == ([2, 0, 1, 0, 0], [131, 0, 130, 64, 128], [3, 64, 1, 64, 2])
     seq, tok0, rows = (t.tolist() for t in ctx.tiles[16])
-    assert seq == [0] * 9 + [1, 2] and tok0[:9] == list(range(0, 130, 16)) and rows[8:] == [2, 1, 3]
+    assert seq == [2] + [0] * 4 + [1] + [0] * 5 and tok0[1:5] == [0, 16, 32, 48] and rows == [3] + [16] * 4 + [1] + [16] * 4 + [2]
     assert all(p.shape == (3, 3) for p in ctx.pages)
     for g in range(2):
         for row, slot in enumerate((a, b, c)):
@@ -37,7 +39,7 @@ def test_packed_arrays_of_an_unequal_batch():
     cache.reserve([(a, 1), (b, 1), (c, 1)])
     d = BatchBuilder(rt, cache, tile_heights=(64,)).build([StepItem(s, [9], [0]) for s in (a, b, c)], pages_width=8)
     assert d.is_decode and d.pages[0].shape == (3, 8) and d.tok_pos.tolist() == [130, 71, 3]
-    assert [t.tolist() for t in d.tiles[64]] == [[0, 1, 2], [0, 1, 2], [1, 1, 1]]
+    assert [t.tolist() for t in d.tiles[64]] == [[2, 1, 0], [2, 1, 0], [1, 1, 1]]   # c holds the fewest positions
     # no mixer asked for tiles: none are made
     assert BatchBuilder(rt, cache).build([StepItem(a, [9], [0])]).tiles == {}
 
