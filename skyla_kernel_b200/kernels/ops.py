@@ -171,8 +171,8 @@ class KernelState:
     * ``error_flag``: one int32 that a kernel raises when a bounded wait ran out (codes 1 to 19),
       when the sampler found no token in a row of logits (31: every logit NaN) or when a token fed
       on the device lies outside the embedding table (32);
-    * counters with which the blocks of a launch find out which of them finishes last (the context
-      splits of decode attention): zero between launches;
+    * counters with which the blocks of a launch find out which of them finishes last (the pieces of a
+      sequence in decode attention): zero between launches;
     * the scratch and the flags of the prompt product's tiles that are cut along K.
 
     An engine owns one (``Runtime.kernel_state``) and hands it to every launch, so two engines on
