@@ -206,18 +206,19 @@ def e2e_decode(model, batch, prompt_len, steps, warmup, vocab):
     prompts = random_prompts(batch, prompt_len, vocab, 23 + batch)
     marks = {}
 
+    from skyla_kernel_b200.engine.batch import BatchBuilder
+
     def on_step(step, live):
         # step 0 is the prefill; the tokens of step s have reached the host when this runs
         if step == warmup:
-            marks["t0"] = time.perf_counter()
+            marks["t0"], marks["b0"] = time.perf_counter(), BatchBuilder.h2d_bytes
         if step == warmup + steps:
-            marks["t1"] = time.perf_counter()
+            marks["t1"], marks["b1"] = time.perf_counter(), BatchBuilder.h2d_bytes
 
     model.generate(prompts, max_new_tokens=warmup + steps + 1, stop_ids=[], max_batch=batch, on_step=on_step)
     dt = marks["t1"] - marks["t0"]
-    pages = -(-(prompt_len + warmup + steps) // model.page_size)
-    groups = len(model.engine.cache.groups)
-    h2d = 4 * (3 * batch + 3 * batch + (batch + 1) + batch + groups * batch * pages)
+    # what the step's builder copied: tokens, positions, rows, slots, page lists, the attention's plan
+    h2d = (marks["b1"] - marks["b0"]) // steps
     return {"value": batch * steps / dt, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4 * (batch + 1),
             "ms_per_step": dt / steps * 1e3, "warmup_steps": warmup}
 

@@ -130,6 +130,9 @@ class StepContext:
 class BatchBuilder:
     """Packs a step's arrays on the host and moves them with one copy."""
 
+    #: bytes that all builders of this process have copied to devices so far (for measurements)
+    h2d_bytes = 0
+
     def _feed_device_tokens(self, items, dev_tokens: torch.Tensor, ns) -> None:
         """Tokens that only exist on the device are copied into place there."""
         fed = [(b, it.device_token) for b, it in enumerate(items) if it.device_token is not None]
@@ -251,6 +254,7 @@ class BatchBuilder:
                 plan.fill(arr, np.asarray(starts), np.asarray(ns), cache.page_size)
                 r_plans[plan.key] = r
         dev[:total].copy_(host[:total], non_blocking=True)
+        BatchBuilder.h2d_bytes += 4 * total
         if self.rt.device.type == "cuda":
             self._copied = torch.cuda.Event()
             self._copied.record()
