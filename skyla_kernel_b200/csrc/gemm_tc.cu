@@ -14,9 +14,9 @@
 //             accumulating in TMEM, and commits each stage back to the loader;
 //   warps 2-5 read the accumulator with tcgen05.ld (lane = output feature,
 //             column = token) and write the epilogue.
-// Two kernels: gemm_tc_kernel (grid = feature tiles x token tiles, whole K in a block:
-// 65 to 128 tokens) and gemm_tc_rows_kernel (up to 64 tokens: every SM streams its
-// share of the weight; see there).  Every mbarrier wait is bounded: on a timeout the
+// Two kernels: gemm_tc_rows_kernel (up to 128 tokens: every SM streams its share of the
+// weight; see there) and gemm_tc_kernel (grid = feature tiles x token tiles, whole K in a
+// block: what the other does not take from 17 tokens on).  Every mbarrier wait is bounded: on a timeout the
 // CTA records an error code, drains what it started, frees its TMEM and returns.
 #include <cuda.h>
 
@@ -795,7 +795,7 @@ int launch_rows(const CUtensorMap& mw, const CUtensorMap& mx, const GemmArgs& a,
   // [source rank][owned token][128 features], and four tokens' room behind it: the owner reads four at a time
   int landing = splits > 1 ? ((BN + splits - 1) / splits * splits + 4) * BM * 4 : 0;
   if (kstack > 1) landing = kstack * BN * rows_per_block * 4;
-  if (a.ahead.xw != nullptr) landing += BN * rows_per_block * 4;  // the squares of the new rows
+  if (a.ahead.xw != nullptr && splits == 1) landing += BN * rows_per_block * 4;  // the squares of the new rows (a cluster's owners add them up in their warps)
   const int over_read = (BM - kstack * rows_per_block) * BK * 2;
   ra.landing_bytes = landing > over_read ? landing : over_read;
   const int fixed = 16 + 8 * (2 * kRowsMaxStages + 3) + 1024 + ra.landing_bytes;
@@ -826,14 +826,16 @@ int launch_rows(const CUtensorMap& mw, const CUtensorMap& mx, const GemmArgs& a,
                               (unsigned)splits, mw, mx, a, ra);
   } else if (kstack > 1) {
     if (MODE == kGluBf16) return fail(kBadArgument, "gemm_tc_rows: the gated product does not stack K blocks");
+    if (BN > 64) return fail(kBadArgument, "gemm_tc_rows: K blocks are stacked for token tiles up to 64");
+    constexpr int BS = BN > 64 ? 64 : BN;  // (no stacked kernel is built for the widest tile)
     static bool configured = false;
     if (!configured) {
-      cudaError_t e = cudaFuncSetAttribute(gemm_tc_rows_kernel<BN, M2, kStacked>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+      cudaError_t e = cudaFuncSetAttribute(gemm_tc_rows_kernel<BS, M2, kStacked>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                            kRowsSmemBytes);
       if (e != cudaSuccess) return fail(kLaunchFailed, "gemm_tc_rows: cannot reserve shared memory: %s", cudaGetErrorString(e));
       configured = true;
     }
-    launch_overlapped(gemm_tc_rows_kernel<BN, M2, kStacked>, grid, dim3(kThreads), (size_t)smem, stream, mw, mx, a, ra);
+    launch_overlapped(gemm_tc_rows_kernel<BS, M2, kStacked>, grid, dim3(kThreads), (size_t)smem, stream, mw, mx, a, ra);
   } else {
     static bool configured = false;
     if (!configured) {
@@ -946,8 +948,8 @@ extern "C" int skyla_gemm_tc_stages(int bn, int mode) {
 }
 
 // map_w: weight [rows, K] with boxes of 128 rows (a gated weight: the N gate rows, then the N up rows);
-// map_x: tokens [M, K] with boxes of bn rows.  Whole K in every block: the products of 65 to 128 tokens, and
-// the fewer tokens of weights whose K is too short (or whose width too odd) for the weight-streaming kernel.
+// map_x: tokens [M, K] with boxes of bn rows.  Whole K in every block: the products of 17 to 128 tokens of
+// weights whose K is too short (or whose width too odd) for the weight-streaming kernel.
 extern "C" int skyla_gemm_tc(const void* map_w, const void* map_x, void* y, int64_t ldy, int M, int N, int K, int bn,
                              int mode, int* error_flag, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return kOk;
@@ -984,7 +986,7 @@ extern "C" int skyla_gemm_tc_rows(const void* map_w, const void* map_x, void* y,
   if (K <= 0 || K % 8) return fail(kBadArgument, "gemm_tc_rows: K=%d must be a positive multiple of 8", K);
   if (rows_per_block < 8 || rows_per_block > BM || rows_per_block % 8)
     return fail(kBadArgument, "gemm_tc_rows: %d rows per block (a multiple of 8 up to 128)", rows_per_block);
-  if (M > bn || (bn != 16 && bn != 32 && bn != 64)) return fail(kBadArgument, "gemm_tc_rows: %d tokens in a tile of %d", M, bn);
+  if (M > bn || (bn != 16 && bn != 32 && bn != 64 && bn != 128)) return fail(kBadArgument, "gemm_tc_rows: %d tokens in a tile of %d", M, bn);
   if (mode != kStoreBf16 && mode != kStoreF32 && mode != kAccumF32 && mode != kGluBf16)
     return fail(kBadArgument, "gemm_tc_rows: epilogue %d is not offered", mode);
   if (kkb < 1 || kkb > 16 || (kkb > 1 && K % BK))
@@ -1017,7 +1019,8 @@ extern "C" int skyla_gemm_tc_rows(const void* map_w, const void* map_x, void* y,
   switch (bn) {                                                                                       \
     case 16: return launch_rows<16, MODE_>(mw, mx, a, rows_per_block, kkb, kstack, splits, stream);   \
     case 32: return launch_rows<32, MODE_>(mw, mx, a, rows_per_block, kkb, kstack, splits, stream);   \
-    default: return launch_rows<64, MODE_>(mw, mx, a, rows_per_block, kkb, kstack, splits, stream);   \
+    case 64: return launch_rows<64, MODE_>(mw, mx, a, rows_per_block, kkb, kstack, splits, stream);   \
+    default: return launch_rows<128, MODE_>(mw, mx, a, rows_per_block, kkb, kstack, splits, stream);  \
   }
   switch (mode) {
     case kStoreBf16: SKYLA_ROWS_BN(kStoreBf16)

@@ -91,7 +91,7 @@ def linear(tokens: int, n_out: int, n_in: int, mode: str, copies: int = 0, reps:
     flops = 2.0 * tokens * rows * n_in
     return {"kernel": "linear", "tokens": tokens, "n_out": n_out, "n_in": n_in, "mode": mode, "us": us,
             "weight_GBps": rows * n_in * 2 / us / 1e3, "TFLOPs": flops / us / 1e6,
-            "rows_kernel": lins[0].streams(tokens), "plan": lins[0].rows_plans[ops.token_tile(min(tokens, 64))]}
+            "rows_kernel": lins[0].streams(tokens), "plan": lins[0].rows_plans[ops.token_tile(min(tokens, ops.ROWS_MAX_TOKENS))]}
 
 
 def _paged(batch: int, context: int, nkv: int, hd: int):

@@ -329,7 +329,7 @@ def gemm_tc(x: torch.Tensor, w_map: TensorMap, n_out: int, y: torch.Tensor, mode
     return y
 
 
-ROWS_MAX_TOKENS = 64
+ROWS_MAX_TOKENS = 128
 ROWS_MAX_SPLITS = 8
 
 
@@ -356,7 +356,7 @@ def rows_cluster_room(device) -> dict:
 
 
 def rows_cluster_plan(n_out: int, n_in: int, bn: int, room: dict):
-    """The plan for 17 to 64 tokens of a product that is not gated: tiles of up to 128 rows whose K is
+    """The plan for 17 to 128 tokens of a product that is not gated: tiles of up to 128 rows whose K is
     cut into a cluster of 2 or 4 splits, chosen so that all blocks run at once (``room``: clusters of
     each size that fit) and a block moves as few bytes as possible (its share of the weight and of the
     tokens' rows, which every tile reads whole).  ``None`` where K is too short to cut."""
@@ -373,7 +373,8 @@ def rows_cluster_plan(n_out: int, n_in: int, bn: int, room: dict):
             continue
         cost = (rows + bn) * -(-n_kb // splits)
         if best_cost is None or cost < best_cost:
-            best, best_cost = (rows, splits, 2, 1), cost
+            # boxes of two K blocks; of one for the widest token tile, whose landing zone leaves the ring less room
+            best, best_cost = (rows, splits, 2 if bn <= 64 else 1, 1), cost
     return best
 
 
@@ -393,7 +394,7 @@ def rows_plan(n_out: int, n_in: int, gated: bool = False, bn: int = 16, n_sms: i
     if n_in % 64:
         return rows, 1, 1, 1
     if gated:
-        return rows, 1, 2, 1
+        return rows, 1, 2 if bn <= 64 else 1, 1        # (a stage holds both halves of the weight tile and the tokens)
     n_kb = n_in // 64
     kstack = max(1, min(128 // rows, 256 // bn, n_kb))
     group = kstack * rows * 128                     # bytes of weights that one MMA takes
@@ -406,7 +407,7 @@ def rows_plan(n_out: int, n_in: int, gated: bool = False, bn: int = 16, n_sms: i
 def gemm_tc_rows(x: torch.Tensor, w_map: TensorMap, rows: int, n_out: int, y: torch.Tensor, mode: int,
                  kkb: int = 1, splits: int = 1, kstack: int = 1, norm_ahead=None, scale_in=None,
                  state: Optional[KernelState] = None) -> torch.Tensor:
-    """y = x W^T for at most 64 tokens, streaming the weight: blocks of ``rows`` weight rows
+    """y = x W^T for at most 128 tokens, streaming the weight: blocks of ``rows`` weight rows
     (a multiple of 8 up to 128), K cut into ``splits`` that meet in a thread-block cluster.
 
     ``w_map`` has boxes of ``rows`` rows and ``kkb`` K blocks, of which one MMA takes ``kstack``

@@ -17,11 +17,12 @@ STORE, ACCUMULATE, GATED = ops.STORE, ops.ACCUMULATE, ops.GATED
 class Linear:
     kernel_modules = ("linear_plain", "gemm_tc", "gemm_prompt")
 
-    #: inputs from which a product of 65 to 128 tokens goes to the prompt kernel
+    #: inputs from which a product of 65 to 128 tokens that the weight-streaming kernel does not take goes to
+    #: the prompt kernel
     PROMPT_LONG_K = 8192
     #: the weight-streaming kernel takes over up to this many tokens: with tall tiles (gated products,
     #: products of many waves) or with tiles whose K is cut into a cluster of splits ...
-    ROWS_MAX_TOKENS = 64
+    ROWS_MAX_TOKENS = ops.ROWS_MAX_TOKENS
     #: ... but where its blocks each read every token's whole row (short tiles, K blocks stacked, no K
     #: split) only up to this many: beyond, the token rows outweigh the block's weights
     STACKED_MAX_TOKENS = 16
@@ -38,16 +39,16 @@ class Linear:
         self.tensor_cores = (not rt.full_precision and weight.dtype == torch.bfloat16 and self.n_in % 8 == 0
                              and weight.is_contiguous() and weight.data_ptr() % 16 == 0)
         #: token tile -> (rows per block, K splits, K blocks per box, K blocks per MMA) of the weight-streaming kernel
-        self.rows_plans = {bn: ops.rows_plan(self.n_out, self.n_in, gated, bn, rt.sm_count) for bn in (16, 32, 64)}
+        self.rows_plans = {bn: ops.rows_plan(self.n_out, self.n_in, gated, bn, rt.sm_count) for bn in (16, 32, 64, 128)}
         self.streams_wide = self.rows_plans[64][0] > 64  # tall tiles: gated products, many-wave products
         if self.tensor_cores and not self.streams_wide and not gated:
-            # 17 to 64 tokens: tiles whose K is cut into a cluster of splits, where K is long enough to cut
-            for bn in (32, 64):
+            # 17 to 128 tokens: tiles whose K is cut into a cluster of splits, where K is long enough to cut
+            for bn in (32, 64, 128):
                 plan = ops.rows_cluster_plan(self.n_out, self.n_in, bn, rt.clusters)
                 if plan is not None:
                     self.rows_plans[bn] = plan
         #: the most tokens that the weight-streaming kernel takes for this weight
-        self.rows_limit = (self.ROWS_MAX_TOKENS if self.streams_wide or all(self.rows_plans[bn][1] > 1 for bn in (32, 64))
+        self.rows_limit = (self.ROWS_MAX_TOKENS if self.streams_wide or all(self.rows_plans[bn][1] > 1 for bn in (32, 64, 128))
                            else self.STACKED_MAX_TOKENS)
 
     def weight_map(self):
@@ -63,10 +64,11 @@ class Linear:
         """Whether ``m`` tokens go to the prompt kernel (tokens are the tile's rows; given operands it takes)."""
         if not self.tensor_cores:
             return False
-        # from 65 tokens already where the reduction is long: the weight-major kernel cuts K for at most 64
-        # tokens, the prompt kernel for few tiles of any height (down product of the 8B shape at 96 and 128
-        # tokens: 41 against 60 us; the products with 4,096 inputs are even or lose)
-        return m >= ops.PROMPT_MIN_TOKENS or (m > self.ROWS_MAX_TOKENS and self.n_in >= self.PROMPT_LONG_K and not self.gated)
+        # from 65 tokens already where the reduction is long and the weight-streaming kernel does not take the
+        # product: the prompt kernel cuts few tiles along K (a down product of the 8B shape at 96 and 128
+        # tokens: 41 against 60 us for the tile kernel; the products with 4,096 inputs are even or lose)
+        return m >= ops.PROMPT_MIN_TOKENS or (m > 64 and not self.streams(m) and self.n_in >= self.PROMPT_LONG_K
+                                              and not self.gated)
 
     def takes_scale_in(self, m: int) -> bool:
         """Whether :meth:`forward` of ``m`` tokens accepts ``scale_in``."""

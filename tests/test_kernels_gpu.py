@@ -533,7 +533,10 @@ def test_prep_takes_32_bit_rows_and_writes_bfloat16():
     (11, 132, 8192, 16, 2, 8, 1), (33, 520, 704, 104, 2, 2, 1), (64, 392, 512, 40, 4, 2, 1), (64, 392, 520, 40, 1, 5, 1),
     (8, 4096, 12288, 112, 2, 4, 1), (3, 200, 1536, 72, 3, 4, 1),
     (8, 4096, 4096, 32, 8, 1, 4), (8, 6144, 4096, 48, 6, 1, 2), (16, 300, 1088, 24, 10, 1, 5), (1, 100, 704, 8, 16, 1, 16),
-    (33, 520, 704, 40, 6, 1, 3), (64, 392, 1536, 32, 4, 1, 4), (50, 200, 960, 56, 4, 1, 2), (8, 4096, 12288, 32, 8, 1, 4)])
+    (33, 520, 704, 40, 6, 1, 3), (64, 392, 1536, 32, 4, 1, 4), (50, 200, 960, 56, 4, 1, 2), (8, 4096, 12288, 32, 8, 1, 4),
+    # 65 to 128 tokens: the widest token tile, plain and with K cut into a cluster
+    (128, 4096, 4096, 128, 1, 4, 1), (100, 520, 1088, 104, 1, 3, 1), (65, 392, 512, 40, 1, 2, 1), (128, 264, 320, 88, 1, 1, 1),
+    (97, 4096, 12288, 128, 1, 4, 1), (127, 132, 1024, 16, 1, 8, 1)])
 def test_gemm_tc_rows_store_accumulate_gated(m, n, k, rows, kkb, splits, kstack):
     """Every epilogue of the weight-streaming product against float64, at tile heights that
     divide nothing (the last block's rows run past the matrix), K cut into clusters of
@@ -572,7 +575,8 @@ def test_gemm_tc_rows_store_accumulate_gated(m, n, k, rows, kkb, splits, kstack)
     (1, 128, 64, 128, 1, 1, 128, 128, 1, 1), (11, 1000, 1536, 56, 4, 2, 520, 88, 2, 1),
     # K cut into a cluster of splits on either side (kstack = -splits): 17 to 64 tokens are served so
     (64, 4096, 4096, 128, 2, -4, 6144, 96, 2, -2), (40, 520, 1088, 104, 1, -3, 200, 72, 2, -2), (17, 328, 704, 40, 2, -2, 136, 128, 1, -3),
-    (3, 264, 640, 24, 1, -4, 264, 24, 1, -5)])
+    (3, 264, 640, 24, 1, -4, 264, 24, 1, -5),
+    (128, 4096, 4096, 128, 1, -4, 6144, 96, 1, -2), (70, 520, 1088, 104, 1, -3, 200, 72, 1, -2), (99, 328, 704, 40, 1, 1, 136, 128, 1, 1)])
 def test_gemm_tc_rows_norm_ahead_then_scale_in(m, n, k, rows, kkb, kstack, n2, rows2, kkb2, kstack2):
     """x += a W^T leaves x * norm weight in bfloat16 and the blocks' shares of the rows' sums of
     squares; the next product takes those and must equal the product of rmsnorm(x)."""
@@ -637,10 +641,13 @@ def test_rows_plan_fills_the_sms():
 def test_gemm_tc_rows_refuses():
     ops = _ops()
     from skyla_kernel_b200.kernels import KernelError
-    x = _rand(70, 64, seed=1, dtype=torch.bfloat16)
+    x = _rand(130, 64, seed=1, dtype=torch.bfloat16)
     w = _rand(128, 64, seed=2, dtype=torch.bfloat16)
     with pytest.raises(KernelError):  # too many tokens
-        ops.gemm_tc_rows(x, ops.TensorMap(w, 128), 128, 128, torch.empty(70, 128, device=DEV), ops.TC_STORE_F32)
+        ops.gemm_tc_rows(x, ops.TensorMap(w, 128), 128, 128, torch.empty(130, 128, device=DEV), ops.TC_STORE_F32)
+    with pytest.raises(KernelError):  # K blocks are stacked for token tiles up to 64
+        ops.gemm_tc_rows(_rand(100, 256, seed=6, dtype=torch.bfloat16), ops.TensorMap(_rand(128, 256, seed=7, dtype=torch.bfloat16), 64, 2),
+                         64, 128, torch.empty(100, 128, device=DEV), ops.TC_STORE_F32, kkb=2, kstack=2)
     with pytest.raises(KernelError):  # a tile height that is no multiple of 8
         ops.gemm_tc_rows(x[:4], ops.TensorMap(w, 100), 100, 128, torch.empty(4, 128, device=DEV), ops.TC_STORE_F32)
     with pytest.raises(KernelError):  # an epilogue it does not have

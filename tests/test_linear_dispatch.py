@@ -24,24 +24,26 @@ def test_few_tokens_stream_the_weight_and_many_go_to_the_prompt_kernel():
         assert all(lin.streams(m) for m in (1, 8, 16))
         assert all(lin.prompts(m) and not lin.streams(m) for m in (129, 2048))
         assert all(lin.takes_scale_in(m) for m in (1, 16, 129, 4096))
-    # 17 to 64 tokens: the tall tiles of the gated product still stream; the others stream as tiles whose K is
+    # 17 to 128 tokens: the tall tiles of the gated product still stream; the others stream as tiles whose K is
     # cut into a cluster of splits, all of whose blocks run at once
-    assert gate_up.streams(17) and gate_up.streams(64) and not gate_up.streams(65)
+    assert gate_up.streams(17) and gate_up.streams(128) and not gate_up.streams(129)
     for lin in (qkv, o, down):
-        assert lin.streams(17) and lin.streams(64) and not lin.streams(65)
-        for bn in (32, 64):
+        assert lin.streams(17) and lin.streams(64) and lin.streams(128) and not lin.streams(129)
+        for bn in (32, 64, 128):
             rows, splits, kkb, kstack = lin.rows_plans[bn]
             assert splits in (2, 4) and kstack == 1 and rows % 8 == 0 and rows <= 128
             assert -(-lin.n_out // rows) <= {2: 72, 4: 33}[splits]
+            assert kkb == (1 if bn == 128 else 2)  # the widest tile's landing zone leaves room for boxes of one K block
         assert lin.rows_plans[16][1] == 1          # up to 16 tokens: short tiles, K blocks stacked, no split
     assert o.rows_plans[64][:2] == (128, 4) and down.rows_plans[64][:2] == (128, 4) and qkv.rows_plans[64][1] == 2
-    # a reduction too short to cut stays with the kernels it had
+    assert o.rows_plans[128][:2] == (128, 4) and gate_up.rows_plans[128][2:] == (1, 1)
+    # a reduction too short to cut stays with the kernels it had: the tile kernel up to 128 tokens, or, where
+    # the reduction is long, the prompt kernel from 65
     short = _lin(H, 512)
-    assert short.streams(16) and not short.streams(17)
-    # 65 to 128 tokens: only the product with the long reduction goes to the prompt kernel
-    assert down.prompts(65) and down.prompts(128)
-    assert not any(lin.prompts(m) for lin in (qkv, o, gate_up) for m in (65, 128))
-    assert not down.prompts(64)
+    assert short.streams(16) and not short.streams(17) and not short.prompts(128)
+    odd = _lin(4098, INTER)                        # outputs that are no multiple of four: no cluster plan
+    assert not odd.streams(17) and odd.prompts(65) and not odd.prompts(64)
+    assert not any(lin.prompts(m) for lin in (qkv, o, gate_up, down) for m in (65, 128))
 
 
 def test_the_32_bit_path_never_takes_a_tensor_core_kernel():
