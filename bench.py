@@ -8,8 +8,10 @@ per second on the device (`value`), the same through the Python entry point with
 host tokens in and out (`e2e`), a 2,048-token prefill, the decode step's HBM
 roofline fraction, and in `points` decode at batch 1 and 64 from 2,048-token prompts and
 at batch 1, 8 and 64 at the far end of the 4,096-token context, each with its own
-fraction of the roofline (`frac_*`).  The library runs on one GPU only; for
---gpus N > 1 it says so and exits with 2.
+fraction of the roofline (`frac_*`).  Every timed loop follows at least 40 untimed
+steps (more if --warmup asks for more): right after long prompts the GPU is still coming
+back from its power cap.  The library runs on one GPU only; for --gpus N > 1 it says so
+and exits with 2.
 """
 from __future__ import annotations
 
@@ -151,6 +153,7 @@ def device_decode(model, batch, prompt_len, steps, warmup, vocab, sampler):
     from skyla_kernel_b200.engine import StepItem
     from skyla_kernel_b200.kernels import ops
     eng = model.engine
+    warmup = max(warmup, MIN_WARMUP)
     prompts = random_prompts(batch, prompt_len, vocab, 11 + batch)
     slots = [eng.alloc_slot() for _ in range(batch)]
     toks = []
@@ -192,11 +195,12 @@ class _NoSampler:
 
 
 #: After a long prompt step the GPU runs at about half its clock for the next 80 to 100 ms (it has just been
-#: capped at its power limit and takes that long to come back: decode steps of the 8B shape take 5.2 ms
-#: there instead of 3.7).  `value` never sees this, because recording the decode graph idles the GPU right
-#: after the prompts; the end-to-end loop, whose graph exists by then, would be timed inside it.  Both
-#: numbers are meant as steady decoding, so the end-to-end loop warms up for at least this many steps.
-E2E_MIN_WARMUP = 40
+#: capped at its power limit and takes that long to come back: decode steps of the 8B shape take up to 5.2 ms
+#: there instead of 3.6, and at 4,094 positions 3.66 instead of 3.36 at batch 1).  Every decode number here
+#: is meant as steady decoding, so every timed loop, on the device and end to end, first runs at least this
+#: many untimed steps, however few --warmup asks for; `config.warmup_steps_run` says how many were run.
+MIN_WARMUP = 40
+E2E_MIN_WARMUP = MIN_WARMUP
 
 
 def e2e_decode(model, batch, prompt_len, steps, warmup, vocab):
@@ -357,7 +361,7 @@ def main() -> int:
     points[f"frac_b{args.batch}"] = main_run["GBps"] / hbm_gbs
     if not args.no_points:
         # the far end of the context: the timed steps end just under CONTEXT positions
-        long_prompt = max(64, CONTEXT - args.warmup - args.steps - 2)
+        long_prompt = max(64, CONTEXT - max(args.warmup, MIN_WARMUP) - args.steps - 2)
         for b in sorted(set(batches)):
             r = device_decode(model, b, long_prompt, args.steps, args.warmup, V, _NoSampler())
             points[f"decode_b{b}_ctx{CONTEXT}"] = r["tok_s"]
@@ -379,7 +383,7 @@ def main() -> int:
             "intermediate_size": cfg.intermediate_size, "vocab_size": cfg.vocab_size,
             "prompt_len": PROMPT_LEN, "context_at_end_of_timing": main_run["context_end"],
             "kv_cache": "bf16 paged, 64 positions per page", "l2": "inputs larger than L2 (weights read every step)",
-            "peaks": peak_kind,
+            "peaks": peak_kind, "warmup_steps_run": max(args.warmup, MIN_WARMUP),
         },
         "e2e": e2e, "gpu_launches": main_run["launches"], "clocks": main_run["clocks"],
         "prefill": prefill,
