@@ -130,3 +130,31 @@ def test_a_parts_plan_travels_with_the_step():
     cache.advance([(a, 1), (b, 1)])
     cache.reserve([(a, 3)])
     assert builder.build([StepItem(a, [1, 2, 3], [])]).plans == {}
+
+
+def test_any_part_can_ask_for_a_plan():
+    """The mechanism knows nothing of attention: a plan of a test's own, for every kind of step."""
+    from skyla_kernel_b200.parts.base import StepPlan
+
+    class EndsOfSequences(StepPlan):
+        key = ("toy", "ends")
+
+        def size(self, n_seqs, pages_width, decode):
+            return n_seqs + 1
+
+        def fill(self, out, starts, ns, page_size):
+            out[:-1] = starts + ns
+            out[-1] = page_size
+
+    rt = Runtime(torch.device("cpu"), "float32", n_sms=2)
+    cache = SequenceCache([KVNeed(1, 16)], [None], 64 * 8, 4, torch.float32, None)
+    a, b = cache.alloc_slot(), cache.alloc_slot()
+    cache.reserve([(a, 70), (b, 3)])
+    builder = BatchBuilder(rt, cache, tile_heights=(16,), plans=(EndsOfSequences(), EndsOfSequences()))
+    ctx = builder.build([StepItem(a, list(range(70)), [69]), StepItem(b, [1, 2, 3], [])])
+    assert ctx.plans[("toy", "ends")].tolist() == [70, 3, 64] and ctx.plans[("toy", "ends")].data_ptr() % 16 == 0
+    assert ctx.tok_pos.tolist() == list(range(70)) + [0, 1, 2] and ctx.want.tolist() == [69]
+    cache.advance([(a, 70), (b, 3)])
+    cache.reserve([(a, 1), (b, 1)])
+    ctx = builder.build([StepItem(a, [5], [0]), StepItem(b, [6], [0])], pages_width=8)
+    assert ctx.plans[("toy", "ends")].tolist() == [71, 4, 64]
