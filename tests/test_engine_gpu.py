@@ -128,6 +128,41 @@ def test_a_batch_of_twenty_decodes(folders, name, dtype):
     eng.cache.check()
 
 
+def test_a_hundred_sequences_decode_on_the_widest_token_tile(folders):
+    """65 to 128 tokens a step go to the weight-streaming product with its widest token tile (K cut into
+    a cluster, the next norm's input prepared on the way) and to a q/k/v preparation of their own: 100
+    sequences of the wide configuration decode together."""
+    from skyla_kernel_b200.engine import StepItem
+    from skyla_kernel_b200.kernels import ops
+    name, dtype = "D", "bfloat16"
+    V = TINY[name][0]["vocab_size"]
+    eng = _engine(folders[name], dtype, max_tokens=100 * 128)
+    mixer = eng.model.blocks[0].mixer
+    assert mixer.qkv.streams(100) and mixer.qkv.rows_plans[128][1] > 1
+    assert not mixer.out.streams(100)      # 512 inputs are too few to cut: this one stays on the tile kernel
+    lens = [2 + (11 * i) % 60 for i in range(100)]
+    seqs = [random_tokens(p + 3, V, 900 + i) for i, p in enumerate(lens)]
+    slots = [eng.alloc_slot() for _ in seqs]
+    got = [[] for _ in seqs]
+    out = eng.step([StepItem(slots[j], seqs[j][:lens[j]], [lens[j] - 1]) for j in range(100)])
+    for j in range(100):
+        got[j].append(out[j:j + 1])
+    before = ops.LAUNCHES
+    for t in range(3):
+        out = eng.step([StepItem(slots[j], [seqs[j][lens[j] + t]], [0]) for j in range(100)])
+        for j in range(100):
+            got[j].append(out[j:j + 1])
+    assert ops.LAUNCHES > before
+    cfg, w = plain.read_folder(folders[name])
+    for j in range(0, 100, 9):
+        ref = plain.forward(cfg, w, seqs[j])[lens[j] - 1:]
+        assert_close(torch.cat(got[j]), ref, dtype, f"request {j} of 100")
+    for sl in slots:
+        eng.free_slot(sl)
+    eng.cache.check()
+    eng.check_errors()
+
+
 def test_more_sequences_than_attention_blocks(folders):
     """With more (sequence, key/value head) pairs than the decode attention has blocks, the step's pages are cut
     into even runs and a block reads the end of one pair and the beginning of the next: 120 sequences of
