@@ -16,8 +16,17 @@ __global__ void __launch_bounds__(256) bandwidth_kernel(const uint4* __restrict_
                                                         uint32_t* __restrict__ sink) {
   uint4 acc = make_uint4(0, 0, 0, 0);
   const size_t stride = (size_t)gridDim.x * blockDim.x;
-  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_vec; i += stride) {
-    const uint4 v = src[i];
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  // eight loads of a thread are in flight at a time: the memory's latency is what a stream has to cover
+  for (; i + 7 * stride < n_vec; i += 8 * stride) {
+    uint4 v[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) v[k] = __ldcs(src + i + k * stride);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) { acc.x ^= v[k].x; acc.y ^= v[k].y; acc.z ^= v[k].z; acc.w ^= v[k].w; }
+  }
+  for (; i < n_vec; i += stride) {
+    const uint4 v = __ldcs(src + i);
     acc.x ^= v.x; acc.y ^= v.y; acc.z ^= v.z; acc.w ^= v.w;
   }
   const uint32_t f = acc.x ^ acc.y ^ acc.z ^ acc.w;
