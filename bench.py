@@ -60,6 +60,7 @@ class ClockSampler:
         self.index, self.period = index, period_s
         self.proc = self.thread = None
         self.samples, self.max_mhz, self.reasons = [], None, set()
+        self.mem_samples, self.power_samples = [], []
         self._stop = threading.Event()
 
     def _nvml_loop(self, nvml, handle):
@@ -70,6 +71,8 @@ class ClockSampler:
         while not self._stop.is_set():
             try:
                 self.samples.append(float(nvml.nvmlDeviceGetClockInfo(handle, nvml.NVML_CLOCK_SM)))
+                self.mem_samples.append(float(nvml.nvmlDeviceGetClockInfo(handle, nvml.NVML_CLOCK_MEM)))
+                self.power_samples.append(nvml.nvmlDeviceGetPowerUsage(handle) / 1000.0)
                 bits = nvml.nvmlDeviceGetCurrentClocksThrottleReasons(handle)
                 self.reasons.update(n for n, m in masks.items() if bits & m)
             except Exception:
@@ -99,8 +102,13 @@ class ClockSampler:
             self._stop.set()
             self.thread.join(timeout=2)
             sm = self.samples
-            return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": self.max_mhz,
-                    "reasons": sorted(self.reasons), "samples": len(sm), "how": "nvml"}
+            out = {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": self.max_mhz,
+                   "reasons": sorted(self.reasons), "samples": len(sm), "how": "nvml"}
+            if self.mem_samples:
+                out["mem_mhz"] = statistics.median(self.mem_samples)
+            if self.power_samples:
+                out["power_w"] = round(statistics.median(self.power_samples), 1)
+            return out
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no clock reading available"]}
         self.proc.terminate()
